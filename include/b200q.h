@@ -1,0 +1,193 @@
+/*
+ * b200q — C ABI of the B200 (sm_100a) backend for tpu-mlir's quantized-inference hot path.
+ *
+ * Two faces:
+ *   (1) the operator face mirrors the interpreter's per-op interface
+ *       (init / inference / deinit over an InferenceParameter of host float buffers,
+ *       include/tpu_mlir/Interfaces/InferenceInterface.td:16-58, InferenceInterface.h:15-19):
+ *       inputs[i] / outputs[i] are HOST float* in operand order, integer tensors stored as
+ *       integral floats exactly as ModuleInterpreter keeps them; attributes that the reference
+ *       reads from the MLIR op arrive in a plain descriptor struct.
+ *   (2) the device face takes native-dtype DEVICE pointers and a CUDA stream and is asynchronous;
+ *       it is what a GPU-resident executor (the role of bindings/pymlir/pycuda.cpp) calls.
+ *
+ * All functions return B200Q_OK (0) or a negative b200q_status; b200q_last_error() gives the
+ * message of the calling thread's last failure.  Nothing here aborts, exits or falls back to the CPU.
+ * Paths in the comments are paths inside the tpu-mlir source tree.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  B200Q_OK = 0,
+  B200Q_ERR_INVALID = -1,     /* bad argument / descriptor */
+  B200Q_ERR_UNSUPPORTED = -2, /* valid in the reference but not implemented by this backend */
+  B200Q_ERR_CUDA = -3,        /* a CUDA call failed */
+  B200Q_ERR_NO_DEVICE = -4,   /* no sm_100 device */
+  B200Q_ERR_TIMEOUT = -5,     /* a bounded device-side wait ran out */
+  B200Q_ERR_NOMEM = -6
+} b200q_status;
+
+/* tpu::RequantMode, include/tpu_mlir/Dialect/Tpu/IR/TpuOps.td:160-172 (same numbering) */
+typedef enum {
+  B200Q_QM_TFLITE_LSHIFT = 0,
+  B200Q_QM_TFLITE = 1,
+  B200Q_QM_MULTIPLIER_SHIFT = 2,
+  B200Q_QM_ONLY_SHIFT = 3,
+  B200Q_QM_QDM = 4,
+  B200Q_QM_ONLY_SCALE = 5
+} b200q_requant_mode;
+
+/* RoundingMode, include/tpu_mlir/Support/MathUtils.h:28-42 (same numbering) */
+typedef enum {
+  B200Q_ROUND_HALF_AWAY_FROM_ZERO = 0,
+  B200Q_ROUND_HALF_UP = 1,
+  B200Q_ROUND_HALF_DOWN = 2,
+  B200Q_ROUND_HALF_TO_EVEN = 3,
+  B200Q_ROUND_HALF_TO_ODD = 4,
+  B200Q_ROUND_HALF_TOWARDS_ZERO = 5,
+  B200Q_ROUND_TOWARDS_ZERO = 6,
+  B200Q_ROUND_AWAY_FROM_ZERO = 7,
+  B200Q_ROUND_UP = 8,
+  B200Q_ROUND_DOWN = 9
+} b200q_round_mode;
+
+/* storage type of a tensor on the device face (module::getStorageType in the reference) */
+typedef enum {
+  B200Q_DT_I8 = 0,
+  B200Q_DT_U8 = 1,
+  B200Q_DT_I16 = 2,
+  B200Q_DT_U16 = 3,
+  B200Q_DT_I32 = 4,
+  B200Q_DT_F32 = 5,
+  B200Q_DT_BF16 = 6,
+  B200Q_DT_F16 = 7
+} b200q_dtype;
+
+/* The arithmetic form a (RequantMode, chip family, op) triple resolves to on the device face;
+ * lib/Support/MathUtils.cpp:538-562.  `shift` below is the per-form shift operand. */
+typedef enum {
+  B200Q_RQ_NONE = 0,                 /* raw int32 accumulator out */
+  B200Q_RQ_MULTIPLIER_SHIFT = 1,     /* RightShiftRound(acc*M, shift, round): shift > 0 right, < 0 left */
+  B200Q_RQ_QDM = 2,                  /* MultiplyByQuantizedMultiplier(acc, M, shift, round): shift > 0 LEFT, < 0 right */
+  B200Q_RQ_MULTIPLIER_SHIFT_F32 = 3, /* CV18xx MultiplierShift: to_int((float)acc*M / (1<<shift), round) */
+  B200Q_RQ_ONLY_SHIFT = 4,           /* RightShiftRound(acc, shift, round) */
+  B200Q_RQ_ONLY_SCALE = 5            /* (int32)roundf(acc * scale) */
+} b200q_rq_dialect;
+
+typedef enum {
+  B200Q_RELU_NONE = 0,
+  B200Q_RELU_BEFORE_REQUANT = 1, /* MatMul order: max(acc+bias, 0) then requant (MatMul.cpp:599-603) */
+  B200Q_RELU_AFTER_REQUANT = 2   /* Conv2D order: max(requant+zp, zp) (Conv2D.cpp:334-336) */
+} b200q_relu_order;
+
+/* Epilogue of the device face: out = saturate(relu(requant(acc + bias[c]) + out_zp)).
+ * All pointers are DEVICE pointers. */
+typedef struct {
+  int32_t dialect;           /* b200q_rq_dialect */
+  int32_t round_mode;        /* b200q_round_mode */
+  int32_t per_channel;       /* 1: multiplier[c], shift[c]; 0: multiplier[0], shift[0] */
+  int32_t out_zp;
+  int32_t relu;              /* b200q_relu_order */
+  int32_t out_dtype;         /* I8 / U8 / I16 / U16 / I32 */
+  float scale;               /* B200Q_RQ_ONLY_SCALE */
+  const int32_t *bias;       /* [C] or NULL */
+  const int32_t *multiplier; /* [C] or [1] */
+  const int32_t *shift;      /* [C] or [1] */
+} b200q_epilogue;
+
+/* ------------------------------------------------------------------ library */
+const char *b200q_version(void);
+const char *b200q_last_error(void);
+/* number of sm_100 devices visible; 0 is not an error */
+int b200q_device_count(void);
+
+/* ------------------------------------------------------------------ tpu.MatMul (INT8)
+ * Descriptor = the attributes tpu::MatMulOp::parseParam derives (matmul_attr_t,
+ * include/tpu_mlir/Support/AttrStruct.h:82-101) plus the requant attributes of the op
+ * (include/tpu_mlir/Dialect/Tpu/IR/TpuOps.td:4592-4616). */
+typedef struct {
+  int64_t batch, M, K, N;
+  int32_t with_bias, do_relu;
+  int32_t right_transpose;   /* right operand stored [N,K] instead of [K,N] */
+  int32_t left_transpose, output_transpose, hdim_is_batch; /* must be 0: B200Q_ERR_UNSUPPORTED otherwise */
+  int32_t right_batched;     /* right operand has the batch dimension (activation x activation) */
+  int32_t right_is_weight;   /* constant right operand: uploaded once per (handle, weight_version) */
+  int32_t weight_version;    /* bump after rewriting the weight buffers in place */
+  int32_t input_zp, right_zp;
+  int32_t input_dtype, right_dtype, out_dtype; /* b200q_dtype: I8/U8 (out also I16/U16/I32) */
+  int32_t quant_mode;        /* b200q_requant_mode */
+  int32_t is_cv18xx;         /* module::isCV18xx(): per-batch requant, half-away rounding, no zero point */
+  int32_t fuse_rq;           /* per-channel multipliers arrive float-stored in operand 3 (MatMul.cpp:709-716) */
+  int32_t out_zp;
+  int32_t n_quant;           /* entries of multipliers / rshifts */
+  const int64_t *multipliers;
+  const int64_t *rshifts;
+  double out_scale;          /* B200Q_QM_ONLY_SCALE */
+  int32_t algo;              /* 0 = auto, 1 = tensor cores only, 2 = CUDA cores only */
+} b200q_matmul_desc;
+
+/* Operator face of tpu::MatMulOp::{init,inference,deinit}
+ * (lib/Dialect/Tpu/Interfaces/Common/MatMul.cpp:400-440,:440-733).  inputs = {input, right, bias, multi,
+ * buffer} as HOST float*, NULL for absent operands (ModuleInterpreter.cpp:456-458); outputs[0] HOST float*.
+ * Like the reference, inference accepts *handle == NULL (it then sets up and tears down its own state). */
+int b200q_matmul_init(const b200q_matmul_desc *desc, void **handle);
+int b200q_matmul_inference(const b200q_matmul_desc *desc, float *const *inputs, int n_inputs,
+                           float *const *outputs, int n_outputs, void **handle);
+void b200q_matmul_deinit(void **handle);
+
+/* Device face: out[M,N] = epilogue(A[M,K] * B^T) with B given K-major as [N,K]; native dtypes, device
+ * pointers, asynchronous on `stream` (a cudaStream_t).  a_dtype / b_dtype are B200Q_DT_I8 or _U8.
+ * `status` is an optional device int that receives a non-zero code if a bounded wait in the kernel ran out.
+ * Replaces MatMul::run (lib/Support/Dnnl/MatMul.cpp:223-241) + the requant loop (MatMul.cpp:636-728). */
+int b200q_gemm_i8_dev(const void *a, int a_dtype, const void *b_nk, int b_dtype, int64_t M, int64_t N, int64_t K,
+                      const b200q_epilogue *epilogue, void *out, int32_t *status, int algo, void *stream);
+
+/* ------------------------------------------------------------------ tpu.Conv2D (INT8)
+ * conv_attr_t (include/tpu_mlir/Support/AttrStruct.h:15-43) + the requant attributes of tpu.Conv2D
+ * (TpuOps.td:1557-1595).  NCHW activations, OIHW filter, like module::getNCHW (Conv2D.cpp:19-72). */
+typedef struct {
+  int64_t n, ic, ih, iw, oc, kh, kw, sh, sw, dh, dw, pht, phb, pwl, pwr, groups;
+  int32_t pad_value;         /* input zero point used for padding */
+  int32_t with_bias, do_relu;
+  int32_t input_dtype, out_dtype;
+  int32_t quant_mode;        /* b200q_requant_mode */
+  int32_t is_cv18xx;
+  int32_t out_zp;
+  int32_t n_quant;           /* oc (per-axis) or 1 */
+  const int64_t *multipliers; /* I64 array attribute `multiplier` (Conv2D.cpp:299-301) */
+  const int64_t *rshifts;     /* I64 array attribute `rshift` */
+  int32_t weight_version;
+  int32_t algo;              /* 0 = auto, 1 = tensor cores only, 2 = CUDA cores only */
+} b200q_conv2d_desc;
+
+/* Operator face of tpu::Conv2DOp::{init,inference,deinit} (Conv2D.cpp:74-86,:88-344).
+ * inputs = {input, filter, bias} HOST float*; outputs[0] HOST float*.  init uploads and repacks the filter
+ * and bias; inference requires a handle (Conv2D.cpp:89-91 fails without one).  Unlike the reference the
+ * bias buffer is NOT zeroed in place (Conv2D.cpp:94-99 mutates its input). */
+int b200q_conv2d_init(const b200q_conv2d_desc *desc, float *const *inputs, int n_inputs, void **handle);
+int b200q_conv2d_inference(const b200q_conv2d_desc *desc, float *const *inputs, int n_inputs,
+                           float *const *outputs, int n_outputs, void **handle);
+void b200q_conv2d_deinit(void **handle);
+
+/* Device face: prepare once (filter s8 OIHW and bias s32 are DEVICE pointers and are repacked into the
+ * handle), then run on native NCHW device tensors, asynchronous on `stream`.  b200q_conv2d_dev_status
+ * synchronises the stream and reports a kernel-side timeout, if any.
+ * Replaces Conv::run (lib/Support/Dnnl/Conv.cpp:234-253) + the requant loop (Conv2D.cpp:295-341). */
+int b200q_conv2d_dev_create(const b200q_conv2d_desc *desc, const void *filter_oihw_s8, const int32_t *bias_s32,
+                            void **handle);
+int b200q_conv2d_dev_run(void *handle, const void *x_nchw, void *y_nchw, void *stream);
+int b200q_conv2d_dev_status(void *handle, void *stream);
+void b200q_conv2d_dev_destroy(void **handle);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -1,0 +1,131 @@
+"""INT8 Conv2D parity on the GPU against the CPU oracle (bit exact), through both faces of the C ABI."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import tpu_mlir_b200._lib as L
+from tpu_mlir_b200 import synth
+from tpu_mlir_b200.ops import Conv2DOp, InferenceParameter
+
+from gpu_util import dev, dt_of, empty_dev, ptr
+
+pytestmark = pytest.mark.gpu
+
+
+def f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def oracle_conv(c, *, stride=(1, 1), pads=(1, 1, 1, 1), dilation=(1, 1), groups=1, qmode, is_cv18xx=False,
+                do_relu=True, out_dt=oracle.DT_I8, out_zp=0, per_axis=True, rshift_sign=1):
+    mult = c["mult"] if per_axis else c["mult"][:1]
+    rshift = (c["rshift"] if per_axis else c["rshift"][:1]) * rshift_sign
+    # oracle pads are (top, bottom, left, right); the op attribute is (top, left, bottom, right)
+    out, viol = oracle.conv2d_int8(c["x"], c["w"], c["bias"], stride=stride, pads=(pads[0], pads[2], pads[1], pads[3]),
+                                   dilation=dilation, groups=groups, do_relu=do_relu, qmode=qmode,
+                                   is_cv18xx=is_cv18xx, mult=mult, rshift=rshift, out_zp=out_zp, out_dt=out_dt,
+                                   return_violations=True)
+    assert viol == 0, "inputs leave the domain where the reference's fp32 accumulation is exact"
+    return out, mult, rshift
+
+
+def run_operator_face(c, *, strides=(1, 1), pads=(1, 1, 1, 1), dilations=(1, 1), group=1, qmode, is_cv18xx=False,
+                      do_relu=True, out_dt=L.DT_I8, out_zp=0, mult, rshift, algo=L.ALGO_AUTO):
+    x, w = c["x"], c["w"]
+    op = Conv2DOp(input_shape=x.shape, oc=w.shape[0], kernel_shape=w.shape[2:], strides=strides, dilations=dilations,
+                  pads=pads, group=group, do_relu=do_relu, input_dtype=dt_of(x), out_dtype=out_dt, quant_mode=qmode,
+                  is_cv18xx=is_cv18xx, out_zp=out_zp, multiplier=mult, rshift=rshift, algo=algo)
+    out = np.full(op.out_shape, -777, np.float32)
+    bias_buf = f32(c["bias"])
+    p = InferenceParameter(inputs=[f32(x), f32(w), bias_buf], outputs=[out])
+    op.init(p)
+    op.inference(p)
+    first = out.copy()
+    out[...] = -777
+    op.inference(p)     # resident weights, reused bordered buffer
+    op.deinit(p)
+    assert np.array_equal(first, out)
+    assert np.array_equal(bias_buf, f32(c["bias"])), "the caller's bias buffer must not be modified"
+    return out
+
+
+@pytest.mark.parametrize("algo", [L.ALGO_TENSOR_CORE, L.ALGO_CUDA_CORE])
+def test_conv3x3_qdm_small(algo):
+    """Shape family of BASELINE config 1 at a size the oracle finishes quickly: 3x3, stride 1, pad 1, ReLU, QDM."""
+    c = synth.conv2d_int8(seed=21, N=3, C=128, H=13, W=11, OC=72)
+    # BASELINE's form RSR(RSR(acc*M,31), rshift, half away) is QDM with the CV18xx shift-sign convention
+    want, mult, rshift = oracle_conv(c, qmode=oracle.QM_QDM, is_cv18xx=True)
+    got = run_operator_face(c, qmode=L.QM_QDM, is_cv18xx=True, mult=mult, rshift=rshift, algo=algo)
+    assert np.array_equal(got, want.astype(np.float32))
+
+
+@pytest.mark.parametrize("case", [
+    dict(N=2, C=256, H=9, W=9, OC=256, k=3, pads=(1, 1, 1, 1)),            # two K blocks per tap, full N tile
+    dict(N=1, C=128, H=8, W=20, OC=40, k=3, pads=(0, 0, 0, 0)),            # "valid" convolution
+    dict(N=2, C=128, H=7, W=7, OC=130, k=3, pads=(1, 0, 0, 1)),            # asymmetric pads
+    dict(N=2, C=64, H=14, W=14, OC=256, k=1, pads=(0, 0, 0, 0)),           # 1x1, K < 128
+    dict(N=1, C=48, H=5, W=6, OC=24, k=1, pads=(0, 0, 0, 0)),              # 1x1, K multiple of 16 only
+    dict(N=1, C=128, H=6, W=6, OC=8, k=5, pads=(2, 2, 2, 2)),              # 5x5
+])
+def test_conv_tensor_core_shapes(case):
+    c = synth.conv2d_int8(seed=case["C"] + case["OC"], N=case["N"], C=case["C"], H=case["H"], W=case["W"],
+                          OC=case["OC"], KH=case["k"], KW=case["k"], unsigned_input=True)
+    c["w"] = np.clip(c["w"] // 2, -127, 127).astype(np.int8)   # u8 activations: keep |acc| < 2^24
+    c["mult"] = np.random.default_rng(1).integers(5000, 30000, size=case["OC"])
+    c["rshift"] = np.random.default_rng(2).integers(18, 26, size=case["OC"])
+    want, mult, rshift = oracle_conv(c, pads=case["pads"], qmode=oracle.QM_MULTIPLIER_SHIFT, out_dt=oracle.DT_U8)
+    got = run_operator_face(c, pads=case["pads"], qmode=L.QM_MULTIPLIER_SHIFT, out_dt=L.DT_U8, mult=mult, rshift=rshift,
+                            algo=L.ALGO_TENSOR_CORE)
+    assert np.array_equal(got, want.astype(np.float32))
+
+
+@pytest.mark.parametrize("case", [
+    dict(N=2, C=3, H=32, W=32, OC=16, k=7, stride=(2, 2), pads=(3, 3, 3, 3), group=1, dil=(1, 1)),   # ResNet stem
+    dict(N=1, C=16, H=12, W=12, OC=16, k=3, stride=(1, 1), pads=(1, 1, 1, 1), group=16, dil=(1, 1)),  # depthwise
+    dict(N=1, C=8, H=15, W=15, OC=12, k=3, stride=(2, 1), pads=(2, 2, 2, 2), group=2, dil=(2, 2)),    # dilation, groups
+])
+def test_conv_cuda_core_shapes(case):
+    rng = np.random.default_rng(77)
+    x = rng.integers(-128, 128, size=(case["N"], case["C"], case["H"], case["W"]), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(case["OC"], case["C"] // case["group"], case["k"], case["k"]), dtype=np.int8)
+    c = dict(x=x, w=w, bias=rng.integers(-500, 500, size=case["OC"], dtype=np.int32),
+             mult=rng.integers(100, 20000, size=case["OC"]), rshift=rng.integers(10, 20, size=case["OC"]))
+    for qmode, per_axis in ((oracle.QM_MULTIPLIER_SHIFT, True), (oracle.QM_ONLY_SHIFT, False), (oracle.QM_TFLITE, True)):
+        sign = -1 if qmode == oracle.QM_TFLITE else 1    # BM168x TFLite: positive shift attribute = left shift
+        want, mult, rshift = oracle_conv(c, stride=case["stride"], pads=case["pads"], dilation=case["dil"],
+                                         groups=case["group"], qmode=qmode, per_axis=per_axis, out_zp=-4,
+                                         do_relu=(qmode != oracle.QM_ONLY_SHIFT), rshift_sign=sign)
+        got = run_operator_face(c, strides=case["stride"], pads=case["pads"], dilations=case["dil"], group=case["group"],
+                                qmode=qmode, mult=mult, rshift=rshift, out_zp=-4,
+                                do_relu=(qmode != oracle.QM_ONLY_SHIFT))
+        assert np.array_equal(got, want.astype(np.float32)), (case, qmode)
+
+
+def test_conv_device_face_matches_operator_face():
+    c = synth.conv2d_int8(seed=8, N=4, C=128, H=10, W=10, OC=64)
+    want, mult, rshift = oracle_conv(c, qmode=oracle.QM_QDM, is_cv18xx=True)
+    d = Conv2DOp(input_shape=c["x"].shape, oc=64, kernel_shape=(3, 3), pads=(1, 1, 1, 1), do_relu=True,
+                 quant_mode=L.QM_QDM, is_cv18xx=True, multiplier=mult, rshift=rshift).desc
+    w_d, b_d, x_d = dev(c["w"]), dev(c["bias"]), dev(c["x"])
+    y_d = empty_dev(want.shape, L.DT_I8)
+    h = C.c_void_p()
+    lib = L.lib()
+    L.check(lib.b200q_conv2d_dev_create(C.byref(d), ptr(w_d), ptr(b_d), C.byref(h)))
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            L.check(lib.b200q_conv2d_dev_run(h, ptr(x_d), ptr(y_d), C.c_void_p(stream.cuda_stream)))
+    L.check(lib.b200q_conv2d_dev_status(h, C.c_void_p(stream.cuda_stream)))
+    lib.b200q_conv2d_dev_destroy(C.byref(h))
+    assert np.array_equal(y_d.cpu().numpy(), want)
+
+
+def test_config1_full_size():
+    """BASELINE config 1 at full size: N=32, C=256, 56x56, OC=256, 3x3, stride 1, pad 1, fused ReLU, QDM requant."""
+    c = synth.conv2d_int8(seed=1)
+    want, mult, rshift = oracle_conv(c, qmode=oracle.QM_QDM, is_cv18xx=True)
+    got = run_operator_face(c, qmode=L.QM_QDM, is_cv18xx=True, mult=mult, rshift=rshift, algo=L.ALGO_TENSOR_CORE)
+    assert np.array_equal(got, want.astype(np.float32))

@@ -1,0 +1,546 @@
+// C ABI for tpu.MatMul and tpu.Conv2D (INT8): the operator face over host float buffers and the device
+// face over native device tensors.  The host side here mirrors what tpu::MatMulOp / tpu::Conv2DOp do around
+// their oneDNN calls: resolve the op attributes to one requantisation form, keep the weights resident, pick
+// the kernel, and convert between the interpreter's float storage and native integers.
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "devbuf.h"
+#include "igemm.h"
+#include "internal.h"
+#include "layout.h"
+
+namespace b200q {
+namespace {
+
+inline bool is_q8(int dt) { return dt == B200Q_DT_I8 || dt == B200Q_DT_U8; }
+inline size_t dtype_size(int dt) {
+  switch (dt) {
+    case B200Q_DT_I8:
+    case B200Q_DT_U8: return 1;
+    case B200Q_DT_I16:
+    case B200Q_DT_U16:
+    case B200Q_DT_BF16:
+    case B200Q_DT_F16: return 2;
+    default: return 4;
+  }
+}
+
+int check_int32(const int64_t* v, int n, const char* what) {
+  for (int i = 0; i < n; ++i)
+    if (v[i] > 2147483647ll || v[i] < -2147483648ll)
+      return set_error(B200Q_ERR_UNSUPPORTED, "%s[%d] = %lld does not fit int32", what, i, (long long)v[i]);
+  return B200Q_OK;
+}
+
+// Host description of a resolved requantisation; uploaded into an Epilogue with device arrays.
+struct ResolvedRequant {
+  int dialect = B200Q_RQ_NONE, round_mode = B200Q_ROUND_HALF_UP, per_channel = 0, out_zp = 0, relu = B200Q_RELU_NONE;
+  int out_dtype = B200Q_DT_I8;
+  float scale = 0.f;
+  std::vector<int32_t> multiplier, shift;
+};
+
+int make_epilogue(const ResolvedRequant& r, const int32_t* d_bias, DevBuf& d_mult, DevBuf& d_shift, cudaStream_t s,
+                  Epilogue* e) {
+  e->dialect = r.dialect;
+  e->round_mode = r.round_mode;
+  e->per_channel = r.per_channel;
+  e->out_zp = r.out_zp;
+  e->relu = r.relu;
+  e->out_dtype = r.out_dtype;
+  e->scale = r.scale;
+  e->bias = d_bias;
+  e->multiplier = nullptr;
+  e->shift = nullptr;
+  if (!r.multiplier.empty()) {
+    B200Q_TRY(d_mult.upload(r.multiplier.data(), r.multiplier.size() * 4, s));
+    e->multiplier = d_mult.as<int32_t>();
+  }
+  if (!r.shift.empty()) {
+    B200Q_TRY(d_shift.upload(r.shift.data(), r.shift.size() * 4, s));
+    e->shift = d_shift.as<int32_t>();
+  }
+  return B200Q_OK;
+}
+
+int read_status(DevBuf& d_status, cudaStream_t s, const char* what) {
+  int h = 0;
+  CUDA_TRY(cudaMemcpyAsync(&h, d_status.p, 4, cudaMemcpyDeviceToHost, s));
+  CUDA_TRY(cudaStreamSynchronize(s));
+  if (h != 0) {
+    cudaMemsetAsync(d_status.p, 0, 4, s);
+    return set_error(B200Q_ERR_TIMEOUT, "%s: a bounded wait inside the kernel ran out (wait site %d)", what, h);
+  }
+  return B200Q_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- MatMul
+// Which requantisation a tpu.MatMul resolves to: MatMul.cpp:636-728 (one entry per batch on CV18xx).
+int resolve_matmul(const b200q_matmul_desc& d, const float* multi_operand, int batch_index, ResolvedRequant* r) {
+  r->out_dtype = d.out_dtype;
+  r->relu = d.do_relu ? B200Q_RELU_BEFORE_REQUANT : B200Q_RELU_NONE;
+  if (d.out_dtype == B200Q_DT_I32 && d.n_quant == 0) {
+    r->dialect = B200Q_RQ_NONE;
+    return B200Q_OK;
+  }
+  if (d.out_dtype >= B200Q_DT_F32) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: float output types are not handled by the INT8 path");
+  const int qm = d.quant_mode;
+  if (qm == B200Q_QM_ONLY_SCALE && !d.is_cv18xx) {
+    if (d.fuse_rq) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: OnlyScale with fuse_rq (asserted off in the reference)");
+    r->dialect = B200Q_RQ_ONLY_SCALE;
+    r->scale = (float)d.out_scale;
+    r->out_zp = d.out_zp;
+    return B200Q_OK;
+  }
+  if (d.n_quant < 1 || !d.multipliers || !d.rshifts) return set_error(B200Q_ERR_INVALID, "matmul: multipliers/rshifts missing");
+  B200Q_TRY(check_int32(d.multipliers, d.n_quant, "multipliers"));
+  B200Q_TRY(check_int32(d.rshifts, d.n_quant, "rshifts"));
+  if (d.is_cv18xx) {  // :638-664, applyMultiplierAndRShift(.., qmode, HALF_AWAY) with isCV18xx()
+    const int bi = batch_index < d.n_quant ? batch_index : 0;
+    r->round_mode = B200Q_ROUND_HALF_AWAY_FROM_ZERO;
+    r->out_zp = 0;
+    r->multiplier.assign(1, (int32_t)d.multipliers[bi]);
+    const int32_t rs = (int32_t)d.rshifts[bi];
+    switch (qm) {
+      case B200Q_QM_MULTIPLIER_SHIFT:
+        if (rs < 0 || rs > 30) return set_error(B200Q_ERR_INVALID, "matmul: cv18xx rshift %d outside [0,30]", rs);
+        r->dialect = B200Q_RQ_MULTIPLIER_SHIFT_F32;
+        r->shift.assign(1, rs);
+        break;
+      case B200Q_QM_ONLY_SHIFT: r->dialect = B200Q_RQ_ONLY_SHIFT; r->shift.assign(1, rs); break;
+      case B200Q_QM_QDM:
+      case B200Q_QM_TFLITE:
+      case B200Q_QM_TFLITE_LSHIFT: r->dialect = B200Q_RQ_QDM; r->shift.assign(1, -rs); break;
+      default: return set_error(B200Q_ERR_UNSUPPORTED, "matmul: quant_mode %d on cv18xx", qm);
+    }
+    return B200Q_OK;
+  }
+  r->out_zp = d.out_zp;
+  if (qm == B200Q_QM_TFLITE || qm == B200Q_QM_TFLITE_LSHIFT) {  // :696-707
+    r->dialect = B200Q_RQ_QDM;
+    r->round_mode = B200Q_ROUND_HALF_AWAY_FROM_ZERO;
+    r->multiplier.assign(1, (int32_t)d.multipliers[0]);
+    r->shift.assign(1, -(int32_t)d.rshifts[0]);
+    return B200Q_OK;
+  }
+  if (qm == B200Q_QM_MULTIPLIER_SHIFT) {  // :708-726
+    r->dialect = B200Q_RQ_MULTIPLIER_SHIFT;
+    r->round_mode = B200Q_ROUND_HALF_UP;
+    if (d.fuse_rq) {
+      if (!multi_operand) return set_error(B200Q_ERR_INVALID, "matmul: fuse_rq needs the multi operand (inputs[3])");
+      r->per_channel = 1;
+      r->multiplier.resize((size_t)d.N);
+      r->shift.assign((size_t)d.N, (int32_t)d.rshifts[0]);
+      for (int64_t n = 0; n < d.N; ++n) {
+        const int64_t m = (int64_t)multi_operand[n];  // the interpreter reads the float operand back as int64
+        if (m > 2147483647ll || m < -2147483648ll) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: multi[%lld] does not fit int32", (long long)n);
+        r->multiplier[(size_t)n] = (int32_t)m;
+      }
+    } else {
+      r->multiplier.assign(1, (int32_t)d.multipliers[0]);
+      r->shift.assign(1, (int32_t)d.rshifts[0]);
+    }
+    return B200Q_OK;
+  }
+  return set_error(B200Q_ERR_UNSUPPORTED, "matmul: quant_mode %d leaves the output un-requantised in the reference", qm);
+}
+
+int validate_matmul(const b200q_matmul_desc& d) {
+  if (d.batch < 1 || d.M < 0 || d.K < 1 || d.N < 1) return set_error(B200Q_ERR_INVALID, "matmul: bad shape");
+  if (d.M * d.batch > 0x7fffffffLL || d.N > 0x7fffffffLL || d.K > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: dimension exceeds int32");
+  if (d.left_transpose || d.output_transpose || d.hdim_is_batch) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: left/output transpose and hdim_is_batch are not implemented");
+  if (!is_q8(d.input_dtype) || !is_q8(d.right_dtype)) return set_error(B200Q_ERR_INVALID, "matmul: operands must be int8/uint8");
+  return B200Q_OK;
+}
+
+// Launch out = epilogue(A * B^T) on the best kernel.  b is [N,K].
+int gemm_dispatch(const void* a, int a_dt, const void* b_nk, int b_dt, int64_t M, int64_t N, int64_t K, int input_zp,
+                  int right_zp, const Epilogue& e, void* out, int* status, int algo, cudaStream_t s) {
+  if (M == 0) return B200Q_OK;
+  IGemmProblem p{};
+  p.a = a;
+  p.b = b_nk;
+  p.a_unsigned = a_dt == B200Q_DT_U8;
+  p.b_unsigned = b_dt == B200Q_DT_U8;
+  p.a_pitch = K;
+  p.b_pitch = K;
+  p.rows = (int)M;
+  p.n = (int)N;
+  p.k_per_tap = (int)K;
+  p.taps_h = p.taps_w = 1;
+  p.out_mode = IGEMM_OUT_ROWMAJOR;
+  p.ldc = N;
+  p.out = out;
+  const char* why = nullptr;
+  const bool tc_ok = igemm_i8_tcgen05_supported(p, &why) && input_zp == 0 && right_zp == 0;
+  if (algo == 1 && !tc_ok)
+    return set_error(B200Q_ERR_UNSUPPORTED, "gemm: tensor-core path unavailable: %s", why ? why : "non-zero zero point");
+  if (tc_ok && algo != 2) return igemm_i8_tcgen05_launch(p, e, status, s);
+  return gemm_i8_direct_launch(a, p.a_unsigned, b_nk, p.b_unsigned, 1, (int)M, (int)N, (int)K, input_zp, right_zp, e, out, s);
+}
+
+struct MatMulHandle {
+  DevBuf stage_f32, a_q8, b_f32, b_nk, bias, mult, shift, out_q, out_f32, status;
+  bool weights_ready = false;
+  int weight_version = -1;
+  const float* weight_ptr = nullptr;
+};
+
+// ---------------------------------------------------------------------------------------------- Conv2D
+int resolve_conv(const b200q_conv2d_desc& d, ResolvedRequant* r) {  // Conv2D.cpp:295-341
+  r->out_dtype = d.out_dtype;
+  r->relu = d.do_relu ? B200Q_RELU_AFTER_REQUANT : B200Q_RELU_NONE;
+  r->out_zp = d.out_zp;
+  if (d.out_dtype >= B200Q_DT_F32) return set_error(B200Q_ERR_UNSUPPORTED, "conv2d: float output types are not handled by the INT8 path");
+  if (d.n_quant < 1 || !d.rshifts) return set_error(B200Q_ERR_INVALID, "conv2d: rshift attribute missing");
+  if (d.n_quant != 1 && d.n_quant != d.oc) return set_error(B200Q_ERR_INVALID, "conv2d: n_quant must be 1 or oc");
+  const int qm = d.quant_mode;
+  r->per_channel = (d.n_quant == d.oc) ? 1 : 0;
+  B200Q_TRY(check_int32(d.rshifts, d.n_quant, "rshift"));
+  r->shift.resize((size_t)d.n_quant);
+  r->multiplier.assign((size_t)d.n_quant, 1);
+  if (qm != B200Q_QM_ONLY_SHIFT) {
+    if (!d.multipliers) return set_error(B200Q_ERR_INVALID, "conv2d: multiplier attribute missing");
+    B200Q_TRY(check_int32(d.multipliers, d.n_quant, "multiplier"));
+    for (int i = 0; i < d.n_quant; ++i) r->multiplier[(size_t)i] = (int32_t)d.multipliers[i];
+  }
+  const bool is_tf = qm == B200Q_QM_QDM || qm == B200Q_QM_TFLITE || qm == B200Q_QM_TFLITE_LSHIFT;
+  r->round_mode = is_tf ? B200Q_ROUND_HALF_AWAY_FROM_ZERO : B200Q_ROUND_HALF_UP;  // :312-315
+  for (int i = 0; i < d.n_quant; ++i) {
+    const int32_t rs = (int32_t)d.rshifts[i];
+    if (qm == B200Q_QM_MULTIPLIER_SHIFT && d.is_cv18xx && (rs < 0 || rs > 30))
+      return set_error(B200Q_ERR_INVALID, "conv2d: cv18xx rshift %d outside [0,30]", rs);
+    r->shift[(size_t)i] = is_tf ? (d.is_cv18xx ? -rs : rs) : rs;  // MathUtils.cpp:549-556
+  }
+  switch (qm) {
+    case B200Q_QM_MULTIPLIER_SHIFT: r->dialect = d.is_cv18xx ? B200Q_RQ_MULTIPLIER_SHIFT_F32 : B200Q_RQ_MULTIPLIER_SHIFT; break;
+    case B200Q_QM_ONLY_SHIFT: r->dialect = B200Q_RQ_ONLY_SHIFT; break;
+    case B200Q_QM_QDM:
+    case B200Q_QM_TFLITE:
+    case B200Q_QM_TFLITE_LSHIFT: r->dialect = B200Q_RQ_QDM; break;
+    default: return set_error(B200Q_ERR_UNSUPPORTED, "conv2d: quant_mode %d (unreachable in the reference)", qm);
+  }
+  return B200Q_OK;
+}
+
+struct ConvHandle {
+  b200q_conv2d_desc d{};
+  ConvGeometry g{};
+  bool use_tc = false;
+  int bh = 0, bw = 0, Hp = 0, Wp = 0;
+  Epilogue epi{};
+  DevBuf w_oihw, w_packed, bias, mult, shift, x_bordered, status;
+  // operator-face staging
+  DevBuf x_f32, x_q8, y_q, y_f32, w_f32, bias_f32;
+};
+
+int conv_out_dims(const b200q_conv2d_desc& d, int64_t* oh, int64_t* ow) {
+  if (d.n < 0 || d.ic < 1 || d.ih < 1 || d.iw < 1 || d.oc < 1 || d.kh < 1 || d.kw < 1 || d.sh < 1 || d.sw < 1 ||
+      d.dh < 1 || d.dw < 1 || d.groups < 1 || d.ic % d.groups || d.oc % d.groups || d.pht < 0 || d.phb < 0 ||
+      d.pwl < 0 || d.pwr < 0)
+    return set_error(B200Q_ERR_INVALID, "conv2d: bad geometry");
+  *oh = (d.ih + d.pht + d.phb - d.dh * (d.kh - 1) - 1) / d.sh + 1;
+  *ow = (d.iw + d.pwl + d.pwr - d.dw * (d.kw - 1) - 1) / d.sw + 1;
+  if (*oh < 1 || *ow < 1) return set_error(B200Q_ERR_INVALID, "conv2d: empty output");
+  if (!is_q8(d.input_dtype)) return set_error(B200Q_ERR_INVALID, "conv2d: input must be int8/uint8");
+  return B200Q_OK;
+}
+
+// filter / bias already on the device in native types
+int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int w_is_f32, const void* bias_dev,
+               int bias_is_f32, cudaStream_t s) {
+  int64_t oh, ow;
+  B200Q_TRY(conv_out_dims(d, &oh, &ow));
+  h->d = d;
+  h->d.multipliers = nullptr;
+  h->d.rshifts = nullptr;
+  ConvGeometry& g = h->g;
+  g = ConvGeometry{(int)d.n, (int)d.ic, (int)d.ih, (int)d.iw, (int)d.oc, (int)oh, (int)ow, (int)d.kh, (int)d.kw,
+                   (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, (int)d.pht, (int)d.pwl, (int)d.groups, d.pad_value};
+  ResolvedRequant r;
+  B200Q_TRY(resolve_conv(d, &r));
+  // bias -> int32 on the device
+  const int32_t* d_bias = nullptr;
+  if (d.with_bias) {
+    if (!bias_dev) return set_error(B200Q_ERR_INVALID, "conv2d: with_bias but no bias operand");
+    B200Q_TRY(h->bias.ensure((size_t)d.oc * 4));
+    if (bias_is_f32) B200Q_TRY(f32_to_i32((const float*)bias_dev, h->bias.as<int32_t>(), d.oc, s));
+    else CUDA_TRY(cudaMemcpyAsync(h->bias.p, bias_dev, (size_t)d.oc * 4, cudaMemcpyDeviceToDevice, s));
+    d_bias = h->bias.as<int32_t>();
+  }
+  B200Q_TRY(make_epilogue(r, d_bias, h->mult, h->shift, s, &h->epi));
+  B200Q_TRY(h->status.ensure(4));
+  CUDA_TRY(cudaMemsetAsync(h->status.p, 0, 4, s));
+
+  // tensor-core path: stride 1, no dilation, no groups, zero padding value, channels fit the K blocking
+  const bool geometry_ok = d.sh == 1 && d.sw == 1 && d.dh == 1 && d.dw == 1 && d.groups == 1 && d.pad_value == 0;
+  const bool k_ok = (d.kh * d.kw == 1) ? (d.ic % 16 == 0) : (d.ic % 128 == 0);
+  h->bh = (int)(d.pht > d.phb ? d.pht : d.phb);
+  h->bw = (int)(d.pwl > d.pwr ? d.pwl : d.pwr);
+  h->Hp = (int)d.ih + 2 * h->bh;
+  h->Wp = (int)d.iw + 2 * h->bw;
+  const long long rows = (long long)d.n * h->Hp * h->Wp;
+  h->use_tc = geometry_ok && k_ok && rows < 0x7fffffffLL && d.algo != 2;
+  if (d.algo == 1 && !h->use_tc)
+    return set_error(B200Q_ERR_UNSUPPORTED, "conv2d: tensor-core path needs stride 1, dilation 1, groups 1, zero pad value and IC %% %d == 0", d.kh * d.kw == 1 ? 16 : 128);
+  const size_t wbytes = (size_t)d.oc * (d.ic / d.groups) * d.kh * d.kw;
+  if (h->use_tc) {
+    B200Q_TRY(h->w_packed.ensure(wbytes));
+    B200Q_TRY(repack_weight_oihw(w_dev, w_is_f32, h->w_packed.p, (int)d.oc, (int)d.ic, (int)d.kh, (int)d.kw, s));
+    B200Q_TRY(h->x_bordered.ensure((size_t)rows * d.ic));
+    CUDA_TRY(cudaMemsetAsync(h->x_bordered.p, 0, (size_t)rows * d.ic, s));  // the border stays zero for every run
+  } else {
+    B200Q_TRY(h->w_oihw.ensure(wbytes));
+    if (w_is_f32) B200Q_TRY(f32_to_q8((const float*)w_dev, h->w_oihw.p, (long long)wbytes, s));
+    else CUDA_TRY(cudaMemcpyAsync(h->w_oihw.p, w_dev, wbytes, cudaMemcpyDeviceToDevice, s));
+  }
+  return B200Q_OK;
+}
+
+// x: device NCHW (bytes, or float holding integers); y: device NCHW native out dtype
+int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s) {
+  const b200q_conv2d_desc& d = h->d;
+  if (d.n == 0) return B200Q_OK;
+  if (h->use_tc) {
+    B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
+    IGemmProblem p{};
+    p.a = h->x_bordered.p;
+    p.b = h->w_packed.p;
+    p.a_unsigned = d.input_dtype == B200Q_DT_U8;
+    p.b_unsigned = 0;
+    p.a_pitch = d.ic;
+    p.b_pitch = d.ic * d.kh * d.kw;
+    p.rows = (int)((long long)d.n * h->Hp * h->Wp);
+    p.n = (int)d.oc;
+    p.k_per_tap = (int)d.ic;
+    p.taps_h = (int)d.kh;
+    p.taps_w = (int)d.kw;
+    p.pad_top = (int)d.pht;
+    p.pad_left = (int)d.pwl;
+    p.row_pitch = h->Wp;
+    p.img_rows = h->Hp * h->Wp;
+    // GEMM row (hp, wp) reads bordered positions (hp + fy - pht, wp + fx - pwl), i.e. it is output pixel
+    // (hp - bh, wp - bw); rows outside [0, oh) x [0, ow) are discarded by the epilogue.
+    p.border_h = h->bh;
+    p.border_w = h->bw;
+    p.out_h = h->g.oh;
+    p.out_w = h->g.ow;
+    p.out_mode = IGEMM_OUT_NCHW;
+    p.ldc = 0;
+    p.out = y;
+    return igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s);
+  }
+  const void* xin = x;
+  if (x_is_f32) {
+    const long long n = (long long)d.n * d.ic * d.ih * d.iw;
+    B200Q_TRY(h->x_q8.ensure((size_t)n));
+    B200Q_TRY(f32_to_q8((const float*)x, h->x_q8.p, n, s));
+    xin = h->x_q8.p;
+  }
+  return conv2d_i8_direct_launch(xin, d.input_dtype == B200Q_DT_U8, h->w_oihw.as<int8_t>(), h->g, h->epi, y, s);
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+// ------------------------------------------------------------------------------------------------ MatMul
+int b200q_matmul_init(const b200q_matmul_desc* desc, void** handle) {
+  if (!desc || !handle) return set_error(B200Q_ERR_INVALID, "matmul_init: null argument");
+  B200Q_TRY(validate_matmul(*desc));
+  auto* h = new (std::nothrow) MatMulHandle();
+  if (!h) return set_error(B200Q_ERR_NOMEM, "matmul_init: out of host memory");
+  *handle = h;
+  return B200Q_OK;
+}
+
+void b200q_matmul_deinit(void** handle) {
+  if (handle && *handle) {
+    delete static_cast<MatMulHandle*>(*handle);
+    *handle = nullptr;
+  }
+}
+
+int b200q_matmul_inference(const b200q_matmul_desc* desc, float* const* inputs, int n_inputs, float* const* outputs,
+                           int n_outputs, void** handle) {
+  if (!desc || !inputs || !outputs || !handle || n_inputs < 2 || n_outputs < 1 || !inputs[0] || !inputs[1] || !outputs[0])
+    return set_error(B200Q_ERR_INVALID, "matmul_inference: null argument");
+  const b200q_matmul_desc& d = *desc;
+  B200Q_TRY(validate_matmul(d));
+  const bool own = (*handle == nullptr);
+  if (own) B200Q_TRY(b200q_matmul_init(desc, handle));
+  MatMulHandle* h = static_cast<MatMulHandle*>(*handle);
+  cudaStream_t s = 0;
+  int rc = B200Q_OK;
+  do {
+    const float* bias_f = (d.with_bias && n_inputs > 2) ? inputs[2] : nullptr;
+    const float* multi_f = (n_inputs > 3) ? inputs[3] : nullptr;
+    if (d.with_bias && !bias_f) { rc = set_error(B200Q_ERR_INVALID, "matmul: with_bias but inputs[2] is null"); break; }
+    const int64_t nb = d.right_batched ? d.batch : 1;
+    const int64_t rows = d.right_batched ? d.M : d.batch * d.M;  // a shared right operand folds the batch into M
+    const size_t a_elems = (size_t)(d.batch * d.M * d.K), b_elems = (size_t)(nb * d.K * d.N), o_elems = (size_t)(d.batch * d.M * d.N);
+    // right operand: [N,K] bytes per batch
+    const bool cached = d.right_is_weight && h->weights_ready && h->weight_version == d.weight_version && h->weight_ptr == inputs[1];
+    if (!cached) {
+      if ((rc = h->b_f32.ensure(b_elems * 4))) break;
+      if ((rc = h->b_nk.ensure(b_elems))) break;
+      if (cudaMemcpyAsync(h->b_f32.p, inputs[1], b_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D right", __FILE__, __LINE__); break; }
+      for (int64_t b = 0; b < nb && rc == B200Q_OK; ++b) {
+        const float* src = h->b_f32.as<float>() + b * d.K * d.N;
+        uint8_t* dst = h->b_nk.as<uint8_t>() + b * d.K * d.N;
+        rc = d.right_transpose ? f32_to_q8(src, dst, d.K * d.N, s) : transpose_to_u8(src, 1, dst, (int)d.K, (int)d.N, s);
+      }
+      if (rc) break;
+      if (bias_f) {
+        if ((rc = h->stage_f32.ensure((size_t)d.N * 4))) break;
+        if ((rc = h->bias.ensure((size_t)d.N * 4))) break;
+        if (cudaMemcpyAsync(h->stage_f32.p, bias_f, (size_t)d.N * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D bias", __FILE__, __LINE__); break; }
+        if ((rc = f32_to_i32(h->stage_f32.as<float>(), h->bias.as<int32_t>(), d.N, s))) break;
+        // the staging buffer is reused for A below; stream order keeps this safe
+      }
+      h->weights_ready = true;
+      h->weight_version = d.weight_version;
+      h->weight_ptr = inputs[1];
+    }
+    if ((rc = h->status.ensure(4))) break;
+    if (cudaMemsetAsync(h->status.p, 0, 4, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "memset", __FILE__, __LINE__); break; }
+    if (a_elems == 0) break;
+    if ((rc = h->stage_f32.ensure(a_elems * 4 > (size_t)d.N * 4 ? a_elems * 4 : (size_t)d.N * 4))) break;
+    if ((rc = h->a_q8.ensure(a_elems))) break;
+    if ((rc = h->out_q.ensure(o_elems * dtype_size(d.out_dtype)))) break;
+    if ((rc = h->out_f32.ensure(o_elems * 4))) break;
+    if (cudaMemcpyAsync(h->stage_f32.p, inputs[0], a_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D input", __FILE__, __LINE__); break; }
+    if ((rc = f32_to_q8(h->stage_f32.as<float>(), h->a_q8.p, (long long)a_elems, s))) break;
+    const int n_launch = (d.right_batched || d.is_cv18xx) ? (int)d.batch : 1;
+    const int64_t rows_per = (n_launch == 1) ? rows : d.M;
+    for (int b = 0; b < n_launch && rc == B200Q_OK; ++b) {
+      ResolvedRequant r;
+      if ((rc = resolve_matmul(d, multi_f, b, &r))) break;
+      Epilogue e;
+      // per-launch multiplier/shift arrays: small, re-uploaded (stream ordered) for each batch entry
+      if ((rc = make_epilogue(r, bias_f ? h->bias.as<int32_t>() : nullptr, h->mult, h->shift, s, &e))) break;
+      const uint8_t* a = h->a_q8.as<uint8_t>() + (size_t)b * d.M * d.K;
+      const uint8_t* bm = h->b_nk.as<uint8_t>() + (d.right_batched ? (size_t)b * d.K * d.N : 0);
+      uint8_t* o = h->out_q.as<uint8_t>() + (size_t)b * d.M * d.N * dtype_size(d.out_dtype);
+      rc = gemm_dispatch(a, d.input_dtype, bm, d.right_dtype, rows_per, d.N, d.K, d.input_zp, d.right_zp, e, o,
+                         h->status.as<int>(), d.algo, s);
+      if (n_launch > 1 && rc == B200Q_OK && cudaStreamSynchronize(s) != cudaSuccess) rc = cuda_error(cudaGetLastError(), "sync", __FILE__, __LINE__);
+    }
+    if (rc) break;
+    if ((rc = q_to_f32(h->out_q.p, d.out_dtype, h->out_f32.as<float>(), (long long)o_elems, s))) break;
+    if (cudaMemcpyAsync(outputs[0], h->out_f32.p, o_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__); break; }
+    rc = read_status(h->status, s, "matmul");
+  } while (0);
+  if (rc != B200Q_OK) cudaStreamSynchronize(s);
+  if (own) b200q_matmul_deinit(handle);
+  return rc;
+}
+
+int b200q_gemm_i8_dev(const void* a, int a_dtype, const void* b_nk, int b_dtype, int64_t M, int64_t N, int64_t K,
+                      const b200q_epilogue* epilogue, void* out, int32_t* status, int algo, void* stream) {
+  if (!a || !b_nk || !epilogue || !out) return set_error(B200Q_ERR_INVALID, "gemm_i8_dev: null argument");
+  if (!is_q8(a_dtype) || !is_q8(b_dtype)) return set_error(B200Q_ERR_INVALID, "gemm_i8_dev: operands must be int8/uint8");
+  if (M < 0 || N < 1 || K < 1 || M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return set_error(B200Q_ERR_INVALID, "gemm_i8_dev: bad shape");
+  Epilogue e;
+  static_assert(sizeof(Epilogue) == sizeof(b200q_epilogue), "public and internal epilogue structs must match");
+  std::memcpy(&e, epilogue, sizeof(e));
+  return gemm_dispatch(a, a_dtype, b_nk, b_dtype, M, N, K, 0, 0, e, out, status, algo, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------------------------------------------ Conv2D
+int b200q_conv2d_init(const b200q_conv2d_desc* desc, float* const* inputs, int n_inputs, void** handle) {
+  if (!desc || !inputs || !handle || n_inputs < 2 || !inputs[1]) return set_error(B200Q_ERR_INVALID, "conv2d_init: null argument");
+  const b200q_conv2d_desc& d = *desc;
+  int64_t oh, ow;
+  B200Q_TRY(conv_out_dims(d, &oh, &ow));
+  auto* h = new (std::nothrow) ConvHandle();
+  if (!h) return set_error(B200Q_ERR_NOMEM, "conv2d_init: out of host memory");
+  cudaStream_t s = 0;
+  int rc = B200Q_OK;
+  do {
+    const size_t w_elems = (size_t)d.oc * (d.ic / d.groups) * d.kh * d.kw;
+    if ((rc = h->w_f32.ensure(w_elems * 4))) break;
+    if (cudaMemcpyAsync(h->w_f32.p, inputs[1], w_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D filter", __FILE__, __LINE__); break; }
+    const float* bias_f = (d.with_bias && n_inputs > 2) ? inputs[2] : nullptr;
+    if (d.with_bias && !bias_f) { rc = set_error(B200Q_ERR_INVALID, "conv2d: with_bias but inputs[2] is null"); break; }
+    if (bias_f) {
+      if ((rc = h->bias_f32.ensure((size_t)d.oc * 4))) break;
+      if (cudaMemcpyAsync(h->bias_f32.p, bias_f, (size_t)d.oc * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D bias", __FILE__, __LINE__); break; }
+    }
+    if ((rc = conv_setup(h, d, h->w_f32.p, 1, bias_f ? h->bias_f32.p : nullptr, 1, s))) break;
+    if (cudaStreamSynchronize(s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "sync", __FILE__, __LINE__); break; }
+  } while (0);
+  if (rc != B200Q_OK) {
+    cudaStreamSynchronize(s);
+    delete h;
+    return rc;
+  }
+  *handle = h;
+  return B200Q_OK;
+}
+
+void b200q_conv2d_deinit(void** handle) {
+  if (handle && *handle) {
+    delete static_cast<ConvHandle*>(*handle);
+    *handle = nullptr;
+  }
+}
+
+int b200q_conv2d_inference(const b200q_conv2d_desc* desc, float* const* inputs, int n_inputs, float* const* outputs,
+                           int n_outputs, void** handle) {
+  (void)desc;
+  if (!handle || !*handle) return set_error(B200Q_ERR_INVALID, "conv2d_inference: no handle (call b200q_conv2d_init first)");
+  if (!inputs || !outputs || n_inputs < 1 || n_outputs < 1 || !inputs[0] || !outputs[0]) return set_error(B200Q_ERR_INVALID, "conv2d_inference: null argument");
+  ConvHandle* h = static_cast<ConvHandle*>(*handle);
+  const b200q_conv2d_desc& d = h->d;
+  cudaStream_t s = 0;
+  const size_t x_elems = (size_t)d.n * d.ic * d.ih * d.iw;
+  const size_t y_elems = (size_t)d.n * d.oc * h->g.oh * h->g.ow;
+  if (x_elems == 0) return B200Q_OK;
+  B200Q_TRY(h->x_f32.ensure(x_elems * 4));
+  B200Q_TRY(h->y_q.ensure(y_elems * dtype_size(d.out_dtype)));
+  B200Q_TRY(h->y_f32.ensure(y_elems * 4));
+  CUDA_TRY(cudaMemcpyAsync(h->x_f32.p, inputs[0], x_elems * 4, cudaMemcpyHostToDevice, s));
+  int rc = conv_run(h, h->x_f32.p, 1, h->y_q.p, s);
+  if (rc == B200Q_OK) rc = q_to_f32(h->y_q.p, d.out_dtype, h->y_f32.as<float>(), (long long)y_elems, s);
+  if (rc == B200Q_OK && cudaMemcpyAsync(outputs[0], h->y_f32.p, y_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__);
+  if (rc == B200Q_OK) rc = read_status(h->status, s, "conv2d");
+  else cudaStreamSynchronize(s);
+  return rc;
+}
+
+int b200q_conv2d_dev_create(const b200q_conv2d_desc* desc, const void* filter_oihw_s8, const int32_t* bias_s32, void** handle) {
+  if (!desc || !filter_oihw_s8 || !handle) return set_error(B200Q_ERR_INVALID, "conv2d_dev_create: null argument");
+  auto* h = new (std::nothrow) ConvHandle();
+  if (!h) return set_error(B200Q_ERR_NOMEM, "conv2d_dev_create: out of host memory");
+  cudaStream_t s = 0;
+  int rc = conv_setup(h, *desc, filter_oihw_s8, 0, bias_s32, 0, s);
+  if (rc == B200Q_OK && cudaStreamSynchronize(s) != cudaSuccess) rc = cuda_error(cudaGetLastError(), "sync", __FILE__, __LINE__);
+  if (rc != B200Q_OK) {
+    delete h;
+    return rc;
+  }
+  *handle = h;
+  return B200Q_OK;
+}
+
+int b200q_conv2d_dev_run(void* handle, const void* x_nchw, void* y_nchw, void* stream) {
+  if (!handle || !x_nchw || !y_nchw) return set_error(B200Q_ERR_INVALID, "conv2d_dev_run: null argument");
+  return conv_run(static_cast<ConvHandle*>(handle), x_nchw, 0, y_nchw, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_conv2d_dev_status(void* handle, void* stream) {
+  if (!handle) return set_error(B200Q_ERR_INVALID, "conv2d_dev_status: null handle");
+  return read_status(static_cast<ConvHandle*>(handle)->status, static_cast<cudaStream_t>(stream), "conv2d");
+}
+
+void b200q_conv2d_dev_destroy(void** handle) { b200q_conv2d_deinit(handle); }
+
+}  // extern "C"

@@ -1,0 +1,53 @@
+// Problem description of the INT8 (implicit) GEMM kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "requant.cuh"
+
+namespace b200q {
+
+enum { IGEMM_OUT_ROWMAJOR = 0, IGEMM_OUT_NCHW = 1, IGEMM_OUT_NHWC_BORDERED = 2 };
+
+// What the host asks for.  A is [rows][k_per_tap] (row pitch a_pitch bytes): the GEMM's left matrix, or the
+// pixels of a zero-bordered NHWC image flattened to rows.  B is [n][taps_h*taps_w*k_per_tap] (K-major weights).
+struct IGemmProblem {
+  const void* a;
+  const void* b;
+  int a_unsigned, b_unsigned;
+  long long a_pitch, b_pitch;
+  int rows, n, k_per_tap;
+  int taps_h, taps_w, pad_top, pad_left;  // 1,1,0,0 for a plain GEMM
+  int row_pitch;                          // Wp: rows per image line (convolution)
+  int img_rows;                           // Hp*Wp: rows per image (convolution)
+  int border_h, border_w;                 // zero border of the A image
+  int out_h, out_w;                       // interior size = output H, W
+  int out_mode;                           // IGEMM_OUT_*
+  long long ldc;                          // elements per output row (ROWMAJOR / NHWC_BORDERED)
+  void* out;
+};
+
+// Kernel argument block (device view of the same problem).
+struct IGemmArgs {
+  int rows, n, num_kb, kb_per_tap, taps_w, tap_org_h, tap_org_w, row_pitch;
+  int out_mode, img_rows, border_h, border_w, out_h, out_w;
+  long long ldc;
+  void* out;
+  Epilogue epi;
+  int* status;
+  uint32_t idesc;
+  int num_m_tiles, num_n_tiles;
+};
+
+int igemm_i8_tcgen05_supported(const IGemmProblem& p, const char** why);
+int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* status, cudaStream_t stream);
+// Plain CUDA-core kernel for shapes the tensor-core path does not take (odd K, strides, groups, dilation).
+struct ConvGeometry {
+  int n, ic, ih, iw, oc, oh, ow, kh, kw, sh, sw, dh, dw, pht, pwl, groups, pad_value;
+};
+int conv2d_i8_direct_launch(const void* x_nchw, int x_unsigned, const int8_t* w_oihw, const ConvGeometry& g,
+                            const Epilogue& epi, void* y_nchw, cudaStream_t stream);
+int gemm_i8_direct_launch(const void* a, int a_unsigned, const void* b, int b_unsigned, int b_is_nk, int m, int n,
+                          int k, int input_zp, int right_zp, const Epilogue& epi, void* out, cudaStream_t stream);
+
+}  // namespace b200q

@@ -1,0 +1,441 @@
+// INT8 GEMM / implicit-GEMM convolution on the 5th-generation tensor cores (tcgen05 kind::i8).
+//
+// One persistent CTA per SM walks output tiles of 128 rows x BLOCK_N channels.  Warp roles:
+//   warp 0      TMA producer: 128-byte-swizzled K-major tiles of A (activations) and B (weights) into a
+//               shared-memory ring, completion counted on mbarriers;
+//   warp 1      allocates TMEM and issues tcgen05.mma (one thread), int32 accumulators live in TMEM,
+//               two accumulator buffers so the next tile's MMAs overlap this tile's epilogue;
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, + bias, ReLU, exact requantisation
+//               (requant.cuh), saturate, store as [rows, N], as NCHW, or as zero-bordered NHWC.
+//
+// The convolution is expressed as a GEMM whose A rows are the pixels of a zero-bordered NHWC image
+// flattened to [N*Hp*Wp, C]: the row block of filter tap (fy, fx) is the same row block shifted by
+// (fy - pad_top) * Wp + (fx - pad_left) rows, so every A tile is still one 2-D TMA box (rows outside the
+// tensor are zero-filled by TMA).  Outputs computed for border pixels are discarded (or written as zero).
+// This replaces tpu::MatMulOp / tpu::Conv2DOp inference (lib/Dialect/Tpu/Interfaces/Common/MatMul.cpp:599-728,
+// Conv2D.cpp:264-341) and the oneDNN primitives behind them (lib/Support/Dnnl/MatMul.cpp, Conv.cpp).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "igemm.h"
+#include "internal.h"
+#include "ptx_sm100.cuh"
+#include "requant.cuh"
+
+namespace b200q {
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 128;  // bytes == int8 elements: one 128-byte swizzle span
+constexpr int UMMA_K = 32;    // K of one tcgen05.mma for 8-bit operands
+constexpr int NUM_EPI_WARPS = 4;
+constexpr int NUM_THREADS = 64 + NUM_EPI_WARPS * 32;
+constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate tile time
+
+template <int BLOCK_N, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K;
+  static constexpr int B_BYTES = BLOCK_N * BLOCK_K;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;  // tmem ptr, abort flag
+  static constexpr int CHAN_OFFSET = MISC_OFFSET + 16;           // bias / multiplier / shift of the tile's channels
+  static constexpr int TOTAL = CHAN_OFFSET + 3 * BLOCK_N * 4;
+  static constexpr int DYN_BYTES = TOTAL + 1024;                 // slack for manual 1024-byte alignment
+};
+
+template <int BLOCK_N>
+struct TmemCols {
+  static constexpr int value = (2 * BLOCK_N) < 32 ? 32 : 2 * BLOCK_N;  // power of two for BLOCK_N in {16,...,256}
+};
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory"); }
+
+template <int BLOCK_N, int STAGES, int DIALECT, int RMODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const IGemmArgs args) {
+  using L = SmemLayout<BLOCK_N, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFFSET + 4);
+  int32_t* chan_bias = reinterpret_cast<int32_t*>(smem + L::CHAN_OFFSET);
+  int32_t* chan_mult = chan_bias + BLOCK_N;
+  int32_t* chan_shift = chan_mult + BLOCK_N;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tmem_full_bar(a), 1);
+      ptx::mbar_init(tmem_empty_bar(a), NUM_EPI_WARPS * 32);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_ptr_smem), TmemCols<BLOCK_N>::value);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int num_tiles = args.num_m_tiles * args.num_n_tiles;
+  const int num_kb = args.num_kb;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / args.num_n_tiles) * BLOCK_M;
+        const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, WAIT_BUDGET_NS);
+          if (!ok) break;
+          const int tap = kb / args.kb_per_tap;
+          const int kc = kb - tap * args.kb_per_tap;
+          const int fy = tap / args.taps_w;
+          const int fx = tap - fy * args.taps_w;
+          const int a_row = m0 + (fy - args.tap_org_h) * args.row_pitch + (fx - args.tap_org_w);
+          ptx::mbar_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
+          const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+          ptx::tma_load_2d(sa, &tmap_a, full_bar(stage), kc * BLOCK_K, a_row);
+          ptx::tma_load_2d(sa + L::A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, n0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        ok = ptx::mbar_wait_bounded(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2, WAIT_BUDGET_NS);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, 3, WAIT_BUDGET_NS);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+          const uint64_t a_desc = ptx::make_smem_desc_kmajor(sa, 1024, 2);
+          const uint64_t b_desc = ptx::make_smem_desc_kmajor(sa + L::A_BYTES, 1024, 2);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            // advancing K inside the swizzle span = advancing the start address (16-byte units)
+            ptx::umma_i8(d_tmem, a_desc + (uint64_t)(k * (UMMA_K / 16)), b_desc + (uint64_t)(k * (UMMA_K / 16)),
+                         args.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        ptx::umma_commit(tmem_full_bar(acc));  // accumulator complete
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. 32*quarter+31
+    const int etid = threadIdx.x - 64;
+    const Epilogue& e = args.epi;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int cached_n0 = -1;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m0 = (tile / args.num_n_tiles) * BLOCK_M;
+      const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
+      if (n0 != cached_n0) {
+        epi_bar_sync();  // everyone is done reading the previous tile's channel parameters
+        for (int c = etid; c < BLOCK_N; c += NUM_EPI_WARPS * 32) {
+          const int n = n0 + c;
+          const bool in = n < args.n;
+          chan_bias[c] = (in && e.bias) ? e.bias[n] : 0;
+          chan_mult[c] = (in && e.multiplier) ? e.multiplier[e.per_channel ? n : 0] : 1;
+          chan_shift[c] = (in && e.shift) ? e.shift[e.per_channel ? n : 0] : 0;
+        }
+        epi_bar_sync();
+        cached_n0 = n0;
+      }
+      if (!ptx::mbar_wait_bounded(tmem_full_bar(acc), acc_phase, abort_flag, 4, WAIT_BUDGET_NS)) break;
+      ptx::tc_fence_after_sync();
+
+      const int row = m0 + quarter * 32 + lane;
+      // where this row goes
+      bool row_valid = row < args.rows;
+      bool write_zero_row = false;
+      long long out_base = 0;  // element offset of (row, channel 0)
+      long long chan_stride = 1;
+      if (args.out_mode == IGEMM_OUT_ROWMAJOR) {
+        out_base = (long long)row * args.ldc;
+      } else {
+        const int img = row / args.img_rows;
+        const int rem = row - img * args.img_rows;
+        const int hp = rem / args.row_pitch;
+        const int wp = rem - hp * args.row_pitch;
+        const int h = hp - args.border_h, w = wp - args.border_w;
+        const bool interior = row_valid && h >= 0 && h < args.out_h && w >= 0 && w < args.out_w;
+        if (args.out_mode == IGEMM_OUT_NCHW) {
+          row_valid = interior;
+          out_base = ((long long)img * args.n * args.out_h + h) * args.out_w + w;
+          chan_stride = (long long)args.out_h * args.out_w;
+        } else {  // zero-bordered NHWC: border rows are written as zeros
+          out_base = (long long)row * args.ldc;
+          write_zero_row = row_valid && !interior;
+          row_valid = interior;
+        }
+      }
+
+#pragma unroll 1
+      for (int cc = 0; cc < BLOCK_N / 32; ++cc) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + cc * 32), r);
+        ptx::tmem_ld_wait();
+        if (cc == BLOCK_N / 32 - 1) {
+          // every column of this accumulator buffer is now in registers: hand it back to the MMA warp
+          ptx::tc_fence_before_sync();
+          ptx::mbar_arrive(tmem_empty_bar(acc));
+        }
+        const int cbase = cc * 32;
+        if (n0 + cbase >= args.n) continue;
+        int32_t q[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          int32_t a = (int32_t)r[j] + chan_bias[cbase + j];
+          if (e.relu == B200Q_RELU_BEFORE_REQUANT && a < 0) a = 0;
+          q[j] = requant_value<DIALECT, RMODE>(a, chan_mult[cbase + j], chan_shift[cbase + j], e);
+        }
+        const int ncols = min(32, args.n - (n0 + cbase));
+        if (args.out_mode == IGEMM_OUT_NCHW) {
+          if (row_valid) {
+            if (e.out_dtype == B200Q_DT_I8 || e.out_dtype == B200Q_DT_U8) {
+              uint8_t* o = reinterpret_cast<uint8_t*>(args.out) + out_base + (long long)(n0 + cbase) * chan_stride;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncols) o[(long long)j * chan_stride] = (uint8_t)q[j];
+            } else if (e.out_dtype == B200Q_DT_I32) {
+              int32_t* o = reinterpret_cast<int32_t*>(args.out) + out_base + (long long)(n0 + cbase) * chan_stride;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncols) o[(long long)j * chan_stride] = q[j];
+            } else {
+              uint16_t* o = reinterpret_cast<uint16_t*>(args.out) + out_base + (long long)(n0 + cbase) * chan_stride;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncols) o[(long long)j * chan_stride] = (uint16_t)q[j];
+            }
+          }
+        } else if (row_valid || write_zero_row) {
+          if (write_zero_row) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) q[j] = 0;
+          }
+          const long long off = out_base + n0 + cbase;
+          if (e.out_dtype == B200Q_DT_I8 || e.out_dtype == B200Q_DT_U8) {
+            uint8_t* o = reinterpret_cast<uint8_t*>(args.out) + off;
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+              uint32_t p[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                p[j] = (uint32_t)(q[4 * j] & 0xff) | ((uint32_t)(q[4 * j + 1] & 0xff) << 8) |
+                       ((uint32_t)(q[4 * j + 2] & 0xff) << 16) | ((uint32_t)(q[4 * j + 3] & 0xff) << 24);
+              reinterpret_cast<uint4*>(o)[0] = make_uint4(p[0], p[1], p[2], p[3]);
+              reinterpret_cast<uint4*>(o)[1] = make_uint4(p[4], p[5], p[6], p[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncols) o[j] = (uint8_t)q[j];
+            }
+          } else if (e.out_dtype == B200Q_DT_I32) {
+            int32_t* o = reinterpret_cast<int32_t*>(args.out) + off;
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<int4*>(o)[j] = make_int4(q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncols) o[j] = q[j];
+            }
+          } else {
+            uint16_t* o = reinterpret_cast<uint16_t*>(args.out) + off;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) o[j] = (uint16_t)q[j];
+          }
+        }
+      }
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, TmemCols<BLOCK_N>::value);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0 && args.status != nullptr) atomicCAS(args.status, 0, *abort_flag);
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+// 2-D uint8 tensor [outer][inner] with row pitch `pitch` bytes, box {128 bytes, box_rows}, 128-byte swizzle.
+int make_tmap_u8_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch,
+                    uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return set_error(B200Q_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch & 15) != 0)
+    return set_error(B200Q_ERR_INVALID, "TMA operand needs a 16-byte aligned base and row pitch (base %p pitch %llu)",
+                     base, (unsigned long long)pitch);
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch};
+  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(B200Q_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return B200Q_OK;
+}
+
+template <int BLOCK_N, int STAGES, int DIALECT, int RMODE>
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& args, int grid, cudaStream_t stream) {
+  using L = SmemLayout<BLOCK_N, STAGES>;
+  auto kfn = igemm_i8_kernel<BLOCK_N, STAGES, DIALECT, RMODE>;
+  CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+  kfn<<<grid, NUM_THREADS, L::DYN_BYTES, stream>>>(ta, tb, args);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+template <int BLOCK_N, int STAGES>
+int launch_dialect(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& a, int grid, cudaStream_t s) {
+  const int d = a.epi.dialect, r = a.epi.round_mode;
+  if (d == B200Q_RQ_MULTIPLIER_SHIFT && r == B200Q_ROUND_HALF_UP)
+    return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP>(ta, tb, a, grid, s);
+  if (d == B200Q_RQ_QDM && r == B200Q_ROUND_HALF_AWAY_FROM_ZERO)
+    return launch_one<BLOCK_N, STAGES, B200Q_RQ_QDM, B200Q_ROUND_HALF_AWAY_FROM_ZERO>(ta, tb, a, grid, s);
+  return launch_one<BLOCK_N, STAGES, -1, -1>(ta, tb, a, grid, s);
+}
+
+}  // namespace
+
+int igemm_i8_tcgen05_supported(const IGemmProblem& p, const char** why) {
+  const char* w = nullptr;
+  if (p.k_per_tap % 16 != 0) w = "K (channels per filter tap) must be a multiple of 16 bytes";
+  else if (p.taps_h * p.taps_w > 1 && p.k_per_tap % BLOCK_K != 0) w = "multi-tap convolution needs C % 128 == 0";
+  else if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15)) w = "unaligned operand";
+  else if (p.a_pitch % 16 != 0 || p.b_pitch % 16 != 0) w = "operand row pitch must be a multiple of 16 bytes";
+  else if (p.rows <= 0 || p.n <= 0) w = "empty problem";
+  if (why) *why = w;
+  return w == nullptr;
+}
+
+// Launch the tcgen05 implicit GEMM.  Asynchronous on `stream`; `status` (device int, may be null) receives a
+// non-zero code if a bounded wait inside the kernel ran out.
+int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* status, cudaStream_t stream) {
+  const char* why = nullptr;
+  if (!igemm_i8_tcgen05_supported(p, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "tcgen05 igemm: %s", why);
+  const int block_n = p.n > 128 ? 256 : (p.n > 64 ? 128 : 64);
+  const int kb_per_tap = (p.k_per_tap + BLOCK_K - 1) / BLOCK_K;
+
+  IGemmArgs a{};
+  a.rows = p.rows;
+  a.n = p.n;
+  a.kb_per_tap = kb_per_tap;
+  a.taps_w = p.taps_w;
+  a.num_kb = kb_per_tap * p.taps_h * p.taps_w;
+  a.tap_org_h = p.pad_top;
+  a.tap_org_w = p.pad_left;
+  a.row_pitch = p.row_pitch > 0 ? p.row_pitch : 1;
+  a.out_mode = p.out_mode;
+  a.img_rows = p.img_rows > 0 ? p.img_rows : 1;
+  a.border_h = p.border_h;
+  a.border_w = p.border_w;
+  a.out_h = p.out_h;
+  a.out_w = p.out_w;
+  a.ldc = p.ldc;
+  a.out = p.out;
+  a.epi = epi;
+  a.status = status;
+  a.idesc = ptx::make_idesc(2u, p.a_unsigned ? 0u : 1u, p.b_unsigned ? 0u : 1u, BLOCK_M, (uint32_t)block_n);
+  a.num_m_tiles = (p.rows + BLOCK_M - 1) / BLOCK_M;
+  a.num_n_tiles = (p.n + block_n - 1) / block_n;
+
+  CUtensorMap ta, tb;
+  int rc = make_tmap_u8_2d(&ta, p.a, (uint64_t)p.k_per_tap, (uint64_t)p.rows, (uint64_t)p.a_pitch, BLOCK_M);
+  if (rc) return rc;
+  // B: [n][taps * k_per_tap]; with several taps k_per_tap is a multiple of BLOCK_K so blocks never straddle taps
+  rc = make_tmap_u8_2d(&tb, p.b, (uint64_t)p.k_per_tap * p.taps_h * p.taps_w, (uint64_t)p.n, (uint64_t)p.b_pitch,
+                       (uint32_t)block_n);
+  if (rc) return rc;
+
+  int dev = 0, sms = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int tiles = a.num_m_tiles * a.num_n_tiles;
+  const int grid = tiles < sms ? tiles : sms;
+  switch (block_n) {
+    case 256: return launch_dialect<256, 4>(ta, tb, a, grid, stream);
+    case 128: return launch_dialect<128, 6>(ta, tb, a, grid, stream);
+    default: return launch_dialect<64, 8>(ta, tb, a, grid, stream);
+  }
+}
+
+}  // namespace b200q

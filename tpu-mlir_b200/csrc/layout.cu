@@ -1,0 +1,156 @@
+// Data-movement kernels around the tensor-core path: layout changes between the interpreter's NCHW
+// tensors and the zero-bordered NHWC image the implicit GEMM reads, weight repacking (once per op),
+// and the float <-> native-integer conversions of the operator face (the interpreter keeps every tensor,
+// integer ones included, as float: bindings/pymlir/host/ModuleInterpreter.cpp:396-492).
+#include "internal.h"
+#include "layout.h"
+
+namespace b200q {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ uint8_t to_byte(T v);
+template <>
+__device__ __forceinline__ uint8_t to_byte<uint8_t>(uint8_t v) { return v; }
+template <>
+__device__ __forceinline__ uint8_t to_byte<float>(float v) { return (uint8_t)(int)v; }  // integral by contract
+
+// x[N][C][H][W] -> y[N][H+2bh][W+2bw][C] interior (the border is zeroed once when the buffer is created).
+// Tile of 32 channels x 32 pixels of one image row through shared memory: reads run along W, writes along C.
+template <typename T>
+__global__ void nchw_to_bordered_nhwc_kernel(const T* __restrict__ x, uint8_t* __restrict__ y, int C, int H, int W,
+                                             int bh, int bw) {
+  __shared__ uint8_t tile[32][33];
+  const int Wp = W + 2 * bw, Hp = H + 2 * bh;
+  const int w0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int nh = blockIdx.z;
+  const int n = nh / H, h = nh - n * H;
+  const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+  for (int i = ty; i < 32; i += 8) {
+    const int c = c0 + i, w = w0 + tx;
+    tile[i][tx] = (c < C && w < W) ? to_byte<T>(x[(((long long)n * C + c) * H + h) * W + w]) : (uint8_t)0;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int w = w0 + i, c = c0 + tx;
+    if (w < W && c < C) y[(((long long)n * Hp + (h + bh)) * Wp + (w + bw)) * C + c] = tile[tx][i];
+  }
+}
+
+// w[OC][IC][KH][KW] -> wr[OC][KH*KW][IC]  (K-major rows for the implicit GEMM: k = tap * IC + ic)
+template <typename T>
+__global__ void repack_weight_kernel(const T* __restrict__ w, uint8_t* __restrict__ wr, int OC, int IC, int KHW) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)OC * IC * KHW;
+  if (idx >= total) return;
+  const int ic = (int)(idx % IC);
+  const int tap = (int)((idx / IC) % KHW);
+  const int oc = (int)(idx / ((long long)IC * KHW));
+  wr[idx] = to_byte<T>(w[((long long)oc * IC + ic) * KHW + tap]);
+}
+
+// [rows][cols] bytes -> [cols][rows] bytes
+template <typename T>
+__global__ void transpose_to_u8_kernel(const T* __restrict__ src, uint8_t* __restrict__ dst, int rows, int cols) {
+  __shared__ uint8_t tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  for (int i = ty; i < 32; i += 8) {
+    const int r = r0 + i, c = c0 + tx;
+    tile[i][tx] = (r < rows && c < cols) ? to_byte<T>(src[(long long)r * cols + c]) : (uint8_t)0;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int c = c0 + i, r = r0 + tx;
+    if (c < cols && r < rows) dst[(long long)c * rows + r] = tile[tx][i];
+  }
+}
+
+__global__ void f32_to_q8_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = (uint8_t)(int)x[i];
+}
+__global__ void f32_to_i32_kernel(const float* __restrict__ x, int32_t* __restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = (int32_t)x[i];
+}
+__global__ void q_to_f32_kernel(const void* __restrict__ x, int dt, float* __restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  switch (dt) {
+    case B200Q_DT_I8: y[i] = (float)reinterpret_cast<const int8_t*>(x)[i]; break;
+    case B200Q_DT_U8: y[i] = (float)reinterpret_cast<const uint8_t*>(x)[i]; break;
+    case B200Q_DT_I16: y[i] = (float)reinterpret_cast<const int16_t*>(x)[i]; break;
+    case B200Q_DT_U16: y[i] = (float)reinterpret_cast<const uint16_t*>(x)[i]; break;
+    default: y[i] = (float)reinterpret_cast<const int32_t*>(x)[i]; break;
+  }
+}
+
+inline unsigned blocks_for(long long n, int threads) { return (unsigned)((n + threads - 1) / threads); }
+
+}  // namespace
+
+int nchw_to_bordered_nhwc(const void* x, int x_is_f32, void* y, int N, int C, int H, int W, int bh, int bw,
+                          cudaStream_t s) {
+  if ((long long)N * H > 65535LL * 32767) return set_error(B200Q_ERR_UNSUPPORTED, "layout: N*H too large");
+  dim3 grid(ceil_div(W, 32), ceil_div(C, 32), N * H), block(32, 8);
+  if (grid.y > 65535 || grid.z > 65535) {
+    // fold: z is limited to 65535; large batches are split
+    const int per = 65535 / H > 0 ? 65535 / H : 1;
+    for (int n0 = 0; n0 < N; n0 += per) {
+      const int nn = (N - n0) < per ? (N - n0) : per;
+      const long long xin = (long long)n0 * C * H * W, yout = (long long)n0 * (H + 2 * bh) * (W + 2 * bw) * C;
+      B200Q_TRY(nchw_to_bordered_nhwc(x_is_f32 ? (const void*)((const float*)x + xin) : (const void*)((const uint8_t*)x + xin),
+                                      x_is_f32, (uint8_t*)y + yout, nn, C, H, W, bh, bw, s));
+    }
+    return B200Q_OK;
+  }
+  if (x_is_f32)
+    nchw_to_bordered_nhwc_kernel<float><<<grid, block, 0, s>>>((const float*)x, (uint8_t*)y, C, H, W, bh, bw);
+  else
+    nchw_to_bordered_nhwc_kernel<uint8_t><<<grid, block, 0, s>>>((const uint8_t*)x, (uint8_t*)y, C, H, W, bh, bw);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int repack_weight_oihw(const void* w, int w_is_f32, void* wr, int OC, int IC, int KH, int KW, cudaStream_t s) {
+  const long long total = (long long)OC * IC * KH * KW;
+  if (total == 0) return B200Q_OK;
+  if (w_is_f32)
+    repack_weight_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)w, (uint8_t*)wr, OC, IC, KH * KW);
+  else
+    repack_weight_kernel<uint8_t><<<blocks_for(total, 256), 256, 0, s>>>((const uint8_t*)w, (uint8_t*)wr, OC, IC, KH * KW);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int transpose_to_u8(const void* src, int src_is_f32, void* dst, int rows, int cols, cudaStream_t s) {
+  if (rows == 0 || cols == 0) return B200Q_OK;
+  dim3 grid(ceil_div(cols, 32), ceil_div(rows, 32)), block(32, 8);
+  if (grid.y > 65535) return set_error(B200Q_ERR_UNSUPPORTED, "transpose: too many rows");
+  if (src_is_f32) transpose_to_u8_kernel<float><<<grid, block, 0, s>>>((const float*)src, (uint8_t*)dst, rows, cols);
+  else transpose_to_u8_kernel<uint8_t><<<grid, block, 0, s>>>((const uint8_t*)src, (uint8_t*)dst, rows, cols);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int f32_to_q8(const float* x, void* y, long long n, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  f32_to_q8_kernel<<<blocks_for(n, 256), 256, 0, s>>>(x, (uint8_t*)y, n);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+int f32_to_i32(const float* x, int32_t* y, long long n, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  f32_to_i32_kernel<<<blocks_for(n, 256), 256, 0, s>>>(x, y, n);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+int q_to_f32(const void* x, int dt, float* y, long long n, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  q_to_f32_kernel<<<blocks_for(n, 256), 256, 0, s>>>(x, dt, y, n);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+}  // namespace b200q
