@@ -1,0 +1,286 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N=1): BASELINE config 1, one tpu.Conv2D INT8 layer: x s8 NCHW [32,256,56,56], filter s8
+[256,256,3,3], stride 1, pad 1, bias, per-channel QDM requant (multiplier in [2^30,2^31), rshift in [8,20],
+half away from zero), fused ReLU, s8 NCHW output.  One step = one pass of that layer over the batch.
+With N > 1 (torchrun, one rank per GPU) every rank runs its own batch of the same layer (no data-path
+collective; weak scaling) and rank 0 reports the whole-job aggregate.
+
+Printed JSON line: `value` = device-resident TOPS (CUDA events around the device-face call, L2 flushed
+between steps); `e2e` = the same metric through the operator face with pinned HOST float buffers, copies
+included; `roofline` = the tensor-core kernel alone against the dense INT8 peak; `cpu_baseline` = the
+reference's arithmetic route (fp32 oneDNN convolution + requant loop) on the host cores.
+`--impl reference` times only that CPU route, on the full workload, with all host threads.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(N=32, C=256, H=56, W=56, OC=256, KH=3, KW=3)
+WORKLOAD = "tpu.Conv2D int8 NCHW n32 c256 56x56 oc256 k3 s1 p1 relu, per-channel QDM requant (BASELINE config 1)"
+OPS_PER_STEP = 2.0 * CFG["N"] * CFG["OC"] * CFG["H"] * CFG["W"] * CFG["C"] * CFG["KH"] * CFG["KW"]
+METRIC, UNIT = "int8 conv TOPS", "TOPS"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(bf16_tflops=float(d["bf16_tflops"]), hbm_gbs=float(d["hbm_gbs"]), source="measured")
+    return dict(bf16_tflops=1590.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def cpu_route(c, n_images, threads):
+    """The reference's CPU arithmetic for this layer on the first n_images images; returns (seconds, output)."""
+    import oracle
+    x = c["x"][:n_images]
+    kw = dict(pads=(1, 1, 1, 1), do_relu=True, qmode=oracle.QM_QDM, is_cv18xx=True, mult=c["mult"], rshift=c["rshift"],
+              threads=threads)
+    oracle.conv2d_int8_fp32_path(x[:1], c["w"], c["bias"], **kw)   # warm the primitive cache
+    t0 = time.perf_counter()
+    out = oracle.conv2d_int8_fp32_path(x, c["w"], c["bias"], **kw)
+    return time.perf_counter() - t0, out
+
+
+def run_reference(args):
+    """--impl reference: the CPU interpreter's arithmetic route, full workload per step, all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from tpu_mlir_b200 import synth
+    import oracle
+    c = synth.conv2d_int8(seed=1, **CFG)
+    threads = os.cpu_count() or 1
+    kw = dict(pads=(1, 1, 1, 1), do_relu=True, qmode=oracle.QM_QDM, is_cv18xx=True, mult=c["mult"], rshift=c["rshift"],
+              threads=threads)
+    for _ in range(max(args.warmup, 1)):
+        oracle.conv2d_int8_fp32_path(c["x"], c["w"], c["bias"], **kw)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.conv2d_int8_fp32_path(c["x"], c["w"], c["bias"], **kw)
+    dt = (time.perf_counter() - t0) / args.steps
+    tops = OPS_PER_STEP / dt / 1e12
+    line = dict(impl="reference", metric=METRIC, value=tops, unit=UNIT, n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None,
+                dtype="f32 (integer-valued, as the reference interpreter computes)", data="synthetic",
+                config=dict(workload=WORKLOAD, route="fp32 oneDNN convolution (torch CPU) + requant loop"),
+                cpu_baseline=dict(value=tops, unit=UNIT, cores=threads, kind="port",
+                                  sample="full batch of 32 images per step"),
+                e2e=dict(value=tops, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    import tpu_mlir_b200._lib as L
+    from tpu_mlir_b200 import synth
+    from tpu_mlir_b200.ops import Conv2DOp, InferenceParameter
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib = L.lib()
+
+    c = synth.conv2d_int8(seed=1 + rank, **CFG) if rank else synth.conv2d_int8(seed=1, **CFG)
+    op = Conv2DOp(input_shape=c["x"].shape, oc=CFG["OC"], kernel_shape=(3, 3), pads=(1, 1, 1, 1), do_relu=True,
+                  quant_mode=L.QM_QDM, is_cv18xx=True, multiplier=c["mult"], rshift=c["rshift"],
+                  algo=L.ALGO_TENSOR_CORE)
+    stream = torch.cuda.Stream()
+    sptr = C.c_void_p(stream.cuda_stream)
+    w_d = torch.from_numpy(c["w"]).cuda()
+    b_d = torch.from_numpy(c["bias"]).cuda()
+    x_d = torch.from_numpy(c["x"]).cuda()
+    y_d = torch.empty(op.out_shape, dtype=torch.int8, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")   # > 126 MB L2
+    h = C.c_void_p()
+    L.check(lib.b200q_conv2d_dev_create(C.byref(op.desc), C.c_void_p(w_d.data_ptr()), C.c_void_p(b_d.data_ptr()),
+                                        C.byref(h)))
+    L.check(lib.b200q_conv2d_dev_set_profiling(h, 1))
+
+    def step_device():
+        L.check(lib.b200q_conv2d_dev_run(h, C.c_void_p(x_d.data_ptr()), C.c_void_p(y_d.data_ptr()), sptr))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            flush.fill_(1)
+            step_device()
+        L.check(lib.b200q_conv2d_dev_status(h, sptr))
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        step_ms, layout_ms, kernel_ms = [], [], []
+        lm, km = C.c_float(), C.c_float()
+        for _ in range(args.steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            step_device()
+            e1.record(stream)
+            e1.synchronize()
+            step_ms.append(e0.elapsed_time(e1))
+            L.check(lib.b200q_conv2d_dev_last_times(h, C.byref(lm), C.byref(km)))
+            layout_ms.append(lm.value)
+            kernel_ms.append(km.value)
+        L.check(lib.b200q_conv2d_dev_status(h, sptr))
+        barrier()
+        clocks = sampler.stop() if rank == 0 else None
+    total_ms = float(np.sum(step_ms))
+    gpu_launches = 2 * args.steps
+
+    # ---- end to end through the operator face: pinned host float buffers, copies inside the timed region
+    e2e = None
+    if not args.skip_e2e:
+        x_h = torch.from_numpy(c["x"]).to(torch.float32).pin_memory()
+        w_h = torch.from_numpy(c["w"]).to(torch.float32)
+        bias_h = torch.from_numpy(c["bias"]).to(torch.float32)
+        y_h = torch.empty(op.out_shape, dtype=torch.float32).pin_memory()
+        p = InferenceParameter(inputs=[x_h.numpy(), w_h.numpy(), bias_h.numpy()], outputs=[y_h.numpy()])
+        op.init(p)
+        for _ in range(3):
+            op.inference(p)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            op.inference(p)          # synchronous: H2D, layout, conv, D2H
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        op.deinit(p)
+        same = bool(np.array_equal(y_h.numpy(), y_d.cpu().numpy().astype(np.float32)))
+        if not same:
+            raise SystemExit("operator face and device face disagree")
+        e2e = dict(s=e2e_s, h2d=int(x_h.numel() * 4), d2h=int(y_h.numel() * 4))
+        gpu_launches += 3 * args.steps      # f32->bordered layout, conv, int8->f32
+
+    # ---- aggregate over ranks (max time)
+    t = torch.tensor([total_ms, e2e["s"] if e2e else 0.0], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_s = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peaks = measured_peaks()
+        int8_peak = 2.0 * peaks["bf16_tflops"]
+        value = world * OPS_PER_STEP * args.steps / (total_ms * 1e-3) / 1e12
+        k_ms = float(np.mean(kernel_ms))
+        achieved = OPS_PER_STEP / (k_ms * 1e-3) / 1e12
+        line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
+                    ms_per_step=total_ms / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
+                    dtype="s8 x s8 -> s32 accumulate -> s8", data="synthetic",
+                    config=dict(workload=WORKLOAD, l2="flushed between steps (256 MiB write)",
+                                per_step_kernels=dict(layout_ms=float(np.mean(layout_ms)), conv_ms=k_ms)),
+                    roofline=dict(bound="tensor", achieved=achieved, peak=int8_peak, unit="TOPS",
+                                  frac=achieved / int8_peak, traffic=None,
+                                  peak_basis=f"2 x {peaks['source']} dense bf16 ({peaks['bf16_tflops']} TFLOP/s); "
+                                             "no measured INT8 figure exists"),
+                    clocks=clocks, gpu_launches=gpu_launches)
+        if e2e:
+            line["e2e"] = dict(value=world * OPS_PER_STEP * args.steps / e2e_s / 1e12, unit=UNIT,
+                               h2d_bytes_per_step=e2e["h2d"], d2h_bytes_per_step=e2e["d2h"],
+                               ms_per_step=e2e_s / args.steps * 1e3,
+                               api="b200q_conv2d_inference (host float32 buffers, pinned)")
+        if not args.skip_cpu and world >= 1:
+            n_img = 8
+            threads = os.cpu_count() or 1
+            secs, out = cpu_route(c, n_img, threads)
+            if not np.array_equal(out, y_d[:n_img].cpu().numpy()):
+                raise SystemExit("GPU result differs from the CPU route on the sampled images")
+            line["cpu_baseline"] = dict(value=OPS_PER_STEP * n_img / CFG["N"] / secs / 1e12, unit=UNIT, cores=threads,
+                                        kind="port", sample=f"first {n_img} of 32 images, fp32 oneDNN conv + requant "
+                                                            f"loop, {secs:.3f} s")
+        print(json.dumps(line))
+    lib.b200q_conv2d_dev_destroy(C.byref(h))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -186,6 +186,11 @@ int b200q_conv2d_dev_create(const b200q_conv2d_desc *desc, const void *filter_oi
 int b200q_conv2d_dev_run(void *handle, const void *x_nchw, void *y_nchw, void *stream);
 int b200q_conv2d_dev_status(void *handle, void *stream);
 void b200q_conv2d_dev_destroy(void **handle);
+/* Optional timing of the device face: when enabled, b200q_conv2d_dev_run records CUDA events on its stream
+ * around the layout kernel and the tensor-core kernel; b200q_conv2d_dev_last_times waits for the last run and
+ * returns both durations in milliseconds.  (The reference has no counterpart; its CUDA path is untimed.) */
+int b200q_conv2d_dev_set_profiling(void *handle, int enable);
+int b200q_conv2d_dev_last_times(void *handle, float *layout_ms, float *kernel_ms);
 
 #ifdef __cplusplus
 }

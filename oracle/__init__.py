@@ -66,6 +66,8 @@ def lib():
                                       i32, vp, vp, f32, i32, i32, vp]
         L.orc_conv2d_int8.restype = i64
         L.orc_conv2d_int8.argtypes = [vp, i32, vp, vp] + [i64] * 16 + [i32, i32, i32, i32, vp, vp, i64, i32, i32, vp]
+        L.orc_conv_requant_from_f32.restype = None
+        L.orc_conv_requant_from_f32.argtypes = [vp, vp, i64, i64, i64, i32, i32, i32, vp, vp, i64, i32, i32, vp]
         L.orc_requant_int_axis.restype = None
         L.orc_requant_int_axis.argtypes = [vp, i64, i64, i64, vp, i32, i32, i32, i32, i32, vp]
         L.orc_requant_int.restype = None
@@ -184,6 +186,35 @@ def conv2d_int8(x, w, bias=None, *, stride=(1, 1), pads=(0, 0, 0, 0), dilation=(
                                  dilation[0], dilation[1], pht, phb, pwl, pwr, groups, pad_value, int(do_relu),
                                  qmode, int(is_cv18xx), _p(mult), _p(rshift), rshift.size, out_zp, out_dt, _p(out))
     return (out, int(viol)) if return_violations else out
+
+
+def conv2d_int8_fp32_path(x, w, bias=None, *, stride=(1, 1), pads=(0, 0, 0, 0), dilation=(1, 1), groups=1,
+                          do_relu=False, qmode=QM_MULTIPLIER_SHIFT, is_cv18xx=False, mult=None, rshift=None, out_zp=0,
+                          out_dt=DT_I8, threads=None):
+    """The reference's own arithmetic route for an INT8 Conv2D: an fp32 oneDNN convolution over integer-valued
+    floats (lib/Support/Dnnl/Conv.cpp:98-145,:234-253; here torch's CPU convolution, the same primitive family)
+    followed by the float-plus-bias requant loop (Conv2D.cpp:295-341).  Symmetric zero padding only.
+    This is what the CPU baseline times."""
+    import torch
+    import torch.nn.functional as F
+    if threads:
+        torch.set_num_threads(int(threads))
+    xf = torch.from_numpy(np.ascontiguousarray(x)).to(torch.float32)
+    wf = torch.from_numpy(np.ascontiguousarray(w)).to(torch.float32)
+    pht, phb, pwl, pwr = pads
+    if pht != phb or pwl != pwr:
+        xf = F.pad(xf, (pwl, pwr, pht, phb))
+        padding = (0, 0)
+    else:
+        padding = (pht, pwl)
+    acc = F.conv2d(xf, wf, None, stride=stride, padding=padding, dilation=dilation, groups=groups).contiguous().numpy()
+    n, oc, oh, ow = acc.shape
+    mult = _c(np.atleast_1d(mult), np.int64)
+    rshift = _c(np.atleast_1d(rshift), np.int64)
+    out = np.empty(acc.shape, dtype=_NP_OF_DT[out_dt])
+    lib().orc_conv_requant_from_f32(_p(acc), _p(_c(bias, np.int32)), n, oc, oh * ow, int(do_relu), qmode,
+                                    int(is_cv18xx), _p(mult), _p(rshift), rshift.size, out_zp, out_dt, _p(out))
+    return out
 
 
 def requant_int_axis(x, quant3, *, qmode, rmode, fuse_rq_axis=False, in_zp=0, out_dt=DT_I8):

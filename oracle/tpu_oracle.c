@@ -282,7 +282,7 @@ int64_t orc_conv2d_int8(const void *x, int x_unsigned, const int8_t *w, const in
         int64_t tmp = (int64_t)acc[p] + b;
         int64_t a1 = acc[p] < 0 ? -(int64_t)acc[p] : acc[p], a2 = tmp < 0 ? -tmp : tmp;
         (void)absmax;
-        if (a1 >= FP32_EXACT_LIMIT || a2 >= FP32_EXACT_LIMIT) viol++;
+        if (a1 >= FP32_EXACT_LIMIT || a2 >= FP32_EXACT_LIMIT || (b < 0 ? -(int64_t)b : b) >= FP32_EXACT_LIMIT) viol++;
         int64_t v = orc_apply_multiplier_rshift(tmp, multi, shift, qmode, rmode, is_cv18xx) + out_zp;
         if (do_relu && v < out_zp) v = out_zp;
         store_q(out, (in * oc + o) * oh * ow + p, out_dt, orc_saturate(v, out_dt));
@@ -292,6 +292,34 @@ int64_t orc_conv2d_int8(const void *x, int x_unsigned, const int8_t *w, const in
     }
   }
   return viol;
+}
+
+/*
+ * The requant half of tpu::Conv2DOp::inference alone (Conv2D.cpp:295-341), applied to the float output of
+ * an fp32 convolution the way the reference does it: `int64_t tmp = p.outputs[0][offset] + bias` is a FLOAT
+ * addition of the float accumulator and the int32 bias (:331).  Used with an fp32 oneDNN convolution
+ * (torch on CPU) to time the reference's own arithmetic path.
+ */
+void orc_conv_requant_from_f32(const float *acc, const int32_t *bias, int64_t n, int64_t oc, int64_t hw, int do_relu,
+                               int qmode, int is_cv18xx, const int64_t *mult, const int64_t *rshift, int64_t n_q,
+                               int out_zp, int out_dt, void *out) {
+  const int per_axis = (n_q == oc);
+  const int is_tf = (qmode == QM_QDM || qmode == QM_TFLITE || qmode == QM_TFLITE_LSHIFT);
+  const int rmode = is_tf ? RM_HALF_AWAY : RM_HALF_UP;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t in = 0; in < n; ++in)
+    for (int64_t o = 0; o < oc; ++o) {
+      const int64_t shift = per_axis ? rshift[o] : rshift[0];
+      const int64_t multi = (qmode == QM_ONLY_SHIFT) ? 1 : (per_axis ? mult[o] : mult[0]);
+      const int32_t b = bias ? bias[o] : 0;
+      for (int64_t p = 0; p < hw; ++p) {
+        const int64_t off = (in * oc + o) * hw + p;
+        int64_t tmp = (int64_t)(acc[off] + (float)b);
+        int64_t v = orc_apply_multiplier_rshift(tmp, multi, shift, qmode, rmode, is_cv18xx) + out_zp;
+        if (do_relu && v < out_zp) v = out_zp;
+        store_q(out, off, out_dt, orc_saturate(v, out_dt));
+      }
+    }
 }
 
 /*

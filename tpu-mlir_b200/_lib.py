@@ -73,6 +73,8 @@ SIGNATURES = {
     "b200q_conv2d_dev_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200q_conv2d_dev_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200q_conv2d_dev_destroy": (None, [_VPP]),
+    "b200q_conv2d_dev_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
+    "b200q_conv2d_dev_last_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
 }
 
 

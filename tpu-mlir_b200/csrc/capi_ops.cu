@@ -235,6 +235,13 @@ struct ConvHandle {
   DevBuf w_oihw, w_packed, bias, mult, shift, x_bordered, status;
   // operator-face staging
   DevBuf x_f32, x_q8, y_q, y_f32, w_f32, bias_f32;
+  // optional per-kernel timing of the device face
+  bool profiling = false;
+  cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+  ~ConvHandle() {
+    for (auto& e : ev)
+      if (e) cudaEventDestroy(e);
+  }
 };
 
 int conv_out_dims(const b200q_conv2d_desc& d, int64_t* oh, int64_t* ow) {
@@ -305,7 +312,9 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
   const b200q_conv2d_desc& d = h->d;
   if (d.n == 0) return B200Q_OK;
   if (h->use_tc) {
+    if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[0], s));
     B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
+    if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[1], s));
     IGemmProblem p{};
     p.a = h->x_bordered.p;
     p.b = h->w_packed.p;
@@ -331,7 +340,9 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.out_mode = IGEMM_OUT_NCHW;
     p.ldc = 0;
     p.out = y;
-    return igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s);
+    B200Q_TRY(igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s));
+    if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[2], s));
+    return B200Q_OK;
   }
   const void* xin = x;
   if (x_is_f32) {
@@ -542,5 +553,25 @@ int b200q_conv2d_dev_status(void* handle, void* stream) {
 }
 
 void b200q_conv2d_dev_destroy(void** handle) { b200q_conv2d_deinit(handle); }
+
+int b200q_conv2d_dev_set_profiling(void* handle, int enable) {
+  if (!handle) return set_error(B200Q_ERR_INVALID, "conv2d_dev_set_profiling: null handle");
+  ConvHandle* h = static_cast<ConvHandle*>(handle);
+  if (enable)
+    for (auto& e : h->ev)
+      if (!e) CUDA_TRY(cudaEventCreate(&e));
+  h->profiling = enable != 0;
+  return B200Q_OK;
+}
+
+int b200q_conv2d_dev_last_times(void* handle, float* layout_ms, float* kernel_ms) {
+  if (!handle || !layout_ms || !kernel_ms) return set_error(B200Q_ERR_INVALID, "conv2d_dev_last_times: null argument");
+  ConvHandle* h = static_cast<ConvHandle*>(handle);
+  if (!h->profiling || !h->use_tc) return set_error(B200Q_ERR_INVALID, "conv2d_dev_last_times: profiling is off or the op runs on the CUDA-core kernel");
+  CUDA_TRY(cudaEventSynchronize(h->ev[2]));
+  CUDA_TRY(cudaEventElapsedTime(layout_ms, h->ev[0], h->ev[1]));
+  CUDA_TRY(cudaEventElapsedTime(kernel_ms, h->ev[1], h->ev[2]));
+  return B200Q_OK;
+}
 
 }  // extern "C"

@@ -5,7 +5,7 @@
 //               shared-memory ring, completion counted on mbarriers;
 //   warp 1      allocates TMEM and issues tcgen05.mma (one thread), int32 accumulators live in TMEM,
 //               two accumulator buffers so the next tile's MMAs overlap this tile's epilogue;
-//   warps 2..5  epilogue: tcgen05.ld the accumulator, + bias, ReLU, exact requantisation
+//   warps 2..   epilogue (one warp per 32 TMEM lanes x 64 columns, 16 warps for a 128 x 256 tile): tcgen05.ld the accumulator, + bias, ReLU, exact requantisation
 //               (requant.cuh), saturate, store as [rows, N], as NCHW, or as zero-bordered NHWC.
 //
 // The convolution is expressed as a GEMM whose A rows are the pixels of a zero-bordered NHWC image
@@ -29,8 +29,7 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;  // bytes == int8 elements: one 128-byte swizzle span
 constexpr int UMMA_K = 32;    // K of one tcgen05.mma for 8-bit operands
-constexpr int NUM_EPI_WARPS = 4;
-constexpr int NUM_THREADS = 64 + NUM_EPI_WARPS * 32;
+constexpr int EPI_COLS_PER_WARP = 64;  // each epilogue warp owns 32 TMEM lanes x 64 columns of the tile
 constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate tile time
 
 template <int BLOCK_N, int STAGES>
@@ -41,9 +40,13 @@ struct SmemLayout {
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;  // tmem ptr, abort flag
-  static constexpr int CHAN_OFFSET = MISC_OFFSET + 16;           // bias / multiplier / shift of the tile's channels
-  static constexpr int TOTAL = CHAN_OFFSET + 3 * BLOCK_N * 4;
+  static constexpr int CHAN_OFFSET = MISC_OFFSET + 16;           // {bias, multiplier, shift, -} of the tile's channels
+  static constexpr int SLOW_OFFSET = CHAN_OFFSET + BLOCK_N * 16;  // per 32-channel chunk: needs the general requant path
+  static constexpr int TOTAL = SLOW_OFFSET + (BLOCK_N / 32) * 4;
   static constexpr int DYN_BYTES = TOTAL + 1024;                 // slack for manual 1024-byte alignment
+  // one epilogue warp per (TMEM lane quarter, 64-column group): 16 warps for BLOCK_N = 256
+  static constexpr int EPI_WARPS = 4 * (BLOCK_N / EPI_COLS_PER_WARP);
+  static constexpr int NUM_THREADS = 64 + EPI_WARPS * 32;
 };
 
 template <int BLOCK_N>
@@ -51,10 +54,48 @@ struct TmemCols {
   static constexpr int value = (2 * BLOCK_N) < 32 ? 32 : 2 * BLOCK_N;  // power of two for BLOCK_N in {16,...,256}
 };
 
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory"); }
+template <int THREADS>
+__device__ __forceinline__ void epi_bar_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
+}
+
+
+__device__ __forceinline__ int32_t add_sat_s32(int32_t a, int32_t b) {
+  int32_t r;
+  asm("add.sat.s32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// Fast requantisation cores for the two forms real graphs use.  They are exact restatements of
+// requant_value<> restricted to a parameter domain that is checked per channel when the channel
+// parameters are staged in shared memory (anything outside takes the general path):
+//   QDM, half away from zero:   multiplier != INT32_MIN, right shift t in [1,31]   (p0 = t, p1 = 2^(t-1))
+//   MultiplierShift, half up:   right shift s in [1,62]                            (p0 = s)
+// Both return a value clamped to int32; zero point, ReLU and the output saturation follow in 32 bits.
+template <int DIALECT>
+__device__ __forceinline__ int32_t requant_core_fast(int32_t a, int32_t m, int32_t p0, int32_t p1) {
+  if (DIALECT == B200Q_RQ_QDM) {
+    const int64_t x = (int64_t)a * (int64_t)m + (1ll << 30);  // floor((a*m + 2^30) / 2^31) == half-up shift by 31
+    const int32_t v = (int32_t)(x >> 31);                     // |a*m| <= 2^62 - 2^31: always fits int32 here
+    const int32_t mant = v & ((p1 << 1) - 1);
+    const int32_t ge0 = (int32_t)((uint32_t)(~v) >> 31);
+    return (v >> p0) + (int32_t)((mant + ge0) > p1);
+  } else {
+    int64_t x = (int64_t)a * (int64_t)m;
+    x = (x + (int64_t)(1ull << (p0 - 1))) >> p0;
+    return x > 2147483647ll ? 2147483647 : (x < -2147483648ll ? (int32_t)(-2147483647 - 1) : (int32_t)x);
+  }
+}
+
+template <int DIALECT, int RMODE>
+__device__ __forceinline__ bool fast_domain(int32_t m, int32_t s) {
+  if (DIALECT == B200Q_RQ_QDM && RMODE == B200Q_ROUND_HALF_AWAY_FROM_ZERO) return m != (-2147483647 - 1) && s <= -1 && s >= -31;
+  if (DIALECT == B200Q_RQ_MULTIPLIER_SHIFT && RMODE == B200Q_ROUND_HALF_UP) return s >= 1 && s <= 62;
+  return false;
+}
 
 template <int BLOCK_N, int STAGES, int DIALECT, int RMODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(SmemLayout<BLOCK_N, STAGES>::NUM_THREADS, 1)
 igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const IGemmArgs args) {
   using L = SmemLayout<BLOCK_N, STAGES>;
@@ -68,9 +109,9 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFFSET + 4);
-  int32_t* chan_bias = reinterpret_cast<int32_t*>(smem + L::CHAN_OFFSET);
-  int32_t* chan_mult = chan_bias + BLOCK_N;
-  int32_t* chan_shift = chan_mult + BLOCK_N;
+  int4* chan = reinterpret_cast<int4*>(smem + L::CHAN_OFFSET);
+  int* chunk_slow = reinterpret_cast<int*>(smem + L::SLOW_OFFSET);
+  constexpr int EPI_THREADS = L::EPI_WARPS * 32;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -82,7 +123,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tmem_full_bar(a), 1);
-      ptx::mbar_init(tmem_empty_bar(a), NUM_EPI_WARPS * 32);
+      ptx::mbar_init(tmem_empty_bar(a), EPI_THREADS);
     }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -172,9 +213,26 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
-    const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. 32*quarter+31
+    const int quarter = warp & 3;                                   // TMEM lanes 32*quarter .. 32*quarter+31
+    const int col0 = ((warp - 2) >> 2) * EPI_COLS_PER_WARP;         // first tile column of this warp
     const int etid = threadIdx.x - 64;
     const Epilogue& e = args.epi;
+    const bool out8 = e.out_dtype == B200Q_DT_I8 || e.out_dtype == B200Q_DT_U8;
+    // the fast cores need an output type whose range lies inside int32 after the zero point is added
+    constexpr bool kFastCompiled = (DIALECT == B200Q_RQ_QDM && RMODE == B200Q_ROUND_HALF_AWAY_FROM_ZERO) ||
+                                   (DIALECT == B200Q_RQ_MULTIPLIER_SHIFT && RMODE == B200Q_ROUND_HALF_UP);
+    const bool kFastDialect = kFastCompiled && e.out_dtype != B200Q_DT_I32;
+    const int32_t zp = e.out_zp;
+    const int32_t floor_pre = e.relu == B200Q_RELU_BEFORE_REQUANT ? 0 : (-2147483647 - 1);
+    const int32_t floor_post = e.relu == B200Q_RELU_AFTER_REQUANT ? zp : (-2147483647 - 1);
+    int32_t sat_lo, sat_hi;
+    switch (e.out_dtype) {
+      case B200Q_DT_I8: sat_lo = -128; sat_hi = 127; break;
+      case B200Q_DT_U8: sat_lo = 0; sat_hi = 255; break;
+      case B200Q_DT_I16: sat_lo = -32768; sat_hi = 32767; break;
+      case B200Q_DT_U16: sat_lo = 0; sat_hi = 65535; break;
+      default: sat_lo = -2147483647 - 1; sat_hi = 2147483647; break;
+    }
     int acc = 0;
     uint32_t acc_phase = 0;
     int cached_n0 = -1;
@@ -182,15 +240,25 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int m0 = (tile / args.num_n_tiles) * BLOCK_M;
       const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
       if (n0 != cached_n0) {
-        epi_bar_sync();  // everyone is done reading the previous tile's channel parameters
-        for (int c = etid; c < BLOCK_N; c += NUM_EPI_WARPS * 32) {
+        epi_bar_sync<EPI_THREADS>();  // everyone is done reading the previous tile's channel parameters
+        if (etid < BLOCK_N / 32) chunk_slow[etid] = kFastDialect ? 0 : 1;
+        epi_bar_sync<EPI_THREADS>();
+        for (int c = etid; c < BLOCK_N; c += EPI_THREADS) {
           const int n = n0 + c;
           const bool in = n < args.n;
-          chan_bias[c] = (in && e.bias) ? e.bias[n] : 0;
-          chan_mult[c] = (in && e.multiplier) ? e.multiplier[e.per_channel ? n : 0] : 1;
-          chan_shift[c] = (in && e.shift) ? e.shift[e.per_channel ? n : 0] : 0;
+          const int32_t bias = (in && e.bias) ? e.bias[n] : 0;
+          const int32_t m = (in && e.multiplier) ? e.multiplier[e.per_channel ? n : 0] : 1;
+          const int32_t sh = (in && e.shift) ? e.shift[e.per_channel ? n : 0] : 0;
+          if (kFastDialect && in && fast_domain<DIALECT, RMODE>(m, sh)) {
+            // fast form: {bias, multiplier, right shift, half}
+            const int32_t t = DIALECT == B200Q_RQ_QDM ? -sh : sh;
+            chan[c] = make_int4(bias, m, t, DIALECT == B200Q_RQ_QDM ? (int32_t)(1u << (t - 1)) : 0);
+          } else {
+            chan[c] = make_int4(bias, m, sh, 0);
+            if (kFastDialect && in) atomicOr(&chunk_slow[c >> 5], 1);
+          }
         }
-        epi_bar_sync();
+        epi_bar_sync<EPI_THREADS>();
         cached_n0 = n0;
       }
       if (!ptx::mbar_wait_bounded(tmem_full_bar(acc), acc_phase, abort_flag, 4, WAIT_BUDGET_NS)) break;
@@ -201,7 +269,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       bool row_valid = row < args.rows;
       bool write_zero_row = false;
       long long out_base = 0;  // element offset of (row, channel 0)
-      long long chan_stride = 1;
+      int chan_stride = 1;
       if (args.out_mode == IGEMM_OUT_ROWMAJOR) {
         out_base = (long long)row * args.ldc;
       } else {
@@ -214,7 +282,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         if (args.out_mode == IGEMM_OUT_NCHW) {
           row_valid = interior;
           out_base = ((long long)img * args.n * args.out_h + h) * args.out_w + w;
-          chan_stride = (long long)args.out_h * args.out_w;
+          chan_stride = args.out_h * args.out_w;
         } else {  // zero-bordered NHWC: border rows are written as zeros
           out_base = (long long)row * args.ldc;
           write_zero_row = row_valid && !interior;
@@ -222,81 +290,97 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
       }
 
+      constexpr int CH = 16;  // columns per TMEM load: keeps the epilogue's live registers low
 #pragma unroll 1
-      for (int cc = 0; cc < BLOCK_N / 32; ++cc) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + cc * 32), r);
+      for (int cc = 0; cc < EPI_COLS_PER_WARP / CH; ++cc) {
+        const int cbase = col0 + cc * CH;
+        uint32_t r[CH];
+        ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + cbase), r);
         ptx::tmem_ld_wait();
-        if (cc == BLOCK_N / 32 - 1) {
-          // every column of this accumulator buffer is now in registers: hand it back to the MMA warp
+        if (cc == EPI_COLS_PER_WARP / CH - 1) {
+          // this warp's share of the accumulator buffer is in registers: hand it back to the MMA warp
           ptx::tc_fence_before_sync();
           ptx::mbar_arrive(tmem_empty_bar(acc));
         }
-        const int cbase = cc * 32;
         if (n0 + cbase >= args.n) continue;
-        int32_t q[32];
+        int32_t q[CH];
+        if (kFastCompiled && kFastDialect && chunk_slow[cbase >> 5] == 0) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          int32_t a = (int32_t)r[j] + chan_bias[cbase + j];
-          if (e.relu == B200Q_RELU_BEFORE_REQUANT && a < 0) a = 0;
-          q[j] = requant_value<DIALECT, RMODE>(a, chan_mult[cbase + j], chan_shift[cbase + j], e);
+          for (int j = 0; j < CH; ++j) {
+            const int4 cp = chan[cbase + j];  // {bias, multiplier, shift, half}: one broadcast 16-byte shared load
+            const int32_t a = max((int32_t)r[j] + cp.x, floor_pre);
+            int32_t v = requant_core_fast<DIALECT>(a, cp.y, cp.z, cp.w);
+            v = max(add_sat_s32(v, zp), floor_post);
+            q[j] = min(max(v, sat_lo), sat_hi);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            const int4 cp = chan[cbase + j];
+            int32_t a = (int32_t)r[j] + cp.x;
+            if (e.relu == B200Q_RELU_BEFORE_REQUANT && a < 0) a = 0;
+            // channels staged in the fast form carry a right shift; turn it back into the dialect's convention
+            int32_t sh = cp.z;
+            if (kFastCompiled && kFastDialect && DIALECT == B200Q_RQ_QDM && cp.w != 0) sh = -cp.z;
+            q[j] = requant_value<-1, -1>(a, cp.y, sh, e);
+          }
         }
-        const int ncols = min(32, args.n - (n0 + cbase));
+        const int ncols = min(CH, args.n - (n0 + cbase));
         if (args.out_mode == IGEMM_OUT_NCHW) {
           if (row_valid) {
-            if (e.out_dtype == B200Q_DT_I8 || e.out_dtype == B200Q_DT_U8) {
-              uint8_t* o = reinterpret_cast<uint8_t*>(args.out) + out_base + (long long)(n0 + cbase) * chan_stride;
+            const long long off0 = out_base + (long long)(n0 + cbase) * chan_stride;
+            if (out8) {
+              uint8_t* o = reinterpret_cast<uint8_t*>(args.out) + off0;
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < ncols) o[(long long)j * chan_stride] = (uint8_t)q[j];
+              for (int j = 0; j < CH; ++j)
+                if (j < ncols) o[j * chan_stride] = (uint8_t)q[j];
             } else if (e.out_dtype == B200Q_DT_I32) {
-              int32_t* o = reinterpret_cast<int32_t*>(args.out) + out_base + (long long)(n0 + cbase) * chan_stride;
+              int32_t* o = reinterpret_cast<int32_t*>(args.out) + off0;
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < ncols) o[(long long)j * chan_stride] = q[j];
+              for (int j = 0; j < CH; ++j)
+                if (j < ncols) o[j * chan_stride] = q[j];
             } else {
-              uint16_t* o = reinterpret_cast<uint16_t*>(args.out) + out_base + (long long)(n0 + cbase) * chan_stride;
+              uint16_t* o = reinterpret_cast<uint16_t*>(args.out) + off0;
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < ncols) o[(long long)j * chan_stride] = (uint16_t)q[j];
+              for (int j = 0; j < CH; ++j)
+                if (j < ncols) o[j * chan_stride] = (uint16_t)q[j];
             }
           }
         } else if (row_valid || write_zero_row) {
           if (write_zero_row) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) q[j] = 0;
+            for (int j = 0; j < CH; ++j) q[j] = 0;
           }
           const long long off = out_base + n0 + cbase;
-          if (e.out_dtype == B200Q_DT_I8 || e.out_dtype == B200Q_DT_U8) {
+          if (out8) {
             uint8_t* o = reinterpret_cast<uint8_t*>(args.out) + off;
-            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-              uint32_t p[8];
+            if (ncols == CH && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+              uint32_t p[CH / 4];
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
+              for (int j = 0; j < CH / 4; ++j)
                 p[j] = (uint32_t)(q[4 * j] & 0xff) | ((uint32_t)(q[4 * j + 1] & 0xff) << 8) |
                        ((uint32_t)(q[4 * j + 2] & 0xff) << 16) | ((uint32_t)(q[4 * j + 3] & 0xff) << 24);
               reinterpret_cast<uint4*>(o)[0] = make_uint4(p[0], p[1], p[2], p[3]);
-              reinterpret_cast<uint4*>(o)[1] = make_uint4(p[4], p[5], p[6], p[7]);
             } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
+              for (int j = 0; j < CH; ++j)
                 if (j < ncols) o[j] = (uint8_t)q[j];
             }
           } else if (e.out_dtype == B200Q_DT_I32) {
             int32_t* o = reinterpret_cast<int32_t*>(args.out) + off;
-            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+            if (ncols == CH && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
+              for (int j = 0; j < CH / 4; ++j)
                 reinterpret_cast<int4*>(o)[j] = make_int4(q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
             } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
+              for (int j = 0; j < CH; ++j)
                 if (j < ncols) o[j] = q[j];
             }
           } else {
             uint16_t* o = reinterpret_cast<uint16_t*>(args.out) + off;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
+            for (int j = 0; j < CH; ++j)
               if (j < ncols) o[j] = (uint16_t)q[j];
           }
         }
@@ -359,7 +443,7 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& ar
   using L = SmemLayout<BLOCK_N, STAGES>;
   auto kfn = igemm_i8_kernel<BLOCK_N, STAGES, DIALECT, RMODE>;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-  kfn<<<grid, NUM_THREADS, L::DYN_BYTES, stream>>>(ta, tb, args);
+  kfn<<<grid, L::NUM_THREADS, L::DYN_BYTES, stream>>>(ta, tb, args);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

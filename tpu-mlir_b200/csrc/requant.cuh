@@ -92,8 +92,33 @@ __host__ __device__ __forceinline__ int32_t requant_value(int32_t acc, int32_t m
   const int rmode = RMODE >= 0 ? RMODE : e.round_mode;
   int64_t v;
   switch (dialect) {
-    case B200Q_RQ_MULTIPLIER_SHIFT: v = rshift_round((int64_t)acc * (int64_t)m, s, rmode); break;
-    case B200Q_RQ_QDM: v = mul_by_quantized_multiplier(acc, m, s, rmode); break;
+    case B200Q_RQ_MULTIPLIER_SHIFT:
+      if (RMODE == B200Q_ROUND_HALF_UP && s >= 1 && s <= 62) {
+        // half-up: val + (mant >= half) == floor((x + half) / 2^s); |x| < 2^62 so the add cannot overflow
+        v = ((int64_t)acc * (int64_t)m + (int64_t)(1ull << (s - 1))) >> s;
+      } else {
+        v = rshift_round((int64_t)acc * (int64_t)m, s, rmode);
+      }
+      break;
+    case B200Q_RQ_QDM:
+      if (RMODE == B200Q_ROUND_HALF_AWAY_FROM_ZERO && s <= 0 && s >= -31) {
+        // first stage in 64 bits (same floor((x + 2^30) / 2^31) identity), second stage in 32 bits:
+        // the clamped first-stage value fits int32, and for a right shift by t in [1,31]
+        //   half away from zero  <=>  (v >> t) + ((v & (2^t - 1)) + (v >= 0) > 2^(t-1))
+        int64_t w = ((int64_t)acc * (int64_t)m + (1ll << 30)) >> 31;
+        if (w > 2147483647ll) w = 2147483647ll;  // only acc == m == INT32_MIN gets here
+        const int32_t v32 = (int32_t)w;
+        const int t = -s;
+        if (t == 0) {
+          v = v32;
+        } else {
+          const int32_t mant = v32 & (int32_t)((1u << t) - 1u);
+          v = (v32 >> t) + (int32_t)((mant + (int32_t)(v32 >= 0)) > (int32_t)(1u << (t - 1)));
+        }
+      } else {
+        v = mul_by_quantized_multiplier(acc, m, s, rmode);
+      }
+      break;
     case B200Q_RQ_MULTIPLIER_SHIFT_F32: {
 #ifdef __CUDA_ARCH__
       const float f = __fdiv_rn(__fmul_rn((float)acc, (float)m), (float)(1 << s));
