@@ -192,6 +192,71 @@ void b200q_conv2d_dev_destroy(void **handle);
 int b200q_conv2d_dev_set_profiling(void *handle, int enable);
 int b200q_conv2d_dev_last_times(void *handle, float *layout_ms, float *kernel_ms);
 
+/* ------------------------------------------------------------------ tpu.A16MatMul (w4 bf16)
+ * Attributes of tpu.A16MatMul (TpuOps.td:495-530) for the static 4-bit path of
+ * tpu::A16MatMulOp::inference (lib/Dialect/Tpu/Interfaces/Common/A16MatMul.cpp:171-208,:240-246):
+ * weight bytes [N, K/2] (w_transpose = true), even k in the low nibble, one bf16 scale and one uint8 zero
+ * point per q_group_size consecutive k of a row: W[n,k] = (q - zp) * scale. */
+typedef struct {
+  int64_t M, K, N;
+  int32_t weight_bits;    /* 4 */
+  int32_t q_group_size;   /* multiple of 64 */
+  int32_t w_transpose;    /* 1 */
+  int32_t with_bias;
+  int32_t out_dtype;      /* B200Q_DT_BF16 */
+  int32_t weight_version; /* bump after rewriting the weight buffers in place */
+} b200q_a16matmul_desc;
+
+/* Operator face of tpu::A16MatMulOp::{init,inference,deinit} (A16MatMul.cpp:16-22,:22-249).
+ * inputs = {input, weight, scale, zp, bias} HOST float* (every one float-stored, like the interpreter's
+ * buffers); outputs[0] HOST float* holding bf16-representable values. */
+int b200q_a16matmul_init(const b200q_a16matmul_desc *desc, void **handle);
+int b200q_a16matmul_inference(const b200q_a16matmul_desc *desc, float *const *inputs, int n_inputs,
+                              float *const *outputs, int n_outputs, void **handle);
+void b200q_a16matmul_deinit(void **handle);
+
+/* Device face: x bf16 [M,K], wq bytes [N,K/2], scale bf16 [N*K/group], zp uint8 [N*K/group] (each <= 127),
+ * bias f32 [N] or NULL, y bf16 [M,N]; asynchronous on `stream`.  Replaces the per-call fp32 dequantisation
+ * and sgemm of A16MatMul.cpp:171-208. */
+int b200q_a16_w4_dev(const void *x_bf16, const void *wq, const void *scale_bf16, const void *zp_u8,
+                     const float *bias_f32, void *y_bf16, int64_t M, int64_t N, int64_t K, int32_t group,
+                     void *stream);
+
+/* ------------------------------------------------------------------ calibration math
+ * A context owns the scratch memory of the kernels; one context per thread/stream.
+ * All tensor pointers are DEVICE pointers unless named *_host. */
+int b200q_calib_create(void **ctx);
+void b200q_calib_destroy(void **ctx);
+
+/* out[s] = {min, max} (float32) of each of `samples` contiguous runs of n_per_sample floats: the running
+ * min/max of ActivationCalibrator.process_statistic (python/calibration/kld_calibrator.py:391-393) takes
+ * its per-sample values from here.  NaNs are ignored.  Asynchronous on `stream`. */
+int b200q_calib_minmax(void *ctx, const float *x, int64_t n_per_sample, int64_t samples, float *out_minmax,
+                       void *stream);
+
+/* CaliMathCpu.histogram (python/calibration/cali_math.py:68-80) for a batch of samples: sample s is
+ * histogrammed over |x| with width th_host[s] / (nbins_host[s] - 1) into nbins_host[s] bins (zeros excluded,
+ * float32 arithmetic, numpy.histogram's float32 bin edges) and ADDED into hist[0 .. nbins_host[s]);
+ * nbins_host[s] == 0 skips the sample.  Because combine_histogram (cali_math.py:82-103) keeps old counts in
+ * their bins, the streaming histogram of a tensor is the sum of such per-sample histograms with the
+ * (threshold, bins) schedule derived from the running abs-max.  int32 counts, like the reference. */
+int b200q_calib_histogram(void *ctx, const float *x, int64_t n_per_sample, int64_t samples, const float *th_host,
+                          const int32_t *nbins_host, int32_t *hist, int64_t hist_len, void *stream);
+
+/* ActivationCalibrator.find_threshold (kld_calibrator.py:321-347) for `tensors` histograms at once: zero-pad
+ * to a multiple of dst_bins, fold pairwise while longer than 131072 bins (doubling the width), then the KLD
+ * search of calibration_math.cpp:158-212,:273-323.  thresholds_host[t] is filled on return (synchronous);
+ * kl_host, if not NULL, receives 1024 floats per tensor (the KL value of every candidate). */
+int b200q_calib_find_thresholds(void *ctx, int32_t tensors, const int32_t *const *hist, const int64_t *n_bins,
+                                const float *widths, int64_t dst_bins, float *thresholds_host, float *kl_host,
+                                void *stream);
+
+/* The two symbols of the reference's calibration_math.so (bindings/kld/calibration_math.cpp:326-337), with
+ * HOST buffers, so python/calibration/kld_calibrator.py:50-59 can load this library in its place.
+ * Failure is reported as NaN (see b200q_last_error). */
+float kl_diversity_hist(int *data, float width, long long num_bins, long long dst_bins);
+float kl_diversity(float *data, long long count, long long num_bins);
+
 #ifdef __cplusplus
 }
 #endif

@@ -53,6 +53,12 @@ class Conv2DDesc(C.Structure):
                 ("weight_version", C.c_int32), ("algo", C.c_int32)]
 
 
+class A16MatMulDesc(C.Structure):
+    _fields_ = [("M", C.c_int64), ("K", C.c_int64), ("N", C.c_int64), ("weight_bits", C.c_int32),
+                ("q_group_size", C.c_int32), ("w_transpose", C.c_int32), ("with_bias", C.c_int32),
+                ("out_dtype", C.c_int32), ("weight_version", C.c_int32)]
+
+
 _FLOATPP = C.POINTER(C.POINTER(C.c_float))
 _VPP = C.POINTER(C.c_void_p)
 
@@ -73,6 +79,20 @@ SIGNATURES = {
     "b200q_conv2d_dev_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200q_conv2d_dev_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200q_conv2d_dev_destroy": (None, [_VPP]),
+    "b200q_a16matmul_init": (C.c_int, [C.POINTER(A16MatMulDesc), _VPP]),
+    "b200q_a16matmul_inference": (C.c_int, [C.POINTER(A16MatMulDesc), _FLOATPP, C.c_int, _FLOATPP, C.c_int, _VPP]),
+    "b200q_a16matmul_deinit": (None, [_VPP]),
+    "b200q_a16_w4_dev": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
+    "b200q_calib_create": (C.c_int, [_VPP]),
+    "b200q_calib_destroy": (None, [_VPP]),
+    "b200q_calib_minmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200q_calib_histogram": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.POINTER(C.c_float),
+                                        C.POINTER(C.c_int32), C.c_void_p, C.c_int64, C.c_void_p]),
+    "b200q_calib_find_thresholds": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_int64),
+                                              C.POINTER(C.c_float), C.c_int64, C.POINTER(C.c_float),
+                                              C.POINTER(C.c_float), C.c_void_p]),
+    "kl_diversity_hist": (C.c_float, [C.POINTER(C.c_int), C.c_float, C.c_longlong, C.c_longlong]),
+    "kl_diversity": (C.c_float, [C.POINTER(C.c_float), C.c_longlong, C.c_longlong]),
     "b200q_conv2d_dev_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
     "b200q_conv2d_dev_last_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
 }

@@ -1,0 +1,282 @@
+"""Activation calibration on the GPU: running min/max, streaming histogram and KLD threshold per tensor.
+
+Mirrors the statistics half of the reference's ``ActivationCalibrator``
+(python/calibration/kld_calibrator.py:364-477 ``process_statistic``, :321-347 ``find_threshold``) and its math
+object (python/calibration/cali_math.py:27-143).  Two things differ in form, not in result:
+
+* ``CaliMathB200`` offers the reference's ``prepare / histogram / combine_histogram`` protocol, computed by the
+  kernels in libb200q.so.
+* ``ShardedCalibrator`` runs the same statistics over samples that are sharded across ranks.  The reference's
+  streaming histogram depends on the sample order only through the running abs-max (cali_math.py:82-103 keeps
+  old counts in their bins when it grows the histogram), so it equals the sum over samples of per-sample
+  histograms taken with a (threshold, bins) schedule derived from the per-sample min/max alone.  Pass 1 gathers
+  the min/max of every sample (all-gather), every rank derives the identical schedule on the host, pass 2
+  histograms the local samples into a buffer of the final size, one all-reduce (sum, int32) merges the ranks.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Callable, Dict, Iterable, List, Optional, Sequence
+
+import numpy as np
+
+from . import _lib as L
+
+MAX_GROWN_BINS = 8000000   # cali_math.py:96
+MAX_KLD_BINS = 64 * 2048   # kld_calibrator.py:338
+ALL_ZERO_EPS = 1e-8        # kld_calibrator.py:395
+
+
+# ----------------------------------------------------------------------------------------------- host logic
+@dataclass
+class Schedule:
+    """What each sample contributes to one tensor's histogram, and the final histogram geometry."""
+    th: np.ndarray          # float32 [S] threshold used for sample s (0 where it contributes nothing)
+    nbins: np.ndarray       # int32 [S] bins used for sample s (0 = skipped)
+    final_bins: int         # length of the final histogram (0 if no sample contributed)
+    width: np.float32       # bin width handed to the KLD search
+    min: np.float32
+    max: np.float32
+    abs_max: np.float32
+
+
+def bin_schedule(sample_min: Sequence[float], sample_max: Sequence[float], bin_num: int = 2048) -> Schedule:
+    """Replays process_statistic + combine_histogram (kld_calibrator.py:391-398,:462-476; cali_math.py:82-103)
+    on the per-sample (min, max) of one tensor, in sample order, in float32 like the reference."""
+    smin = np.asarray(sample_min, dtype=np.float32)
+    smax = np.asarray(sample_max, dtype=np.float32)
+    S = len(smin)
+    th_s = np.zeros(S, np.float32)
+    nb_s = np.zeros(S, np.int32)
+    run_min, run_max = float("inf"), float("-inf")
+    th: Optional[np.float32] = None
+    nb = 0
+    width = np.float32(0)
+    last_reset = 0
+    for i in range(S):
+        run_min = min(smin[i], run_min)
+        run_max = max(smax[i], run_max)
+        abs_value = max(abs(run_min), abs(run_max))
+        if max(abs(smin[i]), abs(smax[i])) < ALL_ZERO_EPS:      # np.abs(activation).max() < 1e-8: no histogram
+            continue
+        if th is None:
+            th, nb = np.float32(abs_value), bin_num
+            width = np.float32(th / (nb - 1))
+        elif abs_value > th:
+            old_step = np.float32(th / nb)
+            inc = int((np.float32(abs_value) - th) // old_step + 1)
+            if inc + nb > MAX_GROWN_BINS:
+                th, nb = np.float32(abs_value), bin_num          # starts over with this sample only
+                last_reset = i
+            else:
+                th = np.float32(inc * old_step + th)
+                nb = inc + nb
+            width = np.float32(th / (nb - 1))
+        th_s[i], nb_s[i] = th, nb
+    nb_s[:last_reset] = 0
+    th_s[:last_reset] = 0
+    amax = np.float32(max(abs(run_min), abs(run_max))) if S else np.float32(0)
+    return Schedule(th=th_s, nbins=nb_s, final_bins=int(nb), width=np.float32(width), min=np.float32(run_min),
+                    max=np.float32(run_max), abs_max=amax)
+
+
+def table_threshold(kl: float, abs_max: float) -> float:
+    """calibration_result.canonicalize (python/calibration/utils.py:53-69) and the 1e-5 floor of
+    dump_cali_table (kld_calibrator.py:848-851)."""
+    th = min(float(kl), float(abs_max))
+    return th if th > 1e-5 else 1e-5
+
+
+# ----------------------------------------------------------------------------------------------- GPU math
+class CaliMathB200:
+    """The reference's math_impl protocol (cali_math.py:27-143: prepare / histogram / combine_histogram) on the
+    GPU.  Arrays passed to ``prepare`` stay on the device; histograms come back as int32 numpy arrays."""
+
+    def __init__(self, device: Optional[int] = None):
+        import torch
+        self.torch = torch
+        if not torch.cuda.is_available():
+            raise L.B200QError(L.ERR_NO_DEVICE, "CaliMathB200 needs a CUDA device (there is no CPU fallback)")
+        self.device = torch.device("cuda", torch.cuda.current_device() if device is None else device)
+        self.ctx = C.c_void_p()
+        L.check(L.lib().b200q_calib_create(C.byref(self.ctx)))
+
+    def __del__(self):
+        try:
+            if self.ctx:
+                L.lib().b200q_calib_destroy(C.byref(self.ctx))
+        except Exception:
+            pass
+
+    # -- device helpers
+    def _dev(self, a):
+        t = self.torch
+        if isinstance(a, t.Tensor):
+            return a.to(self.device, dtype=t.float32).contiguous()
+        return t.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(self.device)
+
+    def _stream(self):
+        return C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)
+
+    def prepare(self, array):
+        return self._dev(array)
+
+    def minmax(self, x, samples: int = 1):
+        """Per-sample (min, max) of a device tensor viewed as [samples, -1]; returns a device tensor [samples, 2]."""
+        x = self._dev(x)
+        n = x.numel() // samples
+        out = self.torch.empty((samples, 2), dtype=self.torch.float32, device=self.device)
+        L.check(L.lib().b200q_calib_minmax(self.ctx, C.c_void_p(x.data_ptr()), n, samples,
+                                           C.c_void_p(out.data_ptr()), self._stream()))
+        return out
+
+    def histogram_into(self, hist, x, th: np.ndarray, nbins: np.ndarray):
+        """hist (device int32) += per-sample histograms of x viewed as [len(th), -1]."""
+        x = self._dev(x)
+        S = len(th)
+        th = np.ascontiguousarray(th, dtype=np.float32)
+        nbins = np.ascontiguousarray(nbins, dtype=np.int32)
+        L.check(L.lib().b200q_calib_histogram(self.ctx, C.c_void_p(x.data_ptr()), x.numel() // S, S,
+                                              th.ctypes.data_as(C.POINTER(C.c_float)),
+                                              nbins.ctypes.data_as(C.POINTER(C.c_int32)),
+                                              C.c_void_p(hist.data_ptr()), hist.numel(), self._stream()))
+
+    def histogram(self, ndarray, abs_max, bin_num: int = 2048):
+        """CaliMathCpu.histogram (cali_math.py:68-80): returns (int32 counts, float32 width)."""
+        hist = self.torch.zeros(bin_num, dtype=self.torch.int32, device=self.device)
+        abs_max = np.float32(abs_max)
+        self.histogram_into(hist, self._dev(ndarray).reshape(-1), np.array([abs_max]), np.array([bin_num]))
+        return hist.cpu().numpy(), np.float32(abs_max / np.float32(bin_num - 1))
+
+    def combine_histogram(self, old_hist, arr, new_min, new_max, new_th, bin_num: int = 2048):
+        """CaliMathCpu.combine_histogram (cali_math.py:82-103) with the histogram taken on the GPU."""
+        (old, old_edges, old_min, old_max, old_th) = old_hist
+        if new_th <= old_th:
+            hist, _ = self.histogram(arr, old_th, len(old))
+            return (old + hist, old_edges, min(old_min, new_min), max(old_max, new_max), old_th)
+        old_bins = len(old)
+        old_step = old_th / old_bins
+        inc = int((new_th - old_th) // old_step + 1)
+        new_bins = inc + old_bins
+        if new_bins > MAX_GROWN_BINS:
+            hist, edges = self.histogram(arr, new_th, bin_num)
+            return (hist, edges, min(old_min, new_min), max(old_max, new_max), new_th)
+        new_th = inc * old_step + old_th
+        hist, edges = self.histogram(arr, new_th, new_bins)
+        hist[0:old_bins] += old
+        return (hist, edges, min(old_min, new_min), max(old_max, new_max), new_th)
+
+    def find_thresholds(self, hists, widths, dst_bins: int = 128, return_kl: bool = False):
+        """find_threshold (kld_calibrator.py:321-347) for a list of device int32 histograms."""
+        T = len(hists)
+        ptrs = (C.c_void_p * T)(*[h.data_ptr() for h in hists])
+        nb = (C.c_int64 * T)(*[h.numel() for h in hists])
+        w = (C.c_float * T)(*[float(np.float32(x)) for x in widths])
+        out = (C.c_float * T)()
+        kl = (C.c_float * (T * 1024))() if return_kl else None
+        L.check(L.lib().b200q_calib_find_thresholds(self.ctx, T, ptrs, nb, w, dst_bins, out, kl, self._stream()))
+        th = np.frombuffer(out, dtype=np.float32).copy()
+        if return_kl:
+            return th, np.frombuffer(kl, dtype=np.float32).reshape(T, 1024).copy()
+        return th
+
+
+def kld_threshold_host(hist: np.ndarray, width, dst_bins: int = 128) -> np.float32:
+    """BaseKldCalibrator.kld_threshold (kld_calibrator.py:55-59) through the reference's own C symbol, served
+    by libb200q.so."""
+    h = np.ascontiguousarray(hist, dtype=np.int32)
+    return np.float32(L.lib().kl_diversity_hist(h.ctypes.data_as(C.POINTER(C.c_int)), C.c_float(float(width)),
+                                                C.c_longlong(h.size), C.c_longlong(dst_bins)))
+
+
+# ----------------------------------------------------------------------------------------------- sharded driver
+@dataclass
+class TensorResult:
+    name: str
+    min: float
+    max: float
+    abs_max: float
+    bins: int
+    width: float
+    kl: float
+    threshold: float     # what the calibration table would hold (min(kl, abs_max), floor 1e-5)
+
+
+class ShardedCalibrator:
+    """Statistics + KLD thresholds for the activations of a forward function, samples sharded across ranks.
+
+    ``forward(batch) -> dict name -> device float32 tensor [B, ...]`` produces every activation of interest for a
+    batch of samples; ``shard`` is the local contiguous range of the global sample order.  ``math`` defaults to
+    the GPU implementation; ``dist`` is a torch.distributed-like module (None = single process).
+    """
+
+    def __init__(self, forward: Callable, math=None, dist=None, bin_num: int = 2048, dst_bins: int = 128):
+        self.forward = forward
+        self.math = math if math is not None else CaliMathB200()
+        self.dist = dist if (dist is not None and dist.is_initialized() and dist.get_world_size() > 1) else None
+        self.bin_num = bin_num
+        self.dst_bins = dst_bins
+
+    def _world(self):
+        return (self.dist.get_rank(), self.dist.get_world_size()) if self.dist else (0, 1)
+
+    def run(self, batches: Iterable, samples_per_rank: int) -> Dict[str, TensorResult]:
+        """``batches`` must be re-iterable (it is walked twice) and cover exactly ``samples_per_rank`` local
+        samples in order; rank r holds global samples [r*samples_per_rank, (r+1)*samples_per_rank)."""
+        import torch
+        rank, world = self._world()
+        m = self.math
+        # ---- pass 1: per-sample min/max of every tensor
+        names: List[str] = []
+        local: Dict[str, List] = {}
+        for batch in batches:
+            acts = self.forward(batch)
+            if not names:
+                names = list(acts.keys())
+                local = {n: [] for n in names}
+            for n in names:
+                a = acts[n]
+                local[n].append(m.minmax(a, samples=a.shape[0]))
+        mm_local = torch.stack([torch.cat(local[n], dim=0) for n in names])            # [T, S_local, 2]
+        assert mm_local.shape[1] == samples_per_rank, "batches do not cover samples_per_rank samples"
+        if self.dist:
+            gathered = [torch.empty_like(mm_local) for _ in range(world)]
+            self.dist.all_gather(gathered, mm_local.contiguous())
+            mm_all = torch.cat(gathered, dim=1)                                          # rank-major = sample order
+        else:
+            mm_all = mm_local
+        mm_all = mm_all.cpu().numpy()
+        # ---- identical schedule on every rank
+        sched = {n: bin_schedule(mm_all[t, :, 0], mm_all[t, :, 1], self.bin_num) for t, n in enumerate(names)}
+        # ---- pass 2: histograms of the local samples into final-size buffers (one flat allocation)
+        sizes = [max(sched[n].final_bins, 1) for n in names]
+        offs = np.concatenate(([0], np.cumsum(sizes)))
+        flat = torch.zeros(int(offs[-1]), dtype=torch.int32, device=mm_local.device)
+        views = {n: flat[int(offs[t]):int(offs[t + 1])] for t, n in enumerate(names)}
+        s0 = rank * samples_per_rank
+        done = 0
+        for batch in batches:
+            acts = self.forward(batch)
+            for n in names:
+                a = acts[n]
+                B = a.shape[0]
+                sc = sched[n]
+                lo = s0 + done
+                if sc.final_bins and sc.nbins[lo:lo + B].any():
+                    m.histogram_into(views[n], a, sc.th[lo:lo + B], sc.nbins[lo:lo + B])
+            done += next(iter(acts.values())).shape[0]
+        if self.dist:
+            self.dist.all_reduce(flat)                                                   # sum of int32 counts
+        # ---- KLD
+        live = [n for n in names if sched[n].final_bins]
+        kl = m.find_thresholds([views[n] for n in live], [sched[n].width for n in live], self.dst_bins) if live else []
+        out: Dict[str, TensorResult] = {}
+        for n in names:
+            sc = sched[n]
+            k = float(kl[live.index(n)]) if n in live else 0.0
+            out[n] = TensorResult(name=n, min=float(sc.min), max=float(sc.max), abs_max=float(sc.abs_max),
+                                  bins=sc.final_bins, width=float(sc.width), kl=k,
+                                  threshold=table_threshold(k, sc.abs_max) if n in live else 1e-5)
+        self.histograms = {n: views[n] for n in names}
+        return out

@@ -1,0 +1,151 @@
+// C ABI for tpu.A16MatMul with 4-bit weights (lib/Dialect/Tpu/Interfaces/Common/A16MatMul.cpp:16-249):
+// operator face over host float buffers and device face over native bf16 / packed-nibble tensors.
+#include <cuda_bf16.h>
+
+#include <new>
+
+#include "a16.h"
+#include "devbuf.h"
+#include "internal.h"
+#include "layout.h"
+
+namespace b200q {
+namespace {
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = __float2bfloat16_rn(x[i]);  // exact: the interpreter's bf16 tensors hold bf16-representable floats
+}
+__global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = __bfloat162float(x[i]);
+}
+
+int f32_to_bf16(const float* x, void* y, long long n, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  f32_to_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, static_cast<__nv_bfloat16*>(y), n);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+int bf16_to_f32(const void* x, float* y, long long n, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  bf16_to_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), y, n);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int validate(const b200q_a16matmul_desc& d) {
+  if (d.M < 0 || d.K < 1 || d.N < 1 || d.M > 0x7fffffffLL || d.K > 0x7fffffffLL || d.N > 0x7fffffffLL)
+    return set_error(B200Q_ERR_INVALID, "a16matmul: bad shape");
+  if (d.weight_bits != 4) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: only weight_bits = 4 is implemented");
+  if (!d.w_transpose) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: only w_transpose = true (weight stored [N, K/2]) is implemented");
+  if (d.q_group_size <= 0) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: per-channel (q_group_size = 0) weights are not implemented");
+  if (d.out_dtype != B200Q_DT_BF16) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: only bf16 activations/outputs are implemented");
+  return B200Q_OK;
+}
+
+// Decode shapes go to the GEMV kernel; larger M is processed in slices of 8 tokens.
+int a16_dispatch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
+                 long long M, int N, int K, int group, cudaStream_t s) {
+  const char* why = nullptr;
+  if (!a16_w4_gemv_supported(1, N, K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: %s", why);
+  for (long long m0 = 0; m0 < M; m0 += 8) {
+    const int mm = (int)((M - m0) < 8 ? (M - m0) : 8);
+    B200Q_TRY(a16_w4_gemv_launch(static_cast<const uint8_t*>(x) + (size_t)m0 * K * 2, wq, scale, zp, bias,
+                                 static_cast<uint8_t*>(y) + (size_t)m0 * N * 2, mm, N, K, group, s));
+  }
+  return B200Q_OK;
+}
+
+struct A16Handle {
+  DevBuf stage, x16, wq, scale, zp, bias, y16, y32;
+  bool weights_ready = false;
+  int weight_version = -1;
+  const float* weight_ptr = nullptr;
+};
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_a16matmul_init(const b200q_a16matmul_desc* desc, void** handle) {
+  if (!desc || !handle) return set_error(B200Q_ERR_INVALID, "a16matmul_init: null argument");
+  B200Q_TRY(validate(*desc));
+  auto* h = new (std::nothrow) A16Handle();
+  if (!h) return set_error(B200Q_ERR_NOMEM, "a16matmul_init: out of host memory");
+  *handle = h;
+  return B200Q_OK;
+}
+
+void b200q_a16matmul_deinit(void** handle) {
+  if (handle && *handle) {
+    delete static_cast<A16Handle*>(*handle);
+    *handle = nullptr;
+  }
+}
+
+int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* inputs, int n_inputs,
+                              float* const* outputs, int n_outputs, void** handle) {
+  if (!desc || !inputs || !outputs || !handle || n_inputs < 4 || n_outputs < 1 || !inputs[0] || !inputs[1] ||
+      !inputs[2] || !inputs[3] || !outputs[0])
+    return set_error(B200Q_ERR_INVALID, "a16matmul_inference: null argument");
+  const b200q_a16matmul_desc& d = *desc;
+  B200Q_TRY(validate(d));
+  const bool own = (*handle == nullptr);
+  if (own) B200Q_TRY(b200q_a16matmul_init(desc, handle));
+  A16Handle* h = static_cast<A16Handle*>(*handle);
+  cudaStream_t s = 0;
+  int rc = B200Q_OK;
+  do {
+    const size_t w_elems = (size_t)d.N * (d.K / 2), q_elems = (size_t)d.N * (d.K / d.q_group_size);
+    const float* bias_f = (d.with_bias && n_inputs > 4) ? inputs[4] : nullptr;
+    if (d.with_bias && !bias_f) { rc = set_error(B200Q_ERR_INVALID, "a16matmul: with_bias but inputs[4] is null"); break; }
+    const bool cached = h->weights_ready && h->weight_version == d.weight_version && h->weight_ptr == inputs[1];
+    if (!cached) {
+      // weight bytes, scales and zero points arrive float-stored (WeightOp::read_as_float)
+      if ((rc = h->stage.ensure(w_elems * 4))) break;
+      if ((rc = h->wq.ensure(w_elems))) break;
+      if ((rc = h->scale.ensure(q_elems * 2))) break;
+      if ((rc = h->zp.ensure(q_elems))) break;
+      if (cudaMemcpyAsync(h->stage.p, inputs[1], w_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D weight", __FILE__, __LINE__); break; }
+      if ((rc = f32_to_q8(h->stage.as<float>(), h->wq.p, (long long)w_elems, s))) break;
+      if (cudaMemcpyAsync(h->stage.p, inputs[2], q_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D scale", __FILE__, __LINE__); break; }
+      if ((rc = f32_to_bf16(h->stage.as<float>(), h->scale.p, (long long)q_elems, s))) break;
+      if (cudaMemcpyAsync(h->stage.p, inputs[3], q_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D zp", __FILE__, __LINE__); break; }
+      if ((rc = f32_to_q8(h->stage.as<float>(), h->zp.p, (long long)q_elems, s))) break;
+      if (bias_f && (rc = h->bias.upload(bias_f, (size_t)d.N * 4, s))) break;
+      h->weights_ready = true;
+      h->weight_version = d.weight_version;
+      h->weight_ptr = inputs[1];
+    }
+    const size_t x_elems = (size_t)d.M * d.K, y_elems = (size_t)d.M * d.N;
+    if (x_elems == 0) break;
+    if ((rc = h->stage.ensure(x_elems * 4 > w_elems * 4 ? x_elems * 4 : w_elems * 4))) break;
+    if ((rc = h->x16.ensure(x_elems * 2))) break;
+    if ((rc = h->y16.ensure(y_elems * 2))) break;
+    if ((rc = h->y32.ensure(y_elems * 4))) break;
+    if (cudaMemcpyAsync(h->stage.p, inputs[0], x_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D input", __FILE__, __LINE__); break; }
+    if ((rc = f32_to_bf16(h->stage.as<float>(), h->x16.p, (long long)x_elems, s))) break;
+    if ((rc = a16_dispatch(h->x16.p, h->wq.p, h->scale.p, h->zp.p, bias_f ? h->bias.as<float>() : nullptr, h->y16.p,
+                           d.M, (int)d.N, (int)d.K, d.q_group_size, s))) break;
+    if ((rc = bf16_to_f32(h->y16.p, h->y32.as<float>(), (long long)y_elems, s))) break;
+    if (cudaMemcpyAsync(outputs[0], h->y32.p, y_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__); break; }
+    if (cudaStreamSynchronize(s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "sync", __FILE__, __LINE__); break; }
+  } while (0);
+  if (rc != B200Q_OK) cudaStreamSynchronize(s);
+  if (own) b200q_a16matmul_deinit(handle);
+  return rc;
+}
+
+int b200q_a16_w4_dev(const void* x_bf16, const void* wq, const void* scale_bf16, const void* zp_u8,
+                     const float* bias_f32, void* y_bf16, int64_t M, int64_t N, int64_t K, int32_t group, void* stream) {
+  if (!x_bf16 || !wq || !scale_bf16 || !zp_u8 || !y_bf16) return set_error(B200Q_ERR_INVALID, "a16_w4_dev: null argument");
+  if (M < 0 || N < 1 || K < 1 || N > 0x7fffffffLL || K > 0x7fffffffLL || group < 1) return set_error(B200Q_ERR_INVALID, "a16_w4_dev: bad shape");
+  return a16_dispatch(x_bf16, wq, scale_bf16, zp_u8, bias_f32, y_bf16, M, (int)N, (int)K, group,
+                      static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -37,6 +37,66 @@ __global__ void nchw_to_bordered_nhwc_kernel(const T* __restrict__ x, uint8_t* _
   }
 }
 
+
+// Fast path of the same transform for H*W % 4 == 0 and C % 4 == 0: a block moves 128 channels x 128 pixels.
+// Reads are 128-byte (512-byte for float input) coalesced runs along W, a 4x4 byte transpose happens in
+// registers (prmt), the tile goes through XOR-swizzled shared memory, and writes are 128-byte runs along C.
+template <typename T>
+struct Pix4;
+template <>
+struct Pix4<uint8_t> {
+  static __device__ __forceinline__ uint32_t load(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+};
+template <>
+struct Pix4<float> {
+  static __device__ __forceinline__ uint32_t load(const float* p) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    return (uint32_t)((int)v.x & 0xff) | ((uint32_t)((int)v.y & 0xff) << 8) | ((uint32_t)((int)v.z & 0xff) << 16) |
+           ((uint32_t)((int)v.w & 0xff) << 24);
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+nchw_to_bordered_nhwc_fast_kernel(const T* __restrict__ x, uint8_t* __restrict__ y, int C, int H, int W, int bh, int bw) {
+  __shared__ uint32_t tile[128][32];  // [pixel][4-channel word], word column XORed with (pixel >> 2) & 31
+  const int HW = H * W, Wp = W + 2 * bw, Hp = H + 2 * bh;
+  const int p0 = blockIdx.x * 128, c0 = blockIdx.y * 128, n = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pix = p0 + 4 * lane;  // this lane's 4 pixels
+  const T* xn = x + (long long)n * C * HW;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int cg = warp * 4 + g;  // channel group of 4 (word column)
+    const int c = c0 + 4 * cg;
+    uint32_t a = 0, b = 0, cc = 0, d = 0;
+    if (pix < HW && c < C) {  // C % 4 == 0: a group is entirely inside or outside
+      a = Pix4<T>::load(xn + (long long)(c + 0) * HW + pix);
+      b = Pix4<T>::load(xn + (long long)(c + 1) * HW + pix);
+      cc = Pix4<T>::load(xn + (long long)(c + 2) * HW + pix);
+      d = Pix4<T>::load(xn + (long long)(c + 3) * HW + pix);
+    }
+    const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(cc, d, 0x5140);
+    const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(cc, d, 0x7362);
+    const int col = cg ^ lane;  // (pixel >> 2) & 31 == lane for all four pixels of this lane
+    tile[4 * lane + 0][col] = __byte_perm(t0, t1, 0x5410);
+    tile[4 * lane + 1][col] = __byte_perm(t0, t1, 0x7632);
+    tile[4 * lane + 2][col] = __byte_perm(t2, t3, 0x5410);
+    tile[4 * lane + 3][col] = __byte_perm(t2, t3, 0x7632);
+  }
+  __syncthreads();
+  uint8_t* yn = y + (long long)n * Hp * Wp * C;
+  for (int r = warp; r < 128; r += 8) {
+    const int p = p0 + r;
+    if (p >= HW) break;
+    const int h = p / W, w = p - h * W;
+    const int cg = lane ^ ((r >> 2) & 31);
+    const int c = c0 + 4 * cg;
+    if (c < C)
+      *reinterpret_cast<uint32_t*>(yn + ((long long)(h + bh) * Wp + (w + bw)) * C + c) = tile[r][lane];
+  }
+}
+
 // w[OC][IC][KH][KW] -> wr[OC][KH*KW][IC]  (K-major rows for the implicit GEMM: k = tap * IC + ic)
 template <typename T>
 __global__ void repack_weight_kernel(const T* __restrict__ w, uint8_t* __restrict__ wr, int OC, int IC, int KHW) {
@@ -92,6 +152,17 @@ inline unsigned blocks_for(long long n, int threads) { return (unsigned)((n + th
 
 int nchw_to_bordered_nhwc(const void* x, int x_is_f32, void* y, int N, int C, int H, int W, int bh, int bw,
                           cudaStream_t s) {
+  const long long HW = (long long)H * W;
+  const bool aligned = (reinterpret_cast<uintptr_t>(x) % (x_is_f32 ? 16 : 4) == 0) && (reinterpret_cast<uintptr_t>(y) % 4 == 0);
+  if (HW % 4 == 0 && C % 4 == 0 && aligned && N <= 65535 && ceil_div(C, 128) <= 65535) {
+    dim3 grid(ceil_div(HW, 128), ceil_div(C, 128), N);
+    if (x_is_f32)
+      nchw_to_bordered_nhwc_fast_kernel<float><<<grid, 256, 0, s>>>((const float*)x, (uint8_t*)y, C, H, W, bh, bw);
+    else
+      nchw_to_bordered_nhwc_fast_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, C, H, W, bh, bw);
+    CUDA_TRY(cudaGetLastError());
+    return B200Q_OK;
+  }
   if ((long long)N * H > 65535LL * 32767) return set_error(B200Q_ERR_UNSUPPORTED, "layout: N*H too large");
   dim3 grid(ceil_div(W, 32), ceil_div(C, 32), N * H), block(32, 8);
   if (grid.y > 65535 || grid.z > 65535) {

@@ -144,3 +144,38 @@ class Conv2DOp:
         if p.handle is not None:
             L.lib().b200q_conv2d_deinit(C.byref(p.handle))
             p.handle = None
+
+
+class A16MatMulOp:
+    """tpu.A16MatMul, static 4-bit weights (lib/Dialect/Tpu/Interfaces/Common/A16MatMul.cpp:16-249).
+
+    Operands: input, weight, scale, zp, bias (TpuOps.td:495-500).  Attributes: ``weight_bits, q_group_size,
+    w_transpose``.  All buffers are float32 host arrays: activations and scales hold bf16-representable
+    values, weight holds the packed bytes [N, K/2] as floats.
+    """
+
+    def __init__(self, *, M, K, N, q_group_size=64, weight_bits=4, w_transpose=True, with_bias=False,
+                 out_dtype=L.DT_BF16):
+        self.desc = L.A16MatMulDesc(M=M, K=K, N=N, weight_bits=weight_bits, q_group_size=q_group_size,
+                                    w_transpose=int(w_transpose), with_bias=int(with_bias), out_dtype=out_dtype,
+                                    weight_version=0)
+
+    def invalidate_weights(self):
+        self.desc.weight_version += 1
+
+    def init(self, p: InferenceParameter):
+        h = C.c_void_p()
+        L.check(L.lib().b200q_a16matmul_init(C.byref(self.desc), C.byref(h)))
+        p.handle = h
+
+    def inference(self, p: InferenceParameter):
+        h = p.handle if p.handle is not None else C.c_void_p()
+        ins = [_f32(a) for a in p.inputs]
+        outs = [_f32(a) for a in p.outputs]
+        L.check(L.lib().b200q_a16matmul_inference(C.byref(self.desc), L.float_pp(ins), len(ins), L.float_pp(outs),
+                                                  len(outs), C.byref(h)))
+
+    def deinit(self, p: InferenceParameter):
+        if p.handle is not None:
+            L.lib().b200q_a16matmul_deinit(C.byref(p.handle))
+            p.handle = None
