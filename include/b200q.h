@@ -234,6 +234,21 @@ void b200q_calib_destroy(void **ctx);
 int b200q_calib_minmax(void *ctx, const float *x, int64_t n_per_sample, int64_t samples, float *out_minmax,
                        void *stream);
 
+/* Same result as b200q_calib_minmax for callers that are not allowed to allocate device memory: code that runs
+ * inside someone else's memory plan (a serving process whose HBM is fully pre-partitioned, a host that forbids
+ * cudaMalloc after start-up because an allocation synchronises the device) still needs per-sample min/max.
+ * This entry point has no counterpart in the reference.  It needs no context: the kernel's scratch (block
+ * partials and ticket counters) lives in a fixed 36 KB device array inside the library, which every GPU that
+ * loads the library holds until the process exits.  It calls no cudaMalloc / cudaFree and no allocating library
+ * routine.  Limits: at most 1024 samples per call (B200Q_ERR_UNSUPPORTED beyond that); x and out_minmax are the
+ * caller's device buffers.  The first call on each device looks up the array's device address (with that device
+ * current); make that first call before starting any stream capture.  All calls on a device share the one
+ * array and it keeps the last call's contents (the counters are cleared on the stream before each launch), so
+ * two calls whose kernels can overlap on the GPU (different streams) race: keep them on one stream or
+ * otherwise ordered.  Asynchronous on `stream`. */
+int b200q_calib_minmax_noalloc(const float *x, int64_t n_per_sample, int64_t samples, float *out_minmax,
+                               void *stream);
+
 /* CaliMathCpu.histogram (python/calibration/cali_math.py:68-80) for a batch of samples: sample s is
  * histogrammed over |x| with width th_host[s] / (nbins_host[s] - 1) into nbins_host[s] bins (zeros excluded,
  * float32 arithmetic, numpy.histogram's float32 bin edges) and ADDED into hist[0 .. nbins_host[s]);

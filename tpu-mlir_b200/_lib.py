@@ -86,6 +86,7 @@ SIGNATURES = {
     "b200q_calib_create": (C.c_int, [_VPP]),
     "b200q_calib_destroy": (None, [_VPP]),
     "b200q_calib_minmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200q_calib_minmax_noalloc": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200q_calib_histogram": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.POINTER(C.c_float),
                                         C.POINTER(C.c_int32), C.c_void_p, C.c_int64, C.c_void_p]),
     "b200q_calib_find_thresholds": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_int64),

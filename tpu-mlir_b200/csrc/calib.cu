@@ -269,6 +269,57 @@ int minmax_launch(const float* x, long long n, long long samples, float* out, vo
   return B200Q_OK;
 }
 
+
+// ------------------------------------------------------------------------------------------- min/max without allocation
+// Scratch of the min/max kernel for callers that must not allocate: a fixed array that lives in the module
+// image of every GPU that loads this library (36 KB per GPU, held until the process exits).
+// Layout: [STATIC_MM_MAX_SAMPLES ticket counters][STATIC_MM_MAX_PARTIALS {min, max} pairs].
+constexpr int STATIC_MM_MAX_SAMPLES = 1024;
+constexpr int STATIC_MM_MAX_PARTIALS = 4096;
+constexpr size_t STATIC_MM_TICKET_BYTES = STATIC_MM_MAX_SAMPLES * sizeof(unsigned int);
+constexpr size_t STATIC_MM_BYTES = STATIC_MM_TICKET_BYTES + (size_t)STATIC_MM_MAX_PARTIALS * 2 * sizeof(float);
+static __device__ __align__(256) unsigned char g_static_minmax_scratch[STATIC_MM_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+static void* g_static_scratch_addr[MAX_DEVICES];  // device address of the array, per device ordinal
+
+// In host code the array's name is only a handle for the runtime, not a device address: the address a
+// kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) return set_error(B200Q_ERR_UNSUPPORTED, "minmax_static: device ordinal %d not supported", dev);
+  if (!g_static_scratch_addr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_minmax_scratch);
+    if (e != cudaSuccess) return cuda_error(e, "cudaGetSymbolAddress(g_static_minmax_scratch)", __FILE__, __LINE__);
+    if (!p) return set_error(B200Q_ERR_CUDA, "minmax_static: the scratch symbol has no device address");
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return B200Q_OK;
+}
+
+int minmax_static_launch(const float* x, long long n, long long samples, float* out, cudaStream_t s) {
+  if (samples == 0) return B200Q_OK;
+  if (samples > STATIC_MM_MAX_SAMPLES)
+    return set_error(B200Q_ERR_UNSUPPORTED, "minmax_static: %lld samples exceed the fixed scratch (at most %d per call)",
+                     samples, STATIC_MM_MAX_SAMPLES);
+  int bps = minmax_blocks_per_sample(n, samples);
+  if ((long long)bps * samples > STATIC_MM_MAX_PARTIALS) bps = (int)(STATIC_MM_MAX_PARTIALS / samples);
+  if (bps < 1) bps = 1;
+  void* base = nullptr;
+  B200Q_TRY(static_scratch_for_current_device(&base));
+  unsigned int* tickets = static_cast<unsigned int*>(base);
+  float* partial = reinterpret_cast<float*>(static_cast<unsigned char*>(base) + STATIC_MM_TICKET_BYTES);
+  // the array keeps whatever the previous call left: the ticket counters must start at zero
+  CUDA_TRY(cudaMemsetAsync(tickets, 0, (size_t)samples * sizeof(unsigned int), s));
+  dim3 grid(bps, (unsigned)samples);
+  minmax_kernel<<<grid, MM_THREADS, 0, s>>>(x, n, out, partial, tickets);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
 int histogram_launch(const float* x, long long n, long long samples, const float* th, const int* nb, int* hist,
                      int max_bins, cudaStream_t s) {
   if (samples == 0 || n == 0) return B200Q_OK;

@@ -10,6 +10,8 @@ size_t minmax_scratch_bytes(long long samples, int blocks_per_sample);
 // out[s] = {min, max} of x[s*n .. (s+1)*n); scratch must be zero-initialised once and is left re-armed
 int minmax_launch(const float* x, long long n, long long samples, float* out, void* scratch, int blocks_per_sample,
                   cudaStream_t s);
+// Same result as minmax_launch with the scratch in a fixed device array of the library: no allocation.
+int minmax_static_launch(const float* x, long long n, long long samples, float* out, cudaStream_t s);
 // hist[0 .. nb[s]) += histogram of sample s with threshold th[s]; th / nb are DEVICE arrays
 int histogram_launch(const float* x, long long n, long long samples, const float* th, const int* nb, int* hist,
                      int max_bins, cudaStream_t s);

@@ -145,6 +145,11 @@ int b200q_calib_minmax(void* ctx, const float* x_dev, int64_t n_per_sample, int6
   return minmax_launch(x_dev, n_per_sample, samples, out_dev, c->mm_scratch.p, bps, s);
 }
 
+int b200q_calib_minmax_noalloc(const float* x_dev, int64_t n_per_sample, int64_t samples, float* out_dev, void* stream) {
+  if (!x_dev || !out_dev || n_per_sample < 1 || samples < 0) return set_error(B200Q_ERR_INVALID, "calib_minmax_noalloc: bad argument");
+  return minmax_static_launch(x_dev, n_per_sample, samples, out_dev, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_calib_histogram(void* ctx, const float* x_dev, int64_t n_per_sample, int64_t samples, const float* th_host,
                           const int32_t* nbins_host, int32_t* hist_dev, int64_t hist_len, void* stream) {
   if (!ctx || !x_dev || !th_host || !nbins_host || !hist_dev || n_per_sample < 1 || samples < 0)
