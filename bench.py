@@ -134,18 +134,123 @@ def run_reference(args):
     return 0
 
 
+def _time_steps(fn, steps, warmup, flush=None, stream=None):
+    """Mean milliseconds per call of fn(), CUDA events on the current stream, optional L2 flush between calls."""
+    import torch
+    for _ in range(warmup):
+        if flush is not None:
+            flush.fill_(1)
+        fn()
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(steps):
+        if flush is not None:
+            flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    return float(np.mean(ms)), float(np.min(ms))
+
+
+def run_kernel_workload(args):
+    """Secondary lines (not the benchmark contract): one kernel each, device resident, against its roofline."""
+    import torch
+    import tpu_mlir_b200._lib as L
+    from tpu_mlir_b200 import synth
+    lib = L.lib()
+    torch.cuda.set_device(0)
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+    lines = []
+    if args.workload == "gemm":
+        M = N = K = 8192
+        a = torch.randint(-128, 128, (M, K), dtype=torch.int8, device="cuda")
+        b = torch.randint(-128, 128, (N, K), dtype=torch.int8, device="cuda")
+        out = torch.empty((M, N), dtype=torch.int8, device="cuda")
+        rng = np.random.default_rng(0)
+        mult, rshift = synth.qdm_params(rng, N)
+        keep = [torch.from_numpy(v.astype(np.int32)).cuda() for v in
+                (rng.integers(-2**16, 2**16, N), mult, -rshift)]
+        e = L.Epilogue(dialect=L.RQ_QDM, round_mode=L.ROUND_HALF_AWAY_FROM_ZERO, per_channel=1, out_zp=0,
+                       relu=L.RELU_NONE, out_dtype=L.DT_I8, scale=0.0, bias=keep[0].data_ptr(),
+                       multiplier=keep[1].data_ptr(), shift=keep[2].data_ptr())
+        st = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+        def go():
+            L.check(lib.b200q_gemm_i8_dev(P(a), L.DT_I8, P(b), L.DT_I8, M, N, K, C.byref(e), P(out), P(st),
+                                          L.ALGO_TENSOR_CORE, None))
+        mean_ms, _ = _time_steps(go, args.steps, args.warmup, flush)
+        assert int(st.item()) == 0
+        tops = 2.0 * M * N * K / (mean_ms * 1e-3) / 1e12
+        peak = 2 * peaks["bf16_tflops"]
+        lines.append(dict(metric="int8 matmul TOPS", value=tops, unit="TOPS", ms_per_step=mean_ms,
+                          config=dict(workload="int8 GEMM 8192x8192x8192, per-channel QDM requant, s8 out",
+                                      l2="flushed between steps"),
+                          roofline=dict(bound="tensor", achieved=tops, peak=peak, unit="TOPS", frac=tops / peak,
+                                        traffic=None, peak_basis=f"2 x {peaks['source']} dense bf16")))
+    elif args.workload == "a16":
+        for M in (1, 4, 8):
+            c = synth.a16_w4(seed=2, M=M)
+            x, wq, sc, zp = (torch.from_numpy(c[k]).cuda() for k in ("x", "wq", "scale", "zp"))
+            y = torch.empty((M, 11008), dtype=torch.uint16, device="cuda")
+
+            def go():
+                L.check(lib.b200q_a16_w4_dev(P(x), P(wq), P(sc), P(zp), None, P(y), M, 11008, 4096, 64, None, None))
+            mean_ms, _ = _time_steps(go, args.steps, args.warmup, flush)
+            nbytes = wq.numel() + sc.numel() * 2 + zp.numel() + x.numel() * 2 + y.numel() * 2
+            gbs = nbytes / (mean_ms * 1e-3) / 1e9
+            lines.append(dict(metric="w4bf16 GEMV GB/s", value=gbs, unit="GB/s", ms_per_step=mean_ms,
+                              config=dict(workload=f"A16MatMul w4bf16 N=11008 K=4096 group 64, M={M}",
+                                          l2="flushed between steps", bytes_per_call=int(nbytes)),
+                              roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s",
+                                            frac=gbs / peaks["hbm_gbs"], traffic=None,
+                                            peak_basis=f"{peaks['source']} copy bandwidth")))
+    else:
+        from tpu_mlir_b200.calibration import CaliMathB200
+        m = CaliMathB200()
+        S, n = 64, 64 * 112 * 112
+        x = torch.randn((S, n), dtype=torch.float32, device="cuda")
+        mm = m.minmax(x, samples=S).cpu().numpy()
+        th = np.maximum(np.abs(mm[:, 0]), np.abs(mm[:, 1])).astype(np.float32)
+        th[:] = th.max()
+        nb = np.full(S, 2048, np.int32)
+        hist = torch.zeros(2048, dtype=torch.int32, device="cuda")
+        mean_h, _ = _time_steps(lambda: m.histogram_into(hist, x, th, nb), args.steps, args.warmup, flush)
+        mean_m, _ = _time_steps(lambda: m.minmax(x, samples=S), args.steps, args.warmup, flush)
+        for name, ms in (("calibration histogram GB/s", mean_h), ("calibration min/max GB/s", mean_m)):
+            gbs = x.numel() * 4 / (ms * 1e-3) / 1e9
+            lines.append(dict(metric=name, value=gbs, unit="GB/s", ms_per_step=ms,
+                              config=dict(workload="64 samples x 64x112x112 float32 (largest ResNet-50 activation), "
+                                                   "2048 bins", l2="flushed between steps"),
+                              roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s",
+                                            frac=gbs / peaks["hbm_gbs"], traffic=None,
+                                            peak_basis=f"{peaks['source']} copy bandwidth (read-only kernel)")))
+    for ln in lines:
+        ln.update(n_gpus=1, steps=args.steps, warmup=args.warmup, higher_is_better=True, data="synthetic")
+        print(json.dumps(ln))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="conv", choices=["conv", "gemm", "a16", "hist"],
+                    help="conv = the benchmark contract (BASELINE config 1); the others time one more kernel each")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload != "conv":
+        return run_kernel_workload(args)
 
     import torch
     import torch.distributed as dist

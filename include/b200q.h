@@ -216,11 +216,12 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc *desc, float *const *in
 void b200q_a16matmul_deinit(void **handle);
 
 /* Device face: x bf16 [M,K], wq bytes [N,K/2], scale bf16 [N*K/group], zp uint8 [N*K/group] (each <= 127),
- * bias f32 [N] or NULL, y bf16 [M,N]; asynchronous on `stream`.  Replaces the per-call fp32 dequantisation
- * and sgemm of A16MatMul.cpp:171-208. */
+ * bias f32 [N] or NULL, y bf16 [M,N]; asynchronous on `stream`.  `status` is an optional device int that
+ * receives a non-zero code if a bounded wait in the kernel ran out.  Replaces the per-call fp32
+ * dequantisation and sgemm of A16MatMul.cpp:171-208. */
 int b200q_a16_w4_dev(const void *x_bf16, const void *wq, const void *scale_bf16, const void *zp_u8,
                      const float *bias_f32, void *y_bf16, int64_t M, int64_t N, int64_t K, int32_t group,
-                     void *stream);
+                     int32_t *status, void *stream);
 
 /* ------------------------------------------------------------------ calibration math
  * A context owns the scratch memory of the kernels; one context per thread/stream.

@@ -29,7 +29,7 @@ def run_dev(c, M, N, K, group, bias=None):
     x, wq, sc, zp = dev(c["x"]), dev(c["wq"]), dev(c["scale"]), dev(c["zp"])
     b = dev(bias) if bias is not None else None
     y = torch.empty((M, N), dtype=torch.uint16, device="cuda")
-    L.check(L.lib().b200q_a16_w4_dev(ptr(x), ptr(wq), ptr(sc), ptr(zp), ptr(b), ptr(y), M, N, K, group, None))
+    L.check(L.lib().b200q_a16_w4_dev(ptr(x), ptr(wq), ptr(sc), ptr(zp), ptr(b), ptr(y), M, N, K, group, None, None))
     torch.cuda.synchronize()
     return y.cpu().numpy()
 

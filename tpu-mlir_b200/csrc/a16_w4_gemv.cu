@@ -4,29 +4,37 @@
 // (lib/Dialect/Tpu/Interfaces/Common/A16MatMul.cpp:171-208,:240-246): weight bytes [N, K/2] with the even k in
 // the low nibble, W[n,k] = (q - zp[n, k/g]) * scale[n, k/g], fp32 accumulation, bf16 output.
 //
-// The kernel is bound by reading the packed weights once from HBM.  A block of 4 warps owns 16 output rows;
-// each warp takes a quarter of K and issues all of its 8-byte weight loads up front.  Nibbles become exact
-// bf16 integers with one logic op each ((w >> 4j) & 0x000F000F | 0x43004300 = 128 + q), the zero point is
-// removed with one bf16x2 subtract, and the products run on the tensor cores as mma.m16n8k16 (bf16 x bf16,
-// fp32 accumulate) with the M tokens in the 8 columns.  Because a dot product does not care about the order
-// of k, the activations are staged in shared memory pre-permuted to the nibble order the extraction yields.
-// The group scale multiplies the fp32 partial sum of each group, so the only rounding is fp32 accumulation.
+// The kernel is bound by reading the packed weights once from HBM.  It is persistent: one block per SM walks
+// slabs of 16 output rows (a contiguous 16 * K/2 byte piece of the weight matrix).  A producer warp streams
+// slabs into a shared-memory ring with bulk copies (cp.async.bulk, one per slab) plus the slab's
+// scales and zero points, running ahead of the 16 consumer warps, which split K.  The activations are staged
+// in shared memory once per block.  Nibbles become exact bf16 integers with one logic op each
+// ((w >> 4j) & 0x000F000F | 0x43004300 = 128 + q), 128 + zero point is removed with one bf16x2 fma, and the
+// products run on the tensor cores as mma.m16n8k16 (bf16 x bf16, fp32 accumulate) with the M tokens in the 8
+// columns.  Because a dot product does not care about the order of k, the activations are stored pre-permuted
+// to the nibble order the extraction yields.  The group scale multiplies the fp32 partial sum of each group,
+// so the only rounding is fp32 accumulation.  Every wait is bounded; a wait that runs out sets *status.
 #include <cuda_bf16.h>
 
 #include "a16.h"
 #include "internal.h"
+#include "ptx_sm100.cuh"
 
 namespace b200q {
 namespace {
 
-constexpr int ROWS_PER_BLOCK = 16;
-constexpr int WARPS = 4;
-constexpr int CHUNK_K = 64;   // k covered by one 8-byte load per (thread, row): the quad of a row covers 64 k
+constexpr int ROWS = 16;           // rows per slab = M of the MMA
+constexpr int CWARPS = 16;         // consumer warps (split K)
+constexpr int THREADS = (CWARPS + 1) * 32;
+constexpr int CHUNK_K = 64;        // k covered by one 8-byte load per (lane, row): the quad of a row covers 64 k
 constexpr int MAX_M = 8;
+constexpr int MAX_STAGES = 4;
+constexpr uint64_t WAIT_NS = 2000000000ull;
 
+// a - b on packed bf16 as one fused multiply-add a * 1.0 + (-b) (exact here: small integers)
 __device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
   uint32_t d;
-  asm("sub.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(0x3F803F80u), "r"(b ^ 0x80008000u));
   return d;
 }
 
@@ -39,116 +47,253 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
-
-// x_perm layout (bf16): row m at m * row_bytes; inside a row, 64-k chunk j at j*128 bytes; inside a chunk,
-// quad lane c (k offset c*16) at c*32 bytes, word w (k offset w*8) at w*16 bytes, then the 8 values in nibble
-// order (0,4,1,5,2,6,3,7).  row_bytes = 2K + 16 keeps two rows a bank group apart.
-__device__ __forceinline__ int xperm_offset_bytes(int k) {
-  const int chunk = k >> 6, c = (k >> 4) & 3, w = (k >> 3) & 1, nib = k & 7;
-  const int pos = ((nib & 3) << 1) | (nib >> 2);  // 0,4,1,5,2,6,3,7 -> 0..7
-  return chunk * 128 + c * 32 + w * 16 + pos * 2;
+// x_perm layout (bf16): row m at m * row_bytes; inside a row, the 8 values k0..k0+7 (k0 % 8 == 0) sit at
+// (k0 / 64) * 128 + ((k0 / 16) % 4) * 32 + ((k0 / 8) % 2) * 16 bytes in nibble order (0,4,1,5,2,6,3,7): exactly the
+// 16 bytes one lane needs for the two MMAs of one packed 32-bit weight word.  row_bytes = 2K + 16 keeps two
+// rows a bank group apart.
+__device__ __forceinline__ int xperm_offset_bytes8(int k0) {
+  return (k0 >> 6) * 128 + ((k0 >> 4) & 3) * 32 + ((k0 >> 3) & 1) * 16;
 }
 
-template <int CHUNKS_PER_WARP_BATCH>
-__global__ void __launch_bounds__(WARPS * 32)
+// Shared-memory plan, identical on host and device.
+struct GemvPlan {
+  int w_pitch;        // weight row pitch in shared memory (dense; the 4-way bank conflict of the 8-byte fragment
+                      // loads costs far less than issuing one small bulk copy per row)
+  int gpr;            // groups per row
+  int scale_off;      // inside a stage: weights | scales (bf16) | zero points
+  int zp_off;
+  int stage_bytes;
+  int x_off, red_off, bar_off, total;
+  int stages;
+};
+__host__ __device__ inline GemvPlan gemv_plan(int M, int K, int group) {
+  GemvPlan p;
+  p.w_pitch = K / 2;  // dense: the slab is one contiguous piece of global memory and arrives as ONE bulk copy
+  p.gpr = K / group;
+  p.scale_off = ROWS * p.w_pitch;
+  p.zp_off = p.scale_off + ((ROWS * p.gpr * 2 + 15) & ~15);
+  p.stage_bytes = (p.zp_off + ROWS * p.gpr + 127) & ~127;
+  const int x_bytes = (M * (2 * K + 16) + 127) & ~127;
+  const int red_bytes = 2 * CWARPS * ROWS * 8 * 4;
+  const int fixed = x_bytes + red_bytes + 128;
+  int st = (220 * 1024 - fixed) / p.stage_bytes;
+  p.stages = st > MAX_STAGES ? MAX_STAGES : st;
+  p.x_off = p.stages * p.stage_bytes;
+  p.red_off = p.x_off + x_bytes;
+  p.bar_off = p.red_off + red_bytes;
+  p.total = p.bar_off + 128;
+  return p;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
 a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
                    const __nv_bfloat16* __restrict__ scale, const uint8_t* __restrict__ zp,
-                   const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int M, int N, int K, int group) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  const int row_bytes = 2 * K + 16;
-  uint8_t* xs = smem;                                                   // M rows of permuted activations
-  float* red = reinterpret_cast<float*>(smem + (size_t)M * row_bytes);  // [WARPS][16 rows][8 cols]
-
+                   const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int M, int N, int K, int group,
+                   int* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const GemvPlan P = gemv_plan(M, K, group);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = lane >> 2, c = lane & 3;
-  // ---- stage the activations (bf16, permuted)
-  for (int i = tid; i < M * K; i += WARPS * 32) {
-    const int m = i / K, k = i - m * K;
-    *reinterpret_cast<__nv_bfloat16*>(xs + (size_t)m * row_bytes + xperm_offset_bytes(k)) = x[i];
+  const uint32_t bar_base = ptx::smem_u32(smem + P.bar_off);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P.bar_off + 16 * MAX_STAGES);
+  const int num_slabs = (N + ROWS - 1) / ROWS;
+  const int row_bytes = 2 * K + 16;
+
+  if (tid == 0) {
+    for (int s = 0; s < P.stages; ++s) {
+      ptx::mbar_init(full_bar(s), 2);  // bulk-copy issue (with byte count) + metadata ready
+      ptx::mbar_init(empty_bar(s), CWARPS);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
   }
   __syncthreads();
 
-  const int n0 = blockIdx.x * ROWS_PER_BLOCK;
-  const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);  // clamped: rows past N are computed, not stored
-  const int chunks = K / CHUNK_K;
-  const int chunks_per_warp = (chunks + WARPS - 1) / WARPS;
-  const int ch_begin = warp * chunks_per_warp, ch_end = min(chunks, ch_begin + chunks_per_warp);
-  const int groups_per_row = K / group;
-  const int chunks_per_group = group / CHUNK_K;
-  const uint8_t* w0p = wq + (size_t)r0 * (K / 2) + c * 8;
-  const uint8_t* w1p = wq + (size_t)r1 * (K / 2) + c * 8;
-  const uint8_t* xrow = xs + (size_t)g * row_bytes + c * 32;  // this lane's token (column g of the MMA)
-  const bool has_x = g < M;
+  if (warp == CWARPS) {
+    // ------------------------------------------------------------ producer warp
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x) {
+      bool ok = true;
+      if (lane == 0) ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, WAIT_NS);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      uint8_t* st = smem + (size_t)stage * P.stage_bytes;
+      const int n0 = slab * ROWS;
+      const int rows = min(ROWS, N - n0);
+      // scales and zero points of the slab are contiguous in global memory (rows are adjacent)
+      const int nmeta = rows * P.gpr;
+      const __nv_bfloat16* gs = scale + (size_t)n0 * P.gpr;
+      const uint8_t* gz = zp + (size_t)n0 * P.gpr;
+      __nv_bfloat16* ss = reinterpret_cast<__nv_bfloat16*>(st + P.scale_off);
+      uint8_t* sz = st + P.zp_off;
+      const bool meta_bulk = (nmeta % 16 == 0) && ((reinterpret_cast<uintptr_t>(gs) & 15) == 0) &&
+                             ((reinterpret_cast<uintptr_t>(gz) & 15) == 0);
+      if (lane == 0) {
+        ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)rows * (uint32_t)(K / 2) + (meta_bulk ? (uint32_t)nmeta * 3u : 0u));
+        ptx::bulk_load_1d(ptx::smem_u32(st), wq + (size_t)n0 * (K / 2), (uint32_t)rows * (uint32_t)(K / 2), full_bar(stage));
+        if (meta_bulk) {
+          ptx::bulk_load_1d(ptx::smem_u32(ss), gs, (uint32_t)nmeta * 2u, full_bar(stage));
+          ptx::bulk_load_1d(ptx::smem_u32(sz), gz, (uint32_t)nmeta, full_bar(stage));
+        }
+      }
+      if (!meta_bulk) {  // ragged tail or unaligned metadata: plain loads, all issued before the stores
+        for (int i0 = 0; i0 < nmeta; i0 += 32 * 8) {
+          __nv_bfloat16 tv[8];
+          uint8_t tz[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * 32 + lane;
+            if (i < nmeta) {
+              tv[j] = gs[i];
+              tz[j] = gz[i];
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * 32 + lane;
+            if (i < nmeta) {
+              ss[i] = tv[j];
+              sz[i] = tz[j];
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(full_bar(stage));  // second arrival of the phase: metadata is in place
+      if (++stage == P.stages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ consumer warps
+    uint8_t* xs = smem + P.x_off;
+    // stage the activations once per block (bf16, 8 values per 16-byte move, permuted to nibble order)
+    const int kv = K / 8;
+    for (int i = tid; i < M * kv; i += CWARPS * 32) {
+      const int m = i / kv, k0 = (i - m * kv) * 8;
+      const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + k0);
+      uint4 o;
+      o.x = __byte_perm(v.x, v.z, 0x5410);  // (k0, k4)
+      o.y = __byte_perm(v.x, v.z, 0x7632);  // (k1, k5)
+      o.z = __byte_perm(v.y, v.w, 0x5410);  // (k2, k6)
+      o.w = __byte_perm(v.y, v.w, 0x7632);  // (k3, k7)
+      *reinterpret_cast<uint4*>(xs + (size_t)m * row_bytes + xperm_offset_bytes8(k0)) = o;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory");
 
-  float tot[4] = {0.f, 0.f, 0.f, 0.f};
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int cb = ch_begin; cb < ch_end; cb += CHUNKS_PER_WARP_BATCH) {
-    uint2 wa[CHUNKS_PER_WARP_BATCH], wb[CHUNKS_PER_WARP_BATCH];
+    const int g = lane >> 2, c = lane & 3;
+    const int chunks = K / CHUNK_K;
+    const int cpw = (chunks + CWARPS - 1) / CWARPS;
+    const int ch_begin = min(warp * cpw, chunks), ch_end = min(chunks, ch_begin + cpw);
+    const int cpg = group / CHUNK_K;  // chunks per group
+    const uint8_t* xrow = xs + (size_t)g * row_bytes + c * 32;  // this lane's token (column g of the MMA)
+    const bool has_x = g < M;
+    float* red = reinterpret_cast<float*>(smem + P.red_off);
+    int stage = 0;
+    uint32_t phase = 0;
+    int it = 0;
+    for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x, ++it) {
+      if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, 2, WAIT_NS)) break;
+      const uint8_t* st = smem + (size_t)stage * P.stage_bytes;
+      const int n0 = slab * ROWS;
+      const int rows = min(ROWS, N - n0);
+      const int rl0 = min(g, rows - 1), rl1 = min(g + 8, rows - 1);  // rows past N are computed from a valid row, not stored
+      const uint8_t* w0p = st + (size_t)rl0 * P.w_pitch + c * 8;
+      const uint8_t* w1p = st + (size_t)rl1 * P.w_pitch + c * 8;
+      const __nv_bfloat16* sc0 = reinterpret_cast<const __nv_bfloat16*>(st + P.scale_off) + rl0 * P.gpr;
+      const __nv_bfloat16* sc1 = reinterpret_cast<const __nv_bfloat16*>(st + P.scale_off) + rl1 * P.gpr;
+      const uint8_t* zp0 = st + P.zp_off + rl0 * P.gpr;
+      const uint8_t* zp1 = st + P.zp_off + rl1 * P.gpr;
+      float tot[4] = {0.f, 0.f, 0.f, 0.f};
+      float acc[4][4] = {};  // one accumulator per k-step of a chunk: four independent MMA chains
+      int grp = ch_begin / cpg, in_grp = ch_begin - grp * cpg;
+      uint32_t z0 = zp0[grp], z1 = zp1[grp];
+      uint32_t zc0 = __byte_perm(z0, 0x43u, 0x4040), zc1 = __byte_perm(z1, 0x43u, 0x4040);  // bf16x2 (128 + zp)
+#pragma unroll 4
+      for (int ch = ch_begin; ch < ch_end; ++ch) {
+        const uint2 wa = *reinterpret_cast<const uint2*>(w0p + ch * 32);
+        const uint2 wb = *reinterpret_cast<const uint2*>(w1p + ch * 32);
+        uint4 xb0 = make_uint4(0, 0, 0, 0), xb1 = make_uint4(0, 0, 0, 0);
+        if (has_x) {
+          xb0 = *reinterpret_cast<const uint4*>(xrow + ch * 128);
+          xb1 = *reinterpret_cast<const uint4*>(xrow + ch * 128 + 16);
+        }
+        const uint32_t wwa[2] = {wa.x, wa.y}, wwb[2] = {wb.x, wb.y};
+        const uint4 xbs[2] = {xb0, xb1};
 #pragma unroll
-    for (int i = 0; i < CHUNKS_PER_WARP_BATCH; ++i) {
-      const int ch = min(cb + i, ch_end - 1);
-      wa[i] = __ldg(reinterpret_cast<const uint2*>(w0p + (size_t)ch * 32));
-      wb[i] = __ldg(reinterpret_cast<const uint2*>(w1p + (size_t)ch * 32));
-    }
+        for (int w = 0; w < 2; ++w) {
+          const uint32_t a = wwa[w], b = wwb[w];
+          const uint32_t a4 = a >> 4, a8 = a >> 8, a12 = a >> 12;
+          const uint32_t b4 = b >> 4, b8 = b >> 8, b12 = b >> 12;
+          // k-step 0 of this word: nibbles (0,4) -> slots (2c, 2c+1), nibbles (1,5) -> slots (2c+8, 2c+9)
+          uint32_t a0 = sub_bf16x2((a & 0x000F000Fu) | 0x43004300u, zc0);
+          uint32_t a2 = sub_bf16x2((a4 & 0x000F000Fu) | 0x43004300u, zc0);
+          uint32_t a1 = sub_bf16x2((b & 0x000F000Fu) | 0x43004300u, zc1);
+          uint32_t a3 = sub_bf16x2((b4 & 0x000F000Fu) | 0x43004300u, zc1);
+          mma_bf16_16816(acc[2 * w], a0, a1, a2, a3, xbs[w].x, xbs[w].y);
+          // k-step 1: nibbles (2,6) and (3,7)
+          a0 = sub_bf16x2((a8 & 0x000F000Fu) | 0x43004300u, zc0);
+          a2 = sub_bf16x2((a12 & 0x000F000Fu) | 0x43004300u, zc0);
+          a1 = sub_bf16x2((b8 & 0x000F000Fu) | 0x43004300u, zc1);
+          a3 = sub_bf16x2((b12 & 0x000F000Fu) | 0x43004300u, zc1);
+          mma_bf16_16816(acc[2 * w + 1], a0, a1, a2, a3, xbs[w].z, xbs[w].w);
+        }
+        if (++in_grp == cpg || ch + 1 == ch_end) {
+          // the group (or this warp's part of it) is complete: apply its scale to the fp32 partial sum
+          const float s0 = __bfloat162float(sc0[grp]), s1 = __bfloat162float(sc1[grp]);
+          float sum4[4];
 #pragma unroll
-    for (int i = 0; i < CHUNKS_PER_WARP_BATCH; ++i) {
-      const int ch = cb + i;
-      if (ch >= ch_end) break;
-      const int grp = ch / chunks_per_group;
-      const uint32_t z0 = zp[(size_t)r0 * groups_per_row + grp], z1 = zp[(size_t)r1 * groups_per_row + grp];
-      const uint32_t zc0 = 0x43004300u | z0 | (z0 << 16), zc1 = 0x43004300u | z1 | (z1 << 16);
-      uint4 xb0 = make_uint4(0, 0, 0, 0), xb1 = make_uint4(0, 0, 0, 0);
-      if (has_x) {
-        xb0 = lds128(xrow + ch * 128);
-        xb1 = lds128(xrow + ch * 128 + 16);
+          for (int j = 0; j < 4; ++j) {
+            sum4[j] = (acc[0][j] + acc[1][j]) + (acc[2][j] + acc[3][j]);
+            acc[0][j] = acc[1][j] = acc[2][j] = acc[3][j] = 0.f;
+          }
+          tot[0] = fmaf(sum4[0], s0, tot[0]);
+          tot[1] = fmaf(sum4[1], s0, tot[1]);
+          tot[2] = fmaf(sum4[2], s1, tot[2]);
+          tot[3] = fmaf(sum4[3], s1, tot[3]);
+          in_grp = 0;
+          ++grp;
+          if (ch + 1 < ch_end) {
+            z0 = zp0[grp];
+            z1 = zp1[grp];
+            zc0 = __byte_perm(z0, 0x43u, 0x4040);
+            zc1 = __byte_perm(z1, 0x43u, 0x4040);
+          }
+        }
       }
-      const uint32_t wwa[2] = {wa[i].x, wa[i].y}, wwb[2] = {wb[i].x, wb[i].y};
-      const uint4 xbs[2] = {xb0, xb1};
-#pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const uint32_t a = wwa[w], b = wwb[w];
-        // k-step 0 of this word: nibbles (0,4) -> slots (2c, 2c+1), nibbles (1,5) -> slots (2c+8, 2c+9)
-        uint32_t a0 = sub_bf16x2((a & 0x000F000Fu) | 0x43004300u, zc0);
-        uint32_t a2 = sub_bf16x2(((a >> 4) & 0x000F000Fu) | 0x43004300u, zc0);
-        uint32_t a1 = sub_bf16x2((b & 0x000F000Fu) | 0x43004300u, zc1);
-        uint32_t a3 = sub_bf16x2(((b >> 4) & 0x000F000Fu) | 0x43004300u, zc1);
-        mma_bf16_16816(acc, a0, a1, a2, a3, xbs[w].x, xbs[w].y);
-        // k-step 1: nibbles (2,6) and (3,7)
-        a0 = sub_bf16x2(((a >> 8) & 0x000F000Fu) | 0x43004300u, zc0);
-        a2 = sub_bf16x2(((a >> 12) & 0x000F000Fu) | 0x43004300u, zc0);
-        a1 = sub_bf16x2(((b >> 8) & 0x000F000Fu) | 0x43004300u, zc1);
-        a3 = sub_bf16x2(((b >> 12) & 0x000F000Fu) | 0x43004300u, zc1);
-        mma_bf16_16816(acc, a0, a1, a2, a3, xbs[w].z, xbs[w].w);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(empty_bar(stage));  // this warp no longer reads the stage
+      if (++stage == P.stages) {
+        stage = 0;
+        phase ^= 1u;
       }
-      if ((ch + 1) % chunks_per_group == 0 || ch + 1 == ch_end) {
-        // the group (or this warp's part of it) is complete: apply its scale to the fp32 partial sum
-        const float s0 = __bfloat162float(scale[(size_t)r0 * groups_per_row + grp]);
-        const float s1 = __bfloat162float(scale[(size_t)r1 * groups_per_row + grp]);
-        tot[0] = fmaf(acc[0], s0, tot[0]);
-        tot[1] = fmaf(acc[1], s0, tot[1]);
-        tot[2] = fmaf(acc[2], s1, tot[2]);
-        tot[3] = fmaf(acc[3], s1, tot[3]);
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      // ---- combine the K parts of the warps: tot[0..1] = (row g, tokens 2c, 2c+1), tot[2..3] = (row g+8, ..)
+      float* mine = red + (size_t)(it & 1) * (CWARPS * ROWS * 8) + warp * (ROWS * 8);
+      mine[g * 8 + 2 * c] = tot[0];
+      mine[g * 8 + 2 * c + 1] = tot[1];
+      mine[(g + 8) * 8 + 2 * c] = tot[2];
+      mine[(g + 8) * 8 + 2 * c + 1] = tot[3];
+      asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory");
+      if (tid < ROWS * 8) {
+        const int row = tid >> 3, m = tid & 7;
+        const int n = n0 + row;
+        if (n < N && m < M) {
+          const float* rb = red + (size_t)(it & 1) * (CWARPS * ROWS * 8) + tid;
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < CWARPS; ++w) v += rb[w * (ROWS * 8)];
+          if (bias) v += bias[n];
+          y[(size_t)m * N + n] = __float2bfloat16_rn(v);
+        }
       }
     }
   }
-  // ---- combine the K quarters of the 4 warps: tot[0..1] = (row g, tokens 2c, 2c+1), tot[2..3] = (row g+8, ..)
-  float* mine = red + warp * (16 * 8);
-  mine[g * 8 + 2 * c] = tot[0];
-  mine[g * 8 + 2 * c + 1] = tot[1];
-  mine[(g + 8) * 8 + 2 * c] = tot[2];
-  mine[(g + 8) * 8 + 2 * c + 1] = tot[3];
   __syncthreads();
-  for (int i = tid; i < 16 * 8; i += WARPS * 32) {
-    const int row = i >> 3, m = i & 7;
-    const int n = n0 + row;
-    if (n < N && m < M) {
-      float v = red[i] + red[128 + i] + red[256 + i] + red[384 + i];
-      if (bias) v += bias[n];
-      y[(size_t)m * N + n] = __float2bfloat16_rn(v);
-    }
-  }
+  if (tid == 0 && *abort_flag != 0 && status != nullptr) atomicCAS(status, 0, *abort_flag);
 }
 
 }  // namespace
@@ -158,24 +303,29 @@ int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why) {
   if (M < 1 || M > MAX_M) w = "M must be in [1, 8]";
   else if (K % CHUNK_K != 0) w = "K must be a multiple of 64";
   else if (group < CHUNK_K || group % CHUNK_K != 0 || K % group != 0) w = "group size must be a multiple of 64 dividing K";
-  else if ((size_t)M * (2 * K + 16) + WARPS * 16 * 8 * 4 > 200 * 1024) w = "activations do not fit in shared memory";
   else if (N < 1) w = "empty N";
+  else if (gemv_plan(M, K, group).stages < 2) w = "two 16-row weight slabs plus the activations do not fit in shared memory";
   if (why) *why = w;
   return w == nullptr;
 }
 
 int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
-                       int M, int N, int K, int group, cudaStream_t stream) {
+                       int M, int N, int K, int group, int* status, cudaStream_t stream) {
   const char* why = nullptr;
   if (!a16_w4_gemv_supported(M, N, K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: %s", why);
-  if ((reinterpret_cast<uintptr_t>(wq) & 7) != 0) return set_error(B200Q_ERR_INVALID, "a16 w4 gemv: weight pointer must be 8-byte aligned");
-  const size_t smem = (size_t)M * (2 * K + 16) + WARPS * 16 * 8 * 4;
-  auto kfn = a16_w4_gemv_kernel<8>;
-  CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const int blocks = (N + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
-  kfn<<<blocks, WARPS * 32, smem, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
+  if ((reinterpret_cast<uintptr_t>(wq) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+    return set_error(B200Q_ERR_INVALID, "a16 w4 gemv: weights and activations must be 16-byte aligned");
+  const GemvPlan P = gemv_plan(M, K, group);
+  auto kfn = a16_w4_gemv_kernel;
+  CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, P.total));
+  int dev = 0, sms = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int slabs = (N + ROWS - 1) / ROWS;
+  const int blocks = slabs < sms ? slabs : sms;
+  kfn<<<blocks, THREADS, P.total, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
                                             static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp),
-                                            bias, static_cast<__nv_bfloat16*>(y), M, N, K, group);
+                                            bias, static_cast<__nv_bfloat16*>(y), M, N, K, group, status);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

@@ -46,19 +46,19 @@ int validate(const b200q_a16matmul_desc& d) {
 
 // Decode shapes go to the GEMV kernel; larger M is processed in slices of 8 tokens.
 int a16_dispatch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
-                 long long M, int N, int K, int group, cudaStream_t s) {
+                 long long M, int N, int K, int group, int* status, cudaStream_t s) {
   const char* why = nullptr;
   if (!a16_w4_gemv_supported(1, N, K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: %s", why);
   for (long long m0 = 0; m0 < M; m0 += 8) {
     const int mm = (int)((M - m0) < 8 ? (M - m0) : 8);
     B200Q_TRY(a16_w4_gemv_launch(static_cast<const uint8_t*>(x) + (size_t)m0 * K * 2, wq, scale, zp, bias,
-                                 static_cast<uint8_t*>(y) + (size_t)m0 * N * 2, mm, N, K, group, s));
+                                 static_cast<uint8_t*>(y) + (size_t)m0 * N * 2, mm, N, K, group, status, s));
   }
   return B200Q_OK;
 }
 
 struct A16Handle {
-  DevBuf stage, x16, wq, scale, zp, bias, y16, y32;
+  DevBuf stage, x16, wq, scale, zp, bias, y16, y32, status;
   bool weights_ready = false;
   int weight_version = -1;
   const float* weight_ptr = nullptr;
@@ -127,13 +127,18 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
     if ((rc = h->x16.ensure(x_elems * 2))) break;
     if ((rc = h->y16.ensure(y_elems * 2))) break;
     if ((rc = h->y32.ensure(y_elems * 4))) break;
+    if ((rc = h->status.ensure(4))) break;
+    if (cudaMemsetAsync(h->status.p, 0, 4, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "memset", __FILE__, __LINE__); break; }
     if (cudaMemcpyAsync(h->stage.p, inputs[0], x_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D input", __FILE__, __LINE__); break; }
     if ((rc = f32_to_bf16(h->stage.as<float>(), h->x16.p, (long long)x_elems, s))) break;
     if ((rc = a16_dispatch(h->x16.p, h->wq.p, h->scale.p, h->zp.p, bias_f ? h->bias.as<float>() : nullptr, h->y16.p,
-                           d.M, (int)d.N, (int)d.K, d.q_group_size, s))) break;
+                           d.M, (int)d.N, (int)d.K, d.q_group_size, h->status.as<int>(), s))) break;
     if ((rc = bf16_to_f32(h->y16.p, h->y32.as<float>(), (long long)y_elems, s))) break;
     if (cudaMemcpyAsync(outputs[0], h->y32.p, y_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__); break; }
+    int hstat = 0;
+    if (cudaMemcpyAsync(&hstat, h->status.p, 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H status", __FILE__, __LINE__); break; }
     if (cudaStreamSynchronize(s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "sync", __FILE__, __LINE__); break; }
+    if (hstat != 0) { rc = set_error(B200Q_ERR_TIMEOUT, "a16matmul: a bounded wait inside the kernel ran out (wait site %d)", hstat); break; }
   } while (0);
   if (rc != B200Q_OK) cudaStreamSynchronize(s);
   if (own) b200q_a16matmul_deinit(handle);
@@ -141,10 +146,11 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
 }
 
 int b200q_a16_w4_dev(const void* x_bf16, const void* wq, const void* scale_bf16, const void* zp_u8,
-                     const float* bias_f32, void* y_bf16, int64_t M, int64_t N, int64_t K, int32_t group, void* stream) {
+                     const float* bias_f32, void* y_bf16, int64_t M, int64_t N, int64_t K, int32_t group,
+                     int32_t* status, void* stream) {
   if (!x_bf16 || !wq || !scale_bf16 || !zp_u8 || !y_bf16) return set_error(B200Q_ERR_INVALID, "a16_w4_dev: null argument");
   if (M < 0 || N < 1 || K < 1 || N > 0x7fffffffLL || K > 0x7fffffffLL || group < 1) return set_error(B200Q_ERR_INVALID, "a16_w4_dev: bad shape");
-  return a16_dispatch(x_bf16, wq, scale_bf16, zp_u8, bias_f32, y_bf16, M, (int)N, (int)K, group,
+  return a16_dispatch(x_bf16, wq, scale_bf16, zp_u8, bias_f32, y_bf16, M, (int)N, (int)K, group, status,
                       static_cast<cudaStream_t>(stream));
 }
 
