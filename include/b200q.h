@@ -223,6 +223,16 @@ int b200q_a16_w4_dev(const void *x_bf16, const void *wq, const void *scale_bf16,
                      const float *bias_f32, void *y_bf16, int64_t M, int64_t N, int64_t K, int32_t group,
                      int32_t *status, void *stream);
 
+/* Device face with a handle: the tensors stay the caller's (not copied).  M <= 8 runs the decode kernel on the
+ * packed weights; larger M dequantises the weight once into bf16 (kept in the handle, N*K*2 bytes) and runs
+ * a bf16 tensor-core GEMM with fp32 accumulation.  b200q_a16_dev_status synchronises the stream and reports a
+ * kernel-side timeout. */
+int b200q_a16_dev_create(const void *wq, const void *scale_bf16, const void *zp_u8, const float *bias_f32,
+                         int64_t N, int64_t K, int32_t group, void **handle);
+int b200q_a16_dev_run(void *handle, const void *x_bf16, void *y_bf16, int64_t M, void *stream);
+int b200q_a16_dev_status(void *handle, void *stream);
+void b200q_a16_dev_destroy(void **handle);
+
 /* ------------------------------------------------------------------ calibration math
  * A context owns the scratch memory of the kernels; one context per thread/stream.
  * All tensor pointers are DEVICE pointers unless named *_host. */

@@ -75,3 +75,57 @@ def test_unsupported_is_reported():
                                                 np.zeros(32, np.float32), np.zeros(32, np.float32), None],
                                         outputs=[np.zeros((1, 16), np.float32)]))
     assert ei.value.code == L.ERR_UNSUPPORTED
+
+
+def check_prefill(y_bits, ref_f32):
+    """Prefill rounds the dequantised weight to bf16 before the tensor-core GEMM (2^-9 relative per weight, which
+    shows up as ~1e-3 * rms(y) of absolute noise), so the floor of the relative bound is rms(y_ref) itself, and
+    both sides are rounded to bf16 afterwards, which can add one bf16 ulp:
+    |y - y_ref| <= 1e-2 * max(|y_ref|, rms(y_ref)) + ulp_bf16(y_ref)."""
+    y = oracle.bf16_bits_to_f32(y_bits).astype(np.float64)
+    r = np.asarray(ref_f32, dtype=np.float64)
+    rms = np.sqrt(np.mean(r * r))
+    ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(r), 1e-30))) - 7)
+    bad = np.abs(y - r) > 1e-2 * np.maximum(np.abs(r), rms) + ulp
+    assert not bad.any(), (int(bad.sum()), float(np.abs(y - r).max()), float(rms))
+    assert float(np.sqrt(np.mean((y - r) ** 2))) < 3e-3 * rms
+
+
+def run_handle(c, M, N, K, group, bias=None):
+    x, wq, sc, zp = dev(c["x"]), dev(c["wq"]), dev(c["scale"]), dev(c["zp"])
+    b = dev(bias) if bias is not None else None
+    y = torch.empty((M, N), dtype=torch.uint16, device="cuda")
+    h = C.c_void_p()
+    lib = L.lib()
+    L.check(lib.b200q_a16_dev_create(ptr(wq), ptr(sc), ptr(zp), ptr(b), N, K, group, C.byref(h)))
+    for _ in range(2):     # the second run reuses the dequantised weight kept in the handle
+        L.check(lib.b200q_a16_dev_run(h, ptr(x), ptr(y), M, None))
+    L.check(lib.b200q_a16_dev_status(h, None))
+    lib.b200q_a16_dev_destroy(C.byref(h))
+    return y.cpu().numpy()
+
+
+@pytest.mark.parametrize("M", [16, 128])
+def test_prefill_llama_mlp_shape_against_oracle(M):
+    c = synth.a16_w4(seed=2, M=M)
+    ref = oracle.bf16_bits_to_f32(oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], group=64))
+    check_prefill(run_handle(c, M, 11008, 4096, 64), ref)
+
+
+def test_prefill_2048_tokens_against_fp32_matmul():
+    """BASELINE config 2 at M=2048: the fp32 reference is the oracle's dequantised weight times x in fp32 (torch)."""
+    M = 2048
+    c = synth.a16_w4(seed=2, M=M)
+    W = torch.from_numpy(oracle.a16_dequant_w4(c["wq"], c["scale"], c["zp"], group=64)).cuda()
+    x = torch.from_numpy(oracle.bf16_bits_to_f32(c["x"])).cuda()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref = (x @ W.T).cpu().numpy()
+    check_prefill(run_handle(c, M, 11008, 4096, 64), ref)
+
+
+def test_prefill_ragged_with_bias():
+    M, K, N, g = 37, 320, 200, 64
+    c = synth.a16_w4(seed=5, M=M, K=K, N=N, group=g)
+    bias = np.random.default_rng(2).standard_normal(N).astype(np.float32)
+    ref = oracle.bf16_bits_to_f32(oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], bias, group=g))
+    check_prefill(run_handle(c, M, N, K, g, bias), ref)

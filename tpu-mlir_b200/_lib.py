@@ -84,6 +84,10 @@ SIGNATURES = {
     "b200q_a16matmul_deinit": (None, [_VPP]),
     "b200q_a16_w4_dev": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
                                    C.c_void_p]),
+    "b200q_a16_dev_create": (C.c_int, [C.c_void_p] * 4 + [C.c_int64, C.c_int64, C.c_int32, _VPP]),
+    "b200q_a16_dev_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "b200q_a16_dev_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200q_a16_dev_destroy": (None, [_VPP]),
     "b200q_calib_create": (C.c_int, [_VPP]),
     "b200q_calib_destroy": (None, [_VPP]),
     "b200q_calib_minmax": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),

@@ -5,6 +5,7 @@
 #include <new>
 
 #include "a16.h"
+#include "igemm.h"
 #include "devbuf.h"
 #include "internal.h"
 #include "layout.h"
@@ -34,6 +35,62 @@ int bf16_to_f32(const void* x, float* y, long long n, cudaStream_t s) {
   return B200Q_OK;
 }
 
+// W[n,k] = bf16((q - zp) * scale): the dequantised weight the prefill GEMM reads (A16MatMul.cpp:190-198 builds
+// the same matrix in fp32 on every call; here it is built once per weight version and kept in bf16).
+__global__ void dequant_w4_bf16_kernel(const uint32_t* __restrict__ wq, const __nv_bfloat16* __restrict__ scale,
+                                       const uint8_t* __restrict__ zp, uint4* __restrict__ W, long long words, int K,
+                                       int group) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one 32-bit word = 8 consecutive k
+  if (i >= words) return;
+  const long long e0 = i * 8;
+  const long long n = e0 / K;
+  const int k = (int)(e0 - n * K);
+  const long long gi = n * (K / group) + k / group;   // group % 8 == 0: the 8 weights share a group
+  const float s = __bfloat162float(scale[gi]);
+  const int z = zp[gi];
+  const uint32_t w = wq[i];
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float a = (float)((int)((w >> (8 * j)) & 0xF) - z) * s;
+    const float b = (float)((int)((w >> (8 * j + 4)) & 0xF) - z) * s;
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    o[j] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  W[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+int dequant_w4_bf16(const void* wq, const void* scale, const void* zp, void* W, long long N, int K, int group,
+                    cudaStream_t s) {
+  const long long words = N * K / 8;
+  if (words == 0) return B200Q_OK;
+  dequant_w4_bf16_kernel<<<(unsigned)((words + 255) / 256), 256, 0, s>>>(
+      static_cast<const uint32_t*>(wq), static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp),
+      static_cast<uint4*>(W), words, K, group);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+// Prefill: y = x * W^T on the bf16 tensor cores (tcgen05 kind::f16, fp32 accumulation in TMEM).
+int a16_prefill_gemm(const void* x, const void* W16, const float* bias, void* y, long long M, int N, int K, int* status,
+                     cudaStream_t s) {
+  IGemmProblem p{};
+  p.kind = IGEMM_KIND_BF16;
+  p.a = x;
+  p.b = W16;
+  p.a_pitch = p.b_pitch = 2LL * K;
+  p.rows = (int)M;
+  p.n = N;
+  p.k_per_tap = 2 * K;
+  p.taps_h = p.taps_w = 1;
+  p.out_mode = IGEMM_OUT_ROWMAJOR;
+  p.ldc = N;
+  p.out = y;
+  p.bias_f32 = bias;
+  Epilogue e{};
+  return igemm_i8_tcgen05_launch(p, e, status, s);
+}
+
 int validate(const b200q_a16matmul_desc& d) {
   if (d.M < 0 || d.K < 1 || d.N < 1 || d.M > 0x7fffffffLL || d.K > 0x7fffffffLL || d.N > 0x7fffffffLL)
     return set_error(B200Q_ERR_INVALID, "a16matmul: bad shape");
@@ -46,8 +103,18 @@ int validate(const b200q_a16matmul_desc& d) {
 
 // Decode shapes go to the GEMV kernel; larger M is processed in slices of 8 tokens.
 int a16_dispatch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
-                 long long M, int N, int K, int group, int* status, cudaStream_t s) {
+                 long long M, int N, int K, int group, int* status, cudaStream_t s, DevBuf* w16 = nullptr,
+                 bool* w16_ready = nullptr) {
   const char* why = nullptr;
+  if (M > 8 && w16 && K % 8 == 0 && group % 8 == 0 && M <= 0x7fffffffLL) {
+    // prefill: dequantise once (kept for the life of the handle / weight version), then a bf16 GEMM
+    if (!*w16_ready) {
+      B200Q_TRY(w16->ensure((size_t)N * K * 2));
+      B200Q_TRY(dequant_w4_bf16(wq, scale, zp, w16->p, N, K, group, s));
+      *w16_ready = true;
+    }
+    return a16_prefill_gemm(x, w16->p, bias, y, M, N, K, status, s);
+  }
   if (!a16_w4_gemv_supported(1, N, K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: %s", why);
   for (long long m0 = 0; m0 < M; m0 += 8) {
     const int mm = (int)((M - m0) < 8 ? (M - m0) : 8);
@@ -58,7 +125,12 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
 }
 
 struct A16Handle {
-  DevBuf stage, x16, wq, scale, zp, bias, y16, y32, status;
+  DevBuf stage, x16, wq, scale, zp, bias, y16, y32, status, w16;
+  bool w16_ready = false;
+  // device face: the caller's tensors (not owned)
+  const void *d_wq = nullptr, *d_scale = nullptr, *d_zp = nullptr;
+  const float* d_bias = nullptr;
+  int N = 0, K = 0, group = 0;
   bool weights_ready = false;
   int weight_version = -1;
   const float* weight_ptr = nullptr;
@@ -118,6 +190,7 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
       if ((rc = f32_to_q8(h->stage.as<float>(), h->zp.p, (long long)q_elems, s))) break;
       if (bias_f && (rc = h->bias.upload(bias_f, (size_t)d.N * 4, s))) break;
       h->weights_ready = true;
+      h->w16_ready = false;
       h->weight_version = d.weight_version;
       h->weight_ptr = inputs[1];
     }
@@ -132,7 +205,7 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
     if (cudaMemcpyAsync(h->stage.p, inputs[0], x_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D input", __FILE__, __LINE__); break; }
     if ((rc = f32_to_bf16(h->stage.as<float>(), h->x16.p, (long long)x_elems, s))) break;
     if ((rc = a16_dispatch(h->x16.p, h->wq.p, h->scale.p, h->zp.p, bias_f ? h->bias.as<float>() : nullptr, h->y16.p,
-                           d.M, (int)d.N, (int)d.K, d.q_group_size, h->status.as<int>(), s))) break;
+                           d.M, (int)d.N, (int)d.K, d.q_group_size, h->status.as<int>(), s, &h->w16, &h->w16_ready))) break;
     if ((rc = bf16_to_f32(h->y16.p, h->y32.as<float>(), (long long)y_elems, s))) break;
     if (cudaMemcpyAsync(outputs[0], h->y32.p, y_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__); break; }
     int hstat = 0;
@@ -153,5 +226,57 @@ int b200q_a16_w4_dev(const void* x_bf16, const void* wq, const void* scale_bf16,
   return a16_dispatch(x_bf16, wq, scale_bf16, zp_u8, bias_f32, y_bf16, M, (int)N, (int)K, group, status,
                       static_cast<cudaStream_t>(stream));
 }
+
+}  // extern "C"
+
+extern "C" {
+
+int b200q_a16_dev_create(const void* wq, const void* scale_bf16, const void* zp_u8, const float* bias_f32, int64_t N,
+                         int64_t K, int32_t group, void** handle) {
+  if (!wq || !scale_bf16 || !zp_u8 || !handle) return set_error(B200Q_ERR_INVALID, "a16_dev_create: null argument");
+  if (N < 1 || K < 1 || group < 1 || N > 0x7fffffffLL || K > 0x7fffffffLL) return set_error(B200Q_ERR_INVALID, "a16_dev_create: bad shape");
+  const char* why = nullptr;
+  if (!a16_w4_gemv_supported(1, (int)N, (int)K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16_dev_create: %s", why);
+  auto* h = new (std::nothrow) A16Handle();
+  if (!h) return set_error(B200Q_ERR_NOMEM, "a16_dev_create: out of host memory");
+  h->d_wq = wq;
+  h->d_scale = scale_bf16;
+  h->d_zp = zp_u8;
+  h->d_bias = bias_f32;
+  h->N = (int)N;
+  h->K = (int)K;
+  h->group = group;
+  int rc = h->status.ensure(4);
+  if (rc == B200Q_OK && cudaMemset(h->status.p, 0, 4) != cudaSuccess) rc = cuda_error(cudaGetLastError(), "memset", __FILE__, __LINE__);
+  if (rc != B200Q_OK) {
+    delete h;
+    return rc;
+  }
+  *handle = h;
+  return B200Q_OK;
+}
+
+int b200q_a16_dev_run(void* handle, const void* x_bf16, void* y_bf16, int64_t M, void* stream) {
+  if (!handle || !x_bf16 || !y_bf16 || M < 0) return set_error(B200Q_ERR_INVALID, "a16_dev_run: bad argument");
+  A16Handle* h = static_cast<A16Handle*>(handle);
+  return a16_dispatch(x_bf16, h->d_wq, h->d_scale, h->d_zp, h->d_bias, y_bf16, M, h->N, h->K, h->group,
+                      h->status.as<int>(), static_cast<cudaStream_t>(stream), &h->w16, &h->w16_ready);
+}
+
+int b200q_a16_dev_status(void* handle, void* stream) {
+  if (!handle) return set_error(B200Q_ERR_INVALID, "a16_dev_status: null handle");
+  A16Handle* h = static_cast<A16Handle*>(handle);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int hstat = 0;
+  CUDA_TRY(cudaMemcpyAsync(&hstat, h->status.p, 4, cudaMemcpyDeviceToHost, s));
+  CUDA_TRY(cudaStreamSynchronize(s));
+  if (hstat != 0) {
+    cudaMemsetAsync(h->status.p, 0, 4, s);
+    return set_error(B200Q_ERR_TIMEOUT, "a16: a bounded wait inside the kernel ran out (wait site %d)", hstat);
+  }
+  return B200Q_OK;
+}
+
+void b200q_a16_dev_destroy(void** handle) { b200q_a16matmul_deinit(handle); }
 
 }  // extern "C"

@@ -8,6 +8,7 @@
 namespace b200q {
 
 enum { IGEMM_OUT_ROWMAJOR = 0, IGEMM_OUT_NCHW = 1, IGEMM_OUT_NHWC_BORDERED = 2 };
+enum { IGEMM_KIND_I8 = 0, IGEMM_KIND_BF16 = 1 };  // operand type; BF16: fp32 accumulate, bf16 row-major output
 
 // What the host asks for.  A is [rows][k_per_tap] (row pitch a_pitch bytes): the GEMM's left matrix, or the
 // pixels of a zero-bordered NHWC image flattened to rows.  B is [n][taps_h*taps_w*k_per_tap] (K-major weights).
@@ -25,6 +26,8 @@ struct IGemmProblem {
   int out_mode;                           // IGEMM_OUT_*
   long long ldc;                          // elements per output row (ROWMAJOR / NHWC_BORDERED)
   void* out;
+  int kind;                               // IGEMM_KIND_*; for BF16 k_per_tap and the pitches are in BYTES (2 per element)
+  const float* bias_f32;                  // BF16 kind: optional per-column bias
 };
 
 // Kernel argument block (device view of the same problem).
@@ -37,6 +40,8 @@ struct IGemmArgs {
   int* status;
   uint32_t idesc;
   int num_m_tiles, num_n_tiles;
+  const float* bias_f32;
+  int bf16;
 };
 
 int igemm_i8_tcgen05_supported(const IGemmProblem& p, const char** why);

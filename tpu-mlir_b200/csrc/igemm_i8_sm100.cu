@@ -15,6 +15,7 @@
 // This replaces tpu::MatMulOp / tpu::Conv2DOp inference (lib/Dialect/Tpu/Interfaces/Common/MatMul.cpp:599-728,
 // Conv2D.cpp:264-341) and the oneDNN primitives behind them (lib/Support/Dnnl/MatMul.cpp, Conv.cpp).
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include "igemm.h"
@@ -29,7 +30,8 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;  // bytes == int8 elements: one 128-byte swizzle span
 constexpr int UMMA_K = 32;    // K of one tcgen05.mma for 8-bit operands
-constexpr int EPI_COLS_PER_WARP = 64;  // each epilogue warp owns 32 TMEM lanes x 64 columns of the tile
+constexpr int EPI_COLS_PER_WARP = 64;
+constexpr int KIND_BF16_TAG = -2;  // value of the DIALECT template argument that selects bf16 operands / output  // each epilogue warp owns 32 TMEM lanes x 64 columns of the tile
 constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate tile time
 
 template <int BLOCK_N, int STAGES>
@@ -194,8 +196,12 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
           for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
             // advancing K inside the swizzle span = advancing the start address (16-byte units)
-            ptx::umma_i8(d_tmem, a_desc + (uint64_t)(k * (UMMA_K / 16)), b_desc + (uint64_t)(k * (UMMA_K / 16)),
-                         args.idesc, (kb | k) != 0 ? 1u : 0u);
+            if (DIALECT == KIND_BF16_TAG)
+              ptx::umma_f16(d_tmem, a_desc + (uint64_t)(k * (UMMA_K / 16)), b_desc + (uint64_t)(k * (UMMA_K / 16)),
+                            args.idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              ptx::umma_i8(d_tmem, a_desc + (uint64_t)(k * (UMMA_K / 16)), b_desc + (uint64_t)(k * (UMMA_K / 16)),
+                           args.idesc, (kb | k) != 0 ? 1u : 0u);
           }
           ptx::umma_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
           if (++stage == STAGES) {
@@ -246,6 +252,10 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         for (int c = etid; c < BLOCK_N; c += EPI_THREADS) {
           const int n = n0 + c;
           const bool in = n < args.n;
+          if (DIALECT == KIND_BF16_TAG) {
+            chan[c] = make_int4((in && args.bias_f32) ? __float_as_int(args.bias_f32[n]) : 0, 0, 0, 0);
+            continue;
+          }
           const int32_t bias = (in && e.bias) ? e.bias[n] : 0;
           const int32_t m = (in && e.multiplier) ? e.multiplier[e.per_channel ? n : 0] : 1;
           const int32_t sh = (in && e.shift) ? e.shift[e.per_channel ? n : 0] : 0;
@@ -303,6 +313,30 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           ptx::mbar_arrive(tmem_empty_bar(acc));
         }
         if (n0 + cbase >= args.n) continue;
+        if (DIALECT == KIND_BF16_TAG) {
+          // fp32 accumulator (+ bias) -> bf16, row-major [rows, N]
+          if (row_valid) {
+            const int nc = min(CH, args.n - (n0 + cbase));
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(args.out) + out_base + n0 + cbase;
+            uint32_t pk[CH / 2];
+#pragma unroll
+            for (int j = 0; j < CH / 2; ++j) {
+              const float v0 = __uint_as_float(r[2 * j]) + __int_as_float(chan[cbase + 2 * j].x);
+              const float v1 = __uint_as_float(r[2 * j + 1]) + __int_as_float(chan[cbase + 2 * j + 1].x);
+              const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+              pk[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            if (nc == CH && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+              reinterpret_cast<uint4*>(o)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              reinterpret_cast<uint4*>(o)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < CH; ++j)
+                if (j < nc) reinterpret_cast<uint16_t*>(o)[j] = (uint16_t)(pk[j >> 1] >> ((j & 1) * 16));
+            }
+          }
+          continue;
+        }
         int32_t q[CH];
         if (kFastCompiled && kFastDialect && chunk_slow[cbase >> 5] == 0) {
 #pragma unroll
@@ -451,6 +485,7 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& ar
 template <int BLOCK_N, int STAGES>
 int launch_dialect(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& a, int grid, cudaStream_t s) {
   const int d = a.epi.dialect, r = a.epi.round_mode;
+  if (a.bf16) return launch_one<BLOCK_N, STAGES, KIND_BF16_TAG, -1>(ta, tb, a, grid, s);
   if (d == B200Q_RQ_MULTIPLIER_SHIFT && r == B200Q_ROUND_HALF_UP)
     return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP>(ta, tb, a, grid, s);
   if (d == B200Q_RQ_QDM && r == B200Q_ROUND_HALF_AWAY_FROM_ZERO)
@@ -498,7 +533,10 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   a.out = p.out;
   a.epi = epi;
   a.status = status;
-  a.idesc = ptx::make_idesc(2u, p.a_unsigned ? 0u : 1u, p.b_unsigned ? 0u : 1u, BLOCK_M, (uint32_t)block_n);
+  a.bf16 = p.kind == IGEMM_KIND_BF16;
+  a.bias_f32 = p.bias_f32;
+  a.idesc = a.bf16 ? ptx::make_idesc(1u, 1u, 1u, BLOCK_M, (uint32_t)block_n)  // f32 accumulate, bf16 x bf16
+                   : ptx::make_idesc(2u, p.a_unsigned ? 0u : 1u, p.b_unsigned ? 0u : 1u, BLOCK_M, (uint32_t)block_n);
   a.num_m_tiles = (p.rows + BLOCK_M - 1) / BLOCK_M;
   a.num_n_tiles = (p.n + block_n - 1) / block_n;
 
