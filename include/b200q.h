@@ -192,6 +192,47 @@ void b200q_conv2d_dev_destroy(void **handle);
 int b200q_conv2d_dev_set_profiling(void *handle, int enable);
 int b200q_conv2d_dev_last_times(void *handle, float *layout_ms, float *kernel_ms);
 
+/* ------------------------------------------------------------------ tpu.RequantIntAxis / tpu.RequantInt
+ * Operator face of tpu::RequantIntAxisOp::inference (lib/Dialect/Tpu/Interfaces/Common/RequantIntAxis.cpp:17-123,
+ * BM1684X quant layout {multiplier, shift, zero point} x C in operand 1, float-stored) and, with per_axis = 0,
+ * of tpu::RequantIntOp::inference (RequantInt.cpp:17-71: multiplier / rshift attributes, output zero point).
+ * The tensor is viewed [outer][channels][inner]; with fuse_rq_axis the channel is the last axis (inner = 1). */
+typedef struct {
+  int64_t outer, channels, inner;
+  int32_t per_axis;       /* 1: RequantIntAxis (quant operand), 0: RequantInt (attributes below) */
+  int32_t quant_mode;     /* TFLite / TFLite_LShift / MultiplierShift */
+  int32_t round_mode;     /* b200q_round_mode (the op's round_mode attribute) */
+  int32_t fuse_rq_axis;
+  int32_t in_zp;          /* input zero point (MultiplierShift only) */
+  int32_t out_dtype;
+  int64_t multiplier, rshift; /* RequantInt attributes */
+  int32_t out_zp;             /* RequantInt: zero point of the output type */
+} b200q_requant_desc;
+int b200q_requant_int_axis_inference(const b200q_requant_desc *desc, float *const *inputs, int n_inputs,
+                                     float *const *outputs, int n_outputs);
+
+/* ------------------------------------------------------------------ glue ops of an INT8 graph, device face
+ * Native NCHW device tensors, asynchronous on `stream`. */
+/* x int32 [outer][C][inner]; per channel multiplier / shift (sign convention of `dialect`) / zero point. */
+int b200q_requant_int_axis_dev(const int32_t *x, int64_t outer, int64_t C, int64_t inner, const int32_t *multiplier,
+                               const int32_t *shift, const int32_t *zero_point, int32_t dialect, int32_t round_mode,
+                               int32_t in_zp, int32_t out_dtype, void *out, void *stream);
+/* tpu.Add, symmetric int8 (lib/Dialect/Tpu/Interfaces/Common/Add.cpp:177-207):
+ * out = saturate(relu(RSR(a*m0, s0, half-up) + RSR(b*m1, s1, half-up))). */
+int b200q_add_i8_dev(const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t count, int32_t m0,
+                     int32_t s0, int32_t m1, int32_t s1, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
+/* tpu.Pool2D int8 (Pool2D.cpp:160-192): max, or average as RSR(window_sum * multiplier, rshift, half-up);
+ * x is [nc][ih][iw] (N and C merged). */
+int b200q_pool2d_i8_dev(const void *x, int32_t dtype, int64_t nc, int32_t ih, int32_t iw, int32_t kh, int32_t kw,
+                        int32_t sh, int32_t sw, int32_t pht, int32_t phb, int32_t pwl, int32_t pwr, int32_t is_avg,
+                        int32_t multiplier, int32_t rshift, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
+/* tpu.Cast f32 <-> int8/uint8 (Cast.cpp:75-116, lib/Support/CastUtils.cpp:15-47):
+ * q = saturate(to_int(round(x * (float)(1/scale)) + zp, round_mode));  x = (float)scale * (q - zp). */
+int b200q_cast_f32_to_q8_dev(const float *x, int64_t count, double scale, int32_t zero_point, int32_t round_mode,
+                             int32_t out_dtype, void *out, void *stream);
+int b200q_cast_q8_to_f32_dev(const void *x, int32_t dtype, int64_t count, double scale, int32_t zero_point, float *out,
+                             void *stream);
+
 /* ------------------------------------------------------------------ tpu.A16MatMul (w4 bf16)
  * Attributes of tpu.A16MatMul (TpuOps.td:495-530) for the static 4-bit path of
  * tpu::A16MatMulOp::inference (lib/Dialect/Tpu/Interfaces/Common/A16MatMul.cpp:171-208,:240-246):

@@ -1,0 +1,93 @@
+"""Glue ops of an INT8 graph (Add, Pool2D, Cast, RequantInt/RequantIntAxis) on the GPU, bit-exact vs the oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import tpu_mlir_b200._lib as L
+
+from gpu_util import dev, dt_of, empty_dev, ptr
+
+pytestmark = pytest.mark.gpu
+lib = L.lib
+
+
+@pytest.mark.parametrize("n", [1, 7, 4096, 100003])
+def test_add(n):
+    rng = np.random.default_rng(n)
+    a = rng.integers(0, 256, n, dtype=np.uint8)
+    b = rng.integers(-128, 128, n, dtype=np.int8)
+    for (m0, s0, m1, s1, relu, odt) in [(77, 6, 100, 7, True, L.DT_U8), (3, 0, 125, 9, False, L.DT_I8)]:
+        want = oracle.add_int8(a, b, m0, s0, m1, s1, do_relu=relu, out_dt=odt)
+        out = empty_dev((n,), odt)
+        a_d, b_d = dev(a), dev(b)          # keep the device tensors alive across the asynchronous call
+        L.check(lib().b200q_add_i8_dev(ptr(a_d), L.DT_U8, ptr(b_d), L.DT_I8, n, m0, s0, m1, s1, int(relu), odt, ptr(out), None))
+        assert np.array_equal(out.cpu().numpy(), want)
+
+
+def test_pool():
+    rng = np.random.default_rng(4)
+    x = rng.integers(0, 256, (3, 5, 17, 14), dtype=np.uint8)
+    xs = rng.integers(-128, 128, (2, 4, 7, 7), dtype=np.int8)
+    want = oracle.pool2d_int8(x, (3, 3), (2, 2), (1, 1, 1, 1), mode="max")
+    out = empty_dev(want.shape, L.DT_U8)
+    x_d, xs_d = dev(x), dev(xs)
+    L.check(lib().b200q_pool2d_i8_dev(ptr(x_d), L.DT_U8, 15, 17, 14, 3, 3, 2, 2, 1, 1, 1, 1, 0, 1, 0, 0, L.DT_U8, ptr(out), None))
+    assert np.array_equal(out.cpu().numpy(), want)
+    want = oracle.pool2d_int8(xs, (7, 7), (1, 1), (0, 0, 0, 0), mode="avg", multi=83, rshift=12, do_relu=True)
+    out = empty_dev(want.shape, L.DT_I8)
+    L.check(lib().b200q_pool2d_i8_dev(ptr(xs_d), L.DT_I8, 8, 7, 7, 7, 7, 1, 1, 0, 0, 0, 0, 1, 83, 12, 1, L.DT_I8, ptr(out), None))
+    assert np.array_equal(out.cpu().numpy(), want)
+
+
+def test_cast_both_ways():
+    rng = np.random.default_rng(6)
+    x = (rng.standard_normal(50001) * 3).astype(np.float32)
+    x[:6] = [0.5 * 0.0371, -0.5 * 0.0371, 1.5 * 0.0371, 1e9, -1e9, 0.0]
+    for scale, zp, odt in [(0.0371, 0, L.DT_I8), (4.1 / 255, 3, L.DT_U8)]:
+        want = oracle.cast_f32_to_q8(x, scale, zp, out_dt=odt)
+        out = empty_dev(x.shape, odt)
+        x_d = dev(x)
+        L.check(lib().b200q_cast_f32_to_q8_dev(ptr(x_d), x.size, scale, zp, L.ROUND_HALF_AWAY_FROM_ZERO, odt, ptr(out), None))
+        assert np.array_equal(out.cpu().numpy(), want)
+        back = torch.empty(x.shape, dtype=torch.float32, device="cuda")
+        L.check(lib().b200q_cast_q8_to_f32_dev(ptr(out), odt, x.size, scale, zp, ptr(back), None))
+        assert np.array_equal(back.cpu().numpy(), oracle.cast_q8_to_f32(want, scale, zp))
+
+
+@pytest.mark.parametrize("mode", ["tflite", "ms", "ms_fuse_axis"])
+def test_requant_int_axis_operator_face(mode):
+    rng = np.random.default_rng(9)
+    Cn = 24
+    x = rng.integers(-2**20, 2**20, (3, Cn, 5, 4) if mode != "ms_fuse_axis" else (3, 5, 4, Cn), dtype=np.int32)
+    if mode == "tflite":
+        quant = np.stack([rng.integers(2**30, 2**31, Cn), -rng.integers(4, 16, Cn), rng.integers(-5, 5, Cn)], axis=1)
+        qmode, rmode = oracle.QM_TFLITE, oracle.RM_HALF_AWAY
+    else:
+        quant = np.stack([rng.integers(1000, 30000, Cn), (-1 if mode == "ms" else 1) * rng.integers(12, 24, Cn), rng.integers(-5, 5, Cn)], axis=1)
+        qmode, rmode = oracle.QM_MULTIPLIER_SHIFT, oracle.RM_HALF_UP
+    quant_f = quant.astype(np.float32)                    # the operand as the interpreter stores it
+    seen = quant_f.astype(np.int64)
+    fuse = mode == "ms_fuse_axis"
+    want = oracle.requant_int_axis(x, seen, qmode=qmode, rmode=rmode, fuse_rq_axis=fuse, out_dt=oracle.DT_I8)
+    d = L.RequantDesc(outer=x.size // Cn if fuse else x.shape[0], channels=Cn, inner=1 if fuse else 20, per_axis=1,
+                      quant_mode=qmode, round_mode=rmode, fuse_rq_axis=int(fuse), in_zp=0, out_dtype=L.DT_I8)
+    out = np.zeros(x.shape, np.float32)
+    L.check(lib().b200q_requant_int_axis_inference(C.byref(d), L.float_pp([x.astype(np.float32), quant_f.reshape(-1)]), 2,
+                                                   L.float_pp([out]), 1))
+    assert np.array_equal(out, want.astype(np.float32))
+
+
+def test_requant_int_operator_face():
+    rng = np.random.default_rng(10)
+    x = rng.integers(-2**18, 2**18, (2, 6, 9), dtype=np.int32)
+    for qmode, rmode, multi, rshift in [(oracle.QM_TFLITE, oracle.RM_HALF_AWAY, 1518500250, 9),
+                                        (oracle.QM_MULTIPLIER_SHIFT, oracle.RM_HALF_UP, 12345, 20)]:
+        want = oracle.requant_int(x, multi, rshift, qmode=qmode, rmode=rmode, out_zp=-3, out_dt=oracle.DT_I8)
+        d = L.RequantDesc(outer=2, channels=6, inner=9, per_axis=0, quant_mode=qmode, round_mode=rmode, fuse_rq_axis=0, in_zp=0,
+                          out_dtype=L.DT_I8, multiplier=multi, rshift=rshift, out_zp=-3)
+        out = np.zeros(x.shape, np.float32)
+        L.check(lib().b200q_requant_int_axis_inference(C.byref(d), L.float_pp([x.astype(np.float32)]), 1, L.float_pp([out]), 1))
+        assert np.array_equal(out, want.astype(np.float32))

@@ -1,0 +1,57 @@
+"""Whole-network INT8 ResNet-50 (BASELINE config 3 at a small batch): executor vs the oracle, every tensor bit exact."""
+import numpy as np
+import pytest
+import torch
+
+import oracle_graph
+from tpu_mlir_b200 import resnet50, synth
+from tpu_mlir_b200.module import module
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lowered():
+    ops = resnet50.build_fp32(seed=3)
+    images = torch.from_numpy(synth.calibration_images(seed=4, count=8)).cuda()
+    table = resnet50.self_calibration_table(ops, images, batch=4)
+    graph, weights = resnet50.lower_int8(ops, table, batch=2)
+    return ops, table, graph, weights
+
+
+def test_int8_graph_matches_oracle_on_every_tensor(lowered):
+    ops, table, graph, weights = lowered
+    x = synth.calibration_images(seed=33, count=2)
+    m = module()
+    m.load(graph, weights)
+    seen = []
+    m.after_invoke(lambda name: seen.append(name))
+    m.set_tensor("input", x)
+    m.invoke()
+    assert seen == [op["name"] for op in graph["ops"]]
+    want = oracle_graph.run(graph, weights, {"input": x})
+    types = {}
+    for op in graph["ops"]:
+        name = op["name"]
+        got = m.get_tensor(name)
+        assert np.array_equal(got, want[name]), (name, op["type"])
+        types[graph["tensors"][name]["dtype"]] = types.get(graph["tensors"][name]["dtype"], 0) + 1
+    assert types.get("u8", 0) > 40 and types.get("i8", 0) > 10      # post-ReLU tensors are unsigned
+    logits = m.get_tensor("fc")
+    assert logits.shape == (2, 1000) and logits.dtype == np.int8 and len(np.unique(logits)) > 20
+    # the expressed (float) view of a quantized tensor
+    info = graph["tensors"]["fc"]
+    assert np.allclose(m.get_fp32_tensor("fc"), logits.astype(np.float32) * np.float32(info["scale"]))
+
+
+def test_int8_logits_track_the_fp32_network(lowered):
+    ops, table, graph, weights = lowered
+    x = synth.calibration_images(seed=34, count=2)
+    m = module()
+    m.load(graph, weights)
+    m.set_tensor("input", x)
+    m.invoke()
+    q = m.get_tensor("output")
+    f = resnet50.Fp32Forward(ops, torch.device("cuda"))(torch.from_numpy(x).cuda())["fc"].cpu().numpy()
+    cos = float((q * f).sum() / (np.linalg.norm(q) * np.linalg.norm(f)))
+    assert cos > 0.95, cos          # the reference's own int8-vs-fp32 acceptance level (test_onnx.py:624-640)

@@ -53,6 +53,12 @@ class Conv2DDesc(C.Structure):
                 ("weight_version", C.c_int32), ("algo", C.c_int32)]
 
 
+class RequantDesc(C.Structure):
+    _fields_ = [("outer", C.c_int64), ("channels", C.c_int64), ("inner", C.c_int64), ("per_axis", C.c_int32),
+                ("quant_mode", C.c_int32), ("round_mode", C.c_int32), ("fuse_rq_axis", C.c_int32), ("in_zp", C.c_int32),
+                ("out_dtype", C.c_int32), ("multiplier", C.c_int64), ("rshift", C.c_int64), ("out_zp", C.c_int32)]
+
+
 class A16MatMulDesc(C.Structure):
     _fields_ = [("M", C.c_int64), ("K", C.c_int64), ("N", C.c_int64), ("weight_bits", C.c_int32),
                 ("q_group_size", C.c_int32), ("w_transpose", C.c_int32), ("with_bias", C.c_int32),
@@ -79,6 +85,17 @@ SIGNATURES = {
     "b200q_conv2d_dev_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200q_conv2d_dev_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200q_conv2d_dev_destroy": (None, [_VPP]),
+    "b200q_requant_int_axis_inference": (C.c_int, [C.POINTER(RequantDesc), _FLOATPP, C.c_int, _FLOATPP, C.c_int]),
+    "b200q_requant_int_axis_dev": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
+                                             C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                             C.c_void_p]),
+    "b200q_add_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 6 +
+                         [C.c_void_p, C.c_void_p]),
+    "b200q_pool2d_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 15 + [C.c_void_p, C.c_void_p]),
+    "b200q_cast_f32_to_q8_dev": (C.c_int, [C.c_void_p, C.c_int64, C.c_double, C.c_int32, C.c_int32, C.c_int32,
+                                           C.c_void_p, C.c_void_p]),
+    "b200q_cast_q8_to_f32_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_double, C.c_int32, C.c_void_p,
+                                           C.c_void_p]),
     "b200q_a16matmul_init": (C.c_int, [C.POINTER(A16MatMulDesc), _VPP]),
     "b200q_a16matmul_inference": (C.c_int, [C.POINTER(A16MatMulDesc), _FLOATPP, C.c_int, _FLOATPP, C.c_int, _VPP]),
     "b200q_a16matmul_deinit": (None, [_VPP]),
@@ -145,4 +162,5 @@ def float_pp(arrays):
     for i, a in enumerate(arrays):
         if a is not None:
             arr[i] = a.ctypes.data_as(C.POINTER(C.c_float))
+    arr._buffers = list(arrays)     # the pointer table keeps its buffers alive
     return arr

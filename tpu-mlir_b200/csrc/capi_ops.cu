@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "devbuf.h"
+#include "eltwise.h"
 #include "igemm.h"
 #include "internal.h"
 #include "layout.h"
@@ -229,10 +230,12 @@ int resolve_conv(const b200q_conv2d_desc& d, ResolvedRequant* r) {  // Conv2D.cp
 struct ConvHandle {
   b200q_conv2d_desc d{};
   ConvGeometry g{};
-  bool use_tc = false;
+  bool use_tc = false;      // tensor cores on the zero-bordered image directly (stride 1, IC fits the K blocking)
+  bool use_im2col = false;  // tensor cores on an im2col matrix (strides, dilation, any IC)
+  int kpad = 0;             // im2col row length (KH*KW*IC rounded up to 16)
   int bh = 0, bw = 0, Hp = 0, Wp = 0;
   Epilogue epi{};
-  DevBuf w_oihw, w_packed, bias, mult, shift, x_bordered, status;
+  DevBuf w_oihw, w_packed, bias, mult, shift, x_bordered, a_cols, status;
   // operator-face staging
   DevBuf x_f32, x_q8, y_q, y_f32, w_f32, bias_f32;
   // optional per-kernel timing of the device face
@@ -291,14 +294,30 @@ int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int
   h->Wp = (int)d.iw + 2 * h->bw;
   const long long rows = (long long)d.n * h->Hp * h->Wp;
   h->use_tc = geometry_ok && k_ok && rows < 0x7fffffffLL && d.algo != 2;
-  if (d.algo == 1 && !h->use_tc)
-    return set_error(B200Q_ERR_UNSUPPORTED, "conv2d: tensor-core path needs stride 1, dilation 1, groups 1, zero pad value and IC %% %d == 0", d.kh * d.kw == 1 ? 16 : 128);
+  const long long out_rows = (long long)d.n * oh * ow;
+  h->kpad = (int)((d.kh * d.kw * d.ic + 15) / 16 * 16);
+  h->use_im2col = !h->use_tc && d.groups == 1 && d.pad_value == 0 && d.algo != 2 && out_rows < 0x7fffffffLL &&
+                  (long long)d.kh * d.kw * d.ic < 0x7fffffffLL;
+  if (d.algo == 1 && !h->use_tc && !h->use_im2col)
+    return set_error(B200Q_ERR_UNSUPPORTED, "conv2d: the tensor-core paths need groups = 1 and a zero padding value");
   const size_t wbytes = (size_t)d.oc * (d.ic / d.groups) * d.kh * d.kw;
   if (h->use_tc) {
     B200Q_TRY(h->w_packed.ensure(wbytes));
     B200Q_TRY(repack_weight_oihw(w_dev, w_is_f32, h->w_packed.p, (int)d.oc, (int)d.ic, (int)d.kh, (int)d.kw, s));
     B200Q_TRY(h->x_bordered.ensure((size_t)rows * d.ic));
     CUDA_TRY(cudaMemsetAsync(h->x_bordered.p, 0, (size_t)rows * d.ic, s));  // the border stays zero for every run
+  } else if (h->use_im2col) {
+    const size_t kk = (size_t)d.kh * d.kw * d.ic;
+    // weights [OC][kk] -> pitch kpad (zero padded)
+    B200Q_TRY(h->w_oihw.ensure(wbytes));
+    B200Q_TRY(repack_weight_oihw(w_dev, w_is_f32, h->w_oihw.p, (int)d.oc, (int)d.ic, (int)d.kh, (int)d.kw, s));
+    B200Q_TRY(h->w_packed.ensure((size_t)d.oc * h->kpad));
+    CUDA_TRY(cudaMemsetAsync(h->w_packed.p, 0, (size_t)d.oc * h->kpad, s));
+    CUDA_TRY(cudaMemcpy2DAsync(h->w_packed.p, (size_t)h->kpad, h->w_oihw.p, kk, kk, (size_t)d.oc, cudaMemcpyDeviceToDevice, s));
+    B200Q_TRY(h->x_bordered.ensure((size_t)rows * d.ic));
+    CUDA_TRY(cudaMemsetAsync(h->x_bordered.p, 0, (size_t)rows * d.ic, s));
+    B200Q_TRY(h->a_cols.ensure((size_t)out_rows * h->kpad));
+    CUDA_TRY(cudaMemsetAsync(h->a_cols.p, 0, (size_t)out_rows * h->kpad, s));  // the pad columns stay zero
   } else {
     B200Q_TRY(h->w_oihw.ensure(wbytes));
     if (w_is_f32) B200Q_TRY(f32_to_q8((const float*)w_dev, h->w_oihw.p, (long long)wbytes, s));
@@ -339,6 +358,32 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.out_w = h->g.ow;
     p.out_mode = IGEMM_OUT_NCHW;
     p.ldc = 0;
+    p.out = y;
+    B200Q_TRY(igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s));
+    if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[2], s));
+    return B200Q_OK;
+  }
+  if (h->use_im2col) {
+    if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[0], s));
+    B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
+    B200Q_TRY(im2col_nhwc_launch(h->x_bordered.p, h->a_cols.p, d.n, (int)d.ic, h->Hp, h->Wp, h->g.oh, h->g.ow, (int)d.kh,
+                                 (int)d.kw, (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, h->bh - (int)d.pht,
+                                 h->bw - (int)d.pwl, h->kpad, s));
+    if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[1], s));
+    IGemmProblem p{};
+    p.a = h->a_cols.p;
+    p.b = h->w_packed.p;
+    p.a_unsigned = d.input_dtype == B200Q_DT_U8;
+    p.a_pitch = p.b_pitch = h->kpad;
+    p.rows = (int)((long long)d.n * h->g.oh * h->g.ow);
+    p.n = (int)d.oc;
+    p.k_per_tap = h->kpad;
+    p.taps_h = p.taps_w = 1;
+    p.row_pitch = h->g.ow;
+    p.img_rows = h->g.oh * h->g.ow;
+    p.out_h = h->g.oh;
+    p.out_w = h->g.ow;
+    p.out_mode = IGEMM_OUT_NCHW;
     p.out = y;
     B200Q_TRY(igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s));
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[2], s));
@@ -567,10 +612,103 @@ int b200q_conv2d_dev_set_profiling(void* handle, int enable) {
 int b200q_conv2d_dev_last_times(void* handle, float* layout_ms, float* kernel_ms) {
   if (!handle || !layout_ms || !kernel_ms) return set_error(B200Q_ERR_INVALID, "conv2d_dev_last_times: null argument");
   ConvHandle* h = static_cast<ConvHandle*>(handle);
-  if (!h->profiling || !h->use_tc) return set_error(B200Q_ERR_INVALID, "conv2d_dev_last_times: profiling is off or the op runs on the CUDA-core kernel");
+  if (!h->profiling || !(h->use_tc || h->use_im2col)) return set_error(B200Q_ERR_INVALID, "conv2d_dev_last_times: profiling is off or the op runs on the CUDA-core kernel");
   CUDA_TRY(cudaEventSynchronize(h->ev[2]));
   CUDA_TRY(cudaEventElapsedTime(layout_ms, h->ev[0], h->ev[1]));
   CUDA_TRY(cudaEventElapsedTime(kernel_ms, h->ev[1], h->ev[2]));
+  return B200Q_OK;
+}
+
+
+// ------------------------------------------------------------------------------------------------ glue ops (device face)
+int b200q_requant_int_axis_dev(const int32_t* x, int64_t outer, int64_t C, int64_t inner, const int32_t* multiplier,
+                               const int32_t* shift, const int32_t* zero_point, int32_t dialect, int32_t round_mode,
+                               int32_t in_zp, int32_t out_dtype, void* out, void* stream) {
+  if (!x || !out || outer < 0 || C < 1 || inner < 1 || C > 0x7fffffffLL) return set_error(B200Q_ERR_INVALID, "requant_int_axis_dev: bad argument");
+  Epilogue e{};
+  e.dialect = dialect;
+  e.round_mode = round_mode;
+  e.out_dtype = out_dtype;
+  return requant_axis_launch(x, outer, (int)C, inner, multiplier, shift, zero_point, 1, in_zp, e, out, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_add_i8_dev(const void* a, int32_t a_dtype, const void* b, int32_t b_dtype, int64_t count, int32_t m0, int32_t s0,
+                     int32_t m1, int32_t s1, int32_t do_relu, int32_t out_dtype, void* out, void* stream) {
+  if (!a || !b || !out || count < 0) return set_error(B200Q_ERR_INVALID, "add_i8_dev: bad argument");
+  return add_i8_launch(a, a_dtype, b, b_dtype, count, m0, s0, m1, s1, do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_pool2d_i8_dev(const void* x, int32_t dtype, int64_t nc, int32_t ih, int32_t iw, int32_t kh, int32_t kw, int32_t sh,
+                        int32_t sw, int32_t pht, int32_t phb, int32_t pwl, int32_t pwr, int32_t is_avg, int32_t multiplier,
+                        int32_t rshift, int32_t do_relu, int32_t out_dtype, void* out, void* stream) {
+  if (!x || !out || nc < 0 || nc > 0x7fffffffLL || ih < 1 || iw < 1 || kh < 1 || kw < 1 || sh < 1 || sw < 1)
+    return set_error(B200Q_ERR_INVALID, "pool2d_i8_dev: bad argument");
+  return pool2d_i8_launch(x, dtype, (int)nc, ih, iw, kh, kw, sh, sw, pht, phb, pwl, pwr, is_avg ? 1 : 0, multiplier, rshift,
+                          do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_cast_f32_to_q8_dev(const float* x, int64_t count, double scale, int32_t zero_point, int32_t round_mode,
+                             int32_t out_dtype, void* out, void* stream) {
+  if (!x || !out || count < 0 || !(scale > 0)) return set_error(B200Q_ERR_INVALID, "cast_f32_to_q8_dev: bad argument");
+  return cast_f32_q8_launch(x, count, scale, zero_point, round_mode, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_cast_q8_to_f32_dev(const void* x, int32_t dtype, int64_t count, double scale, int32_t zero_point, float* out,
+                             void* stream) {
+  if (!x || !out || count < 0) return set_error(B200Q_ERR_INVALID, "cast_q8_to_f32_dev: bad argument");
+  return cast_q8_f32_launch(x, dtype, count, scale, zero_point, out, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------------------------------------------ RequantInt(Axis), operator face
+// Stateless: uploads, runs, downloads (these ops carry no weights worth keeping resident).
+int b200q_requant_int_axis_inference(const b200q_requant_desc* desc, float* const* inputs, int n_inputs,
+                                     float* const* outputs, int n_outputs) {
+  if (!desc || !inputs || !outputs || n_inputs < 1 || n_outputs < 1 || !inputs[0] || !outputs[0])
+    return set_error(B200Q_ERR_INVALID, "requant_int_axis_inference: null argument");
+  const b200q_requant_desc& d = *desc;
+  if (d.outer < 0 || d.channels < 1 || d.inner < 1) return set_error(B200Q_ERR_INVALID, "requant: bad shape");
+  const long long total = d.outer * d.channels * d.inner;
+  const int C = (int)d.channels;
+  std::vector<int32_t> m((size_t)C), sh((size_t)C), zp((size_t)C);
+  int dialect, rmode = d.round_mode;
+  const bool tf = d.quant_mode == B200Q_QM_TFLITE || d.quant_mode == B200Q_QM_TFLITE_LSHIFT;
+  if (!tf && d.quant_mode != B200Q_QM_MULTIPLIER_SHIFT) return set_error(B200Q_ERR_UNSUPPORTED, "requant: quant_mode %d does nothing in the reference", d.quant_mode);
+  dialect = tf ? B200Q_RQ_QDM : B200Q_RQ_MULTIPLIER_SHIFT;
+  if (d.per_axis) {
+    if (n_inputs < 2 || !inputs[1]) return set_error(B200Q_ERR_INVALID, "requant_int_axis: quant operand missing");
+    for (int c = 0; c < C; ++c) {  // BM1684X layout {multiplier, shift, zero point} read back from floats (RequantIntAxis.cpp:45-48)
+      const long long mm = (long long)inputs[1][c * 3], ss = (long long)inputs[1][c * 3 + 1], zz = (long long)inputs[1][c * 3 + 2];
+      if (mm > 2147483647ll || mm < -2147483648ll) return set_error(B200Q_ERR_UNSUPPORTED, "requant: multiplier does not fit int32");
+      m[(size_t)c] = (int32_t)mm;
+      zp[(size_t)c] = (int32_t)zz;
+      // TFLite: MultiplyByQuantizedMultiplier(x, m, shift); MultiplierShift: rshift = shift word when fuse_rq_axis, else -shift
+      sh[(size_t)c] = tf ? (int32_t)ss : (d.fuse_rq_axis ? (int32_t)ss : (int32_t)(-ss));
+    }
+  } else {  // tpu.RequantInt: one multiplier / rshift attribute (RequantInt.cpp:33-36)
+    for (int c = 0; c < C; ++c) {
+      m[(size_t)c] = (int32_t)d.multiplier;
+      zp[(size_t)c] = d.out_zp;
+      sh[(size_t)c] = tf ? (int32_t)(-d.rshift) : (int32_t)d.rshift;
+    }
+  }
+  cudaStream_t s = 0;
+  DevBuf xf, xi, q, of, dm, ds, dz;
+  B200Q_TRY(xf.upload(inputs[0], (size_t)total * 4, s));
+  B200Q_TRY(xi.ensure((size_t)total * 4));
+  B200Q_TRY(f32_to_i32(xf.as<float>(), xi.as<int32_t>(), total, s));
+  B200Q_TRY(dm.upload(m.data(), (size_t)C * 4, s));
+  B200Q_TRY(ds.upload(sh.data(), (size_t)C * 4, s));
+  B200Q_TRY(dz.upload(zp.data(), (size_t)C * 4, s));
+  B200Q_TRY(q.ensure((size_t)total * dtype_size(d.out_dtype)));
+  Epilogue e{};
+  e.dialect = dialect;
+  e.round_mode = rmode;
+  e.out_dtype = d.out_dtype;
+  B200Q_TRY(requant_axis_launch(xi.as<int32_t>(), d.outer, C, d.inner, dm.as<int32_t>(), ds.as<int32_t>(), dz.as<int32_t>(), 1,
+                                tf ? 0 : d.in_zp, e, q.p, s));
+  B200Q_TRY(q_to_f32(q.p, d.out_dtype, xf.as<float>(), total, s));
+  CUDA_TRY(cudaMemcpyAsync(outputs[0], xf.p, (size_t)total * 4, cudaMemcpyDeviceToHost, s));
+  CUDA_TRY(cudaStreamSynchronize(s));
   return B200Q_OK;
 }
 

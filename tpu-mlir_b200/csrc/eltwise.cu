@@ -1,0 +1,218 @@
+// Element-wise and pooling ops of an INT8 graph around the MatMul/Conv2D kernels, on native NCHW tensors:
+// stand-alone requantisation, residual Add, max / average pooling, float <-> int8 casts.  All HBM-bound.
+//
+// Reference semantics (paths inside the tpu-mlir tree):
+//   tpu.RequantIntAxis  lib/Dialect/Tpu/Interfaces/Common/RequantIntAxis.cpp:17-123
+//   tpu.RequantInt      lib/Dialect/Tpu/Interfaces/Common/RequantInt.cpp:17-71
+//   tpu.Add             lib/Dialect/Tpu/Interfaces/Common/Add.cpp:177-207 (symmetric int8, BM168x)
+//   tpu.Pool2D          lib/Dialect/Tpu/Interfaces/Common/Pool2D.cpp:160-192
+//   tpu.Cast            lib/Dialect/Tpu/Interfaces/Common/Cast.cpp:75-116, lib/Support/CastUtils.cpp:15-47
+#include "eltwise.h"
+#include "internal.h"
+#include "requant.cuh"
+
+namespace b200q {
+namespace {
+
+__device__ __forceinline__ int32_t ld_q(const void* p, long long i, int dt) {
+  switch (dt) {
+    case B200Q_DT_I8: return reinterpret_cast<const int8_t*>(p)[i];
+    case B200Q_DT_U8: return reinterpret_cast<const uint8_t*>(p)[i];
+    case B200Q_DT_I16: return reinterpret_cast<const int16_t*>(p)[i];
+    case B200Q_DT_U16: return reinterpret_cast<const uint16_t*>(p)[i];
+    default: return reinterpret_cast<const int32_t*>(p)[i];
+  }
+}
+__device__ __forceinline__ void st_q(void* p, long long i, int dt, int32_t v) {
+  switch (dt) {
+    case B200Q_DT_I8:
+    case B200Q_DT_U8: reinterpret_cast<uint8_t*>(p)[i] = (uint8_t)v; break;
+    case B200Q_DT_I16:
+    case B200Q_DT_U16: reinterpret_cast<uint16_t*>(p)[i] = (uint16_t)v; break;
+    default: reinterpret_cast<int32_t*>(p)[i] = v; break;
+  }
+}
+
+// x int32 viewed [outer][C][inner]; per channel {multiplier, shift, zero point}; e carries dialect / rounding /
+// output type (its own zero point and per-channel arrays are not used here).
+__global__ void requant_axis_kernel(const int32_t* __restrict__ x, long long total, int C, long long inner,
+                                    const int32_t* __restrict__ mult, const int32_t* __restrict__ shift,
+                                    const int32_t* __restrict__ zp, int per_channel, int in_zp, Epilogue e,
+                                    void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = per_channel ? (int)((i / inner) % C) : 0;
+  Epilogue le = e;
+  le.out_zp = zp ? zp[c] : e.out_zp;
+  st_q(out, i, e.out_dtype, requant_value<-1, -1>(x[i] - in_zp, mult ? mult[c] : 1, shift ? shift[c] : 0, le));
+}
+
+__global__ void add_i8_kernel(const void* __restrict__ a, int a_dt, const void* __restrict__ b, int b_dt, long long n,
+                              int m0, int s0, int m1, int s1, int do_relu, int out_dt, void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t l = rshift_round((int64_t)ld_q(a, i, a_dt) * m0, s0, B200Q_ROUND_HALF_UP);
+  const int64_t r = rshift_round((int64_t)ld_q(b, i, b_dt) * m1, s1, B200Q_ROUND_HALF_UP);
+  int64_t v = l + r;
+  if (do_relu && v < 0) v = 0;
+  st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
+}
+
+// 4 elements per thread for the common 8-bit case
+__global__ void add_i8x4_kernel(const uint32_t* __restrict__ a, int a_unsigned, const uint32_t* __restrict__ b,
+                                int b_unsigned, long long n4, int m0, int s0, int m1, int s1, int do_relu, int out_dt,
+                                uint32_t* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const uint32_t wa = a[i], wb = b[i];
+  uint32_t o = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int32_t xa = a_unsigned ? (int32_t)((wa >> (8 * j)) & 0xff) : (int32_t)(int8_t)(wa >> (8 * j));
+    const int32_t xb = b_unsigned ? (int32_t)((wb >> (8 * j)) & 0xff) : (int32_t)(int8_t)(wb >> (8 * j));
+    int64_t v = rshift_round((int64_t)xa * m0, s0, B200Q_ROUND_HALF_UP) + rshift_round((int64_t)xb * m1, s1, B200Q_ROUND_HALF_UP);
+    if (do_relu && v < 0) v = 0;
+    o |= ((uint32_t)clamp_dtype(v, out_dt) & 0xffu) << (8 * j);
+  }
+  out[i] = o;
+}
+
+__global__ void pool2d_i8_kernel(const void* __restrict__ x, int dt, int NC, int ih, int iw, int kh, int kw, int sh,
+                                 int sw, int pht, int pwl, int oh, int ow, int mode, int multi, int rshift, int do_relu,
+                                 int out_dt, void* __restrict__ out) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)NC * oh * ow;
+  if (idx >= total) return;
+  const int xo = (int)(idx % ow), yo = (int)((idx / ow) % oh);
+  const long long nc = idx / ((long long)ow * oh);
+  int64_t best = INT64_MIN, sum = 0;
+  for (int fy = 0; fy < kh; ++fy) {
+    const int iy = yo * sh - pht + fy;
+    if (iy < 0 || iy >= ih) continue;
+    for (int fx = 0; fx < kw; ++fx) {
+      const int ix = xo * sw - pwl + fx;
+      if (ix < 0 || ix >= iw) continue;
+      const int64_t v = ld_q(x, (nc * ih + iy) * iw + ix, dt);
+      best = v > best ? v : best;
+      sum += v;
+    }
+  }
+  int64_t v;
+  if (mode == 0) {
+    v = best;
+    if (do_relu && v < 0) v = 0;
+  } else {
+    v = rshift_round(sum * multi, rshift, B200Q_ROUND_HALF_UP);
+    if (do_relu && v < 0) v = 0;
+    v = clamp_dtype(v, out_dt);
+  }
+  st_q(out, idx, out_dt, (int32_t)v);
+}
+
+__global__ void cast_f32_q8_kernel(const float* __restrict__ x, long long n, float inv_scale, int zp, int rmode,
+                                   int out_dt, void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = __fadd_rn(roundf(__fmul_rn(x[i], inv_scale)), (float)zp);
+  st_q(out, i, out_dt, (int32_t)clamp_dtype(to_int_f32(v, rmode), out_dt));
+}
+
+__global__ void cast_q8_f32_kernel(const void* __restrict__ x, int dt, long long n, float scale, int zp,
+                                   float* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  out[i] = __fmul_rn(scale, __fsub_rn((float)ld_q(x, i, dt), (float)zp));
+}
+
+// NHWC (zero-bordered by `b` pixels) -> im2col rows [N*OH*OW][kpad] with k = (fy*KW + fx)*C + c
+__global__ void im2col_nhwc_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ a, int C, int Hp, int Wp, int OH,
+                                   int OW, int KH, int KW, int sh, int sw, int dh, int dw, int oy0, int ox0, int kpad,
+                                   long long total_units, int vec) {
+  // one unit = (row, tap, vec-byte piece of C); vec = 16 when C % 16 == 0, else 1 unit = (row, tap) with a byte loop
+  const long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= total_units) return;
+  const int pieces = vec == 16 ? C / 16 : 1;
+  const int piece = (int)(u % pieces);
+  const int tap = (int)((u / pieces) % (KH * KW));
+  const long long row = u / ((long long)pieces * KH * KW);
+  const int xo = (int)(row % OW), yo = (int)((row / OW) % OH);
+  const long long n = row / ((long long)OW * OH);
+  const int fy = tap / KW, fx = tap - fy * KW;
+  const int iy = yo * sh + fy * dh + oy0, ix = xo * sw + fx * dw + ox0;   // bordered coordinates
+  const uint8_t* src = x + ((n * Hp + iy) * Wp + ix) * C;
+  uint8_t* dst = a + row * kpad + (long long)tap * C;
+  if (vec == 16) {
+    reinterpret_cast<uint4*>(dst)[piece] = reinterpret_cast<const uint4*>(src)[piece];
+  } else {
+    for (int c = 0; c < C; ++c) dst[c] = src[c];
+  }
+}
+
+inline unsigned nblk(long long n, int t) { return (unsigned)((n + t - 1) / t); }
+
+}  // namespace
+
+int requant_axis_launch(const int32_t* x, long long outer, int C, long long inner, const int32_t* mult,
+                        const int32_t* shift, const int32_t* zp, int per_channel, int in_zp, const Epilogue& e, void* out,
+                        cudaStream_t s) {
+  const long long total = outer * C * inner;
+  if (total == 0) return B200Q_OK;
+  requant_axis_kernel<<<nblk(total, 256), 256, 0, s>>>(x, total, C, inner, mult, shift, zp, per_channel, in_zp, e, out);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int add_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n, int m0, int s0, int m1, int s1,
+                  int do_relu, int out_dt, void* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  const bool q8 = a_dt <= B200Q_DT_U8 && b_dt <= B200Q_DT_U8 && out_dt <= B200Q_DT_U8;
+  const bool al = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 3) == 0;
+  if (q8 && al && n % 4 == 0) {
+    add_i8x4_kernel<<<nblk(n / 4, 256), 256, 0, s>>>((const uint32_t*)a, a_dt == B200Q_DT_U8, (const uint32_t*)b,
+                                                     b_dt == B200Q_DT_U8, n / 4, m0, s0, m1, s1, do_relu, out_dt, (uint32_t*)out);
+  } else {
+    add_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(a, a_dt, b, b_dt, n, m0, s0, m1, s1, do_relu, out_dt, out);
+  }
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int pool2d_i8_launch(const void* x, int dt, int NC, int ih, int iw, int kh, int kw, int sh, int sw, int pht, int phb,
+                     int pwl, int pwr, int mode, int multi, int rshift, int do_relu, int out_dt, void* out, cudaStream_t s) {
+  const int oh = (ih + pht + phb - kh) / sh + 1, ow = (iw + pwl + pwr - kw) / sw + 1;
+  const long long total = (long long)NC * oh * ow;
+  if (total <= 0) return B200Q_OK;
+  pool2d_i8_kernel<<<nblk(total, 256), 256, 0, s>>>(x, dt, NC, ih, iw, kh, kw, sh, sw, pht, pwl, oh, ow, mode, multi, rshift,
+                                                    do_relu, out_dt, out);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int cast_f32_q8_launch(const float* x, long long n, double scale, int zp, int rmode, int out_dt, void* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  cast_f32_q8_kernel<<<nblk(n, 256), 256, 0, s>>>(x, n, (float)(1.0 / scale), zp, rmode, out_dt, out);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int cast_q8_f32_launch(const void* x, int dt, long long n, double scale, int zp, float* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  cast_q8_f32_kernel<<<nblk(n, 256), 256, 0, s>>>(x, dt, n, (float)scale, zp, out);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int im2col_nhwc_launch(const void* x, void* a, long long N, int C, int Hp, int Wp, int OH, int OW, int KH, int KW, int sh,
+                       int sw, int dh, int dw, int oy0, int ox0, int kpad, cudaStream_t s) {
+  const bool v16 = (C % 16 == 0) && (kpad % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
+  const long long units = N * OH * OW * KH * KW * (v16 ? C / 16 : 1);
+  if (units == 0) return B200Q_OK;
+  if ((units + 255) / 256 > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "im2col: too large");
+  im2col_nhwc_kernel<<<nblk(units, 256), 256, 0, s>>>((const uint8_t*)x, (uint8_t*)a, C, Hp, Wp, OH, OW, KH, KW, sh, sw, dh,
+                                                      dw, oy0, ox0, kpad, units, v16 ? 16 : 1);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+}  // namespace b200q

@@ -1,0 +1,25 @@
+// Launchers of eltwise.cu (asynchronous on the given stream).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "requant.cuh"
+
+namespace b200q {
+
+int requant_axis_launch(const int32_t* x, long long outer, int C, long long inner, const int32_t* mult,
+                        const int32_t* shift, const int32_t* zp, int per_channel, int in_zp, const Epilogue& e, void* out,
+                        cudaStream_t s);
+int add_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n, int m0, int s0, int m1, int s1,
+                  int do_relu, int out_dt, void* out, cudaStream_t s);
+// mode 0 = max, 1 = average (window sum * multi >> rshift, half up)
+int pool2d_i8_launch(const void* x, int dt, int NC, int ih, int iw, int kh, int kw, int sh, int sw, int pht, int phb,
+                     int pwl, int pwr, int mode, int multi, int rshift, int do_relu, int out_dt, void* out, cudaStream_t s);
+int cast_f32_q8_launch(const float* x, long long n, double scale, int zp, int rmode, int out_dt, void* out, cudaStream_t s);
+int cast_q8_f32_launch(const void* x, int dt, long long n, double scale, int zp, float* out, cudaStream_t s);
+// x: zero-bordered NHWC bytes [N][Hp][Wp][C]; a: rows [N*OH*OW][kpad], k = (fy*KW+fx)*C + c.  (oy0, ox0) = bordered
+// coordinate of the first tap of output pixel (0,0), i.e. border - pad.
+int im2col_nhwc_launch(const void* x, void* a, long long N, int C, int Hp, int Wp, int OH, int OW, int KH, int KW, int sh,
+                       int sw, int dh, int dw, int oy0, int ox0, int kpad, cudaStream_t s);
+
+}  // namespace b200q

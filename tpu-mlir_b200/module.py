@@ -1,0 +1,196 @@
+"""GPU-resident executor for an INT8 Tpu-dialect graph: the role of the reference's ModuleInterpreter /
+``pymlir.module`` and ``pymlir.cuda`` (bindings/pymlir/pymlir.cpp:101-131,
+bindings/pymlir/host/ModuleInterpreter.cpp:396-492,:631-1012, bindings/pymlir/pycuda.cpp:438-669).
+
+Method names and meaning follow ``pymlir.module``: ``load, set_tensor, invoke, get_tensor, get_fp32_tensor,
+get_all_tensor, before_invoke / after_invoke hooks, get_tensor_qinfo, input_names, output_names,
+all_tensor_names``.  Tensors live on the device in their native storage type (like ``py_cuda``), ops run in graph
+order through the device face of libb200q.so.  Because no MLIR parser is available here, a graph is a plain
+dict whose op types and attribute names are the Tpu dialect's:
+
+    {"inputs": [...], "outputs": [...],
+     "tensors": {name: {"shape": [...], "dtype": "f32|i8|u8|i32", "scale": s, "zp": z}},
+     "ops": [{"type": "tpu.Conv2D", "name": out_tensor, "inputs": [...], "attrs": {...}}, ...]}
+
+with weights in a dict ``name -> numpy array`` (``<op>_filter``, ``<op>_bias``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, Dict, List, Optional
+
+import numpy as np
+
+from . import _lib as L
+
+_DT = {"i8": L.DT_I8, "u8": L.DT_U8, "i32": L.DT_I32, "f32": L.DT_F32}
+_QM = {"TFLite_LShift": 0, "TFLite": 1, "MultiplierShift": 2, "OnlyShift": 3, "QDM": 4, "OnlyScale": 5}
+
+
+def _P(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+class module:  # noqa: N801  (name of the reference class)
+    def __init__(self, device: Optional[int] = None):
+        import torch
+        self.torch = torch
+        if not torch.cuda.is_available():
+            raise L.B200QError(L.ERR_NO_DEVICE, "the executor needs a CUDA device (there is no CPU fallback)")
+        self.device = torch.device("cuda", torch.cuda.current_device() if device is None else device)
+        self.lib = L.lib()
+        self.graph = None
+        self.tensors: Dict[str, "torch.Tensor"] = {}
+        self._plans: List[Callable] = []
+        self._handles: List[C.c_void_p] = []
+        self._keep = []
+        self._before: List[Callable] = []
+        self._after: List[Callable] = []
+
+    # ------------------------------------------------------------------ loading
+    def load(self, graph: dict, weights: Dict[str, np.ndarray]):
+        torch = self.torch
+        self.graph = graph
+        self.input_names = list(graph["inputs"])
+        self.output_names = list(graph["outputs"])
+        self.all_tensor_names = list(graph["tensors"].keys())
+        self.all_weight_names = list(weights.keys())
+        tdt = {"i8": torch.int8, "u8": torch.uint8, "i32": torch.int32, "f32": torch.float32}
+        for name, info in graph["tensors"].items():
+            self.tensors[name] = torch.zeros(tuple(info["shape"]), dtype=tdt[info["dtype"]], device=self.device)
+        self.weights = {k: torch.from_numpy(np.ascontiguousarray(v)).to(self.device) for k, v in weights.items()}
+        for op in graph["ops"]:
+            self._plans.append(self._plan(op))
+        torch.cuda.synchronize(self.device)
+
+    def __del__(self):
+        try:
+            for h in self._handles:
+                self.lib.b200q_conv2d_dev_destroy(C.byref(h))
+        except Exception:
+            pass
+
+    def _info(self, name):
+        return self.graph["tensors"][name]
+
+    def _plan(self, op) -> Callable:
+        t, a, lib = op["type"], op.get("attrs", {}), self.lib
+        ins = [self.tensors[n] for n in op["inputs"]]
+        out = self.tensors[op["name"]]
+        iinfo = [self._info(n) for n in op["inputs"]]
+        oinfo = self._info(op["name"])
+        stream = lambda: C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)  # noqa: E731
+        if t == "tpu.Cast":
+            n = out.numel()
+            if iinfo[0]["dtype"] == "f32":
+                return lambda: L.check(lib.b200q_cast_f32_to_q8_dev(_P(ins[0]), n, float(oinfo["scale"]), int(oinfo["zp"]),
+                                                                    L.ROUND_HALF_AWAY_FROM_ZERO, _DT[oinfo["dtype"]],
+                                                                    _P(out), stream()))
+            return lambda: L.check(lib.b200q_cast_q8_to_f32_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], n,
+                                                                float(iinfo[0]["scale"]), int(iinfo[0]["zp"]), _P(out),
+                                                                stream()))
+        if t == "tpu.Conv2D":
+            from .ops import Conv2DOp
+            w = self.weights[op["name"] + "_filter"]
+            b = self.weights.get(op["name"] + "_bias")
+            pads = a.get("pads", [0, 0, 0, 0])
+            cop = Conv2DOp(input_shape=tuple(iinfo[0]["shape"]), oc=w.shape[0], kernel_shape=tuple(a["kernel_shape"]),
+                           strides=tuple(a.get("strides", [1, 1])), dilations=tuple(a.get("dilations", [1, 1])),
+                           pads=tuple(pads), group=a.get("group", 1), with_bias=b is not None,
+                           do_relu=bool(a.get("do_relu", False)), input_dtype=_DT[iinfo[0]["dtype"]],
+                           out_dtype=_DT[oinfo["dtype"]], quant_mode=_QM[a.get("quant_mode", "MultiplierShift")],
+                           out_zp=int(oinfo.get("zp", 0)), multiplier=a["multiplier"], rshift=a["rshift"])
+            h = C.c_void_p()
+            L.check(lib.b200q_conv2d_dev_create(C.byref(cop.desc), _P(w), _P(b), C.byref(h)))
+            self._handles.append(h)
+            self._keep.append(cop)
+            return lambda: L.check(lib.b200q_conv2d_dev_run(h, _P(ins[0]), _P(out), stream()))
+        if t == "tpu.MatMul":
+            w_kn = self.weights[op["name"] + "_filter"]
+            w_nk = w_kn.t().contiguous()          # the device face takes the right operand K-major
+            b = self.weights.get(op["name"] + "_bias")
+            M = int(np.prod(iinfo[0]["shape"][:-1]))
+            K, N = w_kn.shape
+            mult = self.torch.tensor([int(a["multipliers"][0])], dtype=self.torch.int32, device=self.device)
+            shift = self.torch.tensor([int(a["rshifts"][0])], dtype=self.torch.int32, device=self.device)
+            e = L.Epilogue(dialect=L.RQ_MULTIPLIER_SHIFT, round_mode=L.ROUND_HALF_UP, per_channel=0,
+                           out_zp=int(oinfo.get("zp", 0)), relu=L.RELU_BEFORE_REQUANT if a.get("do_relu") else L.RELU_NONE,
+                           out_dtype=_DT[oinfo["dtype"]], scale=0.0, bias=b.data_ptr() if b is not None else None,
+                           multiplier=mult.data_ptr(), shift=shift.data_ptr())
+            status = self.torch.zeros(1, dtype=self.torch.int32, device=self.device)
+            self._keep += [w_nk, mult, shift, e, status]
+            return lambda: L.check(lib.b200q_gemm_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(w_nk), L.DT_I8, M, N, K,
+                                                         C.byref(e), _P(out), _P(status), L.ALGO_AUTO, stream()))
+        if t == "tpu.Add":
+            m, s = a["multipliers"], a["rshifts"]
+            n = out.numel()
+            return lambda: L.check(lib.b200q_add_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(ins[1]), _DT[iinfo[1]["dtype"]],
+                                                        n, int(m[0]), int(s[0]), int(m[1]), int(s[1]),
+                                                        int(bool(a.get("do_relu", False))), _DT[oinfo["dtype"]], _P(out),
+                                                        stream()))
+        if t == "tpu.Pool2D":
+            nb, c, ih, iw = iinfo[0]["shape"]
+            kh, kw = a["kernel_shape"]
+            sh, sw = a.get("strides", [1, 1])
+            pht, pwl, phb, pwr = a.get("pads", [0, 0, 0, 0])
+            is_avg = a["pool_mode"] == "Avg"
+            return lambda: L.check(lib.b200q_pool2d_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], nb * c, ih, iw, kh, kw, sh, sw,
+                                                           pht, phb, pwl, pwr, int(is_avg), int(a.get("multiplier", 1)),
+                                                           int(a.get("rshift", 0)), int(bool(a.get("do_relu", False))),
+                                                           _DT[oinfo["dtype"]], _P(out), stream()))
+        if t == "tpu.Reshape":
+            return lambda: out.copy_(ins[0].reshape(out.shape))
+        raise L.B200QError(L.ERR_UNSUPPORTED, f"op type {t} is not implemented by the executor")
+
+    # ------------------------------------------------------------------ pymlir.module surface
+    def set_tensor(self, name: str, data, shape=None):
+        """Float input of the graph (quantisation happens in the graph's own tpu.Cast, as in a lowered model)."""
+        t = self.tensors[name]
+        src = self.torch.as_tensor(np.ascontiguousarray(data)) if not isinstance(data, self.torch.Tensor) else data
+        t.copy_(src.reshape(t.shape).to(t.dtype), non_blocking=True)
+
+    def set_tensor_from_int(self, name: str, data, shape=None):
+        self.set_tensor(name, data, shape)
+
+    def before_invoke(self, fn: Callable):
+        self._before.append(fn)
+
+    def after_invoke(self, fn: Callable):
+        self._after.append(fn)
+
+    def clear_hooks(self):
+        self._before, self._after = [], []
+
+    def invoke(self, fixed_to_float: bool = True):
+        for op, run in zip(self.graph["ops"], self._plans):
+            for fn in self._before:
+                fn(op["name"])
+            run()
+            for fn in self._after:
+                fn(op["name"])
+
+    def invoke_at(self, name: str):
+        for op, run in zip(self.graph["ops"], self._plans):
+            if op["name"] == name:
+                run()
+                return self.get_tensor(name)
+        raise KeyError(name)
+
+    def get_tensor(self, name: str) -> np.ndarray:
+        """Raw storage values (integers for quantized tensors)."""
+        return self.tensors[name].cpu().numpy()
+
+    def get_fp32_tensor(self, name: str) -> np.ndarray:
+        """The tensor as the interpreter "expresses" it: (q - zp) * scale (ModuleInterpreter.cpp:992-1011)."""
+        info = self._info(name)
+        v = self.tensors[name].cpu().numpy()
+        if info["dtype"] == "f32":
+            return v
+        return ((v.astype(np.float32) - np.float32(info.get("zp", 0))) * np.float32(info["scale"])).astype(np.float32)
+
+    def get_all_tensor(self) -> Dict[str, np.ndarray]:
+        return {n: self.get_fp32_tensor(n) for n in self.all_tensor_names}
+
+    def get_tensor_qinfo(self, name: str):
+        info = self._info(name)
+        return info["dtype"], float(info.get("scale", 1.0)), int(info.get("zp", 0))
