@@ -186,11 +186,13 @@ int b200q_conv2d_dev_create(const b200q_conv2d_desc *desc, const void *filter_oi
 int b200q_conv2d_dev_run(void *handle, const void *x_nchw, void *y_nchw, void *stream);
 int b200q_conv2d_dev_status(void *handle, void *stream);
 void b200q_conv2d_dev_destroy(void **handle);
-/* Optional timing of the device face: when enabled, b200q_conv2d_dev_run records CUDA events on its stream
- * around the layout kernel and the tensor-core kernel; b200q_conv2d_dev_last_times waits for the last run and
- * returns both durations in milliseconds.  (The reference has no counterpart; its CUDA path is untimed.) */
+/* Optional timing of the device face: while enabled, every b200q_conv2d_dev_run records CUDA events on its
+ * stream before the layout kernel, between the two kernels and after the tensor-core kernel (no host
+ * synchronisation).  b200q_conv2d_dev_profile waits for the recorded runs and returns their number and the
+ * summed durations in milliseconds; enabling again starts a new measurement.  (No counterpart in the
+ * reference, whose CUDA path is untimed.) */
 int b200q_conv2d_dev_set_profiling(void *handle, int enable);
-int b200q_conv2d_dev_last_times(void *handle, float *layout_ms, float *kernel_ms);
+int b200q_conv2d_dev_profile(void *handle, int64_t *runs, double *layout_ms_total, double *kernel_ms_total);
 
 /* ------------------------------------------------------------------ tpu.RequantIntAxis / tpu.RequantInt
  * Operator face of tpu::RequantIntAxisOp::inference (lib/Dialect/Tpu/Interfaces/Common/RequantIntAxis.cpp:17-123,

@@ -117,7 +117,8 @@ SIGNATURES = {
     "kl_diversity_hist": (C.c_float, [C.POINTER(C.c_int), C.c_float, C.c_longlong, C.c_longlong]),
     "kl_diversity": (C.c_float, [C.POINTER(C.c_float), C.c_longlong, C.c_longlong]),
     "b200q_conv2d_dev_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
-    "b200q_conv2d_dev_last_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "b200q_conv2d_dev_profile": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_double),
+                                           C.POINTER(C.c_double)]),
 }
 
 

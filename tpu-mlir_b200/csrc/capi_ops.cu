@@ -238,12 +238,25 @@ struct ConvHandle {
   DevBuf w_oihw, w_packed, bias, mult, shift, x_bordered, a_cols, status;
   // operator-face staging
   DevBuf x_f32, x_q8, y_q, y_f32, w_f32, bias_f32;
-  // optional per-kernel timing of the device face
+  // optional per-kernel timing of the device face: one event triple per run since profiling was switched on
   bool profiling = false;
-  cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+  std::vector<cudaEvent_t> events;  // 3 per run: before the layout kernel, between, after the conv kernel
+  size_t runs_recorded = 0;
+  cudaEvent_t* ev = nullptr;        // the triple of the run being recorded
+  int next_triple() {
+    if (events.size() < (runs_recorded + 1) * 3) {
+      for (int i = 0; i < 3; ++i) {
+        cudaEvent_t e;
+        CUDA_TRY(cudaEventCreate(&e));
+        events.push_back(e);
+      }
+    }
+    ev = &events[runs_recorded * 3];
+    ++runs_recorded;
+    return B200Q_OK;
+  }
   ~ConvHandle() {
-    for (auto& e : ev)
-      if (e) cudaEventDestroy(e);
+    for (auto& e : events) cudaEventDestroy(e);
   }
 };
 
@@ -330,6 +343,7 @@ int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int
 int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s) {
   const b200q_conv2d_desc& d = h->d;
   if (d.n == 0) return B200Q_OK;
+  if (h->profiling && (h->use_tc || h->use_im2col)) B200Q_TRY(h->next_triple());
   if (h->use_tc) {
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[0], s));
     B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
@@ -602,23 +616,28 @@ void b200q_conv2d_dev_destroy(void** handle) { b200q_conv2d_deinit(handle); }
 int b200q_conv2d_dev_set_profiling(void* handle, int enable) {
   if (!handle) return set_error(B200Q_ERR_INVALID, "conv2d_dev_set_profiling: null handle");
   ConvHandle* h = static_cast<ConvHandle*>(handle);
-  if (enable)
-    for (auto& e : h->ev)
-      if (!e) CUDA_TRY(cudaEventCreate(&e));
   h->profiling = enable != 0;
+  h->runs_recorded = 0;  // a new measurement starts
   return B200Q_OK;
 }
 
-int b200q_conv2d_dev_last_times(void* handle, float* layout_ms, float* kernel_ms) {
-  if (!handle || !layout_ms || !kernel_ms) return set_error(B200Q_ERR_INVALID, "conv2d_dev_last_times: null argument");
+int b200q_conv2d_dev_profile(void* handle, int64_t* runs, double* layout_ms_total, double* kernel_ms_total) {
+  if (!handle || !runs || !layout_ms_total || !kernel_ms_total) return set_error(B200Q_ERR_INVALID, "conv2d_dev_profile: null argument");
   ConvHandle* h = static_cast<ConvHandle*>(handle);
-  if (!h->profiling || !(h->use_tc || h->use_im2col)) return set_error(B200Q_ERR_INVALID, "conv2d_dev_last_times: profiling is off or the op runs on the CUDA-core kernel");
-  CUDA_TRY(cudaEventSynchronize(h->ev[2]));
-  CUDA_TRY(cudaEventElapsedTime(layout_ms, h->ev[0], h->ev[1]));
-  CUDA_TRY(cudaEventElapsedTime(kernel_ms, h->ev[1], h->ev[2]));
+  *runs = (int64_t)h->runs_recorded;
+  *layout_ms_total = 0.0;
+  *kernel_ms_total = 0.0;
+  for (size_t r = 0; r < h->runs_recorded; ++r) {
+    cudaEvent_t* e = &h->events[r * 3];
+    float a = 0.f, b = 0.f;
+    CUDA_TRY(cudaEventSynchronize(e[2]));
+    CUDA_TRY(cudaEventElapsedTime(&a, e[0], e[1]));
+    CUDA_TRY(cudaEventElapsedTime(&b, e[1], e[2]));
+    *layout_ms_total += a;
+    *kernel_ms_total += b;
+  }
   return B200Q_OK;
 }
-
 
 // ------------------------------------------------------------------------------------------------ glue ops (device face)
 int b200q_requant_int_axis_dev(const int32_t* x, int64_t outer, int64_t C, int64_t inner, const int32_t* multiplier,
