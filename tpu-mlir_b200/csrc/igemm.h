@@ -42,6 +42,7 @@ struct IGemmArgs {
   int num_m_tiles, num_n_tiles;
   const float* bias_f32;
   int bf16;
+  int acc_small;
 };
 
 int igemm_i8_tcgen05_supported(const IGemmProblem& p, const char** why);

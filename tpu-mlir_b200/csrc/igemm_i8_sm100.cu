@@ -43,7 +43,7 @@ struct SmemLayout {
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;  // tmem ptr, abort flag
   static constexpr int CHAN_OFFSET = MISC_OFFSET + 16;           // {bias, multiplier, shift, -} of the tile's channels
-  static constexpr int SLOW_OFFSET = CHAN_OFFSET + BLOCK_N * 16;  // per 32-channel chunk: needs the general requant path
+  static constexpr int SLOW_OFFSET = CHAN_OFFSET + BLOCK_N * 16;  // per 32-channel chunk: the staged parameter form
   static constexpr int TOTAL = SLOW_OFFSET + (BLOCK_N / 32) * 4;
   static constexpr int DYN_BYTES = TOTAL + 1024;                 // slack for manual 1024-byte alignment
   // one epilogue warp per (TMEM lane quarter, 64-column group): 16 warps for BLOCK_N = 256
@@ -112,7 +112,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFFSET + 4);
   int4* chan = reinterpret_cast<int4*>(smem + L::CHAN_OFFSET);
-  int* chunk_slow = reinterpret_cast<int*>(smem + L::SLOW_OFFSET);
+  int* chunk_form = reinterpret_cast<int*>(smem + L::SLOW_OFFSET);
   constexpr int EPI_THREADS = L::EPI_WARPS * 32;
 
   const int warp = threadIdx.x >> 5;
@@ -231,7 +231,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     const int32_t zp = e.out_zp;
     const int32_t floor_pre = e.relu == B200Q_RELU_BEFORE_REQUANT ? 0 : (-2147483647 - 1);
     const int32_t floor_post = e.relu == B200Q_RELU_AFTER_REQUANT ? zp : (-2147483647 - 1);
-    int32_t sat_lo, sat_hi;
+    int32_t sat_lo, sat_hi;  // output range; the post-ReLU floor is folded into sat_lo below
     switch (e.out_dtype) {
       case B200Q_DT_I8: sat_lo = -128; sat_hi = 127; break;
       case B200Q_DT_U8: sat_lo = 0; sat_hi = 255; break;
@@ -239,6 +239,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       case B200Q_DT_U16: sat_lo = 0; sat_hi = 65535; break;
       default: sat_lo = -2147483647 - 1; sat_hi = 2147483647; break;
     }
+    const int32_t sat_lo2 = max(sat_lo, floor_post);  // clamp(max(v, f), lo, hi) == clamp(v, max(lo, f), hi) for f <= hi
     int acc = 0;
     uint32_t acc_phase = 0;
     int cached_n0 = -1;
@@ -246,8 +247,25 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int m0 = (tile / args.num_n_tiles) * BLOCK_M;
       const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
       if (n0 != cached_n0) {
+        // Stage the tile's channel parameters in the cheapest form every channel of a 32-channel chunk allows:
+        //   FOLDED  {m, C_lo, C_hi, shift}: C = bias*m + rounding constant, one 64-bit multiply-add per element
+        //   FAST    {bias, m, right shift, half}: the pre-ReLU (MatMul) order, or biases too large to fold
+        //   GENERAL {bias, m, shift, 0}: any dialect / rounding mode / parameter value (requant_value<>)
         epi_bar_sync<EPI_THREADS>();  // everyone is done reading the previous tile's channel parameters
-        if (etid < BLOCK_N / 32) chunk_slow[etid] = kFastDialect ? 0 : 1;
+        if (etid < BLOCK_N / 32) chunk_form[etid] = 0;
+        epi_bar_sync<EPI_THREADS>();
+        const bool pre_relu = e.relu == B200Q_RELU_BEFORE_REQUANT;
+        for (int c = etid; c < BLOCK_N; c += EPI_THREADS) {
+          if (DIALECT == KIND_BF16_TAG) break;
+          const int n = n0 + c;
+          if (n >= args.n) continue;
+          const int32_t bias = e.bias ? e.bias[n] : 0;
+          const int32_t m = e.multiplier ? e.multiplier[e.per_channel ? n : 0] : 1;
+          const int32_t sh = e.shift ? e.shift[e.per_channel ? n : 0] : 0;
+          const bool fast_ok = kFastDialect && fast_domain<DIALECT, RMODE>(m, sh);
+          const bool fold_ok = fast_ok && !pre_relu && args.acc_small && bias > -(1 << 28) && bias < (1 << 28);
+          atomicOr(&chunk_form[c >> 5], (fold_ok ? 0 : 1) | (fast_ok ? 0 : 2));
+        }
         epi_bar_sync<EPI_THREADS>();
         for (int c = etid; c < BLOCK_N; c += EPI_THREADS) {
           const int n = n0 + c;
@@ -259,13 +277,19 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const int32_t bias = (in && e.bias) ? e.bias[n] : 0;
           const int32_t m = (in && e.multiplier) ? e.multiplier[e.per_channel ? n : 0] : 1;
           const int32_t sh = (in && e.shift) ? e.shift[e.per_channel ? n : 0] : 0;
-          if (kFastDialect && in && fast_domain<DIALECT, RMODE>(m, sh)) {
-            // fast form: {bias, multiplier, right shift, half}
+          const int form = chunk_form[c >> 5];
+          if (!in) {
+            chan[c] = make_int4(0, 0, 1, 0);
+          } else if (form == 0) {
+            const int32_t t = DIALECT == B200Q_RQ_QDM ? -sh : sh;
+            const long long rc = DIALECT == B200Q_RQ_QDM ? (1ll << 30) : (long long)(1ull << (t - 1));
+            const long long C = (long long)bias * (long long)m + rc;
+            chan[c] = make_int4(m, (int32_t)(uint32_t)(C & 0xffffffffll), (int32_t)(C >> 32), t);
+          } else if ((form & 2) == 0) {
             const int32_t t = DIALECT == B200Q_RQ_QDM ? -sh : sh;
             chan[c] = make_int4(bias, m, t, DIALECT == B200Q_RQ_QDM ? (int32_t)(1u << (t - 1)) : 0);
           } else {
             chan[c] = make_int4(bias, m, sh, 0);
-            if (kFastDialect && in) atomicOr(&chunk_slow[c >> 5], 1);
           }
         }
         epi_bar_sync<EPI_THREADS>();
@@ -338,25 +362,40 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           continue;
         }
         int32_t q[CH];
-        if (kFastCompiled && kFastDialect && chunk_slow[cbase >> 5] == 0) {
+        const int form = kFastCompiled ? chunk_form[cbase >> 5] : 3;
+        if (kFastCompiled && form == 0) {
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
-            const int4 cp = chan[cbase + j];  // {bias, multiplier, shift, half}: one broadcast 16-byte shared load
+            const int4 cp = chan[cbase + j];  // {m, C_lo, C_hi, shift}: one broadcast 16-byte shared load
+            const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
+            const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
+            int32_t v;
+            if (DIALECT == B200Q_RQ_QDM) {
+              const int32_t w = (int32_t)(x >> 31);  // half-up shift by 31: C carries the 2^30
+              // half away from zero for a right shift by t: (w + 2^(t-1) - (w < 0)) >> t; |w| < 2^30 here
+              v = (w + (int32_t)((1u << cp.w) >> 1) + (w >> 31)) >> cp.w;
+            } else {
+              const long long y = x >> cp.w;         // half-up: C carries 2^(s-1)
+              const int32_t lo32 = (int32_t)y;
+              v = ((int32_t)(y >> 32) == (lo32 >> 31)) ? lo32 : (int32_t)(((int32_t)(y >> 63)) ^ 0x7fffffff);
+            }
+            q[j] = min(max(add_sat_s32(v, zp), sat_lo2), sat_hi);
+          }
+        } else if (kFastCompiled && (form & 2) == 0) {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            const int4 cp = chan[cbase + j];  // {bias, multiplier, shift, half}
             const int32_t a = max((int32_t)r[j] + cp.x, floor_pre);
-            int32_t v = requant_core_fast<DIALECT>(a, cp.y, cp.z, cp.w);
-            v = max(add_sat_s32(v, zp), floor_post);
-            q[j] = min(max(v, sat_lo), sat_hi);
+            const int32_t v = requant_core_fast<DIALECT>(a, cp.y, cp.z, cp.w);
+            q[j] = min(max(add_sat_s32(v, zp), sat_lo2), sat_hi);
           }
         } else {
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
-            const int4 cp = chan[cbase + j];
+            const int4 cp = chan[cbase + j];  // {bias, multiplier, shift, -}
             int32_t a = (int32_t)r[j] + cp.x;
             if (e.relu == B200Q_RELU_BEFORE_REQUANT && a < 0) a = 0;
-            // channels staged in the fast form carry a right shift; turn it back into the dialect's convention
-            int32_t sh = cp.z;
-            if (kFastCompiled && kFastDialect && DIALECT == B200Q_RQ_QDM && cp.w != 0) sh = -cp.z;
-            q[j] = requant_value<-1, -1>(a, cp.y, sh, e);
+            q[j] = requant_value<-1, -1>(a, cp.y, cp.z, e);
           }
         }
         const int ncols = min(CH, args.n - (n0 + cbase));
@@ -365,9 +404,14 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             const long long off0 = out_base + (long long)(n0 + cbase) * chan_stride;
             if (out8) {
               uint8_t* o = reinterpret_cast<uint8_t*>(args.out) + off0;
+              if (ncols == CH) {
 #pragma unroll
-              for (int j = 0; j < CH; ++j)
-                if (j < ncols) o[j * chan_stride] = (uint8_t)q[j];
+                for (int j = 0; j < CH; ++j, o += chan_stride) *o = (uint8_t)q[j];
+              } else {
+#pragma unroll
+                for (int j = 0; j < CH; ++j)
+                  if (j < ncols) o[j * chan_stride] = (uint8_t)q[j];
+              }
             } else if (e.out_dtype == B200Q_DT_I32) {
               int32_t* o = reinterpret_cast<int32_t*>(args.out) + off0;
 #pragma unroll
@@ -534,6 +578,8 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   a.epi = epi;
   a.status = status;
   a.bf16 = p.kind == IGEMM_KIND_BF16;
+  // |accumulator| < 2^29 for every 8-bit operand pair: lets the epilogue fold the bias into one 64-bit constant
+  a.acc_small = ((long long)a.num_kb * BLOCK_K * 32640ll) < (1ll << 29);
   a.bias_f32 = p.bias_f32;
   a.idesc = a.bf16 ? ptx::make_idesc(1u, 1u, 1u, BLOCK_M, (uint32_t)block_n)  // f32 accumulate, bf16 x bf16
                    : ptx::make_idesc(2u, p.a_unsigned ? 0u : 1u, p.b_unsigned ? 0u : 1u, BLOCK_M, (uint32_t)block_n);
