@@ -108,7 +108,9 @@ def test_requant_dialects_small(algo, case):
         assert np.array_equal(got.astype(np.int64), want), (d, out_dt)
 
 
-@pytest.mark.parametrize("shape", [(1, 16, 8), (129, 272, 257), (300, 1040, 96), (128, 128, 64), (5, 4096, 1000)])
+# the last shape has enough 128-row tiles for the CTA-pair (256-row tile) form of the tensor-core kernel, ragged in M, K and N
+@pytest.mark.parametrize("shape", [(1, 16, 8), (129, 272, 257), (300, 1040, 96), (128, 128, 64), (5, 4096, 1000),
+                                   (38437, 272, 300)])
 def test_ragged_shapes_tensor_core(shape):
     M, K, N = shape
     rng = np.random.default_rng(M * 7 + N)

@@ -43,6 +43,7 @@ struct IGemmArgs {
   const float* bias_f32;
   int bf16;
   int acc_small;
+  int out_small;
 };
 
 int igemm_i8_tcgen05_supported(const IGemmProblem& p, const char** why);

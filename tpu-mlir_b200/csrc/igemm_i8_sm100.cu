@@ -17,6 +17,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdlib.h>
 
 #include "igemm.h"
 #include "internal.h"
@@ -34,21 +35,26 @@ constexpr int EPI_COLS_PER_WARP = 64;
 constexpr int KIND_BF16_TAG = -2;  // value of the DIALECT template argument that selects bf16 operands / output  // each epilogue warp owns 32 TMEM lanes x 64 columns of the tile
 constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate tile time
 
-template <int BLOCK_N, int STAGES>
+// PAIR: two CTAs of a cluster compute one 256 x BLOCK_N tile with tcgen05 cta_group::2; each CTA stages its own 128
+// rows of A and half of B's N rows, so a CTA pulls 1.5x fewer operand bytes per MMA through L2 and shared memory.
+template <int BLOCK_N, int STAGES, bool PAIR = false>
 struct SmemLayout {
   static constexpr int A_BYTES = BLOCK_M * BLOCK_K;
-  static constexpr int B_BYTES = BLOCK_N * BLOCK_K;
+  static constexpr int B_ROWS = PAIR ? BLOCK_N / 2 : BLOCK_N;  // rows of B this CTA stages
+  static constexpr int B_BYTES = B_ROWS * BLOCK_K;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;  // tmem ptr, abort flag
   static constexpr int CHAN_OFFSET = MISC_OFFSET + 16;           // {bias, multiplier, shift, -} of the tile's channels
   static constexpr int SLOW_OFFSET = CHAN_OFFSET + BLOCK_N * 16;  // per 32-channel chunk: the staged parameter form
-  static constexpr int TOTAL = SLOW_OFFSET + (BLOCK_N / 32) * 4;
+  static constexpr int CHANK_OFFSET = SLOW_OFFSET + (BLOCK_N / 32) * 4;  // folded form: rounding constant + shifted zero point
+  static constexpr int TOTAL = CHANK_OFFSET + BLOCK_N * 4;
   static constexpr int DYN_BYTES = TOTAL + 1024;                 // slack for manual 1024-byte alignment
   // one epilogue warp per (TMEM lane quarter, 64-column group): 16 warps for BLOCK_N = 256
   static constexpr int EPI_WARPS = 4 * (BLOCK_N / EPI_COLS_PER_WARP);
   static constexpr int NUM_THREADS = 64 + EPI_WARPS * 32;
+  // 18 warps land 5,5,4,4 on the four sub-partitions (16384 registers each): 96 registers per thread at most
 };
 
 template <int BLOCK_N>
@@ -96,11 +102,22 @@ __device__ __forceinline__ bool fast_domain(int32_t m, int32_t s) {
   return false;
 }
 
-template <int BLOCK_N, int STAGES, int DIALECT, int RMODE>
-__global__ void __launch_bounds__(SmemLayout<BLOCK_N, STAGES>::NUM_THREADS, 1)
+// Extra conditions of the folded form (on top of fast_domain, |bias| < 2^28 and |accumulator| < 2^29), chosen so
+// that no intermediate can overflow: QDM: |zp| << t < 2^28;  MultiplierShift: s >= 32 (the shifted value then
+// fits 32 bits) and |zp| << s < 2^60.
+template <int DIALECT>
+__device__ __forceinline__ bool fold_domain(int32_t sh, int32_t zp) {
+  const long long az = zp < 0 ? -(long long)zp : (long long)zp;
+  if (DIALECT == B200Q_RQ_QDM) return az < (1ll << 20) && (az << (-sh)) < (1ll << 28);
+  if (DIALECT == B200Q_RQ_MULTIPLIER_SHIFT) return sh >= 32 && az < (1ll << 20) && (zp == 0 || sh <= 40);
+  return false;
+}
+
+template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR>
+__global__ void __launch_bounds__(SmemLayout<BLOCK_N, STAGES, PAIR>::NUM_THREADS, 1)
 igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const IGemmArgs args) {
-  using L = SmemLayout<BLOCK_N, STAGES>;
+  using L = SmemLayout<BLOCK_N, STAGES, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = ptx::smem_u32(smem);
@@ -113,10 +130,16 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFFSET + 4);
   int4* chan = reinterpret_cast<int4*>(smem + L::CHAN_OFFSET);
   int* chunk_form = reinterpret_cast<int*>(smem + L::SLOW_OFFSET);
+  int32_t* chan_k = reinterpret_cast<int32_t*>(smem + L::CHANK_OFFSET);
   constexpr int EPI_THREADS = L::EPI_WARPS * 32;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // PAIR: CTA 0 of the cluster leads (expects the bytes of both CTAs' loads, issues the MMAs); a worker is a CTA pair
+  const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  constexpr int TILE_M = PAIR ? 2 * BLOCK_M : BLOCK_M;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -125,7 +148,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tmem_full_bar(a), 1);
-      ptx::mbar_init(tmem_empty_bar(a), EPI_THREADS);
+      ptx::mbar_init(tmem_empty_bar(a), PAIR ? 2 * L::EPI_WARPS : EPI_THREADS);  // PAIR: one arrival per warp, both CTAs
     }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -133,9 +156,18 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
   }
+  if (PAIR) {
+    __syncthreads();
+    ptx::cluster_sync_all();  // the peer's barriers exist before anything can signal them
+  }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(tmem_ptr_smem), TmemCols<BLOCK_N>::value);
-    ptx::tmem_relinquish();
+    if (PAIR) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(tmem_ptr_smem), TmemCols<BLOCK_N>::value);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(tmem_ptr_smem), TmemCols<BLOCK_N>::value);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -151,8 +183,8 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / args.num_n_tiles) * BLOCK_M;
+      for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
+        const int m0 = (tile / args.num_n_tiles) * TILE_M + (int)cta_rank * BLOCK_M;
         const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, WAIT_BUDGET_NS);
@@ -162,10 +194,18 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const int fy = tap / args.taps_w;
           const int fx = tap - fy * args.taps_w;
           const int a_row = m0 + (fy - args.tap_org_h) * args.row_pitch + (fx - args.tap_org_w);
-          ptx::mbar_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
           const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
-          ptx::tma_load_2d(sa, &tmap_a, full_bar(stage), kc * BLOCK_K, a_row);
-          ptx::tma_load_2d(sa + L::A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, n0);
+          if (PAIR) {
+            // both CTAs' bytes complete on the leader's barrier; only the leader arrives on it
+            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);
+            const uint32_t lead_bar = ptx::map_to_cta(full_bar(stage), 0);
+            ptx::tma_load_2d_pair(sa, &tmap_a, lead_bar, kc * BLOCK_K, a_row);
+            ptx::tma_load_2d_pair(sa + L::A_BYTES, &tmap_b, lead_bar, kb * BLOCK_K, n0 + (int)cta_rank * L::B_ROWS);
+          } else {
+            ptx::mbar_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
+            ptx::tma_load_2d(sa, &tmap_a, full_bar(stage), kc * BLOCK_K, a_row);
+            ptx::tma_load_2d(sa + L::A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, n0);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -175,13 +215,13 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
         ok = ptx::mbar_wait_bounded(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2, WAIT_BUDGET_NS);
         if (!ok) break;
         ptx::tc_fence_after_sync();
@@ -196,21 +236,27 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
           for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
             // advancing K inside the swizzle span = advancing the start address (16-byte units)
-            if (DIALECT == KIND_BF16_TAG)
-              ptx::umma_f16(d_tmem, a_desc + (uint64_t)(k * (UMMA_K / 16)), b_desc + (uint64_t)(k * (UMMA_K / 16)),
-                            args.idesc, (kb | k) != 0 ? 1u : 0u);
-            else
-              ptx::umma_i8(d_tmem, a_desc + (uint64_t)(k * (UMMA_K / 16)), b_desc + (uint64_t)(k * (UMMA_K / 16)),
-                           args.idesc, (kb | k) != 0 ? 1u : 0u);
+            const uint64_t ad = a_desc + (uint64_t)(k * (UMMA_K / 16)), bd = b_desc + (uint64_t)(k * (UMMA_K / 16));
+            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            if (PAIR) {
+              if (DIALECT == KIND_BF16_TAG) ptx::umma_f16_pair(d_tmem, ad, bd, args.idesc, accum);
+              else ptx::umma_i8_pair(d_tmem, ad, bd, args.idesc, accum);
+            } else {
+              if (DIALECT == KIND_BF16_TAG) ptx::umma_f16(d_tmem, ad, bd, args.idesc, accum);
+              else ptx::umma_i8(d_tmem, ad, bd, args.idesc, accum);
+            }
           }
-          ptx::umma_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
+          // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
+          if (PAIR) ptx::umma_commit_pair(empty_bar(stage), 3);
+          else ptx::umma_commit(empty_bar(stage));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        ptx::umma_commit(tmem_full_bar(acc));  // accumulator complete
+        if (PAIR) ptx::umma_commit_pair(tmem_full_bar(acc), 3);  // accumulator complete (each CTA holds its 128 rows)
+        else ptx::umma_commit(tmem_full_bar(acc));
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;
@@ -243,12 +289,14 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     int acc = 0;
     uint32_t acc_phase = 0;
     int cached_n0 = -1;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile / args.num_n_tiles) * BLOCK_M;
+    const uint32_t lead_tmem_empty0 = PAIR ? ptx::map_to_cta(tmem_empty_bar(0), 0) : 0u;
+    for (int tile = worker; tile < num_tiles; tile += num_workers) {
+      const int m0 = (tile / args.num_n_tiles) * TILE_M + (int)cta_rank * BLOCK_M;
       const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
       if (n0 != cached_n0) {
         // Stage the tile's channel parameters in the cheapest form every channel of a 32-channel chunk allows:
-        //   FOLDED  {m, C_lo, C_hi, shift}: C = bias*m + rounding constant, one 64-bit multiply-add per element
+        //   FOLDED  {m, C_lo, C_hi, shift} (+ chan_k): bias, rounding constants and the output zero point are folded
+        //           into one 64-bit and one 32-bit constant; one multiply-add, two shifts and a clamp per element
         //   FAST    {bias, m, right shift, half}: the pre-ReLU (MatMul) order, or biases too large to fold
         //   GENERAL {bias, m, shift, 0}: any dialect / rounding mode / parameter value (requant_value<>)
         epi_bar_sync<EPI_THREADS>();  // everyone is done reading the previous tile's channel parameters
@@ -263,7 +311,8 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const int32_t m = e.multiplier ? e.multiplier[e.per_channel ? n : 0] : 1;
           const int32_t sh = e.shift ? e.shift[e.per_channel ? n : 0] : 0;
           const bool fast_ok = kFastDialect && fast_domain<DIALECT, RMODE>(m, sh);
-          const bool fold_ok = fast_ok && !pre_relu && args.acc_small && bias > -(1 << 28) && bias < (1 << 28);
+          const bool fold_ok = fast_ok && !pre_relu && args.acc_small && bias > -(1 << 28) && bias < (1 << 28) &&
+                               fold_domain<DIALECT>(sh, e.out_zp);
           atomicOr(&chunk_form[c >> 5], (fold_ok ? 0 : 1) | (fast_ok ? 0 : 2));
         }
         epi_bar_sync<EPI_THREADS>();
@@ -281,10 +330,19 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           if (!in) {
             chan[c] = make_int4(0, 0, 1, 0);
           } else if (form == 0) {
-            const int32_t t = DIALECT == B200Q_RQ_QDM ? -sh : sh;
-            const long long rc = DIALECT == B200Q_RQ_QDM ? (1ll << 30) : (long long)(1ull << (t - 1));
-            const long long C = (long long)bias * (long long)m + rc;
-            chan[c] = make_int4(m, (int32_t)(uint32_t)(C & 0xffffffffll), (int32_t)(C >> 32), t);
+            if (DIALECT == B200Q_RQ_QDM) {
+              // w = (acc*m + C) >> 31 (half up), then (w - (w < 0) + K) >> t with K = 2^(t-1) + (zp << t)
+              const int32_t t = -sh;
+              const long long C = (long long)bias * (long long)m + (1ll << 30);
+              chan[c] = make_int4(m, (int32_t)(uint32_t)(C & 0xffffffffll), (int32_t)(C >> 32), t);
+              chan_k[c] = (int32_t)((1u << t) >> 1) + (int32_t)((uint32_t)e.out_zp << t);
+            } else {
+              // (acc*m + C) >> s with C = bias*m + 2^(s-1) + (zp << s); s >= 32, so the result is the high word >> (s-32)
+              const long long C = (long long)bias * (long long)m + (long long)(1ull << (sh - 1)) +
+                                  (long long)((unsigned long long)(long long)e.out_zp << sh);
+              chan[c] = make_int4(m, (int32_t)(uint32_t)(C & 0xffffffffll), (int32_t)(C >> 32), sh - 32);
+              chan_k[c] = 0;
+            }
           } else if ((form & 2) == 0) {
             const int32_t t = DIALECT == B200Q_RQ_QDM ? -sh : sh;
             chan[c] = make_int4(bias, m, t, DIALECT == B200Q_RQ_QDM ? (int32_t)(1u << (t - 1)) : 0);
@@ -334,7 +392,12 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         if (cc == EPI_COLS_PER_WARP / CH - 1) {
           // this warp's share of the accumulator buffer is in registers: hand it back to the MMA warp
           ptx::tc_fence_before_sync();
-          ptx::mbar_arrive(tmem_empty_bar(acc));
+          if (PAIR) {
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(lead_tmem_empty0 + 8u * acc);  // the leader's MMA warp waits on it
+          } else {
+            ptx::mbar_arrive(tmem_empty_bar(acc));
+          }
         }
         if (n0 + cbase >= args.n) continue;
         if (DIALECT == KIND_BF16_TAG) {
@@ -369,17 +432,15 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             const int4 cp = chan[cbase + j];  // {m, C_lo, C_hi, shift}: one broadcast 16-byte shared load
             const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
             const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
-            int32_t v;
+            int32_t v;  // requantised value with the zero point already added
             if (DIALECT == B200Q_RQ_QDM) {
               const int32_t w = (int32_t)(x >> 31);  // half-up shift by 31: C carries the 2^30
               // half away from zero for a right shift by t: (w + 2^(t-1) - (w < 0)) >> t; |w| < 2^30 here
-              v = (w + (int32_t)((1u << cp.w) >> 1) + (w >> 31)) >> cp.w;
+              v = (w + (w >> 31) + chan_k[cbase + j]) >> cp.w;
             } else {
-              const long long y = x >> cp.w;         // half-up: C carries 2^(s-1)
-              const int32_t lo32 = (int32_t)y;
-              v = ((int32_t)(y >> 32) == (lo32 >> 31)) ? lo32 : (int32_t)(((int32_t)(y >> 63)) ^ 0x7fffffff);
+              v = (int32_t)(x >> 32) >> cp.w;  // half-up: C carries 2^(s-1); cp.w = s - 32
             }
-            q[j] = min(max(add_sat_s32(v, zp), sat_lo2), sat_hi);
+            q[j] = min(max(v, sat_lo2), sat_hi);
           }
         } else if (kFastCompiled && (form & 2) == 0) {
 #pragma unroll
@@ -404,7 +465,13 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             const long long off0 = out_base + (long long)(n0 + cbase) * chan_stride;
             if (out8) {
               uint8_t* o = reinterpret_cast<uint8_t*>(args.out) + off0;
-              if (ncols == CH) {
+              if (ncols == CH && args.out_small) {
+                // whole output below 2^31 elements: uniform base + 32-bit per-thread offsets
+                uint8_t* const ob = reinterpret_cast<uint8_t*>(args.out);
+                uint32_t off = (uint32_t)off0;
+#pragma unroll
+                for (int j = 0; j < CH; ++j, off += (uint32_t)chan_stride) ob[off] = (uint8_t)q[j];
+              } else if (ncols == CH) {
 #pragma unroll
                 for (int j = 0; j < CH; ++j, o += chan_stride) *o = (uint8_t)q[j];
               } else {
@@ -473,9 +540,11 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   // ---------------------------------------------------------------- teardown
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) ptx::cluster_sync_all();  // neither CTA frees TMEM or exits while the other can still signal or read it
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, TmemCols<BLOCK_N>::value);
+    if (PAIR) ptx::tmem_dealloc_pair(tmem_base, TmemCols<BLOCK_N>::value);
+    else ptx::tmem_dealloc(tmem_base, TmemCols<BLOCK_N>::value);
   }
   if (threadIdx.x == 0 && *abort_flag != 0 && args.status != nullptr) atomicCAS(args.status, 0, *abort_flag);
 }
@@ -516,28 +585,48 @@ int make_tmap_u8_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
   return B200Q_OK;
 }
 
-template <int BLOCK_N, int STAGES, int DIALECT, int RMODE>
-int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& args, int grid, cudaStream_t stream) {
-  using L = SmemLayout<BLOCK_N, STAGES>;
-  auto kfn = igemm_i8_kernel<BLOCK_N, STAGES, DIALECT, RMODE>;
+template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR>
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& args, int workers, cudaStream_t stream) {
+  using L = SmemLayout<BLOCK_N, STAGES, PAIR>;
+  auto kfn = igemm_i8_kernel<BLOCK_N, STAGES, DIALECT, RMODE, PAIR>;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-  kfn<<<grid, L::NUM_THREADS, L::DYN_BYTES, stream>>>(ta, tb, args);
-  CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(PAIR ? 2 * workers : workers);
+  cfg.blockDim = dim3(L::NUM_THREADS);
+  cfg.dynamicSmemBytes = L::DYN_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, kfn, ta, tb, args));
   return B200Q_OK;
 }
 
-template <int BLOCK_N, int STAGES>
-int launch_dialect(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& a, int grid, cudaStream_t s) {
+template <int BLOCK_N, int STAGES, bool PAIR>
+int launch_dialect(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& a, int workers, cudaStream_t s) {
   const int d = a.epi.dialect, r = a.epi.round_mode;
-  if (a.bf16) return launch_one<BLOCK_N, STAGES, KIND_BF16_TAG, -1>(ta, tb, a, grid, s);
+  if (a.bf16) return launch_one<BLOCK_N, STAGES, KIND_BF16_TAG, -1, PAIR>(ta, tb, a, workers, s);
   if (d == B200Q_RQ_MULTIPLIER_SHIFT && r == B200Q_ROUND_HALF_UP)
-    return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP>(ta, tb, a, grid, s);
+    return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP, PAIR>(ta, tb, a, workers, s);
   if (d == B200Q_RQ_QDM && r == B200Q_ROUND_HALF_AWAY_FROM_ZERO)
-    return launch_one<BLOCK_N, STAGES, B200Q_RQ_QDM, B200Q_ROUND_HALF_AWAY_FROM_ZERO>(ta, tb, a, grid, s);
-  return launch_one<BLOCK_N, STAGES, -1, -1>(ta, tb, a, grid, s);
+    return launch_one<BLOCK_N, STAGES, B200Q_RQ_QDM, B200Q_ROUND_HALF_AWAY_FROM_ZERO, PAIR>(ta, tb, a, workers, s);
+  return launch_one<BLOCK_N, STAGES, -1, -1, PAIR>(ta, tb, a, workers, s);
 }
 
 }  // namespace
+
+// B200Q_IGEMM_PAIR=0 in the environment keeps every launch on single-CTA tiles (for A/B timing).
+static bool pair_mode_allowed() {
+  static const bool on = [] {
+    const char* v = getenv("B200Q_IGEMM_PAIR");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
 
 int igemm_i8_tcgen05_supported(const IGemmProblem& p, const char** why) {
   const char* w = nullptr;
@@ -581,9 +670,22 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   // |accumulator| < 2^29 for every 8-bit operand pair: lets the epilogue fold the bias into one 64-bit constant
   a.acc_small = ((long long)a.num_kb * BLOCK_K * 32640ll) < (1ll << 29);
   a.bias_f32 = p.bias_f32;
-  a.idesc = a.bf16 ? ptx::make_idesc(1u, 1u, 1u, BLOCK_M, (uint32_t)block_n)  // f32 accumulate, bf16 x bf16
-                   : ptx::make_idesc(2u, p.a_unsigned ? 0u : 1u, p.b_unsigned ? 0u : 1u, BLOCK_M, (uint32_t)block_n);
-  a.num_m_tiles = (p.rows + BLOCK_M - 1) / BLOCK_M;
+  {
+    const long long out_elems = p.out_mode == IGEMM_OUT_NCHW
+                                    ? (long long)((p.rows + a.img_rows - 1) / a.img_rows) * p.n * p.out_h * p.out_w
+                                    : (long long)p.rows * p.ldc;
+    a.out_small = out_elems < (1ll << 31);
+  }
+  // CTA pairs (256-row tiles, cta_group::2) once there is more than one wave of 128-row tiles to share out
+  int dev = 0, sms = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const long long tiles128 = (long long)((p.rows + BLOCK_M - 1) / BLOCK_M) * ((p.n + block_n - 1) / block_n);
+  const bool pair = block_n == 256 && pair_mode_allowed() && tiles128 >= 2ll * sms;
+  const int tile_m = pair ? 2 * BLOCK_M : BLOCK_M;
+  a.idesc = a.bf16 ? ptx::make_idesc(1u, 1u, 1u, tile_m, (uint32_t)block_n)  // f32 accumulate, bf16 x bf16
+                   : ptx::make_idesc(2u, p.a_unsigned ? 0u : 1u, p.b_unsigned ? 0u : 1u, tile_m, (uint32_t)block_n);
+  a.num_m_tiles = (p.rows + tile_m - 1) / tile_m;
   a.num_n_tiles = (p.n + block_n - 1) / block_n;
 
   CUtensorMap ta, tb;
@@ -591,18 +693,17 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   if (rc) return rc;
   // B: [n][taps * k_per_tap]; with several taps k_per_tap is a multiple of BLOCK_K so blocks never straddle taps
   rc = make_tmap_u8_2d(&tb, p.b, (uint64_t)p.k_per_tap * p.taps_h * p.taps_w, (uint64_t)p.n, (uint64_t)p.b_pitch,
-                       (uint32_t)block_n);
+                       (uint32_t)(pair ? block_n / 2 : block_n));
   if (rc) return rc;
 
-  int dev = 0, sms = 0;
-  CUDA_TRY(cudaGetDevice(&dev));
-  CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int tiles = a.num_m_tiles * a.num_n_tiles;
-  const int grid = tiles < sms ? tiles : sms;
+  const int slots = pair ? sms / 2 : sms;
+  const int workers = tiles < slots ? tiles : slots;
+  if (pair) return launch_dialect<256, 6, true>(ta, tb, a, workers, stream);
   switch (block_n) {
-    case 256: return launch_dialect<256, 4>(ta, tb, a, grid, stream);
-    case 128: return launch_dialect<128, 6>(ta, tb, a, grid, stream);
-    default: return launch_dialect<64, 8>(ta, tb, a, grid, stream);
+    case 256: return launch_dialect<256, 4, false>(ta, tb, a, workers, stream);
+    case 128: return launch_dialect<128, 6, false>(ta, tb, a, workers, stream);
+    default: return launch_dialect<64, 8, false>(ta, tb, a, workers, stream);
   }
 }
 
