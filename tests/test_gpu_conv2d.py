@@ -69,6 +69,11 @@ def test_conv3x3_qdm_small(algo):
     dict(N=2, C=64, H=14, W=14, OC=256, k=1, pads=(0, 0, 0, 0)),           # 1x1, K < 128
     dict(N=1, C=48, H=5, W=6, OC=24, k=1, pads=(0, 0, 0, 0)),              # 1x1, K multiple of 16 only
     dict(N=1, C=128, H=6, W=6, OC=8, k=5, pads=(2, 2, 2, 2)),              # 5x5
+    # larger images: CTA-pair tiles, several channel tiles, odd sizes
+    dict(N=3, C=128, H=13, W=28, OC=300, k=3, pads=(1, 1, 1, 1)),          # two channel tiles, odd height
+    dict(N=2, C=256, H=30, W=17, OC=136, k=3, pads=(1, 1, 1, 1)),          # odd width
+    dict(N=5, C=128, H=11, W=64, OC=96, k=3, pads=(1, 1, 0, 2)),           # asymmetric pads
+    dict(N=2, C=80, H=16, W=16, OC=512, k=1, pads=(0, 0, 0, 0)),           # 1x1 with a ragged K block
 ])
 def test_conv_tensor_core_shapes(case):
     c = synth.conv2d_int8(seed=case["C"] + case["OC"], N=case["N"], C=case["C"], H=case["H"], W=case["W"],

@@ -275,7 +275,7 @@ int conv_out_dims(const b200q_conv2d_desc& d, int64_t* oh, int64_t* ow) {
 // filter / bias already on the device in native types
 int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int w_is_f32, const void* bias_dev,
                int bias_is_f32, cudaStream_t s) {
-  int64_t oh, ow;
+  int64_t oh = 0, ow = 0;
   B200Q_TRY(conv_out_dims(d, &oh, &ow));
   h->d = d;
   h->d.multipliers = nullptr;

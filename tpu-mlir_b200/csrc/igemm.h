@@ -1,5 +1,6 @@
 // Problem description of the INT8 (implicit) GEMM kernels.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -46,6 +47,8 @@ struct IGemmArgs {
   int out_small;
 };
 
+int make_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                 const uint32_t* box);
 int igemm_i8_tcgen05_supported(const IGemmProblem& p, const char** why);
 int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* status, cudaStream_t stream);
 // Plain CUDA-core kernel for shapes the tensor-core path does not take (odd K, strides, groups, dilation).

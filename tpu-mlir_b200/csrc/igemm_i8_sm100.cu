@@ -30,7 +30,6 @@ namespace {
 
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;  // bytes == int8 elements: one 128-byte swizzle span
-constexpr int UMMA_K = 32;    // K of one tcgen05.mma for 8-bit operands
 constexpr int EPI_COLS_PER_WARP = 64;
 constexpr int KIND_BF16_TAG = -2;  // value of the DIALECT template argument that selects bf16 operands / output  // each epilogue warp owns 32 TMEM lanes x 64 columns of the tile
 constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate tile time
@@ -186,14 +185,12 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
         const int m0 = (tile / args.num_n_tiles) * TILE_M + (int)cta_rank * BLOCK_M;
         const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
+        // k-block inside the tap and the tap's row shift are counted, not divided: this loop is serial
+        int kc = 0, fx = 0;
+        int a_row = m0 - args.tap_org_h * args.row_pitch - args.tap_org_w;  // tap (0,0)
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, WAIT_BUDGET_NS);
           if (!ok) break;
-          const int tap = kb / args.kb_per_tap;
-          const int kc = kb - tap * args.kb_per_tap;
-          const int fy = tap / args.taps_w;
-          const int fx = tap - fy * args.taps_w;
-          const int a_row = m0 + (fy - args.tap_org_h) * args.row_pitch + (fx - args.tap_org_w);
           const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
           if (PAIR) {
             // both CTAs' bytes complete on the leader's barrier; only the leader arrives on it
@@ -205,6 +202,14 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             ptx::mbar_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
             ptx::tma_load_2d(sa, &tmap_a, full_bar(stage), kc * BLOCK_K, a_row);
             ptx::tma_load_2d(sa + L::A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, n0);
+          }
+          if (++kc == args.kb_per_tap) {
+            kc = 0;
+            ++a_row;  // next tap of the filter row
+            if (++fx == args.taps_w) {
+              fx = 0;
+              a_row += args.row_pitch - args.taps_w;  // first tap of the next filter row
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -221,6 +226,11 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      // K-major, 128-byte swizzle, 8-row groups 1024 bytes apart: only the start address differs between tiles
+      const uint64_t desc0 = ptx::make_smem_desc_kmajor(smem_base, 1024, 2);
+      const uint32_t desc_hi = (uint32_t)(desc0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)desc0;
+      const uint32_t b_lo0 = (uint32_t)ptx::make_smem_desc_kmajor(smem_base + L::A_BYTES, 1024, 2);
       for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
         ok = ptx::mbar_wait_bounded(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2, WAIT_BUDGET_NS);
         if (!ok) break;
@@ -230,21 +240,14 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           ok = ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, 3, WAIT_BUDGET_NS);
           if (!ok) break;
           ptx::tc_fence_after_sync();
-          const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
-          const uint64_t a_desc = ptx::make_smem_desc_kmajor(sa, 1024, 2);
-          const uint64_t b_desc = ptx::make_smem_desc_kmajor(sa + L::A_BYTES, 1024, 2);
-#pragma unroll
-          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-            // advancing K inside the swizzle span = advancing the start address (16-byte units)
-            const uint64_t ad = a_desc + (uint64_t)(k * (UMMA_K / 16)), bd = b_desc + (uint64_t)(k * (UMMA_K / 16));
-            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
-            if (PAIR) {
-              if (DIALECT == KIND_BF16_TAG) ptx::umma_f16_pair(d_tmem, ad, bd, args.idesc, accum);
-              else ptx::umma_i8_pair(d_tmem, ad, bd, args.idesc, accum);
-            } else {
-              if (DIALECT == KIND_BF16_TAG) ptx::umma_f16(d_tmem, ad, bd, args.idesc, accum);
-              else ptx::umma_i8(d_tmem, ad, bd, args.idesc, accum);
-            }
+          const uint32_t so = (uint32_t)stage * (uint32_t)(L::STAGE_BYTES >> 4);  // descriptor address units of 16 bytes
+          const uint32_t accum = kb != 0 ? 1u : 0u;
+          if (PAIR) {
+            if (DIALECT == KIND_BF16_TAG) ptx::umma_kblock_f16_pair(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, args.idesc, accum);
+            else ptx::umma_kblock_i8_pair(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, args.idesc, accum);
+          } else {
+            if (DIALECT == KIND_BF16_TAG) ptx::umma_kblock_f16(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, args.idesc, accum);
+            else ptx::umma_kblock_i8(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, args.idesc, accum);
           }
           // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
           if (PAIR) ptx::umma_commit_pair(empty_bar(stage), 3);
@@ -383,20 +386,30 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       }
 
       constexpr int CH = 16;  // columns per TMEM load: keeps the epilogue's live registers low
+      // The TMEM read of the next 16 columns is in flight while this chunk is requantised and stored (a read takes
+      // ~0.5 us while MMAs are running).
+      const uint32_t t_warp = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + col0);
+      uint32_t rn[CH];
+      ptx::tmem_ld_32x32b_x16(t_warp, rn);
 #pragma unroll 1
       for (int cc = 0; cc < EPI_COLS_PER_WARP / CH; ++cc) {
         const int cbase = col0 + cc * CH;
         uint32_t r[CH];
-        ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + cbase), r);
-        ptx::tmem_ld_wait();
-        if (cc == EPI_COLS_PER_WARP / CH - 1) {
-          // this warp's share of the accumulator buffer is in registers: hand it back to the MMA warp
+        ptx::tmem_ld_wait_16(rn);
+#pragma unroll
+        for (int j = 0; j < CH; ++j) r[j] = rn[j];
+        if (cc < EPI_COLS_PER_WARP / CH - 1) {
+          ptx::tmem_ld_32x32b_x16(t_warp + (uint32_t)((cc + 1) * CH), rn);
+        } else {
+          // this warp's share of the accumulator buffer is in registers: hand it back to the MMA warp.  Nothing
+          // written to memory is being published, so the arrival needs no release ordering (which would wait for
+          // this thread's earlier global stores).
           ptx::tc_fence_before_sync();
           if (PAIR) {
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(lead_tmem_empty0 + 8u * acc);  // the leader's MMA warp waits on it
+            if (lane == 0) ptx::mbar_arrive_cluster_relaxed(lead_tmem_empty0 + 8u * acc);  // the leader's MMA warp waits on it
           } else {
-            ptx::mbar_arrive(tmem_empty_bar(acc));
+            ptx::mbar_arrive_relaxed(tmem_empty_bar(acc));
           }
         }
         if (n0 + cbase >= args.n) continue;
@@ -569,20 +582,10 @@ EncodeTiledFn get_encode_fn() {
 // 2-D uint8 tensor [outer][inner] with row pitch `pitch` bytes, box {128 bytes, box_rows}, 128-byte swizzle.
 int make_tmap_u8_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch,
                     uint32_t box_rows) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return set_error(B200Q_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch & 15) != 0)
-    return set_error(B200Q_ERR_INVALID, "TMA operand needs a 16-byte aligned base and row pitch (base %p pitch %llu)",
-                     base, (unsigned long long)pitch);
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {pitch};
-  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return set_error(B200Q_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-  return B200Q_OK;
+  const uint64_t dims[2] = {inner, outer};
+  const uint64_t strides[1] = {pitch};
+  const uint32_t box[2] = {(uint32_t)BLOCK_K, box_rows};
+  return make_tmap_u8(map, base, 2, dims, strides, box);
 }
 
 template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR>
@@ -618,6 +621,32 @@ int launch_dialect(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs
 }
 
 }  // namespace
+
+// uint8 tensor map of `rank` dimensions (dims[0] innermost, strides_bytes[i] = byte pitch of dimension i+1), 128-byte
+// swizzle, zero fill outside the tensor.  box[0] must be 128 (one swizzle span).
+int make_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                 const uint32_t* box) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return set_error(B200Q_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return set_error(B200Q_ERR_INVALID, "TMA operand base %p is not 16-byte aligned", base);
+  cuuint64_t d[5];
+  cuuint64_t st[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) {
+      st[i] = strides_bytes[i];
+      if (st[i] & 15) return set_error(B200Q_ERR_INVALID, "TMA operand pitch %llu is not a multiple of 16 bytes", (unsigned long long)st[i]);
+    }
+  }
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, const_cast<void*>(base), d, st, bx, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(B200Q_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return B200Q_OK;
+}
 
 // B200Q_IGEMM_PAIR=0 in the environment keeps every launch on single-CTA tiles (for A/B timing).
 static bool pair_mode_allowed() {

@@ -45,6 +45,11 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrive without release ordering: for hand-offs where nothing written to memory is being published
+// (an accumulator buffer that has been read into registers).
+__device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar) {
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -92,6 +97,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// 4-D tile load (c0 innermost).  Box elements land densely in shared memory, dimension 0 fastest.
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar, int32_t c0, int32_t c1,
+                                            int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
 
@@ -166,6 +180,9 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 // 2-D tile load into this CTA's shared memory whose completion bytes are counted on a barrier that may
 // live in the peer CTA of the pair (`cluster_bar` is a shared::cluster address).  No multicast.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* m, uint32_t cluster_bar,
@@ -173,6 +190,13 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(cluster_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t smem_dst, const CUtensorMap* m, uint32_t cluster_bar, int32_t c0,
+                                                 int32_t c1, int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
@@ -216,6 +240,49 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
                "h"(cta_mask)
                : "memory");
 }
+
+// ---------------------------------------------------------------- one k-block (128 bytes of K) = four MMAs, one asm block
+// The MMA-issuing thread is a single-thread serial loop; at ~60 dependent instructions per k-block it, not the
+// tensor pipe, sets the pace.  This form takes the descriptors as 32-bit halves (the high word is the same for every
+// K-major 128-byte-swizzled tile), advances K by +2 (32 bytes) on the low word and needs ~12 instructions per k-block.
+#define B200Q_DEFINE_UMMA_KBLOCK(NAME, GROUP, KIND)                                                                   \
+  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc, \
+                                       uint32_t accumulate_first) {                                                     \
+    asm volatile(                                                                                                       \
+        "{\n\t"                                                                                                         \
+        ".reg .pred p;\n\t"                                                                                             \
+        ".reg .b32 al, bl;\n\t"                                                                                         \
+        ".reg .b64 da, db;\n\t"                                                                                         \
+        "setp.ne.b32 p, %5, 0;\n\t"                                                                                     \
+        "mov.b64 da, {%1, %3};\n\t"                                                                                     \
+        "mov.b64 db, {%2, %3};\n\t"                                                                                     \
+        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, p;\n\t"                                      \
+        "setp.eq.b32 p, %4, %4;\n\t"                                                                                    \
+        "add.u32 al, %1, 2;\n\t"                                                                                        \
+        "add.u32 bl, %2, 2;\n\t"                                                                                        \
+        "mov.b64 da, {al, %3};\n\t"                                                                                     \
+        "mov.b64 db, {bl, %3};\n\t"                                                                                     \
+        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, p;\n\t"                                      \
+        "add.u32 al, %1, 4;\n\t"                                                                                        \
+        "add.u32 bl, %2, 4;\n\t"                                                                                        \
+        "mov.b64 da, {al, %3};\n\t"                                                                                     \
+        "mov.b64 db, {bl, %3};\n\t"                                                                                     \
+        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, p;\n\t"                                      \
+        "add.u32 al, %1, 6;\n\t"                                                                                        \
+        "add.u32 bl, %2, 6;\n\t"                                                                                        \
+        "mov.b64 da, {al, %3};\n\t"                                                                                     \
+        "mov.b64 db, {bl, %3};\n\t"                                                                                     \
+        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, p;\n\t"                                      \
+        "}\n" ::"r"(d_tmem),                                                                                            \
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first)                                           \
+        : "memory");                                                                                                    \
+  }
+B200Q_DEFINE_UMMA_KBLOCK(umma_kblock_i8, "1", "i8")
+B200Q_DEFINE_UMMA_KBLOCK(umma_kblock_i8_pair, "2", "i8")
+B200Q_DEFINE_UMMA_KBLOCK(umma_kblock_f16, "1", "f16")
+B200Q_DEFINE_UMMA_KBLOCK(umma_kblock_f16_pair, "2", "f16")
+#undef B200Q_DEFINE_UMMA_KBLOCK
+
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp reads lane (base_lane + i).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -238,7 +305,24 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Wait for this thread's TMEM loads; the loaded registers are named as in/out operands so that the compiler keeps
+// every use of them after the wait.
+__device__ __forceinline__ void tmem_ld_wait_16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
 
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of `row_bytes` (= the
