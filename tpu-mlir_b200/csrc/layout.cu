@@ -97,6 +97,73 @@ nchw_to_bordered_nhwc_fast_kernel(const T* __restrict__ x, uint8_t* __restrict__
   }
 }
 
+// Wider variant for C % 16 == 0 and H*W % 16 == 0: a thread reads 4 channels x 16 pixels as 16-byte runs, transposes
+// four 4x4 byte blocks in registers and parks them in the same XOR-swizzled tile; then every thread writes 16
+// channels of one pixel with one 16-byte store (4 pixels x 128 channels per warp instruction).
+template <typename T>
+struct Pix16;
+template <>
+struct Pix16<uint8_t> {
+  static __device__ __forceinline__ uint4 load(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+};
+template <>
+struct Pix16<float> {
+  static __device__ __forceinline__ uint4 load(const float* p) {
+    return make_uint4(Pix4<float>::load(p), Pix4<float>::load(p + 4), Pix4<float>::load(p + 8), Pix4<float>::load(p + 12));
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+nchw_to_bordered_nhwc_wide_kernel(const T* __restrict__ x, uint8_t* __restrict__ y, int C, int H, int W, int bh, int bw) {
+  __shared__ uint32_t tile[128][32];  // [pixel][4-channel word], word column XORed with (pixel >> 2) & 31
+  const int HW = H * W, Wp = W + 2 * bw, Hp = H + 2 * bh;
+  const int p0 = blockIdx.x * 128, c0 = blockIdx.y * 128, n = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    const int cg = threadIdx.x >> 3;  // channel group of 4 (word column), 0..31
+    const int pc = threadIdx.x & 7;   // 16-pixel chunk of the tile
+    const int c = c0 + 4 * cg, pix = p0 + 16 * pc;
+    uint4 ch[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ch[i] = make_uint4(0, 0, 0, 0);
+    if (pix < HW && c < C) {  // H*W % 16 == 0 and C % 4 == 0: a chunk / group is entirely inside or outside
+      const T* src = x + ((long long)n * C + c) * HW + pix;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ch[i] = Pix16<T>::load(src + (long long)i * HW);
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {  // pixels 4*q4 .. 4*q4+3 of the chunk
+      const uint32_t a = (&ch[0].x)[q4], b = (&ch[1].x)[q4], cc = (&ch[2].x)[q4], d = (&ch[3].x)[q4];
+      const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(cc, d, 0x5140);
+      const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(cc, d, 0x7362);
+      const int row = 16 * pc + 4 * q4;
+      const int col = cg ^ ((row >> 2) & 31);
+      tile[row + 0][col] = __byte_perm(t0, t1, 0x5410);
+      tile[row + 1][col] = __byte_perm(t0, t1, 0x7632);
+      tile[row + 2][col] = __byte_perm(t2, t3, 0x5410);
+      tile[row + 3][col] = __byte_perm(t2, t3, 0x7632);
+    }
+  }
+  __syncthreads();
+  uint8_t* yn = y + (long long)n * Hp * Wp * C;
+  const int k = lane & 7;  // 16-channel chunk of the pixel
+  const int c = c0 + 16 * k;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // the four pixel rows a warp reads at once lie in four different swizzle groups: no bank conflicts
+    const int r = warp * 16 + (lane >> 3) * 4 + i;
+    const int p = p0 + r;
+    if (p < HW && c < C) {
+      const int sw = (r >> 2) & 31;
+      const uint4 v = make_uint4(tile[r][(4 * k + 0) ^ sw], tile[r][(4 * k + 1) ^ sw], tile[r][(4 * k + 2) ^ sw],
+                                 tile[r][(4 * k + 3) ^ sw]);
+      const int h = p / W, w = p - h * W;
+      *reinterpret_cast<uint4*>(yn + ((long long)(h + bh) * Wp + (w + bw)) * C + c) = v;
+    }
+  }
+}
+
 // w[OC][IC][KH][KW] -> wr[OC][KH*KW][IC]  (K-major rows for the implicit GEMM: k = tap * IC + ic)
 template <typename T>
 __global__ void repack_weight_kernel(const T* __restrict__ w, uint8_t* __restrict__ wr, int OC, int IC, int KHW) {
@@ -154,6 +221,16 @@ int nchw_to_bordered_nhwc(const void* x, int x_is_f32, void* y, int N, int C, in
                           cudaStream_t s) {
   const long long HW = (long long)H * W;
   const bool aligned = (reinterpret_cast<uintptr_t>(x) % (x_is_f32 ? 16 : 4) == 0) && (reinterpret_cast<uintptr_t>(y) % 4 == 0);
+  if (HW % 16 == 0 && C % 16 == 0 && N <= 65535 && ceil_div(C, 128) <= 65535 &&
+      reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
+    dim3 grid(ceil_div(HW, 128), ceil_div(C, 128), N);
+    if (x_is_f32)
+      nchw_to_bordered_nhwc_wide_kernel<float><<<grid, 256, 0, s>>>((const float*)x, (uint8_t*)y, C, H, W, bh, bw);
+    else
+      nchw_to_bordered_nhwc_wide_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, C, H, W, bh, bw);
+    CUDA_TRY(cudaGetLastError());
+    return B200Q_OK;
+  }
   if (HW % 4 == 0 && C % 4 == 0 && aligned && N <= 65535 && ceil_div(C, 128) <= 65535) {
     dim3 grid(ceil_div(HW, 128), ceil_div(C, 128), N);
     if (x_is_f32)
