@@ -33,6 +33,10 @@ if ROOT not in sys.path:
 CFG = dict(N=32, C=256, H=56, W=56, OC=256, KH=3, KW=3)
 WORKLOAD = "tpu.Conv2D int8 NCHW n32 c256 56x56 oc256 k3 s1 p1 relu, per-channel QDM requant (BASELINE config 1)"
 OPS_PER_STEP = 2.0 * CFG["N"] * CFG["OC"] * CFG["H"] * CFG["W"] * CFG["C"] * CFG["KH"] * CFG["KW"]
+# DRAM traffic of one launch of the convolution kernel, from one ncu capture of this workload: 28.23 MB read (the
+# bordered image and the filters, once) + 0.03 MB written while the kernel runs (its 25.7 MB output is still in
+# L2 when it ends and is written back afterwards)
+CONV_DRAM_BYTES_PER_LAUNCH = 28_230_144 + 29_696
 METRIC, UNIT = "int8 conv TOPS", "TOPS"
 
 
@@ -472,7 +476,9 @@ def main():
                     config=dict(workload=WORKLOAD, l2="6 input/output sets used round-robin (308 MB > L2), no flush kernel",
                                 per_step_kernels=dict(layout_ms=float(np.mean(layout_ms)), conv_ms=k_ms)),
                     roofline=dict(bound="tensor", achieved=achieved, peak=int8_peak, unit="TOPS",
-                                  frac=achieved / int8_peak, traffic=None,
+                                  frac=achieved / int8_peak, traffic=CONV_DRAM_BYTES_PER_LAUNCH,
+                                  traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch "
+                                                 "(profiles/igemm_i8_conv_config1.md)",
                                   peak_basis=f"2 x {peaks['source']} dense bf16 ({peaks['bf16_tflops']} TFLOP/s); "
                                              "no measured INT8 figure exists"),
                     clocks=clocks, gpu_launches=gpu_launches)
