@@ -280,3 +280,14 @@ class ShardedCalibrator:
                                   threshold=table_threshold(k, sc.abs_max) if n in live else 1e-5)
         self.histograms = {n: views[n] for n in names}
         return out
+
+
+def dump_cali_table(path: str, results: Dict[str, TensorResult], *, order: Optional[List[str]] = None, mlir_file: str = "",
+                    num_samples: int = 0, tune_num: int = 0, histogram_bin_num: int = 2048) -> None:
+    """Write the results of ``ShardedCalibrator.run`` as a calibration table in the reference's text format
+    (kld_calibrator.py:804-884): tensors in graph order, ``threshold min max`` with seven decimals."""
+    from .cali_table import write_cali_table
+    names = order if order is not None else list(results.keys())
+    rows = [(n, float(results[n].threshold), float(results[n].min), float(results[n].max)) for n in names if n in results]
+    write_cali_table(path, rows, mlir_file=mlir_file, method="use_kl", histogram_bin_num=histogram_bin_num,
+                     num_samples=num_samples, tune_num=tune_num)

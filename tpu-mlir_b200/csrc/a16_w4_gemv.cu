@@ -85,6 +85,70 @@ __host__ __device__ inline GemvPlan gemv_plan(int M, int K, int group) {
   return p;
 }
 
+// Producer warp of both decode kernels: streams 16-row weight slabs (one bulk copy each) plus the slab's scales
+// and zero points into the shared-memory ring, running ahead of the consumer warps.
+__device__ __forceinline__ void gemv_producer(uint8_t* smem, const GemvPlan& P, uint32_t bar_base, volatile int* abort_flag,
+                                              const uint8_t* __restrict__ wq, const __nv_bfloat16* __restrict__ scale,
+                                              const uint8_t* __restrict__ zp, int N, int K, int num_slabs, int lane) {
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+  int stage = 0;
+  uint32_t phase = 0;
+  for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x) {
+    bool ok = true;
+    if (lane == 0) ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, WAIT_NS);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) break;
+    uint8_t* st = smem + (size_t)stage * P.stage_bytes;
+    const int n0 = slab * ROWS;
+    const int rows = min(ROWS, N - n0);
+    // scales and zero points of the slab are contiguous in global memory (rows are adjacent)
+    const int nmeta = rows * P.gpr;
+    const __nv_bfloat16* gs = scale + (size_t)n0 * P.gpr;
+    const uint8_t* gz = zp + (size_t)n0 * P.gpr;
+    __nv_bfloat16* ss = reinterpret_cast<__nv_bfloat16*>(st + P.scale_off);
+    uint8_t* sz = st + P.zp_off;
+    const bool meta_bulk = (nmeta % 16 == 0) && ((reinterpret_cast<uintptr_t>(gs) & 15) == 0) &&
+                           ((reinterpret_cast<uintptr_t>(gz) & 15) == 0);
+    if (lane == 0) {
+      ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)rows * (uint32_t)(K / 2) + (meta_bulk ? (uint32_t)nmeta * 3u : 0u));
+      ptx::bulk_load_1d(ptx::smem_u32(st), wq + (size_t)n0 * (K / 2), (uint32_t)rows * (uint32_t)(K / 2), full_bar(stage));
+      if (meta_bulk) {
+        ptx::bulk_load_1d(ptx::smem_u32(ss), gs, (uint32_t)nmeta * 2u, full_bar(stage));
+        ptx::bulk_load_1d(ptx::smem_u32(sz), gz, (uint32_t)nmeta, full_bar(stage));
+      }
+    }
+    if (!meta_bulk) {  // ragged tail or unaligned metadata: plain loads, all issued before the stores
+      for (int i0 = 0; i0 < nmeta; i0 += 32 * 8) {
+        __nv_bfloat16 tv[8];
+        uint8_t tz[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = i0 + j * 32 + lane;
+          if (i < nmeta) {
+            tv[j] = gs[i];
+            tz[j] = gz[i];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = i0 + j * 32 + lane;
+          if (i < nmeta) {
+            ss[i] = tv[j];
+            sz[i] = tz[j];
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(full_bar(stage));  // second arrival of the phase: metadata is in place
+    if (++stage == P.stages) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
                    const __nv_bfloat16* __restrict__ scale, const uint8_t* __restrict__ zp,
@@ -112,62 +176,7 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
   __syncthreads();
 
   if (warp == CWARPS) {
-    // ------------------------------------------------------------ producer warp
-    int stage = 0;
-    uint32_t phase = 0;
-    for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x) {
-      bool ok = true;
-      if (lane == 0) ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, WAIT_NS);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      uint8_t* st = smem + (size_t)stage * P.stage_bytes;
-      const int n0 = slab * ROWS;
-      const int rows = min(ROWS, N - n0);
-      // scales and zero points of the slab are contiguous in global memory (rows are adjacent)
-      const int nmeta = rows * P.gpr;
-      const __nv_bfloat16* gs = scale + (size_t)n0 * P.gpr;
-      const uint8_t* gz = zp + (size_t)n0 * P.gpr;
-      __nv_bfloat16* ss = reinterpret_cast<__nv_bfloat16*>(st + P.scale_off);
-      uint8_t* sz = st + P.zp_off;
-      const bool meta_bulk = (nmeta % 16 == 0) && ((reinterpret_cast<uintptr_t>(gs) & 15) == 0) &&
-                             ((reinterpret_cast<uintptr_t>(gz) & 15) == 0);
-      if (lane == 0) {
-        ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)rows * (uint32_t)(K / 2) + (meta_bulk ? (uint32_t)nmeta * 3u : 0u));
-        ptx::bulk_load_1d(ptx::smem_u32(st), wq + (size_t)n0 * (K / 2), (uint32_t)rows * (uint32_t)(K / 2), full_bar(stage));
-        if (meta_bulk) {
-          ptx::bulk_load_1d(ptx::smem_u32(ss), gs, (uint32_t)nmeta * 2u, full_bar(stage));
-          ptx::bulk_load_1d(ptx::smem_u32(sz), gz, (uint32_t)nmeta, full_bar(stage));
-        }
-      }
-      if (!meta_bulk) {  // ragged tail or unaligned metadata: plain loads, all issued before the stores
-        for (int i0 = 0; i0 < nmeta; i0 += 32 * 8) {
-          __nv_bfloat16 tv[8];
-          uint8_t tz[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int i = i0 + j * 32 + lane;
-            if (i < nmeta) {
-              tv[j] = gs[i];
-              tz[j] = gz[i];
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int i = i0 + j * 32 + lane;
-            if (i < nmeta) {
-              ss[i] = tv[j];
-              sz[i] = tz[j];
-            }
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(full_bar(stage));  // second arrival of the phase: metadata is in place
-      if (++stage == P.stages) {
-        stage = 0;
-        phase ^= 1u;
-      }
-    }
+    gemv_producer(smem, P, bar_base, abort_flag, wq, scale, zp, N, K, num_slabs, lane);
   } else {
     // ------------------------------------------------------------ consumer warps
     uint8_t* xs = smem + P.x_off;
@@ -296,6 +305,157 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
   if (tid == 0 && *abort_flag != 0 && status != nullptr) atomicCAS(status, 0, *abort_flag);
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// M <= 2: CUDA-core form.  One or two tokens waste 7/8 of every MMA above, and mma.sync is the slow legacy tensor path
+// on sm_100, so for these shapes the dot products run as fp32 FMAs.  A lane owns one fixed 32-k slice of K for the
+// whole kernel and keeps its activations in registers (fp32, in nibble order); Tp = round32(K / 32) lanes cover one
+// weight row, 512 / Tp rows are in flight at a time.  Per row a lane reads 16 bytes of weights, turns 32 nibbles into
+// 128 + q (bf16 bit trick, then a shift / mask to fp32) and accumulates (128 + q) * x; the zero point comes off as
+// (128 + zp) * sum(x over the slice), then the group scale multiplies the fp32 partial sum.
+template <int M_T>
+__global__ void __launch_bounds__(THREADS, 1)
+a16_w4_gemv_fma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
+                       const __nv_bfloat16* __restrict__ scale, const uint8_t* __restrict__ zp,
+                       const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int N, int K, int group,
+                       int* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const GemvPlan P = gemv_plan(M_T, K, group);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t bar_base = ptx::smem_u32(smem + P.bar_off);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P.bar_off + 16 * MAX_STAGES);
+  const int num_slabs = (N + ROWS - 1) / ROWS;
+
+  if (tid == 0) {
+    for (int s = 0; s < P.stages; ++s) {
+      ptx::mbar_init(full_bar(s), 2);
+      ptx::mbar_init(empty_bar(s), CWARPS);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+  }
+  __syncthreads();
+
+  if (warp == CWARPS) {
+    gemv_producer(smem, P, bar_base, abort_flag, wq, scale, zp, N, K, num_slabs, lane);
+  } else {
+    const int T = K / 32;                 // 32-k slices per row
+    const int wpr = (T + 31) / 32;        // warps per row
+    const int rows_par = CWARPS / wpr;    // rows in flight
+    const int row_sub = warp / wpr, warp_in_row = warp - row_sub * wpr;
+    const int slice = warp_in_row * 32 + lane;
+    const bool lane_active = row_sub < rows_par && slice < T;
+    const int grp = (slice * 32) / group;
+    // this lane's activations, fp32, in the order the nibble extraction yields: k0,k4,k1,k5,k2,k6,k3,k7 per 8
+    float xr[M_T][32];
+    float xsum[M_T];
+#pragma unroll
+    for (int m = 0; m < M_T; ++m) {
+      xsum[m] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) xr[m][j] = 0.f;
+      if (lane_active) {
+        const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)slice * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {  // 8 bf16 per 16 bytes
+          const uint4 v = xp[q];
+          const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            f[2 * j] = __uint_as_float(wv[j] << 16);
+            f[2 * j + 1] = __uint_as_float(wv[j] & 0xffff0000u);
+          }
+          const int perm[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            xr[m][8 * q + j] = f[perm[j]];
+            xsum[m] += f[j];
+          }
+        }
+      }
+    }
+    const int iters = (ROWS + rows_par - 1) / rows_par;
+    float* red = reinterpret_cast<float*>(smem + P.red_off);
+    int stage = 0;
+    uint32_t phase = 0;
+    int it_slab = 0;
+    for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x, ++it_slab) {
+      if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, 2, WAIT_NS)) break;
+      const uint8_t* st = smem + (size_t)stage * P.stage_bytes;
+      const int n0 = slab * ROWS;
+      const int rows = min(ROWS, N - n0);
+      float* rbuf = red + (size_t)(it_slab & 1) * (M_T * ROWS * CWARPS);
+      for (int it = 0; it < iters; ++it) {
+        const int r = it * rows_par + row_sub;
+        const bool valid = lane_active && r < rows;
+        float part[M_T];
+#pragma unroll
+        for (int m = 0; m < M_T; ++m) part[m] = 0.f;
+        if (valid) {
+          const uint4 wv4 = *reinterpret_cast<const uint4*>(st + (size_t)r * P.w_pitch + (size_t)slice * 16);
+          const float sc = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(st + P.scale_off)[r * P.gpr + grp]);
+          const float zoff = 128.f + (float)(st + P.zp_off)[r * P.gpr + grp];
+          const uint32_t ww[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
+          float acc[M_T][4];
+#pragma unroll
+          for (int m = 0; m < M_T; ++m)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[m][q] = 0.f;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t w = ww[q];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t pq = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // bf16x2 {128 + q_j, 128 + q_(j+4)}
+              const float lo = __uint_as_float(pq << 16), hi = __uint_as_float(pq & 0xffff0000u);
+#pragma unroll
+              for (int m = 0; m < M_T; ++m) {
+                acc[m][q] = fmaf(lo, xr[m][8 * q + 2 * j], acc[m][q]);
+                acc[m][q] = fmaf(hi, xr[m][8 * q + 2 * j + 1], acc[m][q]);
+              }
+            }
+          }
+#pragma unroll
+          for (int m = 0; m < M_T; ++m) {
+            const float raw = (acc[m][0] + acc[m][1]) + (acc[m][2] + acc[m][3]);
+            part[m] = fmaf(-zoff, xsum[m], raw) * sc;
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < M_T; ++m) {
+          float v = part[m];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          if (lane == 0 && row_sub < rows_par && r < ROWS) rbuf[(m * ROWS + r) * CWARPS + warp_in_row] = v;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(empty_bar(stage));  // this warp no longer reads the stage
+      if (++stage == P.stages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory");
+      if (tid < ROWS * M_T) {
+        const int row = tid / M_T, m = tid - row * M_T;
+        const int n = n0 + row;
+        if (n < N) {
+          float v = 0.f;
+          for (int w = 0; w < wpr; ++w) v += rbuf[(m * ROWS + row) * CWARPS + w];
+          if (bias) v += bias[n];
+          y[(size_t)m * N + n] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0 && status != nullptr) atomicCAS(status, 0, *abort_flag);
+}
+
 }  // namespace
 
 int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why) {
@@ -316,13 +476,23 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
   if ((reinterpret_cast<uintptr_t>(wq) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
     return set_error(B200Q_ERR_INVALID, "a16 w4 gemv: weights and activations must be 16-byte aligned");
   const GemvPlan P = gemv_plan(M, K, group);
-  auto kfn = a16_w4_gemv_kernel;
-  CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, P.total));
   int dev = 0, sms = 0;
   CUDA_TRY(cudaGetDevice(&dev));
   CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int slabs = (N + ROWS - 1) / ROWS;
   const int blocks = slabs < sms ? slabs : sms;
+  if (M <= 2 && K <= 32 * 32 * CWARPS && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (K * 2) % 16 == 0) {
+    // one or two tokens: fp32 FMAs on the CUDA cores (a lane per 32-k slice, at most 512 slices per row)
+    auto ffn = M == 1 ? a16_w4_gemv_fma_kernel<1> : a16_w4_gemv_fma_kernel<2>;
+    CUDA_TRY(cudaFuncSetAttribute(ffn, cudaFuncAttributeMaxDynamicSharedMemorySize, P.total));
+    ffn<<<blocks, THREADS, P.total, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
+                                              static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp),
+                                              bias, static_cast<__nv_bfloat16*>(y), N, K, group, status);
+    CUDA_TRY(cudaGetLastError());
+    return B200Q_OK;
+  }
+  auto kfn = a16_w4_gemv_kernel;
+  CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, P.total));
   kfn<<<blocks, THREADS, P.total, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
                                             static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp),
                                             bias, static_cast<__nv_bfloat16*>(y), M, N, K, group, status);
