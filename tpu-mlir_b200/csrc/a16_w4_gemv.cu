@@ -38,6 +38,20 @@ __device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
   return d;
 }
 
+// acc += a.lo * b.lo + a.hi * b.hi for packed bf16 pairs, fp32 accumulate (mixed-precision FMA: the bf16 halves are
+// read in place, products are exact, one rounding per addition)
+__device__ __forceinline__ void fma2_f32_bf16(float& acc, uint32_t a, uint32_t b) {
+  asm("{\n\t"
+      ".reg .b16 al, ah, bl, bh;\n\t"
+      "mov.b32 {al, ah}, %1;\n\t"
+      "mov.b32 {bl, bh}, %2;\n\t"
+      "fma.rn.f32.bf16 %0, al, bl, %0;\n\t"
+      "fma.rn.f32.bf16 %0, ah, bh, %0;\n\t"
+      "}"
+      : "+f"(acc)
+      : "r"(a), "r"(b));
+}
+
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -66,14 +80,14 @@ struct GemvPlan {
   int x_off, red_off, bar_off, total;
   int stages;
 };
-__host__ __device__ inline GemvPlan gemv_plan(int M, int K, int group) {
+__host__ __device__ inline GemvPlan gemv_plan(int M, int K, int group, bool x_in_smem = true) {
   GemvPlan p;
   p.w_pitch = K / 2;  // dense: the slab is one contiguous piece of global memory and arrives as ONE bulk copy
   p.gpr = K / group;
   p.scale_off = ROWS * p.w_pitch;
   p.zp_off = p.scale_off + ((ROWS * p.gpr * 2 + 15) & ~15);
   p.stage_bytes = (p.zp_off + ROWS * p.gpr + 127) & ~127;
-  const int x_bytes = (M * (2 * K + 16) + 127) & ~127;
+  const int x_bytes = x_in_smem ? ((M * (2 * K + 16) + 127) & ~127) : 0;  // the CUDA-core kernel keeps x in registers
   const int red_bytes = 2 * CWARPS * ROWS * 8 * 4;
   const int fixed = x_bytes + red_bytes + 128;
   int st = (220 * 1024 - fixed) / p.stage_bytes;
@@ -309,18 +323,18 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
 // ---------------------------------------------------------------------------------------------------------------
 // M <= 2: CUDA-core form.  One or two tokens waste 7/8 of every MMA above, and mma.sync is the slow legacy tensor path
 // on sm_100, so for these shapes the dot products run as fp32 FMAs.  A lane owns one fixed 32-k slice of K for the
-// whole kernel and keeps its activations in registers (fp32, in nibble order); Tp = round32(K / 32) lanes cover one
-// weight row, 512 / Tp rows are in flight at a time.  Per row a lane reads 16 bytes of weights, turns 32 nibbles into
-// 128 + q (bf16 bit trick, then a shift / mask to fp32) and accumulates (128 + q) * x; the zero point comes off as
+// whole kernel and keeps its activations in registers (packed bf16, in nibble-pair order).  A lane owns SL fixed 32-k
+// slices; round32(K / 32 / SL) lanes cover one weight row and 512 / that many rows are in flight at a time.  Per row a lane reads 16 bytes of weights, turns 32 nibbles into
+// 128 + q (bf16 bit trick) and accumulates (128 + q) * x with mixed-precision FMAs (bf16 x bf16 + fp32); the zero point comes off as
 // (128 + zp) * sum(x over the slice), then the group scale multiplies the fp32 partial sum.
-template <int M_T>
+template <int M_T, int SL>
 __global__ void __launch_bounds__(THREADS, 1)
 a16_w4_gemv_fma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
                        const __nv_bfloat16* __restrict__ scale, const uint8_t* __restrict__ zp,
                        const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int N, int K, int group,
                        int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const GemvPlan P = gemv_plan(M_T, K, group);
+  const GemvPlan P = gemv_plan(M_T, K, group, false);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t bar_base = ptx::smem_u32(smem + P.bar_off);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -342,38 +356,36 @@ a16_w4_gemv_fma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __res
   if (warp == CWARPS) {
     gemv_producer(smem, P, bar_base, abort_flag, wq, scale, zp, N, K, num_slabs, lane);
   } else {
-    const int T = K / 32;                 // 32-k slices per row
-    const int wpr = (T + 31) / 32;        // warps per row
-    const int rows_par = CWARPS / wpr;    // rows in flight
+    const int T = K / 32;                          // 32-k slices per row
+    const int wpr = (T + 32 * SL - 1) / (32 * SL);  // warps per row (a lane owns SL slices, 32 * wpr apart)
+    const int rows_par = CWARPS / wpr;             // rows in flight
     const int row_sub = warp / wpr, warp_in_row = warp - row_sub * wpr;
-    const int slice = warp_in_row * 32 + lane;
-    const bool lane_active = row_sub < rows_par && slice < T;
-    const int grp = (slice * 32) / group;
-    // this lane's activations, fp32, in the order the nibble extraction yields: k0,k4,k1,k5,k2,k6,k3,k7 per 8
-    float xr[M_T][32];
-    float xsum[M_T];
+    const int lane_slot = warp_in_row * 32 + lane;
+    const int slot_stride = 32 * wpr;
+    const bool warp_active = row_sub < rows_par;
+    // this lane's activations as packed bf16 pairs (x_j, x_j+4) per 8 values: the pairing the nibble extraction yields
+    uint32_t xw[M_T][SL][16];
+    float xsum[M_T][SL];
 #pragma unroll
     for (int m = 0; m < M_T; ++m) {
-      xsum[m] = 0.f;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) xr[m][j] = 0.f;
-      if (lane_active) {
-        const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)slice * 32);
+      for (int sl = 0; sl < SL; ++sl) {
+        const int slice = sl * slot_stride + lane_slot;
+        xsum[m][sl] = 0.f;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {  // 8 bf16 per 16 bytes
-          const uint4 v = xp[q];
-          const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-          float f[8];
+        for (int j = 0; j < 16; ++j) xw[m][sl][j] = 0u;
+        if (warp_active && slice < T) {
+          const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)slice * 32);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            f[2 * j] = __uint_as_float(wv[j] << 16);
-            f[2 * j + 1] = __uint_as_float(wv[j] & 0xffff0000u);
-          }
-          const int perm[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+          for (int q = 0; q < 4; ++q) {  // 8 bf16 per 16 bytes
+            const uint4 v = xp[q];
+            xw[m][sl][4 * q + 0] = __byte_perm(v.x, v.z, 0x5410);  // (x0, x4)
+            xw[m][sl][4 * q + 1] = __byte_perm(v.x, v.z, 0x7632);  // (x1, x5)
+            xw[m][sl][4 * q + 2] = __byte_perm(v.y, v.w, 0x5410);  // (x2, x6)
+            xw[m][sl][4 * q + 3] = __byte_perm(v.y, v.w, 0x7632);  // (x3, x7)
+            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            xr[m][8 * q + j] = f[perm[j]];
-            xsum[m] += f[j];
+            for (int j = 0; j < 4; ++j) xsum[m][sl] += __uint_as_float(wv[j] << 16) + __uint_as_float(wv[j] & 0xffff0000u);
           }
         }
       }
@@ -386,43 +398,46 @@ a16_w4_gemv_fma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __res
     for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x, ++it_slab) {
       if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, 2, WAIT_NS)) break;
       const uint8_t* st = smem + (size_t)stage * P.stage_bytes;
+      const __nv_bfloat16* st_scale = reinterpret_cast<const __nv_bfloat16*>(st + P.scale_off);
+      const uint8_t* st_zp = st + P.zp_off;
       const int n0 = slab * ROWS;
       const int rows = min(ROWS, N - n0);
       float* rbuf = red + (size_t)(it_slab & 1) * (M_T * ROWS * CWARPS);
       for (int it = 0; it < iters; ++it) {
         const int r = it * rows_par + row_sub;
-        const bool valid = lane_active && r < rows;
+        const bool row_ok = warp_active && r < rows;
         float part[M_T];
 #pragma unroll
         for (int m = 0; m < M_T; ++m) part[m] = 0.f;
-        if (valid) {
-          const uint4 wv4 = *reinterpret_cast<const uint4*>(st + (size_t)r * P.w_pitch + (size_t)slice * 16);
-          const float sc = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(st + P.scale_off)[r * P.gpr + grp]);
-          const float zoff = 128.f + (float)(st + P.zp_off)[r * P.gpr + grp];
-          const uint32_t ww[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
-          float acc[M_T][4];
 #pragma unroll
-          for (int m = 0; m < M_T; ++m)
+        for (int sl = 0; sl < SL; ++sl) {
+          const int slice = sl * slot_stride + lane_slot;
+          if (row_ok && slice < T) {
+            const uint4 wv4 = *reinterpret_cast<const uint4*>(st + (size_t)r * P.w_pitch + (size_t)slice * 16);
+            const int gi = r * P.gpr + (slice * 32) / group;
+            const float sc = __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(st_scale)[gi] << 16);
+            const float zoff = __uint_as_float(0x43000000u | ((uint32_t)st_zp[gi] << 16));  // 128 + zp, zp <= 127
+            const uint32_t ww[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
+            float acc[M_T][4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) acc[m][q] = 0.f;
+            for (int m = 0; m < M_T; ++m)
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint32_t w = ww[q];
+              for (int q = 0; q < 4; ++q) acc[m][q] = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t pq = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // bf16x2 {128 + q_j, 128 + q_(j+4)}
-              const float lo = __uint_as_float(pq << 16), hi = __uint_as_float(pq & 0xffff0000u);
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t w = ww[q];
 #pragma unroll
-              for (int m = 0; m < M_T; ++m) {
-                acc[m][q] = fmaf(lo, xr[m][8 * q + 2 * j], acc[m][q]);
-                acc[m][q] = fmaf(hi, xr[m][8 * q + 2 * j + 1], acc[m][q]);
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t pq = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // bf16x2 {128 + q_j, 128 + q_(j+4)}
+#pragma unroll
+                for (int m = 0; m < M_T; ++m) fma2_f32_bf16(acc[m][q], pq, xw[m][sl][4 * q + j]);
               }
             }
-          }
 #pragma unroll
-          for (int m = 0; m < M_T; ++m) {
-            const float raw = (acc[m][0] + acc[m][1]) + (acc[m][2] + acc[m][3]);
-            part[m] = fmaf(-zoff, xsum[m], raw) * sc;
+            for (int m = 0; m < M_T; ++m) {
+              const float raw = (acc[m][0] + acc[m][1]) + (acc[m][2] + acc[m][3]);
+              part[m] = fmaf(fmaf(-zoff, xsum[m][sl], raw), sc, part[m]);
+            }
           }
         }
 #pragma unroll
@@ -430,7 +445,13 @@ a16_w4_gemv_fma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __res
           float v = part[m];
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-          if (lane == 0 && row_sub < rows_par && r < ROWS) rbuf[(m * ROWS + r) * CWARPS + warp_in_row] = v;
+          if (lane == 0 && warp_active && r < ROWS) {
+            if (wpr == 1) {  // the warp holds the whole row: no cross-warp sum
+              if (r < rows) y[(size_t)m * N + n0 + r] = __float2bfloat16_rn(bias ? v + bias[n0 + r] : v);
+            } else {
+              rbuf[(m * ROWS + r) * CWARPS + warp_in_row] = v;
+            }
+          }
         }
       }
       __syncwarp();
@@ -439,15 +460,17 @@ a16_w4_gemv_fma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __res
         stage = 0;
         phase ^= 1u;
       }
-      asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory");
-      if (tid < ROWS * M_T) {
-        const int row = tid / M_T, m = tid - row * M_T;
-        const int n = n0 + row;
-        if (n < N) {
-          float v = 0.f;
-          for (int w = 0; w < wpr; ++w) v += rbuf[(m * ROWS + row) * CWARPS + w];
-          if (bias) v += bias[n];
-          y[(size_t)m * N + n] = __float2bfloat16_rn(v);
+      if (wpr > 1) {
+        asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory");
+        if (tid < ROWS * M_T) {
+          const int row = tid / M_T, m = tid - row * M_T;
+          const int n = n0 + row;
+          if (n < N) {
+            float v = 0.f;
+            for (int w = 0; w < wpr; ++w) v += rbuf[(m * ROWS + row) * CWARPS + w];
+            if (bias) v += bias[n];
+            y[(size_t)m * N + n] = __float2bfloat16_rn(v);
+          }
         }
       }
     }
@@ -458,13 +481,16 @@ a16_w4_gemv_fma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __res
 
 }  // namespace
 
+// one or two tokens: fp32 FMAs on the CUDA cores (a lane per 32-k slice, at most 512 slices per row)
+static bool gemv_uses_fma(int M, int K) { return M <= 2 && K <= 32 * 32 * CWARPS; }
+
 int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why) {
   const char* w = nullptr;
   if (M < 1 || M > MAX_M) w = "M must be in [1, 8]";
   else if (K % CHUNK_K != 0) w = "K must be a multiple of 64";
   else if (group < CHUNK_K || group % CHUNK_K != 0 || K % group != 0) w = "group size must be a multiple of 64 dividing K";
   else if (N < 1) w = "empty N";
-  else if (gemv_plan(M, K, group).stages < 2) w = "two 16-row weight slabs plus the activations do not fit in shared memory";
+  else if (gemv_plan(M, K, group, !gemv_uses_fma(M, K)).stages < 2) w = "two 16-row weight slabs plus the activations do not fit in shared memory";
   if (why) *why = w;
   return w == nullptr;
 }
@@ -475,15 +501,19 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
   if (!a16_w4_gemv_supported(M, N, K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: %s", why);
   if ((reinterpret_cast<uintptr_t>(wq) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
     return set_error(B200Q_ERR_INVALID, "a16 w4 gemv: weights and activations must be 16-byte aligned");
-  const GemvPlan P = gemv_plan(M, K, group);
+  const bool fma = gemv_uses_fma(M, K) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  const GemvPlan P = gemv_plan(M, K, group, !fma);
+  if (P.stages < 2) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: the weight slabs do not fit in shared memory");
   int dev = 0, sms = 0;
   CUDA_TRY(cudaGetDevice(&dev));
   CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int slabs = (N + ROWS - 1) / ROWS;
   const int blocks = slabs < sms ? slabs : sms;
-  if (M <= 2 && K <= 32 * 32 * CWARPS && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (K * 2) % 16 == 0) {
-    // one or two tokens: fp32 FMAs on the CUDA cores (a lane per 32-k slice, at most 512 slices per row)
-    auto ffn = M == 1 ? a16_w4_gemv_fma_kernel<1> : a16_w4_gemv_fma_kernel<2>;
+  if (fma) {
+    // one token and K <= 4096: a lane owns four slices, one warp covers a row and stores its result directly
+    // one token: two slices per lane (fewer warps per row to sum over); four would not leave registers to schedule with
+    auto ffn = M == 1 ? (K <= 8192 ? a16_w4_gemv_fma_kernel<1, 2> : a16_w4_gemv_fma_kernel<1, 1>)
+                      : a16_w4_gemv_fma_kernel<2, 1>;
     CUDA_TRY(cudaFuncSetAttribute(ffn, cudaFuncAttributeMaxDynamicSharedMemorySize, P.total));
     ffn<<<blocks, THREADS, P.total, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
                                               static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp),
@@ -501,3 +531,4 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
 }
 
 }  // namespace b200q
+

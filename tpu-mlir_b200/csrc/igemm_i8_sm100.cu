@@ -288,6 +288,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       case B200Q_DT_U16: sat_lo = 0; sat_hi = 65535; break;
       default: sat_lo = -2147483647 - 1; sat_hi = 2147483647; break;
     }
+    const bool relu_after = e.relu == B200Q_RELU_AFTER_REQUANT;
     const int32_t sat_lo2 = max(sat_lo, floor_post);  // clamp(max(v, f), lo, hi) == clamp(v, max(lo, f), hi) for f <= hi
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -439,7 +440,19 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         int32_t q[CH];
         const int form = kFastCompiled ? chunk_form[cbase >> 5] : 3;
-        if (kFastCompiled && form == 0) {
+        if (kFastCompiled && form == 0 && DIALECT == B200Q_RQ_QDM && relu_after) {
+          // With the ReLU after the requantisation every negative result ends at the zero point, and half-away
+          // differs from half-up only for negative values (a tie at -0.5 gives -1 or 0, both clamp): the sign term of
+          // the second rounding can go.
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            const int4 cp = chan[cbase + j];  // {m, C_lo, C_hi, shift}
+            const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
+            const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
+            const int32_t v = ((int32_t)(x >> 31) + chan_k[cbase + j]) >> cp.w;
+            q[j] = min(max(v, sat_lo2), sat_hi);
+          }
+        } else if (kFastCompiled && form == 0) {
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
             const int4 cp = chan[cbase + j];  // {m, C_lo, C_hi, shift}: one broadcast 16-byte shared load
