@@ -27,6 +27,22 @@ def test_add(n):
         assert np.array_equal(out.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("a_unsigned,b_unsigned", [(True, True), (True, False), (False, True), (False, False)])
+def test_add_wide_kernel_all_sign_combinations(a_unsigned, b_unsigned):
+    """n % 16 == 0 with 8-bit multipliers takes the 16-elements-per-thread kernel (32-bit arithmetic)."""
+    n = 16 * 4099
+    rng = np.random.default_rng(11)
+    a = rng.integers(0, 256, n, dtype=np.uint8) if a_unsigned else rng.integers(-128, 128, n, dtype=np.int8)
+    b = rng.integers(0, 256, n, dtype=np.uint8) if b_unsigned else rng.integers(-128, 128, n, dtype=np.int8)
+    a_d, b_d = dev(a), dev(b)
+    for (m0, s0, m1, s1, relu, odt) in [(127, 1, -128, 31, True, L.DT_I8), (64, 6, 127, 7, False, L.DT_I8),
+                                        (99, 5, 17, 3, True, L.DT_U8), (1, 1, 1, 1, False, L.DT_U8)]:
+        want = oracle.add_int8(a, b, m0, s0, m1, s1, do_relu=relu, out_dt=odt)
+        out = empty_dev((n,), odt)
+        L.check(lib().b200q_add_i8_dev(ptr(a_d), dt_of(a), ptr(b_d), dt_of(b), n, m0, s0, m1, s1, int(relu), odt, ptr(out), None))
+        assert np.array_equal(out.cpu().numpy(), want), (m0, s0, m1, s1, relu, odt)
+
+
 def test_pool():
     rng = np.random.default_rng(4)
     x = rng.integers(0, 256, (3, 5, 17, 14), dtype=np.uint8)

@@ -77,6 +77,34 @@ __global__ void add_i8x4_kernel(const uint32_t* __restrict__ a, int a_unsigned, 
   out[i] = o;
 }
 
+// 16 elements per thread (one 16-byte access per operand) for 8-bit tensors with multipliers / shifts in the range the
+// lowering emits (|m| < 2^23, shift in [1, 31]): x*m + 2^(s-1) fits 32 bits, so the half-up shift is one
+// multiply-add and one arithmetic shift per input (MathUtils.cpp:474-514 RightShiftRound, ROUNDING_HALF_UP).
+template <bool A_UNS, bool B_UNS>
+__global__ void __launch_bounds__(256)
+add_i8x16_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, long long n16, int m0, int s0, int m1, int s1,
+                 int lo, int hi, uint4* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n16) return;
+  const uint4 va = a[i], vb = b[i];
+  const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+  const int32_t h0 = 1 << (s0 - 1), h1 = 1 << (s1 - 1);
+  uint32_t o[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    uint32_t r = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int32_t xa = A_UNS ? (int32_t)((wa[w] >> (8 * j)) & 0xff) : (int32_t)(int8_t)(wa[w] >> (8 * j));
+      const int32_t xb = B_UNS ? (int32_t)((wb[w] >> (8 * j)) & 0xff) : (int32_t)(int8_t)(wb[w] >> (8 * j));
+      const int32_t v = ((xa * m0 + h0) >> s0) + ((xb * m1 + h1) >> s1);
+      r |= ((uint32_t)min(max(v, lo), hi) & 0xffu) << (8 * j);
+    }
+    o[w] = r;
+  }
+  out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 __global__ void pool2d_i8_kernel(const void* __restrict__ x, int dt, int NC, int ih, int iw, int kh, int kw, int sh,
                                  int sw, int pht, int pwl, int oh, int ow, int mode, int multi, int rshift, int do_relu,
                                  int out_dt, void* __restrict__ out) {
@@ -167,7 +195,21 @@ int add_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n,
   if (n == 0) return B200Q_OK;
   const bool q8 = a_dt <= B200Q_DT_U8 && b_dt <= B200Q_DT_U8 && out_dt <= B200Q_DT_U8;
   const bool al = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 3) == 0;
-  if (q8 && al && n % 4 == 0) {
+  const bool al16 = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const bool small = m0 > -(1 << 23) && m0 < (1 << 23) && m1 > -(1 << 23) && m1 < (1 << 23) && s0 >= 1 && s0 <= 31 &&
+                     s1 >= 1 && s1 <= 31;
+  if (q8 && al16 && small && n % 16 == 0) {
+    // output range with the ReLU floor folded in
+    const int lo = out_dt == B200Q_DT_U8 ? 0 : (do_relu ? 0 : -128), hi = out_dt == B200Q_DT_U8 ? 255 : 127;
+    const long long n16 = n / 16;
+    const bool au = a_dt == B200Q_DT_U8, bu = b_dt == B200Q_DT_U8;
+    const uint4 *pa = (const uint4*)a, *pb = (const uint4*)b;
+    uint4* po = (uint4*)out;
+    if (au && bu) add_i8x16_kernel<true, true><<<nblk(n16, 256), 256, 0, s>>>(pa, pb, n16, m0, s0, m1, s1, lo, hi, po);
+    else if (au) add_i8x16_kernel<true, false><<<nblk(n16, 256), 256, 0, s>>>(pa, pb, n16, m0, s0, m1, s1, lo, hi, po);
+    else if (bu) add_i8x16_kernel<false, true><<<nblk(n16, 256), 256, 0, s>>>(pa, pb, n16, m0, s0, m1, s1, lo, hi, po);
+    else add_i8x16_kernel<false, false><<<nblk(n16, 256), 256, 0, s>>>(pa, pb, n16, m0, s0, m1, s1, lo, hi, po);
+  } else if (q8 && al && n % 4 == 0) {
     add_i8x4_kernel<<<nblk(n / 4, 256), 256, 0, s>>>((const uint32_t*)a, a_dt == B200Q_DT_U8, (const uint32_t*)b,
                                                      b_dt == B200Q_DT_U8, n / 4, m0, s0, m1, s1, do_relu, out_dt, (uint32_t*)out);
   } else {

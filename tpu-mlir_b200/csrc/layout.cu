@@ -164,6 +164,30 @@ nchw_to_bordered_nhwc_wide_kernel(const T* __restrict__ x, uint8_t* __restrict__
   }
 }
 
+// Small images with any H*W (7x7 and the like), C % 64 == 0: a block takes 64 channels of one image, which are one
+// contiguous run of 64*H*W source elements, parks them as bytes in shared memory with 4-element accesses, and writes
+// every pixel's 64 channels as 16 four-byte words (64 contiguous bytes per pixel).
+template <typename T>
+__global__ void __launch_bounds__(256)
+nchw_to_bordered_nhwc_small_kernel(const T* __restrict__ x, uint8_t* __restrict__ y, int C, int H, int W, int bh, int bw) {
+  extern __shared__ __align__(16) uint8_t stile[];  // [64][H*W]
+  const int HW = H * W, Wp = W + 2 * bw, Hp = H + 2 * bh;
+  const int c0 = blockIdx.x * 64, n = blockIdx.y;
+  const T* src = x + ((long long)n * C + c0) * HW;
+  const int words = 16 * HW;  // 64*HW bytes
+  for (int i = threadIdx.x; i < words; i += 256)
+    reinterpret_cast<uint32_t*>(stile)[i] = Pix4<T>::load(src + 4 * i);
+  __syncthreads();
+  uint8_t* yn = y + (long long)n * Hp * Wp * C + c0;
+  for (int i = threadIdx.x; i < words; i += 256) {
+    const int p = i >> 4, wq = i & 15;
+    const uint8_t* t = stile + (4 * wq) * HW + p;
+    const uint32_t v = (uint32_t)t[0] | ((uint32_t)t[HW] << 8) | ((uint32_t)t[2 * HW] << 16) | ((uint32_t)t[3 * HW] << 24);
+    const int h = p / W, w = p - h * W;
+    *reinterpret_cast<uint32_t*>(yn + ((long long)(h + bh) * Wp + (w + bw)) * C + 4 * wq) = v;
+  }
+}
+
 // w[OC][IC][KH][KW] -> wr[OC][KH*KW][IC]  (K-major rows for the implicit GEMM: k = tap * IC + ic)
 template <typename T>
 __global__ void repack_weight_kernel(const T* __restrict__ w, uint8_t* __restrict__ wr, int OC, int IC, int KHW) {
@@ -228,6 +252,17 @@ int nchw_to_bordered_nhwc(const void* x, int x_is_f32, void* y, int N, int C, in
       nchw_to_bordered_nhwc_wide_kernel<float><<<grid, 256, 0, s>>>((const float*)x, (uint8_t*)y, C, H, W, bh, bw);
     else
       nchw_to_bordered_nhwc_wide_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, C, H, W, bh, bw);
+    CUDA_TRY(cudaGetLastError());
+    return B200Q_OK;
+  }
+  if (HW % 16 != 0 && C % 64 == 0 && HW * 64 <= 48 * 1024 && N <= 65535 && aligned) {
+    // (64 channels of one image start 64 elements-aligned: every 4-element load above is aligned)
+    dim3 grid(C / 64, N);
+    const size_t smem = (size_t)HW * 64;
+    if (x_is_f32)
+      nchw_to_bordered_nhwc_small_kernel<float><<<grid, 256, smem, s>>>((const float*)x, (uint8_t*)y, C, H, W, bh, bw);
+    else
+      nchw_to_bordered_nhwc_small_kernel<uint8_t><<<grid, 256, smem, s>>>((const uint8_t*)x, (uint8_t*)y, C, H, W, bh, bw);
     CUDA_TRY(cudaGetLastError());
     return B200Q_OK;
   }
