@@ -74,6 +74,11 @@ def test_conv3x3_qdm_small(algo):
     dict(N=2, C=256, H=30, W=17, OC=136, k=3, pads=(1, 1, 1, 1)),          # odd width
     dict(N=5, C=128, H=11, W=64, OC=96, k=3, pads=(1, 1, 0, 2)),           # asymmetric pads
     dict(N=2, C=80, H=16, W=16, OC=512, k=1, pads=(0, 0, 0, 0)),           # 1x1 with a ragged K block
+    # 64 channels: horizontally adjacent taps are paired into one 128-byte K block
+    dict(N=3, C=64, H=12, W=20, OC=64, k=3, pads=(1, 1, 1, 1)),            # 3x3: the third tap pairs with zeros
+    dict(N=2, C=64, H=9, W=11, OC=200, k=3, pads=(0, 0, 0, 0)),            # no border: the last pixel is data
+    dict(N=1, C=64, H=10, W=10, OC=32, k=2, pads=(0, 1, 1, 0)),            # even filter width
+    dict(N=1, C=64, H=8, W=9, OC=16, k=5, pads=(2, 2, 2, 2)),              # 5x5
 ])
 def test_conv_tensor_core_shapes(case):
     c = synth.conv2d_int8(seed=case["C"] + case["OC"], N=case["N"], C=case["C"], H=case["H"], W=case["W"],

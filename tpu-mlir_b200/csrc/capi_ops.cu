@@ -231,6 +231,7 @@ struct ConvHandle {
   b200q_conv2d_desc d{};
   ConvGeometry g{};
   bool use_tc = false;      // tensor cores on the zero-bordered image directly (stride 1, IC fits the K blocking)
+  bool pair_taps = false;   // use_tc with 64 channels: adjacent taps paired into 128-byte K blocks
   bool use_im2col = false;  // tensor cores on an im2col matrix (strides, dilation, any IC)
   int kpad = 0;             // im2col row length (KH*KW*IC rounded up to 16)
   int bh = 0, bw = 0, Hp = 0, Wp = 0;
@@ -300,7 +301,10 @@ int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int
 
   // tensor-core path: stride 1, no dilation, no groups, zero padding value, channels fit the K blocking
   const bool geometry_ok = d.sh == 1 && d.sw == 1 && d.dh == 1 && d.dw == 1 && d.groups == 1 && d.pad_value == 0;
-  const bool k_ok = (d.kh * d.kw == 1) ? (d.ic % 16 == 0) : (d.ic % 128 == 0);
+  // 64 input channels and a filter wider than one tap: two horizontally adjacent taps form one 128-byte K block
+  // (the bordered NHWC image holds pixel p+1's 64 channels right behind pixel p's), an odd last tap pairs with zeros
+  h->pair_taps = d.ic == 64 && d.kw >= 2;
+  const bool k_ok = (d.kh * d.kw == 1) ? (d.ic % 16 == 0) : (d.ic % 128 == 0 || h->pair_taps);
   h->bh = (int)(d.pht > d.phb ? d.pht : d.phb);
   h->bw = (int)(d.pwl > d.pwr ? d.pwl : d.pwr);
   h->Hp = (int)d.ih + 2 * h->bh;
@@ -314,7 +318,14 @@ int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int
   if (d.algo == 1 && !h->use_tc && !h->use_im2col)
     return set_error(B200Q_ERR_UNSUPPORTED, "conv2d: the tensor-core paths need groups = 1 and a zero padding value");
   const size_t wbytes = (size_t)d.oc * (d.ic / d.groups) * d.kh * d.kw;
-  if (h->use_tc) {
+  if (h->use_tc && h->pair_taps) {
+    const size_t pbytes = (size_t)d.oc * d.kh * ((d.kw + 1) / 2) * 128;
+    B200Q_TRY(h->w_packed.ensure(pbytes));
+    B200Q_TRY(repack_weight_pairs64(w_dev, w_is_f32, h->w_packed.p, (int)d.oc, (int)d.kh, (int)d.kw, s));
+    // one extra (zero) pixel behind the image: the zero-weight partner of an odd last tap may read one pixel further
+    B200Q_TRY(h->x_bordered.ensure((size_t)rows * d.ic + 64));
+    CUDA_TRY(cudaMemsetAsync(h->x_bordered.p, 0, (size_t)rows * d.ic + 64, s));
+  } else if (h->use_tc) {
     B200Q_TRY(h->w_packed.ensure(wbytes));
     B200Q_TRY(repack_weight_oihw(w_dev, w_is_f32, h->w_packed.p, (int)d.oc, (int)d.ic, (int)d.kh, (int)d.kw, s));
     B200Q_TRY(h->x_bordered.ensure((size_t)rows * d.ic));
@@ -373,6 +384,12 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.out_mode = IGEMM_OUT_NCHW;
     p.ldc = 0;
     p.out = y;
+    if (h->pair_taps) {
+      p.k_per_tap = 128;                    // two pixels' channels
+      p.taps_w = (int)((d.kw + 1) / 2);
+      p.tap_step_w = 2;
+      p.b_pitch = (long long)d.kh * p.taps_w * 128;
+    }
     B200Q_TRY(igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s));
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[2], s));
     return B200Q_OK;

@@ -20,6 +20,7 @@ struct IGemmProblem {
   long long a_pitch, b_pitch;
   int rows, n, k_per_tap;
   int taps_h, taps_w, pad_top, pad_left;  // 1,1,0,0 for a plain GEMM
+  int tap_step_w;                         // rows between horizontally adjacent taps (0 or 1: one pixel; 2: paired taps)
   int row_pitch;                          // Wp: rows per image line (convolution)
   int img_rows;                           // Hp*Wp: rows per image (convolution)
   int border_h, border_w;                 // zero border of the A image
@@ -33,7 +34,7 @@ struct IGemmProblem {
 
 // Kernel argument block (device view of the same problem).
 struct IGemmArgs {
-  int rows, n, num_kb, kb_per_tap, taps_w, tap_org_h, tap_org_w, row_pitch;
+  int rows, n, num_kb, kb_per_tap, taps_w, tap_step_w, tap_org_h, tap_org_w, row_pitch;
   int out_mode, img_rows, border_h, border_w, out_h, out_w;
   long long ldc;
   void* out;

@@ -205,10 +205,10 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
           if (++kc == args.kb_per_tap) {
             kc = 0;
-            ++a_row;  // next tap of the filter row
+            a_row += args.tap_step_w;  // next tap of the filter row
             if (++fx == args.taps_w) {
               fx = 0;
-              a_row += args.row_pitch - args.taps_w;  // first tap of the next filter row
+              a_row += args.row_pitch - args.taps_w * args.tap_step_w;  // first tap of the next filter row
             }
           }
           if (++stage == STAGES) {
@@ -694,6 +694,7 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   a.n = p.n;
   a.kb_per_tap = kb_per_tap;
   a.taps_w = p.taps_w;
+  a.tap_step_w = p.tap_step_w > 0 ? p.tap_step_w : 1;
   a.num_kb = kb_per_tap * p.taps_h * p.taps_w;
   a.tap_org_h = p.pad_top;
   a.tap_org_w = p.pad_left;
@@ -731,6 +732,8 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   a.num_n_tiles = (p.n + block_n - 1) / block_n;
 
   CUtensorMap ta, tb;
+  // (a_pitch < k_per_tap: overlapping rows, each spanning several consecutive pixels; the caller keeps
+  // k_per_tap - a_pitch readable bytes behind the last row)
   int rc = make_tmap_u8_2d(&ta, p.a, (uint64_t)p.k_per_tap, (uint64_t)p.rows, (uint64_t)p.a_pitch, BLOCK_M);
   if (rc) return rc;
   // B: [n][taps * k_per_tap]; with several taps k_per_tap is a multiple of BLOCK_K so blocks never straddle taps

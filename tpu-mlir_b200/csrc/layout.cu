@@ -200,6 +200,23 @@ __global__ void repack_weight_kernel(const T* __restrict__ w, uint8_t* __restric
   wr[idx] = to_byte<T>(w[((long long)oc * IC + ic) * KHW + tap]);
 }
 
+// 64-channel filters with horizontally adjacent taps paired into one 128-byte K block:
+// w[OC][64][KH][KW] -> wr[OC][KH][ceil(KW/2)][2][64], a missing second tap (odd KW) is zero.
+template <typename T>
+__global__ void repack_weight_pairs_kernel(const T* __restrict__ w, uint8_t* __restrict__ wr, int OC, int KH, int KW) {
+  const int KW2 = (KW + 1) / 2;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)OC * KH * KW2 * 128;
+  if (idx >= total) return;
+  const int ic = (int)(idx % 64);
+  const int sub = (int)((idx / 64) % 2);
+  const int fx2 = (int)((idx / 128) % KW2);
+  const int fy = (int)((idx / (128LL * KW2)) % KH);
+  const int oc = (int)(idx / (128LL * KW2 * KH));
+  const int fx = 2 * fx2 + sub;
+  wr[idx] = fx < KW ? to_byte<T>(w[(((long long)oc * 64 + ic) * KH + fy) * KW + fx]) : (uint8_t)0;
+}
+
 // [rows][cols] bytes -> [cols][rows] bytes
 template <typename T>
 __global__ void transpose_to_u8_kernel(const T* __restrict__ src, uint8_t* __restrict__ dst, int rows, int cols) {
@@ -303,6 +320,17 @@ int repack_weight_oihw(const void* w, int w_is_f32, void* wr, int OC, int IC, in
     repack_weight_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)w, (uint8_t*)wr, OC, IC, KH * KW);
   else
     repack_weight_kernel<uint8_t><<<blocks_for(total, 256), 256, 0, s>>>((const uint8_t*)w, (uint8_t*)wr, OC, IC, KH * KW);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int repack_weight_pairs64(const void* w, int w_is_f32, void* wr, int OC, int KH, int KW, cudaStream_t s) {
+  const long long total = (long long)OC * KH * ((KW + 1) / 2) * 128;
+  if (total == 0) return B200Q_OK;
+  if (w_is_f32)
+    repack_weight_pairs_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)w, (uint8_t*)wr, OC, KH, KW);
+  else
+    repack_weight_pairs_kernel<uint8_t><<<blocks_for(total, 256), 256, 0, s>>>((const uint8_t*)w, (uint8_t*)wr, OC, KH, KW);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }
