@@ -396,10 +396,17 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
   }
   if (h->use_im2col) {
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[0], s));
-    B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
-    B200Q_TRY(im2col_nhwc_launch(h->x_bordered.p, h->a_cols.p, d.n, (int)d.ic, h->Hp, h->Wp, h->g.oh, h->g.ow, (int)d.kh,
-                                 (int)d.kw, (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, h->bh - (int)d.pht,
-                                 h->bw - (int)d.pwl, h->kpad, s));
+    if (d.ic <= 4) {
+      // few input channels (a network's stem): rows are gathered straight from the NCHW input
+      B200Q_TRY(im2col_nchw_small_c_launch(x, x_is_f32, h->a_cols.p, d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->g.oh, h->g.ow,
+                                           (int)d.kh, (int)d.kw, (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, (int)d.pht,
+                                           (int)d.pwl, h->kpad, s));
+    } else {
+      B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
+      B200Q_TRY(im2col_nhwc_launch(h->x_bordered.p, h->a_cols.p, d.n, (int)d.ic, h->Hp, h->Wp, h->g.oh, h->g.ow, (int)d.kh,
+                                   (int)d.kw, (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, h->bh - (int)d.pht,
+                                   h->bw - (int)d.pwl, h->kpad, s));
+    }
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[1], s));
     IGemmProblem p{};
     p.a = h->a_cols.p;

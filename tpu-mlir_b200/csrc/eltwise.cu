@@ -13,6 +13,9 @@
 
 namespace b200q {
 namespace {
+__device__ __forceinline__ uint8_t to_u8(uint8_t v) { return v; }
+__device__ __forceinline__ uint8_t to_u8(float v) { return (uint8_t)(int)v; }  // integral by contract
+
 
 __device__ __forceinline__ int32_t ld_q(const void* p, long long i, int dt) {
   switch (dt) {
@@ -137,6 +140,40 @@ __global__ void pool2d_i8_kernel(const void* __restrict__ x, int dt, int NC, int
   st_q(out, idx, out_dt, (int32_t)v);
 }
 
+// 8-bit max pooling, input and output of the same type, no ReLU clamp needed beyond max(v, 0): typed loads and 32-bit
+// arithmetic (the general kernel above dispatches on the type per load and works in 64 bits).
+template <typename T>
+__global__ void __launch_bounds__(256)
+maxpool_q8_kernel(const T* __restrict__ x, long long total, int ih, int iw, int kh, int kw, int sh, int sw, int pht, int pwl,
+                  int oh, int ow, int do_relu, T* __restrict__ out) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  int xo, yo;
+  long long nc;
+  if (total < (1ll << 31)) {  // 32-bit index arithmetic (a 64-bit division costs ~100 instructions)
+    const uint32_t i32 = (uint32_t)idx, t32 = i32 / (uint32_t)ow;
+    xo = (int)(i32 - t32 * (uint32_t)ow);
+    const uint32_t n32 = t32 / (uint32_t)oh;
+    yo = (int)(t32 - n32 * (uint32_t)oh);
+    nc = n32;
+  } else {
+    xo = (int)(idx % ow);
+    const long long t = idx / ow;
+    yo = (int)(t % oh);
+    nc = t / oh;
+  }
+  const int y0 = yo * sh - pht, x0 = xo * sw - pwl;
+  const int fy0 = max(0, -y0), fy1 = min(kh, ih - y0), fx0 = max(0, -x0), fx1 = min(kw, iw - x0);
+  const T* src = x + nc * (long long)ih * iw;
+  int best = -2147483647 - 1;
+  for (int fy = fy0; fy < fy1; ++fy) {
+    const T* row = src + (long long)(y0 + fy) * iw + x0;
+    for (int fx = fx0; fx < fx1; ++fx) best = max(best, (int)row[fx]);
+  }
+  if (do_relu && best < 0) best = 0;
+  out[idx] = (T)best;
+}
+
 __global__ void cast_f32_q8_kernel(const float* __restrict__ x, long long n, float inv_scale, int zp, int rmode,
                                    int out_dt, void* __restrict__ out) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -174,6 +211,48 @@ __global__ void im2col_nhwc_kernel(const uint8_t* __restrict__ x, uint8_t* __res
   } else {
     for (int c = 0; c < C; ++c) dst[c] = src[c];
   }
+}
+
+// im2col straight from the NCHW input for few input channels (the 3-channel stem of a vision network): no bordered
+// NHWC copy in between.  A thread assembles one 16-byte piece of a row [kpad] with k = (fy*KW + fx)*C + c from
+// single-byte reads (neighbouring rows share them in L1) and stores it once; positions in the padding and the
+// k >= KH*KW*C tail are zero.  The (c, fy, fx) of every k come from a table in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256)
+im2col_nchw_small_c_kernel(const T* __restrict__ x, uint8_t* __restrict__ a, int C, int H, int W, int OH, int OW, int KH,
+                           int KW, int sh, int sw, int dh, int dw, int pht, int pwl, int kpad, long long total_units) {
+  extern __shared__ int ktab[];  // per k: c | fy << 8 | fx << 16, or -1 past the filter
+  const int kk = KH * KW * C;
+  for (int k = threadIdx.x; k < kpad; k += 256) {
+    int v = -1;
+    if (k < kk) {
+      const int tap = k / C, c = k - tap * C;
+      const int fy = tap / KW, fx = tap - fy * KW;
+      v = c | (fy << 8) | (fx << 16);
+    }
+    ktab[k] = v;
+  }
+  __syncthreads();
+  const long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= total_units) return;
+  const int pieces = kpad / 16;
+  const int piece = (int)(u % pieces);
+  const long long row = u / pieces;
+  const int xo = (int)(row % OW), yo = (int)((row / OW) % OH);
+  const long long n = row / ((long long)OW * OH);
+  const int y0 = yo * sh - pht, x0 = xo * sw - pwl;
+  const T* xn = x + n * (long long)C * H * W;
+  uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int b = 0; b < 16; ++b) {
+    const int e = ktab[piece * 16 + b];
+    if (e >= 0) {
+      const int c = e & 0xff, iy = y0 + ((e >> 8) & 0xff) * dh, ix = x0 + (e >> 16) * dw;
+      if (iy >= 0 && iy < H && ix >= 0 && ix < W)
+        w[b >> 2] |= (uint32_t)to_u8(xn[((long long)c * H + iy) * W + ix]) << (8 * (b & 3));
+    }
+  }
+  reinterpret_cast<uint4*>(a + row * kpad)[piece] = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 inline unsigned nblk(long long n, int t) { return (unsigned)((n + t - 1) / t); }
@@ -224,6 +303,16 @@ int pool2d_i8_launch(const void* x, int dt, int NC, int ih, int iw, int kh, int 
   const int oh = (ih + pht + phb - kh) / sh + 1, ow = (iw + pwl + pwr - kw) / sw + 1;
   const long long total = (long long)NC * oh * ow;
   if (total <= 0) return B200Q_OK;
+  if (mode == 0 && dt == out_dt && (dt == B200Q_DT_I8 || dt == B200Q_DT_U8)) {
+    if (dt == B200Q_DT_I8)
+      maxpool_q8_kernel<int8_t><<<nblk(total, 256), 256, 0, s>>>((const int8_t*)x, total, ih, iw, kh, kw, sh, sw, pht, pwl, oh, ow,
+                                                                 do_relu, (int8_t*)out);
+    else
+      maxpool_q8_kernel<uint8_t><<<nblk(total, 256), 256, 0, s>>>((const uint8_t*)x, total, ih, iw, kh, kw, sh, sw, pht, pwl, oh,
+                                                                  ow, do_relu, (uint8_t*)out);
+    CUDA_TRY(cudaGetLastError());
+    return B200Q_OK;
+  }
   pool2d_i8_kernel<<<nblk(total, 256), 256, 0, s>>>(x, dt, NC, ih, iw, kh, kw, sh, sw, pht, pwl, oh, ow, mode, multi, rshift,
                                                     do_relu, out_dt, out);
   CUDA_TRY(cudaGetLastError());
@@ -253,6 +342,24 @@ int im2col_nhwc_launch(const void* x, void* a, long long N, int C, int Hp, int W
   if ((units + 255) / 256 > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "im2col: too large");
   im2col_nhwc_kernel<<<nblk(units, 256), 256, 0, s>>>((const uint8_t*)x, (uint8_t*)a, C, Hp, Wp, OH, OW, KH, KW, sh, sw, dh,
                                                       dw, oy0, ox0, kpad, units, v16 ? 16 : 1);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int im2col_nchw_small_c_launch(const void* x, int x_is_f32, void* a, long long N, int C, int H, int W, int OH, int OW, int KH,
+                               int KW, int sh, int sw, int dh, int dw, int pht, int pwl, int kpad, cudaStream_t s) {
+  if (kpad % 16 != 0 || (reinterpret_cast<uintptr_t>(a) & 15) != 0 || KH > 255 || KW > 255 || C > 255)
+    return set_error(B200Q_ERR_INVALID, "im2col (small C): row length and buffer must be 16-byte aligned");
+  const long long units = N * OH * OW * (kpad / 16);
+  if (units == 0) return B200Q_OK;
+  if ((units + 255) / 256 > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "im2col: too large");
+  const size_t smem = (size_t)kpad * sizeof(int);
+  if (x_is_f32)
+    im2col_nchw_small_c_kernel<float><<<nblk(units, 256), 256, smem, s>>>((const float*)x, (uint8_t*)a, C, H, W, OH, OW, KH, KW,
+                                                                            sh, sw, dh, dw, pht, pwl, kpad, units);
+  else
+    im2col_nchw_small_c_kernel<uint8_t><<<nblk(units, 256), 256, smem, s>>>((const uint8_t*)x, (uint8_t*)a, C, H, W, OH, OW, KH,
+                                                                              KW, sh, sw, dh, dw, pht, pwl, kpad, units);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

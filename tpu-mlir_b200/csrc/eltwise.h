@@ -21,5 +21,8 @@ int cast_q8_f32_launch(const void* x, int dt, long long n, double scale, int zp,
 // coordinate of the first tap of output pixel (0,0), i.e. border - pad.
 int im2col_nhwc_launch(const void* x, void* a, long long N, int C, int Hp, int Wp, int OH, int OW, int KH, int KW, int sh,
                        int sw, int dh, int dw, int oy0, int ox0, int kpad, cudaStream_t s);
+// im2col straight from NCHW (bytes, or floats holding integers) for few input channels; zero padding
+int im2col_nchw_small_c_launch(const void* x, int x_is_f32, void* a, long long N, int C, int H, int W, int OH, int OW, int KH,
+                               int KW, int sh, int sw, int dh, int dw, int pht, int pwl, int kpad, cudaStream_t s);
 
 }  // namespace b200q

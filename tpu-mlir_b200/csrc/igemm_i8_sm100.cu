@@ -5,7 +5,7 @@
 //               shared-memory ring, completion counted on mbarriers;
 //   warp 1      allocates TMEM and issues tcgen05.mma (one thread), int32 accumulators live in TMEM,
 //               two accumulator buffers so the next tile's MMAs overlap this tile's epilogue;
-//   warps 2..   epilogue (one warp per 32 TMEM lanes x 64 columns, 16 warps for a 128 x 256 tile): tcgen05.ld the accumulator, + bias, ReLU, exact requantisation
+//   warps 2..17 epilogue (one warp per 32 TMEM lanes x BLOCK_N/4 columns): tcgen05.ld the accumulator, + bias, ReLU, exact requantisation
 //               (requant.cuh), saturate, store as [rows, N], as NCHW, or as zero-bordered NHWC.
 //
 // The convolution is expressed as a GEMM whose A rows are the pixels of a zero-bordered NHWC image
@@ -30,7 +30,6 @@ namespace {
 
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;  // bytes == int8 elements: one 128-byte swizzle span
-constexpr int EPI_COLS_PER_WARP = 64;
 constexpr int KIND_BF16_TAG = -2;  // value of the DIALECT template argument that selects bf16 operands / output  // each epilogue warp owns 32 TMEM lanes x 64 columns of the tile
 constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate tile time
 
@@ -50,8 +49,10 @@ struct SmemLayout {
   static constexpr int CHANK_OFFSET = SLOW_OFFSET + (BLOCK_N / 32) * 4;  // folded form: rounding constant + shifted zero point
   static constexpr int TOTAL = CHANK_OFFSET + BLOCK_N * 4;
   static constexpr int DYN_BYTES = TOTAL + 1024;                 // slack for manual 1024-byte alignment
-  // one epilogue warp per (TMEM lane quarter, 64-column group): 16 warps for BLOCK_N = 256
-  static constexpr int EPI_WARPS = 4 * (BLOCK_N / EPI_COLS_PER_WARP);
+  // always 16 epilogue warps (4 TMEM lane quarters x 4 column groups): a narrow tile is split finer instead of
+  // leaving warps idle, its epilogue costs as much per element as a wide one's
+  static constexpr int EPI_WARPS = 16;
+  static constexpr int EPI_COLS = BLOCK_N / 4;  // columns per epilogue warp: 64, 32 or 16
   static constexpr int NUM_THREADS = 64 + EPI_WARPS * 32;
   // 18 warps land 5,5,4,4 on the four sub-partitions (16384 registers each): 96 registers per thread at most
 };
@@ -269,7 +270,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   } else {
     // ------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;                                   // TMEM lanes 32*quarter .. 32*quarter+31
-    const int col0 = ((warp - 2) >> 2) * EPI_COLS_PER_WARP;         // first tile column of this warp
+    const int col0 = ((warp - 2) >> 2) * L::EPI_COLS;               // first tile column of this warp
     const int etid = threadIdx.x - 64;
     const Epilogue& e = args.epi;
     const bool out8 = e.out_dtype == B200Q_DT_I8 || e.out_dtype == B200Q_DT_U8;
@@ -393,13 +394,13 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       uint32_t rn[CH];
       ptx::tmem_ld_32x32b_x16(t_warp, rn);
 #pragma unroll 1
-      for (int cc = 0; cc < EPI_COLS_PER_WARP / CH; ++cc) {
+      for (int cc = 0; cc < L::EPI_COLS / CH; ++cc) {
         const int cbase = col0 + cc * CH;
         uint32_t r[CH];
         ptx::tmem_ld_wait_16(rn);
 #pragma unroll
         for (int j = 0; j < CH; ++j) r[j] = rn[j];
-        if (cc < EPI_COLS_PER_WARP / CH - 1) {
+        if (cc < L::EPI_COLS / CH - 1) {
           ptx::tmem_ld_32x32b_x16(t_warp + (uint32_t)((cc + 1) * CH), rn);
         } else {
           // this warp's share of the accumulator buffer is in registers: hand it back to the MMA warp.  Nothing
