@@ -46,6 +46,7 @@ struct IGemmArgs {
   int bf16;
   int acc_small;
   int out_small;
+  int acc_bound;  // |accumulator| <= this for every 8-bit operand pair (valid when acc_small)
 };
 
 int make_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,

@@ -62,6 +62,9 @@ struct TmemCols {
   static constexpr int value = (2 * BLOCK_N) < 32 ? 32 : 2 * BLOCK_N;  // power of two for BLOCK_N in {16,...,256}
 };
 
+// how a 32-channel chunk's requantisation parameters are staged (see the epilogue)
+enum { FORM_FOLD_QDM = 0, FORM_FAST = 1, FORM_GENERAL = 3, FORM_FOLD_HI = 4, FORM_FOLD_FUNNEL = 5 };
+
 template <int THREADS>
 __device__ __forceinline__ void epi_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
@@ -102,14 +105,14 @@ __device__ __forceinline__ bool fast_domain(int32_t m, int32_t s) {
   return false;
 }
 
-// Extra conditions of the folded form (on top of fast_domain, |bias| < 2^28 and |accumulator| < 2^29), chosen so
-// that no intermediate can overflow: QDM: |zp| << t < 2^28;  MultiplierShift: s >= 32 (the shifted value then
-// fits 32 bits) and |zp| << s < 2^60.
+// Extra conditions of the folded forms (on top of fast_domain, |bias| < 2^28 and |accumulator| < 2^29), chosen so
+// that no 64-bit intermediate can overflow: QDM: |zp| << t < 2^28;  MultiplierShift: |zp| << s < 2^60 (the epilogue
+// additionally proves that a value shifted by s < 32 fits 32 bits).
 template <int DIALECT>
 __device__ __forceinline__ bool fold_domain(int32_t sh, int32_t zp) {
   const long long az = zp < 0 ? -(long long)zp : (long long)zp;
   if (DIALECT == B200Q_RQ_QDM) return az < (1ll << 20) && (az << (-sh)) < (1ll << 28);
-  if (DIALECT == B200Q_RQ_MULTIPLIER_SHIFT) return sh >= 32 && az < (1ll << 20) && (zp == 0 || sh <= 40);
+  if (DIALECT == B200Q_RQ_MULTIPLIER_SHIFT) return sh >= 1 && sh <= 62 && az < (1ll << 20) && (zp == 0 || sh <= 40);
   return false;
 }
 
@@ -300,14 +303,20 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
       if (n0 != cached_n0) {
         // Stage the tile's channel parameters in the cheapest form every channel of a 32-channel chunk allows:
-        //   FOLDED  {m, C_lo, C_hi, shift} (+ chan_k): bias, rounding constants and the output zero point are folded
-        //           into one 64-bit and one 32-bit constant; one multiply-add, two shifts and a clamp per element
-        //   FAST    {bias, m, right shift, half}: the pre-ReLU (MatMul) order, or biases too large to fold
-        //   GENERAL {bias, m, shift, 0}: any dialect / rounding mode / parameter value (requant_value<>)
+        //   FOLD_HI     {m, C_lo, C_hi, sh}: v = hi32(acc*m + C) >> sh.  Bias, every rounding constant and the zero
+        //               point live in C.  QDM with the ReLU after the requantisation (the sign term of the second,
+        //               half-away rounding only matters for results the ReLU clamps anyway): C = bias*m + 2^30 +
+        //               (2^(t-1) + (zp << t)) * 2^31, sh = t - 1.  MultiplierShift with s >= 32: sh = s - 32.
+        //   FOLD_FUNNEL MultiplierShift with s in [1,31] whose shifted value provably fits 32 bits:
+        //               v = low32((acc*m + C) >> s), C = bias*m + 2^(s-1) + (zp << s).
+        //   FOLD_QDM    {m, C_lo, C_hi, t} + chan_k: QDM half-away without the ReLU shortcut.
+        //   FAST        {bias, m, right shift, half}: the pre-ReLU (MatMul) order, or biases too large to fold
+        //   GENERAL     {bias, m, shift, 0}: any dialect / rounding mode / parameter value (requant_value<>)
         epi_bar_sync<EPI_THREADS>();  // everyone is done reading the previous tile's channel parameters
         if (etid < BLOCK_N / 32) chunk_form[etid] = 0;
         epi_bar_sync<EPI_THREADS>();
         const bool pre_relu = e.relu == B200Q_RELU_BEFORE_REQUANT;
+        const long long az = e.out_zp < 0 ? -(long long)e.out_zp : (long long)e.out_zp;
         for (int c = etid; c < BLOCK_N; c += EPI_THREADS) {
           if (DIALECT == KIND_BF16_TAG) break;
           const int n = n0 + c;
@@ -316,43 +325,82 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const int32_t m = e.multiplier ? e.multiplier[e.per_channel ? n : 0] : 1;
           const int32_t sh = e.shift ? e.shift[e.per_channel ? n : 0] : 0;
           const bool fast_ok = kFastDialect && fast_domain<DIALECT, RMODE>(m, sh);
-          const bool fold_ok = fast_ok && !pre_relu && args.acc_small && bias > -(1 << 28) && bias < (1 << 28) &&
-                               fold_domain<DIALECT>(sh, e.out_zp);
-          atomicOr(&chunk_form[c >> 5], (fold_ok ? 0 : 1) | (fast_ok ? 0 : 2));
+          bool fold_ok = fast_ok && !pre_relu && args.acc_small && bias > -(1 << 28) && bias < (1 << 28) &&
+                         fold_domain<DIALECT>(sh, e.out_zp);
+          int width_bits = 0;
+          if (DIALECT == B200Q_RQ_MULTIPLIER_SHIFT && fold_ok) {
+            if (sh >= 32) {
+              width_bits = 8;
+            } else {  // the value shifted by s must fit 32 bits for every accumulator this K can produce
+              const unsigned long long am = (unsigned long long)(m < 0 ? -(long long)m : (long long)m);
+              const unsigned long long ab = (unsigned long long)(bias < 0 ? -(long long)bias : (long long)bias);
+              const unsigned long long bound = (unsigned long long)args.acc_bound * am + ab * am + (1ull << (sh - 1)) +
+                                               ((unsigned long long)az << sh);
+              fold_ok = bound < (1ull << (31 + sh));
+              width_bits = 4;
+            }
+          }
+          atomicOr(&chunk_form[c >> 5], (fold_ok ? width_bits : 1) | (fast_ok ? 0 : 2));
         }
         epi_bar_sync<EPI_THREADS>();
-        for (int c = etid; c < BLOCK_N; c += EPI_THREADS) {
+        int my_form[(BLOCK_N + EPI_THREADS - 1) / EPI_THREADS];
+#pragma unroll
+        for (int i = 0; i < (BLOCK_N + EPI_THREADS - 1) / EPI_THREADS; ++i) {
+          const int c = etid + i * EPI_THREADS;
+          if (c >= BLOCK_N) break;
           const int n = n0 + c;
           const bool in = n < args.n;
           if (DIALECT == KIND_BF16_TAG) {
             chan[c] = make_int4((in && args.bias_f32) ? __float_as_int(args.bias_f32[n]) : 0, 0, 0, 0);
+            my_form[i] = FORM_GENERAL;
             continue;
           }
           const int32_t bias = (in && e.bias) ? e.bias[n] : 0;
           const int32_t m = (in && e.multiplier) ? e.multiplier[e.per_channel ? n : 0] : 1;
           const int32_t sh = (in && e.shift) ? e.shift[e.per_channel ? n : 0] : 0;
-          const int form = chunk_form[c >> 5];
+          const int st = chunk_form[c >> 5];
+          int form;
+          if (st & 2) form = FORM_GENERAL;
+          else if (st & 1) form = FORM_FAST;
+          else if (DIALECT == B200Q_RQ_QDM) form = relu_after ? FORM_FOLD_HI : FORM_FOLD_QDM;
+          else form = ((st & 4) && (st & 8)) ? FORM_FAST : ((st & 4) ? FORM_FOLD_FUNNEL : FORM_FOLD_HI);
+          my_form[i] = form;
           if (!in) {
-            chan[c] = make_int4(0, 0, 1, 0);
-          } else if (form == 0) {
+            chan[c] = make_int4(0, 0, 0, 1);
+            chan_k[c] = 0;
+          } else if (form == FORM_FOLD_HI || form == FORM_FOLD_FUNNEL || form == FORM_FOLD_QDM) {
+            long long C;
+            int32_t s4;
             if (DIALECT == B200Q_RQ_QDM) {
-              // w = (acc*m + C) >> 31 (half up), then (w - (w < 0) + K) >> t with K = 2^(t-1) + (zp << t)
               const int32_t t = -sh;
-              const long long C = (long long)bias * (long long)m + (1ll << 30);
-              chan[c] = make_int4(m, (int32_t)(uint32_t)(C & 0xffffffffll), (int32_t)(C >> 32), t);
-              chan_k[c] = (int32_t)((1u << t) >> 1) + (int32_t)((uint32_t)e.out_zp << t);
+              const long long K = (long long)((1u << t) >> 1) + (long long)((unsigned long long)(long long)e.out_zp << t);
+              C = (long long)bias * (long long)m + (1ll << 30);
+              if (form == FORM_FOLD_HI) {
+                C += (long long)((unsigned long long)K << 31);
+                s4 = t - 1;
+              } else {  // (w - (w < 0) + K) >> t after w = (acc*m + C) >> 31
+                chan_k[c] = (int32_t)K;
+                s4 = t;
+              }
             } else {
-              // (acc*m + C) >> s with C = bias*m + 2^(s-1) + (zp << s); s >= 32, so the result is the high word >> (s-32)
-              const long long C = (long long)bias * (long long)m + (long long)(1ull << (sh - 1)) +
-                                  (long long)((unsigned long long)(long long)e.out_zp << sh);
-              chan[c] = make_int4(m, (int32_t)(uint32_t)(C & 0xffffffffll), (int32_t)(C >> 32), sh - 32);
-              chan_k[c] = 0;
+              C = (long long)bias * (long long)m + (long long)(1ull << (sh - 1)) +
+                  (long long)((unsigned long long)(long long)e.out_zp << sh);
+              s4 = form == FORM_FOLD_HI ? sh - 32 : sh;
             }
-          } else if ((form & 2) == 0) {
+            chan[c] = make_int4(m, (int32_t)(uint32_t)(C & 0xffffffffll), (int32_t)(C >> 32), s4);
+          } else if (form == FORM_FAST) {
             const int32_t t = DIALECT == B200Q_RQ_QDM ? -sh : sh;
             chan[c] = make_int4(bias, m, t, DIALECT == B200Q_RQ_QDM ? (int32_t)(1u << (t - 1)) : 0);
           } else {
             chan[c] = make_int4(bias, m, sh, 0);
+          }
+        }
+        epi_bar_sync<EPI_THREADS>();  // every thread has read its chunks' classification bits
+        if (DIALECT != KIND_BF16_TAG) {
+#pragma unroll
+          for (int i = 0; i < (BLOCK_N + EPI_THREADS - 1) / EPI_THREADS; ++i) {
+            const int c = etid + i * EPI_THREADS;
+            if (c < BLOCK_N && (c & 31) == 0) chunk_form[c >> 5] = my_form[i];
           }
         }
         epi_bar_sync<EPI_THREADS>();
@@ -440,36 +488,37 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           continue;
         }
         int32_t q[CH];
-        const int form = kFastCompiled ? chunk_form[cbase >> 5] : 3;
-        if (kFastCompiled && form == 0 && DIALECT == B200Q_RQ_QDM && relu_after) {
-          // With the ReLU after the requantisation every negative result ends at the zero point, and half-away
-          // differs from half-up only for negative values (a tie at -0.5 gives -1 or 0, both clamp): the sign term of
-          // the second rounding can go.
+        const int form = kFastCompiled ? chunk_form[cbase >> 5] : FORM_GENERAL;
+        if (kFastCompiled && (form == FORM_FOLD_HI || form == FORM_FOLD_FUNNEL)) {
+          if (form == FORM_FOLD_HI) {
 #pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            const int4 cp = chan[cbase + j];  // {m, C_lo, C_hi, shift}
-            const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
-            const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
-            const int32_t v = ((int32_t)(x >> 31) + chan_k[cbase + j]) >> cp.w;
-            q[j] = min(max(v, sat_lo2), sat_hi);
-          }
-        } else if (kFastCompiled && form == 0) {
-#pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            const int4 cp = chan[cbase + j];  // {m, C_lo, C_hi, shift}: one broadcast 16-byte shared load
-            const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
-            const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
-            int32_t v;  // requantised value with the zero point already added
-            if (DIALECT == B200Q_RQ_QDM) {
-              const int32_t w = (int32_t)(x >> 31);  // half-up shift by 31: C carries the 2^30
-              // half away from zero for a right shift by t: (w + 2^(t-1) - (w < 0)) >> t; |w| < 2^30 here
-              v = (w + (w >> 31) + chan_k[cbase + j]) >> cp.w;
-            } else {
-              v = (int32_t)(x >> 32) >> cp.w;  // half-up: C carries 2^(s-1); cp.w = s - 32
+            for (int j = 0; j < CH; ++j) {
+              const int4 cp = chan[cbase + j];  // {m, C_lo, C_hi, sh}: one broadcast 16-byte shared load
+              const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
+              const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
+              q[j] = min(max((int32_t)(x >> 32) >> cp.w, sat_lo2), sat_hi);
             }
-            q[j] = min(max(v, sat_lo2), sat_hi);
+          } else {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int4 cp = chan[cbase + j];
+              const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
+              const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
+              const int32_t v = (int32_t)__funnelshift_r((uint32_t)x, (uint32_t)(x >> 32), (uint32_t)cp.w);
+              q[j] = min(max(v, sat_lo2), sat_hi);
+            }
           }
-        } else if (kFastCompiled && (form & 2) == 0) {
+        } else if (kFastCompiled && form == FORM_FOLD_QDM) {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            const int4 cp = chan[cbase + j];  // {m, C_lo, C_hi, t}
+            const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
+            const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
+            const int32_t w = (int32_t)(x >> 31);  // half-up shift by 31: C carries the 2^30
+            // half away from zero for a right shift by t: (w + 2^(t-1) - (w < 0)) >> t, zero point inside chan_k
+            q[j] = min(max((w + (w >> 31) + chan_k[cbase + j]) >> cp.w, sat_lo2), sat_hi);
+          }
+        } else if (kFastCompiled && form == FORM_FAST) {
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
             const int4 cp = chan[cbase + j];  // {bias, multiplier, shift, half}
@@ -713,6 +762,7 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   a.bf16 = p.kind == IGEMM_KIND_BF16;
   // |accumulator| < 2^29 for every 8-bit operand pair: lets the epilogue fold the bias into one 64-bit constant
   a.acc_small = ((long long)a.num_kb * BLOCK_K * 32640ll) < (1ll << 29);
+  a.acc_bound = a.acc_small ? (int)((long long)a.num_kb * BLOCK_K * 32640ll) : (1 << 29);
   a.bias_f32 = p.bias_f32;
   {
     const long long out_elems = p.out_mode == IGEMM_OUT_NCHW
