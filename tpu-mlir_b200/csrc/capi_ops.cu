@@ -233,6 +233,7 @@ struct ConvHandle {
   bool use_tc = false;      // tensor cores on the zero-bordered image directly (stride 1, IC fits the K blocking)
   bool pair_taps = false;   // use_tc with 64 channels: adjacent taps paired into 128-byte K blocks
   bool use_im2col = false;  // tensor cores on an im2col matrix (strides, dilation, any IC)
+  bool few_channels = false;  // use_im2col with the (fy, c, fx8) row order gathered straight from NCHW (a network's stem)
   int kpad = 0;             // im2col row length (KH*KW*IC rounded up to 16)
   int bh = 0, bw = 0, Hp = 0, Wp = 0;
   Epilogue epi{};
@@ -315,6 +316,9 @@ int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int
   h->kpad = (int)((d.kh * d.kw * d.ic + 15) / 16 * 16);
   h->use_im2col = !h->use_tc && d.groups == 1 && d.pad_value == 0 && d.algo != 2 && out_rows < 0x7fffffffLL &&
                   (long long)d.kh * d.kw * d.ic < 0x7fffffffLL;
+  h->few_channels = h->use_im2col && im2col_few_channels_ok((int)d.ic, (int)d.ih, (int)d.iw, (int)d.kh, (int)d.kw, (int)d.sh,
+                                                            (int)d.sw, (int)d.dh, (int)d.dw, (int)d.pwl, (int)ow);
+  if (h->few_channels) h->kpad = (int)((d.kh * d.ic * 8 + 63) / 64 * 64);  // rows start on 64-byte boundaries: whole sectors per TMA row
   if (d.algo == 1 && !h->use_tc && !h->use_im2col)
     return set_error(B200Q_ERR_UNSUPPORTED, "conv2d: the tensor-core paths need groups = 1 and a zero padding value");
   const size_t wbytes = (size_t)d.oc * (d.ic / d.groups) * d.kh * d.kw;
@@ -330,6 +334,10 @@ int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int
     B200Q_TRY(repack_weight_oihw(w_dev, w_is_f32, h->w_packed.p, (int)d.oc, (int)d.ic, (int)d.kh, (int)d.kw, s));
     B200Q_TRY(h->x_bordered.ensure((size_t)rows * d.ic));
     CUDA_TRY(cudaMemsetAsync(h->x_bordered.p, 0, (size_t)rows * d.ic, s));  // the border stays zero for every run
+  } else if (h->use_im2col && h->few_channels) {
+    B200Q_TRY(h->w_packed.ensure((size_t)d.oc * h->kpad));
+    B200Q_TRY(repack_weight_fy_c_fx8(w_dev, w_is_f32, h->w_packed.p, (int)d.oc, (int)d.ic, (int)d.kh, (int)d.kw, h->kpad, s));
+    B200Q_TRY(h->a_cols.ensure((size_t)out_rows * h->kpad));
   } else if (h->use_im2col) {
     const size_t kk = (size_t)d.kh * d.kw * d.ic;
     // weights [OC][kk] -> pitch kpad (zero padded)
@@ -396,8 +404,12 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
   }
   if (h->use_im2col) {
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[0], s));
-    if (d.ic <= 4) {
-      // few input channels (a network's stem): rows are gathered straight from the NCHW input
+    if (h->few_channels) {
+      // few input channels (a network's stem): rows are built from 8-byte runs of the NCHW input
+      B200Q_TRY(im2col_few_channels_launch(x, x_is_f32, h->a_cols.p, d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->g.oh, h->g.ow,
+                                           (int)d.kh, (int)d.sh, (int)d.sw, (int)d.pht, (int)d.pwl, h->kpad, s));
+    } else if (d.ic <= 4) {
+      // few input channels, other geometry: rows are gathered byte by byte straight from the NCHW input
       B200Q_TRY(im2col_nchw_small_c_launch(x, x_is_f32, h->a_cols.p, d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->g.oh, h->g.ow,
                                            (int)d.kh, (int)d.kw, (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, (int)d.pht,
                                            (int)d.pwl, h->kpad, s));

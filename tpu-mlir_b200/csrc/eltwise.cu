@@ -16,6 +16,13 @@ namespace {
 __device__ __forceinline__ uint8_t to_u8(uint8_t v) { return v; }
 __device__ __forceinline__ uint8_t to_u8(float v) { return (uint8_t)(int)v; }  // integral by contract
 
+__device__ __forceinline__ uint32_t ld4_as_bytes(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+__device__ __forceinline__ uint32_t ld4_as_bytes(const float* p) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  return (uint32_t)((int)v.x & 0xff) | ((uint32_t)((int)v.y & 0xff) << 8) | ((uint32_t)((int)v.z & 0xff) << 16) |
+         ((uint32_t)((int)v.w & 0xff) << 24);
+}
+
 
 __device__ __forceinline__ int32_t ld_q(const void* p, long long i, int dt) {
   switch (dt) {
@@ -174,12 +181,63 @@ maxpool_q8_kernel(const T* __restrict__ x, long long total, int ih, int iw, int 
   out[idx] = (T)best;
 }
 
+// The same for planes that fit shared memory: a block loads one (n, c) plane with 16-byte accesses, then every
+// output reads its window from shared memory (the direct kernel spends its time on strided single-byte global loads).
+template <typename T>
+__global__ void __launch_bounds__(256)
+maxpool_q8_plane_kernel(const T* __restrict__ x, int ih, int iw, int kh, int kw, int sh, int sw, int pht, int pwl, int oh,
+                        int ow, int do_relu, T* __restrict__ out) {
+  extern __shared__ __align__(16) uint8_t plane_raw[];
+  T* plane = reinterpret_cast<T*>(plane_raw);
+  const long long nc = blockIdx.x;
+  const int n_in = ih * iw;
+  const T* src = x + nc * n_in;
+  if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    for (int i = threadIdx.x; i < n_in / 16; i += 256)
+      reinterpret_cast<uint4*>(plane_raw)[i] = reinterpret_cast<const uint4*>(src)[i];
+    for (int i = (n_in / 16) * 16 + threadIdx.x; i < n_in; i += 256) plane[i] = src[i];
+  } else {
+    for (int i = threadIdx.x; i < n_in; i += 256) plane[i] = src[i];
+  }
+  __syncthreads();
+  T* dst = out + nc * (long long)oh * ow;
+  for (int o = threadIdx.x; o < oh * ow; o += 256) {
+    const int yo = o / ow, xo = o - yo * ow;
+    const int y0 = yo * sh - pht, x0 = xo * sw - pwl;
+    const int fy0 = max(0, -y0), fy1 = min(kh, ih - y0), fx0 = max(0, -x0), fx1 = min(kw, iw - x0);
+    int best = -2147483647 - 1;
+    for (int fy = fy0; fy < fy1; ++fy) {
+      const T* row = plane + (y0 + fy) * iw + x0;
+      for (int fx = fx0; fx < fx1; ++fx) best = max(best, (int)row[fx]);
+    }
+    if (do_relu && best < 0) best = 0;
+    dst[o] = (T)best;
+  }
+}
+
 __global__ void cast_f32_q8_kernel(const float* __restrict__ x, long long n, float inv_scale, int zp, int rmode,
                                    int out_dt, void* __restrict__ out) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float v = __fadd_rn(roundf(__fmul_rn(x[i], inv_scale)), (float)zp);
   st_q(out, i, out_dt, (int32_t)clamp_dtype(to_int_f32(v, rmode), out_dt));
+}
+
+// four elements per thread for 8-bit outputs (16-byte load, 4-byte store), same arithmetic
+__global__ void __launch_bounds__(256)
+cast_f32_q8x4_kernel(const float4* __restrict__ x, long long n4, float inv_scale, int zp, int rmode, int out_dt,
+                     uint32_t* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const float4 v4 = x[i];
+  const float f[4] = {v4.x, v4.y, v4.z, v4.w};
+  uint32_t o = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float v = __fadd_rn(roundf(__fmul_rn(f[j], inv_scale)), (float)zp);
+    o |= ((uint32_t)clamp_dtype(to_int_f32(v, rmode), out_dt) & 0xffu) << (8 * j);
+  }
+  out[i] = o;
 }
 
 __global__ void cast_q8_f32_kernel(const void* __restrict__ x, int dt, long long n, float scale, int zp,
@@ -255,6 +313,70 @@ im2col_nchw_small_c_kernel(const T* __restrict__ x, uint8_t* __restrict__ a, int
   reinterpret_cast<uint4*>(a + row * kpad)[piece] = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// im2col for few input channels and filters up to 8 taps wide, K order (fy, c, fx padded to 8): the eight input bytes
+// of one (fy, c) segment are contiguous in the NCHW row, so a row of A is built from unaligned 8-byte reads instead of
+// single bytes.  A block stages the input rows of a band of output rows in shared memory (zero padding included),
+// then every thread assembles 16-byte pieces (two segments) with three aligned word reads and two funnel shifts per
+// segment.  The eighth byte of a segment is whatever pixel follows; its filter weight is zero.
+template <typename T>
+__global__ void __launch_bounds__(256)
+im2col_few_channels_kernel(const T* __restrict__ x, uint8_t* __restrict__ a, int C, int H, int W, int OH, int OW, int KH,
+                           int sh, int sw, int pht, int pwl, int kpad, int band, int wpad, int pwl_s) {
+  extern __shared__ __align__(16) uint8_t tile[];  // [C][rows_in][wpad]
+  const int n = blockIdx.y, oy0 = blockIdx.x * band;
+  const int rows_out = min(band, OH - oy0);
+  const int rows_in = (rows_out - 1) * sh + KH;
+  const int iy0 = oy0 * sh - pht;
+  // ---- fill (zeros first, then the valid parts of the rows)
+  const int tile_words = C * rows_in * wpad / 4;
+  for (int i = threadIdx.x; i < tile_words; i += 256) reinterpret_cast<uint32_t*>(tile)[i] = 0u;
+  __syncthreads();
+  const T* xn = x + (long long)n * C * H * W;
+  if ((W & 3) == 0) {
+    const int wq = W / 4;
+    for (int i = threadIdx.x; i < C * rows_in * wq; i += 256) {
+      const int q = i % wq, cr = i / wq;
+      const int r = cr % rows_in, c = cr / rows_in;
+      const int iy = iy0 + r;
+      if (iy >= 0 && iy < H)
+        *reinterpret_cast<uint32_t*>(tile + (c * rows_in + r) * wpad + pwl_s + 4 * q) = ld4_as_bytes(xn + ((long long)c * H + iy) * W + 4 * q);
+    }
+  } else {
+    for (int i = threadIdx.x; i < C * rows_in * W; i += 256) {
+      const int q = i % W, cr = i / W;
+      const int r = cr % rows_in, c = cr / rows_in;
+      const int iy = iy0 + r;
+      if (iy >= 0 && iy < H) tile[(c * rows_in + r) * wpad + pwl_s + q] = to_u8(xn[((long long)c * H + iy) * W + q]);
+    }
+  }
+  __syncthreads();
+  // ---- rows of A: piece = 16 bytes = two (fy, c) segments
+  const int ppr = kpad / 16, nseg = KH * C;
+  uint8_t* an = a + ((long long)n * OH + oy0) * OW * kpad;
+  for (int i = threadIdx.x; i < rows_out * OW * ppr; i += 256) {
+    const int pp = i % ppr, rl = i / ppr;
+    const int ox = rl % OW, oyl = rl / OW;
+    const int xs = ox * sw - pwl + pwl_s;  // window start in tile columns
+    const int sh8 = (xs & 3) * 8;
+    uint32_t w[4];
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      const int seg = 2 * pp + g;
+      uint32_t lo = 0, hi = 0;
+      if (seg < nseg) {
+        const int fy = seg / C, c = seg - fy * C;
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(tile + (c * rows_in + oyl * sh + fy) * wpad + (xs & ~3));
+        const uint32_t w0 = src[0], w1 = src[1], w2 = src[2];
+        lo = __funnelshift_r(w0, w1, sh8);
+        hi = __funnelshift_r(w1, w2, sh8);
+      }
+      w[2 * g] = lo;
+      w[2 * g + 1] = hi;
+    }
+    *reinterpret_cast<uint4*>(an + (long long)rl * kpad + pp * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 inline unsigned nblk(long long n, int t) { return (unsigned)((n + t - 1) / t); }
 
 }  // namespace
@@ -303,6 +425,17 @@ int pool2d_i8_launch(const void* x, int dt, int NC, int ih, int iw, int kh, int 
   const int oh = (ih + pht + phb - kh) / sh + 1, ow = (iw + pwl + pwr - kw) / sw + 1;
   const long long total = (long long)NC * oh * ow;
   if (total <= 0) return B200Q_OK;
+  if (mode == 0 && dt == out_dt && (dt == B200Q_DT_I8 || dt == B200Q_DT_U8) && (long long)ih * iw <= 48 * 1024 && NC > 0) {
+    const size_t smem = (size_t)ih * iw;
+    if (dt == B200Q_DT_I8)
+      maxpool_q8_plane_kernel<int8_t><<<(unsigned)NC, 256, smem, s>>>((const int8_t*)x, ih, iw, kh, kw, sh, sw, pht, pwl, oh, ow,
+                                                                      do_relu, (int8_t*)out);
+    else
+      maxpool_q8_plane_kernel<uint8_t><<<(unsigned)NC, 256, smem, s>>>((const uint8_t*)x, ih, iw, kh, kw, sh, sw, pht, pwl, oh, ow,
+                                                                       do_relu, (uint8_t*)out);
+    CUDA_TRY(cudaGetLastError());
+    return B200Q_OK;
+  }
   if (mode == 0 && dt == out_dt && (dt == B200Q_DT_I8 || dt == B200Q_DT_U8)) {
     if (dt == B200Q_DT_I8)
       maxpool_q8_kernel<int8_t><<<nblk(total, 256), 256, 0, s>>>((const int8_t*)x, total, ih, iw, kh, kw, sh, sw, pht, pwl, oh, ow,
@@ -321,7 +454,11 @@ int pool2d_i8_launch(const void* x, int dt, int NC, int ih, int iw, int kh, int 
 
 int cast_f32_q8_launch(const float* x, long long n, double scale, int zp, int rmode, int out_dt, void* out, cudaStream_t s) {
   if (n == 0) return B200Q_OK;
-  cast_f32_q8_kernel<<<nblk(n, 256), 256, 0, s>>>(x, n, (float)(1.0 / scale), zp, rmode, out_dt, out);
+  if (out_dt <= B200Q_DT_U8 && n % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 3) == 0)
+    cast_f32_q8x4_kernel<<<nblk(n / 4, 256), 256, 0, s>>>((const float4*)x, n / 4, (float)(1.0 / scale), zp, rmode, out_dt,
+                                                          (uint32_t*)out);
+  else
+    cast_f32_q8_kernel<<<nblk(n, 256), 256, 0, s>>>(x, n, (float)(1.0 / scale), zp, rmode, out_dt, out);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }
@@ -360,6 +497,39 @@ int im2col_nchw_small_c_launch(const void* x, int x_is_f32, void* a, long long N
   else
     im2col_nchw_small_c_kernel<uint8_t><<<nblk(units, 256), 256, smem, s>>>((const uint8_t*)x, (uint8_t*)a, C, H, W, OH, OW, KH,
                                                                               KW, sh, sw, dh, dw, pht, pwl, kpad, units);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+// K order (fy, c, fx padded to 8), kpad = round16(KH*C*8).  Geometry limits are checked by im2col_few_channels_ok.
+bool im2col_few_channels_ok(int C, int H, int W, int KH, int KW, int sh, int sw, int dh, int dw, int pwl, int OW) {
+  if (C < 1 || C > 4 || KW > 8 || dh != 1 || dw != 1 || W < 1) return false;
+  const int pwl_s = (pwl + 3) & ~3;
+  const int wpad = ((max((OW - 1) * sw - pwl + pwl_s + 8, pwl_s + W) + 3) & ~3) + 4;
+  const int rows_in = 7 * sh + KH;  // band of 8 output rows
+  return (size_t)C * rows_in * wpad <= 96 * 1024;
+}
+
+int im2col_few_channels_launch(const void* x, int x_is_f32, void* a, long long N, int C, int H, int W, int OH, int OW, int KH,
+                               int sh, int sw, int pht, int pwl, int kpad, cudaStream_t s) {
+  if (N == 0) return B200Q_OK;
+  if (N > 65535) return set_error(B200Q_ERR_UNSUPPORTED, "im2col (few channels): at most 65535 images per call");
+  if ((reinterpret_cast<uintptr_t>(a) & 15) != 0 || kpad % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+    return set_error(B200Q_ERR_INVALID, "im2col (few channels): buffers must be 16-byte aligned");
+  const int band = 8;
+  const int pwl_s = (pwl + 3) & ~3;
+  const int wpad = ((max((OW - 1) * sw - pwl + pwl_s + 8, pwl_s + W) + 3) & ~3) + 4;  // + one word: the third read of a window
+  const size_t smem = (size_t)C * ((band - 1) * sh + KH) * wpad;
+  dim3 grid((OH + band - 1) / band, (unsigned)N);
+  if (x_is_f32) {
+    auto k = im2col_few_channels_kernel<float>;
+    if (smem > 48 * 1024) CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k<<<grid, 256, smem, s>>>((const float*)x, (uint8_t*)a, C, H, W, OH, OW, KH, sh, sw, pht, pwl, kpad, band, wpad, pwl_s);
+  } else {
+    auto k = im2col_few_channels_kernel<uint8_t>;
+    if (smem > 48 * 1024) CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k<<<grid, 256, smem, s>>>((const uint8_t*)x, (uint8_t*)a, C, H, W, OH, OW, KH, sh, sw, pht, pwl, kpad, band, wpad, pwl_s);
+  }
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

@@ -24,5 +24,10 @@ int im2col_nhwc_launch(const void* x, void* a, long long N, int C, int Hp, int W
 // im2col straight from NCHW (bytes, or floats holding integers) for few input channels; zero padding
 int im2col_nchw_small_c_launch(const void* x, int x_is_f32, void* a, long long N, int C, int H, int W, int OH, int OW, int KH,
                                int KW, int sh, int sw, int dh, int dw, int pht, int pwl, int kpad, cudaStream_t s);
+// im2col for at most 4 input channels and filters up to 8 taps wide, straight from NCHW; K order (fy, c, fx padded
+// to 8), row length kpad = round16(KH*C*8)
+bool im2col_few_channels_ok(int C, int H, int W, int KH, int KW, int sh, int sw, int dh, int dw, int pwl, int OW);
+int im2col_few_channels_launch(const void* x, int x_is_f32, void* a, long long N, int C, int H, int W, int OH, int OW, int KH,
+                               int sh, int sw, int pht, int pwl, int kpad, cudaStream_t s);
 
 }  // namespace b200q

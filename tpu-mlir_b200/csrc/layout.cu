@@ -217,6 +217,22 @@ __global__ void repack_weight_pairs_kernel(const T* __restrict__ w, uint8_t* __r
   wr[idx] = fx < KW ? to_byte<T>(w[(((long long)oc * 64 + ic) * KH + fy) * KW + fx]) : (uint8_t)0;
 }
 
+// filters for the few-channel im2col: w[OC][C][KH][KW] -> wr[OC][kpad], k = (fy*C + c)*8 + fx, zero elsewhere
+template <typename T>
+__global__ void repack_weight_fy_c_fx8_kernel(const T* __restrict__ w, uint8_t* __restrict__ wr, int OC, int C, int KH, int KW,
+                                              int kpad) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)OC * kpad) return;
+  const int k = (int)(idx % kpad), oc = (int)(idx / kpad);
+  const int fx = k & 7, seg = k >> 3;
+  uint8_t v = 0;
+  if (seg < KH * C && fx < KW) {
+    const int fy = seg / C, c = seg - fy * C;
+    v = to_byte<T>(w[(((long long)oc * C + c) * KH + fy) * KW + fx]);
+  }
+  wr[idx] = v;
+}
+
 // [rows][cols] bytes -> [cols][rows] bytes
 template <typename T>
 __global__ void transpose_to_u8_kernel(const T* __restrict__ src, uint8_t* __restrict__ dst, int rows, int cols) {
@@ -331,6 +347,17 @@ int repack_weight_pairs64(const void* w, int w_is_f32, void* wr, int OC, int KH,
     repack_weight_pairs_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)w, (uint8_t*)wr, OC, KH, KW);
   else
     repack_weight_pairs_kernel<uint8_t><<<blocks_for(total, 256), 256, 0, s>>>((const uint8_t*)w, (uint8_t*)wr, OC, KH, KW);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int repack_weight_fy_c_fx8(const void* w, int w_is_f32, void* wr, int OC, int C, int KH, int KW, int kpad, cudaStream_t s) {
+  const long long total = (long long)OC * kpad;
+  if (total == 0) return B200Q_OK;
+  if (w_is_f32)
+    repack_weight_fy_c_fx8_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)w, (uint8_t*)wr, OC, C, KH, KW, kpad);
+  else
+    repack_weight_fy_c_fx8_kernel<uint8_t><<<blocks_for(total, 256), 256, 0, s>>>((const uint8_t*)w, (uint8_t*)wr, OC, C, KH, KW, kpad);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

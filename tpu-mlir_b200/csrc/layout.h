@@ -12,6 +12,8 @@ int nchw_to_bordered_nhwc(const void* x, int x_is_f32, void* y, int N, int C, in
 int repack_weight_oihw(const void* w, int w_is_f32, void* wr, int OC, int IC, int KH, int KW, cudaStream_t s);
 // 64-channel filters, horizontally adjacent taps paired: [OC][64][KH][KW] -> [OC][KH][ceil(KW/2)][2][64]
 int repack_weight_pairs64(const void* w, int w_is_f32, void* wr, int OC, int KH, int KW, cudaStream_t s);
+// few-channel im2col order: [OC][C][KH][KW] -> [OC][kpad], k = (fy*C + c)*8 + fx
+int repack_weight_fy_c_fx8(const void* w, int w_is_f32, void* wr, int OC, int C, int KH, int KW, int kpad, cudaStream_t s);
 // [rows][cols] -> [cols][rows] bytes.
 int transpose_to_u8(const void* src, int src_is_f32, void* dst, int rows, int cols, cudaStream_t s);
 int f32_to_q8(const float* x, void* y, long long n, cudaStream_t s);
