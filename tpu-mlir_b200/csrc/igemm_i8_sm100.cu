@@ -35,12 +35,17 @@ constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legiti
 
 // PAIR: two CTAs of a cluster compute one 256 x BLOCK_N tile with tcgen05 cta_group::2; each CTA stages its own 128
 // rows of A and half of B's N rows, so a CTA pulls 1.5x fewer operand bytes per MMA through L2 and shared memory.
-template <int BLOCK_N, int STAGES, bool PAIR = false>
+// TAPW = 3: the three taps of a filter row share ONE activation block of 128 + 2 rows per stage (tap fx starts fx
+// rows into it), next to the three taps' weight tiles: a third of the activation traffic per MMA.
+template <int BLOCK_N, int STAGES, bool PAIR = false, int TAPW = 1>
 struct SmemLayout {
-  static constexpr int A_BYTES = BLOCK_M * BLOCK_K;
+  static constexpr int A_ROWS = BLOCK_M + (TAPW - 1);
+  static constexpr int A_BOX_BYTES = A_ROWS * BLOCK_K;                 // what the TMA box delivers
+  static constexpr int A_BYTES = (A_BOX_BYTES + 1023) & ~1023;         // B tiles stay 1024-byte aligned
   static constexpr int B_ROWS = PAIR ? BLOCK_N / 2 : BLOCK_N;  // rows of B this CTA stages
   static constexpr int B_BYTES = B_ROWS * BLOCK_K;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + TAPW * B_BYTES;
+  static constexpr int STAGE_TX = A_BOX_BYTES + TAPW * B_BYTES;        // bytes one CTA's loads deliver per stage
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;  // tmem ptr, abort flag
@@ -116,11 +121,12 @@ __device__ __forceinline__ bool fold_domain(int32_t sh, int32_t zp) {
   return false;
 }
 
-template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR>
-__global__ void __launch_bounds__(SmemLayout<BLOCK_N, STAGES, PAIR>::NUM_THREADS, 1)
+template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR, int TAPW>
+__global__ void __launch_bounds__(SmemLayout<BLOCK_N, STAGES, PAIR, TAPW>::NUM_THREADS, 1)
 igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const IGemmArgs args) {
-  using L = SmemLayout<BLOCK_N, STAGES, PAIR>;
+  using L = SmemLayout<BLOCK_N, STAGES, PAIR, TAPW>;
+  static_assert(TAPW == 1 || PAIR, "the tap-fused form exists for CTA pairs only");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = ptx::smem_u32(smem);
@@ -192,6 +198,32 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         // k-block inside the tap and the tap's row shift are counted, not divided: this loop is serial
         int kc = 0, fx = 0;
         int a_row = m0 - args.tap_org_h * args.row_pitch - args.tap_org_w;  // tap (0,0)
+        if (TAPW > 1) {
+          // one stage = the three taps of filter row fy at k-block kc: one 130-row activation block, three weight tiles
+          const int groups = num_kb / TAPW;
+          int fy = 0;
+          for (int g = 0; g < groups; ++g) {
+            ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, WAIT_BUDGET_NS);
+            if (!ok) break;
+            const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_TX);
+            const uint32_t lead_bar = ptx::map_to_cta(full_bar(stage), 0);
+            ptx::tma_load_2d_pair(sa, &tmap_a, lead_bar, kc * BLOCK_K, a_row);
+#pragma unroll
+            for (int t = 0; t < TAPW; ++t)
+              ptx::tma_load_2d_pair(sa + L::A_BYTES + t * L::B_BYTES, &tmap_b, lead_bar,
+                                    ((fy * TAPW + t) * args.kb_per_tap + kc) * BLOCK_K, n0 + (int)cta_rank * L::B_ROWS);
+            if (++kc == args.kb_per_tap) {
+              kc = 0;
+              ++fy;
+              a_row += args.row_pitch;
+            }
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        } else {
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, WAIT_BUDGET_NS);
           if (!ok) break;
@@ -220,6 +252,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             phase ^= 1u;
           }
         }
+        }
       }
     }
   } else if (warp == 1) {
@@ -240,18 +273,29 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < num_kb / TAPW; ++kb) {
           ok = ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, 3, WAIT_BUDGET_NS);
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t so = (uint32_t)stage * (uint32_t)(L::STAGE_BYTES >> 4);  // descriptor address units of 16 bytes
           const uint32_t accum = kb != 0 ? 1u : 0u;
-          if (PAIR) {
-            if (DIALECT == KIND_BF16_TAG) ptx::umma_kblock_f16_pair(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, args.idesc, accum);
-            else ptx::umma_kblock_i8_pair(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, args.idesc, accum);
+          if (TAPW > 1) {
+#pragma unroll
+            for (int t = 0; t < TAPW; ++t) {
+              // tap t reads the activation block from row t on: only the start address moves.  The 128-byte swizzle is
+              // a function of the shared-memory address bits, which TMA used when it wrote the block, so no
+              // base-offset correction is needed (measured: setting the descriptor's base-offset field breaks it).
+              const uint32_t al = a_lo0 + so + (uint32_t)(t * (BLOCK_K >> 4));
+              const uint32_t bl = b_lo0 + so + (uint32_t)(t * (L::B_BYTES >> 4));
+              if (DIALECT == KIND_BF16_TAG) ptx::umma_kblock_f16_pair(d_tmem, al, bl, desc_hi, desc_hi, args.idesc, (t | (int)accum) != 0 ? 1u : 0u);
+              else ptx::umma_kblock_i8_pair(d_tmem, al, bl, desc_hi, desc_hi, args.idesc, (t | (int)accum) != 0 ? 1u : 0u);
+            }
+          } else if (PAIR) {
+            if (DIALECT == KIND_BF16_TAG) ptx::umma_kblock_f16_pair(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, desc_hi, args.idesc, accum);
+            else ptx::umma_kblock_i8_pair(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, desc_hi, args.idesc, accum);
           } else {
-            if (DIALECT == KIND_BF16_TAG) ptx::umma_kblock_f16(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, args.idesc, accum);
-            else ptx::umma_kblock_i8(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, args.idesc, accum);
+            if (DIALECT == KIND_BF16_TAG) ptx::umma_kblock_f16(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, desc_hi, args.idesc, accum);
+            else ptx::umma_kblock_i8(d_tmem, a_lo0 + so, b_lo0 + so, desc_hi, desc_hi, args.idesc, accum);
           }
           // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
           if (PAIR) ptx::umma_commit_pair(empty_bar(stage), 3);
@@ -651,10 +695,10 @@ int make_tmap_u8_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
   return make_tmap_u8(map, base, 2, dims, strides, box);
 }
 
-template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR>
+template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR, int TAPW>
 int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& args, int workers, cudaStream_t stream) {
-  using L = SmemLayout<BLOCK_N, STAGES, PAIR>;
-  auto kfn = igemm_i8_kernel<BLOCK_N, STAGES, DIALECT, RMODE, PAIR>;
+  using L = SmemLayout<BLOCK_N, STAGES, PAIR, TAPW>;
+  auto kfn = igemm_i8_kernel<BLOCK_N, STAGES, DIALECT, RMODE, PAIR, TAPW>;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(PAIR ? 2 * workers : workers);
@@ -672,15 +716,15 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& ar
   return B200Q_OK;
 }
 
-template <int BLOCK_N, int STAGES, bool PAIR>
+template <int BLOCK_N, int STAGES, bool PAIR, int TAPW = 1>
 int launch_dialect(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& a, int workers, cudaStream_t s) {
   const int d = a.epi.dialect, r = a.epi.round_mode;
-  if (a.bf16) return launch_one<BLOCK_N, STAGES, KIND_BF16_TAG, -1, PAIR>(ta, tb, a, workers, s);
+  if (a.bf16) return launch_one<BLOCK_N, STAGES, KIND_BF16_TAG, -1, PAIR, TAPW>(ta, tb, a, workers, s);
   if (d == B200Q_RQ_MULTIPLIER_SHIFT && r == B200Q_ROUND_HALF_UP)
-    return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP, PAIR>(ta, tb, a, workers, s);
+    return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP, PAIR, TAPW>(ta, tb, a, workers, s);
   if (d == B200Q_RQ_QDM && r == B200Q_ROUND_HALF_AWAY_FROM_ZERO)
-    return launch_one<BLOCK_N, STAGES, B200Q_RQ_QDM, B200Q_ROUND_HALF_AWAY_FROM_ZERO, PAIR>(ta, tb, a, workers, s);
-  return launch_one<BLOCK_N, STAGES, -1, -1, PAIR>(ta, tb, a, workers, s);
+    return launch_one<BLOCK_N, STAGES, B200Q_RQ_QDM, B200Q_ROUND_HALF_AWAY_FROM_ZERO, PAIR, TAPW>(ta, tb, a, workers, s);
+  return launch_one<BLOCK_N, STAGES, -1, -1, PAIR, TAPW>(ta, tb, a, workers, s);
 }
 
 }  // namespace
@@ -709,6 +753,15 @@ int make_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* d
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(B200Q_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
   return B200Q_OK;
+}
+
+// B200Q_IGEMM_TAPFUSE=0 in the environment keeps 3-tap filter rows on one activation load per tap (for A/B timing).
+static bool tapfuse_allowed() {
+  static const bool on = [] {
+    const char* v = getenv("B200Q_IGEMM_TAPFUSE");
+    return !(v && v[0] == '0');
+  }();
+  return on;
 }
 
 // B200Q_IGEMM_PAIR=0 in the environment keeps every launch on single-CTA tiles (for A/B timing).
@@ -776,6 +829,8 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const long long tiles128 = (long long)((p.rows + BLOCK_M - 1) / BLOCK_M) * ((p.n + block_n - 1) / block_n);
   const bool pair = block_n == 256 && pair_mode_allowed() && tiles128 >= 2ll * sms;
+  // three taps per filter row, one pixel apart, no ragged K block: the taps of a row share one activation block
+  const bool tapfuse = pair && tapfuse_allowed() && p.taps_w == 3 && a.tap_step_w == 1 && p.k_per_tap % BLOCK_K == 0 && !a.bf16;
   const int tile_m = pair ? 2 * BLOCK_M : BLOCK_M;
   a.idesc = a.bf16 ? ptx::make_idesc(1u, 1u, 1u, tile_m, (uint32_t)block_n)  // f32 accumulate, bf16 x bf16
                    : ptx::make_idesc(2u, p.a_unsigned ? 0u : 1u, p.b_unsigned ? 0u : 1u, tile_m, (uint32_t)block_n);
@@ -785,7 +840,8 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   CUtensorMap ta, tb;
   // (a_pitch < k_per_tap: overlapping rows, each spanning several consecutive pixels; the caller keeps
   // k_per_tap - a_pitch readable bytes behind the last row)
-  int rc = make_tmap_u8_2d(&ta, p.a, (uint64_t)p.k_per_tap, (uint64_t)p.rows, (uint64_t)p.a_pitch, BLOCK_M);
+  int rc = make_tmap_u8_2d(&ta, p.a, (uint64_t)p.k_per_tap, (uint64_t)p.rows, (uint64_t)p.a_pitch,
+                           tapfuse ? BLOCK_M + 2 : BLOCK_M);
   if (rc) return rc;
   // B: [n][taps * k_per_tap]; with several taps k_per_tap is a multiple of BLOCK_K so blocks never straddle taps
   rc = make_tmap_u8_2d(&tb, p.b, (uint64_t)p.k_per_tap * p.taps_h * p.taps_w, (uint64_t)p.n, (uint64_t)p.b_pitch,
@@ -795,6 +851,7 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   const int tiles = a.num_m_tiles * a.num_n_tiles;
   const int slots = pair ? sms / 2 : sms;
   const int workers = tiles < slots ? tiles : slots;
+  if (tapfuse) return launch_dialect<256, 3, true, 3>(ta, tb, a, workers, stream);
   if (pair) return launch_dialect<256, 6, true>(ta, tb, a, workers, stream);
   switch (block_n) {
     case 256: return launch_dialect<256, 4, false>(ta, tb, a, workers, stream);

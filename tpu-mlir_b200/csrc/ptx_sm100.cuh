@@ -228,37 +228,38 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
 // ---------------------------------------------------------------- one k-block (128 bytes of K) = four MMAs, one asm block
 // The MMA-issuing thread is a single-thread serial loop; at ~60 dependent instructions per k-block it, not the
 // tensor pipe, sets the pace.  This form takes the descriptors as 32-bit halves (the high word is the same for every
-// K-major 128-byte-swizzled tile), advances K by +2 (32 bytes) on the low word and needs ~12 instructions per k-block.
+// K-major 128-byte-swizzled tile, up to the base-offset field of a tile that starts inside an 8-row swizzle group),
+// advances K by +2 (32 bytes) on the low word and needs ~12 instructions per k-block.
 #define B200Q_DEFINE_UMMA_KBLOCK(NAME, GROUP, KIND)                                                                   \
-  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc, \
-                                       uint32_t accumulate_first) {                                                     \
+  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t a_hi, uint32_t b_hi,     \
+                                       uint32_t idesc, uint32_t accumulate_first) {                                     \
     asm volatile(                                                                                                       \
         "{\n\t"                                                                                                         \
         ".reg .pred p;\n\t"                                                                                             \
         ".reg .b32 al, bl;\n\t"                                                                                         \
         ".reg .b64 da, db;\n\t"                                                                                         \
-        "setp.ne.b32 p, %5, 0;\n\t"                                                                                     \
+        "setp.ne.b32 p, %6, 0;\n\t"                                                                                     \
         "mov.b64 da, {%1, %3};\n\t"                                                                                     \
-        "mov.b64 db, {%2, %3};\n\t"                                                                                     \
-        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, p;\n\t"                                      \
-        "setp.eq.b32 p, %4, %4;\n\t"                                                                                    \
+        "mov.b64 db, {%2, %4};\n\t"                                                                                     \
+        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %5, p;\n\t"                                      \
+        "setp.eq.b32 p, %5, %5;\n\t"                                                                                    \
         "add.u32 al, %1, 2;\n\t"                                                                                        \
         "add.u32 bl, %2, 2;\n\t"                                                                                        \
         "mov.b64 da, {al, %3};\n\t"                                                                                     \
-        "mov.b64 db, {bl, %3};\n\t"                                                                                     \
-        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, p;\n\t"                                      \
+        "mov.b64 db, {bl, %4};\n\t"                                                                                     \
+        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %5, p;\n\t"                                      \
         "add.u32 al, %1, 4;\n\t"                                                                                        \
         "add.u32 bl, %2, 4;\n\t"                                                                                        \
         "mov.b64 da, {al, %3};\n\t"                                                                                     \
-        "mov.b64 db, {bl, %3};\n\t"                                                                                     \
-        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, p;\n\t"                                      \
+        "mov.b64 db, {bl, %4};\n\t"                                                                                     \
+        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %5, p;\n\t"                                      \
         "add.u32 al, %1, 6;\n\t"                                                                                        \
         "add.u32 bl, %2, 6;\n\t"                                                                                        \
         "mov.b64 da, {al, %3};\n\t"                                                                                     \
-        "mov.b64 db, {bl, %3};\n\t"                                                                                     \
-        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %4, p;\n\t"                                      \
+        "mov.b64 db, {bl, %4};\n\t"                                                                                     \
+        "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %5, p;\n\t"                                      \
         "}\n" ::"r"(d_tmem),                                                                                            \
-        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first)                                           \
+        "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi), "r"(idesc), "r"(accumulate_first)                                   \
         : "memory");                                                                                                    \
   }
 B200Q_DEFINE_UMMA_KBLOCK(umma_kblock_i8, "1", "i8")
