@@ -257,8 +257,24 @@ struct ConvHandle {
     ++runs_recorded;
     return B200Q_OK;
   }
+  // operator face: host copies pipelined over pieces of the batch (copy-in, compute, copy-out streams)
+  cudaStream_t pipe[3] = {nullptr, nullptr, nullptr};
+  std::vector<cudaEvent_t> pipe_ev;
+  int ensure_pipe(int pieces) {
+    for (int i = 0; i < 3; ++i)
+      if (!pipe[i]) CUDA_TRY(cudaStreamCreateWithFlags(&pipe[i], cudaStreamNonBlocking));
+    while ((int)pipe_ev.size() < 2 * pieces) {
+      cudaEvent_t e;
+      CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+      pipe_ev.push_back(e);
+    }
+    return B200Q_OK;
+  }
   ~ConvHandle() {
     for (auto& e : events) cudaEventDestroy(e);
+    for (auto& e : pipe_ev) cudaEventDestroy(e);
+    for (auto& st : pipe)
+      if (st) cudaStreamDestroy(st);
   }
 };
 
@@ -359,13 +375,16 @@ int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int
 }
 
 // x: device NCHW (bytes, or float holding integers); y: device NCHW native out dtype
-int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s) {
+// `images` < 0: the whole batch of the descriptor; otherwise the first `images` images of x / y (the operator face
+// pipelines its host copies over pieces of the batch)
+int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s, long long images = -1) {
   const b200q_conv2d_desc& d = h->d;
-  if (d.n == 0) return B200Q_OK;
+  const long long nb = images < 0 ? (long long)d.n : images;
+  if (nb == 0) return B200Q_OK;
   if (h->profiling && (h->use_tc || h->use_im2col)) B200Q_TRY(h->next_triple());
   if (h->use_tc) {
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[0], s));
-    B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
+    B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)nb, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[1], s));
     IGemmProblem p{};
     p.a = h->x_bordered.p;
@@ -374,7 +393,7 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.b_unsigned = 0;
     p.a_pitch = d.ic;
     p.b_pitch = d.ic * d.kh * d.kw;
-    p.rows = (int)((long long)d.n * h->Hp * h->Wp);
+    p.rows = (int)(nb * h->Hp * h->Wp);
     p.n = (int)d.oc;
     p.k_per_tap = (int)d.ic;
     p.taps_h = (int)d.kh;
@@ -406,16 +425,16 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[0], s));
     if (h->few_channels) {
       // few input channels (a network's stem): rows are built from 8-byte runs of the NCHW input
-      B200Q_TRY(im2col_few_channels_launch(x, x_is_f32, h->a_cols.p, d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->g.oh, h->g.ow,
+      B200Q_TRY(im2col_few_channels_launch(x, x_is_f32, h->a_cols.p, nb, (int)d.ic, (int)d.ih, (int)d.iw, h->g.oh, h->g.ow,
                                            (int)d.kh, (int)d.sh, (int)d.sw, (int)d.pht, (int)d.pwl, h->kpad, s));
     } else if (d.ic <= 4) {
       // few input channels, other geometry: rows are gathered byte by byte straight from the NCHW input
-      B200Q_TRY(im2col_nchw_small_c_launch(x, x_is_f32, h->a_cols.p, d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->g.oh, h->g.ow,
+      B200Q_TRY(im2col_nchw_small_c_launch(x, x_is_f32, h->a_cols.p, nb, (int)d.ic, (int)d.ih, (int)d.iw, h->g.oh, h->g.ow,
                                            (int)d.kh, (int)d.kw, (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, (int)d.pht,
                                            (int)d.pwl, h->kpad, s));
     } else {
-      B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)d.n, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
-      B200Q_TRY(im2col_nhwc_launch(h->x_bordered.p, h->a_cols.p, d.n, (int)d.ic, h->Hp, h->Wp, h->g.oh, h->g.ow, (int)d.kh,
+      B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)nb, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
+      B200Q_TRY(im2col_nhwc_launch(h->x_bordered.p, h->a_cols.p, nb, (int)d.ic, h->Hp, h->Wp, h->g.oh, h->g.ow, (int)d.kh,
                                    (int)d.kw, (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, h->bh - (int)d.pht,
                                    h->bw - (int)d.pwl, h->kpad, s));
     }
@@ -425,7 +444,7 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.b = h->w_packed.p;
     p.a_unsigned = d.input_dtype == B200Q_DT_U8;
     p.a_pitch = p.b_pitch = h->kpad;
-    p.rows = (int)((long long)d.n * h->g.oh * h->g.ow);
+    p.rows = (int)(nb * h->g.oh * h->g.ow);
     p.n = (int)d.oc;
     p.k_per_tap = h->kpad;
     p.taps_h = p.taps_w = 1;
@@ -441,12 +460,14 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
   }
   const void* xin = x;
   if (x_is_f32) {
-    const long long n = (long long)d.n * d.ic * d.ih * d.iw;
+    const long long n = nb * d.ic * d.ih * d.iw;
     B200Q_TRY(h->x_q8.ensure((size_t)n));
     B200Q_TRY(f32_to_q8((const float*)x, h->x_q8.p, n, s));
     xin = h->x_q8.p;
   }
-  return conv2d_i8_direct_launch(xin, d.input_dtype == B200Q_DT_U8, h->w_oihw.as<int8_t>(), h->g, h->epi, y, s);
+  ConvGeometry g = h->g;
+  g.n = (int)nb;
+  return conv2d_i8_direct_launch(xin, d.input_dtype == B200Q_DT_U8, h->w_oihw.as<int8_t>(), g, h->epi, y, s);
 }
 
 }  // namespace
@@ -612,13 +633,50 @@ int b200q_conv2d_inference(const b200q_conv2d_desc* desc, float* const* inputs, 
   B200Q_TRY(h->x_f32.ensure(x_elems * 4));
   B200Q_TRY(h->y_q.ensure(y_elems * dtype_size(d.out_dtype)));
   B200Q_TRY(h->y_f32.ensure(y_elems * 4));
-  CUDA_TRY(cudaMemcpyAsync(h->x_f32.p, inputs[0], x_elems * 4, cudaMemcpyHostToDevice, s));
-  int rc = conv_run(h, h->x_f32.p, 1, h->y_q.p, s);
-  if (rc == B200Q_OK) rc = q_to_f32(h->y_q.p, d.out_dtype, h->y_f32.as<float>(), (long long)y_elems, s);
-  if (rc == B200Q_OK && cudaMemcpyAsync(outputs[0], h->y_f32.p, y_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess)
-    rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__);
-  if (rc == B200Q_OK) rc = read_status(h->status, s, "conv2d");
-  else cudaStreamSynchronize(s);
+  // The float ABI makes this call a PCIe transfer with a convolution in the middle: the batch is cut into pieces so
+  // that the upload of piece i+1, the kernels of piece i and the download of piece i-1 overlap (both directions of
+  // the link at once; the host buffers should be pinned for that).
+  const size_t xi = (size_t)d.ic * d.ih * d.iw, yi = (size_t)d.oc * h->g.oh * h->g.ow;  // elements per image
+  const long long min_imgs = (long long)((((size_t)8 << 20) + xi * 4 - 1) / (xi * 4));    // pieces of >= 8 MB
+  long long per = d.n / 8 > min_imgs ? d.n / 8 : min_imgs;
+  if (per > d.n) per = d.n;
+  const int pieces = (int)((d.n + per - 1) / per);
+  int rc = B200Q_OK;
+  if (pieces <= 1) {
+    CUDA_TRY(cudaMemcpyAsync(h->x_f32.p, inputs[0], x_elems * 4, cudaMemcpyHostToDevice, s));
+    rc = conv_run(h, h->x_f32.p, 1, h->y_q.p, s);
+    if (rc == B200Q_OK) rc = q_to_f32(h->y_q.p, d.out_dtype, h->y_f32.as<float>(), (long long)y_elems, s);
+    if (rc == B200Q_OK && cudaMemcpyAsync(outputs[0], h->y_f32.p, y_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess)
+      rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__);
+    if (rc == B200Q_OK) rc = read_status(h->status, s, "conv2d");
+    else cudaStreamSynchronize(s);
+    return rc;
+  }
+  CUDA_TRY(cudaStreamSynchronize(s));  // whatever the caller queued on the default stream comes first
+  B200Q_TRY(h->ensure_pipe(pieces));
+  cudaStream_t s_in = h->pipe[0], s_cmp = h->pipe[1], s_out = h->pipe[2];
+  const size_t ysz = dtype_size(d.out_dtype);
+  for (int c = 0; c < pieces && rc == B200Q_OK; ++c) {
+    const long long i0 = (long long)c * per, cnt = (i0 + per <= d.n) ? per : d.n - i0;
+    float* xd = h->x_f32.as<float>() + (size_t)i0 * xi;
+    uint8_t* yq = h->y_q.as<uint8_t>() + (size_t)i0 * yi * ysz;
+    float* yd = h->y_f32.as<float>() + (size_t)i0 * yi;
+    CUDA_TRY(cudaMemcpyAsync(xd, inputs[0] + (size_t)i0 * xi, (size_t)cnt * xi * 4, cudaMemcpyHostToDevice, s_in));
+    CUDA_TRY(cudaEventRecord(h->pipe_ev[2 * c], s_in));
+    CUDA_TRY(cudaStreamWaitEvent(s_cmp, h->pipe_ev[2 * c], 0));
+    rc = conv_run(h, xd, 1, yq, s_cmp, cnt);
+    if (rc == B200Q_OK) rc = q_to_f32(yq, d.out_dtype, yd, (long long)((size_t)cnt * yi), s_cmp);
+    if (rc != B200Q_OK) break;
+    CUDA_TRY(cudaEventRecord(h->pipe_ev[2 * c + 1], s_cmp));
+    CUDA_TRY(cudaStreamWaitEvent(s_out, h->pipe_ev[2 * c + 1], 0));
+    CUDA_TRY(cudaMemcpyAsync(outputs[0] + (size_t)i0 * yi, yd, (size_t)cnt * yi * 4, cudaMemcpyDeviceToHost, s_out));
+  }
+  if (rc == B200Q_OK) {
+    CUDA_TRY(cudaStreamSynchronize(s_out));
+    rc = read_status(h->status, s_cmp, "conv2d");
+  } else {
+    for (auto& st : h->pipe) cudaStreamSynchronize(st);
+  }
   return rc;
 }
 
