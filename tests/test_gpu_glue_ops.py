@@ -107,3 +107,24 @@ def test_requant_int_operator_face():
         out = np.zeros(x.shape, np.float32)
         L.check(lib().b200q_requant_int_axis_inference(C.byref(d), L.float_pp([x.astype(np.float32)]), 1, L.float_pp([out]), 1))
         assert np.array_equal(out, want.astype(np.float32))
+
+
+def test_executor_loads_mlir_text(tmp_path):
+    """The same small graph through module.load(dict) and module.load(<file>.mlir) gives identical tensors."""
+    from test_mlir_text import small_graph
+    from tpu_mlir_b200 import mlir_text as MT
+    from tpu_mlir_b200.module import module
+    graph, weights = small_graph()
+    (tmp_path / "m.mlir").write_text(MT.emit_module(graph, weights, weight_file="w.npz"))
+    np.savez(tmp_path / "w.npz", **weights)
+    x = np.random.default_rng(3).standard_normal((2, 3, 8, 8)).astype(np.float32)
+    outs = []
+    for src in ((graph, weights), (str(tmp_path / "m.mlir"), None)):
+        m = module()
+        m.load(*src)
+        m.set_tensor("input", x)
+        m.invoke()
+        outs.append({n: m.get_tensor(n) for n in ("conv", "pool", "sum", "fc", "output")})
+    for n in outs[0]:
+        assert np.array_equal(outs[0][n], outs[1][n]), n
+    assert outs[0]["fc"].any()

@@ -5,8 +5,8 @@ bindings/pymlir/host/ModuleInterpreter.cpp:396-492,:631-1012, bindings/pymlir/py
 Method names and meaning follow ``pymlir.module``: ``load, set_tensor, invoke, get_tensor, get_fp32_tensor,
 get_all_tensor, before_invoke / after_invoke hooks, get_tensor_qinfo, input_names, output_names,
 all_tensor_names``.  Tensors live on the device in their native storage type (like ``py_cuda``), ops run in graph
-order through the device face of libb200q.so.  Because no MLIR parser is available here, a graph is a plain
-dict whose op types and attribute names are the Tpu dialect's:
+order through the device face of libb200q.so.  A graph is a plain dict whose op types and attribute names are the Tpu
+dialect's (``load`` also takes the path of a lowered model's ``.mlir`` text and reads it into this form, mlir_text.py):
 
     {"inputs": [...], "outputs": [...],
      "tensors": {name: {"shape": [...], "dtype": "f32|i8|u8|i32", "scale": s, "zp": z}},
@@ -48,8 +48,14 @@ class module:  # noqa: N801  (name of the reference class)
         self._after: List[Callable] = []
 
     # ------------------------------------------------------------------ loading
-    def load(self, graph: dict, weights: Dict[str, np.ndarray]):
+    def load(self, graph, weights: Optional[Dict[str, np.ndarray]] = None):
+        """``graph`` is the dict described above, or the path of a lowered model's ``.mlir`` text (module state
+        TPU_LOWERED); in that case ``weights`` may name the weight file, else the module's ``module.weight_file``
+        attribute is followed (mlir_text.load_mlir)."""
         torch = self.torch
+        if isinstance(graph, str):
+            from .mlir_text import load_mlir
+            graph, weights = load_mlir(graph, weights if isinstance(weights, str) else None)
         self.graph = graph
         self.input_names = list(graph["inputs"])
         self.output_names = list(graph["outputs"])
