@@ -61,6 +61,29 @@ def test_histogram_matches_oracle_many_bin_counts(m, bins):
     assert np.array_equal(got, want) and got.sum() < np.count_nonzero(x)
 
 
+def test_histogram_quotient_is_exact_for_many_widths(m):
+    """The kernel forms t / width from a reciprocal and two FMAs; the counts must equal float32 division for widths of
+    every magnitude, values on bin boundaries, and the widths (significand all ones) that take the dividing path."""
+    rng = np.random.default_rng(99)
+    bins = 2048
+    for i in range(48):
+        if i < 40:
+            th = np.float32(10.0 ** rng.uniform(-20, 20) * rng.uniform(1, 10))
+        else:   # width = th / 2047 with an all-ones significand: th = width * 2047 rounded, then checked
+            w = np.nextafter(np.float32(2.0 ** rng.integers(-10, 10)), np.float32(0))
+            th = np.float32(w * np.float32(bins - 1))
+        width = np.float32(th) / np.float32(bins - 1)
+        k = rng.integers(0, bins, 60000).astype(np.float32)
+        # values at and just around the rounding boundaries (k +- 0.5) * width, plus random ones
+        x = np.concatenate([(k + np.float32(0.5)) * width, np.nextafter((k + np.float32(0.5)) * width, np.float32(0)),
+                            np.nextafter((k + np.float32(0.5)) * width, np.float32(np.inf)),
+                            rng.uniform(0, float(th), 60000).astype(np.float32)]).astype(np.float32)
+        x *= rng.choice(np.array([-1, 1], np.float32), x.size)
+        want, _ = oracle.histogram(x, th, bins)
+        got, _ = m.histogram(x, th, bins)
+        assert np.array_equal(got, want), (i, float(th))
+
+
 def test_histogram_batch_with_schedule(m):
     rng = np.random.default_rng(3)
     S, n = 9, 5000

@@ -131,10 +131,23 @@ histogram_kernel(const float* __restrict__ x, long long n, const float* __restri
   const float* xs = x + (long long)s * n;
   const long long n4 = ((reinterpret_cast<uintptr_t>(xs) & 15) == 0) ? n / 4 : 0;
   const float4* x4 = reinterpret_cast<const float4*>(xs);
+  // t / width, correctly rounded, without a division per element: with r = RN(1/width), q0 = RN(t*r),
+  // rem = t - q0*width (exact in an FMA) and q = RN(q0 + rem*r) is the correctly rounded quotient (Markstein) unless
+  // width's significand is all ones; that case, and widths whose reciprocal is not a normal number, divide.
+  const float rw = __frcp_rn(width);
+  const uint32_t wbits = __float_as_uint(width);
+  const bool quick = (wbits & 0x007fffffu) != 0x007fffffu && width >= 1e-30f && width <= 1e30f;
   auto one = [&](float v) {
     const float t = fabsf(v);
     if (!(t > 0.f)) return;  // zeros are excluded (cali_math.py:70); NaN falls out here too
-    const float k = floorf(__fadd_rn(__fdiv_rn(t, width), 0.5f));
+    float q;
+    if (quick) {
+      const float q0 = __fmul_rn(t, rw);
+      q = __fmaf_rn(__fmaf_rn(-q0, width, t), rw, q0);
+    } else {
+      q = __fdiv_rn(t, width);
+    }
+    const float k = floorf(__fadd_rn(q, 0.5f));
     if (!(k <= binsm1)) return;  // outside range=(0, bins-1): dropped by numpy.histogram
     atomicAdd(&dst[numpy_bin(k, bins, binsf, step)], 1);
   };
