@@ -184,6 +184,13 @@ void b200q_conv2d_deinit(void **handle);
 int b200q_conv2d_dev_create(const b200q_conv2d_desc *desc, const void *filter_oihw_s8, const int32_t *bias_s32,
                             void **handle);
 int b200q_conv2d_dev_run(void *handle, const void *x_nchw, void *y_nchw, void *stream);
+/* The same run with the activation layouts named: B200Q_LAYOUT_NHWC tensors are [N][H][W][C] bytes (channels a
+ * multiple of 16, 16-byte aligned).  A graph that keeps its activations channels-last between ops runs no
+ * transposing kernel: a 1x1 stride-1 filter reads x in place, other filters copy it into the zero-bordered
+ * image, and the output is stored as whole channel runs.  Only the tensor-core routes take NHWC tensors
+ * (B200Q_ERR_UNSUPPORTED otherwise).  The values are those of b200q_conv2d_dev_run, permuted. */
+enum { B200Q_LAYOUT_NCHW = 0, B200Q_LAYOUT_NHWC = 1 };
+int b200q_conv2d_dev_run_layout(void *handle, const void *x, int32_t x_layout, void *y, int32_t y_layout, void *stream);
 int b200q_conv2d_dev_status(void *handle, void *stream);
 void b200q_conv2d_dev_destroy(void **handle);
 /* Optional timing of the device face: while enabled, every b200q_conv2d_dev_run records CUDA events on its
@@ -228,6 +235,12 @@ int b200q_add_i8_dev(const void *a, int32_t a_dtype, const void *b, int32_t b_dt
 int b200q_pool2d_i8_dev(const void *x, int32_t dtype, int64_t nc, int32_t ih, int32_t iw, int32_t kh, int32_t kw,
                         int32_t sh, int32_t sw, int32_t pht, int32_t phb, int32_t pwl, int32_t pwr, int32_t is_avg,
                         int32_t multiplier, int32_t rshift, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
+/* The same op on a channels-last tensor x [n][ih][iw][c] -> out [n][oh][ow][c] (max pooling: equal 8-bit types,
+ * c a multiple of 16, 16-byte aligned buffers). */
+int b200q_pool2d_i8_nhwc_dev(const void *x, int32_t dtype, int64_t n, int32_t c, int32_t ih, int32_t iw, int32_t kh,
+                             int32_t kw, int32_t sh, int32_t sw, int32_t pht, int32_t phb, int32_t pwl, int32_t pwr,
+                             int32_t is_avg, int32_t multiplier, int32_t rshift, int32_t do_relu, int32_t out_dtype,
+                             void *out, void *stream);
 /* tpu.Cast f32 <-> int8/uint8 (Cast.cpp:75-116, lib/Support/CastUtils.cpp:15-47):
  * q = saturate(to_int(round(x * (float)(1/scale)) + zp, round_mode));  x = (float)scale * (q - zp). */
 int b200q_cast_f32_to_q8_dev(const float *x, int64_t count, double scale, int32_t zero_point, int32_t round_mode,

@@ -133,6 +133,59 @@ def test_conv_device_face_matches_operator_face():
     assert np.array_equal(y_d.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("case", [
+    dict(N=2, C=64, H=14, W=14, OC=256, k=1, stride=(1, 1), pads=(0, 0, 0, 0)),     # 1x1: x is read in place
+    dict(N=3, C=128, H=13, W=11, OC=80, k=3, stride=(1, 1), pads=(1, 1, 1, 1)),     # 3x3 through the bordered image
+    dict(N=2, C=64, H=12, W=20, OC=64, k=3, stride=(1, 1), pads=(1, 1, 1, 1)),      # 64 channels: paired taps
+    dict(N=2, C=128, H=9, W=8, OC=48, k=3, stride=(1, 1), pads=(0, 0, 0, 0)),       # "valid" 3x3 read in place
+    dict(N=2, C=128, H=14, W=14, OC=128, k=3, stride=(2, 2), pads=(1, 1, 1, 1)),    # strided 3x3: im2col rows
+    dict(N=2, C=256, H=14, W=14, OC=512, k=1, stride=(2, 2), pads=(0, 0, 0, 0)),    # strided 1x1 (a downsample branch)
+    dict(N=1, C=32, H=7, W=9, OC=272, k=1, stride=(1, 1), pads=(0, 0, 0, 0)),       # ragged channel tile
+])
+@pytest.mark.parametrize("layouts", [(1, 1), (0, 1), (1, 0)])
+def test_conv_device_face_channels_last(case, layouts):
+    """b200q_conv2d_dev_run_layout: the same values as the NCHW run, for every mix of input and output layout."""
+    c = synth.conv2d_int8(seed=case["C"] + case["OC"] + case["H"], N=case["N"], C=case["C"], H=case["H"], W=case["W"],
+                          OC=case["OC"], KH=case["k"], KW=case["k"], unsigned_input=True)
+    c["w"] = np.clip(c["w"] // 2, -127, 127).astype(np.int8)
+    c["mult"] = np.random.default_rng(1).integers(5000, 30000, size=case["OC"])
+    c["rshift"] = np.random.default_rng(2).integers(18, 26, size=case["OC"])
+    want, mult, rshift = oracle_conv(c, stride=case["stride"], pads=case["pads"], qmode=oracle.QM_MULTIPLIER_SHIFT,
+                                     out_dt=oracle.DT_U8)
+    d = Conv2DOp(input_shape=c["x"].shape, oc=case["OC"], kernel_shape=(case["k"], case["k"]), strides=case["stride"],
+                 pads=case["pads"], do_relu=True, input_dtype=L.DT_U8, out_dtype=L.DT_U8, quant_mode=L.QM_MULTIPLIER_SHIFT,
+                 multiplier=mult, rshift=rshift).desc
+    xl, yl = layouts
+    x = c["x"].transpose(0, 2, 3, 1) if xl else c["x"]
+    w_d, b_d, x_d = dev(c["w"]), dev(c["bias"]), dev(np.ascontiguousarray(x))
+    y_shape = (want.shape[0], want.shape[2], want.shape[3], want.shape[1]) if yl else want.shape
+    y_d = torch.full(y_shape, 77, dtype=torch.uint8, device="cuda")
+    h = C.c_void_p()
+    lib = L.lib()
+    L.check(lib.b200q_conv2d_dev_create(C.byref(d), ptr(w_d), ptr(b_d), C.byref(h)))
+    for _ in range(2):
+        L.check(lib.b200q_conv2d_dev_run_layout(h, ptr(x_d), xl, ptr(y_d), yl, None))
+    L.check(lib.b200q_conv2d_dev_status(h, None))
+    lib.b200q_conv2d_dev_destroy(C.byref(h))
+    got = y_d.cpu().numpy()
+    assert np.array_equal(got.transpose(0, 3, 1, 2) if yl else got, want)
+
+
+def test_conv_channels_last_needs_a_tensor_core_route():
+    rng = np.random.default_rng(5)
+    w = rng.integers(-127, 128, size=(16, 1, 3, 3), dtype=np.int8)
+    d = Conv2DOp(input_shape=(1, 16, 8, 8), oc=16, kernel_shape=(3, 3), pads=(1, 1, 1, 1), group=16,
+                 quant_mode=L.QM_MULTIPLIER_SHIFT, multiplier=[1000] * 16, rshift=[12] * 16, with_bias=False).desc
+    w_d = dev(w)
+    x_d, y_d = torch.zeros(1, 8, 8, 16, dtype=torch.int8, device="cuda"), torch.zeros(1, 8, 8, 16, dtype=torch.int8, device="cuda")
+    h = C.c_void_p()
+    lib = L.lib()
+    L.check(lib.b200q_conv2d_dev_create(C.byref(d), ptr(w_d), None, C.byref(h)))
+    assert lib.b200q_conv2d_dev_run_layout(h, ptr(x_d), 1, ptr(y_d), 1, None) == L.ERR_UNSUPPORTED
+    assert lib.b200q_conv2d_dev_run_layout(h, ptr(x_d), 7, ptr(y_d), 0, None) == L.ERR_INVALID
+    lib.b200q_conv2d_dev_destroy(C.byref(h))
+
+
 def test_config1_full_size():
     """BASELINE config 1 at full size: N=32, C=256, 56x56, OC=256, 3x3, stride 1, pad 1, fused ReLU, QDM requant."""
     c = synth.conv2d_int8(seed=1)

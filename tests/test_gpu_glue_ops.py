@@ -58,6 +58,32 @@ def test_pool():
     assert np.array_equal(out.cpu().numpy(), want)
 
 
+def test_pool_channels_last():
+    """b200q_pool2d_i8_nhwc_dev: the NCHW op's values on [N][H][W][C] tensors."""
+    rng = np.random.default_rng(14)
+    for dt, lo, hi, relu in ((np.uint8, 0, 256, False), (np.int8, -128, 128, False), (np.int8, -128, 128, True)):
+        x = rng.integers(lo, hi, (3, 32, 17, 14), dtype=dt)
+        odt = L.DT_U8 if dt == np.uint8 else L.DT_I8
+        for kernel, stride, pads in (((3, 3), (2, 2), (1, 1, 1, 1)), ((2, 3), (1, 2), (0, 1, 1, 0))):
+            want = oracle.pool2d_int8(x, kernel, stride, pads, mode="max", do_relu=relu)
+            x_d = dev(np.ascontiguousarray(x.transpose(0, 2, 3, 1)))
+            out = empty_dev((want.shape[0], want.shape[2], want.shape[3], want.shape[1]), odt)
+            # oracle pads are (top, bottom, left, right), the order of the C arguments
+            L.check(lib().b200q_pool2d_i8_nhwc_dev(ptr(x_d), odt, 3, 32, 17, 14, kernel[0], kernel[1], stride[0], stride[1],
+                                                   pads[0], pads[1], pads[2], pads[3], 0, 1, 0, int(relu), odt, ptr(out), None))
+            assert np.array_equal(out.cpu().numpy().transpose(0, 3, 1, 2), want), (dt, kernel)
+    xs = rng.integers(-128, 128, (2, 24, 7, 7), dtype=np.int8)
+    want = oracle.pool2d_int8(xs, (7, 7), (1, 1), (0, 0, 0, 0), mode="avg", multi=83, rshift=12, do_relu=True)
+    xs_d = dev(np.ascontiguousarray(xs.transpose(0, 2, 3, 1)))
+    out = empty_dev((2, 1, 1, 24), L.DT_I8)
+    L.check(lib().b200q_pool2d_i8_nhwc_dev(ptr(xs_d), L.DT_I8, 2, 24, 7, 7, 7, 7, 1, 1, 0, 0, 0, 0, 1, 83, 12, 1, L.DT_I8,
+                                           ptr(out), None))
+    assert np.array_equal(out.cpu().numpy().transpose(0, 3, 1, 2), want)
+    # max pooling of a channel count that is not a multiple of 16 is refused, not silently mis-indexed
+    assert lib().b200q_pool2d_i8_nhwc_dev(ptr(xs_d), L.DT_I8, 2, 24, 7, 7, 3, 3, 1, 1, 0, 0, 0, 0, 0, 1, 0, 0, L.DT_I8,
+                                          ptr(out), None) == L.ERR_UNSUPPORTED
+
+
 def test_cast_both_ways():
     rng = np.random.default_rng(6)
     x = (rng.standard_normal(50001) * 3).astype(np.float32)

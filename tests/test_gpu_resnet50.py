@@ -19,16 +19,19 @@ def lowered():
     return ops, table, graph, weights
 
 
-def test_int8_graph_matches_oracle_on_every_tensor(lowered):
+@pytest.mark.parametrize("channels_last", [False, True])
+def test_int8_graph_matches_oracle_on_every_tensor(lowered, channels_last):
     ops, table, graph, weights = lowered
     x = synth.calibration_images(seed=33, count=2)
-    m = module()
+    m = module(channels_last=channels_last)
     m.load(graph, weights)
     seen = []
     m.after_invoke(lambda name: seen.append(name))
     m.set_tensor("input", x)
     m.invoke()
     assert seen == [op["name"] for op in graph["ops"]]
+    if channels_last:   # every activation between the stem and the classifier lives as [N][H][W][C]
+        assert len(m._nhwc) > 60 and tuple(m.tensors["conv1"].shape) == (2, 112, 112, 64)
     want = oracle_graph.run(graph, weights, {"input": x})
     types = {}
     for op in graph["ops"]:

@@ -17,6 +17,7 @@ DT_I8, DT_U8, DT_I16, DT_U16, DT_I32, DT_F32, DT_BF16, DT_F16 = range(8)
 RQ_NONE, RQ_MULTIPLIER_SHIFT, RQ_QDM, RQ_MULTIPLIER_SHIFT_F32, RQ_ONLY_SHIFT, RQ_ONLY_SCALE = range(6)
 RELU_NONE, RELU_BEFORE_REQUANT, RELU_AFTER_REQUANT = range(3)
 ALGO_AUTO, ALGO_TENSOR_CORE, ALGO_CUDA_CORE = 0, 1, 2
+LAYOUT_NCHW, LAYOUT_NHWC = 0, 1
 
 
 class B200QError(RuntimeError):
@@ -83,6 +84,7 @@ SIGNATURES = {
     "b200q_conv2d_deinit": (None, [_VPP]),
     "b200q_conv2d_dev_create": (C.c_int, [C.POINTER(Conv2DDesc), C.c_void_p, C.c_void_p, _VPP]),
     "b200q_conv2d_dev_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200q_conv2d_dev_run_layout": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "b200q_conv2d_dev_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200q_conv2d_dev_destroy": (None, [_VPP]),
     "b200q_requant_int_axis_inference": (C.c_int, [C.POINTER(RequantDesc), _FLOATPP, C.c_int, _FLOATPP, C.c_int]),
@@ -92,6 +94,7 @@ SIGNATURES = {
     "b200q_add_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 6 +
                          [C.c_void_p, C.c_void_p]),
     "b200q_pool2d_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 15 + [C.c_void_p, C.c_void_p]),
+    "b200q_pool2d_i8_nhwc_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 16 + [C.c_void_p, C.c_void_p]),
     "b200q_cast_f32_to_q8_dev": (C.c_int, [C.c_void_p, C.c_int64, C.c_double, C.c_int32, C.c_int32, C.c_int32,
                                            C.c_void_p, C.c_void_p]),
     "b200q_cast_q8_to_f32_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_double, C.c_int32, C.c_void_p,

@@ -377,17 +377,32 @@ int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int
 // x: device NCHW (bytes, or float holding integers); y: device NCHW native out dtype
 // `images` < 0: the whole batch of the descriptor; otherwise the first `images` images of x / y (the operator face
 // pipelines its host copies over pieces of the batch)
-int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s, long long images = -1) {
+// x_nhwc / y_nhwc: the tensor is [N][H][W][C] bytes instead of NCHW (the tensor-core routes only; a channels-last
+// graph keeps its activations in that form between ops, so no transposing kernel runs and outputs are stored as
+// whole 16-byte channel runs)
+int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s, long long images = -1, bool x_nhwc = false,
+             bool y_nhwc = false) {
   const b200q_conv2d_desc& d = h->d;
   const long long nb = images < 0 ? (long long)d.n : images;
   if (nb == 0) return B200Q_OK;
+  if ((x_nhwc || y_nhwc) && !(h->use_tc || h->use_im2col))
+    return set_error(B200Q_ERR_UNSUPPORTED, "conv2d: channels-last tensors need one of the tensor-core routes");
+  if (x_nhwc && (x_is_f32 || d.ic % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0))
+    return set_error(B200Q_ERR_UNSUPPORTED, "conv2d: a channels-last input is 16-byte aligned bytes with channels %% 16 == 0");
   if (h->profiling && (h->use_tc || h->use_im2col)) B200Q_TRY(h->next_triple());
   if (h->use_tc) {
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[0], s));
-    B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)nb, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
+    // a channels-last input without a border is the GEMM's left operand as it lies
+    const bool direct = x_nhwc && h->bh == 0 && h->bw == 0 && !h->pair_taps;
+    if (direct) {
+    } else if (x_nhwc) {
+      B200Q_TRY(nhwc_to_bordered_launch(x, h->x_bordered.p, nb, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
+    } else {
+      B200Q_TRY(nchw_to_bordered_nhwc(x, x_is_f32, h->x_bordered.p, (int)nb, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
+    }
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[1], s));
     IGemmProblem p{};
-    p.a = h->x_bordered.p;
+    p.a = direct ? x : h->x_bordered.p;
     p.b = h->w_packed.p;
     p.a_unsigned = d.input_dtype == B200Q_DT_U8;
     p.b_unsigned = 0;
@@ -408,8 +423,8 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.border_w = h->bw;
     p.out_h = h->g.oh;
     p.out_w = h->g.ow;
-    p.out_mode = IGEMM_OUT_NCHW;
-    p.ldc = 0;
+    p.out_mode = y_nhwc ? IGEMM_OUT_NHWC : IGEMM_OUT_NCHW;
+    p.ldc = y_nhwc ? (long long)d.oc : 0;
     p.out = y;
     if (h->pair_taps) {
       p.k_per_tap = 128;                    // two pixels' channels
@@ -423,7 +438,13 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
   }
   if (h->use_im2col) {
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[0], s));
-    if (h->few_channels) {
+    if (x_nhwc) {
+      const bool plain = h->bh == 0 && h->bw == 0;
+      if (!plain) B200Q_TRY(nhwc_to_bordered_launch(x, h->x_bordered.p, nb, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
+      B200Q_TRY(im2col_nhwc_launch(plain ? x : h->x_bordered.p, h->a_cols.p, nb, (int)d.ic, h->Hp, h->Wp, h->g.oh, h->g.ow,
+                                   (int)d.kh, (int)d.kw, (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, h->bh - (int)d.pht,
+                                   h->bw - (int)d.pwl, h->kpad, s));
+    } else if (h->few_channels) {
       // few input channels (a network's stem): rows are built from 8-byte runs of the NCHW input
       B200Q_TRY(im2col_few_channels_launch(x, x_is_f32, h->a_cols.p, nb, (int)d.ic, (int)d.ih, (int)d.iw, h->g.oh, h->g.ow,
                                            (int)d.kh, (int)d.sh, (int)d.sw, (int)d.pht, (int)d.pwl, h->kpad, s));
@@ -452,7 +473,8 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.img_rows = h->g.oh * h->g.ow;
     p.out_h = h->g.oh;
     p.out_w = h->g.ow;
-    p.out_mode = IGEMM_OUT_NCHW;
+    p.out_mode = y_nhwc ? IGEMM_OUT_ROWMAJOR : IGEMM_OUT_NCHW;  // the rows are the output pixels in NHW order
+    p.ldc = y_nhwc ? (long long)d.oc : 0;
     p.out = y;
     B200Q_TRY(igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s));
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[2], s));
@@ -700,6 +722,14 @@ int b200q_conv2d_dev_run(void* handle, const void* x_nchw, void* y_nchw, void* s
   return conv_run(static_cast<ConvHandle*>(handle), x_nchw, 0, y_nchw, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_conv2d_dev_run_layout(void* handle, const void* x, int32_t x_layout, void* y, int32_t y_layout, void* stream) {
+  if (!handle || !x || !y) return set_error(B200Q_ERR_INVALID, "conv2d_dev_run_layout: null argument");
+  if ((x_layout != B200Q_LAYOUT_NCHW && x_layout != B200Q_LAYOUT_NHWC) || (y_layout != B200Q_LAYOUT_NCHW && y_layout != B200Q_LAYOUT_NHWC))
+    return set_error(B200Q_ERR_INVALID, "conv2d_dev_run_layout: unknown layout");
+  return conv_run(static_cast<ConvHandle*>(handle), x, 0, y, static_cast<cudaStream_t>(stream), -1, x_layout == B200Q_LAYOUT_NHWC,
+                  y_layout == B200Q_LAYOUT_NHWC);
+}
+
 int b200q_conv2d_dev_status(void* handle, void* stream) {
   if (!handle) return set_error(B200Q_ERR_INVALID, "conv2d_dev_status: null handle");
   return read_status(static_cast<ConvHandle*>(handle)->status, static_cast<cudaStream_t>(stream), "conv2d");
@@ -749,6 +779,15 @@ int b200q_add_i8_dev(const void* a, int32_t a_dtype, const void* b, int32_t b_dt
                      int32_t m1, int32_t s1, int32_t do_relu, int32_t out_dtype, void* out, void* stream) {
   if (!a || !b || !out || count < 0) return set_error(B200Q_ERR_INVALID, "add_i8_dev: bad argument");
   return add_i8_launch(a, a_dtype, b, b_dtype, count, m0, s0, m1, s1, do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_pool2d_i8_nhwc_dev(const void* x, int32_t dtype, int64_t n, int32_t c, int32_t ih, int32_t iw, int32_t kh, int32_t kw,
+                             int32_t sh, int32_t sw, int32_t pht, int32_t phb, int32_t pwl, int32_t pwr, int32_t is_avg,
+                             int32_t multiplier, int32_t rshift, int32_t do_relu, int32_t out_dtype, void* out, void* stream) {
+  if (!x || !out || n < 0 || n > 0x7fffffffLL || c < 1 || ih < 1 || iw < 1 || kh < 1 || kw < 1 || sh < 1 || sw < 1)
+    return set_error(B200Q_ERR_INVALID, "pool2d_i8_nhwc_dev: bad argument");
+  return pool2d_i8_nhwc_launch(x, dtype, n, c, ih, iw, kh, kw, sh, sw, pht, phb, pwl, pwr, is_avg ? 1 : 0, multiplier, rshift,
+                               do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
 }
 
 int b200q_pool2d_i8_dev(const void* x, int32_t dtype, int64_t nc, int32_t ih, int32_t iw, int32_t kh, int32_t kw, int32_t sh,

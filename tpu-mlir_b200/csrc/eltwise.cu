@@ -377,6 +377,74 @@ im2col_few_channels_kernel(const T* __restrict__ x, uint8_t* __restrict__ a, int
   }
 }
 
+// ------------------------------------------------------------------------------------------- NHWC-resident graphs
+// [N][H][W][C] -> the interior of the zero-bordered [N][H+2bh][W+2bw][C] (16 channels per thread)
+__global__ void __launch_bounds__(256)
+nhwc_to_bordered_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, long long total16, int c16, int H, int W, int bh, int bw) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total16) return;
+  const int c = (int)(i % c16);
+  const long long p = i / c16;
+  const int w = (int)(p % W);
+  const long long t = p / W;
+  const int h = (int)(t % H);
+  const long long n = t / H;
+  y[((n * (H + 2 * bh) + h + bh) * (W + 2 * bw) + w + bw) * c16 + c] = x[i];
+}
+
+// 8-bit max pooling on NHWC: one thread per (output pixel, 16 channels)
+template <bool SIGNED>
+__global__ void __launch_bounds__(256)
+maxpool_nhwc_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, long long total16, int c16, int ih, int iw, int kh, int kw,
+                    int sh, int sw, int pht, int pwl, int oh, int ow, int do_relu) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total16) return;
+  const int c = (int)(i % c16);
+  const long long p = i / c16;
+  const int xo = (int)(p % ow);
+  const long long t = p / ow;
+  const int yo = (int)(t % oh);
+  const long long n = t / oh;
+  const int y0 = yo * sh - pht, x0 = xo * sw - pwl;
+  const uint32_t lowest = SIGNED ? 0x80808080u : 0u;
+  uint32_t b0 = lowest, b1 = lowest, b2 = lowest, b3 = lowest;
+  for (int fy = max(0, -y0); fy < min(kh, ih - y0); ++fy)
+    for (int fx = max(0, -x0); fx < min(kw, iw - x0); ++fx) {
+      const uint4 v = x[((n * ih + y0 + fy) * iw + x0 + fx) * c16 + c];
+      if (SIGNED) {
+        b0 = __vmaxs4(b0, v.x); b1 = __vmaxs4(b1, v.y); b2 = __vmaxs4(b2, v.z); b3 = __vmaxs4(b3, v.w);
+      } else {
+        b0 = __vmaxu4(b0, v.x); b1 = __vmaxu4(b1, v.y); b2 = __vmaxu4(b2, v.z); b3 = __vmaxu4(b3, v.w);
+      }
+    }
+  if (SIGNED && do_relu) {
+    b0 = __vmaxs4(b0, 0u); b1 = __vmaxs4(b1, 0u); b2 = __vmaxs4(b2, 0u); b3 = __vmaxs4(b3, 0u);
+  }
+  y[i] = make_uint4(b0, b1, b2, b3);
+}
+
+// average pooling over the whole kh x kw window grid on NHWC (Pool2D.cpp:162-200: the window sum, MultiplierShift
+// half-up, optional ReLU, saturate); one thread per (output pixel, channel), channels along the warp
+__global__ void __launch_bounds__(256)
+avgpool_nhwc_kernel(const void* __restrict__ x, int dt, long long total, int C, int ih, int iw, int kh, int kw, int sh, int sw,
+                    int pht, int pwl, int oh, int ow, int multi, int rshift, int do_relu, int out_dt, void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = (int)(i % C);
+  const long long p = i / C;
+  const int xo = (int)(p % ow);
+  const long long t = p / ow;
+  const int yo = (int)(t % oh);
+  const long long n = t / oh;
+  const int y0 = yo * sh - pht, x0 = xo * sw - pwl;
+  int64_t sum = 0;
+  for (int fy = max(0, -y0); fy < min(kh, ih - y0); ++fy)
+    for (int fx = max(0, -x0); fx < min(kw, iw - x0); ++fx) sum += ld_q(x, ((n * ih + y0 + fy) * iw + x0 + fx) * C + c, dt);
+  int64_t v = rshift_round(sum * multi, rshift, B200Q_ROUND_HALF_UP);
+  if (do_relu && v < 0) v = 0;
+  st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
+}
+
 inline unsigned nblk(long long n, int t) { return (unsigned)((n + t - 1) / t); }
 
 }  // namespace
@@ -529,6 +597,41 @@ int im2col_few_channels_launch(const void* x, int x_is_f32, void* a, long long N
     auto k = im2col_few_channels_kernel<uint8_t>;
     if (smem > 48 * 1024) CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k<<<grid, 256, smem, s>>>((const uint8_t*)x, (uint8_t*)a, C, H, W, OH, OW, KH, sh, sw, pht, pwl, kpad, band, wpad, pwl_s);
+  }
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int nhwc_to_bordered_launch(const void* x, void* y, long long N, int C, int H, int W, int bh, int bw, cudaStream_t s) {
+  if (C % 16 != 0 || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
+    return set_error(B200Q_ERR_UNSUPPORTED, "nhwc_to_bordered: channels must be a multiple of 16 and the buffers 16-byte aligned");
+  const long long total16 = N * H * W * (C / 16);
+  if (total16 == 0) return B200Q_OK;
+  nhwc_to_bordered_kernel<<<nblk(total16, 256), 256, 0, s>>>((const uint4*)x, (uint4*)y, total16, C / 16, H, W, bh, bw);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int pool2d_i8_nhwc_launch(const void* x, int dt, long long N, int C, int ih, int iw, int kh, int kw, int sh, int sw, int pht,
+                          int phb, int pwl, int pwr, int mode, int multi, int rshift, int do_relu, int out_dt, void* out,
+                          cudaStream_t s) {
+  const int oh = (ih + pht + phb - kh) / sh + 1, ow = (iw + pwl + pwr - kw) / sw + 1;
+  const long long total = N * oh * ow * C;
+  if (total <= 0) return B200Q_OK;
+  const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (mode == 0 && dt == out_dt && (dt == B200Q_DT_I8 || dt == B200Q_DT_U8) && C % 16 == 0 && al) {
+    const long long t16 = total / 16;
+    if (dt == B200Q_DT_I8)
+      maxpool_nhwc_kernel<true><<<nblk(t16, 256), 256, 0, s>>>((const uint4*)x, (uint4*)out, t16, C / 16, ih, iw, kh, kw, sh, sw, pht,
+                                                               pwl, oh, ow, do_relu);
+    else
+      maxpool_nhwc_kernel<false><<<nblk(t16, 256), 256, 0, s>>>((const uint4*)x, (uint4*)out, t16, C / 16, ih, iw, kh, kw, sh, sw, pht,
+                                                                pwl, oh, ow, do_relu);
+  } else if (mode == 1) {
+    avgpool_nhwc_kernel<<<nblk(total, 256), 256, 0, s>>>(x, dt, total, C, ih, iw, kh, kw, sh, sw, pht, pwl, oh, ow, multi, rshift,
+                                                         do_relu, out_dt, out);
+  } else {
+    return set_error(B200Q_ERR_UNSUPPORTED, "pool2d (NHWC): max pooling needs equal 8-bit types and channels %% 16 == 0");
   }
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;

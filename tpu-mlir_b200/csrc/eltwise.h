@@ -15,6 +15,11 @@ int add_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n,
 // mode 0 = max, 1 = average (window sum * multi >> rshift, half up)
 int pool2d_i8_launch(const void* x, int dt, int NC, int ih, int iw, int kh, int kw, int sh, int sw, int pht, int phb,
                      int pwl, int pwr, int mode, int multi, int rshift, int do_relu, int out_dt, void* out, cudaStream_t s);
+// NHWC-resident graphs: [N][H][W][C] -> interior of the zero-bordered image; pooling on [N][H][W][C]
+int nhwc_to_bordered_launch(const void* x, void* y, long long N, int C, int H, int W, int bh, int bw, cudaStream_t s);
+int pool2d_i8_nhwc_launch(const void* x, int dt, long long N, int C, int ih, int iw, int kh, int kw, int sh, int sw, int pht,
+                          int phb, int pwl, int pwr, int mode, int multi, int rshift, int do_relu, int out_dt, void* out,
+                          cudaStream_t s);
 int cast_f32_q8_launch(const float* x, long long n, double scale, int zp, int rmode, int out_dt, void* out, cudaStream_t s);
 int cast_q8_f32_launch(const void* x, int dt, long long n, double scale, int zp, float* out, cudaStream_t s);
 // x: zero-bordered NHWC bytes [N][Hp][Wp][C]; a: rows [N*OH*OW][kpad], k = (fy*KW+fx)*C + c.  (oy0, ox0) = bordered

@@ -8,7 +8,7 @@
 
 namespace b200q {
 
-enum { IGEMM_OUT_ROWMAJOR = 0, IGEMM_OUT_NCHW = 1, IGEMM_OUT_NHWC_BORDERED = 2 };
+enum { IGEMM_OUT_ROWMAJOR = 0, IGEMM_OUT_NCHW = 1, IGEMM_OUT_NHWC_BORDERED = 2, IGEMM_OUT_NHWC = 3 };  // NHWC: interior pixels only, [N][out_h][out_w][ldc]
 enum { IGEMM_KIND_I8 = 0, IGEMM_KIND_BF16 = 1 };  // operand type; BF16: fp32 accumulate, bf16 row-major output
 
 // What the host asks for.  A is [rows][k_per_tap] (row pitch a_pitch bytes): the GEMM's left matrix, or the

@@ -472,6 +472,9 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           row_valid = interior;
           out_base = ((long long)img * args.n * args.out_h + h) * args.out_w + w;
           chan_stride = args.out_h * args.out_w;
+        } else if (args.out_mode == IGEMM_OUT_NHWC) {  // unbordered NHWC: border rows are dropped
+          row_valid = interior;
+          out_base = (((long long)img * args.out_h + h) * args.out_w + w) * args.ldc;
         } else {  // zero-bordered NHWC: border rows are written as zeros
           out_base = (long long)row * args.ldc;
           write_zero_row = row_valid && !interior;
@@ -820,7 +823,7 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   {
     const long long out_elems = p.out_mode == IGEMM_OUT_NCHW
                                     ? (long long)((p.rows + a.img_rows - 1) / a.img_rows) * p.n * p.out_h * p.out_w
-                                    : (long long)p.rows * p.ldc;
+                                    : (long long)p.rows * p.ldc;  // (an upper bound for IGEMM_OUT_NHWC)
     a.out_small = out_elems < (1ll << 31);
   }
   // CTA pairs (256-row tiles, cta_group::2) once there is more than one wave of 128-row tiles to share out

@@ -13,6 +13,10 @@ dialect's (``load`` also takes the path of a lowered model's ``.mlir`` text and 
      "ops": [{"type": "tpu.Conv2D", "name": out_tensor, "inputs": [...], "attrs": {...}}, ...]}
 
 with weights in a dict ``name -> numpy array`` (``<op>_filter``, ``<op>_bias``).
+
+``module(channels_last=True)`` keeps the 4-D activations that convolutions, adds and pools produce as [N][H][W][C]
+on the device (the order the tensor-core kernels read and write), so no transposing kernel runs between ops;
+``get_tensor`` / ``set_tensor`` still speak NCHW, and the values are identical.
 """
 from __future__ import annotations
 
@@ -32,8 +36,10 @@ def _P(t):
 
 
 class module:  # noqa: N801  (name of the reference class)
-    def __init__(self, device: Optional[int] = None):
+    def __init__(self, device: Optional[int] = None, channels_last: bool = False):
         import torch
+        self.channels_last = bool(channels_last)
+        self._nhwc = set()  # names of the tensors stored as [N][H][W][C]
         self.torch = torch
         if not torch.cuda.is_available():
             raise L.B200QError(L.ERR_NO_DEVICE, "the executor needs a CUDA device (there is no CPU fallback)")
@@ -62,8 +68,12 @@ class module:  # noqa: N801  (name of the reference class)
         self.all_tensor_names = list(graph["tensors"].keys())
         self.all_weight_names = list(weights.keys())
         tdt = {"i8": torch.int8, "u8": torch.uint8, "i32": torch.int32, "f32": torch.float32}
+        self._nhwc = self._assign_layouts(graph, weights) if self.channels_last else set()
         for name, info in graph["tensors"].items():
-            self.tensors[name] = torch.zeros(tuple(info["shape"]), dtype=tdt[info["dtype"]], device=self.device)
+            shape = tuple(info["shape"])
+            if name in self._nhwc:
+                shape = (shape[0], shape[2], shape[3], shape[1])
+            self.tensors[name] = torch.zeros(shape, dtype=tdt[info["dtype"]], device=self.device)
         self.weights = {k: torch.from_numpy(np.ascontiguousarray(v)).to(self.device) for k, v in weights.items()}
         for op in graph["ops"]:
             self._plans.append(self._plan(op))
@@ -78,6 +88,33 @@ class module:  # noqa: N801  (name of the reference class)
 
     def _info(self, name):
         return self.graph["tensors"][name]
+
+    @staticmethod
+    def _assign_layouts(graph, weights):
+        """Which tensors are stored channels-last: the output of a convolution that a tensor-core route takes (one
+        group, output channels a multiple of 16), and whatever an Add, Pool2D or Cast derives from such tensors."""
+        nhwc = set()
+        tens = graph["tensors"]
+        for op in graph["ops"]:
+            t, a, name = op["type"], op.get("attrs", {}), op["name"]
+            ins = op["inputs"]
+            if len(tens[name]["shape"]) != 4:
+                continue
+            if t == "tpu.Conv2D":
+                oc = tens[name]["shape"][1]
+                if a.get("group", 1) == 1 and oc % 16 == 0 and tens[name]["dtype"] in ("i8", "u8"):
+                    nhwc.add(name)
+                elif ins[0] in nhwc:
+                    raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: a grouped convolution cannot read a channels-last tensor")
+            elif t == "tpu.Add":
+                if ins[0] in nhwc and ins[1] in nhwc:
+                    nhwc.add(name)
+                elif ins[0] in nhwc or ins[1] in nhwc:
+                    raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: operands in different layouts")
+            elif t in ("tpu.Pool2D", "tpu.Cast"):
+                if ins[0] in nhwc:
+                    nhwc.add(name)
+        return nhwc
 
     def _plan(self, op) -> Callable:
         t, a, lib = op["type"], op.get("attrs", {}), self.lib
@@ -110,6 +147,10 @@ class module:  # noqa: N801  (name of the reference class)
             L.check(lib.b200q_conv2d_dev_create(C.byref(cop.desc), _P(w), _P(b), C.byref(h)))
             self._handles.append(h)
             self._keep.append(cop)
+            if self.channels_last:
+                xl = L.LAYOUT_NHWC if op["inputs"][0] in self._nhwc else L.LAYOUT_NCHW
+                yl = L.LAYOUT_NHWC if op["name"] in self._nhwc else L.LAYOUT_NCHW
+                return lambda: L.check(lib.b200q_conv2d_dev_run_layout(h, _P(ins[0]), xl, _P(out), yl, stream()))
             return lambda: L.check(lib.b200q_conv2d_dev_run(h, _P(ins[0]), _P(out), stream()))
         if t == "tpu.MatMul":
             w_kn = self.weights[op["name"] + "_filter"]
@@ -140,11 +181,18 @@ class module:  # noqa: N801  (name of the reference class)
             sh, sw = a.get("strides", [1, 1])
             pht, pwl, phb, pwr = a.get("pads", [0, 0, 0, 0])
             is_avg = a["pool_mode"] == "Avg"
+            if op["inputs"][0] in self._nhwc:
+                return lambda: L.check(lib.b200q_pool2d_i8_nhwc_dev(
+                    _P(ins[0]), _DT[iinfo[0]["dtype"]], nb, c, ih, iw, kh, kw, sh, sw, pht, phb, pwl, pwr, int(is_avg),
+                    int(a.get("multiplier", 1)), int(a.get("rshift", 0)), int(bool(a.get("do_relu", False))),
+                    _DT[oinfo["dtype"]], _P(out), stream()))
             return lambda: L.check(lib.b200q_pool2d_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], nb * c, ih, iw, kh, kw, sh, sw,
                                                            pht, phb, pwl, pwr, int(is_avg), int(a.get("multiplier", 1)),
                                                            int(a.get("rshift", 0)), int(bool(a.get("do_relu", False))),
                                                            _DT[oinfo["dtype"]], _P(out), stream()))
         if t == "tpu.Reshape":
+            if op["inputs"][0] in self._nhwc:
+                return lambda: out.copy_(ins[0].permute(0, 3, 1, 2).reshape(out.shape))
             return lambda: out.copy_(ins[0].reshape(out.shape))
         raise L.B200QError(L.ERR_UNSUPPORTED, f"op type {t} is not implemented by the executor")
 
@@ -153,6 +201,9 @@ class module:  # noqa: N801  (name of the reference class)
         """Float input of the graph (quantisation happens in the graph's own tpu.Cast, as in a lowered model)."""
         t = self.tensors[name]
         src = self.torch.as_tensor(np.ascontiguousarray(data)) if not isinstance(data, self.torch.Tensor) else data
+        if name in self._nhwc:
+            n, h, w, c = t.shape
+            src = src.reshape(n, c, h, w).permute(0, 2, 3, 1)
         t.copy_(src.reshape(t.shape).to(t.dtype), non_blocking=True)
 
     def set_tensor_from_int(self, name: str, data, shape=None):
@@ -183,13 +234,17 @@ class module:  # noqa: N801  (name of the reference class)
         raise KeyError(name)
 
     def get_tensor(self, name: str) -> np.ndarray:
-        """Raw storage values (integers for quantized tensors)."""
-        return self.tensors[name].cpu().numpy()
+        """Raw storage values (integers for quantized tensors), in the graph's own (NCHW) shape."""
+        return self._nchw(name).cpu().numpy()
+
+    def _nchw(self, name: str):
+        t = self.tensors[name]
+        return t.permute(0, 3, 1, 2).contiguous() if name in self._nhwc else t
 
     def get_fp32_tensor(self, name: str) -> np.ndarray:
         """The tensor as the interpreter "expresses" it: (q - zp) * scale (ModuleInterpreter.cpp:992-1011)."""
         info = self._info(name)
-        v = self.tensors[name].cpu().numpy()
+        v = self._nchw(name).cpu().numpy()
         if info["dtype"] == "f32":
             return v
         return ((v.astype(np.float32) - np.float32(info.get("zp", 0))) * np.float32(info["scale"])).astype(np.float32)
