@@ -141,6 +141,10 @@ def test_conv_device_face_matches_operator_face():
     dict(N=2, C=128, H=14, W=14, OC=128, k=3, stride=(2, 2), pads=(1, 1, 1, 1)),    # strided 3x3: im2col rows
     dict(N=2, C=256, H=14, W=14, OC=512, k=1, stride=(2, 2), pads=(0, 0, 0, 0)),    # strided 1x1 (a downsample branch)
     dict(N=1, C=32, H=7, W=9, OC=272, k=1, stride=(1, 1), pads=(0, 0, 0, 0)),       # ragged channel tile
+    # output channels a multiple of 128: the transposed product (rows = channels, per-row requantisation constants)
+    dict(N=3, C=128, H=9, W=7, OC=128, k=1, stride=(1, 1), pads=(0, 0, 0, 0)),      # one row tile, ragged pixel tile
+    dict(N=2, C=48, H=20, W=20, OC=384, k=1, stride=(1, 1), pads=(0, 0, 0, 0)),     # three row tiles
+    dict(N=40, C=64, H=28, W=28, OC=256, k=1, stride=(1, 1), pads=(0, 0, 0, 0)),    # enough tiles for CTA pairs
 ])
 @pytest.mark.parametrize("layouts", [(1, 1), (0, 1), (1, 0)])
 def test_conv_device_face_channels_last(case, layouts):

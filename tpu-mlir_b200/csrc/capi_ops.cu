@@ -377,6 +377,42 @@ int conv_setup(ConvHandle* h, const b200q_conv2d_desc& d, const void* w_dev, int
 // x: device NCHW (bytes, or float holding integers); y: device NCHW native out dtype
 // `images` < 0: the whole batch of the descriptor; otherwise the first `images` images of x / y (the operator face
 // pipelines its host copies over pieces of the batch)
+// The transposed product for a channels-last output: the GEMM's rows are the output channels (left operand = the
+// filter [OC][K]), its columns the pixels (right operand = the activation rows [pixels][K]); element (oc, pixel)
+// goes to out[pixel * OC + oc].  Every epilogue thread then owns one channel and keeps its requantisation constants
+// in registers, which is what a short-K product (epilogue-bound) needs.  Expressed through the NCHW output mode:
+// one "image" of OC x 1 "pixels" whose "channels" are the GEMM's columns.
+bool transposed_product_ok(const Epilogue& e, int oc, long long pixels) {
+  const bool fast = (e.dialect == B200Q_RQ_MULTIPLIER_SHIFT && e.round_mode == B200Q_ROUND_HALF_UP) ||
+                    (e.dialect == B200Q_RQ_QDM && e.round_mode == B200Q_ROUND_HALF_AWAY_FROM_ZERO);
+  static const bool on = [] {
+    const char* v = getenv("B200Q_CONV_TRANSPOSED");  // =0 keeps the pixel-major product (for A/B timing)
+    return !(v && v[0] == '0');
+  }();
+  return on && fast && oc % 128 == 0 && pixels > 128 && pixels < 0x7fffffffLL;
+}
+
+void make_transposed(IGemmProblem* p, int oc) {
+  IGemmProblem q = *p;
+  q.a = p->b;
+  q.b = p->a;
+  q.a_unsigned = p->b_unsigned;
+  q.b_unsigned = p->a_unsigned;
+  q.a_pitch = p->b_pitch;
+  q.b_pitch = p->a_pitch;
+  q.rows = oc;
+  q.n = p->rows;
+  q.row_pitch = 1;
+  q.img_rows = 0x7fffffff;
+  q.border_h = q.border_w = 0;
+  q.out_h = oc;
+  q.out_w = 1;
+  q.out_mode = IGEMM_OUT_NCHW;
+  q.ldc = 0;
+  q.per_row_params = 1;
+  *p = q;
+}
+
 // x_nhwc / y_nhwc: the tensor is [N][H][W][C] bytes instead of NCHW (the tensor-core routes only; a channels-last
 // graph keeps its activations in that form between ops, so no transposing kernel runs and outputs are stored as
 // whole 16-byte channel runs)
@@ -432,6 +468,9 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
       p.tap_step_w = 2;
       p.b_pitch = (long long)d.kh * p.taps_w * 128;
     }
+    // a 1x1 filter without a border is a plain GEMM whose rows are exactly the output pixels
+    if (y_nhwc && d.kh * d.kw == 1 && h->bh == 0 && h->bw == 0 && transposed_product_ok(h->epi, (int)d.oc, p.rows))
+      make_transposed(&p, (int)d.oc);
     B200Q_TRY(igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s));
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[2], s));
     return B200Q_OK;
@@ -476,6 +515,7 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.out_mode = y_nhwc ? IGEMM_OUT_ROWMAJOR : IGEMM_OUT_NCHW;  // the rows are the output pixels in NHW order
     p.ldc = y_nhwc ? (long long)d.oc : 0;
     p.out = y;
+    if (y_nhwc && transposed_product_ok(h->epi, (int)d.oc, p.rows)) make_transposed(&p, (int)d.oc);
     B200Q_TRY(igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s));
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[2], s));
     return B200Q_OK;

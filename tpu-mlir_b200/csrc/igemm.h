@@ -30,6 +30,8 @@ struct IGemmProblem {
   void* out;
   int kind;                               // IGEMM_KIND_*; for BF16 k_per_tap and the pitches are in BYTES (2 per element)
   const float* bias_f32;                  // BF16 kind: optional per-column bias
+  int per_row_params;                     // the epilogue's per-channel arrays index the GEMM's ROWS (transposed product);
+                                          // 8-bit kinds with a fast dialect, n > 128
 };
 
 // Kernel argument block (device view of the same problem).
@@ -46,6 +48,7 @@ struct IGemmArgs {
   int bf16;
   int acc_small;
   int out_small;
+  int floor_pre, sat_lo2, sat_hi, pack_sat, floor_needed;  // epilogue constants derived from epi (see the kernel)
   int acc_bound;  // |accumulator| <= this for every 8-bit operand pair (valid when acc_small)
 };
 

@@ -121,7 +121,81 @@ __device__ __forceinline__ bool fold_domain(int32_t sh, int32_t zp) {
   return false;
 }
 
-template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR, int TAPW>
+
+// Classification of one output channel's parameters: bit 1 = not foldable, 2 = not in the fast domain,
+// 4 = foldable MultiplierShift with s in [1,31] (funnel form), 8 = foldable MultiplierShift with s >= 32.
+template <int DIALECT, int RMODE>
+__device__ __forceinline__ int classify_channel(int32_t bias, int32_t m, int32_t sh, const IGemmArgs& args, bool fast_dialect) {
+  const Epilogue& e = args.epi;
+  const bool pre_relu = e.relu == B200Q_RELU_BEFORE_REQUANT;
+  const long long az = e.out_zp < 0 ? -(long long)e.out_zp : (long long)e.out_zp;
+  const bool fast_ok = fast_dialect && fast_domain<DIALECT, RMODE>(m, sh);
+  bool fold_ok = fast_ok && !pre_relu && args.acc_small && bias > -(1 << 28) && bias < (1 << 28) &&
+                 fold_domain<DIALECT>(sh, e.out_zp);
+  int width_bits = 0;
+  if (DIALECT == B200Q_RQ_MULTIPLIER_SHIFT && fold_ok) {
+    if (sh >= 32) {
+      width_bits = 8;
+    } else {  // the value shifted by s must fit 32 bits for every accumulator this K can produce
+      const unsigned long long am = (unsigned long long)(m < 0 ? -(long long)m : (long long)m);
+      const unsigned long long ab = (unsigned long long)(bias < 0 ? -(long long)bias : (long long)bias);
+      const unsigned long long bound = (unsigned long long)args.acc_bound * am + ab * am + (1ull << (sh - 1)) +
+                                       ((unsigned long long)az << sh);
+      fold_ok = bound < (1ull << (31 + sh));
+      width_bits = 4;
+    }
+  }
+  return (fold_ok ? width_bits : 1) | (fast_ok ? 0 : 2);
+}
+
+// The cheapest form every channel of a group allows, from the OR of the group's classification bits.
+template <int DIALECT>
+__device__ __forceinline__ int form_of_bits(int st, bool relu_after) {
+  if (st & 2) return FORM_GENERAL;
+  if (st & 1) return FORM_FAST;
+  if (DIALECT == B200Q_RQ_QDM) return relu_after ? FORM_FOLD_HI : FORM_FOLD_QDM;
+  return ((st & 4) && (st & 8)) ? FORM_FAST : ((st & 4) ? FORM_FOLD_FUNNEL : FORM_FOLD_HI);
+}
+
+// One channel's constants in the layout `form` reads (see the table in the kernel); `in` false: a channel past N.
+template <int DIALECT>
+__device__ __forceinline__ void form_constants(int form, bool in, int32_t bias, int32_t m, int32_t sh, int32_t out_zp,
+                                               int4* cp, int32_t* ck) {
+  *ck = 0;
+  if (!in) {
+    *cp = make_int4(0, 0, 0, 1);
+  } else if (form == FORM_FOLD_HI || form == FORM_FOLD_FUNNEL || form == FORM_FOLD_QDM) {
+    long long C;
+    int32_t s4;
+    if (DIALECT == B200Q_RQ_QDM) {
+      const int32_t t = -sh;
+      const long long K = (long long)((1u << t) >> 1) + (long long)((unsigned long long)(long long)out_zp << t);
+      C = (long long)bias * (long long)m + (1ll << 30);
+      if (form == FORM_FOLD_HI) {
+        C += (long long)((unsigned long long)K << 31);
+        s4 = t - 1;
+      } else {  // (w - (w < 0) + K) >> t after w = (acc*m + C) >> 31
+        *ck = (int32_t)K;
+        s4 = t;
+      }
+    } else {
+      C = (long long)bias * (long long)m + (long long)(1ull << (sh - 1)) + (long long)((unsigned long long)(long long)out_zp << sh);
+      s4 = form == FORM_FOLD_HI ? sh - 32 : sh;
+    }
+    *cp = make_int4((int32_t)(uint32_t)(C & 0xffffffffll), (int32_t)(C >> 32), m, s4);  // C: an aligned register pair
+  } else if (form == FORM_FAST) {
+    const int32_t t = DIALECT == B200Q_RQ_QDM ? -sh : sh;
+    *cp = make_int4(bias, m, t, DIALECT == B200Q_RQ_QDM ? (int32_t)(1u << (t - 1)) : 0);
+  } else {
+    *cp = make_int4(bias, m, sh, 0);
+  }
+}
+
+// PERROW: the requantisation parameters belong to the GEMM's ROWS (the transposed product: rows are output channels,
+// columns pixels).  Every epilogue thread then keeps its own row's constants in registers; no shared-memory
+// parameter read is left in the per-element path, whose 16 bytes per lane and element otherwise saturate the
+// load/store pipe of a short-K product.
+template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR, int TAPW, bool PERROW = false>
 __global__ void __launch_bounds__(SmemLayout<BLOCK_N, STAGES, PAIR, TAPW>::NUM_THREADS, 1)
 igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const IGemmArgs args) {
@@ -326,26 +400,40 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                                    (DIALECT == B200Q_RQ_MULTIPLIER_SHIFT && RMODE == B200Q_ROUND_HALF_UP);
     const bool kFastDialect = kFastCompiled && e.out_dtype != B200Q_DT_I32;
     const int32_t zp = e.out_zp;
-    const int32_t floor_pre = e.relu == B200Q_RELU_BEFORE_REQUANT ? 0 : (-2147483647 - 1);
-    const int32_t floor_post = e.relu == B200Q_RELU_AFTER_REQUANT ? zp : (-2147483647 - 1);
-    int32_t sat_lo, sat_hi;  // output range; the post-ReLU floor is folded into sat_lo below
-    switch (e.out_dtype) {
-      case B200Q_DT_I8: sat_lo = -128; sat_hi = 127; break;
-      case B200Q_DT_U8: sat_lo = 0; sat_hi = 255; break;
-      case B200Q_DT_I16: sat_lo = -32768; sat_hi = 32767; break;
-      case B200Q_DT_U16: sat_lo = 0; sat_hi = 65535; break;
-      default: sat_lo = -2147483647 - 1; sat_hi = 2147483647; break;
-    }
+    // The output range, the ReLU floors and the flags derived from them are kernel parameters (the host fills them in):
+    // as constant-bank operands they hold no registers across the tile loop.
+    //   sat_lo2 = max(type minimum, post-ReLU floor): clamp(max(v, f), lo, hi) == clamp(v, max(lo, f), hi) for f <= hi
+    //   pack_sat: rows of packed bytes leave the clamping to the saturating pack (plus one max when floor_needed, i.e.
+    //   a post-ReLU floor lies above the type's lowest value)
     const bool relu_after = e.relu == B200Q_RELU_AFTER_REQUANT;
-    const int32_t sat_lo2 = max(sat_lo, floor_post);  // clamp(max(v, f), lo, hi) == clamp(v, max(lo, f), hi) for f <= hi
+#define floor_pre (args.floor_pre)
+#define sat_lo2 (args.sat_lo2)
+#define sat_hi (args.sat_hi)
+#define pack_sat (args.pack_sat != 0)
+#define floor_needed (args.floor_needed != 0)
     int acc = 0;
     uint32_t acc_phase = 0;
     int cached_n0 = -1;
+    int row_form = FORM_GENERAL;  // PERROW: this thread's row
+    int4 row_cp = make_int4(0, 0, 0, 1);
+    int32_t row_ck = 0;
     const uint32_t lead_tmem_empty0 = PAIR ? ptx::map_to_cta(tmem_empty_bar(0), 0) : 0u;
     for (int tile = worker; tile < num_tiles; tile += num_workers) {
       const int m0 = (tile / args.num_n_tiles) * TILE_M + (int)cta_rank * BLOCK_M;
       const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
-      if (n0 != cached_n0) {
+      if (PERROW) {
+        if (m0 != cached_n0) {  // (cached_n0 holds the row tile here) the constants of this thread's row
+          const int ch = m0 + quarter * 32 + lane;
+          const bool in = ch < args.rows;
+          const int32_t bias = (in && e.bias) ? e.bias[ch] : 0;
+          const int32_t m = (in && e.multiplier) ? e.multiplier[e.per_channel ? ch : 0] : 1;
+          const int32_t sh = (in && e.shift) ? e.shift[e.per_channel ? ch : 0] : 0;
+          const int bits = in ? classify_channel<DIALECT, RMODE>(bias, m, sh, args, kFastDialect) : 0;
+          row_form = form_of_bits<DIALECT>((int)__reduce_or_sync(0xffffffffu, (unsigned)bits), relu_after);  // one form per warp
+          form_constants<DIALECT>(row_form, in, bias, m, sh, e.out_zp, &row_cp, &row_ck);
+          cached_n0 = m0;
+        }
+      } else if (n0 != cached_n0) {
         // Stage the tile's channel parameters in the cheapest form every channel of a 32-channel chunk allows:
         //   FOLD_HI     {m, C_lo, C_hi, sh}: v = hi32(acc*m + C) >> sh.  Bias, every rounding constant and the zero
         //               point live in C.  QDM with the ReLU after the requantisation (the sign term of the second,
@@ -359,8 +447,6 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         epi_bar_sync<EPI_THREADS>();  // everyone is done reading the previous tile's channel parameters
         if (etid < BLOCK_N / 32) chunk_form[etid] = 0;
         epi_bar_sync<EPI_THREADS>();
-        const bool pre_relu = e.relu == B200Q_RELU_BEFORE_REQUANT;
-        const long long az = e.out_zp < 0 ? -(long long)e.out_zp : (long long)e.out_zp;
         for (int c = etid; c < BLOCK_N; c += EPI_THREADS) {
           if (DIALECT == KIND_BF16_TAG) break;
           const int n = n0 + c;
@@ -368,23 +454,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const int32_t bias = e.bias ? e.bias[n] : 0;
           const int32_t m = e.multiplier ? e.multiplier[e.per_channel ? n : 0] : 1;
           const int32_t sh = e.shift ? e.shift[e.per_channel ? n : 0] : 0;
-          const bool fast_ok = kFastDialect && fast_domain<DIALECT, RMODE>(m, sh);
-          bool fold_ok = fast_ok && !pre_relu && args.acc_small && bias > -(1 << 28) && bias < (1 << 28) &&
-                         fold_domain<DIALECT>(sh, e.out_zp);
-          int width_bits = 0;
-          if (DIALECT == B200Q_RQ_MULTIPLIER_SHIFT && fold_ok) {
-            if (sh >= 32) {
-              width_bits = 8;
-            } else {  // the value shifted by s must fit 32 bits for every accumulator this K can produce
-              const unsigned long long am = (unsigned long long)(m < 0 ? -(long long)m : (long long)m);
-              const unsigned long long ab = (unsigned long long)(bias < 0 ? -(long long)bias : (long long)bias);
-              const unsigned long long bound = (unsigned long long)args.acc_bound * am + ab * am + (1ull << (sh - 1)) +
-                                               ((unsigned long long)az << sh);
-              fold_ok = bound < (1ull << (31 + sh));
-              width_bits = 4;
-            }
-          }
-          atomicOr(&chunk_form[c >> 5], (fold_ok ? width_bits : 1) | (fast_ok ? 0 : 2));
+          atomicOr(&chunk_form[c >> 5], classify_channel<DIALECT, RMODE>(bias, m, sh, args, kFastDialect));
         }
         epi_bar_sync<EPI_THREADS>();
         int my_form[(BLOCK_N + EPI_THREADS - 1) / EPI_THREADS];
@@ -402,42 +472,13 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const int32_t bias = (in && e.bias) ? e.bias[n] : 0;
           const int32_t m = (in && e.multiplier) ? e.multiplier[e.per_channel ? n : 0] : 1;
           const int32_t sh = (in && e.shift) ? e.shift[e.per_channel ? n : 0] : 0;
-          const int st = chunk_form[c >> 5];
-          int form;
-          if (st & 2) form = FORM_GENERAL;
-          else if (st & 1) form = FORM_FAST;
-          else if (DIALECT == B200Q_RQ_QDM) form = relu_after ? FORM_FOLD_HI : FORM_FOLD_QDM;
-          else form = ((st & 4) && (st & 8)) ? FORM_FAST : ((st & 4) ? FORM_FOLD_FUNNEL : FORM_FOLD_HI);
+          const int form = form_of_bits<DIALECT>(chunk_form[c >> 5], relu_after);
           my_form[i] = form;
-          if (!in) {
-            chan[c] = make_int4(0, 0, 0, 1);
-            chan_k[c] = 0;
-          } else if (form == FORM_FOLD_HI || form == FORM_FOLD_FUNNEL || form == FORM_FOLD_QDM) {
-            long long C;
-            int32_t s4;
-            if (DIALECT == B200Q_RQ_QDM) {
-              const int32_t t = -sh;
-              const long long K = (long long)((1u << t) >> 1) + (long long)((unsigned long long)(long long)e.out_zp << t);
-              C = (long long)bias * (long long)m + (1ll << 30);
-              if (form == FORM_FOLD_HI) {
-                C += (long long)((unsigned long long)K << 31);
-                s4 = t - 1;
-              } else {  // (w - (w < 0) + K) >> t after w = (acc*m + C) >> 31
-                chan_k[c] = (int32_t)K;
-                s4 = t;
-              }
-            } else {
-              C = (long long)bias * (long long)m + (long long)(1ull << (sh - 1)) +
-                  (long long)((unsigned long long)(long long)e.out_zp << sh);
-              s4 = form == FORM_FOLD_HI ? sh - 32 : sh;
-            }
-            chan[c] = make_int4(m, (int32_t)(uint32_t)(C & 0xffffffffll), (int32_t)(C >> 32), s4);
-          } else if (form == FORM_FAST) {
-            const int32_t t = DIALECT == B200Q_RQ_QDM ? -sh : sh;
-            chan[c] = make_int4(bias, m, t, DIALECT == B200Q_RQ_QDM ? (int32_t)(1u << (t - 1)) : 0);
-          } else {
-            chan[c] = make_int4(bias, m, sh, 0);
-          }
+          int4 cp;
+          int32_t ck;
+          form_constants<DIALECT>(form, in, bias, m, sh, e.out_zp, &cp, &ck);
+          chan[c] = cp;
+          chan_k[c] = ck;
         }
         epi_bar_sync<EPI_THREADS>();  // every thread has read its chunks' classification bits
         if (DIALECT != KIND_BF16_TAG) {
@@ -482,22 +523,18 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
       }
 
-      constexpr int CH = 16;  // columns per TMEM load: keeps the epilogue's live registers low
-      // The TMEM read of the next 16 columns is in flight while this chunk is requantised and stored (a read takes
-      // ~0.5 us while MMAs are running).
+      // 16 columns per TMEM load keep the epilogue's live registers low.  The read is not overlapped with the previous
+      // chunk's arithmetic inside a warp (a second register set costs more in spills and lost instruction-level
+      // parallelism than the read's latency, which the other warps of the scheduler cover).
+      constexpr int CH = 16;
       const uint32_t t_warp = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + col0);
-      uint32_t rn[CH];
-      ptx::tmem_ld_32x32b_x16(t_warp, rn);
 #pragma unroll 1
       for (int cc = 0; cc < L::EPI_COLS / CH; ++cc) {
         const int cbase = col0 + cc * CH;
         uint32_t r[CH];
-        ptx::tmem_ld_wait_16(rn);
-#pragma unroll
-        for (int j = 0; j < CH; ++j) r[j] = rn[j];
-        if (cc < L::EPI_COLS / CH - 1) {
-          ptx::tmem_ld_32x32b_x16(t_warp + (uint32_t)((cc + 1) * CH), rn);
-        } else {
+        ptx::tmem_ld_32x32b_x16(t_warp + (uint32_t)(cc * CH), r);
+        ptx::tmem_ld_wait_16(r);
+        if (cc == L::EPI_COLS / CH - 1) {
           // this warp's share of the accumulator buffer is in registers: hand it back to the MMA warp.  Nothing
           // written to memory is being published, so the arrival needs no release ordering (which would wait for
           // this thread's earlier global stores).
@@ -535,40 +572,54 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           continue;
         }
         int32_t q[CH];
-        const int form = kFastCompiled ? chunk_form[cbase >> 5] : FORM_GENERAL;
+        const int form = !kFastCompiled ? FORM_GENERAL : (PERROW ? row_form : chunk_form[cbase >> 5]);
+        // packed 8-bit rows: the saturating pack does the clamping, four values per two instructions
+        bool raw = false;
         if (kFastCompiled && (form == FORM_FOLD_HI || form == FORM_FOLD_FUNNEL)) {
           if (form == FORM_FOLD_HI) {
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-              const int4 cp = chan[cbase + j];  // {m, C_lo, C_hi, sh}: one broadcast 16-byte shared load
-              const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
-              const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
-              q[j] = min(max((int32_t)(x >> 32) >> cp.w, sat_lo2), sat_hi);
+              const int4 cp = PERROW ? row_cp : chan[cbase + j];  // {C_lo, C_hi, m, sh}: one broadcast 16-byte shared load
+              const long long C = (long long)(((unsigned long long)(uint32_t)cp.y << 32) | (uint32_t)cp.x);
+              const long long x = (long long)(int32_t)r[j] * (long long)cp.z + C;
+              q[j] = (int32_t)(x >> 32) >> cp.w;
             }
           } else {
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-              const int4 cp = chan[cbase + j];
-              const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
-              const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
-              const int32_t v = (int32_t)__funnelshift_r((uint32_t)x, (uint32_t)(x >> 32), (uint32_t)cp.w);
-              q[j] = min(max(v, sat_lo2), sat_hi);
+              const int4 cp = PERROW ? row_cp : chan[cbase + j];
+              const long long C = (long long)(((unsigned long long)(uint32_t)cp.y << 32) | (uint32_t)cp.x);
+              const long long x = (long long)(int32_t)r[j] * (long long)cp.z + C;
+              q[j] = (int32_t)__funnelshift_r((uint32_t)x, (uint32_t)(x >> 32), (uint32_t)cp.w);
             }
+          }
+          raw = pack_sat;
+          if (!raw) {
+            if (sat_lo2 == 0) {  // the usual case after a ReLU: max(min(v, hi), 0) is one instruction
+#pragma unroll
+              for (int j = 0; j < CH; ++j) q[j] = __vimin_s32_relu(q[j], sat_hi);
+            } else {
+#pragma unroll
+              for (int j = 0; j < CH; ++j) q[j] = min(max(q[j], sat_lo2), sat_hi);
+            }
+          } else if (floor_needed) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) q[j] = max(q[j], sat_lo2);
           }
         } else if (kFastCompiled && form == FORM_FOLD_QDM) {
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
-            const int4 cp = chan[cbase + j];  // {m, C_lo, C_hi, t}
-            const long long C = (long long)(((unsigned long long)(uint32_t)cp.z << 32) | (uint32_t)cp.y);
-            const long long x = (long long)(int32_t)r[j] * (long long)cp.x + C;
+            const int4 cp = PERROW ? row_cp : chan[cbase + j];  // {C_lo, C_hi, m, t}
+            const long long C = (long long)(((unsigned long long)(uint32_t)cp.y << 32) | (uint32_t)cp.x);
+            const long long x = (long long)(int32_t)r[j] * (long long)cp.z + C;
             const int32_t w = (int32_t)(x >> 31);  // half-up shift by 31: C carries the 2^30
             // half away from zero for a right shift by t: (w + 2^(t-1) - (w < 0)) >> t, zero point inside chan_k
-            q[j] = min(max((w + (w >> 31) + chan_k[cbase + j]) >> cp.w, sat_lo2), sat_hi);
+            q[j] = min(max((w + (w >> 31) + (PERROW ? row_ck : chan_k[cbase + j])) >> cp.w, sat_lo2), sat_hi);
           }
         } else if (kFastCompiled && form == FORM_FAST) {
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
-            const int4 cp = chan[cbase + j];  // {bias, multiplier, shift, half}
+            const int4 cp = PERROW ? row_cp : chan[cbase + j];  // {bias, multiplier, shift, half}
             const int32_t a = max((int32_t)r[j] + cp.x, floor_pre);
             const int32_t v = requant_core_fast<DIALECT>(a, cp.y, cp.z, cp.w);
             q[j] = min(max(add_sat_s32(v, zp), sat_lo2), sat_hi);
@@ -576,7 +627,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         } else {
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
-            const int4 cp = chan[cbase + j];  // {bias, multiplier, shift, -}
+            const int4 cp = PERROW ? row_cp : chan[cbase + j];  // {bias, multiplier, shift, -}
             int32_t a = (int32_t)r[j] + cp.x;
             if (e.relu == B200Q_RELU_BEFORE_REQUANT && a < 0) a = 0;
             q[j] = requant_value<-1, -1>(a, cp.y, cp.z, e);
@@ -624,15 +675,23 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             uint8_t* o = reinterpret_cast<uint8_t*>(args.out) + off;
             if (ncols == CH && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
               uint32_t p[CH / 4];
+              if (raw && e.out_dtype == B200Q_DT_U8) {
 #pragma unroll
-              for (int j = 0; j < CH / 4; ++j)
-                p[j] = (uint32_t)(q[4 * j] & 0xff) | ((uint32_t)(q[4 * j + 1] & 0xff) << 8) |
-                       ((uint32_t)(q[4 * j + 2] & 0xff) << 16) | ((uint32_t)(q[4 * j + 3] & 0xff) << 24);
+                for (int j = 0; j < CH / 4; ++j) p[j] = ptx::pack4_sat_u8(q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
+              } else if (raw) {
+#pragma unroll
+                for (int j = 0; j < CH / 4; ++j) p[j] = ptx::pack4_sat_s8(q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < CH / 4; ++j)
+                  p[j] = (uint32_t)(q[4 * j] & 0xff) | ((uint32_t)(q[4 * j + 1] & 0xff) << 8) |
+                         ((uint32_t)(q[4 * j + 2] & 0xff) << 16) | ((uint32_t)(q[4 * j + 3] & 0xff) << 24);
+              }
               reinterpret_cast<uint4*>(o)[0] = make_uint4(p[0], p[1], p[2], p[3]);
             } else {
 #pragma unroll
               for (int j = 0; j < CH; ++j)
-                if (j < ncols) o[j] = (uint8_t)q[j];
+                if (j < ncols) o[j] = (uint8_t)(raw ? min(max(q[j], sat_lo2), sat_hi) : q[j]);
             }
           } else if (e.out_dtype == B200Q_DT_I32) {
             int32_t* o = reinterpret_cast<int32_t*>(args.out) + off;
@@ -671,6 +730,11 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   }
   if (threadIdx.x == 0 && *abort_flag != 0 && args.status != nullptr) atomicCAS(args.status, 0, *abort_flag);
 }
+#undef floor_pre
+#undef sat_lo2
+#undef sat_hi
+#undef pack_sat
+#undef floor_needed
 
 // ---------------------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -698,10 +762,10 @@ int make_tmap_u8_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
   return make_tmap_u8(map, base, 2, dims, strides, box);
 }
 
-template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR, int TAPW>
+template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR, int TAPW, bool PERROW = false>
 int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& args, int workers, cudaStream_t stream) {
   using L = SmemLayout<BLOCK_N, STAGES, PAIR, TAPW>;
-  auto kfn = igemm_i8_kernel<BLOCK_N, STAGES, DIALECT, RMODE, PAIR, TAPW>;
+  auto kfn = igemm_i8_kernel<BLOCK_N, STAGES, DIALECT, RMODE, PAIR, TAPW, PERROW>;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(PAIR ? 2 * workers : workers);
@@ -728,6 +792,17 @@ int launch_dialect(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs
   if (d == B200Q_RQ_QDM && r == B200Q_ROUND_HALF_AWAY_FROM_ZERO)
     return launch_one<BLOCK_N, STAGES, B200Q_RQ_QDM, B200Q_ROUND_HALF_AWAY_FROM_ZERO, PAIR, TAPW>(ta, tb, a, workers, s);
   return launch_one<BLOCK_N, STAGES, -1, -1, PAIR, TAPW>(ta, tb, a, workers, s);
+}
+
+// per-row parameters: built for the two dialects that have fast forms
+template <int BLOCK_N, int STAGES, bool PAIR>
+int launch_per_row(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& a, int workers, cudaStream_t s) {
+  const int d = a.epi.dialect, r = a.epi.round_mode;
+  if (d == B200Q_RQ_MULTIPLIER_SHIFT && r == B200Q_ROUND_HALF_UP)
+    return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP, PAIR, 1, true>(ta, tb, a, workers, s);
+  if (d == B200Q_RQ_QDM && r == B200Q_ROUND_HALF_AWAY_FROM_ZERO)
+    return launch_one<BLOCK_N, STAGES, B200Q_RQ_QDM, B200Q_ROUND_HALF_AWAY_FROM_ZERO, PAIR, 1, true>(ta, tb, a, workers, s);
+  return set_error(B200Q_ERR_UNSUPPORTED, "igemm: per-row parameters exist for MultiplierShift/half-up and QDM/half-away only");
 }
 
 }  // namespace
@@ -818,6 +893,23 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   a.bf16 = p.kind == IGEMM_KIND_BF16;
   // |accumulator| < 2^29 for every 8-bit operand pair: lets the epilogue fold the bias into one 64-bit constant
   a.acc_small = ((long long)a.num_kb * BLOCK_K * 32640ll) < (1ll << 29);
+  {
+    int lo, hi;
+    switch (epi.out_dtype) {
+      case B200Q_DT_I8: lo = -128; hi = 127; break;
+      case B200Q_DT_U8: lo = 0; hi = 255; break;
+      case B200Q_DT_I16: lo = -32768; hi = 32767; break;
+      case B200Q_DT_U16: lo = 0; hi = 65535; break;
+      default: lo = -2147483647 - 1; hi = 2147483647; break;
+    }
+    const int floor_post = epi.relu == B200Q_RELU_AFTER_REQUANT ? epi.out_zp : (-2147483647 - 1);
+    const bool out8 = epi.out_dtype == B200Q_DT_I8 || epi.out_dtype == B200Q_DT_U8;
+    a.floor_pre = epi.relu == B200Q_RELU_BEFORE_REQUANT ? 0 : (-2147483647 - 1);
+    a.sat_hi = hi;
+    a.sat_lo2 = lo > floor_post ? lo : floor_post;
+    a.pack_sat = out8 && p.out_mode != IGEMM_OUT_NCHW;
+    a.floor_needed = a.sat_lo2 > lo;
+  }
   a.acc_bound = a.acc_small ? (int)((long long)a.num_kb * BLOCK_K * 32640ll) : (1 << 29);
   a.bias_f32 = p.bias_f32;
   {
@@ -831,7 +923,7 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   CUDA_TRY(cudaGetDevice(&dev));
   CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const long long tiles128 = (long long)((p.rows + BLOCK_M - 1) / BLOCK_M) * ((p.n + block_n - 1) / block_n);
-  const bool pair = block_n == 256 && pair_mode_allowed() && tiles128 >= 2ll * sms;
+  const bool pair = block_n == 256 && pair_mode_allowed() && tiles128 >= 2ll * sms && p.rows > BLOCK_M;
   // three taps per filter row, one pixel apart, no ragged K block: the taps of a row share one activation block
   const bool tapfuse = pair && tapfuse_allowed() && p.taps_w == 3 && a.tap_step_w == 1 && p.k_per_tap % BLOCK_K == 0 && !a.bf16;
   const int tile_m = pair ? 2 * BLOCK_M : BLOCK_M;
@@ -854,6 +946,10 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   const int tiles = a.num_m_tiles * a.num_n_tiles;
   const int slots = pair ? sms / 2 : sms;
   const int workers = tiles < slots ? tiles : slots;
+  if (p.per_row_params) {
+    if (a.bf16 || block_n != 256) return set_error(B200Q_ERR_UNSUPPORTED, "igemm: per-row parameters need the 256-column tile");
+    return pair ? launch_per_row<256, 6, true>(ta, tb, a, workers, stream) : launch_per_row<256, 4, false>(ta, tb, a, workers, stream);
+  }
   if (tapfuse) return launch_dialect<256, 3, true, 3>(ta, tb, a, workers, stream);
   if (pair) return launch_dialect<256, 6, true>(ta, tb, a, workers, stream);
   switch (block_n) {

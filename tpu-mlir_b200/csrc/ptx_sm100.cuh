@@ -14,6 +14,21 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// four int32 values saturated to 8 bits and packed, first value in the lowest byte.
+// cvt.pack.sat d, a, b, c: d = (c << 16) | (sat(a) << 8) | sat(b)
+__device__ __forceinline__ uint32_t pack4_sat_u8(int32_t v0, int32_t v1, int32_t v2, int32_t v3) {
+  uint32_t hi, d;
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(v3), "r"(v2));
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(v1), "r"(v0), "r"(hi));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack4_sat_s8(int32_t v0, int32_t v1, int32_t v2, int32_t v3) {
+  uint32_t hi, d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(v3), "r"(v2));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(v1), "r"(v0), "r"(hi));
+  return d;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -66,6 +81,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same test, but the thread may stay suspended up to `hint_ns` while the phase is incomplete (it resumes as
+// soon as the phase completes): a long wait then costs a handful of instructions instead of a polling loop that
+// competes with the other warps of its scheduler for issue slots.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 
 // Wait for `parity` of barrier `bar`, giving up after `budget_ns`.  `abort_flag` (shared memory) is
 // polled so that one role's timeout releases every other role; on timeout the code `where` is left in it.
@@ -75,8 +106,8 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;  // suspended up to 20 us per try
+    if ((++spins & 7u) == 0u) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > budget_ns) {
         *abort_flag = where;
