@@ -36,7 +36,7 @@ OPS_PER_STEP = 2.0 * CFG["N"] * CFG["OC"] * CFG["H"] * CFG["W"] * CFG["C"] * CFG
 # DRAM traffic of one launch of the convolution kernel, from one ncu capture of this workload: 28.38 MB read (the
 # bordered image and the filters, once) + 0.03 MB written while the kernel runs (its 25.7 MB output is still in
 # L2 when it ends and is written back afterwards)
-CONV_DRAM_BYTES_PER_LAUNCH = 28_383_744 + 31_488
+CONV_DRAM_BYTES_PER_LAUNCH = 28_233_728 + 11_264
 METRIC, UNIT = "int8 conv TOPS", "TOPS"
 
 
@@ -224,6 +224,36 @@ def run_kernel_workload(args):
                                       l2="operands + output = 192 MB > L2"),
                           roofline=dict(bound="tensor", achieved=tops, peak=peak, unit="TOPS", frac=tops / peak,
                                         traffic=None, peak_basis=f"2 x {peaks['source']} dense bf16")))
+    elif args.workload == "conv1x1":
+        # the short-K layer of a bottleneck block (ResNet-50 layer1 conv3), channels-last in and out: the product is
+        # bound by its output stream, not by the tensor pipe
+        from tpu_mlir_b200.ops import Conv2DOp
+        N, Cin, H, W, OC = 256, 64, 56, 56, 256
+        rng = np.random.default_rng(0)
+        op = Conv2DOp(input_shape=(N, Cin, H, W), oc=OC, kernel_shape=(1, 1), pads=(0, 0, 0, 0), do_relu=True,
+                      input_dtype=L.DT_U8, out_dtype=L.DT_U8, quant_mode=L.QM_MULTIPLIER_SHIFT,
+                      multiplier=rng.integers(5000, 30000, OC), rshift=rng.integers(18, 26, OC))
+        d = op.desc     # (the op owns the arrays the descriptor points to)
+        x = torch.randint(0, 255, (N, H, W, Cin), dtype=torch.uint8, device="cuda")
+        w = torch.randint(-64, 64, (OC, Cin, 1, 1), dtype=torch.int8, device="cuda")
+        bias = torch.randint(-4096, 4096, (OC,), dtype=torch.int32, device="cuda")
+        y = torch.empty((N, H, W, OC), dtype=torch.uint8, device="cuda")
+        h = C.c_void_p()
+        L.check(lib.b200q_conv2d_dev_create(C.byref(d), P(w), P(bias), C.byref(h)))
+        mean_ms = _time_steps(lambda i: L.check(lib.b200q_conv2d_dev_run_layout(h, P(x), L.LAYOUT_NHWC, P(y), L.LAYOUT_NHWC,
+                                                                                 None)), args.steps, args.warmup)
+        L.check(lib.b200q_conv2d_dev_status(h, None))
+        lib.b200q_conv2d_dev_destroy(C.byref(h))
+        nbytes = x.numel() + y.numel() + w.numel()
+        gbs = nbytes / (mean_ms * 1e-3) / 1e9
+        lines.append(dict(metric="int8 1x1 conv GB/s", value=gbs, unit="GB/s", ms_per_step=mean_ms,
+                          config=dict(workload="tpu.Conv2D int8 channels-last n256 c64 56x56 oc256 k1, per-channel "
+                                               "MultiplierShift requant + ReLU, u8 out (transposed product)",
+                                      l2="input + output = 257 MB > L2", bytes_per_call=int(nbytes),
+                                      tops=2.0 * N * H * W * OC * Cin / (mean_ms * 1e-3) / 1e12),
+                          roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s",
+                                        frac=gbs / peaks["hbm_gbs"], traffic=None,
+                                        peak_basis=f"{peaks['source']} copy bandwidth")))
     elif args.workload == "a16":
         for M in (1, 4, 8):
             c = synth.a16_w4(seed=2, M=M)
@@ -397,7 +427,7 @@ def main():
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="conv", choices=["conv", "gemm", "a16", "hist", "resnet50", "calib"],
+    ap.add_argument("--workload", default="conv", choices=["conv", "gemm", "conv1x1", "a16", "hist", "resnet50", "calib"],
                     help="conv = the benchmark contract (BASELINE config 1); the others time one more kernel each")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")

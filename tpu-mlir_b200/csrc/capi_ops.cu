@@ -478,11 +478,9 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
   if (h->use_im2col) {
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[0], s));
     if (x_nhwc) {
-      const bool plain = h->bh == 0 && h->bw == 0;
-      if (!plain) B200Q_TRY(nhwc_to_bordered_launch(x, h->x_bordered.p, nb, (int)d.ic, (int)d.ih, (int)d.iw, h->bh, h->bw, s));
-      B200Q_TRY(im2col_nhwc_launch(plain ? x : h->x_bordered.p, h->a_cols.p, nb, (int)d.ic, h->Hp, h->Wp, h->g.oh, h->g.ow,
-                                   (int)d.kh, (int)d.kw, (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, h->bh - (int)d.pht,
-                                   h->bw - (int)d.pwl, h->kpad, s));
+      // rows gathered straight from the channels-last input; taps that fall into the padding read zeros
+      B200Q_TRY(im2col_nhwc_launch(x, h->a_cols.p, nb, (int)d.ic, (int)d.ih, (int)d.iw, h->g.oh, h->g.ow, (int)d.kh, (int)d.kw,
+                                   (int)d.sh, (int)d.sw, (int)d.dh, (int)d.dw, -(int)d.pht, -(int)d.pwl, h->kpad, s));
     } else if (h->few_channels) {
       // few input channels (a network's stem): rows are built from 8-byte runs of the NCHW input
       B200Q_TRY(im2col_few_channels_launch(x, x_is_f32, h->a_cols.p, nb, (int)d.ic, (int)d.ih, (int)d.iw, h->g.oh, h->g.ow,

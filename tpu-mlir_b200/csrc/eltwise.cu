@@ -247,7 +247,9 @@ __global__ void cast_q8_f32_kernel(const void* __restrict__ x, int dt, long long
   out[i] = __fmul_rn(scale, __fsub_rn((float)ld_q(x, i, dt), (float)zp));
 }
 
-// NHWC (zero-bordered by `b` pixels) -> im2col rows [N*OH*OW][kpad] with k = (fy*KW + fx)*C + c
+// NHWC [N][Hp][Wp][C] -> im2col rows [N*OH*OW][kpad] with k = (fy*KW + fx)*C + c.  Tap (fy, fx) of output pixel
+// (yo, xo) reads position (yo*sh + fy*dh + oy0, xo*sw + fx*dw + ox0); positions outside the image are zeros, so the
+// image may carry its padding as a zero border (oy0, ox0 >= 0) or not at all (oy0 = -pad_top, ox0 = -pad_left).
 __global__ void im2col_nhwc_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ a, int C, int Hp, int Wp, int OH,
                                    int OW, int KH, int KW, int sh, int sw, int dh, int dw, int oy0, int ox0, int kpad,
                                    long long total_units, int vec) {
@@ -262,12 +264,13 @@ __global__ void im2col_nhwc_kernel(const uint8_t* __restrict__ x, uint8_t* __res
   const long long n = row / ((long long)OW * OH);
   const int fy = tap / KW, fx = tap - fy * KW;
   const int iy = yo * sh + fy * dh + oy0, ix = xo * sw + fx * dw + ox0;   // bordered coordinates
+  const bool inside = iy >= 0 && iy < Hp && ix >= 0 && ix < Wp;
   const uint8_t* src = x + ((n * Hp + iy) * Wp + ix) * C;
   uint8_t* dst = a + row * kpad + (long long)tap * C;
   if (vec == 16) {
-    reinterpret_cast<uint4*>(dst)[piece] = reinterpret_cast<const uint4*>(src)[piece];
+    reinterpret_cast<uint4*>(dst)[piece] = inside ? reinterpret_cast<const uint4*>(src)[piece] : make_uint4(0u, 0u, 0u, 0u);
   } else {
-    for (int c = 0; c < C; ++c) dst[c] = src[c];
+    for (int c = 0; c < C; ++c) dst[c] = inside ? src[c] : (uint8_t)0;
   }
 }
 

@@ -122,6 +122,7 @@ class Conv2DOp:
                                  quant_mode=quant_mode, is_cv18xx=int(is_cv18xx), out_zp=out_zp,
                                  n_quant=self._rs.size, multipliers=mult_p, rshifts=rs_p, weight_version=0,
                                  algo=algo)
+        self.desc._arrays = (self._mult, self._rs)  # the descriptor points into these: they live as long as it does
         self.out_shape = (n, oc,
                           (ih + pht + phb - dilations[0] * (kernel_shape[0] - 1) - 1) // strides[0] + 1,
                           (iw + pwl + pwr - dilations[1] * (kernel_shape[1] - 1) - 1) // strides[1] + 1)
