@@ -91,14 +91,13 @@ __device__ __forceinline__ int32_t add_sat_s32(int32_t a, int32_t b) {
 template <int DIALECT>
 __device__ __forceinline__ int32_t requant_core_fast(int32_t a, int32_t m, int32_t p0, int32_t p1) {
   if (DIALECT == B200Q_RQ_QDM) {
-    const int64_t x = (int64_t)a * (int64_t)m + (1ll << 30);  // floor((a*m + 2^30) / 2^31) == half-up shift by 31
+    const int64_t x = ptx::mad_wide_s32(a, m, 1ll << 30);  // floor((a*m + 2^30) / 2^31) == half-up shift by 31
     const int32_t v = (int32_t)(x >> 31);                     // |a*m| <= 2^62 - 2^31: always fits int32 here
     const int32_t mant = v & ((p1 << 1) - 1);
     const int32_t ge0 = (int32_t)((uint32_t)(~v) >> 31);
     return (v >> p0) + (int32_t)((mant + ge0) > p1);
   } else {
-    int64_t x = (int64_t)a * (int64_t)m;
-    x = (x + (int64_t)(1ull << (p0 - 1))) >> p0;
+    int64_t x = ptx::mad_wide_s32(a, m, (int64_t)(1ull << (p0 - 1))) >> p0;
     return x > 2147483647ll ? 2147483647 : (x < -2147483648ll ? (int32_t)(-2147483647 - 1) : (int32_t)x);
   }
 }
@@ -581,7 +580,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             for (int j = 0; j < CH; ++j) {
               const int4 cp = PERROW ? row_cp : chan[cbase + j];  // {C_lo, C_hi, m, sh}: one broadcast 16-byte shared load
               const long long C = (long long)(((unsigned long long)(uint32_t)cp.y << 32) | (uint32_t)cp.x);
-              const long long x = (long long)(int32_t)r[j] * (long long)cp.z + C;
+              const long long x = ptx::mad_wide_s32((int32_t)r[j], cp.z, C);
               q[j] = (int32_t)(x >> 32) >> cp.w;
             }
           } else {
@@ -589,7 +588,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             for (int j = 0; j < CH; ++j) {
               const int4 cp = PERROW ? row_cp : chan[cbase + j];
               const long long C = (long long)(((unsigned long long)(uint32_t)cp.y << 32) | (uint32_t)cp.x);
-              const long long x = (long long)(int32_t)r[j] * (long long)cp.z + C;
+              const long long x = ptx::mad_wide_s32((int32_t)r[j], cp.z, C);
               q[j] = (int32_t)__funnelshift_r((uint32_t)x, (uint32_t)(x >> 32), (uint32_t)cp.w);
             }
           }
@@ -611,7 +610,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           for (int j = 0; j < CH; ++j) {
             const int4 cp = PERROW ? row_cp : chan[cbase + j];  // {C_lo, C_hi, m, t}
             const long long C = (long long)(((unsigned long long)(uint32_t)cp.y << 32) | (uint32_t)cp.x);
-            const long long x = (long long)(int32_t)r[j] * (long long)cp.z + C;
+            const long long x = ptx::mad_wide_s32((int32_t)r[j], cp.z, C);
             const int32_t w = (int32_t)(x >> 31);  // half-up shift by 31: C carries the 2^30
             // half away from zero for a right shift by t: (w + 2^(t-1) - (w < 0)) >> t, zero point inside chan_k
             q[j] = min(max((w + (w >> 31) + (PERROW ? row_ck : chan_k[cbase + j])) >> cp.w, sat_lo2), sat_hi);
@@ -914,7 +913,7 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   a.bias_f32 = p.bias_f32;
   {
     const long long out_elems = p.out_mode == IGEMM_OUT_NCHW
-                                    ? (long long)((p.rows + a.img_rows - 1) / a.img_rows) * p.n * p.out_h * p.out_w
+                                    ? (((long long)p.rows + a.img_rows - 1) / a.img_rows) * p.n * p.out_h * p.out_w
                                     : (long long)p.rows * p.ldc;  // (an upper bound for IGEMM_OUT_NHWC)
     a.out_small = out_elems < (1ll << 31);
   }

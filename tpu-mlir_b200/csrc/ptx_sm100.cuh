@@ -14,6 +14,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// a * b + c with a 32 x 32 -> 64-bit product: one widening multiply-add (written out so that the compiler cannot
+// fall back to a 64 x 64 multiply sequence)
+__device__ __forceinline__ long long mad_wide_s32(int32_t a, int32_t b, long long c) {
+  long long d;
+  asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(d) : "r"(a), "r"(b), "l"(c));
+  return d;
+}
+
 // four int32 values saturated to 8 bits and packed, first value in the lowest byte.
 // cvt.pack.sat d, a, b, c: d = (c << 16) | (sat(a) << 8) | sat(b)
 __device__ __forceinline__ uint32_t pack4_sat_u8(int32_t v0, int32_t v1, int32_t v2, int32_t v3) {
