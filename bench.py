@@ -352,7 +352,8 @@ def run_network_workload(args):
         cal_images = torch.from_numpy(synth.calibration_images(seed=4, count=64)).to(dev)
         table = resnet50.self_calibration_table(ops, cal_images, batch=16)          # every rank derives the same table
         graph, weights = resnet50.lower_int8(ops, table, batch=per)
-        m = module(channels_last=os.environ.get("B200Q_RESNET_LAYOUT", "nhwc") == "nhwc")
+        m = module(channels_last=os.environ.get("B200Q_RESNET_LAYOUT", "nhwc") == "nhwc",
+                   cuda_graph=os.environ.get("B200Q_RESNET_GRAPH", "1") == "1")
         m.load(graph, weights)
         x_h = torch.from_numpy(synth.calibration_images(seed=5, count=per, start=rank * per)).pin_memory()
         m.set_tensor("input", x_h)

@@ -47,6 +47,26 @@ def test_int8_graph_matches_oracle_on_every_tensor(lowered, channels_last):
     assert np.allclose(m.get_fp32_tensor("fc"), logits.astype(np.float32) * np.float32(info["scale"]))
 
 
+def test_cuda_graph_replay_matches_eager(lowered):
+    ops, table, graph, weights = lowered
+    eager = module(channels_last=True)
+    eager.load(graph, weights)
+    fast = module(channels_last=True, cuda_graph=True)
+    fast.load(graph, weights)
+    for seed in (35, 36):       # the second input goes through the replay of the graph captured for the first
+        x = synth.calibration_images(seed=seed, count=2)
+        for m in (eager, fast):
+            m.set_tensor("input", x)
+            m.invoke()
+        for name in ("conv1", "layer2.0.add", "layer4.2.conv3", "fc", "output"):
+            assert np.array_equal(eager.get_tensor(name), fast.get_tensor(name)), (seed, name)
+    assert fast._graph is not None
+    seen = []
+    fast.after_invoke(lambda name: seen.append(name))      # hooks need the op-by-op path
+    fast.invoke()
+    assert len(seen) == len(graph["ops"])
+
+
 def test_int8_logits_track_the_fp32_network(lowered):
     ops, table, graph, weights = lowered
     x = synth.calibration_images(seed=34, count=2)

@@ -16,7 +16,9 @@ with weights in a dict ``name -> numpy array`` (``<op>_filter``, ``<op>_bias``).
 
 ``module(channels_last=True)`` keeps the 4-D activations that convolutions, adds and pools produce as [N][H][W][C]
 on the device (the order the tensor-core kernels read and write), so no transposing kernel runs between ops;
-``get_tensor`` / ``set_tensor`` still speak NCHW, and the values are identical.
+``get_tensor`` / ``set_tensor`` still speak NCHW, and the values are identical.  ``module(cuda_graph=True)`` makes
+``invoke()`` replay one captured CUDA graph of all ops while no hook is registered (small per-GPU batches are
+otherwise bound by the host's launch rate).
 """
 from __future__ import annotations
 
@@ -36,9 +38,11 @@ def _P(t):
 
 
 class module:  # noqa: N801  (name of the reference class)
-    def __init__(self, device: Optional[int] = None, channels_last: bool = False):
+    def __init__(self, device: Optional[int] = None, channels_last: bool = False, cuda_graph: bool = False):
         import torch
         self.channels_last = bool(channels_last)
+        self.cuda_graph = bool(cuda_graph)  # invoke() without hooks replays one captured CUDA graph of all ops
+        self._graph = None
         self._nhwc = set()  # names of the tensors stored as [N][H][W][C]
         self.torch = torch
         if not torch.cuda.is_available():
@@ -218,7 +222,25 @@ class module:  # noqa: N801  (name of the reference class)
     def clear_hooks(self):
         self._before, self._after = [], []
 
+    def _capture(self):
+        """All ops of the graph as one CUDA graph (every launch of the device face is asynchronous on the current
+        stream and allocates nothing).  One eager pass first, so that one-time set-up is not captured."""
+        torch = self.torch
+        for run in self._plans:
+            run()
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for run in self._plans:
+                run()
+        self._graph = g
+
     def invoke(self, fixed_to_float: bool = True):
+        if self.cuda_graph and not self._before and not self._after:
+            if self._graph is None:
+                self._capture()
+            self._graph.replay()
+            return
         for op, run in zip(self.graph["ops"], self._plans):
             for fn in self._before:
                 fn(op["name"])
