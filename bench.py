@@ -491,9 +491,10 @@ def main():
         for i in range(args.warmup):
             step_device(i)
         L.check(lib.b200q_conv2d_dev_status(h, sptr))
-        L.check(lib.b200q_conv2d_dev_set_profiling(h, 1))
         barrier()
         t_wall0 = time.time()
+        # pass 1, the timed region: K steps as a user runs them (no events between the kernels, so the convolution
+        # kernel launches as a programmatic dependent of its layout kernel)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for i in range(args.steps):
@@ -502,8 +503,16 @@ def main():
         e1.synchronize()
         L.check(lib.b200q_conv2d_dev_status(h, sptr))
         barrier()
-        clocks = sampler.stop(t_wall0, time.time()) if rank == 0 else None
         step_ms = [e0.elapsed_time(e1)]
+        # pass 2, the same K steps with the library recording events around each kernel: the per-kernel durations
+        # behind `roofline` (the events serialise the two kernels, so their sum is a little above a step of pass 1)
+        L.check(lib.b200q_conv2d_dev_set_profiling(h, 1))
+        for i in range(args.steps):
+            step_device(i)
+        stream.synchronize()
+        L.check(lib.b200q_conv2d_dev_status(h, sptr))
+        barrier()
+        clocks = sampler.stop(t_wall0, time.time()) if rank == 0 else None
         runs, lay, ker = C.c_int64(), C.c_double(), C.c_double()
         L.check(lib.b200q_conv2d_dev_profile(h, C.byref(runs), C.byref(lay), C.byref(ker)))
         layout_ms, kernel_ms = [lay.value / runs.value], [ker.value / runs.value]
@@ -552,7 +561,9 @@ def main():
                     ms_per_step=total_ms / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
                     dtype="s8 x s8 -> s32 accumulate -> s8", data="synthetic",
                     config=dict(workload=WORKLOAD, l2="6 input/output sets used round-robin (308 MB > L2), no flush kernel",
-                                per_step_kernels=dict(layout_ms=float(np.mean(layout_ms)), conv_ms=k_ms)),
+                                per_step_kernels=dict(layout_ms=float(np.mean(layout_ms)), conv_ms=k_ms,
+                                                      source="a second pass of the same K steps with CUDA events "
+                                                             "recorded around each kernel")),
                     roofline=dict(bound="tensor", achieved=achieved, peak=int8_peak, unit="TOPS",
                                   frac=achieved / int8_peak, traffic=CONV_DRAM_BYTES_PER_LAUNCH,
                                   traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch "

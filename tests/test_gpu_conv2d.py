@@ -190,6 +190,31 @@ def test_conv_channels_last_needs_a_tensor_core_route():
     lib.b200q_conv2d_dev_destroy(C.byref(h))
 
 
+def test_conv_back_to_back_runs_read_fresh_inputs():
+    """The convolution kernel launches as a programmatic dependent of its layout kernel (it becomes resident while the
+    layout kernel drains and waits for it before reading the image): alternating inputs queued without any
+    synchronisation must each produce their own result."""
+    ca = synth.conv2d_int8(seed=91, N=8, C=128, H=28, W=28, OC=128)
+    cb = dict(ca)
+    cb["x"] = np.random.default_rng(92).integers(-128, 128, size=ca["x"].shape, dtype=np.int8)
+    want_a, mult, rshift = oracle_conv(ca, qmode=oracle.QM_QDM, is_cv18xx=True)
+    want_b, _, _ = oracle_conv(cb, qmode=oracle.QM_QDM, is_cv18xx=True)
+    d = Conv2DOp(input_shape=ca["x"].shape, oc=128, kernel_shape=(3, 3), pads=(1, 1, 1, 1), do_relu=True,
+                 quant_mode=L.QM_QDM, is_cv18xx=True, multiplier=mult, rshift=rshift).desc
+    w_d, b_d, xa_d, xb_d = dev(ca["w"]), dev(ca["bias"]), dev(ca["x"]), dev(cb["x"])
+    ya_d, yb_d = empty_dev(want_a.shape, L.DT_I8), empty_dev(want_a.shape, L.DT_I8)
+    h = C.c_void_p()
+    lib = L.lib()
+    L.check(lib.b200q_conv2d_dev_create(C.byref(d), ptr(w_d), ptr(b_d), C.byref(h)))
+    for _ in range(25):
+        L.check(lib.b200q_conv2d_dev_run(h, ptr(xa_d), ptr(ya_d), None))
+        L.check(lib.b200q_conv2d_dev_run(h, ptr(xb_d), ptr(yb_d), None))
+    L.check(lib.b200q_conv2d_dev_status(h, None))
+    lib.b200q_conv2d_dev_destroy(C.byref(h))
+    assert np.array_equal(ya_d.cpu().numpy(), want_a)
+    assert np.array_equal(yb_d.cpu().numpy(), want_b)
+
+
 def test_config1_full_size():
     """BASELINE config 1 at full size: N=32, C=256, 56x56, OC=256, 3x3, stride 1, pad 1, fused ReLU, QDM requant."""
     c = synth.conv2d_int8(seed=1)

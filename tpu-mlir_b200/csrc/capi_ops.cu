@@ -462,6 +462,9 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.out_mode = y_nhwc ? IGEMM_OUT_NHWC : IGEMM_OUT_NCHW;
     p.ldc = y_nhwc ? (long long)d.oc : 0;
     p.out = y;
+    // Programmatic dependent launch: behind a kernel of this library (layout, im2col, add, pool, another convolution)
+    // the grid sets itself up while that kernel drains; behind any other kernel the attribute changes nothing.
+    p.dependent_launch = h->profiling ? 0 : 1;
     if (h->pair_taps) {
       p.k_per_tap = 128;                    // two pixels' channels
       p.taps_w = (int)((d.kw + 1) / 2);
@@ -513,6 +516,7 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.out_mode = y_nhwc ? IGEMM_OUT_ROWMAJOR : IGEMM_OUT_NCHW;  // the rows are the output pixels in NHW order
     p.ldc = y_nhwc ? (long long)d.oc : 0;
     p.out = y;
+    p.dependent_launch = h->profiling ? 0 : 1;
     if (y_nhwc && transposed_product_ok(h->epi, (int)d.oc, p.rows)) make_transposed(&p, (int)d.oc);
     B200Q_TRY(igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s));
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[2], s));

@@ -94,6 +94,7 @@ template <bool A_UNS, bool B_UNS>
 __global__ void __launch_bounds__(256)
 add_i8x16_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, long long n16, int m0, int s0, int m1, int s1,
                  int lo, int hi, uint4* __restrict__ out) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a dependent convolution may set itself up meanwhile
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n16) return;
   const uint4 va = a[i], vb = b[i];
@@ -253,6 +254,7 @@ __global__ void cast_q8_f32_kernel(const void* __restrict__ x, int dt, long long
 __global__ void im2col_nhwc_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ a, int C, int Hp, int Wp, int OH,
                                    int OW, int KH, int KW, int sh, int sw, int dh, int dw, int oy0, int ox0, int kpad,
                                    long long total_units, int vec) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a dependent convolution may set itself up meanwhile
   // one unit = (row, tap, vec-byte piece of C); vec = 16 when C % 16 == 0, else 1 unit = (row, tap) with a byte loop
   const long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (u >= total_units) return;
@@ -325,6 +327,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 im2col_few_channels_kernel(const T* __restrict__ x, uint8_t* __restrict__ a, int C, int H, int W, int OH, int OW, int KH,
                            int sh, int sw, int pht, int pwl, int kpad, int band, int wpad, int pwl_s) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a dependent convolution may set itself up meanwhile
   extern __shared__ __align__(16) uint8_t tile[];  // [C][rows_in][wpad]
   const int n = blockIdx.y, oy0 = blockIdx.x * band;
   const int rows_out = min(band, OH - oy0);
@@ -384,6 +387,7 @@ im2col_few_channels_kernel(const T* __restrict__ x, uint8_t* __restrict__ a, int
 // [N][H][W][C] -> the interior of the zero-bordered [N][H+2bh][W+2bw][C] (16 channels per thread)
 __global__ void __launch_bounds__(256)
 nhwc_to_bordered_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, long long total16, int c16, int H, int W, int bh, int bw) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a dependent convolution may set itself up meanwhile
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total16) return;
   const int c = (int)(i % c16);
@@ -400,6 +404,7 @@ template <bool SIGNED>
 __global__ void __launch_bounds__(256)
 maxpool_nhwc_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, long long total16, int c16, int ih, int iw, int kh, int kw,
                     int sh, int sw, int pht, int pwl, int oh, int ow, int do_relu) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a dependent convolution may set itself up meanwhile
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total16) return;
   const int c = (int)(i % c16);

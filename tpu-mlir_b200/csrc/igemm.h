@@ -30,6 +30,7 @@ struct IGemmProblem {
   void* out;
   int kind;                               // IGEMM_KIND_*; for BF16 k_per_tap and the pitches are in BYTES (2 per element)
   const float* bias_f32;                  // BF16 kind: optional per-column bias
+  int dependent_launch;                   // launch as a programmatic dependent of the previous kernel in the stream
   int per_row_params;                     // the epilogue's per-channel arrays index the GEMM's ROWS (transposed product);
                                           // 8-bit kinds with a fast dialect, n > 128
 };
@@ -49,6 +50,7 @@ struct IGemmArgs {
   int acc_small;
   int out_small;
   int floor_pre, sat_lo2, sat_hi, pack_sat, floor_needed;  // epilogue constants derived from epi (see the kernel)
+  int dependent_launch;
   int acc_bound;  // |accumulator| <= this for every 8-bit operand pair (valid when acc_small)
 };
 

@@ -200,6 +200,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 const IGemmArgs args) {
   using L = SmemLayout<BLOCK_N, STAGES, PAIR, TAPW>;
   static_assert(TAPW == 1 || PAIR, "the tap-fused form exists for CTA pairs only");
+  ptx::griddep_launch_dependents();  // a dependent kernel may become resident as this grid's CTAs retire
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = ptx::smem_u32(smem);
@@ -265,6 +266,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      ptx::griddep_wait();  // the operands may be the previous kernel's output (the set-up above overlapped its tail)
       for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
         const int m0 = (tile / args.num_n_tiles) * TILE_M + (int)cta_rank * BLOCK_M;
         const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
@@ -410,6 +412,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #define sat_hi (args.sat_hi)
 #define pack_sat (args.pack_sat != 0)
 #define floor_needed (args.floor_needed != 0)
+    ptx::griddep_wait();  // before the first read of a parameter array or write of the output
     int acc = 0;
     uint32_t acc_phase = 0;
     int cached_n0 = -1;
@@ -771,13 +774,17 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& ar
   cfg.blockDim = dim3(L::NUM_THREADS);
   cfg.dynamicSmemBytes = L::DYN_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = PAIR ? 2 : 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // after a kernel that releases its dependents early (the layout kernel of a convolution): this grid may become
+  // resident and set itself up while that kernel drains; every role waits before its first global access
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = args.dependent_launch ? 2 : 1;
   CUDA_TRY(cudaLaunchKernelEx(&cfg, kfn, ta, tb, args));
   return B200Q_OK;
 }
@@ -909,6 +916,7 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
     a.pack_sat = out8 && p.out_mode != IGEMM_OUT_NCHW;
     a.floor_needed = a.sat_lo2 > lo;
   }
+  a.dependent_launch = p.dependent_launch;
   a.acc_bound = a.acc_small ? (int)((long long)a.num_kb * BLOCK_K * 32640ll) : (1 << 29);
   a.bias_f32 = p.bias_f32;
   {

@@ -14,6 +14,12 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// Programmatic dependent launch.  griddep_wait: the calling thread waits until the grids this one depends on have
+// completed and their memory is visible (a no-op for a launch without the attribute).  griddep_launch_dependents:
+// this CTA no longer holds back the launch of a dependent grid.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // a * b + c with a 32 x 32 -> 64-bit product: one widening multiply-add (written out so that the compiler cannot
 // fall back to a 64 x 64 multiply sequence)
 __device__ __forceinline__ long long mad_wide_s32(int32_t a, int32_t b, long long c) {
