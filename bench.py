@@ -543,7 +543,7 @@ def main():
         if not same:
             raise SystemExit("operator face and device face disagree")
         e2e = dict(s=e2e_s, h2d=int(x_h.numel() * 4), d2h=int(y_h.numel() * 4))
-        gpu_launches += 3 * args.steps      # f32->bordered layout, conv, int8->f32
+        gpu_launches += 3 * 8 * args.steps  # per piece of the batch (8 pieces): f32->bordered layout, conv, int8->f32
 
     # ---- aggregate over ranks (max time)
     t = torch.tensor([total_ms, e2e["s"] if e2e else 0.0], dtype=torch.float64, device="cuda")
