@@ -230,6 +230,16 @@ int b200q_requant_int_axis_dev(const int32_t *x, int64_t outer, int64_t C, int64
  * out = saturate(relu(RSR(a*m0, s0, half-up) + RSR(b*m1, s1, half-up))). */
 int b200q_add_i8_dev(const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t count, int32_t m0,
                      int32_t s0, int32_t m1, int32_t s1, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
+/* tpu.Lut (lib/Dialect/Tpu/Interfaces/Common/Lut.cpp:20-32): out[i] = table[x[i] mod 256] (a negative int8 index
+ * wraps by +256).  x is 8-bit; `table` holds 256 entries of `table_dtype`, which is also the output type. */
+int b200q_lut_dev(const void *x, int64_t count, const void *table, int32_t table_dtype, void *out, void *stream);
+/* tpu.MulShift (MulShift.cpp:19-41): out = saturate(RSR((x - in_zp) * multiplier, rshift, half-up) + out_zp). */
+int b200q_mulshift_i8_dev(const void *x, int32_t dtype, int64_t count, int32_t multiplier, int32_t rshift,
+                          int32_t in_zp, int32_t out_zp, int32_t out_dtype, void *out, void *stream);
+/* tpu.Mul, symmetric int8 operands of equal shape (Mul.cpp:23-29,:72-85): the op's ReLU acts on the product, then
+ * out = saturate(RSR(product * multiplier, rshift, half-up)).  Broadcasting operands are not implemented. */
+int b200q_mul_i8_dev(const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t count,
+                     int32_t multiplier, int32_t rshift, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
 /* tpu.Pool2D int8 (Pool2D.cpp:160-192): max, or average as RSR(window_sum * multiplier, rshift, half-up);
  * x is [nc][ih][iw] (N and C merged). */
 int b200q_pool2d_i8_dev(const void *x, int32_t dtype, int64_t nc, int32_t ih, int32_t iw, int32_t kh, int32_t kw,

@@ -72,6 +72,12 @@ def lib():
         L.orc_requant_int_axis.argtypes = [vp, i64, i64, i64, vp, i32, i32, i32, i32, i32, vp]
         L.orc_requant_int.restype = None
         L.orc_requant_int.argtypes = [vp, i64, i64, i64, i32, i32, i32, i32, i32, vp]
+        L.orc_lut.restype = None
+        L.orc_lut.argtypes = [vp, i32, i64, vp, i32, vp]
+        L.orc_mulshift_int8.restype = None
+        L.orc_mulshift_int8.argtypes = [vp, i32, i64, i64, i64, i64, i64, i32, vp]
+        L.orc_mul_int8.restype = None
+        L.orc_mul_int8.argtypes = [vp, i32, vp, i32, i64, i64, i64, i32, i32, vp]
         L.orc_add_int8.restype = None
         L.orc_add_int8.argtypes = [vp, i32, vp, i32, i64, i64, i64, i64, i64, i32, i32, vp]
         L.orc_pool2d_int8.restype = None
@@ -248,6 +254,31 @@ def add_int8(a, b, m0, s0, m1, s1, *, do_relu=False, out_dt=DT_I8):
     a, b = _c(a), _c(b)
     out = np.empty(a.shape, dtype=_NP_OF_DT[out_dt])
     lib().orc_add_int8(_p(a), _is_u(a), _p(b), _is_u(b), a.size, m0, s0, m1, s1, int(do_relu), out_dt, _p(out))
+    return out
+
+
+def lut(x, table):
+    """tpu.Lut (Lut.cpp:20-32): out = table[x mod 256]; the table's dtype is the output's."""
+    x, table = _c(x), _c(table)
+    assert table.size == 256
+    out = np.empty(x.shape, dtype=table.dtype)
+    lib().orc_lut(_p(x), _is_u(x), x.size, _p(table), table.dtype.itemsize, _p(out))
+    return out
+
+
+def mulshift_int8(x, multiplier, rshift, *, in_zp=0, out_zp=0, out_dt=DT_I8):
+    """tpu.MulShift (MulShift.cpp:19-41)."""
+    x = _c(x)
+    out = np.empty(x.shape, dtype=_NP_OF_DT[out_dt])
+    lib().orc_mulshift_int8(_p(x), _is_u(x), x.size, multiplier, rshift, in_zp, out_zp, out_dt, _p(out))
+    return out
+
+
+def mul_int8(a, b, multiplier, rshift, *, do_relu=False, out_dt=DT_I8):
+    """tpu.Mul, symmetric int8, equal shapes (Mul.cpp:72-85)."""
+    a, b = _c(a), _c(b)
+    out = np.empty(a.shape, dtype=_NP_OF_DT[out_dt])
+    lib().orc_mul_int8(_p(a), _is_u(a), _p(b), _is_u(b), a.size, multiplier, rshift, int(do_relu), out_dt, _p(out))
     return out
 
 

@@ -384,6 +384,40 @@ void orc_add_int8(const void *a, int a_unsigned, const void *b, int b_unsigned, 
   }
 }
 
+/* tpu::LutOp::inference, lib/Dialect/Tpu/Interfaces/Common/Lut.cpp:20-32: out[i] = table[x[i] mod 256]
+ * (a negative index wraps by +256); `esize` bytes per table entry / output element. */
+void orc_lut(const void *x, int x_unsigned, int64_t count, const void *table, int esize, void *out) {
+  for (int64_t i = 0; i < count; ++i) {
+    int64_t off = load_q8(x, i, x_unsigned);
+    if (off < 0) off += 256;
+    memcpy((char *)out + i * esize, (const char *)table + off * esize, (size_t)esize);
+  }
+}
+
+/* tpu::MulShiftOp::inference, lib/Dialect/Tpu/Interfaces/Common/MulShift.cpp:19-41:
+ * out = saturate(applyMultiplierAndRShift(x - in_zp, multiplier, rshift) + out_zp)  (MultiplierShift, half-up). */
+void orc_mulshift_int8(const void *x, int x_unsigned, int64_t count, int64_t multiplier, int64_t rshift, int64_t in_zp,
+                       int64_t out_zp, int out_dt, void *out) {
+  for (int64_t i = 0; i < count; ++i) {
+    int64_t v = orc_apply_multiplier_rshift(load_q8(x, i, x_unsigned) - in_zp, multiplier, rshift, QM_MULTIPLIER_SHIFT,
+                                            RM_HALF_UP, 0);
+    store_q(out, i, out_dt, orc_saturate(v + out_zp, out_dt));
+  }
+}
+
+/* tpu::MulOp::inference, symmetric int8, equal shapes, non-cv18xx: lib/Dialect/Tpu/Interfaces/Common/Mul.cpp:72-85:
+ * the product (exact in the reference's float) is rescaled with MultiplierShift/half-up and saturated; the ReLU of
+ * the op is applied to the product by the binary primitive (Mul.cpp:23-29: do_relu is an argument of its set-up). */
+void orc_mul_int8(const void *a, int a_unsigned, const void *b, int b_unsigned, int64_t count, int64_t multiplier,
+                  int64_t rshift, int do_relu, int out_dt, void *out) {
+  for (int64_t i = 0; i < count; ++i) {
+    int64_t prod = load_q8(a, i, a_unsigned) * load_q8(b, i, b_unsigned);
+    if (do_relu && prod < 0) prod = 0;
+    int64_t v = orc_apply_multiplier_rshift(prod, multiplier, rshift, QM_MULTIPLIER_SHIFT, RM_HALF_UP, 0);
+    store_q(out, i, out_dt, orc_saturate(v, out_dt));
+  }
+}
+
 /* tpu::Pool2DOp::inference, lib/Dialect/Tpu/Interfaces/Common/Pool2D.cpp:160-192.
  *   mode 0 = max (pad cells never win), mode 1 = avg: the window SUM (count_include_pad, zero pad) is
  *   recovered as to_int(avg*kh*kw) and rescaled with MultiplierShift/half-up, ReLU, saturate. */

@@ -84,6 +84,50 @@ def test_pool_channels_last():
                                           ptr(out), None) == L.ERR_UNSUPPORTED
 
 
+@pytest.mark.parametrize("n", [1, 15, 16, 4099, 1 << 20])
+def test_lut(n):
+    rng = np.random.default_rng(n)
+    for xdt in (np.int8, np.uint8):
+        x = rng.integers(np.iinfo(xdt).min, np.iinfo(xdt).max + 1, n, dtype=xdt)
+        for tdt, code in ((np.int8, L.DT_I8), (np.uint8, L.DT_U8), (np.float32, L.DT_F32)):
+            table = (rng.integers(-128, 128, 256).astype(tdt) if tdt != np.float32
+                     else rng.standard_normal(256).astype(np.float32))
+            want = oracle.lut(x, table)
+            x_d, t_d = dev(x), dev(table)
+            out = torch.empty(n, dtype=getattr(torch, np.dtype(tdt).name), device="cuda")
+            L.check(lib().b200q_lut_dev(ptr(x_d), n, ptr(t_d), code, ptr(out), None))
+            assert np.array_equal(out.cpu().numpy(), want), (xdt, tdt)
+
+
+def test_lut_unaligned_views():
+    rng = np.random.default_rng(3)
+    x = rng.integers(-128, 128, 1000, dtype=np.int8)
+    table = rng.integers(0, 256, 256).astype(np.uint8)
+    x_d, t_d = dev(x), dev(table)
+    out = torch.zeros(1000, dtype=torch.uint8, device="cuda")
+    L.check(lib().b200q_lut_dev(C.c_void_p(x_d.data_ptr() + 3), 900, ptr(t_d), L.DT_U8, C.c_void_p(out.data_ptr() + 5), None))
+    assert np.array_equal(out.cpu().numpy()[5:905], oracle.lut(x[3:903], table))
+
+
+def test_mulshift_and_mul():
+    rng = np.random.default_rng(12)
+    n = 70001
+    a = rng.integers(-128, 128, n, dtype=np.int8)
+    b = rng.integers(0, 256, n, dtype=np.uint8)
+    a_d, b_d = dev(a), dev(b)
+    for x, x_d, m, s, izp, ozp, odt in ((a, a_d, 77, 5, 0, 0, L.DT_I8), (b, b_d, 19000, 14, 128, -3, L.DT_I8),
+                                        (a, a_d, -3, 0, 0, 7, L.DT_U8), (b, b_d, 2**30, 31, 5, 0, L.DT_U8)):
+        want = oracle.mulshift_int8(x, m, s, in_zp=izp, out_zp=ozp, out_dt=odt)
+        out = empty_dev((n,), odt)
+        L.check(lib().b200q_mulshift_i8_dev(ptr(x_d), dt_of(x), n, m, s, izp, ozp, odt, ptr(out), None))
+        assert np.array_equal(out.cpu().numpy(), want), (m, s, izp, ozp, odt)
+    for m, s, relu, odt in ((3, 4, True, L.DT_U8), (1200, 17, False, L.DT_I8), (1, 0, False, L.DT_I8), (2**20, 30, True, L.DT_I8)):
+        want = oracle.mul_int8(a, b, m, s, do_relu=relu, out_dt=odt)
+        out = empty_dev((n,), odt)
+        L.check(lib().b200q_mul_i8_dev(ptr(a_d), dt_of(a), ptr(b_d), dt_of(b), n, m, s, int(relu), odt, ptr(out), None))
+        assert np.array_equal(out.cpu().numpy(), want), (m, s, relu, odt)
+
+
 def test_cast_both_ways():
     rng = np.random.default_rng(6)
     x = (rng.standard_normal(50001) * 3).astype(np.float32)

@@ -94,6 +94,10 @@ SIGNATURES = {
     "b200q_add_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 6 +
                          [C.c_void_p, C.c_void_p]),
     "b200q_pool2d_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 15 + [C.c_void_p, C.c_void_p]),
+    "b200q_lut_dev": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
+    "b200q_mulshift_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 5 + [C.c_void_p, C.c_void_p]),
+    "b200q_mul_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 4 +
+                         [C.c_void_p, C.c_void_p]),
     "b200q_pool2d_i8_nhwc_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 16 + [C.c_void_p, C.c_void_p]),
     "b200q_cast_f32_to_q8_dev": (C.c_int, [C.c_void_p, C.c_int64, C.c_double, C.c_int32, C.c_int32, C.c_int32,
                                            C.c_void_p, C.c_void_p]),

@@ -832,6 +832,25 @@ int b200q_add_i8_dev(const void* a, int32_t a_dtype, const void* b, int32_t b_dt
   return add_i8_launch(a, a_dtype, b, b_dtype, count, m0, s0, m1, s1, do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_lut_dev(const void* x, int64_t count, const void* table, int32_t table_dtype, void* out, void* stream) {
+  if (!x || !table || !out || count < 0) return set_error(B200Q_ERR_INVALID, "lut_dev: bad argument");
+  return lut_launch(x, count, table, (int)dtype_size(table_dtype), out, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_mulshift_i8_dev(const void* x, int32_t dtype, int64_t count, int32_t multiplier, int32_t rshift, int32_t in_zp,
+                          int32_t out_zp, int32_t out_dtype, void* out, void* stream) {
+  if (!x || !out || count < 0 || !is_q8(dtype) || rshift < 0 || rshift > 62)
+    return set_error(B200Q_ERR_INVALID, "mulshift_i8_dev: bad argument");
+  return mulshift_i8_launch(x, dtype, count, multiplier, rshift, in_zp, out_zp, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_mul_i8_dev(const void* a, int32_t a_dtype, const void* b, int32_t b_dtype, int64_t count, int32_t multiplier,
+                     int32_t rshift, int32_t do_relu, int32_t out_dtype, void* out, void* stream) {
+  if (!a || !b || !out || count < 0 || !is_q8(a_dtype) || !is_q8(b_dtype) || rshift < 0 || rshift > 62)
+    return set_error(B200Q_ERR_INVALID, "mul_i8_dev: bad argument");
+  return mul_i8_launch(a, a_dtype, b, b_dtype, count, multiplier, rshift, do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_pool2d_i8_nhwc_dev(const void* x, int32_t dtype, int64_t n, int32_t c, int32_t ih, int32_t iw, int32_t kh, int32_t kw,
                              int32_t sh, int32_t sw, int32_t pht, int32_t phb, int32_t pwl, int32_t pwr, int32_t is_avg,
                              int32_t multiplier, int32_t rshift, int32_t do_relu, int32_t out_dtype, void* out, void* stream) {

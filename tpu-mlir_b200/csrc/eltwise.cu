@@ -383,6 +383,58 @@ im2col_few_channels_kernel(const T* __restrict__ x, uint8_t* __restrict__ a, int
   }
 }
 
+// ------------------------------------------------------------------------------------------- Lut / MulShift / Mul
+// tpu.Lut (Lut.cpp:20-32): out = table[x mod 256].  The 256-entry table sits in shared memory; 8-bit tensors move as
+// 16-byte words (16 look-ups per thread).
+template <typename E>
+__global__ void __launch_bounds__(256)
+lut_kernel(const uint8_t* __restrict__ x, long long n, const E* __restrict__ table, E* __restrict__ out, int vec16) {
+  __shared__ E tab[256];
+  tab[threadIdx.x] = table[threadIdx.x];
+  __syncthreads();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (sizeof(E) == 1 && vec16) {
+    const long long n16 = n / 16;
+    if (i < n16) {
+      const uint4 v = reinterpret_cast<const uint4*>(x)[i];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        o[k] = (uint32_t)tab[w[k] & 0xff] | ((uint32_t)tab[(w[k] >> 8) & 0xff] << 8) |
+               ((uint32_t)tab[(w[k] >> 16) & 0xff] << 16) | ((uint32_t)tab[w[k] >> 24] << 24);
+      reinterpret_cast<uint4*>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    const long long t = n16 * 16 + i;  // the tail, one element per thread of the first blocks
+    if (i < n - n16 * 16) out[t] = tab[x[t]];
+  } else {
+    if (i < n) out[i] = tab[x[i]];
+  }
+}
+
+// tpu.MulShift (MulShift.cpp:19-41): out = saturate(RSR((x - in_zp) * m, s, half-up) + out_zp)
+__global__ void __launch_bounds__(256)
+mulshift_i8_kernel(const void* __restrict__ x, int dt, long long n, int m, int sft, int in_zp, int out_zp, int out_dt,
+                   void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t v = rshift_round((int64_t)(ld_q(x, i, dt) - in_zp) * m, sft, B200Q_ROUND_HALF_UP) + out_zp;
+  st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
+}
+
+// tpu.Mul, symmetric 8-bit tensors of equal shape (Mul.cpp:23-29,:72-85): the ReLU acts on the product, then
+// out = saturate(RSR(prod * m, s, half-up))
+__global__ void __launch_bounds__(256)
+mul_i8_kernel(const void* __restrict__ a, int a_dt, const void* __restrict__ b, int b_dt, long long n, int m, int sft,
+              int do_relu, int out_dt, void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int64_t prod = (int64_t)ld_q(a, i, a_dt) * ld_q(b, i, b_dt);
+  if (do_relu && prod < 0) prod = 0;
+  const int64_t v = rshift_round(prod * m, sft, B200Q_ROUND_HALF_UP);
+  st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
+}
+
 // ------------------------------------------------------------------------------------------- NHWC-resident graphs
 // [N][H][W][C] -> the interior of the zero-bordered [N][H+2bh][W+2bw][C] (16 channels per thread)
 __global__ void __launch_bounds__(256)
@@ -606,6 +658,39 @@ int im2col_few_channels_launch(const void* x, int x_is_f32, void* a, long long N
     if (smem > 48 * 1024) CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k<<<grid, 256, smem, s>>>((const uint8_t*)x, (uint8_t*)a, C, H, W, OH, OW, KH, sh, sw, pht, pwl, kpad, band, wpad, pwl_s);
   }
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int lut_launch(const void* x, long long n, const void* table, int elem_size, void* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  if (elem_size == 1) {
+    const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const long long threads = al ? (n / 16 > 16 ? n / 16 : 16) : n;  // vector form: at least the (< 16 element) tail
+    lut_kernel<uint8_t><<<nblk(threads, 256), 256, 0, s>>>((const uint8_t*)x, n, (const uint8_t*)table, (uint8_t*)out, al ? 1 : 0);
+  } else if (elem_size == 2) {
+    lut_kernel<uint16_t><<<nblk(n, 256), 256, 0, s>>>((const uint8_t*)x, n, (const uint16_t*)table, (uint16_t*)out, 0);
+  } else if (elem_size == 4) {
+    lut_kernel<uint32_t><<<nblk(n, 256), 256, 0, s>>>((const uint8_t*)x, n, (const uint32_t*)table, (uint32_t*)out, 0);
+  } else {
+    return set_error(B200Q_ERR_INVALID, "lut: table entries are 1, 2 or 4 bytes");
+  }
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int mulshift_i8_launch(const void* x, int dt, long long n, int m, int sft, int in_zp, int out_zp, int out_dt, void* out,
+                       cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  mulshift_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(x, dt, n, m, sft, in_zp, out_zp, out_dt, out);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int mul_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n, int m, int sft, int do_relu, int out_dt,
+                  void* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  mul_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(a, a_dt, b, b_dt, n, m, sft, do_relu, out_dt, out);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

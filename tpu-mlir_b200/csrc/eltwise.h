@@ -15,6 +15,12 @@ int add_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n,
 // mode 0 = max, 1 = average (window sum * multi >> rshift, half up)
 int pool2d_i8_launch(const void* x, int dt, int NC, int ih, int iw, int kh, int kw, int sh, int sw, int pht, int phb,
                      int pwl, int pwr, int mode, int multi, int rshift, int do_relu, int out_dt, void* out, cudaStream_t s);
+// tpu.Lut / tpu.MulShift / tpu.Mul (8-bit, equal shapes)
+int lut_launch(const void* x, long long n, const void* table, int elem_size, void* out, cudaStream_t s);
+int mulshift_i8_launch(const void* x, int dt, long long n, int m, int sft, int in_zp, int out_zp, int out_dt, void* out,
+                       cudaStream_t s);
+int mul_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n, int m, int sft, int do_relu, int out_dt,
+                  void* out, cudaStream_t s);
 // NHWC-resident graphs: [N][H][W][C] -> interior of the zero-bordered image; pooling on [N][H][W][C]
 int nhwc_to_bordered_launch(const void* x, void* y, long long N, int C, int H, int W, int bh, int bw, cudaStream_t s);
 int pool2d_i8_nhwc_launch(const void* x, int dt, long long N, int C, int ih, int iw, int kh, int kw, int sh, int sw, int pht,

@@ -115,9 +115,14 @@ class module:  # noqa: N801  (name of the reference class)
                     nhwc.add(name)
                 elif ins[0] in nhwc or ins[1] in nhwc:
                     raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: operands in different layouts")
-            elif t in ("tpu.Pool2D", "tpu.Cast"):
+            elif t in ("tpu.Pool2D", "tpu.Cast", "tpu.Lut", "tpu.MulShift"):
                 if ins[0] in nhwc:
                     nhwc.add(name)
+            elif t == "tpu.Mul":
+                if ins[0] in nhwc and ins[1] in nhwc:
+                    nhwc.add(name)
+                elif ins[0] in nhwc or ins[1] in nhwc:
+                    raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: operands in different layouts")
         return nhwc
 
     def _plan(self, op) -> Callable:
@@ -194,6 +199,23 @@ class module:  # noqa: N801  (name of the reference class)
                                                            pht, phb, pwl, pwr, int(is_avg), int(a.get("multiplier", 1)),
                                                            int(a.get("rshift", 0)), int(bool(a.get("do_relu", False))),
                                                            _DT[oinfo["dtype"]], _P(out), stream()))
+        if t == "tpu.Lut":
+            table = self.weights[op["name"] + "_table"]      # 256 entries in the output's storage type
+            n = out.numel()
+            return lambda: L.check(lib.b200q_lut_dev(_P(ins[0]), n, _P(table), _DT[oinfo["dtype"]], _P(out), stream()))
+        if t == "tpu.MulShift":
+            n = out.numel()
+            return lambda: L.check(lib.b200q_mulshift_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], n, int(a["multiplier"]),
+                                                             int(a["rshift"]), int(iinfo[0].get("zp", 0)),
+                                                             int(oinfo.get("zp", 0)), _DT[oinfo["dtype"]], _P(out), stream()))
+        if t == "tpu.Mul":
+            if tuple(iinfo[0]["shape"]) != tuple(iinfo[1]["shape"]):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.Mul with broadcasting is not implemented")
+            n = out.numel()
+            return lambda: L.check(lib.b200q_mul_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(ins[1]), _DT[iinfo[1]["dtype"]],
+                                                        n, int(a["multiplier"]), int(a["rshift"]),
+                                                        int(bool(a.get("do_relu", False))), _DT[oinfo["dtype"]], _P(out),
+                                                        stream()))
         if t == "tpu.Reshape":
             if op["inputs"][0] in self._nhwc:
                 return lambda: out.copy_(ins[0].permute(0, 3, 1, 2).reshape(out.shape))
