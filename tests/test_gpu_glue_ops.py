@@ -198,3 +198,43 @@ def test_executor_loads_mlir_text(tmp_path):
     for n in outs[0]:
         assert np.array_equal(outs[0][n], outs[1][n]), n
     assert outs[0]["fc"].any()
+
+
+@pytest.mark.parametrize("channels_last", [False, True])
+def test_executor_runs_lut_mulshift_mul(channels_last):
+    """A small graph of the element-wise ops through the executor, every tensor against the oracle functions."""
+    from tpu_mlir_b200.module import module
+    rng = np.random.default_rng(8)
+    oc = 32
+    w = rng.integers(-20, 20, (oc, 16, 1, 1), dtype=np.int8)
+    mult, rs = rng.integers(900, 1500, oc), rng.integers(9, 12, oc)
+    table = rng.integers(-128, 128, 256).astype(np.int8)
+    shp = [2, oc, 6, 5]
+    tens = {"input": dict(shape=[2, 16, 6, 5], dtype="f32"),
+            "q": dict(shape=[2, 16, 6, 5], dtype="i8", scale=0.05, zp=0),
+            "conv": dict(shape=shp, dtype="i8", scale=0.1, zp=0),
+            "lut": dict(shape=shp, dtype="i8", scale=0.1, zp=0),
+            "ms": dict(shape=shp, dtype="i8", scale=0.1, zp=0),
+            "mul": dict(shape=shp, dtype="u8", scale=0.1, zp=0)}
+    ops = [dict(type="tpu.Cast", name="q", inputs=["input"]),
+           dict(type="tpu.Conv2D", name="conv", inputs=["q"],
+                attrs=dict(kernel_shape=[1, 1], group=1, quant_mode="MultiplierShift", multiplier=mult.tolist(),
+                           rshift=rs.tolist(), do_relu=False)),
+           dict(type="tpu.Lut", name="lut", inputs=["conv"]),
+           dict(type="tpu.MulShift", name="ms", inputs=["conv"], attrs=dict(multiplier=90, rshift=6)),
+           dict(type="tpu.Mul", name="mul", inputs=["lut", "ms"], attrs=dict(multiplier=5, rshift=7, do_relu=True))]
+    graph = dict(inputs=["input"], outputs=["mul"], tensors=tens, ops=ops)
+    weights = {"conv_filter": w, "lut_table": table}
+    x = rng.standard_normal((2, 16, 6, 5)).astype(np.float32)
+    m = module(channels_last=channels_last)
+    m.load(graph, weights)
+    m.set_tensor("input", x)
+    m.invoke()
+    conv = m.get_tensor("conv")
+    assert conv.shape == tuple(shp) and len(np.unique(conv)) > 20
+    assert (("conv" in m._nhwc) and ("mul" in m._nhwc)) == channels_last
+    lut = oracle.lut(conv, table)
+    ms = oracle.mulshift_int8(conv, 90, 6)
+    assert np.array_equal(m.get_tensor("lut"), lut)
+    assert np.array_equal(m.get_tensor("ms"), ms)
+    assert np.array_equal(m.get_tensor("mul"), oracle.mul_int8(lut, ms, 5, 7, do_relu=True, out_dt=oracle.DT_U8))
