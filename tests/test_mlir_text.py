@@ -96,3 +96,27 @@ def test_divided_modules_are_rejected():
            '    %0 = "func.call"(%arg0) : (tensor<1xf32>) -> tensor<1xf32> loc(#loc)\n    return %0 : tensor<1xf32> loc(#loc)\n  }\n}\n'
     with pytest.raises(MT.MlirTextError):
         MT.parse_module(text)
+
+
+def test_elementwise_ops_round_trip(tmp_path):
+    """tpu.Lut (with its table as a weight operand), tpu.MulShift and tpu.Mul survive emit -> load."""
+    rng = np.random.default_rng(1)
+    shp = [1, 16, 4, 4]
+    tensors = {"input": dict(shape=shp, dtype="f32"),
+               "q": dict(shape=shp, dtype="i8", scale=0.25, zp=0),
+               "lut": dict(shape=shp, dtype="i8", scale=0.25, zp=0),
+               "ms": dict(shape=shp, dtype="u8", scale=0.5, zp=3),
+               "mul": dict(shape=shp, dtype="i8", scale=0.125, zp=0)}
+    ops = [dict(type="tpu.Cast", name="q", inputs=["input"]),
+           dict(type="tpu.Lut", name="lut", inputs=["q"]),
+           dict(type="tpu.MulShift", name="ms", inputs=["q"], attrs=dict(multiplier=90, rshift=6)),
+           dict(type="tpu.Mul", name="mul", inputs=["lut", "ms"], attrs=dict(multiplier=5, rshift=7, do_relu=True))]
+    graph = dict(inputs=["input"], outputs=["mul"], tensors=tensors, ops=ops)
+    weights = {"lut_table": rng.integers(-128, 128, 256).astype(np.int8)}
+    (tmp_path / "m.mlir").write_text(MT.emit_module(graph, weights, weight_file="w.npz"))
+    np.savez(tmp_path / "w.npz", **weights)
+    g2, w2 = MT.load_mlir(str(tmp_path / "m.mlir"))
+    assert [(o["type"], o["name"], o["inputs"], o.get("attrs", {})) for o in g2["ops"]] == \
+           [(o["type"], o["name"], o["inputs"], o.get("attrs", {})) for o in ops]
+    assert np.array_equal(w2["lut_table"].reshape(-1), weights["lut_table"])
+    assert g2["tensors"]["ms"]["zp"] == 3 and g2["tensors"]["ms"]["dtype"] == "u8"

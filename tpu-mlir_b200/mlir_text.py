@@ -320,7 +320,8 @@ def _parse_op(s: str, locs: Dict[str, str]) -> Op:
 
 
 # ------------------------------------------------------------------------------------------------ executor graph
-_SUPPORTED = {"tpu.Conv2D", "tpu.MatMul", "tpu.Add", "tpu.Pool2D", "tpu.Cast", "tpu.Reshape"}
+_SUPPORTED = {"tpu.Conv2D", "tpu.MatMul", "tpu.Add", "tpu.Pool2D", "tpu.Cast", "tpu.Reshape", "tpu.Lut", "tpu.MulShift",
+              "tpu.Mul"}
 
 
 def _tensor_entry(t: TensorType) -> dict:
@@ -363,6 +364,8 @@ def to_graph(mod: Module, weight_arrays: Dict[str, np.ndarray]):
                 names = ["_filter", "_bias"]
             elif op.type == "tpu.MatMul":
                 names = ["_filter", "_bias"]
+            elif op.type == "tpu.Lut":
+                names = ["_table"]      # operands: input, table (TpuOps.td LutOp)
             else:
                 names = []
             # operand order: input, filter/right, bias (None operands keep their slot)
@@ -460,8 +463,8 @@ def emit_module(graph: dict, weights: Dict[str, np.ndarray], name: str = "model"
     none = None
     for op in graph["ops"]:
         operands, types = [ssa[i] for i in op["inputs"]], [ttype(i) for i in op["inputs"]]
-        if op["type"] in ("tpu.Conv2D", "tpu.MatMul"):
-            for suffix in ("_filter", "_bias"):
+        if op["type"] in ("tpu.Conv2D", "tpu.MatMul", "tpu.Lut"):
+            for suffix in (("_table",) if op["type"] == "tpu.Lut" else ("_filter", "_bias")):
                 key = op["name"] + suffix
                 if key in weights:
                     w = weights[key]
