@@ -6,15 +6,18 @@ CPU-baseline leg of the benchmark may import this package; the shipped library n
 
 Pinning status
 --------------
-* rounding helpers: pinned by the known answers in the reference header
-  ``include/tpu_mlir/Support/MathUtils.h:29-40``.
+* rounding / requantisation helpers (to_int, RightShiftRound, MultiplyByQuantizedMultiplier,
+  applyMultiplierAndRShift): pinned against the reference's own functions, compiled out of
+  ``lib/Support/MathUtils.cpp:179-213,:474-562`` into ``oracle/_ref/mathutils_ref.so`` by ``oracle/Makefile``, and
+  by the known answers in the reference header ``include/tpu_mlir/Support/MathUtils.h:29-40``.
 * histogram / combine_histogram / find_threshold / KLD: pinned by golden vectors generated from the
   reference's own ``python/calibration/cali_math.py`` and ``bindings/kld/calibration_math.cpp``
   (``tests/golden/make_golden.py``), and, when ``oracle/_ref/calibration_math.so`` exists, by
   calling that compiled reference directly.
 * MatMul / Conv2D / A16MatMul / RequantInt(Axis) / Add / Pool2D / Cast op-level arithmetic:
   restated from the cited lines; the reference interpreter cannot be built without MLIR and
-  oneDNN, so these are *parity unpinned* beyond the rounding known answers.
+  oneDNN, so the loops around the pinned requantisation arithmetic (operand order, bias, ReLU placement,
+  saturation) are *parity unpinned*.
 """
 from __future__ import annotations
 
@@ -483,3 +486,27 @@ def ref_kl_diversity_hist(hist, width, dst_bins=128):
     h = _c(hist, np.int32)
     return np.float32(_ref_kld.kl_diversity_hist(h.ctypes.data_as(C.POINTER(C.c_int)), C.c_float(float(width)),
                                                  C.c_longlong(h.size), C.c_longlong(dst_bins)))
+
+
+# ------------------------------------------------------------------------------------------------------------
+# The reference's own rounding / requantisation functions (lib/Support/MathUtils.cpp:179-213,:474-562), compiled by
+# oracle/Makefile (target ref_mathutils) out of the reference checkout into oracle/_ref/mathutils_ref.so.
+_ref_mu = None
+
+
+def ref_mathutils_available() -> bool:
+    return os.path.exists(os.path.join(_HERE, "_ref", "mathutils_ref.so"))
+
+
+def ref_mathutils():
+    global _ref_mu
+    if _ref_mu is None:
+        L = C.CDLL(os.path.join(_HERE, "_ref", "mathutils_ref.so"))
+        i32, i64 = C.c_int, C.c_longlong
+        L.ref_to_int_f32.restype, L.ref_to_int_f32.argtypes = i64, [C.c_float, i32]
+        L.ref_rshift_round.restype, L.ref_rshift_round.argtypes = i64, [i64, i32, i32]
+        L.ref_mbqm.restype, L.ref_mbqm.argtypes = i32, [i32, i32, i32, i32]
+        L.ref_apply_multiplier_rshift.restype = i64
+        L.ref_apply_multiplier_rshift.argtypes = [i64, i64, i64, i32, i32, i32]
+        _ref_mu = L
+    return _ref_mu

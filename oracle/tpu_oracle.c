@@ -7,12 +7,16 @@
  * threshold search.  It is the checker the CUDA kernels are compared against; nothing in the
  * shipped library may call it.
  *
- * Pinning: the rounding helpers are checked against the known answers written in the
- * reference header include/tpu_mlir/Support/MathUtils.h:29-40; the histogram and KLD parts
+ * Pinning: the rounding / requantisation helpers (to_int, RightShiftRound, MultiplyByQuantizedMultiplier,
+ * applyMultiplierAndRShift) are checked against the reference's OWN functions, cut out of
+ * lib/Support/MathUtils.cpp:179-213,:474-562 by the build recipe and compiled into oracle/_ref/
+ * (tests/test_oracle_golden.py), and against the known answers written in the reference header
+ * include/tpu_mlir/Support/MathUtils.h:29-40; the histogram and KLD parts
  * are checked against outputs of the reference's own python/calibration/cali_math.py and
  * bindings/kld/calibration_math.cpp (golden vectors under tests/golden/).  The MatMul/Conv2D
  * op-level code cannot be pinned against a run of the reference (it needs MLIR + oneDNN to
- * build), so for those ops parity is "unpinned" beyond the rounding known answers.
+ * build), so for those ops parity is "unpinned" above the pinned requantisation arithmetic: the
+ * loops around it (operand order, bias, ReLU placement, saturation) are restated from the cited lines.
  *
  * Every function cites the reference file:line it follows (paths inside the reference tree).
  */

@@ -122,3 +122,57 @@ def test_kld_matches_compiled_reference_random():
             x = np.maximum(x, 0)
         h, w = oracle.histogram(x, np.abs(x).max(), bins)
         assert oracle.kl_diversity_hist(h, w).tobytes() == oracle.ref_kl_diversity_hist(h, w).tobytes()
+
+
+@pytest.mark.skipif(not oracle.ref_mathutils_available(), reason="compiled reference MathUtils functions not present")
+def test_requant_arithmetic_matches_compiled_reference():
+    """to_int, RightShiftRound, MultiplyByQuantizedMultiplier and applyMultiplierAndRShift of the oracle against the
+    reference's own functions (MathUtils.cpp:179-213,:474-562) on edge values and random draws."""
+    R = oracle.ref_mathutils()
+    rng = np.random.default_rng(11)
+    rmodes = [oracle.RM_HALF_AWAY, oracle.RM_HALF_UP, oracle.RM_HALF_DOWN, oracle.RM_HALF_EVEN, oracle.RM_TOWARDS_ZERO,
+              oracle.RM_UP, oracle.RM_DOWN]
+    # to_int on halves, near-halves and random floats
+    vals = [0.0, 0.5, -0.5, 1.5, -1.5, 2.5, -2.5, 0.49999997, -0.49999997, 1e6 + 0.5, -1e6 - 0.5, 123456.75]
+    vals += list((rng.standard_normal(300) * 1000).astype(np.float32))
+    for rm in rmodes:
+        for v in vals:
+            assert oracle.to_int(v, rm) == R.ref_to_int_f32(float(np.float32(v)), rm), (v, rm)
+    # RightShiftRound: every mode the function knows, shifts 0..63 and negative (left) shifts, ties included
+    srcs = [0, 1, -1, 3, -3, 5, -5, 6, -6, 2**31 - 1, -2**31, 2**40 + 2**20, -(2**40) - 2**20, 2**62, -(2**62)]
+    srcs += [int(v) for v in rng.integers(-2**50, 2**50, 200)]
+    for rm in rmodes:
+        for s in list(range(0, 64)) + [-1, -3]:
+            for x in srcs:
+                if s < 0 and abs(x) >= 2**58:
+                    continue   # the left shift would overflow int64 (undefined in the reference too)
+                assert oracle.rshift_round(x, s, rm) == R.ref_rshift_round(x, s, rm), (x, s, rm)
+    # MultiplyByQuantizedMultiplier: TFLite multipliers, right and (small) left shifts
+    for _ in range(4000):
+        x = int(rng.integers(-2**24, 2**24))
+        m = int(rng.integers(2**30, 2**31))
+        sh = int(rng.integers(-31, 3))
+        if sh > 0 and abs(x) >= 2**28:
+            continue
+        for rm in (oracle.RM_HALF_AWAY, oracle.RM_HALF_UP):
+            assert oracle.mbqm(x, m, sh, rm) == R.ref_mbqm(x, m, sh, rm), (x, m, sh, rm)
+    # applyMultiplierAndRShift: every requant mode, both chip families
+    for _ in range(4000):
+        v = int(rng.integers(-2**24, 2**24))
+        for qm in (oracle.QM_MULTIPLIER_SHIFT, oracle.QM_ONLY_SHIFT, oracle.QM_QDM, oracle.QM_TFLITE, oracle.QM_TFLITE_LSHIFT):
+            for cv in (0, 1):
+                if qm == oracle.QM_MULTIPLIER_SHIFT:
+                    m, s = (int(rng.integers(1, 2**15)), int(rng.integers(0, 31)))
+                    if cv:
+                        m, s = int(rng.integers(1, 2**12)), int(rng.integers(0, 20))   # float path: keep v*m exact in fp32
+                        v2 = int(rng.integers(-2**11, 2**11))
+                    else:
+                        v2 = v
+                elif qm == oracle.QM_ONLY_SHIFT:
+                    m, s, v2 = 1, int(rng.integers(0, 31)), v
+                else:
+                    m, v2 = int(rng.integers(2**30, 2**31)), v
+                    s = int(rng.integers(0, 31)) if cv else -int(rng.integers(0, 31))   # CV18xx negates the attribute
+                rm = oracle.RM_HALF_AWAY if (cv or qm != oracle.QM_MULTIPLIER_SHIFT) else oracle.RM_HALF_UP
+                got = oracle.apply_multiplier_rshift(v2, m, s, qm, rm, bool(cv))
+                assert got == R.ref_apply_multiplier_rshift(v2, m, s, qm, rm, cv), (v2, m, s, qm, rm, cv)
