@@ -10,6 +10,8 @@ Pinning status
   applyMultiplierAndRShift): pinned against the reference's own functions, compiled out of
   ``lib/Support/MathUtils.cpp:179-213,:474-562`` into ``oracle/_ref/mathutils_ref.so`` by ``oracle/Makefile``, and
   by the known answers in the reference header ``include/tpu_mlir/Support/MathUtils.h:29-40``.
+* bf16 rounding: pinned against the reference's own ``lib/Support/Float16.cpp``, compiled whole from the checkout
+  into ``oracle/_ref/float16_ref.so`` (``oracle/ref_shim`` stands in for the one header that needs MLIR).
 * histogram / combine_histogram / find_threshold / KLD: pinned by golden vectors generated from the
   reference's own ``python/calibration/cali_math.py`` and ``bindings/kld/calibration_math.cpp``
   (``tests/golden/make_golden.py``), and, when ``oracle/_ref/calibration_math.so`` exists, by
@@ -510,3 +512,23 @@ def ref_mathutils():
         L.ref_apply_multiplier_rshift.argtypes = [i64, i64, i64, i32, i32, i32]
         _ref_mu = L
     return _ref_mu
+
+
+_ref_f16 = None
+
+
+def ref_float16_available() -> bool:
+    return os.path.exists(os.path.join(_HERE, "_ref", "float16_ref.so"))
+
+
+def ref_float16():
+    """The reference's own lib/Support/Float16.cpp compiled into oracle/_ref/float16_ref.so (BM168x conversions)."""
+    global _ref_f16
+    if _ref_f16 is None:
+        L = C.CDLL(os.path.join(_HERE, "_ref", "float16_ref.so"))
+        L.ref_f32_to_bf16.restype, L.ref_f32_to_bf16.argtypes = C.c_uint, [C.c_float]
+        L.ref_bf16_to_f32.restype, L.ref_bf16_to_f32.argtypes = C.c_float, [C.c_uint]
+        L.ref_f32_to_f16.restype, L.ref_f32_to_f16.argtypes = C.c_uint, [C.c_float]
+        L.ref_f16_to_f32.restype, L.ref_f16_to_f32.argtypes = C.c_float, [C.c_uint]
+        _ref_f16 = L
+    return _ref_f16

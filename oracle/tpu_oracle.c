@@ -10,7 +10,8 @@
  * Pinning: the rounding / requantisation helpers (to_int, RightShiftRound, MultiplyByQuantizedMultiplier,
  * applyMultiplierAndRShift) are checked against the reference's OWN functions, cut out of
  * lib/Support/MathUtils.cpp:179-213,:474-562 by the build recipe and compiled into oracle/_ref/
- * (tests/test_oracle_golden.py), and against the known answers written in the reference header
+ * (tests/test_oracle_golden.py), the bf16 rounding against the reference's lib/Support/Float16.cpp compiled
+ * whole the same way, and both against the known answers written in the reference header
  * include/tpu_mlir/Support/MathUtils.h:29-40; the histogram and KLD parts
  * are checked against outputs of the reference's own python/calibration/cali_math.py and
  * bindings/kld/calibration_math.cpp (golden vectors under tests/golden/).  The MatMul/Conv2D

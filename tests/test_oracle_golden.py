@@ -176,3 +176,22 @@ def test_requant_arithmetic_matches_compiled_reference():
                 rm = oracle.RM_HALF_AWAY if (cv or qm != oracle.QM_MULTIPLIER_SHIFT) else oracle.RM_HALF_UP
                 got = oracle.apply_multiplier_rshift(v2, m, s, qm, rm, bool(cv))
                 assert got == R.ref_apply_multiplier_rshift(v2, m, s, qm, rm, cv), (v2, m, s, qm, rm, cv)
+
+
+@pytest.mark.skipif(not oracle.ref_float16_available(), reason="compiled reference Float16.cpp not present")
+def test_bf16_conversion_matches_compiled_reference():
+    """The oracle's BF16 rounding against the reference's own f32_to_bf16 (lib/Support/Float16.cpp, BM168x branch) on
+    random bit patterns (normals, denormals, infinities, NaNs) and the edges of every case."""
+    R = oracle.ref_float16()
+    rng = np.random.default_rng(0)
+    edge = [0, 0x80000000, 0x7f800000, 0xff800000, 0x7fc00000, 0x7f800001, 0x00000001, 0x007fffff, 0x007f8000, 0x007f7fff,
+            0x807f8000, 0x807f7fff, 0x3f808000, 0x3f818000, 0x3f807fff, 0x3f808001, 0x7f7fffff, 0x7f7f8000, 0x7f7f7fff,
+            0x00800000, 0x00808000]
+    bits = np.concatenate([rng.integers(0, 2**32, 60000, dtype=np.uint64).astype(np.uint32), np.array(edge, dtype=np.uint32)])
+    f = oracle.lib().orc_f32_to_bf16_bits
+    for v, b in zip(bits.view(np.float32), bits):
+        assert int(f(float(v))) == int(R.ref_f32_to_bf16(float(v))), hex(int(b))
+    for b in list(range(0, 1 << 16, 7)) + [0x7f80, 0xff80, 0x7fc0, 0x0001, 0x8001]:
+        got = oracle.bf16_bits_to_f32(np.array([b], dtype=np.uint16))[0]
+        want = np.float32(R.ref_bf16_to_f32(b))
+        assert got.tobytes() == want.tobytes() or (np.isnan(got) and np.isnan(want)), hex(b)
