@@ -255,18 +255,25 @@ def run_kernel_workload(args):
                                         frac=gbs / peaks["hbm_gbs"], traffic=None,
                                         peak_basis=f"{peaks['source']} copy bandwidth")))
     elif args.workload == "a16":
-        for M in (1, 4, 8):
+        for M in (1, 2, 4, 8):
             c = synth.a16_w4(seed=2, M=M)
-            NS = 8   # 8 copies of the weight set (198 MB > L2) used round-robin
+            NS = 8   # 8 copies of the weight set (198 MB > L2) used round-robin, one handle each (decode keeps them resident)
             x = torch.from_numpy(c["x"]).cuda()
             sets = [tuple(torch.from_numpy(c[k]).cuda() for k in ("wq", "scale", "zp")) for _ in range(NS)]
             wq, sc, zp = sets[0]
             y = torch.empty((M, 11008), dtype=torch.uint16, device="cuda")
+            hs = []
+            for w_, s_, z_ in sets:
+                h = C.c_void_p()
+                L.check(lib.b200q_a16_dev_create(P(w_), P(s_), P(z_), None, 11008, 4096, 64, C.byref(h)))
+                hs.append(h)
 
             def go(i, stream):
-                w_, s_, z_ = sets[i % NS]
-                L.check(lib.b200q_a16_w4_dev(P(x), P(w_), P(s_), P(z_), None, P(y), M, 11008, 4096, 64, None, stream))
+                L.check(lib.b200q_a16_dev_run(hs[i % NS], P(x), P(y), M, stream))
             mean_ms = _time_steps_graph(go, min(args.steps, 200), args.warmup)
+            for h in hs:
+                L.check(lib.b200q_a16_dev_status(h, None))
+                lib.b200q_a16_dev_destroy(C.byref(h))
             nbytes = wq.numel() + sc.numel() * 2 + zp.numel() + x.numel() * 2 + y.numel() * 2
             gbs = nbytes / (mean_ms * 1e-3) / 1e9
             lines.append(dict(metric="w4bf16 GEMV GB/s", value=gbs, unit="GB/s", ms_per_step=mean_ms,

@@ -289,6 +289,13 @@ int b200q_a16_w4_dev(const void *x_bf16, const void *wq, const void *scale_bf16,
                      const float *bias_f32, void *y_bf16, int64_t M, int64_t N, int64_t K, int32_t group,
                      int32_t *status, void *stream);
 
+/* Which kernel serves b200q_a16_*, process-wide: 0 = chosen per call (default: one or two tokens take the CUDA-core
+ * GEMV, everything else the fused-dequantisation tensor-core kernel); 1 = the decode kernels only (8 tokens per
+ * launch); 2 = the tensor-core kernel for every M; 3 = handle API with M > 8: dequantise once into a bf16 copy kept in
+ * the handle and run a bf16 GEMM (rounds the weight to bf16, which the reference does not).  A measuring control;
+ * no counterpart in the reference. */
+void b200q_a16_set_route(int32_t route);
+
 /* Device face with a handle: the tensors stay the caller's (not copied).  M <= 8 runs the decode kernel on the
  * packed weights; larger M dequantises the weight once into bf16 (kept in the handle, N*K*2 bytes) and runs
  * a bf16 tensor-core GEMM with fp32 accumulation.  b200q_a16_dev_status synchronises the stream and reports a
@@ -334,6 +341,12 @@ int b200q_calib_minmax_noalloc(const float *x, int64_t n_per_sample, int64_t sam
  * (threshold, bins) schedule derived from the running abs-max.  int32 counts, like the reference. */
 int b200q_calib_histogram(void *ctx, const float *x, int64_t n_per_sample, int64_t samples, const float *th_host,
                           const int32_t *nbins_host, int32_t *hist, int64_t hist_len, void *stream);
+
+/* Counter layout of the histogram kernel, process-wide: -1 = chosen per launch from the bin count and the work
+ * per block (default); 0..4 = 2^mode 32-bit copies of every bin per block; 5 = one 16-bit counter per (bin, lane).
+ * Every layout produces the same counts; this only exists to measure them against each other.  (No counterpart in
+ * the reference, whose histogram is numpy's.) */
+void b200q_calib_set_histogram_layout(int32_t mode);
 
 /* ActivationCalibrator.find_threshold (kld_calibrator.py:321-347) for `tensors` histograms at once: zero-pad
  * to a multiple of dst_bins, fold pairwise while longer than 131072 bins (doubling the width), then the KLD

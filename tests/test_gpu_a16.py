@@ -46,7 +46,10 @@ def test_llama_mlp_shape(M):
                                   dict(M=4, K=192, N=100, g=64),
                                   # one or two tokens take the CUDA-core kernel (K <= 16384): ragged lane/row splits
                                   dict(M=2, K=11008, N=50, g=128), dict(M=1, K=8192, N=33, g=64),
-                                  dict(M=2, K=12288, N=20, g=256)])
+                                  dict(M=2, K=12288, N=20, g=256),
+                                  # groups of 32, several slices per lane, rows fewer than row lanes
+                                  dict(M=1, K=96, N=7, g=32), dict(M=2, K=160, N=9, g=32), dict(M=1, K=32768, N=5, g=128),
+                                  dict(M=2, K=20480, N=3, g=64), dict(M=1, K=4096, N=1200, g=64)])
 def test_small_and_ragged_shapes_with_bias(case):
     c = synth.a16_w4(seed=7, M=case["M"], K=case["K"], N=case["N"], group=case["g"])
     bias = np.random.default_rng(1).standard_normal(case["N"]).astype(np.float32)
@@ -72,9 +75,10 @@ def test_operator_face():
 
 
 def test_unsupported_is_reported():
-    op = A16MatMulOp(M=1, K=64, N=16, q_group_size=32)
+    # a group size that is not a multiple of 32 has no kernel
+    op = A16MatMulOp(M=1, K=96, N=16, q_group_size=48)
     with pytest.raises(L.B200QError) as ei:
-        op.inference(InferenceParameter(inputs=[np.zeros((1, 64), np.float32), np.zeros((16, 32), np.float32),
+        op.inference(InferenceParameter(inputs=[np.zeros((1, 96), np.float32), np.zeros((16, 48), np.float32),
                                                 np.zeros(32, np.float32), np.zeros(32, np.float32), None],
                                         outputs=[np.zeros((1, 16), np.float32)]))
     assert ei.value.code == L.ERR_UNSUPPORTED

@@ -108,6 +108,7 @@ SIGNATURES = {
     "b200q_a16matmul_deinit": (None, [_VPP]),
     "b200q_a16_w4_dev": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
                                    C.c_void_p]),
+    "b200q_a16_set_route": (None, [C.c_int32]),
     "b200q_a16_dev_create": (C.c_int, [C.c_void_p] * 4 + [C.c_int64, C.c_int64, C.c_int32, _VPP]),
     "b200q_a16_dev_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "b200q_a16_dev_status": (C.c_int, [C.c_void_p, C.c_void_p]),
@@ -118,6 +119,7 @@ SIGNATURES = {
     "b200q_calib_minmax_noalloc": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200q_calib_histogram": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.POINTER(C.c_float),
                                         C.POINTER(C.c_int32), C.c_void_p, C.c_int64, C.c_void_p]),
+    "b200q_calib_set_histogram_layout": (None, [C.c_int32]),
     "b200q_calib_find_thresholds": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_int64),
                                               C.POINTER(C.c_float), C.c_int64, C.POINTER(C.c_float),
                                               C.POINTER(C.c_float), C.c_void_p]),

@@ -321,206 +321,292 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
 
 
 // ---------------------------------------------------------------------------------------------------------------
-// M <= 2: CUDA-core form.  One or two tokens waste 7/8 of every MMA above, and mma.sync is the slow legacy tensor path
-// on sm_100, so for these shapes the dot products run as fp32 FMAs.  A lane owns one fixed 32-k slice of K for the
-// whole kernel and keeps its activations in registers (packed bf16, in nibble-pair order).  A lane owns SL fixed 32-k
-// slices; round32(K / 32 / SL) lanes cover one weight row and 512 / that many rows are in flight at a time.  Per row a lane reads 16 bytes of weights, turns 32 nibbles into
-// 128 + q (bf16 bit trick) and accumulates (128 + q) * x with mixed-precision FMAs (bf16 x bf16 + fp32); the zero point comes off as
-// (128 + zp) * sum(x over the slice), then the group scale multiplies the fp32 partial sum.
-template <int M_T, int SL>
-__global__ void __launch_bounds__(THREADS, 1)
-a16_w4_gemv_fma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
-                       const __nv_bfloat16* __restrict__ scale, const uint8_t* __restrict__ zp,
-                       const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int N, int K, int group,
-                       int* __restrict__ status) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  const GemvPlan P = gemv_plan(M_T, K, group, false);
+// M <= 2: CUDA-core form, weights straight from global memory.  One or two tokens waste 7/8 of every MMA above, and
+// mma.sync is the slow legacy tensor path on sm_100, so for these shapes the dot products run as fp32 FMAs.
+//
+// No shared-memory ring, no producer warp: a lane owns SL fixed 32-k slices of K for the whole kernel and keeps
+// their activations in registers (packed bf16, in nibble-pair order); `wpr` warps side by side cover one weight
+// row, 16 / wpr row lanes per block walk disjoint contiguous row ranges.  Per row a lane issues one 16-byte
+// streaming load per slice (plus the slice's scale and zero point) and keeps PF rows of them in flight, so a block
+// of 16 warps has 16 * PF * 512 bytes of weights on their way at any time; nothing in the loop waits on another
+// warp.  32 nibbles become 128 + q with the bf16 bit trick and accumulate (128 + q) * x with mixed-precision FMAs
+// (bf16 x bf16 + fp32); the zero point comes off as (128 + zp) * sum(x over the slice), then the group scale
+// multiplies the fp32 partial sum.  The PF rows of an iteration are reduced together (interleaved warp shuffles);
+// with more than one warp per row the partial sums meet in a double-buffered shared array behind one named barrier
+// per iteration.
+//
+// Programmatic dependent launch: every block releases its dependents at once, and when the caller vouches that the
+// weights are constant (`early_weights`) the first PF rows are requested BEFORE griddepcontrol.wait, i.e. while the
+// previous kernel of the stream is still draining; activations are read and results written only after the wait.
+template <int M_T, int SL, int PF, int MINB>
+__global__ void __launch_bounds__(512, MINB)
+a16_w4_gemv_direct_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
+                          const __nv_bfloat16* __restrict__ scale, const uint8_t* __restrict__ zp,
+                          const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int N, int K, int group,
+                          int wpr, int early_weights) {
+  __shared__ float red[2][16][PF][M_T];   // [buffer][warp][row of the iteration][token]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t bar_base = ptx::smem_u32(smem + P.bar_off);
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P.bar_off + 16 * MAX_STAGES);
-  const int num_slabs = (N + ROWS - 1) / ROWS;
+  const int T = K >> 5;                    // 32-k slices per row
+  const int gpr = K / group;
+  const int rows_par = 16 / wpr;
+  const int rs = warp / wpr, kq = warp - rs * wpr;
+  const long long units = (long long)gridDim.x * rows_par;
+  const long long unit = (long long)blockIdx.x * rows_par + rs;
+  const int r0 = (int)(unit * N / units), r1 = (int)((unit + 1) * N / units);
+  const uint16_t* sc16 = reinterpret_cast<const uint16_t*>(scale);
+  ptx::griddep_launch_dependents();
 
-  if (tid == 0) {
-    for (int s = 0; s < P.stages; ++s) {
-      ptx::mbar_init(full_bar(s), 2);
-      ptx::mbar_init(empty_bar(s), CWARPS);
-    }
-    *abort_flag = 0;
-    ptx::fence_barrier_init();
-    ptx::fence_proxy_async_smem();
-  }
-  __syncthreads();
-
-  if (warp == CWARPS) {
-    gemv_producer(smem, P, bar_base, abort_flag, wq, scale, zp, N, K, num_slabs, lane);
-  } else {
-    const int T = K / 32;                          // 32-k slices per row
-    const int wpr = (T + 32 * SL - 1) / (32 * SL);  // warps per row (a lane owns SL slices, 32 * wpr apart)
-    const int rows_par = CWARPS / wpr;             // rows in flight
-    const int row_sub = warp / wpr, warp_in_row = warp - row_sub * wpr;
-    const int lane_slot = warp_in_row * 32 + lane;
-    const int slot_stride = 32 * wpr;
-    const bool warp_active = row_sub < rows_par;
-    // this lane's activations as packed bf16 pairs (x_j, x_j+4) per 8 values: the pairing the nibble extraction yields
-    uint32_t xw[M_T][SL][16];
-    float xsum[M_T][SL];
+  int slice[SL];
+  bool live[SL];
+  const uint4* wnext[SL];     // the next row to request: rows are requested strictly in order
+  const uint16_t* snext[SL];
+  const uint8_t* znext[SL];
+  const int wstride = K >> 5;  // row pitch in 16-byte units
 #pragma unroll
-    for (int m = 0; m < M_T; ++m) {
+  for (int sl = 0; sl < SL; ++sl) {
+    slice[sl] = (sl * wpr + kq) * 32 + lane;
+    live[sl] = slice[sl] < T;
+    const int sidx = live[sl] ? slice[sl] : 0;
+    const size_t gi = (size_t)r0 * gpr + (sidx * 32) / group;
+    wnext[sl] = reinterpret_cast<const uint4*>(wq) + (size_t)r0 * wstride + sidx;
+    snext[sl] = sc16 + gi;
+    znext[sl] = zp + gi;
+  }
+  uint4 wb[PF][SL];
+  uint32_t sb[PF][SL], zb[PF][SL];
+#pragma unroll
+  for (int p = 0; p < PF; ++p)
+#pragma unroll
+    for (int sl = 0; sl < SL; ++sl) {
+      wb[p][sl] = make_uint4(0u, 0u, 0u, 0u);
+      sb[p][sl] = 0u;
+      zb[p][sl] = 0u;
+    }
+  int to_request = r1 - r0;
+  auto request = [&](int p) {
+    if (to_request > 0) {
 #pragma unroll
       for (int sl = 0; sl < SL; ++sl) {
-        const int slice = sl * slot_stride + lane_slot;
-        xsum[m][sl] = 0.f;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) xw[m][sl][j] = 0u;
-        if (warp_active && slice < T) {
-          const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)slice * 32);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {  // 8 bf16 per 16 bytes
-            const uint4 v = xp[q];
-            xw[m][sl][4 * q + 0] = __byte_perm(v.x, v.z, 0x5410);  // (x0, x4)
-            xw[m][sl][4 * q + 1] = __byte_perm(v.x, v.z, 0x7632);  // (x1, x5)
-            xw[m][sl][4 * q + 2] = __byte_perm(v.y, v.w, 0x5410);  // (x2, x6)
-            xw[m][sl][4 * q + 3] = __byte_perm(v.y, v.w, 0x7632);  // (x3, x7)
-            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) xsum[m][sl] += __uint_as_float(wv[j] << 16) + __uint_as_float(wv[j] & 0xffff0000u);
-          }
+        if (live[sl]) {
+          wb[p][sl] = __ldcs(wnext[sl]);
+          sb[p][sl] = __ldg(snext[sl]);
+          zb[p][sl] = __ldg(znext[sl]);
         }
+        wnext[sl] += wstride;
+        snext[sl] += gpr;
+        znext[sl] += gpr;
       }
     }
-    const int iters = (ROWS + rows_par - 1) / rows_par;
-    float* red = reinterpret_cast<float*>(smem + P.red_off);
-    int stage = 0;
-    uint32_t phase = 0;
-    int it_slab = 0;
-    for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x, ++it_slab) {
-      if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, 2, WAIT_NS)) break;
-      const uint8_t* st = smem + (size_t)stage * P.stage_bytes;
-      const __nv_bfloat16* st_scale = reinterpret_cast<const __nv_bfloat16*>(st + P.scale_off);
-      const uint8_t* st_zp = st + P.zp_off;
-      const int n0 = slab * ROWS;
-      const int rows = min(ROWS, N - n0);
-      float* rbuf = red + (size_t)(it_slab & 1) * (M_T * ROWS * CWARPS);
-      for (int it = 0; it < iters; ++it) {
-        const int r = it * rows_par + row_sub;
-        const bool row_ok = warp_active && r < rows;
-        float part[M_T];
+    --to_request;
+  };
+  if (early_weights) {
 #pragma unroll
-        for (int m = 0; m < M_T; ++m) part[m] = 0.f;
+    for (int p = 0; p < PF; ++p) request(p);
+  }
+  ptx::griddep_wait();
+  if (!early_weights) {
 #pragma unroll
-        for (int sl = 0; sl < SL; ++sl) {
-          const int slice = sl * slot_stride + lane_slot;
-          if (row_ok && slice < T) {
-            const uint4 wv4 = *reinterpret_cast<const uint4*>(st + (size_t)r * P.w_pitch + (size_t)slice * 16);
-            const int gi = r * P.gpr + (slice * 32) / group;
-            const float sc = __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(st_scale)[gi] << 16);
-            const float zoff = __uint_as_float(0x43000000u | ((uint32_t)st_zp[gi] << 16));  // 128 + zp, zp <= 127
-            const uint32_t ww[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
-            float acc[M_T][4];
+    for (int p = 0; p < PF; ++p) request(p);
+  }
+
+  // this lane's activations as packed bf16 pairs (x_j, x_j+4) per 8 values: the pairing the nibble extraction yields
+  uint32_t xw[M_T][SL][16];
+  float xsum[M_T][SL];
 #pragma unroll
-            for (int m = 0; m < M_T; ++m)
+  for (int m = 0; m < M_T; ++m) {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) acc[m][q] = 0.f;
+    for (int sl = 0; sl < SL; ++sl) {
+      xsum[m][sl] = 0.f;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint32_t w = ww[q];
+      for (int j = 0; j < 16; ++j) xw[m][sl][j] = 0u;
+      if (live[sl]) {
+        const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)slice[sl] * 32);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint32_t pq = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // bf16x2 {128 + q_j, 128 + q_(j+4)}
+        for (int q = 0; q < 4; ++q) {  // 8 bf16 per 16 bytes
+          const uint4 v = __ldg(xp + q);
+          xw[m][sl][4 * q + 0] = __byte_perm(v.x, v.z, 0x5410);  // (x0, x4)
+          xw[m][sl][4 * q + 1] = __byte_perm(v.x, v.z, 0x7632);  // (x1, x5)
+          xw[m][sl][4 * q + 2] = __byte_perm(v.y, v.w, 0x5410);  // (x2, x6)
+          xw[m][sl][4 * q + 3] = __byte_perm(v.y, v.w, 0x7632);  // (x3, x7)
+          const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                for (int m = 0; m < M_T; ++m) fma2_f32_bf16(acc[m][q], pq, xw[m][sl][4 * q + j]);
-              }
-            }
-#pragma unroll
-            for (int m = 0; m < M_T; ++m) {
-              const float raw = (acc[m][0] + acc[m][1]) + (acc[m][2] + acc[m][3]);
-              part[m] = fmaf(fmaf(-zoff, xsum[m][sl], raw), sc, part[m]);
-            }
-          }
-        }
-#pragma unroll
-        for (int m = 0; m < M_T; ++m) {
-          float v = part[m];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-          if (lane == 0 && warp_active && r < ROWS) {
-            if (wpr == 1) {  // the warp holds the whole row: no cross-warp sum
-              if (r < rows) y[(size_t)m * N + n0 + r] = __float2bfloat16_rn(bias ? v + bias[n0 + r] : v);
-            } else {
-              rbuf[(m * ROWS + r) * CWARPS + warp_in_row] = v;
-            }
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(empty_bar(stage));  // this warp no longer reads the stage
-      if (++stage == P.stages) {
-        stage = 0;
-        phase ^= 1u;
-      }
-      if (wpr > 1) {
-        asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory");
-        if (tid < ROWS * M_T) {
-          const int row = tid / M_T, m = tid - row * M_T;
-          const int n = n0 + row;
-          if (n < N) {
-            float v = 0.f;
-            for (int w = 0; w < wpr; ++w) v += rbuf[(m * ROWS + row) * CWARPS + w];
-            if (bias) v += bias[n];
-            y[(size_t)m * N + n] = __float2bfloat16_rn(v);
-          }
+          for (int j = 0; j < 4; ++j) xsum[m][sl] += __uint_as_float(wv[j] << 16) + __uint_as_float(wv[j] & 0xffff0000u);
         }
       }
     }
   }
-  __syncthreads();
-  if (tid == 0 && *abort_flag != 0 && status != nullptr) atomicCAS(status, 0, *abort_flag);
+
+  int it = 0;
+  for (int r = r0; r < r1; r += PF, ++it) {
+    float part[PF][M_T];
+#pragma unroll
+    for (int p = 0; p < PF; ++p) {
+#pragma unroll
+      for (int m = 0; m < M_T; ++m) part[p][m] = 0.f;
+      if (r + p < r1) {   // same for every lane of the warp
+#pragma unroll
+        for (int sl = 0; sl < SL; ++sl) {
+          const uint32_t ww[4] = {wb[p][sl].x, wb[p][sl].y, wb[p][sl].z, wb[p][sl].w};
+          const float sc = __uint_as_float(sb[p][sl] << 16);
+          const float zoff = __uint_as_float(0x43000000u | (zb[p][sl] << 16));  // 128 + zp, zp <= 127
+          float acc[M_T][4];
+#pragma unroll
+          for (int m = 0; m < M_T; ++m)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[m][q] = 0.f;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t pq = ((ww[q] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // bf16x2 {128 + q_j, 128 + q_(j+4)}
+#pragma unroll
+              for (int m = 0; m < M_T; ++m) fma2_f32_bf16(acc[m][q], pq, xw[m][sl][4 * q + j]);
+            }
+          }
+#pragma unroll
+          for (int m = 0; m < M_T; ++m) {
+            const float raw = (acc[m][0] + acc[m][1]) + (acc[m][2] + acc[m][3]);
+            part[p][m] = fmaf(fmaf(-zoff, xsum[m][sl], raw), sc, part[p][m]);  // a dead slice carries sc = 0
+          }
+        }
+        request(p);  // the registers of row r + p are free again: ask for row r + p + PF
+      }
+    }
+    // sum over the 32 lanes.  Four rows at a time fold into one value per lane first (a lane keeps half of its
+    // values and hands the other half to its partner), so the 4 rows cost 6 shuffles instead of 20; afterwards lane
+    // 8 * i holds row i.
+    float mine[M_T];
+    int my_row;
+    if (PF == 4) {
+      const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0;
+#pragma unroll
+      for (int m = 0; m < M_T; ++m) {
+        float k0 = h16 ? part[2 % PF][m] : part[0][m], k1 = h16 ? part[3 % PF][m] : part[1 % PF][m];
+        const float s0 = h16 ? part[0][m] : part[2 % PF][m], s1 = h16 ? part[1 % PF][m] : part[3 % PF][m];
+        k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+        k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+        float k = h8 ? k1 : k0;
+        const float sx = h8 ? k0 : k1;
+        k += __shfl_xor_sync(0xffffffffu, sx, 8);
+        k += __shfl_xor_sync(0xffffffffu, k, 4);
+        k += __shfl_xor_sync(0xffffffffu, k, 2);
+        k += __shfl_xor_sync(0xffffffffu, k, 1);
+        mine[m] = k;
+      }
+      my_row = ((lane & 7) == 0) ? (lane >> 3) : -1;
+    } else {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int p = 0; p < PF; ++p)
+#pragma unroll
+          for (int m = 0; m < M_T; ++m) part[p][m] += __shfl_xor_sync(0xffffffffu, part[p][m], o);
+      my_row = lane < PF ? lane : -1;
+#pragma unroll
+      for (int m = 0; m < M_T; ++m) {
+        mine[m] = 0.f;
+#pragma unroll
+        for (int p = 0; p < PF; ++p)
+          if (p == lane) mine[m] = part[p][m];
+      }
+    }
+    if (wpr == 1) {
+      if (my_row >= 0 && r + my_row < r1) {
+#pragma unroll
+        for (int m = 0; m < M_T; ++m)
+          y[(size_t)m * N + r + my_row] = __float2bfloat16_rn(bias ? mine[m] + bias[r + my_row] : mine[m]);
+      }
+    } else {
+      if (my_row >= 0) {
+#pragma unroll
+        for (int m = 0; m < M_T; ++m) red[it & 1][warp][my_row][m] = mine[m];
+      }
+      // the wpr warps of this row lane run the same number of iterations: one barrier per iteration, and the
+      // buffer written two iterations later is read (by warp kq == 0) before that warp reaches the barrier between
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + rs), "r"(wpr * 32) : "memory");
+      if (kq == 0 && lane < PF * M_T) {
+        const int p = lane / M_T, m = lane - p * M_T;
+        float v = 0.f;
+        for (int w = 0; w < wpr; ++w) v += red[it & 1][warp + w][p][m];
+        if (r + p < r1) y[(size_t)m * N + r + p] = __float2bfloat16_rn(bias ? v + bias[r + p] : v);
+      }
+    }
+  }
 }
 
 }  // namespace
 
-// one or two tokens: fp32 FMAs on the CUDA cores (a lane per 32-k slice, at most 512 slices per row)
-static bool gemv_uses_fma(int M, int K) { return M <= 2 && K <= 32 * 32 * CWARPS; }
+// one or two tokens: fp32 FMAs on the CUDA cores, a lane per 32-k slice (at most 4 slices per lane, 16 warps per row)
+// (the activations of a lane live in registers: 16 per slice and token)
+static bool gemv_uses_fma(int M, int K, int group) {
+  return M <= 2 && K % 32 == 0 && group % 32 == 0 && K <= 32 * 32 * 16 * (M == 1 ? 4 : 2);
+}
 
 int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why) {
   const char* w = nullptr;
   if (M < 1 || M > MAX_M) w = "M must be in [1, 8]";
-  else if (K % CHUNK_K != 0) w = "K must be a multiple of 64";
-  else if (group < CHUNK_K || group % CHUNK_K != 0 || K % group != 0) w = "group size must be a multiple of 64 dividing K";
   else if (N < 1) w = "empty N";
-  else if (gemv_plan(M, K, group, !gemv_uses_fma(M, K)).stages < 2) w = "two 16-row weight slabs plus the activations do not fit in shared memory";
+  else if (group < 1 || K % group != 0) w = "the group size must divide K";
+  else if (gemv_uses_fma(M, K, group)) w = nullptr;
+  else if (K % CHUNK_K != 0) w = "K must be a multiple of 64";
+  else if (group < CHUNK_K || group % CHUNK_K != 0) w = "group size must be a multiple of 64 dividing K";
+  else if (gemv_plan(M, K, group, true).stages < 2) w = "two 16-row weight slabs plus the activations do not fit in shared memory";
   if (why) *why = w;
   return w == nullptr;
 }
 
+template <int M_T, int SL, int PF, int MINB>
+static int launch_direct(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
+                         int N, int K, int group, int wpr, int blocks, int early, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(512);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, a16_w4_gemv_direct_kernel<M_T, SL, PF, MINB>, static_cast<const __nv_bfloat16*>(x),
+                              static_cast<const uint8_t*>(wq), static_cast<const __nv_bfloat16*>(scale),
+                              static_cast<const uint8_t*>(zp), bias, static_cast<__nv_bfloat16*>(y), N, K, group, wpr,
+                              early));
+  return B200Q_OK;
+}
+
 int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
-                       int M, int N, int K, int group, int* status, cudaStream_t stream) {
+                       int M, int N, int K, int group, int* status, cudaStream_t stream, bool weights_constant) {
   const char* why = nullptr;
   if (!a16_w4_gemv_supported(M, N, K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: %s", why);
   if ((reinterpret_cast<uintptr_t>(wq) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
     return set_error(B200Q_ERR_INVALID, "a16 w4 gemv: weights and activations must be 16-byte aligned");
-  const bool fma = gemv_uses_fma(M, K) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-  const GemvPlan P = gemv_plan(M, K, group, !fma);
-  if (P.stages < 2) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: the weight slabs do not fit in shared memory");
   int dev = 0, sms = 0;
   CUDA_TRY(cudaGetDevice(&dev));
   CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (gemv_uses_fma(M, K, group)) {
+    // warps per row: the smallest power of two that leaves a lane at most SL slices
+    const int T = K / 32;
+    const int early = weights_constant ? 1 : 0;
+    if (M == 1) {
+      int sl = 1, wpr = 1;
+      while (wpr < 16 && wpr * 32 < T) wpr *= 2;
+      while (sl * wpr * 32 < T) sl *= 2;  // K > 16384: more slices per lane
+      const int blocks = 2 * sms;
+      if (sl == 1) return launch_direct<1, 1, 4, 2>(x, wq, scale, zp, bias, y, N, K, group, wpr, blocks, early, stream);
+      if (sl == 2) return launch_direct<1, 2, 4, 1>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
+      return launch_direct<1, 4, 1, 1>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
+    }
+    int sl = 1, wpr = 1;
+    while (wpr < 16 && wpr * 32 < T) wpr *= 2;
+    while (sl * wpr * 32 < T) sl *= 2;
+    if (sl == 1) return launch_direct<2, 1, 6, 1>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
+    return launch_direct<2, 2, 3, 1>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
+  }
+  const GemvPlan P = gemv_plan(M, K, group, true);
+  if (P.stages < 2) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: the weight slabs do not fit in shared memory");
   const int slabs = (N + ROWS - 1) / ROWS;
   const int blocks = slabs < sms ? slabs : sms;
-  if (fma) {
-    // one token and K <= 4096: a lane owns four slices, one warp covers a row and stores its result directly
-    // one token: two slices per lane (fewer warps per row to sum over); four would not leave registers to schedule with
-    auto ffn = M == 1 ? (K <= 8192 ? a16_w4_gemv_fma_kernel<1, 2> : a16_w4_gemv_fma_kernel<1, 1>)
-                      : a16_w4_gemv_fma_kernel<2, 1>;
-    CUDA_TRY(cudaFuncSetAttribute(ffn, cudaFuncAttributeMaxDynamicSharedMemorySize, P.total));
-    ffn<<<blocks, THREADS, P.total, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
-                                              static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp),
-                                              bias, static_cast<__nv_bfloat16*>(y), N, K, group, status);
-    CUDA_TRY(cudaGetLastError());
-    return B200Q_OK;
-  }
   auto kfn = a16_w4_gemv_kernel;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, P.total));
   kfn<<<blocks, THREADS, P.total, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),

@@ -15,6 +15,9 @@ int minmax_static_launch(const float* x, long long n, long long samples, float* 
 // hist[0 .. nb[s]) += histogram of sample s with threshold th[s]; th / nb are DEVICE arrays
 int histogram_launch(const float* x, long long n, long long samples, const float* th, const int* nb, int* hist,
                      int max_bins, cudaStream_t s);
+// Counter layout of the histogram kernel: -1 = chosen per launch (default); 0..4 = 2^mode 32-bit copies per bin;
+// 5 = lane-owned 16-bit counters.  A tuning control for measurements; every layout gives the same counts.
+void histogram_set_mode(int mode);
 int kl_raw_histogram_launch(const float* x, long long n, float width, int bins, int* hist, cudaStream_t s);
 int fold_launch(const int* in, long long n_in, int* out, long long n_out, cudaStream_t s);
 // thresholds[t] for histograms hist_all[offsets[t] .. offsets[t+1]); kl_dev (optional) gets 1024 floats per tensor

@@ -101,12 +101,27 @@ int validate(const b200q_a16matmul_desc& d) {
   return B200Q_OK;
 }
 
+// Route of b200q_a16_*: 0 = chosen per call; 1 = CUDA-core / mma.sync decode kernels (8 tokens at a time);
+// 2 = fused-dequantisation tensor-core kernel; 3 = one-time bf16 copy of the weight + bf16 GEMM (handle API, M > 8).
+int g_a16_route = 0;
+
 // Decode shapes go to the GEMV kernel; larger M is processed in slices of 8 tokens.
 int a16_dispatch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
                  long long M, int N, int K, int group, int* status, cudaStream_t s, DevBuf* w16 = nullptr,
-                 bool* w16_ready = nullptr) {
+                 bool* w16_ready = nullptr, bool weights_constant = false) {
   const char* why = nullptr;
-  if (M > 8 && w16 && K % 8 == 0 && group % 8 == 0 && M <= 0x7fffffffLL) {
+  // both routes index scales and zero points as [n][k / group]: the group must tile K exactly, and a byte holds
+  // two consecutive k of one row
+  if (group < 1 || K % group != 0 || (K & 1)) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: K must be even and a multiple of the group size");
+  const int route = g_a16_route;
+  const bool umma_ok = a16_w4_umma_supported(M > 0 ? M : 1, N, K, group, nullptr) != 0;
+  const bool simt_ok = M <= 2 && a16_w4_gemv_supported((int)(M > 0 ? M : 1), N, K, group, nullptr) != 0;
+  if (M == 0) return B200Q_OK;
+  if (route == 2 || (route == 0 && umma_ok && !simt_ok)) {
+    if (!umma_ok) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: the tensor-core kernel needs K and the group size to be multiples of 64");
+    return a16_w4_umma_launch(x, wq, scale, zp, bias, y, M, N, K, group, status, s);
+  }
+  if (route == 3 && M > 8 && w16 && K % 8 == 0 && group % 8 == 0 && M <= 0x7fffffffLL) {
     // prefill: dequantise once (kept for the life of the handle / weight version), then a bf16 GEMM
     if (!*w16_ready) {
       B200Q_TRY(w16->ensure((size_t)N * K * 2));
@@ -119,7 +134,8 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
   for (long long m0 = 0; m0 < M; m0 += 8) {
     const int mm = (int)((M - m0) < 8 ? (M - m0) : 8);
     B200Q_TRY(a16_w4_gemv_launch(static_cast<const uint8_t*>(x) + (size_t)m0 * K * 2, wq, scale, zp, bias,
-                                 static_cast<uint8_t*>(y) + (size_t)m0 * N * 2, mm, N, K, group, status, s));
+                                 static_cast<uint8_t*>(y) + (size_t)m0 * N * 2, mm, N, K, group, status, s,
+                                 weights_constant));
   }
   return B200Q_OK;
 }
@@ -218,6 +234,8 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
   return rc;
 }
 
+void b200q_a16_set_route(int32_t route) { g_a16_route = (route >= 0 && route <= 3) ? route : 0; }
+
 int b200q_a16_w4_dev(const void* x_bf16, const void* wq, const void* scale_bf16, const void* zp_u8,
                      const float* bias_f32, void* y_bf16, int64_t M, int64_t N, int64_t K, int32_t group,
                      int32_t* status, void* stream) {
@@ -260,7 +278,7 @@ int b200q_a16_dev_run(void* handle, const void* x_bf16, void* y_bf16, int64_t M,
   if (!handle || !x_bf16 || !y_bf16 || M < 0) return set_error(B200Q_ERR_INVALID, "a16_dev_run: bad argument");
   A16Handle* h = static_cast<A16Handle*>(handle);
   return a16_dispatch(x_bf16, h->d_wq, h->d_scale, h->d_zp, h->d_bias, y_bf16, M, h->N, h->K, h->group,
-                      h->status.as<int>(), static_cast<cudaStream_t>(stream), &h->w16, &h->w16_ready);
+                      h->status.as<int>(), static_cast<cudaStream_t>(stream), &h->w16, &h->w16_ready, true);
 }
 
 int b200q_a16_dev_status(void* handle, void* stream) {

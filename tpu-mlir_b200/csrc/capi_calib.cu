@@ -172,6 +172,8 @@ int b200q_calib_histogram(void* ctx, const float* x_dev, int64_t n_per_sample, i
                           reinterpret_cast<const int*>(c->params.as<char>() + (size_t)samples * 4), hist_dev, max_bins, s);
 }
 
+void b200q_calib_set_histogram_layout(int32_t mode) { histogram_set_mode(mode); }
+
 int b200q_calib_find_thresholds(void* ctx, int32_t tensors, const int32_t* const* hist_dev, const int64_t* n_bins,
                                 const float* widths, int64_t dst_bins, float* thresholds_host, float* kl_host,
                                 void* stream) {
