@@ -84,10 +84,16 @@ def test_unsupported_is_reported():
     assert ei.value.code == L.ERR_UNSUPPORTED
 
 
-def check_prefill(y_bits, ref_f32):
-    """Prefill rounds the dequantised weight to bf16 before the tensor-core GEMM (2^-9 relative per weight, which
-    shows up as ~1e-3 * rms(y) of absolute noise), so the floor of the relative bound is rms(y_ref) itself, and
-    both sides are rounded to bf16 afterwards, which can add one bf16 ulp:
+def check_f32(y_bits, ref_f32):
+    """The plain bound of `check` against an fp32 reference: |y - y_ref| <= 1e-2 * max(|y_ref|, 1e-2 * rms(y_ref)),
+    after rounding the reference to bf16 like the reference's own output."""
+    check(y_bits, oracle.f32_to_bf16_bits_fast(np.asarray(ref_f32, dtype=np.float32)))
+
+
+def check_rounded_weight(y_bits, ref_f32):
+    """The route that keeps a bf16 copy of the dequantised weight (b200q_a16_set_route(3), and the handle's choice from
+    512 tokens on) rounds W to bf16 (2^-9 relative per weight, ~1e-3 * rms(y) of absolute noise), which the reference
+    does not; its bound has rms(y_ref) as the floor and one bf16 ulp for the output rounding on both sides:
     |y - y_ref| <= 1e-2 * max(|y_ref|, rms(y_ref)) + ulp_bf16(y_ref)."""
     y = oracle.bf16_bits_to_f32(y_bits).astype(np.float64)
     r = np.asarray(ref_f32, dtype=np.float64)
@@ -98,6 +104,17 @@ def check_prefill(y_bits, ref_f32):
     assert float(np.sqrt(np.mean((y - r) ** 2))) < 3e-3 * rms
 
 
+@pytest.fixture
+def route():
+    """Selects the kernel behind b200q_a16_* for one test and restores the default."""
+    lib = L.lib()
+
+    def set_route(r):
+        lib.b200q_a16_set_route(r)
+    yield set_route
+    lib.b200q_a16_set_route(0)
+
+
 def run_handle(c, M, N, K, group, bias=None):
     x, wq, sc, zp = dev(c["x"]), dev(c["wq"]), dev(c["scale"]), dev(c["zp"])
     b = dev(bias) if bias is not None else None
@@ -105,7 +122,7 @@ def run_handle(c, M, N, K, group, bias=None):
     h = C.c_void_p()
     lib = L.lib()
     L.check(lib.b200q_a16_dev_create(ptr(wq), ptr(sc), ptr(zp), ptr(b), N, K, group, C.byref(h)))
-    for _ in range(2):     # the second run reuses the dequantised weight kept in the handle
+    for _ in range(2):     # the second run reuses what the handle keeps
         L.check(lib.b200q_a16_dev_run(h, ptr(x), ptr(y), M, None))
     L.check(lib.b200q_a16_dev_status(h, None))
     lib.b200q_a16_dev_destroy(C.byref(h))
@@ -114,25 +131,54 @@ def run_handle(c, M, N, K, group, bias=None):
 
 @pytest.mark.parametrize("M", [16, 128])
 def test_prefill_llama_mlp_shape_against_oracle(M):
+    """Default route above 8 tokens: the fused-dequantisation tensor-core kernel, held to the plain bound."""
     c = synth.a16_w4(seed=2, M=M)
-    ref = oracle.bf16_bits_to_f32(oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], group=64))
-    check_prefill(run_handle(c, M, 11008, 4096, 64), ref)
+    ref = oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], group=64)
+    check(run_handle(c, M, 11008, 4096, 64), ref)
 
 
-def test_prefill_2048_tokens_against_fp32_matmul():
-    """BASELINE config 2 at M=2048: the fp32 reference is the oracle's dequantised weight times x in fp32 (torch)."""
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 33, 300])
+def test_tensor_core_kernel_every_token_count(route, M):
+    """The fused kernel forced for every M (few-token form up to 4 tokens, token tiles of 32 / 64 / 128 above)."""
+    route(2)
+    c = synth.a16_w4(seed=11, M=M, K=4096, N=1000, group=64)
+    bias = np.random.default_rng(3).standard_normal(1000).astype(np.float32)
+    ref = oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], bias, group=64)
+    check(run_dev(c, M, 1000, 4096, 64, bias), ref)
+
+
+@pytest.mark.parametrize("case", [dict(M=1, K=64, N=16, g=64), dict(M=4, K=192, N=100, g=64), dict(M=9, K=256, N=128, g=64),
+                                  dict(M=2, K=11008, N=130, g=64), dict(M=33, K=11008, N=130, g=64),
+                                  dict(M=100, K=4096, N=384, g=128), dict(M=40, K=2048, N=17, g=256),
+                                  dict(M=3, K=8192, N=300, g=128)])
+def test_tensor_core_kernel_shapes(route, case):
+    """Ragged rows, K that is not a multiple of a raw stage (256), groups of 128 and 256, many groups per row."""
+    route(2)
+    c = synth.a16_w4(seed=13, M=case["M"], K=case["K"], N=case["N"], group=case["g"])
+    ref = oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], group=case["g"])
+    check(run_dev(c, case["M"], case["N"], case["K"], case["g"]), ref)
+
+
+def test_prefill_2048_tokens_against_fp32_matmul(route):
+    """BASELINE config 2 at M=2048: the fp32 reference is the oracle's dequantised weight times x in fp32 (torch).
+    The handle's own choice at this size (the bf16 copy of the weight) is held to its wider bound, the fused kernel
+    to the plain one."""
     M = 2048
     c = synth.a16_w4(seed=2, M=M)
     W = torch.from_numpy(oracle.a16_dequant_w4(c["wq"], c["scale"], c["zp"], group=64)).cuda()
     x = torch.from_numpy(oracle.bf16_bits_to_f32(c["x"])).cuda()
     torch.backends.cuda.matmul.allow_tf32 = False
     ref = (x @ W.T).cpu().numpy()
-    check_prefill(run_handle(c, M, 11008, 4096, 64), ref)
+    check_rounded_weight(run_handle(c, M, 11008, 4096, 64), ref)
+    route(2)
+    check_f32(run_handle(c, M, 11008, 4096, 64), ref)
 
 
-def test_prefill_ragged_with_bias():
+def test_prefill_ragged_with_bias(route):
     M, K, N, g = 37, 320, 200, 64
     c = synth.a16_w4(seed=5, M=M, K=K, N=N, group=g)
     bias = np.random.default_rng(2).standard_normal(N).astype(np.float32)
-    ref = oracle.bf16_bits_to_f32(oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], bias, group=g))
-    check_prefill(run_handle(c, M, N, K, g, bias), ref)
+    ref = oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], bias, group=g)
+    check(run_handle(c, M, N, K, g, bias), ref)
+    route(3)
+    check_rounded_weight(run_handle(c, M, N, K, g, bias), oracle.bf16_bits_to_f32(ref))

@@ -584,7 +584,10 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
   int dev = 0, sms = 0;
   CUDA_TRY(cudaGetDevice(&dev));
   CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  if (gemv_uses_fma(M, K, group)) {
+  // two tokens: the tensor-core decode kernel is the faster one where it applies (measured 14.3 us against 16.2 us at
+  // N = 11008, K = 4096); the CUDA-core form then only takes what that kernel cannot (groups of 32, K % 64 != 0)
+  const bool mma_ok = K % CHUNK_K == 0 && group >= CHUNK_K && group % CHUNK_K == 0 && gemv_plan(M, K, group, true).stages >= 2;
+  if (gemv_uses_fma(M, K, group) && (M == 1 || !mma_ok)) {
     // warps per row: the smallest power of two that leaves a lane at most SL slices
     const int T = K / 32;
     const int early = weights_constant ? 1 : 0;

@@ -1,6 +1,6 @@
 // A16MatMul with 4-bit group-quantized weights on the 5th-generation tensor cores: the packed weights are dequantised
-// in registers, written to shared memory as the bf16 A operand of tcgen05.mma (kind::f16, fp32 accumulation in TMEM),
-// and never exist in global memory in any wider form.
+// in registers and handed to tcgen05.mma as its A operand through TENSOR MEMORY (kind::f16, bf16 x bf16, fp32
+// accumulation in TMEM); they never exist in global or shared memory in any wider form.
 //
 // Semantics: tpu::A16MatMulOp::inference, static w4 path with w_transpose
 // (lib/Dialect/Tpu/Interfaces/Common/A16MatMul.cpp:171-208,:240-246): weight bytes [N, K/2], even k in the low
@@ -10,25 +10,31 @@
 // fp32 partial sum of each group afterwards.
 //
 // The product is computed transposed, D[n, m] = sum_k A[n, k] * B[m, k]: the 128 TMEM lanes are output channels,
-// the columns are tokens.  One persistent CTA per SM, 20 warps:
-//   warp 0       TMA producer: packed weights, boxes of 16 rows x 128 bytes (= 256 k) with the 128-byte swizzle into
-//                a ring of raw stages; in the many-token form also the activation tile of each k-block.
-//   warp 1       owns TMEM, issues the MMAs (one thread): per k-block of 64 k four MMAs 128 x N x 16.
-//   warps 4-11   dequantisation, four teams of two warps; team t converts k-block t of every raw stage, so four
-//                k-blocks are in the making at any time: one 32-bit word (8 nibbles) -> 128 + q as bf16 by the bit
-//                trick, minus (128 + zp) in one packed bf16 FMA, 16 bytes of A, written as rows of the 128-byte
-//                swizzled K-major layout.  In the few-token form the team also writes the k-block's activations
-//                into the B operand.
-//   warps 12-19  epilogue: drain the accumulator of each period, running[n][m] += scale[n][g] * partial; at the end of
-//                a work item add the bias, round to bf16 and store y[m][n].
+// the columns are tokens.  One persistent CTA per SM, 32 warps:
+//   warp 0        TMA producer of the packed weights: boxes of 16 rows x 128 bytes (= 256 k, four k-blocks) with the
+//                 128-byte swizzle into a ring of raw stages.
+//   warp 1        owns TMEM, issues the MMAs (one thread): per k-block of 64 k four MMAs 128 x N x 16, A from TMEM.
+//   warp 2        many-token form: TMA producer of the activation tile (B operand) of each k-block.
+//   dequantisers  W warps per TMEM lane quarter.  The warp of quarter q with slot s converts its quarter's 32 rows of
+//                 every k-block j with j mod W == s: a lane reads its row's 32 bytes of nibbles, turns each 32-bit word
+//                 into 128 + q as bf16 by the bit trick, subtracts (128 + zp) with one packed bf16 FMA, and writes the
+//                 64 values as 32 columns of its TMEM lane (tcgen05.st).  A k-block is complete when the four
+//                 quarters have arrived on its barrier.
+//   epilogue      drains the accumulator of each period, running[n][m] += scale[n][g] * partial; at the end of a
+//                 work item adds the bias, rounds to bf16 and stores y[m][n].
 //
 // Groups and columns.  The group scale cannot ride through the MMA, so partial sums of different groups must stay
-// apart.  With many tokens (M > 16) the accumulator is drained after every group (two TMEM buffers alternate).  With
-// few tokens the accumulator has spare columns: column j = g_local * MTOK + m belongs to group g_local of the current
-// period of G = 16 / MTOK groups, and the B operand of a k-block of group g_local is zero except in its MTOK rows.  That
-// operand is a window into one small buffer, (G-1)*MTOK zero rows | the MTOK activation rows | (G-1)*MTOK zero rows,
-// starting (G-1-g_local)*MTOK rows into it, so only the MTOK live rows are rewritten per k-block.  One drain then serves G
-// groups (for one token and K = 4096: four drains per row instead of 64).
+// apart.  With many tokens the accumulator is drained after every group (several TMEM buffers alternate).  With few
+// tokens (M <= 4) the accumulator has spare columns: column j = g_local * MTOK + m belongs to group g_local of the
+// current period of G = 16 / MTOK groups, and the B operand of a k-block of group g_local is zero except in its MTOK
+// rows.  That operand is a window into one small buffer, (G-1)*MTOK zero rows | the MTOK activation rows | (G-1)*MTOK
+// zero rows, starting (G-1-g_local)*MTOK rows into it, so only the MTOK live rows are rewritten per k-block (from a copy
+// of the activations that stays in shared memory).  One drain then serves G groups: for one token and K = 4096, four
+// drains per row instead of 64.
+//
+// Rows and lanes.  A work item covers up to 128 output channels; with few tokens the items are smaller (a multiple of
+// 16 rows) so that every SM gets one.  Row r of an item lives in TMEM lane 32 * q + 8 * (r / 32) + r % 8 with
+// q = (r / 8) % 4: 8-row groups go round the four lane quarters, so a partial item still loads the quarters evenly.
 //
 // Every mbarrier wait is bounded (2 s); a wait that runs out leaves its site code in a shared flag, every role
 // unwinds, TMEM is freed and *status receives the code.
@@ -45,17 +51,41 @@ namespace b200q {
 namespace {
 
 constexpr int TILE_ROWS = 128;           // output channels per work item = MMA M
-constexpr int KB = 64;                   // k per k-block: 64 bf16 = one 128-byte swizzle span
+constexpr int KB = 64;                   // k per k-block: 64 bf16 = one 128-byte swizzle span of B
 constexpr int RAW_KB = 4;                // k-blocks per raw stage (128 bytes of nibbles per row)
 constexpr int RAW_STAGE_BYTES = TILE_ROWS * 128;
-constexpr int A_STAGE_BYTES = TILE_ROWS * 128;
-constexpr int MAX_STAGES = 8;
-constexpr int DQ_WARPS = 8, EPI_WARPS = 8, TEAM_THREADS = 64;  // four teams of two warps
-constexpr int FIRST_DQ_WARP = 4, FIRST_EPI_WARP = 12;
-constexpr int THREADS = (FIRST_EPI_WARP + EPI_WARPS) * 32;  // 640
+constexpr int A_COLS = 32;               // TMEM columns of one k-block of A (two bf16 per column)
+constexpr int TMEM_COLS = 512;
+constexpr int MAX_RAW = 8, MAX_AS = 12, MAX_ACC = 4;
+constexpr int THREADS = 1024;
 constexpr int SCALE_PITCH = TILE_ROWS + 2;   // scaleT[g][n], bf16: transposed so that lanes (rows) read one group conflict-free
 constexpr int ZP_PITCH = TILE_ROWS + 4;      // zpT[g][n], bytes
 constexpr uint64_t WAIT_NS = 2000000000ull;
+
+// MT == 0: few-token form (M <= 4); else the token tile width of the many-token form
+template <int MT>
+struct Cfg {
+  static constexpr bool FEW = MT == 0;
+  static constexpr int W = FEW ? 6 : (MT == 128 ? 3 : 5);     // dequantisation warps per lane quarter
+  static constexpr int E = FEW ? 4 : (MT == 128 ? 16 : 8);    // epilogue warps (a multiple of 4)
+  static constexpr int N_MMA = FEW ? 16 : MT;
+  static constexpr int NACC = FEW ? 2 : (MT == 128 ? 2 : 4);  // accumulator buffers
+  static constexpr int AS = FEW ? 12 : (MT == 32 ? 12 : 8);   // k-blocks of A in TMEM
+  static constexpr int A_COL0 = TMEM_COLS - AS * A_COLS;      // accumulators from column 0, A stages at the top
+  static constexpr int B_STAGE_BYTES = FEW ? 32 * 128 : MT * 128;
+  static constexpr int FIRST_DQ = 4, FIRST_EPI = 4 + 4 * W;
+  static constexpr int MY_COLS = N_MMA / (E / 4);             // accumulator columns per epilogue thread
+  static_assert(FIRST_EPI + E == THREADS / 32, "32 warps");
+  static_assert(NACC * N_MMA <= A_COL0, "accumulators and A stages share 512 columns");
+  // shared memory: raw ring | B ring | barriers | misc | scaleT | zpT | resident activations (few-token form)
+  static constexpr int NUM_BARS = 2 * MAX_RAW + 2 * MAX_AS + 2 * MAX_ACC + 2;
+  __host__ __device__ static int b_off(int rs) { return rs * RAW_STAGE_BYTES; }
+  __host__ __device__ static int bar_off(int rs) { return b_off(rs) + AS * B_STAGE_BYTES; }
+  __host__ __device__ static int misc_off(int rs) { return bar_off(rs) + NUM_BARS * 8; }
+  __host__ __device__ static int meta_off(int rs) { return (misc_off(rs) + 16 + 127) & ~127; }
+  __host__ __device__ static int x_off(int rs, int gpr) { return meta_off(rs) + ((gpr * (SCALE_PITCH * 2 + ZP_PITCH) + 15) & ~15); }
+  __host__ __device__ static int total(int rs, int gpr, int x_bytes) { return x_off(rs, gpr) + x_bytes + 1024; }
+};
 
 struct UmmaArgs {
   const uint8_t* x;       // bf16 [M][K]
@@ -66,30 +96,13 @@ struct UmmaArgs {
   int M, N, K, group, gpr;
   int num_kb;             // K / 64
   int kpg;                // k-blocks per group
-  int mtok;               // few-token form: token rows per group slot (1, 2, 4, 8 or 16); many-token form: tile width
+  int mtok;               // few-token form: token rows per group slot (1, 2 or 4)
   int G;                  // groups per drain period
-  int n_mma;              // MMA N = accumulator columns
   int rows_item;          // output channels per work item (multiple of 16, <= 128)
   int items_n, items_m;   // work items: items_n row chunks x items_m token tiles
-  int raw_stages, op_stages;  // ring depths (chosen by the host so that everything fits in shared memory)
+  int raw_stages;         // depth of the raw ring (chosen by the host so that everything fits in shared memory)
   uint32_t idesc;
   int* status;
-};
-
-// Shared-memory plan, the same on host and device: raw ring | A ring | B ring | barriers | misc | scaleT | zpT
-template <int MT_LARGE>
-struct Smem {
-  // MT_LARGE == 0: few-token form (B written by the dequantisation teams, 32-row window buffer); else B by TMA
-  static constexpr int B_STAGE_BYTES = MT_LARGE == 0 ? 32 * 128 : MT_LARGE * 128;
-  static constexpr int NUM_BARS = 4 * MAX_STAGES + 6;
-  __host__ __device__ static int a_off(int raw_stages) { return raw_stages * RAW_STAGE_BYTES; }
-  __host__ __device__ static int b_off(int raw_stages, int op_stages) { return a_off(raw_stages) + op_stages * A_STAGE_BYTES; }
-  __host__ __device__ static int bar_off(int raw_stages, int op_stages) { return b_off(raw_stages, op_stages) + op_stages * B_STAGE_BYTES; }
-  __host__ __device__ static int misc_off(int raw_stages, int op_stages) { return bar_off(raw_stages, op_stages) + NUM_BARS * 8; }
-  __host__ __device__ static int meta_off(int raw_stages, int op_stages) { return (misc_off(raw_stages, op_stages) + 16 + 127) & ~127; }
-  __host__ __device__ static int total(int raw_stages, int op_stages, int gpr) {
-    return meta_off(raw_stages, op_stages) + gpr * (SCALE_PITCH * 2 + ZP_PITCH) + 1024;
-  }
 };
 
 // 8 nibbles of `w` (k0..k7, k0 lowest) -> four bf16x2 words {q_j - zp, q_(j+4) - zp}, j = 0..3
@@ -101,77 +114,151 @@ __device__ __forceinline__ void dequant_word(uint32_t w, uint32_t negz, uint32_t
   }
 }
 
-template <int MT_LARGE>
+// Scales (bf16) or zero points (bytes) of the rows [row0, row0 + nrows) transposed into shared memory as T[g][n]:
+// every thread first requests all its 16-byte pieces, then scatters them (one round trip to global memory).
+template <typename T, int PITCH>
+__device__ __forceinline__ void stage_meta(T* dstT, const T* src, int row0, int nrows, int gpr, int tid, int nthreads) {
+  constexpr int PER = 16 / (int)sizeof(T);   // entries per 16-byte piece
+  const T* base = src + (size_t)row0 * gpr;
+  const int total = nrows * gpr;
+  if ((gpr % PER) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
+    const int pieces = total / PER;
+    constexpr int BATCH = 4;
+    for (int p0 = tid; p0 < pieces; p0 += nthreads * BATCH) {
+      uint4 v[BATCH];
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int p = p0 + u * nthreads;
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (p < pieces) v[u] = __ldg(reinterpret_cast<const uint4*>(base) + p);
+      }
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int p = p0 + u * nthreads;
+        if (p < pieces) {
+          const int i = p * PER, n = i / gpr, g = i - n * gpr;
+          const uint32_t wv[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+          for (int k = 0; k < PER; ++k) {
+            const uint32_t word = wv[(k * (int)sizeof(T)) >> 2];
+            dstT[(g + k) * PITCH + n] = (T)(word >> (8 * ((k * (int)sizeof(T)) & 3)));
+          }
+        }
+      }
+    }
+  } else {
+    constexpr int BATCH = 8;
+    for (int i0 = tid; i0 < total; i0 += nthreads * BATCH) {
+      T v[BATCH];
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int i = i0 + u * nthreads;
+        v[u] = i < total ? __ldg(base + i) : T(0);
+      }
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int i = i0 + u * nthreads;
+        if (i < total) {
+          const int n = i / gpr, g = i - n * gpr;
+          dstT[g * PITCH + n] = v[u];
+        }
+      }
+    }
+  }
+}
+
+template <int MT>
 __global__ void __launch_bounds__(THREADS, 1)
 a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                    const UmmaArgs args) {
-  using L = Smem<MT_LARGE>;
-  constexpr bool FEW = MT_LARGE == 0;
+  using C = Cfg<MT>;
+  constexpr bool FEW = C::FEW;
+  constexpr int W = C::W, E = C::E, AS = C::AS, NACC = C::NACC, N_MMA = C::N_MMA;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int RS = args.raw_stages, OS = args.op_stages;
+  const int RS = args.raw_stages;
   const uint32_t smem_base = ptx::smem_u32(smem);
-  const int a_off = L::a_off(RS), b_off = L::b_off(RS, OS), misc_off = L::misc_off(RS, OS);
-  const uint32_t bar_base = smem_base + (uint32_t)L::bar_off(RS, OS);
+  const int b_off = C::b_off(RS), misc_off = C::misc_off(RS), meta_off = C::meta_off(RS);
+  const uint32_t bar_base = smem_base + (uint32_t)C::bar_off(RS);
   auto raw_full = [&](int s) { return bar_base + 8u * s; };
-  auto raw_empty = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
-  auto op_full = [&](int s) { return bar_base + 8u * (2 * MAX_STAGES + s); };
-  auto op_empty = [&](int s) { return bar_base + 8u * (3 * MAX_STAGES + s); };
-  auto acc_full = [&](int a) { return bar_base + 8u * (4 * MAX_STAGES + a); };
-  auto acc_empty = [&](int a) { return bar_base + 8u * (4 * MAX_STAGES + 2 + a); };
+  auto raw_empty = [&](int s) { return bar_base + 8u * (MAX_RAW + s); };
+  auto a_full = [&](int s) { return bar_base + 8u * (2 * MAX_RAW + s); };
+  auto a_empty = [&](int s) { return bar_base + 8u * (2 * MAX_RAW + MAX_AS + s); };
+  auto acc_full = [&](int a) { return bar_base + 8u * (2 * MAX_RAW + 2 * MAX_AS + a); };
+  auto acc_empty = [&](int a) { return bar_base + 8u * (2 * MAX_RAW + 2 * MAX_AS + MAX_ACC + a); };
+  const uint32_t dq_sync_bar = bar_base + 8u * (2 * MAX_RAW + 2 * MAX_AS + 2 * MAX_ACC), epi_sync_bar = dq_sync_bar + 8u;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + misc_off + 4);
-  uint16_t* scaleT = reinterpret_cast<uint16_t*>(smem + L::meta_off(RS, OS));
-  uint8_t* zpT = smem + L::meta_off(RS, OS) + args.gpr * SCALE_PITCH * 2;
+  uint16_t* scaleT = reinterpret_cast<uint16_t*>(smem + meta_off);
+  uint8_t* zpT = smem + meta_off + args.gpr * SCALE_PITCH * 2;
+  // few-token form: the activations, resident for the whole kernel: xs[m][K] bf16, each 16-byte piece already in the
+  // nibble-pair order of the A operand
+  uint8_t* xs = smem + C::x_off(RS, args.gpr);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t dq_sync_bar = bar_base + 8u * (4 * MAX_STAGES + 4), epi_sync_bar = bar_base + 8u * (4 * MAX_STAGES + 5);
-  // Meeting point of the 8 warps of a role on an mbarrier (one arrival per warp), with the same bounded wait as
-  // every other wait of the kernel: a plain bar.sync would hang if one warp had already given up.
+  // Meeting point of the warps of a role on an mbarrier (one arrival per warp), with the same bounded wait as every
+  // other wait of the kernel: a plain bar.sync would hang if one warp had already given up.
   auto role_sync = [&](uint32_t bar, uint32_t& count, int where) -> bool {
     __syncwarp();
     bool ok_ = true;
     if (lane == 0) {
       ptx::mbar_arrive(bar);
-      ok_ = ptx::mbar_wait_bounded(bar, count & 1u, abort_flag, where, WAIT_NS);
+      ok_ = ptx::mbar_wait_bounded_fast(bar, count & 1u, abort_flag, where, WAIT_NS);
     }
     ++count;
     ok_ = __shfl_sync(0xffffffffu, ok_, 0);
     return ok_;
   };
-  const int tmem_cols = 2 * args.n_mma < 32 ? 32 : 2 * args.n_mma;  // power of two: n_mma is 16, 32, 64 or 128
+  // every lane of the warp runs the same wait (the barrier test is one warp instruction either way)
+  auto warp_wait = [&](uint32_t bar, uint32_t parity, int where) -> bool {
+    return ptx::mbar_wait_bounded_fast(bar, parity, abort_flag, where, WAIT_NS);
+  };
 
   ptx::griddep_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < RS; ++s) {
       ptx::mbar_init(raw_full(s), 1);
-      ptx::mbar_init(raw_empty(s), DQ_WARPS);
+      ptx::mbar_init(raw_empty(s), 4 * RAW_KB);   // one arrival per (k-block, lane quarter)
     }
-    for (int s = 0; s < OS; ++s) {
-      ptx::mbar_init(op_full(s), FEW ? 2 : 3);  // the two warps of a team (+ the TMA producer's activation tile)
-      ptx::mbar_init(op_empty(s), 1);
+    for (int s = 0; s < AS; ++s) {
+      ptx::mbar_init(a_full(s), FEW ? 4 : 5);     // the four quarters (+ the activation tile's TMA)
+      ptx::mbar_init(a_empty(s), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < NACC; ++a) {
       ptx::mbar_init(acc_full(a), 1);
-      ptx::mbar_init(acc_empty(a), EPI_WARPS);
+      ptx::mbar_init(acc_empty(a), E);
     }
-    ptx::mbar_init(dq_sync_bar, DQ_WARPS);
-    ptx::mbar_init(epi_sync_bar, EPI_WARPS);
+    ptx::mbar_init(dq_sync_bar, 4 * W);
+    ptx::mbar_init(epi_sync_bar, E);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
     ptx::prefetch_tensormap(&tmap_w);
     if (!FEW) ptx::prefetch_tensormap(&tmap_x);
   }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_ptr_smem), (uint32_t)TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::griddep_wait();
   if (FEW) {
     // the window buffers start as zeros; only their live rows are ever rewritten
     uint4* b = reinterpret_cast<uint4*>(smem + b_off);
-    for (int i = threadIdx.x; i < OS * L::B_STAGE_BYTES / 16; i += THREADS) b[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = threadIdx.x; i < AS * C::B_STAGE_BYTES / 16; i += THREADS) b[i] = make_uint4(0u, 0u, 0u, 0u);
+    // activations: rows past M are zeros
+    const int pieces = args.mtok * (args.K >> 3);
+    for (int i = threadIdx.x; i < pieces; i += THREADS) {
+      const int m = i / (args.K >> 3), c = i - m * (args.K >> 3);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (m < args.M) v = __ldg(reinterpret_cast<const uint4*>(args.x + ((size_t)m * args.K + (size_t)c * 8) * 2));
+      uint4 o;   // k order 0,4,1,5,2,6,3,7
+      o.x = __byte_perm(v.x, v.z, 0x5410);
+      o.y = __byte_perm(v.x, v.z, 0x7632);
+      o.z = __byte_perm(v.y, v.w, 0x5410);
+      o.w = __byte_perm(v.y, v.w, 0x7632);
+      reinterpret_cast<uint4*>(xs)[i] = o;
+    }
     ptx::fence_proxy_async_smem();
-  }
-  if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(tmem_ptr_smem), (uint32_t)tmem_cols);
-    ptx::tmem_relinquish();
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -179,8 +266,8 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   // work items of this CTA: a contiguous range, token tiles innermost (consecutive items share their weight rows'
-  // scales and zero points).  Ring positions derive from running counts: k-block j of the CTA uses operand stage
-  // j % OS in phase (j / OS) & 1, raw stage r likewise.
+  // scales and zero points).  Every role walks the same sequence of k-blocks, raw stages and drain periods; ring
+  // positions derive from running counts: k-block j of the CTA uses A stage j % AS in phase (j / AS) & 1.
   const int items = args.items_n * args.items_m;
   const int item_begin = (int)((long long)blockIdx.x * items / gridDim.x);
   const int item_end = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
@@ -188,35 +275,50 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const int raws_per_item = (num_kb + RAW_KB - 1) / RAW_KB;
   const int kb_per_period = args.G * args.kpg;
   const int periods_per_item = (num_kb + kb_per_period - 1) / kb_per_period;
-  ptx::griddep_wait();
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer: packed weights
     if (lane == 0) {
       bool ok = true;
+      int rs = 0;
+      uint32_t rphase = 0;
       for (int it = item_begin; it < item_end && ok; ++it) {
-        const int in_ = it / args.items_m, im = it - in_ * args.items_m;
+        const int in_ = it / args.items_m;
         const int row0 = in_ * args.rows_item;
         const int nrows = min(args.rows_item, args.N - row0);
         const int boxes = (nrows + 15) >> 4;
-        const int jbase = (it - item_begin) * num_kb, rbase = (it - item_begin) * raws_per_item;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-          if ((kb & (RAW_KB - 1)) == 0) {
-            const int r = rbase + kb / RAW_KB, rs = r % RS;
-            ok = ptx::mbar_wait_bounded(raw_empty(rs), (((uint32_t)(r / RS)) & 1u) ^ 1u, abort_flag, 1, WAIT_NS);
-            if (!ok) break;
-            ptx::mbar_arrive_expect_tx(raw_full(rs), (uint32_t)boxes * 16u * 128u);
-            const uint32_t dst = smem_base + (uint32_t)rs * RAW_STAGE_BYTES;
-            for (int b = 0; b < boxes; ++b)
-              ptx::tma_load_2d(dst + (uint32_t)b * 2048u, &tmap_w, raw_full(rs), (kb / RAW_KB) * 128, row0 + b * 16);
+        for (int rsi = 0; rsi < raws_per_item; ++rsi) {
+          ok = ptx::mbar_wait_bounded_fast(raw_empty(rs), rphase ^ 1u, abort_flag, 1, WAIT_NS);
+          if (!ok) break;
+          ptx::mbar_arrive_expect_tx(raw_full(rs), (uint32_t)boxes * 16u * 128u);
+          const uint32_t dst = smem_base + (uint32_t)rs * RAW_STAGE_BYTES;
+          for (int b = 0; b < boxes; ++b) ptx::tma_load_2d(dst + (uint32_t)b * 2048u, &tmap_w, raw_full(rs), rsi * 128, row0 + b * 16);
+          // a last raw stage with fewer than four k-blocks: nobody reads the missing ones, stand in for their arrivals
+          const int nreal = min(RAW_KB, num_kb - rsi * RAW_KB);
+          if (nreal < RAW_KB) ptx::mbar_arrive_n(raw_empty(rs), (uint32_t)(4 * (RAW_KB - nreal)));
+          if (++rs == RS) {
+            rs = 0;
+            rphase ^= 1u;
           }
-          if (!FEW) {
-            const int j = jbase + kb, os = j % OS;
-            ok = ptx::mbar_wait_bounded(op_empty(os), (((uint32_t)(j / OS)) & 1u) ^ 1u, abort_flag, 2, WAIT_NS);
-            if (!ok) break;
-            ptx::mbar_arrive_expect_tx(op_full(os), (uint32_t)MT_LARGE * 128u);
-            ptx::tma_load_2d(smem_base + (uint32_t)b_off + (uint32_t)os * L::B_STAGE_BYTES, &tmap_x, op_full(os), kb * 128,
-                             im * MT_LARGE);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------ TMA producer: activation tiles (many-token form)
+    if (!FEW && lane == 0) {
+      bool ok = true;
+      int as = 0;
+      uint32_t aphase = 0;
+      for (int it = item_begin; it < item_end && ok; ++it) {
+        const int im = it % args.items_m;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = ptx::mbar_wait_bounded_fast(a_empty(as), aphase ^ 1u, abort_flag, 2, WAIT_NS);
+          if (!ok) break;
+          ptx::mbar_arrive_expect_tx(a_full(as), (uint32_t)C::B_STAGE_BYTES);
+          ptx::tma_load_2d(smem_base + (uint32_t)b_off + (uint32_t)as * C::B_STAGE_BYTES, &tmap_x, a_full(as), kb * 128, im * MT);
+          if (++as == AS) {
+            as = 0;
+            aphase ^= 1u;
           }
         }
       }
@@ -225,240 +327,216 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = true;
-      const uint64_t desc0 = ptx::make_smem_desc_kmajor(smem_base + (uint32_t)a_off, 1024, 2);
-      const uint32_t desc_hi = (uint32_t)(desc0 >> 32);
-      const uint32_t a_lo0 = (uint32_t)desc0;
-      const uint32_t b_lo0 = (uint32_t)ptx::make_smem_desc_kmajor(smem_base + (uint32_t)b_off, 1024, 2);
+      const uint64_t bdesc0 = ptx::make_smem_desc_kmajor(smem_base + (uint32_t)b_off, 1024, 2);
+      const uint32_t b_hi = (uint32_t)(bdesc0 >> 32);
+      const uint32_t b_lo0 = (uint32_t)bdesc0;
+      const uint32_t a_t0 = tmem_base + (uint32_t)C::A_COL0;
+      const uint32_t idesc = args.idesc;
+      const int kpg = args.kpg;
+      // few-token form: the window of group slot g starts (G - 1 - g) * mtok rows (of 128 bytes) into the buffer
+      const uint32_t b_row_step = FEW ? (uint32_t)args.mtok * 8u : 0u;
+      const uint32_t b_row_first = FEW ? (uint32_t)(args.G - 1) * b_row_step : 0u;
+      int as = 0, acc = 0;
+      uint32_t aphase = 0, acc_phase = 0;
+      uint32_t a_t = a_t0, b_lo = b_lo0;
       for (int it = item_begin; it < item_end && ok; ++it) {
-        const int jbase = (it - item_begin) * num_kb, pbase = (it - item_begin) * periods_per_item;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-          const int in_period = kb % kb_per_period;
-          const int pd = pbase + kb / kb_per_period, acc = pd & 1;
+        int in_period = 0, in_group = 0;
+        uint32_t b_row = b_row_first;
+        for (int kb = 0; kb < num_kb; ++kb) {
           if (in_period == 0) {
-            ok = ptx::mbar_wait_bounded(acc_empty(acc), (((uint32_t)(pd >> 1)) & 1u) ^ 1u, abort_flag, 3, WAIT_NS);
+            ok = ptx::mbar_wait_bounded_fast(acc_empty(acc), acc_phase ^ 1u, abort_flag, 3, WAIT_NS);
             if (!ok) break;
             ptx::tc_fence_after_sync();
           }
-          const int j = jbase + kb, os = j % OS;
-          ok = ptx::mbar_wait_bounded(op_full(os), ((uint32_t)(j / OS)) & 1u, abort_flag, 4, WAIT_NS);
+          ok = ptx::mbar_wait_bounded_fast(a_full(as), aphase, abort_flag, 4, WAIT_NS);
           if (!ok) break;
           ptx::tc_fence_after_sync();
-          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * args.n_mma);
-          const int g_local = in_period / args.kpg;
-          // few-token form: the window starts (G - 1 - g_local) * mtok rows into the buffer
-          const uint32_t b_row = FEW ? (uint32_t)((args.G - 1 - g_local) * args.mtok) : 0u;
-          const uint32_t a_lo = a_lo0 + (uint32_t)os * (A_STAGE_BYTES >> 4);
-          const uint32_t b_lo = b_lo0 + (uint32_t)os * (L::B_STAGE_BYTES >> 4) + b_row * (128u >> 4);
-          ptx::umma_kblock_f16(d_tmem, a_lo, b_lo, desc_hi, desc_hi, args.idesc, in_period != 0 ? 1u : 0u);
-          ptx::umma_commit(op_empty(os));
-          if (in_period == kb_per_period - 1 || kb == num_kb - 1) ptx::umma_commit(acc_full(acc));
+          ptx::umma_kblock_f16_ts(tmem_base + (uint32_t)(acc * N_MMA), a_t, b_lo + b_row, b_hi, idesc, in_period != 0 ? 1u : 0u);
+          ptx::umma_commit(a_empty(as));
+          if (++as == AS) {
+            as = 0;
+            aphase ^= 1u;
+            a_t = a_t0;
+            b_lo = b_lo0;
+          } else {
+            a_t += A_COLS;
+            b_lo += C::B_STAGE_BYTES >> 4;
+          }
+          if (++in_group == kpg) {
+            in_group = 0;
+            b_row -= b_row_step;
+          }
+          if (++in_period == kb_per_period || kb == num_kb - 1) {
+            ptx::umma_commit(acc_full(acc));
+            in_period = 0;
+            b_row = b_row_first;
+            if (++acc == NACC) {
+              acc = 0;
+              acc_phase ^= 1u;
+            }
+          }
         }
       }
     }
-  } else if (warp >= FIRST_DQ_WARP && warp < FIRST_EPI_WARP) {
-    // ------------------------------------------------------------ dequantisation teams
-    const int dq = warp - FIRST_DQ_WARP;          // 0..7
-    const int dtid = dq * 32 + lane;              // 0..255
-    const int team = dq >> 1;                     // converts k-block `team` of every raw stage
-    const int ttid = (dq & 1) * 32 + lane;        // 0..63 inside the team
+  } else if (warp >= C::FIRST_DQ && warp < C::FIRST_EPI) {
+    // ------------------------------------------------------------ dequantisation warps
+    const int dq = warp - C::FIRST_DQ;
+    const int quarter = warp & 3;                 // the TMEM lane quarter this warp may write (FIRST_DQ is a multiple of 4)
+    const int slot = dq >> 2;                     // 0..W-1
+    const int dtid = dq * 32 + lane;
+    const int row = 8 * (4 * (lane >> 3) + quarter) + (lane & 7);   // row of the work item held by this TMEM lane
     bool ok = true;
     int staged_chunk = -1;
     uint32_t sync_count = 0;
     const int mtok = args.mtok;
     const int live_row0 = (args.G - 1) * mtok;    // few-token form: first live row of the window buffer
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)C::A_COL0;
     for (int it = item_begin; it < item_end && ok; ++it) {
       const int in_ = it / args.items_m;
       const int row0 = in_ * args.rows_item;
       const int nrows = min(args.rows_item, args.N - row0);
-      const int rows8 = (nrows + 7) & ~7;         // tasks are laid out over whole 8-row groups
       if (in_ != staged_chunk) {
-        // zero points of this row chunk, transposed: zpT[g][n]
         if (!(ok = role_sync(dq_sync_bar, sync_count, 9))) break;  // everyone is done with the previous chunk's
-        const int total = nrows * args.gpr;
-        for (int i = dtid; i < total; i += DQ_WARPS * 32) {
-          const int n = i / args.gpr, g = i - n * args.gpr;
-          zpT[g * ZP_PITCH + n] = __ldg(args.zp + (size_t)(row0 + n) * args.gpr + g);
-        }
+        stage_meta<uint8_t, ZP_PITCH>(zpT, args.zp, row0, nrows, args.gpr, dtid, 4 * W * 32);
         if (!(ok = role_sync(dq_sync_bar, sync_count, 9))) break;
         staged_chunk = in_;
       }
+      const bool live = row < nrows;
       const int jbase = (it - item_begin) * num_kb, rbase = (it - item_begin) * raws_per_item;
-      for (int rsi = 0; rsi < raws_per_item && ok; ++rsi) {
-        const int r = rbase + rsi, rs = r % RS;
-        const int kb = rsi * RAW_KB + team;
-        const bool have = kb < num_kb;
-        // few-token form: this k-block's activations (global memory; requested before the waits)
-        uint4 xv[2];
-        if (FEW && have) {
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int c = ttid + TEAM_THREADS * u;   // 16-byte chunk: token c / 8, chunk c % 8
-            xv[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (c < mtok * 8 && (c >> 3) < args.M)
-              xv[u] = __ldg(reinterpret_cast<const uint4*>(args.x + ((size_t)(c >> 3) * args.K + (size_t)kb * KB + (c & 7) * 8) * 2));
-          }
+      int kb = slot - jbase % W;
+      if (kb < 0) kb += W;
+      for (; kb < num_kb; kb += W) {
+        const int j = jbase + kb, as = j % AS;
+        const uint32_t aphase = (uint32_t)(j / AS) & 1u;
+        const int r = rbase + kb / RAW_KB, rs = r % RS, sub = kb & (RAW_KB - 1);
+        if (!(ok = warp_wait(raw_full(rs), (uint32_t)(r / RS) & 1u, 6))) break;
+        // this lane's row: 32 bytes of nibbles = logical 16-byte chunks 2*sub and 2*sub+1 of the swizzled raw row
+        uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = w0;
+        if (live) {
+          const uint8_t* rrow = smem + (size_t)rs * RAW_STAGE_BYTES + row * 128;
+          w0 = *reinterpret_cast<const uint4*>(rrow + (((2 * sub) ^ (row & 7)) << 4));
+          w1 = *reinterpret_cast<const uint4*>(rrow + (((2 * sub + 1) ^ (row & 7)) << 4));
         }
-        if (lane == 0) ok = ptx::mbar_wait_bounded(raw_full(rs), ((uint32_t)(r / RS)) & 1u, abort_flag, 6, WAIT_NS);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        // a task = (row, half of the k-block): 16 bytes of nibbles -> 64 bytes of A.  Lanes of a quarter warp take
-        // consecutive rows of one half, which keeps the swizzled reads and writes free of bank conflicts.
-        constexpr int MAX_TASKS = 2 * TILE_ROWS / TEAM_THREADS;  // 4
-        uint4 wv[MAX_TASKS];
-        const uint8_t* rst = smem + (size_t)rs * RAW_STAGE_BYTES;
+        const uint32_t z = live ? zpT[(kb / args.kpg) * ZP_PITCH + row] : 0u;
+        const uint32_t negz = __byte_perm(z, 0xC3u, 0x4040);  // bf16x2 {-(128 + zp), -(128 + zp)}: 0xC300 | zp
+        if (!(ok = warp_wait(a_empty(as), aphase ^ 1u, 7))) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int t = 0; t < MAX_TASKS; ++t) {
-          const int task = ttid + TEAM_THREADS * t;
-          const int half = task >= rows8 ? 1 : 0, row = task - half * rows8;
-          wv[t] = make_uint4(0u, 0u, 0u, 0u);
-          if (have && task < 2 * rows8)
-            wv[t] = *reinterpret_cast<const uint4*>(rst + row * 128 + (((2 * team + half) ^ (row & 7)) << 4));
-        }
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(raw_empty(rs));   // this warp has read its part of the raw stage
-        if (!have) continue;
-        const int j = jbase + kb, os = j % OS;
-        const int g = kb / args.kpg;
-        if (lane == 0) ok = ptx::mbar_wait_bounded(op_empty(os), (((uint32_t)(j / OS)) & 1u) ^ 1u, abort_flag, 7, WAIT_NS);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        uint8_t* ast = smem + a_off + (size_t)os * A_STAGE_BYTES;
+        for (int h = 0; h < 2; ++h) {
+          uint32_t o[16];
 #pragma unroll
-        for (int t = 0; t < MAX_TASKS; ++t) {
-          const int task = ttid + TEAM_THREADS * t;
-          if (task < 2 * rows8) {
-            const int half = task >= rows8 ? 1 : 0, row = task - half * rows8;
-            const uint32_t z = zpT[g * ZP_PITCH + row];
-            const uint32_t negz = __byte_perm(z, 0xC3u, 0x4040);  // bf16x2 {-(128 + zp), -(128 + zp)}: 0xC300 | zp
-            const uint32_t ww[4] = {wv[t].x, wv[t].y, wv[t].z, wv[t].w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint32_t p[4];
-              dequant_word(ww[q], negz, p);
-              uint4 o;
-              if (FEW) {
-                o = make_uint4(p[0], p[1], p[2], p[3]);   // k order 0,4,1,5,2,6,3,7 (B is written in the same order)
-              } else {
-                o.x = __byte_perm(p[0], p[1], 0x5410);    // natural k order: B arrives by TMA
-                o.y = __byte_perm(p[2], p[3], 0x5410);
-                o.z = __byte_perm(p[0], p[1], 0x7632);
-                o.w = __byte_perm(p[2], p[3], 0x7632);
-              }
-              const int ch = half * 4 + q;   // logical 16-byte chunk of the A row
-              *reinterpret_cast<uint4*>(ast + row * 128 + ((ch ^ (row & 7)) << 4)) = o;
+          for (int q = 0; q < 4; ++q) {
+            uint32_t p[4];
+            dequant_word(ww[4 * h + q], negz, p);
+            if (FEW) {   // k order 0,4,1,5,2,6,3,7 inside every 8 (B is written in the same order)
+              o[4 * q + 0] = p[0];
+              o[4 * q + 1] = p[1];
+              o[4 * q + 2] = p[2];
+              o[4 * q + 3] = p[3];
+            } else {     // natural k order: B arrives by TMA
+              o[4 * q + 0] = __byte_perm(p[0], p[1], 0x5410);
+              o[4 * q + 1] = __byte_perm(p[2], p[3], 0x5410);
+              o[4 * q + 2] = __byte_perm(p[0], p[1], 0x7632);
+              o[4 * q + 3] = __byte_perm(p[2], p[3], 0x7632);
             }
           }
+          ptx::tmem_st_32x32b_x16(t_lane + (uint32_t)(as * A_COLS + 16 * h), o);
         }
-        if (FEW) {
-          uint8_t* bst = smem + b_off + (size_t)os * L::B_STAGE_BYTES;
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int c = ttid + TEAM_THREADS * u;
-            if (c < mtok * 8) {
-              const int rr = live_row0 + (c >> 3), ch = c & 7;
-              // the k order inside a 16-byte chunk follows the nibble-pair order of the A operand: 0,4,1,5,2,6,3,7
-              uint4 o;
-              o.x = __byte_perm(xv[u].x, xv[u].z, 0x5410);
-              o.y = __byte_perm(xv[u].x, xv[u].z, 0x7632);
-              o.z = __byte_perm(xv[u].y, xv[u].w, 0x5410);
-              o.w = __byte_perm(xv[u].y, xv[u].w, 0x7632);
-              *reinterpret_cast<uint4*>(bst + rr * 128 + ((ch ^ (rr & 7)) << 4)) = o;
-            }
+        if (FEW && quarter == 0) {
+          // this k-block's activations from the resident copy into the live rows of the window buffer
+          uint8_t* bst = smem + b_off + (size_t)as * C::B_STAGE_BYTES;
+          if (lane < mtok * 8) {
+            const int m = lane >> 3, ch = lane & 7, rr = live_row0 + m;
+            const uint4 v = *reinterpret_cast<const uint4*>(xs + ((size_t)m * args.K + (size_t)kb * KB + ch * 8) * 2);
+            *reinterpret_cast<uint4*>(bst + rr * 128 + ((ch ^ (rr & 7)) << 4)) = v;
           }
+          ptx::fence_proxy_async_smem();
         }
-        ptx::fence_proxy_async_smem();
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(op_full(os));
+        if (lane == 0) {
+          ptx::mbar_arrive(raw_empty(rs));   // after the values were used: the reads are complete for certain
+          ptx::mbar_arrive(a_full(as));
+        }
       }
     }
-  } else if (warp >= FIRST_EPI_WARP) {
+  } else if (warp >= C::FIRST_EPI) {
     // ------------------------------------------------------------ epilogue warps
-    const int e = warp - FIRST_EPI_WARP;       // 0..7
+    const int e = warp - C::FIRST_EPI;
     const int quarter = warp & 3;              // TMEM lanes 32*quarter .. +31 (a warp may only touch its own quarter)
-    const int chalf = e >> 2;                  // which half of the accumulator columns
+    const int part = e >> 2;                   // which slice of the accumulator columns
     const int etid = e * 32 + lane;
-    const int n_loc = quarter * 32 + lane;     // output channel inside the work item
-    constexpr int MY_COLS = FEW ? 16 : MT_LARGE / 2;
-    const bool active_warp = FEW ? (chalf == 0) : true;   // few-token form: one warp per quarter takes all 16 columns
+    const int row = 8 * (4 * (lane >> 3) + quarter) + (lane & 7);
+    constexpr int MY_COLS = C::MY_COLS;
     bool ok = true;
     int staged_chunk = -1;
     uint32_t sync_count = 0;
     const int mtok = args.mtok;
-    const int mtok_shift = 31 - __clz(mtok);   // mtok is a power of two
+    const int mtok_shift = FEW ? 31 - __clz(mtok) : 0;   // mtok is a power of two
+    int acc = 0;
+    uint32_t acc_phase = 0;
     for (int it = item_begin; it < item_end && ok; ++it) {
       const int in_ = it / args.items_m, im = it - in_ * args.items_m;
       const int row0 = in_ * args.rows_item;
       const int nrows = min(args.rows_item, args.N - row0);
       if (in_ != staged_chunk) {
         if (!(ok = role_sync(epi_sync_bar, sync_count, 10))) break;
-        const int total = nrows * args.gpr;
-        for (int i = etid; i < total; i += EPI_WARPS * 32) {
-          const int n = i / args.gpr, g = i - n * args.gpr;
-          scaleT[g * SCALE_PITCH + n] = __ldg(args.scale + (size_t)(row0 + n) * args.gpr + g);
-        }
+        stage_meta<uint16_t, SCALE_PITCH>(scaleT, args.scale, row0, nrows, args.gpr, etid, E * 32);
         if (!(ok = role_sync(epi_sync_bar, sync_count, 10))) break;
         staged_chunk = in_;
       }
       float running[MY_COLS];
 #pragma unroll
       for (int c = 0; c < MY_COLS; ++c) running[c] = 0.f;
-      const bool live = n_loc < nrows;
-      const int n_safe = live ? n_loc : 0;
-      const int pbase = (it - item_begin) * periods_per_item;
+      const bool live = row < nrows;
+      const int n_safe = live ? row : 0;
       for (int pi = 0; pi < periods_per_item && ok; ++pi) {
-        const int pd = pbase + pi, acc = pd & 1;
-        if (lane == 0) ok = ptx::mbar_wait_bounded(acc_full(acc), ((uint32_t)(pd >> 1)) & 1u, abort_flag, 8, WAIT_NS);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
+        if (!(ok = warp_wait(acc_full(acc), acc_phase, 8))) break;
         ptx::tc_fence_after_sync();
-        const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * args.n_mma) +
-                                (FEW ? 0u : (uint32_t)(chalf * MY_COLS));
+        const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * N_MMA + part * MY_COLS);
         const int g0 = pi * args.G;
-        if (FEW) {
-          uint32_t r[16];
+        float s;
+        if (!FEW) s = __uint_as_float((uint32_t)scaleT[min(g0, args.gpr - 1) * SCALE_PITCH + n_safe] << 16);
 #pragma unroll
-          for (int c = 0; c < 16; ++c) r[c] = 0u;
-          if (active_warp) {
-            ptx::tmem_ld_32x32b_x16(t_addr, r);
-            ptx::tmem_ld_wait_16(r);
+        for (int c0 = 0; c0 < MY_COLS / 16; ++c0) {
+          uint32_t r[16];
+          ptx::tmem_ld_32x32b_x16(t_addr + (uint32_t)(c0 * 16), r);
+          ptx::tmem_ld_wait_16(r);
+          if (c0 == MY_COLS / 16 - 1) {   // the last columns are in registers: the buffer goes back before the arithmetic
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(acc_empty(acc));
           }
-          ptx::tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(acc_empty(acc));
-          if (active_warp) {
+          if (FEW) {
             // column c = g_local * mtok + token; running[] stays indexed by column so that every index is a constant
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
               int g = g0 + (c >> mtok_shift);
               if (g >= args.gpr) g = args.gpr - 1;   // columns of groups past K hold zeros
-              const float s = __uint_as_float((uint32_t)scaleT[g * SCALE_PITCH + n_safe] << 16);
-              running[c] = fmaf(s, __uint_as_float(r[c]), running[c]);
+              const float sg = __uint_as_float((uint32_t)scaleT[g * SCALE_PITCH + n_safe] << 16);
+              running[c] = fmaf(sg, __uint_as_float(r[c]), running[c]);
             }
-          }
-        } else {
-          const float s = __uint_as_float((uint32_t)scaleT[min(g0, args.gpr - 1) * SCALE_PITCH + n_safe] << 16);
+          } else {
 #pragma unroll
-          for (int c0 = 0; c0 < MY_COLS; c0 += 16) {
-            uint32_t r[16];
-            ptx::tmem_ld_32x32b_x16(t_addr + (uint32_t)c0, r);
-            ptx::tmem_ld_wait_16(r);
-#pragma unroll
-            for (int c = 0; c < 16; ++c) running[c0 + c] = fmaf(s, __uint_as_float(r[c]), running[c0 + c]);
+            for (int c = 0; c < 16; ++c) running[c0 * 16 + c] = fmaf(s, __uint_as_float(r[c]), running[c0 * 16 + c]);
           }
-          ptx::tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(acc_empty(acc));
+        }
+        if (++acc == NACC) {
+          acc = 0;
+          acc_phase ^= 1u;
         }
       }
       if (!ok) break;
-      // ---- store: y[m][row0 + n_loc] = bf16(sum + bias)
-      if (live && active_warp) {
-        const int n = row0 + n_loc;
+      // ---- store: y[m][row0 + row] = bf16(sum + bias)
+      if (live) {
+        const int n = row0 + row;
         const float b = args.bias ? args.bias[n] : 0.f;
         if (FEW) {
           // fold the G group slots of each token: column c holds token c & (mtok - 1)
 #pragma unroll
-          for (int m = 0; m < 16; ++m) {
+          for (int m = 0; m < 4; ++m) {
             if (m < mtok && m < args.M) {
               float v = 0.f;
 #pragma unroll
@@ -468,7 +546,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             }
           }
         } else {
-          const int m0 = im * MT_LARGE + chalf * MY_COLS;
+          const int m0 = im * MT + part * MY_COLS;
 #pragma unroll
           for (int c = 0; c < MY_COLS; ++c) {
             const int m = m0 + c;
@@ -484,15 +562,22 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, (uint32_t)tmem_cols);
+    ptx::tmem_dealloc(tmem_base, (uint32_t)TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_flag != 0 && args.status != nullptr) atomicCAS(args.status, 0, *abort_flag);
 }
 
-template <int MT_LARGE>
-int launch_umma(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaArgs& a, int grid, cudaStream_t stream) {
-  const int smem = Smem<MT_LARGE>::total(a.raw_stages, a.op_stages, a.gpr);
-  auto kfn = a16_w4_umma_kernel<MT_LARGE>;
+template <int MT>
+int launch_umma(const CUtensorMap& tw, const CUtensorMap& tx, UmmaArgs a, int grid, cudaStream_t stream) {
+  using C = Cfg<MT>;
+  const int x_bytes = MT == 0 ? a.mtok * a.K * 2 : 0;
+  // raw ring: as deep as shared memory allows (each stage carries 256 k of every row in flight), at most 8
+  a.raw_stages = MAX_RAW;
+  while (a.raw_stages > 2 && C::total(a.raw_stages, a.gpr, x_bytes) > 227 * 1024) --a.raw_stages;
+  const int smem = C::total(a.raw_stages, a.gpr, x_bytes);
+  if (smem > 227 * 1024) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 tensor-core kernel: shared memory does not hold two raw stages");
+  a.idesc = ptx::make_idesc(1u, 1u, 1u, (uint32_t)TILE_ROWS, (uint32_t)C::N_MMA);
+  auto kfn = a16_w4_umma_kernel<MT>;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)grid);
@@ -508,6 +593,389 @@ int launch_umma(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaArgs& a,
   return B200Q_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Few-token form (M <= 4): the kernel is bound by streaming and converting the weights, and a single MMA-issuing
+// thread cannot keep up with one small MMA every ~28 cycles next to two dozen busy warps.  So there is no central
+// issuer: the dequantisation warps form FW teams of four (one warp per TMEM lane quarter); team t owns the k-blocks
+// j with j mod FW == t, two TMEM stages of A, two window buffers of B and ITS OWN 16 accumulator columns.  When the
+// four quarters of a k-block have stored their rows, the team's quarter-0 warp issues its four MMAs and commits them.
+// MMAs of different teams never touch the same accumulator columns, so their order does not matter; the epilogue adds
+// the FW column sets of a period before it applies the group scales.
+struct FewCfg {
+  static constexpr int FW = 5;                       // teams
+  static constexpr int E = 4;                        // epilogue warps, one per lane quarter
+  static constexpr int NTHREADS = (4 + 4 * FW + E) * 32;   // 896
+  static constexpr int AS = 2 * FW;                  // A stages in TMEM, B window buffers in shared memory
+  static constexpr int ACC_COLS = FW * 16;           // accumulator columns per buffer
+  static constexpr int A_COL0 = TMEM_COLS - AS * A_COLS;
+  static constexpr int B_STAGE_BYTES = 32 * 128;
+  static constexpr int FIRST_DQ = 4, FIRST_EPI = 4 + 4 * FW;
+  static_assert(2 * ACC_COLS <= A_COL0, "accumulators and A stages share 512 columns");
+  static constexpr int NUM_BARS = 2 * MAX_RAW + 2 * AS + 4 + 2;
+  __host__ __device__ static int b_off(int rs) { return rs * RAW_STAGE_BYTES; }
+  __host__ __device__ static int bar_off(int rs) { return b_off(rs) + AS * B_STAGE_BYTES; }
+  __host__ __device__ static int misc_off(int rs) { return bar_off(rs) + NUM_BARS * 8; }
+  __host__ __device__ static int meta_off(int rs) { return (misc_off(rs) + 16 + 127) & ~127; }
+  __host__ __device__ static int x_off(int rs, int gpr) { return meta_off(rs) + ((gpr * (SCALE_PITCH * 2 + ZP_PITCH) + 15) & ~15); }
+  __host__ __device__ static int total(int rs, int gpr, int x_bytes) { return x_off(rs, gpr) + x_bytes + 1024; }
+};
+
+__global__ void __launch_bounds__(FewCfg::NTHREADS, 1)
+a16_w4_umma_few_kernel(const __grid_constant__ CUtensorMap tmap_w, const UmmaArgs args) {
+  using C = FewCfg;
+  constexpr int FW = C::FW, E = C::E, AS = C::AS;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int RS = args.raw_stages;              // a power of two
+  const int rs_shift = 31 - __clz(RS);
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const int b_off = C::b_off(RS), misc_off = C::misc_off(RS), meta_off = C::meta_off(RS);
+  const uint32_t bar_base = smem_base + (uint32_t)C::bar_off(RS);
+  auto raw_full = [&](int s) { return bar_base + 8u * s; };
+  auto raw_empty = [&](int s) { return bar_base + 8u * (MAX_RAW + s); };
+  auto a_ready = [&](int s) { return bar_base + 8u * (2 * MAX_RAW + s); };
+  auto a_free = [&](int s) { return bar_base + 8u * (2 * MAX_RAW + AS + s); };
+  auto acc_full = [&](int a) { return bar_base + 8u * (2 * MAX_RAW + 2 * AS + a); };
+  auto acc_empty = [&](int a) { return bar_base + 8u * (2 * MAX_RAW + 2 * AS + 2 + a); };
+  const uint32_t dq_sync_bar = bar_base + 8u * (2 * MAX_RAW + 2 * AS + 4), epi_sync_bar = dq_sync_bar + 8u;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + misc_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + misc_off + 4);
+  uint16_t* scaleT = reinterpret_cast<uint16_t*>(smem + meta_off);
+  uint8_t* zpT = smem + meta_off + args.gpr * SCALE_PITCH * 2;
+  uint8_t* xs = smem + C::x_off(RS, args.gpr);   // xs[m][K] bf16, 16-byte pieces in the nibble-pair order of A
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  auto role_sync = [&](uint32_t bar, uint32_t& count, int where) -> bool {
+    __syncwarp();
+    bool ok_ = true;
+    if (lane == 0) {
+      ptx::mbar_arrive(bar);
+      ok_ = ptx::mbar_wait_bounded_fast(bar, count & 1u, abort_flag, where, WAIT_NS);
+    }
+    ++count;
+    ok_ = __shfl_sync(0xffffffffu, ok_, 0);
+    return ok_;
+  };
+  // every lane of the warp runs the same wait (the barrier test is one warp instruction either way)
+  auto warp_wait = [&](uint32_t bar, uint32_t parity, int where) -> bool {
+    return ptx::mbar_wait_bounded_fast(bar, parity, abort_flag, where, WAIT_NS);
+  };
+
+  ptx::griddep_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < RS; ++s) {
+      ptx::mbar_init(raw_full(s), 1);
+      ptx::mbar_init(raw_empty(s), 4 * RAW_KB);   // one arrival per (k-block, lane quarter)
+    }
+    for (int s = 0; s < AS; ++s) {
+      ptx::mbar_init(a_ready(s), 4);              // the four quarters of the team
+      ptx::mbar_init(a_free(s), 1);               // the team's MMAs have read the stage
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(acc_full(a), FW);            // every team closes every period
+      ptx::mbar_init(acc_empty(a), E);
+    }
+    ptx::mbar_init(dq_sync_bar, 4 * FW);
+    ptx::mbar_init(epi_sync_bar, E);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+    ptx::prefetch_tensormap(&tmap_w);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_ptr_smem), (uint32_t)TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::griddep_wait();
+  {
+    // the window buffers start as zeros; only their live rows are ever rewritten
+    uint4* b = reinterpret_cast<uint4*>(smem + b_off);
+    for (int i = threadIdx.x; i < AS * C::B_STAGE_BYTES / 16; i += C::NTHREADS) b[i] = make_uint4(0u, 0u, 0u, 0u);
+    // activations: rows past M are zeros
+    const int pieces = args.mtok * (args.K >> 3);
+    for (int i = threadIdx.x; i < pieces; i += C::NTHREADS) {
+      const int m = i / (args.K >> 3), c = i - m * (args.K >> 3);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (m < args.M) v = __ldg(reinterpret_cast<const uint4*>(args.x + ((size_t)m * args.K + (size_t)c * 8) * 2));
+      uint4 o;   // k order 0,4,1,5,2,6,3,7
+      o.x = __byte_perm(v.x, v.z, 0x5410);
+      o.y = __byte_perm(v.x, v.z, 0x7632);
+      o.z = __byte_perm(v.y, v.w, 0x5410);
+      o.w = __byte_perm(v.y, v.w, 0x7632);
+      reinterpret_cast<uint4*>(xs)[i] = o;
+    }
+    ptx::fence_proxy_async_smem();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int items = args.items_n;
+  const int item_begin = (int)((long long)blockIdx.x * items / gridDim.x);
+  const int item_end = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
+  const int num_kb = args.num_kb;
+  const int raws_per_item = (num_kb + RAW_KB - 1) / RAW_KB;
+  const int kb_per_period = args.G * args.kpg;
+  const int periods_per_item = (num_kb + kb_per_period - 1) / kb_per_period;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer: packed weights
+    if (lane == 0) {
+      bool ok = true;
+      int rs = 0;
+      uint32_t rphase = 0;
+      for (int it = item_begin; it < item_end && ok; ++it) {
+        const int row0 = it * args.rows_item;
+        const int nrows = min(args.rows_item, args.N - row0);
+        const int boxes = (nrows + 15) >> 4;
+        for (int rsi = 0; rsi < raws_per_item; ++rsi) {
+          ok = ptx::mbar_wait_bounded_fast(raw_empty(rs), rphase ^ 1u, abort_flag, 1, WAIT_NS);
+          if (!ok) break;
+          ptx::mbar_arrive_expect_tx(raw_full(rs), (uint32_t)boxes * 16u * 128u);
+          const uint32_t dst = smem_base + (uint32_t)rs * RAW_STAGE_BYTES;
+          for (int b = 0; b < boxes; ++b) ptx::tma_load_2d(dst + (uint32_t)b * 2048u, &tmap_w, raw_full(rs), rsi * 128, row0 + b * 16);
+          const int nreal = min(RAW_KB, num_kb - rsi * RAW_KB);
+          if (nreal < RAW_KB) ptx::mbar_arrive_n(raw_empty(rs), (uint32_t)(4 * (RAW_KB - nreal)));
+          if (++rs == RS) {
+            rs = 0;
+            rphase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp >= C::FIRST_DQ && warp < C::FIRST_EPI) {
+    // ------------------------------------------------------------ dequantisation teams (quarter 0 also issues the MMAs)
+    const int dq = warp - C::FIRST_DQ;
+    const int quarter = warp & 3;
+    const int team = dq >> 2;
+    const int dtid = dq * 32 + lane;
+    const int row = 8 * (4 * (lane >> 3) + quarter) + (lane & 7);   // row of the work item held by this TMEM lane
+    bool ok = true;
+    int staged_item = -1;
+    uint32_t sync_count = 0;
+    const int mtok = args.mtok;
+    const int live_row0 = (args.G - 1) * mtok;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)C::A_COL0;
+    const uint64_t bdesc0 = ptx::make_smem_desc_kmajor(smem_base + (uint32_t)b_off, 1024, 2);
+    const uint32_t b_hi = (uint32_t)(bdesc0 >> 32), b_lo0 = (uint32_t)bdesc0;
+    const uint32_t idesc = args.idesc;
+    const int kpg = args.kpg;
+    const int pshift = (kb_per_period & (kb_per_period - 1)) == 0 ? 31 - __clz(kb_per_period) : -1;
+    uint32_t cnt = 0;   // k-blocks this team has handled: stage 2 * team + (cnt & 1), phase (cnt >> 1) & 1
+    for (int it = item_begin; it < item_end && ok; ++it) {
+      const int row0 = it * args.rows_item;
+      const int nrows = min(args.rows_item, args.N - row0);
+      if (it != staged_item) {
+        if (!(ok = role_sync(dq_sync_bar, sync_count, 9))) break;  // everyone is done with the previous item's
+        stage_meta<uint8_t, ZP_PITCH>(zpT, args.zp, row0, nrows, args.gpr, dtid, 4 * FW * 32);
+        if (!(ok = role_sync(dq_sync_bar, sync_count, 9))) break;
+        staged_item = it;
+      }
+      const bool live = row < nrows;
+      const int jbase = (it - item_begin) * num_kb, rbase = (it - item_begin) * raws_per_item;
+      const int pbase = (it - item_begin) * periods_per_item;
+      int kb = team - jbase % FW;
+      if (kb < 0) kb += FW;
+      int pcur = -1;   // issuer: the last period this team has entered
+      // issuer: a period in which the team has no k-block still needs its arrival (after the buffer's previous use)
+      auto close_empty_periods = [&](int from, int to) -> bool {
+        for (int p = from; p < to; ++p) {
+          const int pd = pbase + p, buf = pd & 1;
+          if (!warp_wait(acc_empty(buf), (((uint32_t)(pd >> 1)) & 1u) ^ 1u, 3)) return false;
+          if (lane == 0) ptx::mbar_arrive(acc_full(buf));
+        }
+        return true;
+      };
+      for (; kb < num_kb && ok; kb += FW, ++cnt) {
+        const int stage = 2 * team + (int)(cnt & 1u);
+        const uint32_t sphase = (cnt >> 1) & 1u;
+        const int r = rbase + (kb >> 2), rs = r & (RS - 1), sub = kb & (RAW_KB - 1);
+        if (!(ok = warp_wait(raw_full(rs), (uint32_t)(r >> rs_shift) & 1u, 6))) break;
+        uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = w0;
+        if (live) {
+          const uint8_t* rrow = smem + (size_t)rs * RAW_STAGE_BYTES + row * 128;
+          w0 = *reinterpret_cast<const uint4*>(rrow + (((2 * sub) ^ (row & 7)) << 4));
+          w1 = *reinterpret_cast<const uint4*>(rrow + (((2 * sub + 1) ^ (row & 7)) << 4));
+        }
+        const int g = kpg == 1 ? kb : kb / kpg;
+        const uint32_t z = live ? zpT[g * ZP_PITCH + row] : 0u;
+        const uint32_t negz = __byte_perm(z, 0xC3u, 0x4040);  // bf16x2 {-(128 + zp), -(128 + zp)}: 0xC300 | zp
+        if (!(ok = warp_wait(a_free(stage), sphase ^ 1u, 7))) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t o[16];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t p[4];
+            dequant_word(ww[4 * h + q], negz, p);   // k order 0,4,1,5,2,6,3,7 inside every 8, like B
+            o[4 * q + 0] = p[0];
+            o[4 * q + 1] = p[1];
+            o[4 * q + 2] = p[2];
+            o[4 * q + 3] = p[3];
+          }
+          ptx::tmem_st_32x32b_x16(t_lane + (uint32_t)(stage * A_COLS + 16 * h), o);
+        }
+        if (quarter == 0) {
+          // this k-block's activations from the resident copy into the live rows of the team's window buffer
+          uint8_t* bst = smem + b_off + (size_t)stage * C::B_STAGE_BYTES;
+          if (lane < mtok * 8) {
+            const int m = lane >> 3, ch = lane & 7, rr = live_row0 + m;
+            const uint4 v = *reinterpret_cast<const uint4*>(xs + ((size_t)m * args.K + (size_t)kb * KB + ch * 8) * 2);
+            *reinterpret_cast<uint4*>(bst + rr * 128 + ((ch ^ (rr & 7)) << 4)) = v;
+          }
+          ptx::fence_proxy_async_smem();
+        }
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::mbar_arrive(raw_empty(rs));   // after the values were used: the reads are complete for certain
+          ptx::mbar_arrive(a_ready(stage));
+        }
+        if (quarter == 0) {
+          // ---- issue this k-block's MMAs into the team's accumulator columns
+          const int pi = pshift >= 0 ? (kb >> pshift) : kb / kb_per_period, pd = pbase + pi, buf = pd & 1;
+          bool first = false;
+          if (pi != pcur) {
+            if (!(ok = close_empty_periods(pcur + 1, pi))) break;
+            if (!(ok = warp_wait(acc_empty(buf), (((uint32_t)(pd >> 1)) & 1u) ^ 1u, 3))) break;
+            first = true;
+            pcur = pi;
+          }
+          if (!(ok = warp_wait(a_ready(stage), sphase, 4))) break;
+          ptx::tc_fence_after_sync();
+          if (lane == 0) {
+            const int g_local = g - pi * args.G;
+            const uint32_t b_lo = b_lo0 + (uint32_t)stage * (C::B_STAGE_BYTES >> 4) + (uint32_t)((args.G - 1 - g_local) * mtok) * 8u;
+            ptx::umma_kblock_f16_ts(tmem_base + (uint32_t)(buf * C::ACC_COLS + team * 16), tmem_base + (uint32_t)(C::A_COL0 + stage * A_COLS),
+                                    b_lo, b_hi, idesc, first ? 0u : 1u);
+            ptx::umma_commit(a_free(stage));
+            // the team's last k-block of this period: its part of the accumulator is complete when these MMAs are
+            if (kb + FW >= num_kb || kb + FW >= (pi + 1) * kb_per_period) ptx::umma_commit(acc_full(buf));
+          }
+          __syncwarp();
+        }
+      }
+      if (ok && quarter == 0) ok = close_empty_periods(pcur + 1, periods_per_item);
+    }
+  } else if (warp >= C::FIRST_EPI) {
+    // ------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;
+    const int etid = (warp - C::FIRST_EPI) * 32 + lane;
+    const int row = 8 * (4 * (lane >> 3) + quarter) + (lane & 7);
+    bool ok = true;
+    int staged_item = -1;
+    uint32_t sync_count = 0;
+    const int mtok = args.mtok;
+    const int mtok_shift = 31 - __clz(mtok);   // mtok is a power of two
+    for (int it = item_begin; it < item_end && ok; ++it) {
+      const int row0 = it * args.rows_item;
+      const int nrows = min(args.rows_item, args.N - row0);
+      if (it != staged_item) {
+        if (!(ok = role_sync(epi_sync_bar, sync_count, 10))) break;
+        stage_meta<uint16_t, SCALE_PITCH>(scaleT, args.scale, row0, nrows, args.gpr, etid, E * 32);
+        if (!(ok = role_sync(epi_sync_bar, sync_count, 10))) break;
+        staged_item = it;
+      }
+      float running[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) running[c] = 0.f;
+      const bool live = row < nrows;
+      const int n_safe = live ? row : 0;
+      const int pbase = (it - item_begin) * periods_per_item;
+      for (int pi = 0; pi < periods_per_item && ok; ++pi) {
+        const int pd = pbase + pi, buf = pd & 1;
+        if (!(ok = warp_wait(acc_full(buf), ((uint32_t)(pd >> 1)) & 1u, 8))) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * C::ACC_COLS);
+        float sum[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) sum[c] = 0.f;
+        // the column sets of the teams that had a k-block in this period (a set without one holds old values)
+        const int lo = pi * kb_per_period, hi = min(lo + kb_per_period, num_kb);
+        const int jlo = ((it - item_begin) * num_kb + lo) % FW;   // team of the period's first k-block
+#pragma unroll
+        for (int t = 0; t < FW; ++t) {
+          int d = t - jlo;
+          if (d < 0) d += FW;
+          if (lo + d < hi) {   // same for every thread
+            uint32_t r[16];
+            ptx::tmem_ld_32x32b_x16(t_addr + (uint32_t)(t * 16), r);
+            ptx::tmem_ld_wait_16(r);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) sum[c] += __uint_as_float(r[c]);
+          }
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(acc_empty(buf));
+        // column c = g_local * mtok + token; running[] stays indexed by column so that every index is a constant
+        const int g0 = pi * args.G;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          int g = g0 + (c >> mtok_shift);
+          if (g >= args.gpr) g = args.gpr - 1;   // columns of groups past K hold zeros
+          const float s = __uint_as_float((uint32_t)scaleT[g * SCALE_PITCH + n_safe] << 16);
+          running[c] = fmaf(s, sum[c], running[c]);
+        }
+      }
+      if (!ok) break;
+      if (live) {
+        const int n = row0 + row;
+        const float b = args.bias ? args.bias[n] : 0.f;
+        // fold the G group slots of each token: column c holds token c & (mtok - 1)
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          if (m < mtok && m < args.M) {
+            float v = 0.f;
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              if ((c & (mtok - 1)) == m) v += running[c];
+            args.y[(size_t)m * args.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(v + b));
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, (uint32_t)TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0 && args.status != nullptr) atomicCAS(args.status, 0, *abort_flag);
+}
+
+int launch_umma_few(const CUtensorMap& tw, UmmaArgs a, int grid, cudaStream_t stream) {
+  using C = FewCfg;
+  const int x_bytes = a.mtok * a.K * 2;
+  a.raw_stages = MAX_RAW;   // a power of two: 8, 4 or 2
+  while (a.raw_stages > 2 && C::total(a.raw_stages, a.gpr, x_bytes) > 227 * 1024) a.raw_stages >>= 1;
+  const int smem = C::total(a.raw_stages, a.gpr, x_bytes);
+  if (smem > 227 * 1024) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 tensor-core kernel: shared memory does not hold two raw stages");
+  a.idesc = ptx::make_idesc(1u, 1u, 1u, (uint32_t)TILE_ROWS, 16u);
+  auto kfn = a16_w4_umma_few_kernel;
+  CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(C::NTHREADS);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, kfn, tw, a));
+  return B200Q_OK;
+}
+
 }  // namespace
 
 int a16_w4_umma_supported(long long M, int N, int K, int group, const char** why) {
@@ -517,7 +985,7 @@ int a16_w4_umma_supported(long long M, int N, int K, int group, const char** why
   else if (K % KB != 0) w = "K must be a multiple of 64";
   else if (group < KB || group % KB != 0 || K % group != 0) w = "the group size must be a multiple of 64 that divides K";
   else if ((K / 2) % 16 != 0) w = "the weight row pitch must be a multiple of 16 bytes";
-  else if (Smem<128>::total(2, 2, K / group) > 227 * 1024) w = "the scales and zero points of one 128-row tile do not fit in shared memory";
+  else if (Cfg<32>::total(2, K / group, 0) > 227 * 1024) w = "the scales and zero points of one 128-row tile do not fit in shared memory";
   if (why) *why = w;
   return w == nullptr;
 }
@@ -545,19 +1013,22 @@ int a16_w4_umma_launch(const void* x, const void* wq, const void* scale, const v
   a.num_kb = K / KB;
   a.kpg = group / KB;
   a.status = status;
-  const bool few = M <= 16;
-  int mt_large = 0;
+  // few-token form: up to 4 tokens whose activations fit in shared memory next to two raw stages
+  const int mtok_few = M <= 1 ? 1 : M <= 2 ? 2 : 4;
+  const bool few = M <= 4 && FewCfg::total(2, a.gpr, mtok_few * K * 2) <= 227 * 1024;
+  int mt = 0;
   if (few) {
-    a.mtok = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16;
+    a.mtok = mtok_few;
     a.G = 16 / a.mtok;
-    a.n_mma = 16;
     a.items_m = 1;
   } else {
-    mt_large = M <= 32 ? 32 : M <= 64 ? 64 : 128;
-    a.mtok = mt_large;
+    mt = M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    // many groups per row leave less shared memory for the activation ring: narrower token tiles then
+    if (mt == 128 && Cfg<128>::total(2, a.gpr, 0) > 227 * 1024) mt = 64;
+    if (mt == 64 && Cfg<64>::total(2, a.gpr, 0) > 227 * 1024) mt = 32;
+    a.mtok = mt;
     a.G = 1;
-    a.n_mma = mt_large;
-    a.items_m = (int)((M + mt_large - 1) / mt_large);
+    a.items_m = (int)((M + mt - 1) / mt);
   }
   // rows per work item: full 128-row tiles when they fill the SMs twice over, else row chunks (multiples of 16) sized
   // so that every SM gets one
@@ -572,26 +1043,8 @@ int a16_w4_umma_launch(const void* x, const void* wq, const void* scale, const v
     a.rows_item = (int)per;
   }
   a.items_n = (N + a.rows_item - 1) / a.rows_item;
-  a.idesc = ptx::make_idesc(1u, 1u, 1u, (uint32_t)TILE_ROWS, (uint32_t)a.n_mma);
   const long long items = (long long)a.items_n * a.items_m;
   const int grid = (int)(items < sms ? items : sms);
-
-  // ring depths: as deep as shared memory allows next to the scales and zero points (at most 4 raw stages of 256 k,
-  // at most 6 k-blocks of operands)
-  a.raw_stages = 4;
-  a.op_stages = few ? 6 : 4;
-  auto fits = [&](int rs, int os) {
-    const int t = few ? Smem<0>::total(rs, os, a.gpr)
-                      : mt_large == 32 ? Smem<32>::total(rs, os, a.gpr)
-                                       : mt_large == 64 ? Smem<64>::total(rs, os, a.gpr) : Smem<128>::total(rs, os, a.gpr);
-    return t <= 227 * 1024;
-  };
-  while (!fits(a.raw_stages, a.op_stages)) {
-    if (a.op_stages > 4) --a.op_stages;
-    else if (a.raw_stages > 2) --a.raw_stages;
-    else if (a.op_stages > 2) --a.op_stages;
-    else return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 tensor-core kernel: shared memory does not hold two stages");
-  }
 
   CUtensorMap tw, tx;
   {
@@ -600,18 +1053,15 @@ int a16_w4_umma_launch(const void* x, const void* wq, const void* scale, const v
     const uint32_t box[2] = {128u, 16u};
     B200Q_TRY(make_tmap_u8(&tw, wq, 2, dims, strides, box));
   }
-  if (few) {
-    tx = tw;  // not used by the few-token form
-    return launch_umma<0>(tw, tx, a, grid, stream);
-  }
+  if (few) return launch_umma_few(tw, a, grid, stream);
   {
     const uint64_t dims[2] = {(uint64_t)K * 2, (uint64_t)M};
     const uint64_t strides[1] = {(uint64_t)K * 2};
-    const uint32_t box[2] = {128u, (uint32_t)mt_large};
+    const uint32_t box[2] = {128u, (uint32_t)mt};
     B200Q_TRY(make_tmap_u8(&tx, x, 2, dims, strides, box));
   }
-  if (mt_large == 32) return launch_umma<32>(tw, tx, a, grid, stream);
-  if (mt_large == 64) return launch_umma<64>(tw, tx, a, grid, stream);
+  if (mt == 32) return launch_umma<32>(tw, tx, a, grid, stream);
+  if (mt == 64) return launch_umma<64>(tw, tx, a, grid, stream);
   return launch_umma<128>(tw, tx, a, grid, stream);
 }
 

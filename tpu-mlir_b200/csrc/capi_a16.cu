@@ -114,15 +114,29 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
   // two consecutive k of one row
   if (group < 1 || K % group != 0 || (K & 1)) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: K must be even and a multiple of the group size");
   const int route = g_a16_route;
-  const bool umma_ok = a16_w4_umma_supported(M > 0 ? M : 1, N, K, group, nullptr) != 0;
-  const bool simt_ok = M <= 2 && a16_w4_gemv_supported((int)(M > 0 ? M : 1), N, K, group, nullptr) != 0;
   if (M == 0) return B200Q_OK;
-  if (route == 2 || (route == 0 && umma_ok && !simt_ok)) {
-    if (!umma_ok) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: the tensor-core kernel needs K and the group size to be multiples of 64");
-    return a16_w4_umma_launch(x, wq, scale, zp, bias, y, M, N, K, group, status, s);
+  const bool umma_ok = a16_w4_umma_supported(M, N, K, group, nullptr) != 0;
+  const bool gemv_ok = M <= 8 && a16_w4_gemv_supported((int)M, N, K, group, nullptr) != 0;
+  // the one-time bf16 copy + bf16 GEMM: only through a handle (which owns the copy), only for prefill-sized M
+  const bool resident_ok = M > 8 && w16 && K % 8 == 0 && group % 8 == 0 && M <= 0x7fffffffLL;
+  bool use_umma = false, use_resident = false;
+  switch (route) {
+    case 1: break;
+    case 2:
+      if (!umma_ok) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: the tensor-core kernel needs K and the group size to be multiples of 64");
+      use_umma = true;
+      break;
+    case 3: use_resident = resident_ok; use_umma = !resident_ok && !gemv_ok && umma_ok; break;
+    default:
+      // up to 8 tokens: the decode kernels.  Above: the fused kernel (exact group scaling, no copy of the weight);
+      // from 512 tokens on a handle trades 2^-9 of relative weight rounding for the plain bf16 GEMM's speed.
+      if (gemv_ok) break;
+      if (resident_ok && M >= 512) use_resident = true;
+      else use_umma = umma_ok;
   }
-  if (route == 3 && M > 8 && w16 && K % 8 == 0 && group % 8 == 0 && M <= 0x7fffffffLL) {
-    // prefill: dequantise once (kept for the life of the handle / weight version), then a bf16 GEMM
+  if (use_umma) return a16_w4_umma_launch(x, wq, scale, zp, bias, y, M, N, K, group, status, s);
+  if (use_resident) {
+    // dequantise once (kept for the life of the handle / weight version), then a bf16 GEMM
     if (!*w16_ready) {
       B200Q_TRY(w16->ensure((size_t)N * K * 2));
       B200Q_TRY(dequant_w4_bf16(wq, scale, zp, w16->p, N, K, group, s));
@@ -130,7 +144,8 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
     }
     return a16_prefill_gemm(x, w16->p, bias, y, M, N, K, status, s);
   }
-  if (!a16_w4_gemv_supported(1, N, K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: %s", why);
+  // decode kernels, 8 tokens per launch (also the fallback for shapes the tensor-core kernel does not take)
+  if (!a16_w4_gemv_supported((int)(M < 8 ? M : 8), N, K, group, &why) || (M > 8 && !a16_w4_gemv_supported(8, N, K, group, &why))) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: %s", why);
   for (long long m0 = 0; m0 < M; m0 += 8) {
     const int mm = (int)((M - m0) < 8 ? (M - m0) : 8);
     B200Q_TRY(a16_w4_gemv_launch(static_cast<const uint8_t*>(x) + (size_t)m0 * K * 2, wq, scale, zp, bias,

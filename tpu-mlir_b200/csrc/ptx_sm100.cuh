@@ -74,6 +74,9 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t n) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(n) : "memory");
+}
 // Arrive without release ordering: for hand-offs where nothing written to memory is being published
 // (an accumulator buffer that has been read into registers).
 __device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar) {
@@ -122,6 +125,26 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   while (true) {
     if (mbar_try_wait_hint(bar, parity, 20000u)) return true;  // suspended up to 20 us per try
     if ((++spins & 7u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (globaltimer_ns() - t0 > budget_ns) {
+        *abort_flag = where;
+        return false;
+      }
+    }
+  }
+}
+
+// The same bounded wait for hand-offs that happen every few hundred cycles: plain try_wait in a loop (each try blocks
+// in hardware for a short, system-chosen time), no software back-off whose sleep would add to every hand-off.
+__device__ __forceinline__ bool mbar_wait_bounded_fast(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where,
+                                                       uint64_t budget_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(40);   // a waiting warp must not take issue slots from the warps it is waiting for
+    if ((++spins & 255u) == 0u) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > budget_ns) {
         *abort_flag = where;
@@ -342,6 +365,48 @@ __device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[
       : "r"(taddr)
       : "memory");
 }
+// 32 lanes x 16 consecutive 32-bit columns, registers -> TMEM: thread i of the warp writes lane (base_lane + i).
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// The calling thread's tcgen05.st operations have completed.
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// One k-block (64 16-bit elements of K) with the A operand in TENSOR MEMORY (lane = row, two elements per 32-bit
+// column, 8 columns per K = 16 step) and B from shared memory (K-major, 128-byte swizzle): four MMAs, one asm block.
+__device__ __forceinline__ void umma_kblock_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                                   uint32_t idesc, uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b32 at, bl;\n\t"
+      ".reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "setp.eq.b32 p, %4, %4;\n\t"
+      "add.u32 at, %1, 8;\n\t"
+      "add.u32 bl, %2, 2;\n\t"
+      "mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p;\n\t"
+      "add.u32 at, %1, 16;\n\t"
+      "add.u32 bl, %2, 4;\n\t"
+      "mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p;\n\t"
+      "add.u32 at, %1, 24;\n\t"
+      "add.u32 bl, %2, 6;\n\t"
+      "mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate_first)
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Wait for this thread's TMEM loads; the loaded registers are named as in/out operands so that the compiler keeps
