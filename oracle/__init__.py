@@ -532,3 +532,39 @@ def ref_float16():
         L.ref_f16_to_f32.restype, L.ref_f16_to_f32.argtypes = C.c_float, [C.c_uint]
         _ref_f16 = L
     return _ref_f16
+
+
+def ref_oploops_available() -> bool:
+    return os.path.exists(os.path.join(_HERE, "_ref", "oploops_ref.so"))
+
+
+_ref_oploops = None
+
+
+def ref_oploops():
+    """The reference's own operator loops (requantisation of Conv2D / MatMul, Add, average pool, A16 dequantisation,
+    RequantInt(Axis), Cast, saturate), cut from the checkout and compiled by `make -C oracle ref_oploops`."""
+    global _ref_oploops
+    if _ref_oploops is None:
+        L = C.CDLL(os.path.join(_HERE, "_ref", "oploops_ref.so"))
+        i32, i64, f32, f64, vp = C.c_int, C.c_longlong, C.c_float, C.c_double, C.c_void_p
+        L.ref_saturate_i64.restype, L.ref_saturate_i64.argtypes = i64, [i64, i32, i32]
+        L.ref_saturate_f32.restype, L.ref_saturate_f32.argtypes = i64, [f32, i32, i32, i32]
+        L.ref_conv2d_requant.restype = None
+        L.ref_conv2d_requant.argtypes = [vp, i64, i64, i64, vp, i32, vp, i32, vp, i32, i32, i64, i32, i32, i32]
+        L.ref_matmul_requant.restype = None
+        L.ref_matmul_requant.argtypes = [vp, i64, i64, i64, vp, i32, vp, i32, vp, i32, i32, f64, i64, i32, i32, i32, i32]
+        L.ref_add_int8.restype = None
+        L.ref_add_int8.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32]
+        L.ref_avgpool_int8.restype = None
+        L.ref_avgpool_int8.argtypes = [vp, i64, i32, i32, i32, i64, i32, i64, i32, i32, i32, i32]
+        L.ref_a16_dequant_w4.restype = None
+        L.ref_a16_dequant_w4.argtypes = [vp, vp, vp, i64, i64, i32, vp]
+        L.ref_requant_int_axis.restype = None
+        L.ref_requant_int_axis.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i64, i32, i32]
+        L.ref_requant_int.restype = None
+        L.ref_requant_int.argtypes = [vp, vp, vp, i32, i64, i64, i32, i32, i32, i64, i64, i32, i32]
+        L.ref_cast_requant.restype, L.ref_cast_requant.argtypes = f32, [f32, f64, i64, i32]
+        L.ref_cast_dequant.restype, L.ref_cast_dequant.argtypes = f32, [f32, f64, i64, i32]
+        _ref_oploops = L
+    return _ref_oploops
