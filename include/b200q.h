@@ -14,6 +14,16 @@
  * All functions return B200Q_OK (0) or a negative b200q_status; b200q_last_error() gives the
  * message of the calling thread's last failure.  Nothing here aborts, exits or falls back to the CPU.
  * Paths in the comments are paths inside the tpu-mlir source tree.
+ *
+ * Threads and streams.  The reference walks a graph on one interpreter thread (ModuleInterpreter.cpp:957-965) and
+ * only reads tensors from a small thread pool after invoke has returned (kld_calibrator.py:606-615); this library
+ * assumes the same.  The operator face runs on the legacy default stream (and, for Conv2D, on three streams private
+ * to the handle), is synchronous (results are in the output buffers on return) and synchronises the default stream
+ * first, so work the caller queued there is finished before it starts.  A handle (the void* of init / dev_create,
+ * a calibration context) holds staging buffers and device-side status words that every call on it reuses: calls on
+ * ONE handle must not overlap, whichever threads make them; calls on DIFFERENT handles may run from different
+ * threads at the same time.  The device face is asynchronous on the stream it is given; two calls on one handle are
+ * ordered by issuing them on the same stream (or by the caller's events).  b200q_last_error() is per thread.
  */
 #ifndef B200Q_H_
 #define B200Q_H_
@@ -171,7 +181,11 @@ typedef struct {
 /* Operator face of tpu::Conv2DOp::{init,inference,deinit} (Conv2D.cpp:74-86,:88-344).
  * inputs = {input, filter, bias} HOST float*; outputs[0] HOST float*.  init uploads and repacks the filter
  * and bias; inference requires a handle (Conv2D.cpp:89-91 fails without one).  Unlike the reference the
- * bias buffer is NOT zeroed in place (Conv2D.cpp:94-99 mutates its input). */
+ * bias buffer is NOT zeroed in place (Conv2D.cpp:94-99 mutates its input).  The handle keeps its device copy of
+ * the filter until inference is called with a descriptor whose weight_version differs from the one the copy was made
+ * with, or with another filter pointer (the interpreter rewrites filters in place: setTensor, fake_quant_weight,
+ * ModuleInterpreter.cpp:583-612); then filter and bias are uploaded and repacked again.  A NULL descriptor keeps
+ * the copy. */
 int b200q_conv2d_init(const b200q_conv2d_desc *desc, float *const *inputs, int n_inputs, void **handle);
 int b200q_conv2d_inference(const b200q_conv2d_desc *desc, float *const *inputs, int n_inputs,
                            float *const *outputs, int n_outputs, void **handle);
@@ -216,6 +230,9 @@ typedef struct {
   int32_t out_dtype;
   int64_t multiplier, rshift; /* RequantInt attributes */
   int32_t out_zp;             /* RequantInt: zero point of the output type */
+  int32_t quant_words;        /* RequantIntAxis: words per channel of the quant operand: 3 = {multiplier, shift, zero
+                               * point} (BM1684X, RequantIntAxis.cpp:45-48; also meant by 0), 2 = {multiplier, shift in
+                               * the low byte | zero point in the high half-word} (every other chip, :49-54) */
 } b200q_requant_desc;
 int b200q_requant_int_axis_inference(const b200q_requant_desc *desc, float *const *inputs, int n_inputs,
                                      float *const *outputs, int n_outputs);

@@ -29,8 +29,11 @@ def run(graph, weights, inputs):
             assert viol == 0, name
             T[name] = out
         elif t == "tpu.MatMul":
+            fuse_rq = bool(a.get("fuse_rq", False))
+            mult = oracle.through_f32(weights[name + "_multi"]) if fuse_rq else a["multipliers"]
             T[name] = oracle.matmul_int8(x, weights[name + "_filter"], weights.get(name + "_bias"), do_relu=a["do_relu"],
-                                         qmode=_QM[a["quant_mode"]], mult=a["multipliers"], rshift=a["rshifts"],
+                                         right_transpose=bool(a.get("right_transpose", False)),
+                                         qmode=_QM[a["quant_mode"]], fuse_rq=fuse_rq, mult=mult, rshift=a["rshifts"][:1] if fuse_rq else a["rshifts"],
                                          out_zp=o["zp"], out_dt=_DT[o["dtype"]])
         elif t == "tpu.Add":
             m, s = a["multipliers"], a["rshifts"]

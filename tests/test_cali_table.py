@@ -7,7 +7,8 @@ import pytest
 
 from tpu_mlir_b200 import cali_table as CT
 
-REF_TABLES = "/root/reference/regression/cali_tables"
+# a checkout of the reference, when there is one (TPU_MLIR_REFERENCE overrides the default location)
+REF_TABLES = os.path.join(os.environ.get("TPU_MLIR_REFERENCE", "/root/reference"), "regression/cali_tables")
 
 
 def test_write_then_read_round_trip(tmp_path):

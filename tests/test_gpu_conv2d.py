@@ -53,6 +53,36 @@ def run_operator_face(c, *, strides=(1, 1), pads=(1, 1, 1, 1), dilations=(1, 1),
 
 
 @pytest.mark.parametrize("algo", [L.ALGO_TENSOR_CORE, L.ALGO_CUDA_CORE])
+def test_operator_face_follows_weight_version(algo):
+    """The interpreter rewrites filters in place (setTensor, fake_quant_weight: ModuleInterpreter.cpp:583-612).  The
+    handle keeps its device copy until the descriptor's weight_version changes: the same version returns the cached
+    result, a bumped version the result of the new filter and bias."""
+    c = synth.conv2d_int8(seed=41, N=2, C=128, H=10, W=10, OC=32)
+    c2 = synth.conv2d_int8(seed=42, N=2, C=128, H=10, W=10, OC=32)
+    want1, mult, rshift = oracle_conv(c, qmode=oracle.QM_MULTIPLIER_SHIFT)
+    want2, _, _ = oracle_conv(dict(c, w=c2["w"], bias=c2["bias"]), qmode=oracle.QM_MULTIPLIER_SHIFT)
+    assert not np.array_equal(want1, want2)
+    op = Conv2DOp(input_shape=c["x"].shape, oc=32, kernel_shape=(3, 3), pads=(1, 1, 1, 1), do_relu=True,
+                  quant_mode=L.QM_MULTIPLIER_SHIFT, multiplier=mult, rshift=rshift, algo=algo)
+    w_buf, b_buf = f32(c["w"]), f32(c["bias"])
+    out = np.zeros(op.out_shape, np.float32)
+    p = InferenceParameter(inputs=[f32(c["x"]), w_buf, b_buf], outputs=[out])
+    op.init(p)
+    op.inference(p)
+    assert np.array_equal(out, want1.astype(np.float32))
+    w_buf[...] = c2["w"]          # rewritten in place, version not bumped: the resident copy still answers
+    b_buf[...] = c2["bias"]
+    op.inference(p)
+    assert np.array_equal(out, want1.astype(np.float32))
+    op.invalidate_weights()
+    op.inference(p)
+    assert np.array_equal(out, want2.astype(np.float32))
+    op.inference(p)
+    assert np.array_equal(out, want2.astype(np.float32))
+    op.deinit(p)
+
+
+@pytest.mark.parametrize("algo", [L.ALGO_TENSOR_CORE, L.ALGO_CUDA_CORE])
 def test_conv3x3_qdm_small(algo):
     """Shape family of BASELINE config 1 at a size the oracle finishes quickly: 3x3, stride 1, pad 1, ReLU, QDM."""
     c = synth.conv2d_int8(seed=21, N=3, C=128, H=13, W=11, OC=72)

@@ -166,6 +166,34 @@ def test_requant_int_axis_operator_face(mode):
     assert np.array_equal(out, want.astype(np.float32))
 
 
+@pytest.mark.parametrize("mode", ["tflite", "ms", "ms_fuse_axis"])
+def test_requant_int_axis_two_word_quant_operand(mode):
+    """Chips other than BM1684X pack the quant operand in two words per channel: the multiplier, then the shift in the
+    low byte (signed char) and the zero point in the high half-word (signed short), RequantIntAxis.cpp:49-54."""
+    rng = np.random.default_rng(21)
+    Cn = 7
+    x = rng.integers(-2**20, 2**20, (3, Cn, 5, 4) if mode != "ms_fuse_axis" else (3, 5, 4, Cn), dtype=np.int32)
+    zp = rng.integers(0, 90, Cn)       # non-negative: the packed word stays below 2^24 and survives its float buffer
+    if mode == "tflite":
+        mult, shift = oracle.through_f32(rng.integers(2**30, 2**31, Cn)), -rng.integers(4, 16, Cn)
+        qmode, rmode = oracle.QM_TFLITE, oracle.RM_HALF_AWAY
+    else:
+        mult, shift = rng.integers(1000, 30000, Cn), (-1 if mode == "ms" else 1) * rng.integers(12, 24, Cn)
+        qmode, rmode = oracle.QM_MULTIPLIER_SHIFT, oracle.RM_HALF_UP
+    packed = (shift.astype(np.int64) & 0xFF) | (zp.astype(np.int64) << 16)
+    quant2 = np.stack([mult, packed], axis=1).astype(np.float32)
+    assert np.array_equal(quant2[:, 1].astype(np.int64), packed)
+    fuse = mode == "ms_fuse_axis"
+    want = oracle.requant_int_axis(x, np.stack([mult, shift, zp], axis=1), qmode=qmode, rmode=rmode, fuse_rq_axis=fuse,
+                                   out_dt=oracle.DT_I8)
+    d = L.RequantDesc(outer=x.size // Cn if fuse else x.shape[0], channels=Cn, inner=1 if fuse else 20, per_axis=1,
+                      quant_mode=qmode, round_mode=rmode, fuse_rq_axis=int(fuse), in_zp=0, out_dtype=L.DT_I8, quant_words=2)
+    out = np.zeros(x.shape, np.float32)
+    L.check(lib().b200q_requant_int_axis_inference(C.byref(d), L.float_pp([x.astype(np.float32), quant2.reshape(-1)]), 2,
+                                                   L.float_pp([out]), 1))
+    assert np.array_equal(out, want.astype(np.float32))
+
+
 def test_requant_int_operator_face():
     rng = np.random.default_rng(10)
     x = rng.integers(-2**18, 2**18, (2, 6, 9), dtype=np.int32)
@@ -193,7 +221,7 @@ def test_executor_loads_mlir_text(tmp_path):
         m = module()
         m.load(*src)
         m.set_tensor("input", x)
-        m.invoke()
+        m.invoke(fixed_to_float=False)
         outs.append({n: m.get_tensor(n) for n in ("conv", "pool", "sum", "fc", "output")})
     for n in outs[0]:
         assert np.array_equal(outs[0][n], outs[1][n]), n
@@ -229,7 +257,7 @@ def test_executor_runs_lut_mulshift_mul(channels_last):
     m = module(channels_last=channels_last)
     m.load(graph, weights)
     m.set_tensor("input", x)
-    m.invoke()
+    m.invoke(fixed_to_float=False)
     conv = m.get_tensor("conv")
     assert conv.shape == tuple(shp) and len(np.unique(conv)) > 20
     assert (("conv" in m._nhwc) and ("mul" in m._nhwc)) == channels_last
@@ -238,3 +266,109 @@ def test_executor_runs_lut_mulshift_mul(channels_last):
     assert np.array_equal(m.get_tensor("lut"), lut)
     assert np.array_equal(m.get_tensor("ms"), ms)
     assert np.array_equal(m.get_tensor("mul"), oracle.mul_int8(lut, ms, 5, 7, do_relu=True, out_dt=oracle.DT_U8))
+
+
+def _matmul_graph(attrs, weights_extra=None, w_shape=(64, 24), zp=0):
+    rng = np.random.default_rng(12)
+    tens = {"input": dict(shape=[5, 64], dtype="f32"), "q": dict(shape=[5, 64], dtype="i8", scale=0.05, zp=0),
+            "fc": dict(shape=[5, 24], dtype="i8", scale=0.2, zp=zp), "out": dict(shape=[5, 24], dtype="f32")}
+    ops = [dict(type="tpu.Cast", name="q", inputs=["input"]),
+           dict(type="tpu.MatMul", name="fc", inputs=["q"], attrs=dict(do_relu=False, **attrs)),
+           dict(type="tpu.Cast", name="out", inputs=["fc"])]
+    weights = {"fc_filter": rng.integers(-127, 128, w_shape, dtype=np.int8), "fc_bias": rng.integers(-500, 500, 24, dtype=np.int32)}
+    weights.update(weights_extra or {})
+    return dict(inputs=["input"], outputs=["out"], tensors=tens, ops=ops), weights
+
+
+@pytest.mark.parametrize("case", ["tflite", "tflite_lshift", "right_transpose", "fuse_rq"])
+def test_executor_matmul_honours_its_attributes(case, tmp_path):
+    """tpu.MatMul through the executor with the attributes a lowered model can carry (MatMul.cpp:636-728): TFLite
+    requantisation, a right operand stored [N, K], per-channel multipliers with a common shift; the graph goes through
+    the .mlir text on the way, and every tensor is compared with the oracle walk."""
+    import oracle_graph
+    from tpu_mlir_b200 import mlir_text as MT
+    from tpu_mlir_b200.module import module
+    rng = np.random.default_rng(13)
+    if case in ("tflite", "tflite_lshift"):
+        g, w = _matmul_graph(dict(quant_mode="TFLite" if case == "tflite" else "TFLite_LShift", multipliers=[1518500250], rshifts=[9]), zp=3)
+    elif case == "right_transpose":
+        g, w = _matmul_graph(dict(quant_mode="MultiplierShift", right_transpose=True, multipliers=[777], rshifts=[14]), w_shape=(24, 64))
+    else:
+        multi = rng.integers(300, 900, 24).astype(np.float32)
+        g, w = _matmul_graph(dict(quant_mode="MultiplierShift", fuse_rq=True, multipliers=[1] * 24, rshifts=[14] * 24), {"fc_multi": multi})
+    (tmp_path / "m.mlir").write_text(MT.emit_module(g, w, weight_file="w.npz"))
+    np.savez(tmp_path / "w.npz", **w)
+    x = rng.standard_normal((5, 64)).astype(np.float32)
+    want = oracle_graph.run(g, w, {"input": x})
+    for src in ((g, w), (str(tmp_path / "m.mlir"), None)):
+        m = module()
+        m.load(*src)
+        m.set_tensor("input", x)
+        m.invoke(fixed_to_float=False)
+        assert np.array_equal(m.get_tensor("fc"), want["fc"]) and want["fc"].any()
+
+
+def test_executor_refuses_matmul_attributes_it_does_not_honour():
+    from tpu_mlir_b200.module import module
+    for bad in (dict(left_transpose=True), dict(hdim_is_batch=True), dict(output_transpose=True), dict(input_zp=4),
+                dict(quant_mode="OnlyScale")):
+        attrs = dict(quant_mode="MultiplierShift", multipliers=[77], rshifts=[12])
+        attrs.update(bad)
+        g, w = _matmul_graph(attrs)
+        with pytest.raises(L.B200QError) as ei:
+            module().load(g, w)
+        assert ei.value.code == L.ERR_UNSUPPORTED
+
+
+def test_executor_invoke_surface():
+    """invoke(fixed_to_float), invoke_at, invoke_from and fake_quant_weight of pymlir.module
+    (pymlir.cpp:108-112, ModuleInterpreter.cpp:583-612,:992-1011,:1210-1253)."""
+    import oracle_graph
+    from test_mlir_text import small_graph
+    from tpu_mlir_b200.module import module
+    graph, weights = small_graph()
+    x = np.random.default_rng(3).standard_normal((2, 3, 8, 8)).astype(np.float32)
+    want = oracle_graph.run(graph, weights, {"input": x})
+    m = module()
+    m.load(graph, weights)
+    m.set_tensor("input", x)
+    # fixed_to_float (the default): get_tensor returns the expressed values (q - zp) * scale
+    m.invoke()
+    sc = np.float32(graph["tensors"]["conv"]["scale"])
+    assert np.array_equal(m.get_tensor("conv"), want["conv"].astype(np.float32) * sc)
+    assert np.array_equal(m.get_raw_tensor("conv"), want["conv"])
+    m.invoke(fixed_to_float=False)
+    assert np.array_equal(m.get_tensor("conv"), want["conv"])
+    # invoke_at: one op with its hooks, result as stored
+    seen = []
+    m.before_invoke(lambda n: seen.append(("b", n)))
+    m.after_invoke(lambda n: seen.append(("a", n)))
+    assert np.array_equal(m.invoke_at("pool"), want["pool"]) and seen == [("b", "pool"), ("a", "pool")]
+    # invoke_from: overwrite an intermediate tensor, run the rest
+    seen.clear()
+    m.tensors["pool"].zero_()
+    m.invoke_from("sum")
+    assert [n for k, n in seen if k == "a"] == ["sum", "flat", "fc", "output"]
+    assert not m.get_tensor("sum").any()
+    m.clear_hooks()
+    m.invoke(fixed_to_float=False)
+    assert np.array_equal(m.get_tensor("fc"), want["fc"])
+    # fake_quant_weight: filters rounded to 127 levels of their own maximum, biases untouched; the ops follow
+    w2 = {k: v.copy() for k, v in weights.items()}
+    w2["conv_filter"] = (w2["conv_filter"].astype(np.int32) // 3).astype(np.int8)      # maximum 42: the rounding changes values
+    m2 = module()
+    m2.load(graph, w2)
+    m2.fake_quant_weight()
+    fq = {}
+    for k, v in w2.items():
+        if k.endswith("_bias"):
+            fq[k] = v
+        else:
+            f = v.astype(np.float32)
+            mx = np.abs(f).max()
+            fq[k] = (np.round(f * 127 / mx) * mx / 127).astype(v.dtype)
+    want2 = oracle_graph.run(graph, fq, {"input": x})
+    m2.set_tensor("input", x)
+    m2.invoke(fixed_to_float=False)
+    assert np.array_equal(m2.get_tensor("fc"), want2["fc"])
+    assert m2.parser.get_next_op_by_op_name("pool") == ["sum"]

@@ -28,7 +28,7 @@ def test_int8_graph_matches_oracle_on_every_tensor(lowered, channels_last):
     seen = []
     m.after_invoke(lambda name: seen.append(name))
     m.set_tensor("input", x)
-    m.invoke()
+    m.invoke(fixed_to_float=False)
     assert seen == [op["name"] for op in graph["ops"]]
     if channels_last:   # every activation between the stem and the classifier lives as [N][H][W][C]
         assert len(m._nhwc) > 60 and tuple(m.tensors["conv1"].shape) == (2, 112, 112, 64)
@@ -57,13 +57,13 @@ def test_cuda_graph_replay_matches_eager(lowered):
         x = synth.calibration_images(seed=seed, count=2)
         for m in (eager, fast):
             m.set_tensor("input", x)
-            m.invoke()
+            m.invoke(fixed_to_float=False)
         for name in ("conv1", "layer2.0.add", "layer4.2.conv3", "fc", "output"):
             assert np.array_equal(eager.get_tensor(name), fast.get_tensor(name)), (seed, name)
     assert fast._graph is not None
     seen = []
     fast.after_invoke(lambda name: seen.append(name))      # hooks need the op-by-op path
-    fast.invoke()
+    fast.invoke(fixed_to_float=False)
     assert len(seen) == len(graph["ops"])
 
 
@@ -73,7 +73,7 @@ def test_int8_logits_track_the_fp32_network(lowered):
     m = module()
     m.load(graph, weights)
     m.set_tensor("input", x)
-    m.invoke()
+    m.invoke(fixed_to_float=False)
     q = m.get_tensor("output")
     f = resnet50.Fp32Forward(ops, torch.device("cuda"))(torch.from_numpy(x).cuda())["fc"].cpu().numpy()
     cos = float((q * f).sum() / (np.linalg.norm(q) * np.linalg.norm(f)))

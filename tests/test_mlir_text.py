@@ -6,7 +6,8 @@ import pytest
 
 from tpu_mlir_b200 import mlir_text as MT
 
-REF_SAMPLE = "/root/reference/test/Transforms/Parallel/Conv.mlir"
+# a checkout of the reference, when there is one (TPU_MLIR_REFERENCE overrides the default location)
+REF_SAMPLE = os.path.join(os.environ.get("TPU_MLIR_REFERENCE", "/root/reference"), "test/Transforms/Parallel/Conv.mlir")
 
 
 def test_types():

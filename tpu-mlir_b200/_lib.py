@@ -57,7 +57,7 @@ class Conv2DDesc(C.Structure):
 class RequantDesc(C.Structure):
     _fields_ = [("outer", C.c_int64), ("channels", C.c_int64), ("inner", C.c_int64), ("per_axis", C.c_int32),
                 ("quant_mode", C.c_int32), ("round_mode", C.c_int32), ("fuse_rq_axis", C.c_int32), ("in_zp", C.c_int32),
-                ("out_dtype", C.c_int32), ("multiplier", C.c_int64), ("rshift", C.c_int64), ("out_zp", C.c_int32)]
+                ("out_dtype", C.c_int32), ("multiplier", C.c_int64), ("rshift", C.c_int64), ("out_zp", C.c_int32), ("quant_words", C.c_int32)]
 
 
 class A16MatMulDesc(C.Structure):

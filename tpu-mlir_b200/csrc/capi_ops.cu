@@ -240,6 +240,9 @@ struct ConvHandle {
   DevBuf w_oihw, w_packed, bias, mult, shift, x_bordered, a_cols, status;
   // operator-face staging
   DevBuf x_f32, x_q8, y_q, y_f32, w_f32, bias_f32;
+  // operator face: which host filter the device copy was made from (b200q_conv2d_desc::weight_version)
+  int weight_version = -1;
+  const float* weight_ptr = nullptr;
   // optional per-kernel timing of the device face: one event triple per run since profiling was switched on
   bool profiling = false;
   std::vector<cudaEvent_t> events;  // 3 per run: before the layout kernel, between, after the conv kernel
@@ -645,6 +648,24 @@ int b200q_gemm_i8_dev(const void* a, int a_dtype, const void* b_nk, int b_dtype,
 }
 
 // ------------------------------------------------------------------------------------------------ Conv2D
+// Operator face: filter and bias from the host float buffers into the handle (upload, conversion, repacking).
+static int conv_upload_weights(ConvHandle* h, const b200q_conv2d_desc& d, float* const* inputs, int n_inputs, cudaStream_t s) {
+  const size_t w_elems = (size_t)d.oc * (d.ic / d.groups) * d.kh * d.kw;
+  B200Q_TRY(h->w_f32.ensure(w_elems * 4));
+  CUDA_TRY(cudaMemcpyAsync(h->w_f32.p, inputs[1], w_elems * 4, cudaMemcpyHostToDevice, s));
+  const float* bias_f = (d.with_bias && n_inputs > 2) ? inputs[2] : nullptr;
+  if (d.with_bias && !bias_f) return set_error(B200Q_ERR_INVALID, "conv2d: with_bias but inputs[2] is null");
+  if (bias_f) {
+    B200Q_TRY(h->bias_f32.ensure((size_t)d.oc * 4));
+    CUDA_TRY(cudaMemcpyAsync(h->bias_f32.p, bias_f, (size_t)d.oc * 4, cudaMemcpyHostToDevice, s));
+  }
+  B200Q_TRY(conv_setup(h, d, h->w_f32.p, 1, bias_f ? h->bias_f32.p : nullptr, 1, s));
+  CUDA_TRY(cudaStreamSynchronize(s));
+  h->weight_version = d.weight_version;
+  h->weight_ptr = inputs[1];
+  return B200Q_OK;
+}
+
 int b200q_conv2d_init(const b200q_conv2d_desc* desc, float* const* inputs, int n_inputs, void** handle) {
   if (!desc || !inputs || !handle || n_inputs < 2 || !inputs[1]) return set_error(B200Q_ERR_INVALID, "conv2d_init: null argument");
   const b200q_conv2d_desc& d = *desc;
@@ -653,20 +674,7 @@ int b200q_conv2d_init(const b200q_conv2d_desc* desc, float* const* inputs, int n
   auto* h = new (std::nothrow) ConvHandle();
   if (!h) return set_error(B200Q_ERR_NOMEM, "conv2d_init: out of host memory");
   cudaStream_t s = 0;
-  int rc = B200Q_OK;
-  do {
-    const size_t w_elems = (size_t)d.oc * (d.ic / d.groups) * d.kh * d.kw;
-    if ((rc = h->w_f32.ensure(w_elems * 4))) break;
-    if (cudaMemcpyAsync(h->w_f32.p, inputs[1], w_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D filter", __FILE__, __LINE__); break; }
-    const float* bias_f = (d.with_bias && n_inputs > 2) ? inputs[2] : nullptr;
-    if (d.with_bias && !bias_f) { rc = set_error(B200Q_ERR_INVALID, "conv2d: with_bias but inputs[2] is null"); break; }
-    if (bias_f) {
-      if ((rc = h->bias_f32.ensure((size_t)d.oc * 4))) break;
-      if (cudaMemcpyAsync(h->bias_f32.p, bias_f, (size_t)d.oc * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D bias", __FILE__, __LINE__); break; }
-    }
-    if ((rc = conv_setup(h, d, h->w_f32.p, 1, bias_f ? h->bias_f32.p : nullptr, 1, s))) break;
-    if (cudaStreamSynchronize(s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "sync", __FILE__, __LINE__); break; }
-  } while (0);
+  const int rc = conv_upload_weights(h, d, inputs, n_inputs, s);
   if (rc != B200Q_OK) {
     cudaStreamSynchronize(s);
     delete h;
@@ -685,12 +693,19 @@ void b200q_conv2d_deinit(void** handle) {
 
 int b200q_conv2d_inference(const b200q_conv2d_desc* desc, float* const* inputs, int n_inputs, float* const* outputs,
                            int n_outputs, void** handle) {
-  (void)desc;
   if (!handle || !*handle) return set_error(B200Q_ERR_INVALID, "conv2d_inference: no handle (call b200q_conv2d_init first)");
   if (!inputs || !outputs || n_inputs < 1 || n_outputs < 1 || !inputs[0] || !outputs[0]) return set_error(B200Q_ERR_INVALID, "conv2d_inference: null argument");
   ConvHandle* h = static_cast<ConvHandle*>(*handle);
-  const b200q_conv2d_desc& d = h->d;
   cudaStream_t s = 0;
+  // The interpreter may rewrite a filter in place (setTensor, fake_quant_weight: ModuleInterpreter.cpp:583-612); the
+  // caller says so by bumping weight_version (or by handing in another buffer), and the device copy is remade.
+  if (desc && n_inputs >= 2 && inputs[1] && (desc->weight_version != h->weight_version || inputs[1] != h->weight_ptr)) {
+    if (desc->n != h->d.n || desc->ic != h->d.ic || desc->ih != h->d.ih || desc->iw != h->d.iw || desc->oc != h->d.oc ||
+        desc->kh != h->d.kh || desc->kw != h->d.kw || desc->groups != h->d.groups)
+      return set_error(B200Q_ERR_INVALID, "conv2d_inference: the descriptor's shape differs from the one the handle was made for");
+    B200Q_TRY(conv_upload_weights(h, *desc, inputs, n_inputs, s));
+  }
+  const b200q_conv2d_desc& d = h->d;
   const size_t x_elems = (size_t)d.n * d.ic * d.ih * d.iw;
   const size_t y_elems = (size_t)d.n * d.oc * h->g.oh * h->g.ow;
   if (x_elems == 0) return B200Q_OK;
@@ -898,8 +913,21 @@ int b200q_requant_int_axis_inference(const b200q_requant_desc* desc, float* cons
   dialect = tf ? B200Q_RQ_QDM : B200Q_RQ_MULTIPLIER_SHIFT;
   if (d.per_axis) {
     if (n_inputs < 2 || !inputs[1]) return set_error(B200Q_ERR_INVALID, "requant_int_axis: quant operand missing");
-    for (int c = 0; c < C; ++c) {  // BM1684X layout {multiplier, shift, zero point} read back from floats (RequantIntAxis.cpp:45-48)
-      const long long mm = (long long)inputs[1][c * 3], ss = (long long)inputs[1][c * 3 + 1], zz = (long long)inputs[1][c * 3 + 2];
+    if (d.quant_words != 0 && d.quant_words != 2 && d.quant_words != 3) return set_error(B200Q_ERR_INVALID, "requant_int_axis: quant_words must be 2 or 3");
+    for (int c = 0; c < C; ++c) {
+      long long mm, ss, zz;
+      if (d.quant_words == 2) {
+        // every chip but BM1684X: {multiplier, packed word}, shift = the low byte as a signed char, zero point = the
+        // high half-word as a signed short (RequantIntAxis.cpp:49-54), both read back from floats
+        mm = (long long)inputs[1][c * 2];
+        const uint32_t tmp = (uint32_t)inputs[1][c * 2 + 1];
+        ss = (long long)(signed char)(tmp & 0xffu);
+        zz = (long long)(short)((tmp & 0xffff0000u) >> 16);
+      } else {  // BM1684X: {multiplier, shift, zero point} (RequantIntAxis.cpp:45-48)
+        mm = (long long)inputs[1][c * 3];
+        ss = (long long)inputs[1][c * 3 + 1];
+        zz = (long long)inputs[1][c * 3 + 2];
+      }
       if (mm > 2147483647ll || mm < -2147483648ll) return set_error(B200Q_ERR_UNSUPPORTED, "requant: multiplier does not fit int32");
       m[(size_t)c] = (int32_t)mm;
       zp[(size_t)c] = (int32_t)zz;

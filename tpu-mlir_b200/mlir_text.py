@@ -363,7 +363,7 @@ def to_graph(mod: Module, weight_arrays: Dict[str, np.ndarray]):
             if op.type == "tpu.Conv2D":
                 names = ["_filter", "_bias"]
             elif op.type == "tpu.MatMul":
-                names = ["_filter", "_bias"]
+                names = ["_filter", "_bias", "_multi"]   # operands: input, right, bias, multi, buffer (TpuOps.td:4592-4616)
             elif op.type == "tpu.Lut":
                 names = ["_table"]      # operands: input, table (TpuOps.td LutOp)
             else:
@@ -388,6 +388,8 @@ def to_graph(mod: Module, weight_arrays: Dict[str, np.ndarray]):
                 weights[op.loc + "_filter"] = w.reshape(w.shape[-2], w.shape[-1]).astype(np.int8)
                 if (op.loc + "_bias") in weights:
                     weights[op.loc + "_bias"] = weights[op.loc + "_bias"].reshape(-1).astype(np.int32)
+                if (op.loc + "_multi") in weights:   # per-channel multipliers of fuse_rq, float-stored
+                    weights[op.loc + "_multi"] = weights[op.loc + "_multi"].reshape(-1).astype(np.float32)
             tensors[op.loc] = _tensor_entry(op.out_types[0])
             gops.append(dict(type=op.type, name=op.loc, inputs=[name_of[o] for o in acts], attrs=attrs))
         else:
@@ -464,12 +466,13 @@ def emit_module(graph: dict, weights: Dict[str, np.ndarray], name: str = "model"
     for op in graph["ops"]:
         operands, types = [ssa[i] for i in op["inputs"]], [ttype(i) for i in op["inputs"]]
         if op["type"] in ("tpu.Conv2D", "tpu.MatMul", "tpu.Lut"):
-            for suffix in (("_table",) if op["type"] == "tpu.Lut" else ("_filter", "_bias")):
+            suffixes = ("_table",) if op["type"] == "tpu.Lut" else ("_filter", "_bias", "_multi") if op["type"] == "tpu.MatMul" else ("_filter", "_bias")
+            for suffix in suffixes:
                 key = op["name"] + suffix
                 if key in weights:
                     w = weights[key]
                     r = new()
-                    wt = format_type(TensorType(list(w.shape), {"int8": "i8", "int32": "i32", "uint8": "u8"}[str(w.dtype)]))
+                    wt = format_type(TensorType(list(w.shape), {"int8": "i8", "int32": "i32", "uint8": "u8", "float32": "f32"}[str(w.dtype)]))
                     body.append('%s = "top.Weight"() : () -> %s %s' % (r, wt, loc(key)))
                     operands.append(r)
                     types.append(wt)

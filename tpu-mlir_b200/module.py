@@ -2,9 +2,10 @@
 ``pymlir.module`` and ``pymlir.cuda`` (bindings/pymlir/pymlir.cpp:101-131,
 bindings/pymlir/host/ModuleInterpreter.cpp:396-492,:631-1012, bindings/pymlir/pycuda.cpp:438-669).
 
-Method names and meaning follow ``pymlir.module``: ``load, set_tensor, invoke, get_tensor, get_fp32_tensor,
-get_all_tensor, before_invoke / after_invoke hooks, get_tensor_qinfo, input_names, output_names,
-all_tensor_names``.  Tensors live on the device in their native storage type (like ``py_cuda``), ops run in graph
+Method names and meaning follow ``pymlir.module``: ``load, set_tensor, set_tensor_from_int, invoke(fixed_to_float),
+invoke_at, invoke_from, fake_quant_weight, get_tensor, get_fp32_tensor, get_all_tensor, before_invoke / after_invoke /
+clear_hooks, get_tensor_qinfo, input_names, output_names, all_tensor_names, all_weight_names``; ``parser`` answers the
+graph queries of the reference's MlirParser (graph_queries.py).  Tensors live on the device in their native storage type (like ``py_cuda``), ops run in graph
 order through the device face of libb200q.so.  A graph is a plain dict whose op types and attribute names are the Tpu
 dialect's (``load`` also takes the path of a lowered model's ``.mlir`` text and reads it into this form, mlir_text.py):
 
@@ -56,6 +57,8 @@ class module:  # noqa: N801  (name of the reference class)
         self._keep = []
         self._before: List[Callable] = []
         self._after: List[Callable] = []
+        self._expressed = False   # the last invoke() asked for float ("expressed") tensors
+        self._status: List = []   # (op name, device status word or conv handle): checked after invoke
 
     # ------------------------------------------------------------------ loading
     def load(self, graph, weights: Optional[Dict[str, np.ndarray]] = None):
@@ -79,14 +82,25 @@ class module:  # noqa: N801  (name of the reference class)
                 shape = (shape[0], shape[2], shape[3], shape[1])
             self.tensors[name] = torch.zeros(shape, dtype=tdt[info["dtype"]], device=self.device)
         self.weights = {k: torch.from_numpy(np.ascontiguousarray(v)).to(self.device) for k, v in weights.items()}
-        for op in graph["ops"]:
+        from .graph_queries import MlirParser
+        self.parser = MlirParser(graph)
+        self._build_plans()
+
+    def _build_plans(self):
+        self._release_handles()
+        self._plans, self._keep, self._status, self._graph = [], [], [], None
+        for op in self.graph["ops"]:
             self._plans.append(self._plan(op))
-        torch.cuda.synchronize(self.device)
+        self.torch.cuda.synchronize(self.device)
+
+    def _release_handles(self):
+        for h in self._handles:
+            self.lib.b200q_conv2d_dev_destroy(C.byref(h))
+        self._handles = []
 
     def __del__(self):
         try:
-            for h in self._handles:
-                self.lib.b200q_conv2d_dev_destroy(C.byref(h))
+            self._release_handles()
         except Exception:
             pass
 
@@ -156,25 +170,52 @@ class module:  # noqa: N801  (name of the reference class)
             L.check(lib.b200q_conv2d_dev_create(C.byref(cop.desc), _P(w), _P(b), C.byref(h)))
             self._handles.append(h)
             self._keep.append(cop)
+            self._status.append((op["name"], h))
             if self.channels_last:
                 xl = L.LAYOUT_NHWC if op["inputs"][0] in self._nhwc else L.LAYOUT_NCHW
                 yl = L.LAYOUT_NHWC if op["name"] in self._nhwc else L.LAYOUT_NCHW
                 return lambda: L.check(lib.b200q_conv2d_dev_run_layout(h, _P(ins[0]), xl, _P(out), yl, stream()))
             return lambda: L.check(lib.b200q_conv2d_dev_run(h, _P(ins[0]), _P(out), stream()))
         if t == "tpu.MatMul":
-            w_kn = self.weights[op["name"] + "_filter"]
-            w_nk = w_kn.t().contiguous()          # the device face takes the right operand K-major
+            # What the reference reads from the op (MatMul.cpp:24-135,:636-728): anything this plan does not honour is
+            # refused, never computed differently.
+            qmode = a.get("quant_mode", "MultiplierShift")
+            for key in ("left_transpose", "output_transpose", "hdim_is_batch"):
+                if a.get(key, False):
+                    raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.MatMul with {key} is not implemented")
+            if int(a.get("input_zp", 0)) != 0 or int(a.get("right_zp", 0)) != 0 or int(iinfo[0].get("zp", 0)) != 0:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.MatMul with operand zero points is not implemented by the executor")
+            w = self.weights[op["name"] + "_filter"]
+            w_nk = w.contiguous() if a.get("right_transpose", False) else w.t().contiguous()   # right operand K-major
             b = self.weights.get(op["name"] + "_bias")
             M = int(np.prod(iinfo[0]["shape"][:-1]))
-            K, N = w_kn.shape
-            mult = self.torch.tensor([int(a["multipliers"][0])], dtype=self.torch.int32, device=self.device)
-            shift = self.torch.tensor([int(a["rshifts"][0])], dtype=self.torch.int32, device=self.device)
-            e = L.Epilogue(dialect=L.RQ_MULTIPLIER_SHIFT, round_mode=L.ROUND_HALF_UP, per_channel=0,
+            N, K = w_nk.shape
+            mults, shifts = [int(v) for v in a["multipliers"]], [int(v) for v in a["rshifts"]]
+            fuse_rq = bool(a.get("fuse_rq", False))
+            if qmode == "MultiplierShift" and fuse_rq:
+                # per-channel multipliers arrive as the float `multi` operand, one common shift (MatMul.cpp:709-716)
+                multi = self.weights[op["name"] + "_multi"].to(self.torch.float32).to(self.torch.int64)
+                mult = multi.to(self.torch.int32).contiguous()
+                shift = self.torch.full((N,), shifts[0], dtype=self.torch.int32, device=self.device)
+                dialect, rmode, per_channel = L.RQ_MULTIPLIER_SHIFT, L.ROUND_HALF_UP, 1
+            elif qmode == "MultiplierShift":
+                mult = self.torch.tensor([mults[0]], dtype=self.torch.int32, device=self.device)
+                shift = self.torch.tensor([shifts[0]], dtype=self.torch.int32, device=self.device)
+                dialect, rmode, per_channel = L.RQ_MULTIPLIER_SHIFT, L.ROUND_HALF_UP, 0
+            elif qmode in ("TFLite", "TFLite_LShift"):
+                # MultiplyByQuantizedMultiplier(acc, multiplier, -rshift), half away from zero (MatMul.cpp:696-707)
+                mult = self.torch.tensor([mults[0]], dtype=self.torch.int32, device=self.device)
+                shift = self.torch.tensor([-shifts[0]], dtype=self.torch.int32, device=self.device)
+                dialect, rmode, per_channel = L.RQ_QDM, L.ROUND_HALF_AWAY_FROM_ZERO, 0
+            else:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.MatMul quant_mode {qmode} is not implemented by the executor")
+            e = L.Epilogue(dialect=dialect, round_mode=rmode, per_channel=per_channel,
                            out_zp=int(oinfo.get("zp", 0)), relu=L.RELU_BEFORE_REQUANT if a.get("do_relu") else L.RELU_NONE,
                            out_dtype=_DT[oinfo["dtype"]], scale=0.0, bias=b.data_ptr() if b is not None else None,
                            multiplier=mult.data_ptr(), shift=shift.data_ptr())
             status = self.torch.zeros(1, dtype=self.torch.int32, device=self.device)
             self._keep += [w_nk, mult, shift, e, status]
+            self._status.append((op["name"], status))
             return lambda: L.check(lib.b200q_gemm_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(w_nk), L.DT_I8, M, N, K,
                                                          C.byref(e), _P(out), _P(status), L.ALGO_AUTO, stream()))
         if t == "tpu.Add":
@@ -233,6 +274,8 @@ class module:  # noqa: N801  (name of the reference class)
         t.copy_(src.reshape(t.shape).to(t.dtype), non_blocking=True)
 
     def set_tensor_from_int(self, name: str, data, shape=None):
+        """``setTensor(..., is_integer=true)`` (ModuleInterpreter.cpp:1313-1362): `data` already holds storage values.
+        This executor keeps tensors in their storage type, so integer and float-stored-integer data take one route."""
         self.set_tensor(name, data, shape)
 
     def before_invoke(self, fn: Callable):
@@ -257,28 +300,88 @@ class module:  # noqa: N801  (name of the reference class)
                 run()
         self._graph = g
 
-    def invoke(self, fixed_to_float: bool = True):
-        if self.cuda_graph and not self._before and not self._after:
-            if self._graph is None:
-                self._capture()
-            self._graph.replay()
-            return
-        for op, run in zip(self.graph["ops"], self._plans):
+    def _run_ops(self, ops_and_plans):
+        for op, run in ops_and_plans:
             for fn in self._before:
                 fn(op["name"])
             run()
             for fn in self._after:
                 fn(op["name"])
 
+    def invoke(self, fixed_to_float: bool = True):
+        """Runs every op in graph order.  As in the reference (ModuleInterpreter.cpp:992-1011), ``fixed_to_float``
+        decides what ``get_tensor`` returns afterwards for quantized tensors: their expressed float values
+        ``(q - zp) * scale`` (True, the default) or the raw storage values (False).  The device tensors themselves
+        always keep the storage values."""
+        self._expressed = bool(fixed_to_float)
+        if self.cuda_graph and not self._before and not self._after:
+            if self._graph is None:
+                self._capture()
+            self._graph.replay()
+            return
+        self._run_ops(zip(self.graph["ops"], self._plans))
+
     def invoke_at(self, name: str):
+        """One op, with its hooks; returns its output as stored (ModuleInterpreter.cpp:1210-1231)."""
         for op, run in zip(self.graph["ops"], self._plans):
             if op["name"] == name:
-                run()
+                self._expressed = False
+                self._run_ops([(op, run)])
                 return self.get_tensor(name)
         raise KeyError(name)
 
+    def invoke_from(self, name: str):
+        """Every op from `name` to the end of the graph, with hooks (ModuleInterpreter.cpp:1233-1253)."""
+        names = [op["name"] for op in self.graph["ops"]]
+        if name not in names:
+            raise KeyError(name)
+        i = names.index(name)
+        self._expressed = False
+        self._run_ops(list(zip(self.graph["ops"], self._plans))[i:])
+
+    def fake_quant_weight(self):
+        """ModuleInterpreter::fake_quant_weight (ModuleInterpreter.cpp:583-612): every weight except the bias operand
+        of a convolution / matmul is rounded to 127 levels of its own absolute maximum,
+        ``round(w * 127 / max) * max / 127``; the operators then work from the rewritten weights."""
+        torch = self.torch
+        for name, w in self.weights.items():
+            if name.endswith("_bias"):
+                continue
+            f = w.to(torch.float32)
+            mx = f.abs().max()
+            if float(mx) == 0.0:
+                continue
+            q = torch.round(f * 127 / mx) * mx / 127
+            self.weights[name] = q.to(w.dtype) if not w.dtype.is_floating_point else q
+        self._build_plans()   # device handles hold repacked copies of the weights
+
+    def check_status(self):
+        """Raises B200QError(ERR_TIMEOUT) if a bounded wait inside one of the graph's tensor-core kernels ran out
+        during an earlier invoke (the kernel returns early then and its output is not valid)."""
+        self.torch.cuda.synchronize(self.device)
+        for name, st in self._status:
+            if isinstance(st, C.c_void_p):
+                rc = self.lib.b200q_conv2d_dev_status(st, None)
+                if rc != L.OK:
+                    raise L.B200QError(rc, f"{name}: " + self.lib.b200q_last_error().decode("utf-8", "replace"))
+            else:
+                code = int(st.item())
+                if code != 0:
+                    st.zero_()
+                    raise L.B200QError(L.ERR_TIMEOUT, f"{name}: a bounded wait inside the kernel ran out (wait site {code})")
+
     def get_tensor(self, name: str) -> np.ndarray:
-        """Raw storage values (integers for quantized tensors), in the graph's own (NCHW) shape."""
+        """The tensor in the graph's own (NCHW) shape: expressed float values after ``invoke(fixed_to_float=True)``,
+        raw storage values (integers for quantized tensors) otherwise.  Reading a tensor is where a kernel-side timeout
+        of the preceding run surfaces."""
+        self.check_status()
+        if self._expressed:
+            return self.get_fp32_tensor(name)
+        return self._nchw(name).cpu().numpy()
+
+    def get_raw_tensor(self, name: str) -> np.ndarray:
+        """Storage values regardless of the last invoke's ``fixed_to_float``."""
+        self.check_status()
         return self._nchw(name).cpu().numpy()
 
     def _nchw(self, name: str):
@@ -294,6 +397,7 @@ class module:  # noqa: N801  (name of the reference class)
         return ((v.astype(np.float32) - np.float32(info.get("zp", 0))) * np.float32(info["scale"])).astype(np.float32)
 
     def get_all_tensor(self) -> Dict[str, np.ndarray]:
+        self.check_status()
         return {n: self.get_fp32_tensor(n) for n in self.all_tensor_names}
 
     def get_tensor_qinfo(self, name: str):

@@ -127,6 +127,11 @@ class Conv2DOp:
                           (ih + pht + phb - dilations[0] * (kernel_shape[0] - 1) - 1) // strides[0] + 1,
                           (iw + pwl + pwr - dilations[1] * (kernel_shape[1] - 1) - 1) // strides[1] + 1)
 
+    def invalidate_weights(self):
+        """Call after rewriting the filter / bias buffers in place (the interpreter does that in setTensor and
+        fake_quant_weight): the next inference uploads and repacks them again."""
+        self.desc.weight_version += 1
+
     def init(self, p: InferenceParameter):
         ins = [_f32(a) for a in p.inputs]
         h = C.c_void_p()
