@@ -136,3 +136,27 @@ def test_single_process_path():
     want = _single_process_reference(samples)
     assert np.array_equal(cal.histograms["b"].numpy(), want["b"][0])
     assert np.float32(res["b"].kl).tobytes() == np.float32(want["b"][2]).tobytes()
+
+
+def test_bin_schedule_many_equals_the_scalar_recurrence():
+    """The per-tensor recurrence vectorised over tensors (what the sharded calibrator runs on every rank) against the
+    scalar form, including tensors that never contribute, all-zero samples, no growth, and a reset past 8M bins."""
+    from tpu_mlir_b200.calibration import bin_schedule, bin_schedule_many
+    rng = np.random.default_rng(0)
+    T, S = 24, 300
+    smax = np.abs(rng.standard_normal((T, S)).astype(np.float32)) * rng.uniform(0.1, 30, (T, 1)).astype(np.float32)
+    smin = -np.abs(rng.standard_normal((T, S)).astype(np.float32)) * rng.uniform(0, 30, (T, 1)).astype(np.float32)
+    smin[3] = 0
+    smax[5, :10] = 0
+    smin[5, :10] = 0
+    smax[7], smin[7] = 1, -1
+    smax[7, 0], smin[7, 0], smax[7, 150] = 1e-6, 0, 5000.0
+    smax[8], smin[8] = np.float32(2.5), np.float32(-1)
+    smax[9], smin[9] = 0, 0
+    many = bin_schedule_many(smin, smax)
+    for t in range(T):
+        a, b = bin_schedule(smin[t], smax[t]), many[t]
+        assert np.array_equal(a.th, b.th) and np.array_equal(a.nbins, b.nbins), t
+        assert a.final_bins == b.final_bins and a.width.tobytes() == b.width.tobytes(), t
+        assert (a.min.tobytes(), a.max.tobytes(), a.abs_max.tobytes()) == (b.min.tobytes(), b.max.tobytes(), b.abs_max.tobytes()), t
+    assert many[7].nbins[149] == 0 and many[7].nbins[150] == 2048 and many[7].final_bins == 2048 and many[9].final_bins == 0
