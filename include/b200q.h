@@ -306,6 +306,22 @@ int b200q_a16_w4_dev(const void *x_bf16, const void *wq, const void *scale_bf16,
                      const float *bias_f32, void *y_bf16, int64_t M, int64_t N, int64_t K, int32_t group,
                      int32_t *status, void *stream);
 
+/* Test aid (no counterpart in the reference): makes a bounded wait of the tensor-core INT8 GEMM/convolution kernel run
+ * out without faulting anything.  While extra_tx_bytes > 0 every pipeline stage's barrier expects that many bytes more
+ * than the stage's loads deliver, so the consumer's wait ends after `budget_ns` (0 = the default of 2 s) with the
+ * kernel's status set to the wait site; the calls then return B200Q_ERR_TIMEOUT and leave the context usable.
+ * (0, 0) restores normal operation.  Process-wide; not for use while other threads launch. */
+void b200q_debug_set_wait_fault(int32_t extra_tx_bytes, int64_t budget_ns);
+
+/* Tensor-pipe peak probe (a measuring aid; no counterpart in the reference): every SM issues tcgen05.mma on operand
+ * tiles resident in its shared memory and nothing else.  kind 0 = kind::i8 (s8 x s8 -> s32), 1 = kind::f16 on bf16
+ * operands (f32 accumulate); pair != 0 uses cta_group::2 (256 x 256 x 32-byte MMAs over two SMs) instead of 128 x 256.
+ * `launches` kernels of `kblocks` k-blocks (four MMAs each, a multiple of 8) per CTA run back to back on `stream`
+ * inside one event pair; *ms receives the elapsed milliseconds and *ops the operations (2 x multiply-accumulates)
+ * issued in that time.  Synchronises the stream.  B200Q_ERR_TIMEOUT if a wait inside the kernel ran out. */
+int b200q_probe_tensor_peak(int32_t kind, int32_t pair, int32_t kblocks, int32_t launches, double *ms, double *ops,
+                            void *stream);
+
 /* Which kernel serves b200q_a16_*, process-wide: 0 = chosen per call (default: one or two tokens take the CUDA-core
  * GEMV, everything else the fused-dequantisation tensor-core kernel); 1 = the decode kernels only (8 tokens per
  * launch); 2 = the tensor-core kernel for every M; 3 = handle API with M > 8: dequantise once into a bf16 copy kept in

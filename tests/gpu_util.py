@@ -28,6 +28,25 @@ def empty_dev(shape, dt):
     return torch.empty(shape, dtype=TORCH_OF_NP[np.dtype(NP_OF_DT[dt])], device="cuda")
 
 
+class Guarded:
+    """A device buffer of `shape` with 4 KB of canary bytes on both sides: `view` is what the kernel gets, `check()`
+    fails if anything outside the view changed (a store past a ragged edge)."""
+    PAD = 4096
+
+    def __init__(self, shape, torch_dtype, fill=None):
+        n = int(np.prod(shape)) * torch.empty(0, dtype=torch_dtype).element_size()
+        self.raw = torch.full((n + 2 * self.PAD,), 0xA5, dtype=torch.uint8, device="cuda")
+        self.view = self.raw[self.PAD:self.PAD + n].view(torch_dtype).reshape(shape)
+        if fill is not None:
+            self.view.fill_(fill)
+        self.n = n
+
+    def check(self):
+        torch.cuda.synchronize()
+        assert bool((self.raw[:self.PAD] == 0xA5).all()), "bytes before the output buffer were overwritten"
+        assert bool((self.raw[self.PAD + self.n:] == 0xA5).all()), "bytes after the output buffer were overwritten"
+
+
 def make_epilogue(*, dialect, round_mode, mult=None, shift=None, bias=None, per_channel=True, out_zp=0,
                   relu=L.RELU_NONE, out_dtype=L.DT_I8, scale=0.0):
     """Returns (Epilogue, keepalive list of device tensors)."""

@@ -10,7 +10,7 @@ import tpu_mlir_b200._lib as L
 from tpu_mlir_b200 import synth
 from tpu_mlir_b200.ops import Conv2DOp, InferenceParameter
 
-from gpu_util import dev, dt_of, empty_dev, ptr
+from gpu_util import Guarded, dev, dt_of, empty_dev, ptr
 
 pytestmark = pytest.mark.gpu
 
@@ -193,7 +193,8 @@ def test_conv_device_face_channels_last(case, layouts):
     x = c["x"].transpose(0, 2, 3, 1) if xl else c["x"]
     w_d, b_d, x_d = dev(c["w"]), dev(c["bias"]), dev(np.ascontiguousarray(x))
     y_shape = (want.shape[0], want.shape[2], want.shape[3], want.shape[1]) if yl else want.shape
-    y_d = torch.full(y_shape, 77, dtype=torch.uint8, device="cuda")
+    guard = Guarded(y_shape, torch.uint8, fill=77)     # canary bytes around the output (ragged pixel and channel tiles)
+    y_d = guard.view
     h = C.c_void_p()
     lib = L.lib()
     L.check(lib.b200q_conv2d_dev_create(C.byref(d), ptr(w_d), ptr(b_d), C.byref(h)))
@@ -201,6 +202,7 @@ def test_conv_device_face_channels_last(case, layouts):
         L.check(lib.b200q_conv2d_dev_run_layout(h, ptr(x_d), xl, ptr(y_d), yl, None))
     L.check(lib.b200q_conv2d_dev_status(h, None))
     lib.b200q_conv2d_dev_destroy(C.byref(h))
+    guard.check()
     got = y_d.cpu().numpy()
     assert np.array_equal(got.transpose(0, 3, 1, 2) if yl else got, want)
 

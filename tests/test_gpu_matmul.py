@@ -10,7 +10,7 @@ import tpu_mlir_b200._lib as L
 from tpu_mlir_b200 import synth
 from tpu_mlir_b200.ops import InferenceParameter, MatMulOp
 
-from gpu_util import dev, dt_of, empty_dev, make_epilogue, ptr
+from gpu_util import Guarded, NP_OF_DT, TORCH_OF_NP, dev, dt_of, empty_dev, make_epilogue, ptr
 
 pytestmark = pytest.mark.gpu
 
@@ -20,12 +20,15 @@ def run_gemm_dev(A, B_kn, epi_kwargs, algo):
     N = B_kn.shape[1]
     e, keep = make_epilogue(**epi_kwargs)
     a_d, b_d = dev(A), dev(np.ascontiguousarray(B_kn.T))
-    out = empty_dev((M, N), epi_kwargs.get("out_dtype", L.DT_I8))
+    # canary bytes around the output: a store past a ragged edge of the last tile fails the test
+    guard = Guarded((M, N), TORCH_OF_NP[np.dtype(NP_OF_DT[epi_kwargs.get("out_dtype", L.DT_I8)])])
+    out = guard.view
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     L.check(L.lib().b200q_gemm_i8_dev(ptr(a_d), dt_of(A), ptr(b_d), dt_of(B_kn), M, N, K, C.byref(e), ptr(out),
                                       ptr(status), algo, None))
     torch.cuda.synchronize()
     assert int(status.item()) == 0, f"kernel wait timed out at site {int(status.item())}"
+    guard.check()
     return out.cpu().numpy()
 
 
@@ -215,3 +218,69 @@ def test_empty_and_errors():
         op.inference(InferenceParameter(inputs=[np.zeros((4, 16), np.float32), np.zeros((16, 8), np.float32)],
                                         outputs=[np.zeros((4, 8), np.float32)]))
     assert ei.value.code == L.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 256), (4864, 2048, 128)], ids=["one_tile", "cta_pairs"])
+def test_a_wait_that_runs_out_is_reported_and_the_next_launch_is_exact(shape):
+    """Failure detection without a fault: every stage's barrier is told to expect 16 bytes more than the stage's loads
+    deliver, so the consumer's bounded wait runs out after 1 ms.  The kernel ends by itself with the wait site in its
+    status word, and the same launch without the aid is bit exact afterwards."""
+    M, N, K = shape
+    rng = np.random.default_rng(77)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    mult, rshift = synth.qdm_params(rng, N)
+    e, keep = make_epilogue(dialect=L.RQ_QDM, round_mode=L.ROUND_HALF_AWAY_FROM_ZERO, mult=mult, shift=-rshift)
+    a_d, b_d = dev(A), dev(np.ascontiguousarray(B.T))
+    out = empty_dev((M, N), L.DT_I8)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib = L.lib()
+
+    def launch():
+        L.check(lib.b200q_gemm_i8_dev(ptr(a_d), L.DT_I8, ptr(b_d), L.DT_I8, M, N, K, C.byref(e), ptr(out), ptr(status),
+                                      L.ALGO_TENSOR_CORE, None))
+        torch.cuda.synchronize()
+        return int(status.item())
+
+    lib.b200q_debug_set_wait_fault(16, 1_000_000)
+    try:
+        site = launch()
+    finally:
+        lib.b200q_debug_set_wait_fault(0, 0)
+    assert site in (1, 2, 3, 4), site          # a wait site of the pipeline, most often 3: the MMA warp's wait for a stage
+    status.zero_()
+    assert launch() == 0
+    acc = A.astype(np.int32) @ B.astype(np.int32)
+    want = oracle.requant_int_axis(acc.reshape(M, N, 1), np.stack([mult, -rshift, np.zeros_like(mult)], axis=1),
+                                   qmode=oracle.QM_TFLITE, rmode=oracle.RM_HALF_AWAY, out_dt=oracle.DT_I8).reshape(M, N)
+    assert np.array_equal(out.cpu().numpy(), want)
+
+
+def test_operator_face_reports_the_timeout_code():
+    rng = np.random.default_rng(6)
+    A = rng.integers(-128, 128, (128, 256), dtype=np.int8)
+    B = rng.integers(-128, 128, (256, 128), dtype=np.int8)
+    want = oracle.matmul_int8(A, B, None, qmode=oracle.QM_MULTIPLIER_SHIFT, mult=[3], rshift=[12])
+    op = MatMulOp(M=128, K=256, N=128, multipliers=[3], rshifts=[12], algo=L.ALGO_TENSOR_CORE)
+    y = np.zeros((128, 128), np.float32)
+    p = InferenceParameter(inputs=[f32(A), f32(B)], outputs=[y])
+    op.init(p)
+    lib = L.lib()
+    lib.b200q_debug_set_wait_fault(16, 1_000_000)
+    try:
+        with pytest.raises(L.B200QError) as ei:
+            op.inference(p)
+    finally:
+        lib.b200q_debug_set_wait_fault(0, 0)
+    assert ei.value.code == L.ERR_TIMEOUT
+    op.inference(p)          # the context is intact: the next call succeeds and is exact
+    op.deinit(p)
+    assert np.array_equal(y, want.astype(np.float32))
+
+
+def test_tensor_pipe_probe_reports_a_plausible_peak():
+    ms, ops = C.c_double(), C.c_double()
+    for kind, pair, lo, hi in ((0, 0, 1500, 5000), (0, 1, 1500, 5000), (1, 0, 800, 2500)):
+        L.check(L.lib().b200q_probe_tensor_peak(kind, pair, 8000, 4, C.byref(ms), C.byref(ops), None))
+        t = ops.value / (ms.value * 1e-3) / 1e12
+        assert lo < t < hi, (kind, pair, t)

@@ -279,15 +279,35 @@ class ShardedCalibrator:
     def _world(self):
         return (self.dist.get_rank(), self.dist.get_world_size()) if self.dist else (0, 1)
 
-    def run(self, batches: Iterable, samples_per_rank: int) -> Dict[str, TensorResult]:
+    def run(self, batches: Iterable, samples_per_rank: int, cache_bytes: Optional[int] = None) -> Dict[str, TensorResult]:
         """``batches`` must be re-iterable (it is walked twice) and cover exactly ``samples_per_rank`` local
-        samples in order; rank r holds global samples [r*samples_per_rank, (r+1)*samples_per_rank)."""
+        samples in order; rank r holds global samples [r*samples_per_rank, (r+1)*samples_per_rank).
+
+        The activations of the first pass stay on the device for the second pass while they fit in ``cache_bytes``
+        (default: half of the device memory that is free when the run starts); batches past that budget are
+        forwarded a second time, as the reference does for every batch (kld_calibrator.py:629-760 runs the network
+        once for min/max and once more for the histograms).  ``self.timings`` holds the seconds spent per phase."""
+        import time
         import torch
         rank, world = self._world()
         m = self.math
+        tm: Dict[str, float] = {}
+        cuda = torch.cuda.is_available()
+
+        def lap(key, t0):
+            if cuda:
+                torch.cuda.synchronize()
+            tm[key] = tm.get(key, 0.0) + time.perf_counter() - t0
+            return time.perf_counter()
+
+        if cache_bytes is None:
+            cache_bytes = torch.cuda.mem_get_info()[0] // 2 if cuda else 0
         # ---- pass 1: per-sample min/max of every tensor
+        t0 = time.perf_counter()
         names: List[str] = []
         local: Dict[str, List] = {}
+        cache: List[Dict] = []
+        held = 0
         for batch in batches:
             acts = self.forward(batch)
             if not names:
@@ -296,8 +316,15 @@ class ShardedCalibrator:
             for n in names:
                 a = acts[n]
                 local[n].append(m.minmax(a, samples=a.shape[0]))
+            need = sum(acts[n].numel() * acts[n].element_size() for n in names)
+            if held + need <= cache_bytes and (not cache or cache[-1] is not None):
+                cache.append(acts)
+                held += need
+            else:
+                cache.append(None)
         mm_local = torch.stack([torch.cat(local[n], dim=0) for n in names])            # [T, S_local, 2]
         assert mm_local.shape[1] == samples_per_rank, "batches do not cover samples_per_rank samples"
+        t0 = lap("pass1_forward_minmax", t0)
         if self.dist:
             gathered = [torch.empty_like(mm_local) for _ in range(world)]
             self.dist.all_gather(gathered, mm_local.contiguous())
@@ -305,8 +332,10 @@ class ShardedCalibrator:
         else:
             mm_all = mm_local
         mm_all = mm_all.cpu().numpy()
+        t0 = lap("gather_minmax", t0)
         # ---- identical schedule on every rank
         sched = dict(zip(names, bin_schedule_many(mm_all[:, :, 0], mm_all[:, :, 1], self.bin_num)))
+        t0 = lap("bin_schedule", t0)
         # ---- pass 2: histograms of the local samples into final-size buffers (one flat allocation)
         sizes = [max(sched[n].final_bins, 1) for n in names]
         offs = np.concatenate(([0], np.cumsum(sizes)))
@@ -314,8 +343,9 @@ class ShardedCalibrator:
         views = {n: flat[int(offs[t]):int(offs[t + 1])] for t, n in enumerate(names)}
         s0 = rank * samples_per_rank
         done = 0
-        for batch in batches:
-            acts = self.forward(batch)
+        for bi, batch in enumerate(batches):
+            acts = cache[bi] if cache[bi] is not None else self.forward(batch)
+            cache[bi] = None
             for n in names:
                 a = acts[n]
                 B = a.shape[0]
@@ -324,8 +354,13 @@ class ShardedCalibrator:
                 if sc.final_bins and sc.nbins[lo:lo + B].any():
                     m.histogram_into(views[n], a, sc.th[lo:lo + B], sc.nbins[lo:lo + B])
             done += next(iter(acts.values())).shape[0]
+            del acts
+        t0 = lap("pass2_histograms", t0)
+        self.allreduce_bytes = int(flat.numel() * 4) if self.dist else 0
+        self.cached_bytes = int(held)
         if self.dist:
             self.dist.all_reduce(flat)                                                   # sum of int32 counts
+        t0 = lap("allreduce_histograms", t0)
         # ---- KLD
         live = [n for n in names if sched[n].final_bins]
         kl = m.find_thresholds([views[n] for n in live], [sched[n].width for n in live], self.dst_bins) if live else []
@@ -336,6 +371,8 @@ class ShardedCalibrator:
             out[n] = TensorResult(name=n, min=float(sc.min), max=float(sc.max), abs_max=float(sc.abs_max),
                                   bins=sc.final_bins, width=float(sc.width), kl=k,
                                   threshold=table_threshold(k, sc.abs_max) if n in live else 1e-5)
+        lap("kld", t0)
+        self.timings = tm
         self.histograms = {n: views[n] for n in names}
         return out
 

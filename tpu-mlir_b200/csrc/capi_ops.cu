@@ -963,3 +963,9 @@ int b200q_requant_int_axis_inference(const b200q_requant_desc* desc, float* cons
 }
 
 }  // extern "C"
+
+// Test aid (no counterpart in the reference): the tensor-core GEMM/convolution launches that follow expect
+// `extra_tx_bytes` more per stage than their loads deliver and give every wait `budget_ns`; (0, 0) restores normal use.
+extern "C" void b200q_debug_set_wait_fault(int32_t extra_tx_bytes, int64_t budget_ns) {
+  b200q::igemm_set_wait_test(extra_tx_bytes, budget_ns);
+}

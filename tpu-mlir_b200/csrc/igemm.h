@@ -52,12 +52,15 @@ struct IGemmArgs {
   int floor_pre, sat_lo2, sat_hi, pack_sat, floor_needed;  // epilogue constants derived from epi (see the kernel)
   int dependent_launch;
   int acc_bound;  // |accumulator| <= this for every 8-bit operand pair (valid when acc_small)
+  unsigned long long wait_budget_ns;  // every mbarrier wait of the kernel gives up after this long
+  int expect_extra;                   // test aid: bytes added to what a stage's barrier expects (0 in normal use)
 };
 
 int make_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                  const uint32_t* box);
 int igemm_i8_tcgen05_supported(const IGemmProblem& p, const char** why);
 int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* status, cudaStream_t stream);
+void igemm_set_wait_test(int extra_tx_bytes, long long budget_ns);
 // Plain CUDA-core kernel for shapes the tensor-core path does not take (odd K, strides, groups, dilation).
 struct ConvGeometry {
   int n, ic, ih, iw, oc, oh, ow, kh, kw, sh, sw, dh, dw, pht, pwl, groups, pad_value;

@@ -22,6 +22,8 @@
 #include "igemm.h"
 #include "internal.h"
 #include "ptx_sm100.cuh"
+#include <atomic>
+
 #include "requant.cuh"
 
 namespace b200q {
@@ -31,7 +33,7 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;  // bytes == int8 elements: one 128-byte swizzle span
 constexpr int KIND_BF16_TAG = -2;  // value of the DIALECT template argument that selects bf16 operands / output  // each epilogue warp owns 32 TMEM lanes x 64 columns of the tile
-constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate tile time
+constexpr uint64_t DEFAULT_WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate tile time
 
 // PAIR: two CTAs of a cluster compute one 256 x BLOCK_N tile with tcgen05 cta_group::2; each CTA stages its own 128
 // rows of A and half of B's N rows, so a CTA pulls 1.5x fewer operand bytes per MMA through L2 and shared memory.
@@ -278,10 +280,10 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const int groups = num_kb / TAPW;
           int fy = 0;
           for (int g = 0; g < groups; ++g) {
-            ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, WAIT_BUDGET_NS);
+            ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, args.wait_budget_ns);
             if (!ok) break;
             const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
-            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_TX);
+            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_TX + args.expect_extra);
             const uint32_t lead_bar = ptx::map_to_cta(full_bar(stage), 0);
             ptx::tma_load_2d_pair(sa, &tmap_a, lead_bar, kc * BLOCK_K, a_row);
 #pragma unroll
@@ -300,17 +302,17 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
         } else {
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, WAIT_BUDGET_NS);
+          ok = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, 1, args.wait_budget_ns);
           if (!ok) break;
           const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
           if (PAIR) {
             // both CTAs' bytes complete on the leader's barrier; only the leader arrives on it
-            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);
+            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES + args.expect_extra);
             const uint32_t lead_bar = ptx::map_to_cta(full_bar(stage), 0);
             ptx::tma_load_2d_pair(sa, &tmap_a, lead_bar, kc * BLOCK_K, a_row);
             ptx::tma_load_2d_pair(sa + L::A_BYTES, &tmap_b, lead_bar, kb * BLOCK_K, n0 + (int)cta_rank * L::B_ROWS);
           } else {
-            ptx::mbar_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
+            ptx::mbar_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES + args.expect_extra);
             ptx::tma_load_2d(sa, &tmap_a, full_bar(stage), kc * BLOCK_K, a_row);
             ptx::tma_load_2d(sa + L::A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, n0);
           }
@@ -344,12 +346,12 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const uint32_t a_lo0 = (uint32_t)desc0;
       const uint32_t b_lo0 = (uint32_t)ptx::make_smem_desc_kmajor(smem_base + L::A_BYTES, 1024, 2);
       for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
-        ok = ptx::mbar_wait_bounded(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2, WAIT_BUDGET_NS);
+        ok = ptx::mbar_wait_bounded(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2, args.wait_budget_ns);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
         for (int kb = 0; kb < num_kb / TAPW; ++kb) {
-          ok = ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, 3, WAIT_BUDGET_NS);
+          ok = ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, 3, args.wait_budget_ns);
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t so = (uint32_t)stage * (uint32_t)(L::STAGE_BYTES >> 4);  // descriptor address units of 16 bytes
@@ -493,7 +495,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         epi_bar_sync<EPI_THREADS>();
         cached_n0 = n0;
       }
-      if (!ptx::mbar_wait_bounded(tmem_full_bar(acc), acc_phase, abort_flag, 4, WAIT_BUDGET_NS)) break;
+      if (!ptx::mbar_wait_bounded(tmem_full_bar(acc), acc_phase, abort_flag, 4, args.wait_budget_ns)) break;
       ptx::tc_fence_after_sync();
 
       const int row = m0 + quarter * 32 + lane;
@@ -722,6 +724,8 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   }
 
   // ---------------------------------------------------------------- teardown
+  // a wait that ran out in one CTA of a pair ends the other CTA's waits too (they poll their own flag)
+  if (PAIR && *abort_flag != 0) ptx::st_shared_cluster_u32(ptx::map_to_cta(ptx::smem_u32((const void*)abort_flag), cta_rank ^ 1u), (uint32_t)*abort_flag);
   ptx::tc_fence_before_sync();
   __syncthreads();
   if (PAIR) ptx::cluster_sync_all();  // neither CTA frees TMEM or exits while the other can still signal or read it
@@ -840,6 +844,14 @@ int make_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* d
 }
 
 // B200Q_IGEMM_TAPFUSE=0 in the environment keeps 3-tap filter rows on one activation load per tap (for A/B timing).
+// Test aid: launches wait for `extra` bytes more than their loads deliver, for at most `budget_ns` (0 = default).
+static std::atomic<unsigned long long> g_wait_budget_ns{DEFAULT_WAIT_BUDGET_NS};
+static std::atomic<int> g_expect_extra{0};
+void igemm_set_wait_test(int extra_tx_bytes, long long budget_ns) {
+  g_expect_extra.store(extra_tx_bytes < 0 ? 0 : extra_tx_bytes, std::memory_order_relaxed);
+  g_wait_budget_ns.store(budget_ns > 0 ? (unsigned long long)budget_ns : DEFAULT_WAIT_BUDGET_NS, std::memory_order_relaxed);
+}
+
 static bool tapfuse_allowed() {
   static const bool on = [] {
     const char* v = getenv("B200Q_IGEMM_TAPFUSE");
@@ -896,6 +908,8 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   a.out = p.out;
   a.epi = epi;
   a.status = status;
+  a.wait_budget_ns = g_wait_budget_ns.load(std::memory_order_relaxed);
+  a.expect_extra = g_expect_extra.load(std::memory_order_relaxed);
   a.bf16 = p.kind == IGEMM_KIND_BF16;
   // |accumulator| < 2^29 for every 8-bit operand pair: lets the epilogue fold the bias into one 64-bit constant
   a.acc_small = ((long long)a.num_kb * BLOCK_K * 32640ll) < (1ll << 29);
