@@ -225,7 +225,7 @@ def tensor_peaks(sustained=True):
     return out
 
 
-def kernel_lines(workload, steps, warmup):
+def kernel_lines(workload, steps, warmup, a16_m=(1, 2, 4, 8, 16, 128, 2048)):
     """Single-kernel lines, device resident, each against its roofline (N=1 only)."""
     import torch
     import tpu_mlir_b200._lib as L
@@ -304,7 +304,7 @@ def kernel_lines(workload, steps, warmup):
             L.check(lib.b200q_a16_dev_create(P(w_), P(s_), P(z_), None, 11008, 4096, 64, C.byref(h)))
             hs.append(h)
         packed = wq.numel() + sc.numel() * 2 + zp.numel()
-        for M in (1, 2, 4, 8, 16, 128, 2048):
+        for M in a16_m:
             x = torch.from_numpy(synth.a16_w4(seed=2, M=M)["x"]).cuda()
             y = torch.empty((M, 11008), dtype=torch.uint16, device="cuda")
 
@@ -418,7 +418,7 @@ def resnet50_line(R, steps, warmup, check=True):
     import torch
     from tpu_mlir_b200 import resnet50, synth
     from tpu_mlir_b200.module import module
-    GLOBAL_BATCH = 256
+    GLOBAL_BATCH = int(os.environ.get("B200Q_RESNET_BATCH", "256"))     # BASELINE config 3: 256
     per = GLOBAL_BATCH // R.world
     ops = resnet50.build_fp32(seed=3)
     cal_images = torch.from_numpy(synth.calibration_images(seed=4, count=64)).to(R.dev)
@@ -426,8 +426,10 @@ def resnet50_line(R, steps, warmup, check=True):
     del cal_images
     graph, weights = resnet50.lower_int8(ops, table, batch=per)
     m = module(channels_last=os.environ.get("B200Q_RESNET_LAYOUT", "nhwc") == "nhwc",
-               cuda_graph=os.environ.get("B200Q_RESNET_GRAPH", "1") == "1")
+               cuda_graph=os.environ.get("B200Q_RESNET_GRAPH", "1") == "1",
+               fuse_residual_add=os.environ.get("B200Q_RESNET_FUSE_ADD", "1") == "1")
     m.load(graph, weights)
+    n_fused = len(m._fused_adds)
     x_h = torch.from_numpy(synth.calibration_images(seed=5, count=per, start=R.rank * per)).pin_memory()
     m.set_tensor("input", x_h)
     for _ in range(warmup):
@@ -477,9 +479,10 @@ def resnet50_line(R, steps, warmup, check=True):
         return None
     return dict(metric="ResNet-50 int8 img/s", value=GLOBAL_BATCH * steps / (total_ms * 1e-3), unit="img/s",
                 ms_per_step=total_ms / steps, steps=steps, warmup=warmup, scaling="strong", n_gpus=R.world,
-                config=dict(workload="ResNet-50 INT8 symmetric (random init, calibrated on 64 synthetic images), "
-                                     "global batch 256 of 3x224x224, batch sharded over the ranks",
-                            per_gpu_batch=per, kernels_per_step=len(graph["ops"])),
+                config=dict(workload=f"ResNet-50 INT8 symmetric (random init, calibrated on 64 synthetic images), "
+                                     f"global batch {GLOBAL_BATCH} of 3x224x224, batch sharded over the ranks",
+                            per_gpu_batch=per, ops_in_graph=len(graph["ops"]), residual_adds_fused=n_fused,
+                            kernels_per_step=len(graph["ops"]) - n_fused),
                 parity=parity, logits_sha256=digest,
                 e2e=dict(value=GLOBAL_BATCH * e2e_steps / e2e_s, unit="img/s", steps=e2e_steps,
                          h2d_bytes_per_step=int(x_h.numel() * 4), d2h_bytes_per_step=int(logits.numel())))
@@ -697,6 +700,7 @@ def main():
                     help="conv = the benchmark contract (BASELINE config 1) with every other workload under `extras`; "
                          "any other value prints that workload's lines alone")
     ap.add_argument("--no-extras", action="store_true", help="headline only")
+    ap.add_argument("--a16-m", default="1,2,4,8,16,128,2048", help="token counts of --workload a16 (profiling runs pick one)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU legs (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
@@ -718,7 +722,7 @@ def main():
     elif args.workload != "conv":
         if R.world != 1:
             raise SystemExit("the single-kernel workloads run on one GPU")
-        for ln in kernel_lines(args.workload, args.steps, args.warmup):
+        for ln in kernel_lines(args.workload, args.steps, args.warmup, tuple(int(v) for v in args.a16_m.split(","))):
             ln.update(n_gpus=1, steps=ln.get("steps", args.steps), warmup=args.warmup)
             emit(ln)
     else:

@@ -205,6 +205,26 @@ int b200q_conv2d_dev_run(void *handle, const void *x_nchw, void *y_nchw, void *s
  * (B200Q_ERR_UNSUPPORTED otherwise).  The values are those of b200q_conv2d_dev_run, permuted. */
 enum { B200Q_LAYOUT_NCHW = 0, B200Q_LAYOUT_NHWC = 1 };
 int b200q_conv2d_dev_run_layout(void *handle, const void *x, int32_t x_layout, void *y, int32_t y_layout, void *stream);
+/* The same run with the tpu.Add that consumes the convolution's output fused into the kernel (a residual connection:
+ * Add.cpp:177-207, symmetric 8-bit form).  `residual` is the Add's other operand, a device tensor of the output's shape
+ * in the output's layout; y receives clamp(((v * conv_multiplier + 2^(conv_rshift-1)) >> conv_rshift) +
+ * ((r * residual_multiplier + 2^(residual_rshift-1)) >> residual_rshift)) in `out_dtype` (with do_relu the lower bound
+ * is 0), where v is the convolution's own requantised, saturated output, which is not stored.  Multipliers below 2^23
+ * in magnitude and shifts in [1,31] (what the lowering emits; B200Q_ERR_UNSUPPORTED otherwise, also for the CUDA-core
+ * route).  The values are those of b200q_conv2d_dev_run_layout followed by b200q_add_i8_dev. */
+typedef struct b200q_fused_add {
+  const void *residual;
+  int32_t residual_dtype;                       /* B200Q_DT_I8 / B200Q_DT_U8 */
+  int32_t conv_multiplier, conv_rshift;         /* the Add's pair for the operand that is this convolution's output */
+  int32_t residual_multiplier, residual_rshift; /* the Add's pair for the other operand */
+  int32_t do_relu;
+  int32_t out_dtype;                            /* the Add's output type, B200Q_DT_I8 / B200Q_DT_U8 */
+} b200q_fused_add;
+int b200q_conv2d_dev_run_add(void *handle, const void *x, int32_t x_layout, void *y, int32_t y_layout,
+                             const b200q_fused_add *add, void *stream);
+/* Which kernels serve this handle: 1 = tensor cores on the (bordered) channels-last image, 2 = tensor cores on
+ * gathered im2col rows, 0 = the CUDA-core kernel (groups, dilation, odd channel counts); negative = error. */
+int b200q_conv2d_dev_route(void *handle);
 int b200q_conv2d_dev_status(void *handle, void *stream);
 void b200q_conv2d_dev_destroy(void **handle);
 /* Optional timing of the device face: while enabled, every b200q_conv2d_dev_run records CUDA events on its

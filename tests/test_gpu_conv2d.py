@@ -253,3 +253,70 @@ def test_config1_full_size():
     want, mult, rshift = oracle_conv(c, qmode=oracle.QM_QDM, is_cv18xx=True)
     got = run_operator_face(c, qmode=L.QM_QDM, is_cv18xx=True, mult=mult, rshift=rshift, algo=L.ALGO_TENSOR_CORE)
     assert np.array_equal(got, want.astype(np.float32))
+
+
+@pytest.mark.parametrize("case", [
+    dict(N=2, C=64, H=12, W=20, OC=256, k=1, do_relu=False),     # 1x1, channels a multiple of 128: transposed product
+    dict(N=3, C=128, H=9, W=7, OC=80, k=1, do_relu=False),       # pixel-major, ragged channel tile
+    dict(N=2, C=128, H=13, W=11, OC=96, k=3, do_relu=True),      # 3x3 through the bordered image
+    dict(N=2, C=256, H=14, W=14, OC=512, k=1, stride=(2, 2), do_relu=False),   # strided 1x1 (downsample branch): im2col rows
+    dict(N=40, C=64, H=28, W=28, OC=256, k=1, do_relu=False),    # enough tiles for CTA pairs
+])
+@pytest.mark.parametrize("layout", [1, 0])
+@pytest.mark.parametrize("res_unsigned,add_relu", [(True, True), (False, False)])
+def test_conv_with_fused_residual_add(case, layout, res_unsigned, add_relu):
+    """b200q_conv2d_dev_run_add: the convolution followed by tpu.Add (Add.cpp:177-207) in one kernel equals the oracle's
+    convolution followed by the oracle's Add, in both layouts, with the convolution as either kind of operand."""
+    stride = case.get("stride", (1, 1))
+    pads = (1, 1, 1, 1) if case["k"] == 3 else (0, 0, 0, 0)
+    c = synth.conv2d_int8(seed=case["C"] + case["OC"], N=case["N"], C=case["C"], H=case["H"], W=case["W"], OC=case["OC"],
+                          KH=case["k"], KW=case["k"], unsigned_input=True)
+    c["w"] = np.clip(c["w"] // 2, -127, 127).astype(np.int8)
+    c["mult"] = np.random.default_rng(1).integers(5000, 30000, size=case["OC"])
+    c["rshift"] = np.random.default_rng(2).integers(18, 24, size=case["OC"])
+    conv_dt = oracle.DT_U8 if case["do_relu"] else oracle.DT_I8
+    conv_out, mult, rshift = oracle_conv(c, stride=stride, pads=pads, qmode=oracle.QM_MULTIPLIER_SHIFT, do_relu=case["do_relu"],
+                                         out_dt=conv_dt)
+    rng = np.random.default_rng(9)
+    res = rng.integers(0, 256, conv_out.shape).astype(np.uint8) if res_unsigned else rng.integers(-128, 128, conv_out.shape).astype(np.int8)
+    m_c, s_c, m_r, s_r = 19001, 14, 23456, 15
+    out_dt = oracle.DT_U8 if add_relu else oracle.DT_I8
+    want = oracle.add_int8(conv_out, res, m_c, s_c, m_r, s_r, do_relu=add_relu, out_dt=out_dt)
+    assert len(np.unique(want)) > 50
+    d = Conv2DOp(input_shape=c["x"].shape, oc=case["OC"], kernel_shape=(case["k"], case["k"]), strides=stride, pads=pads,
+                 do_relu=case["do_relu"], input_dtype=L.DT_U8, out_dtype=L.DT_U8 if case["do_relu"] else L.DT_I8,
+                 quant_mode=L.QM_MULTIPLIER_SHIFT, multiplier=mult, rshift=rshift).desc
+    to_l = (lambda t: np.ascontiguousarray(t.transpose(0, 2, 3, 1))) if layout else (lambda t: np.ascontiguousarray(t))
+    w_d, b_d, x_d, r_d = dev(c["w"]), dev(c["bias"]), dev(to_l(c["x"])), dev(to_l(res))
+    guard = Guarded(to_l(want).shape, torch.uint8 if add_relu else torch.int8, fill=77)
+    h = C.c_void_p()
+    lib = L.lib()
+    L.check(lib.b200q_conv2d_dev_create(C.byref(d), ptr(w_d), ptr(b_d), C.byref(h)))
+    assert lib.b200q_conv2d_dev_route(h) in (1, 2)
+    fa = L.FusedAdd(residual=r_d.data_ptr(), residual_dtype=L.DT_U8 if res_unsigned else L.DT_I8, conv_multiplier=m_c,
+                    conv_rshift=s_c, residual_multiplier=m_r, residual_rshift=s_r, do_relu=int(add_relu),
+                    out_dtype=L.DT_U8 if add_relu else L.DT_I8)
+    for _ in range(2):
+        L.check(lib.b200q_conv2d_dev_run_add(h, ptr(x_d), layout, ptr(guard.view), layout, C.byref(fa), None))
+    L.check(lib.b200q_conv2d_dev_status(h, None))
+    lib.b200q_conv2d_dev_destroy(C.byref(h))
+    guard.check()
+    got = guard.view.cpu().numpy()
+    assert np.array_equal(got.transpose(0, 3, 1, 2) if layout else got, want)
+
+
+def test_fused_add_refusals():
+    c = synth.conv2d_int8(seed=3, N=1, C=32, H=8, W=8, OC=32, KH=3, KW=3)
+    d = Conv2DOp(input_shape=c["x"].shape, oc=32, kernel_shape=(3, 3), pads=(1, 1, 1, 1), quant_mode=L.QM_MULTIPLIER_SHIFT,
+                 multiplier=[3], rshift=[9]).desc
+    w_d, b_d, x_d = dev(c["w"]), dev(c["bias"]), dev(c["x"])
+    y = empty_dev((1, 32, 8, 8), L.DT_I8)
+    h = C.c_void_p()
+    lib = L.lib()
+    L.check(lib.b200q_conv2d_dev_create(C.byref(d), ptr(w_d), ptr(b_d), C.byref(h)))
+    fa = L.FusedAdd(residual=y.data_ptr(), residual_dtype=L.DT_I8, conv_multiplier=1 << 24, conv_rshift=3,
+                    residual_multiplier=5, residual_rshift=3, do_relu=0, out_dtype=L.DT_I8)
+    assert lib.b200q_conv2d_dev_run_add(h, ptr(x_d), 0, ptr(y), 0, C.byref(fa), None) == L.ERR_UNSUPPORTED   # multiplier too wide
+    fa.conv_multiplier, fa.residual_dtype = 7, L.DT_I32
+    assert lib.b200q_conv2d_dev_run_add(h, ptr(x_d), 0, ptr(y), 0, C.byref(fa), None) == L.ERR_INVALID
+    lib.b200q_conv2d_dev_destroy(C.byref(h))

@@ -78,3 +78,26 @@ def test_int8_logits_track_the_fp32_network(lowered):
     f = resnet50.Fp32Forward(ops, torch.device("cuda"))(torch.from_numpy(x).cuda())["fc"].cpu().numpy()
     cos = float((q * f).sum() / (np.linalg.norm(q) * np.linalg.norm(f)))
     assert cos > 0.95, cos          # the reference's own int8-vs-fp32 acceptance level (test_onnx.py:624-640)
+
+
+def test_fused_residual_adds_keep_every_other_tensor(lowered):
+    """module(fuse_residual_add=True): the 16 residual Adds run inside the kernels of the convolutions that feed them;
+    every tensor that is still materialised equals the oracle's, the fused-away convolution outputs raise."""
+    ops, table, graph, weights = lowered
+    x = synth.calibration_images(seed=37, count=2)
+    m = module(channels_last=True, cuda_graph=True, fuse_residual_add=True)
+    m.load(graph, weights)
+    assert len(m._fused_adds) == 16
+    m.set_tensor("input", x)
+    m.invoke(fixed_to_float=False)
+    want = oracle_graph.run(graph, weights, {"input": x})
+    for op in graph["ops"]:
+        name = op["name"]
+        if name in m._fuse_into:
+            with pytest.raises(Exception):
+                m.get_tensor(name)
+            continue
+        assert np.array_equal(m.get_tensor(name), want[name]), (name, op["type"])
+    # one op at a time: a fused Add is produced by running its convolution
+    add = next(iter(m._fused_adds))
+    assert np.array_equal(m.invoke_at(add), want[add])

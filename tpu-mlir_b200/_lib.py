@@ -44,6 +44,13 @@ class MatMulDesc(C.Structure):
                 ("out_scale", C.c_double), ("algo", C.c_int32)]
 
 
+class FusedAdd(C.Structure):
+    """b200q_fused_add: the tpu.Add fused into a convolution's epilogue."""
+    _fields_ = [("residual", C.c_void_p), ("residual_dtype", C.c_int32), ("conv_multiplier", C.c_int32),
+                ("conv_rshift", C.c_int32), ("residual_multiplier", C.c_int32), ("residual_rshift", C.c_int32),
+                ("do_relu", C.c_int32), ("out_dtype", C.c_int32)]
+
+
 class Conv2DDesc(C.Structure):
     _fields_ = [(k, C.c_int64) for k in ("n", "ic", "ih", "iw", "oc", "kh", "kw", "sh", "sw", "dh", "dw", "pht",
                                          "phb", "pwl", "pwr", "groups")] + \
@@ -85,6 +92,8 @@ SIGNATURES = {
     "b200q_conv2d_dev_create": (C.c_int, [C.POINTER(Conv2DDesc), C.c_void_p, C.c_void_p, _VPP]),
     "b200q_conv2d_dev_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200q_conv2d_dev_run_layout": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
+    "b200q_conv2d_dev_run_add": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(FusedAdd), C.c_void_p]),
+    "b200q_conv2d_dev_route": (C.c_int, [C.c_void_p]),
     "b200q_conv2d_dev_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200q_conv2d_dev_destroy": (None, [_VPP]),
     "b200q_requant_int_axis_inference": (C.c_int, [C.POINTER(RequantDesc), _FLOATPP, C.c_int, _FLOATPP, C.c_int]),

@@ -306,8 +306,35 @@ class ShardedCalibrator:
         t0 = time.perf_counter()
         names: List[str] = []
         local: Dict[str, List] = {}
-        cache: List[Dict] = []
+        cache: List[Optional[Dict]] = []
         held = 0
+        # The kept activations are copied into a few large slabs: holding the forward's own tensors would make the
+        # allocator ask the driver for fresh memory on every batch (slow once peer access is enabled by NCCL), while a
+        # copy costs a fraction of the forward and lets the forward reuse its blocks.
+        SLAB = 4 << 30
+        slabs: List = []
+        slab_off = 0
+
+        def keep(acts):
+            nonlocal slab_off
+            out = {}
+            for n in names:
+                a = acts[n]
+                if not a.is_cuda or a.dtype != torch.float32 or not a.is_contiguous():
+                    out[n] = a
+                    continue
+                nbytes = (a.numel() * 4 + 255) & ~255
+                if not slabs or slab_off + nbytes > slabs[-1].numel():
+                    ta = time.perf_counter()
+                    slabs.append(torch.empty(max(SLAB, nbytes), dtype=torch.uint8, device=a.device))
+                    tm["cache_alloc"] = tm.get("cache_alloc", 0.0) + time.perf_counter() - ta
+                    slab_off = 0
+                v = slabs[-1][slab_off:slab_off + a.numel() * 4].view(torch.float32).view(a.shape)
+                v.copy_(a)
+                slab_off += nbytes
+                out[n] = v
+            return out
+
         for batch in batches:
             acts = self.forward(batch)
             if not names:
@@ -318,10 +345,11 @@ class ShardedCalibrator:
                 local[n].append(m.minmax(a, samples=a.shape[0]))
             need = sum(acts[n].numel() * acts[n].element_size() for n in names)
             if held + need <= cache_bytes and (not cache or cache[-1] is not None):
-                cache.append(acts)
+                cache.append(keep(acts))
                 held += need
             else:
                 cache.append(None)
+            del acts
         mm_local = torch.stack([torch.cat(local[n], dim=0) for n in names])            # [T, S_local, 2]
         assert mm_local.shape[1] == samples_per_rank, "batches do not cover samples_per_rank samples"
         t0 = lap("pass1_forward_minmax", t0)

@@ -419,8 +419,28 @@ void make_transposed(IGemmProblem* p, int oc) {
 // x_nhwc / y_nhwc: the tensor is [N][H][W][C] bytes instead of NCHW (the tensor-core routes only; a channels-last
 // graph keeps its activations in that form between ops, so no transposing kernel runs and outputs are stored as
 // whole 16-byte channel runs)
+// `add`: fuse a tpu.Add of the output with add->residual (same shape and layout as y) into the epilogue; y then
+// receives the Add's result and the convolution's own output is not stored (tensor-core routes only)
 int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s, long long images = -1, bool x_nhwc = false,
-             bool y_nhwc = false) {
+             bool y_nhwc = false, const b200q_fused_add* add = nullptr) {
+  auto set_add = [&](IGemmProblem* p) {
+    if (!add) return;
+    p->res = add->residual;
+    p->res_unsigned = add->residual_dtype == B200Q_DT_U8;
+    p->add_m_self = add->conv_multiplier;
+    p->add_s_self = add->conv_rshift;
+    p->add_m_res = add->residual_multiplier;
+    p->add_s_res = add->residual_rshift;
+    const int lo = add->out_dtype == B200Q_DT_U8 ? 0 : -128, hi = add->out_dtype == B200Q_DT_U8 ? 255 : 127;
+    p->add_lo = add->do_relu && lo < 0 ? 0 : lo;
+    p->add_hi = hi;
+  };
+  if (add) {
+    const bool t8 = (add->residual_dtype == B200Q_DT_I8 || add->residual_dtype == B200Q_DT_U8) &&
+                    (add->out_dtype == B200Q_DT_I8 || add->out_dtype == B200Q_DT_U8);
+    if (!add->residual || !t8) return set_error(B200Q_ERR_INVALID, "conv2d: fused Add needs an 8-bit residual tensor and output type");
+    if (!(h->use_tc || h->use_im2col)) return set_error(B200Q_ERR_UNSUPPORTED, "conv2d: fused Add needs one of the tensor-core routes");
+  }
   const b200q_conv2d_desc& d = h->d;
   const long long nb = images < 0 ? (long long)d.n : images;
   if (nb == 0) return B200Q_OK;
@@ -477,6 +497,7 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     // a 1x1 filter without a border is a plain GEMM whose rows are exactly the output pixels
     if (y_nhwc && d.kh * d.kw == 1 && h->bh == 0 && h->bw == 0 && transposed_product_ok(h->epi, (int)d.oc, p.rows))
       make_transposed(&p, (int)d.oc);
+    set_add(&p);
     B200Q_TRY(igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s));
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[2], s));
     return B200Q_OK;
@@ -521,6 +542,7 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
     p.out = y;
     p.dependent_launch = h->profiling ? 0 : 1;
     if (y_nhwc && transposed_product_ok(h->epi, (int)d.oc, p.rows)) make_transposed(&p, (int)d.oc);
+    set_add(&p);
     B200Q_TRY(igemm_i8_tcgen05_launch(p, h->epi, h->status.as<int>(), s));
     if (h->profiling) CUDA_TRY(cudaEventRecord(h->ev[2], s));
     return B200Q_OK;
@@ -794,6 +816,21 @@ int b200q_conv2d_dev_run_layout(void* handle, const void* x, int32_t x_layout, v
     return set_error(B200Q_ERR_INVALID, "conv2d_dev_run_layout: unknown layout");
   return conv_run(static_cast<ConvHandle*>(handle), x, 0, y, static_cast<cudaStream_t>(stream), -1, x_layout == B200Q_LAYOUT_NHWC,
                   y_layout == B200Q_LAYOUT_NHWC);
+}
+
+int b200q_conv2d_dev_run_add(void* handle, const void* x, int32_t x_layout, void* y, int32_t y_layout, const b200q_fused_add* add,
+                             void* stream) {
+  if (!handle || !x || !y || !add) return set_error(B200Q_ERR_INVALID, "conv2d_dev_run_add: null argument");
+  if ((x_layout != B200Q_LAYOUT_NCHW && x_layout != B200Q_LAYOUT_NHWC) || (y_layout != B200Q_LAYOUT_NCHW && y_layout != B200Q_LAYOUT_NHWC))
+    return set_error(B200Q_ERR_INVALID, "conv2d_dev_run_add: unknown layout");
+  return conv_run(static_cast<ConvHandle*>(handle), x, 0, y, static_cast<cudaStream_t>(stream), -1, x_layout == B200Q_LAYOUT_NHWC,
+                  y_layout == B200Q_LAYOUT_NHWC, add);
+}
+
+int b200q_conv2d_dev_route(void* handle) {
+  if (!handle) return set_error(B200Q_ERR_INVALID, "conv2d_dev_route: null handle");
+  ConvHandle* h = static_cast<ConvHandle*>(handle);
+  return h->use_tc ? 1 : (h->use_im2col ? 2 : 0);
 }
 
 int b200q_conv2d_dev_status(void* handle, void* stream) {

@@ -31,6 +31,13 @@ struct IGemmProblem {
   int kind;                               // IGEMM_KIND_*; for BF16 k_per_tap and the pitches are in BYTES (2 per element)
   const float* bias_f32;                  // BF16 kind: optional per-column bias
   int dependent_launch;                   // launch as a programmatic dependent of the previous kernel in the stream
+  // Fused residual Add (tpu.Add of this product's 8-bit output with another 8-bit tensor of the same shape and
+  // layout, Add.cpp:177-207): out = clamp(((v*m_self + 2^(s_self-1)) >> s_self) + ((r*m_res + 2^(s_res-1)) >> s_res),
+  // lo, hi) where v is the product's own requantised and saturated output, which is then not stored.  res == nullptr:
+  // no fusion.  |m| < 2^23 and shifts in [1,31] (everything fits 32 bits).
+  const void* res;
+  int res_unsigned;
+  int add_m_self, add_s_self, add_m_res, add_s_res, add_lo, add_hi;
   int per_row_params;                     // the epilogue's per-channel arrays index the GEMM's ROWS (transposed product);
                                           // 8-bit kinds with a fast dialect, n > 128
 };
@@ -53,6 +60,9 @@ struct IGemmArgs {
   int dependent_launch;
   int acc_bound;  // |accumulator| <= this for every 8-bit operand pair (valid when acc_small)
   unsigned long long wait_budget_ns;  // every mbarrier wait of the kernel gives up after this long
+  const uint8_t* res;                 // fused residual Add (see IGemmProblem); nullptr = none
+  int res_unsigned, add_m_self, add_s_self, add_m_res, add_s_res, add_lo, add_hi;
+  int band_m;                         // row tiles per band of the tile walk (<= 1: row-major over the column tiles)
   int expect_extra;                   // test aid: bytes added to what a stage's barrier expects (0 in normal use)
 };
 

@@ -23,6 +23,7 @@
 #include "internal.h"
 #include "ptx_sm100.cuh"
 #include <atomic>
+#include <cmath>
 
 #include "requant.cuh"
 
@@ -54,7 +55,8 @@ struct SmemLayout {
   static constexpr int CHAN_OFFSET = MISC_OFFSET + 16;           // {bias, multiplier, shift, -} of the tile's channels
   static constexpr int SLOW_OFFSET = CHAN_OFFSET + BLOCK_N * 16;  // per 32-channel chunk: the staged parameter form
   static constexpr int CHANK_OFFSET = SLOW_OFFSET + (BLOCK_N / 32) * 4;  // folded form: rounding constant + shifted zero point
-  static constexpr int TOTAL = CHANK_OFFSET + BLOCK_N * 4;
+  static constexpr int RES_OFFSET = (CHANK_OFFSET + BLOCK_N * 4 + 15) & ~15;  // fused Add: 512 bytes of scratch per epilogue warp
+  static constexpr int TOTAL = RES_OFFSET + 16 * 512;
   static constexpr int DYN_BYTES = TOTAL + 1024;                 // slack for manual 1024-byte alignment
   // always 16 epilogue warps (4 TMEM lane quarters x 4 column groups): a narrow tile is split finer instead of
   // leaving warps idle, its epilogue costs as much per element as a wide one's
@@ -71,6 +73,24 @@ struct TmemCols {
 
 // how a 32-channel chunk's requantisation parameters are staged (see the epilogue)
 enum { FORM_FOLD_QDM = 0, FORM_FAST = 1, FORM_GENERAL = 3, FORM_FOLD_HI = 4, FORM_FOLD_FUNNEL = 5 };
+
+// Tile index -> (row tile, column tile).  Tiles are walked in bands of `band_m` row tiles, column tile by column tile
+// inside a band, so that the tiles in flight at any moment (consecutive indices: the workers stride by their count)
+// form a roughly square block and share their operand rows in L2 instead of sweeping all of B once per row of tiles.
+__device__ __forceinline__ void tile_coords(const IGemmArgs& args, int tile, int& mt, int& nt) {
+  if (args.band_m <= 1) {
+    mt = tile / args.num_n_tiles;
+    nt = tile - mt * args.num_n_tiles;
+    return;
+  }
+  const int per_band = args.band_m * args.num_n_tiles;
+  const int band = tile / per_band;
+  const int idx = tile - band * per_band;
+  const int m_first = band * args.band_m;
+  const int height = min(args.band_m, args.num_m_tiles - m_first);
+  nt = idx / height;
+  mt = m_first + (idx - nt * height);
+}
 
 template <int THREADS>
 __device__ __forceinline__ void epi_bar_sync() {
@@ -196,7 +216,7 @@ __device__ __forceinline__ void form_constants(int form, bool in, int32_t bias, 
 // columns pixels).  Every epilogue thread then keeps its own row's constants in registers; no shared-memory
 // parameter read is left in the per-element path, whose 16 bytes per lane and element otherwise saturate the
 // load/store pipe of a short-K product.
-template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR, int TAPW, bool PERROW = false>
+template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR, int TAPW, bool PERROW = false, bool ADD = false>
 __global__ void __launch_bounds__(SmemLayout<BLOCK_N, STAGES, PAIR, TAPW>::NUM_THREADS, 1)
 igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const IGemmArgs args) {
@@ -270,8 +290,10 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       bool ok = true;
       ptx::griddep_wait();  // the operands may be the previous kernel's output (the set-up above overlapped its tail)
       for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
-        const int m0 = (tile / args.num_n_tiles) * TILE_M + (int)cta_rank * BLOCK_M;
-        const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
+        int mt, nt;
+        tile_coords(args, tile, mt, nt);
+        const int m0 = mt * TILE_M + (int)cta_rank * BLOCK_M;
+        const int n0 = nt * BLOCK_N;
         // k-block inside the tap and the tap's row shift are counted, not divided: this loop is serial
         int kc = 0, fx = 0;
         int a_row = m0 - args.tap_org_h * args.row_pitch - args.tap_org_w;  // tap (0,0)
@@ -423,8 +445,10 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     int32_t row_ck = 0;
     const uint32_t lead_tmem_empty0 = PAIR ? ptx::map_to_cta(tmem_empty_bar(0), 0) : 0u;
     for (int tile = worker; tile < num_tiles; tile += num_workers) {
-      const int m0 = (tile / args.num_n_tiles) * TILE_M + (int)cta_rank * BLOCK_M;
-      const int n0 = (tile % args.num_n_tiles) * BLOCK_N;
+      int mt, nt;
+      tile_coords(args, tile, mt, nt);
+      const int m0 = mt * TILE_M + (int)cta_rank * BLOCK_M;
+      const int n0 = nt * BLOCK_N;
       if (PERROW) {
         if (m0 != cached_n0) {  // (cached_n0 holds the row tile here) the constants of this thread's row
           const int ch = m0 + quarter * 32 + lane;
@@ -495,9 +519,6 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         epi_bar_sync<EPI_THREADS>();
         cached_n0 = n0;
       }
-      if (!ptx::mbar_wait_bounded(tmem_full_bar(acc), acc_phase, abort_flag, 4, args.wait_budget_ns)) break;
-      ptx::tc_fence_after_sync();
-
       const int row = m0 + quarter * 32 + lane;
       // where this row goes
       bool row_valid = row < args.rows;
@@ -532,9 +553,57 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       // parallelism than the read's latency, which the other warps of the scheduler cover).
       constexpr int CH = 16;
       const uint32_t t_warp = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + col0);
+      // Fused residual Add: the other operand's 16 bytes of a chunk, packed four to a register, requested one chunk
+      // ahead (the first before the wait for the accumulator) so that their latency hides behind the tensor-memory
+      // read and the requantisation of the chunk before.
+      // Transposed product (rows = channels): a chunk's residual bytes are 16 pixels x this warp's 32 channels, 32
+      // contiguous bytes per pixel.  Lane i fetches the 16-byte piece i (pixel i / 2, half i % 2) with one load; when
+      // the chunk is processed the pieces go through 512 bytes of warp-private shared memory, from which every lane
+      // reads its own channel's byte of each pixel.
+      const bool res_vec = ADD && PERROW && ((reinterpret_cast<uintptr_t>(args.res) & 15) == 0) && (chan_stride & 15) == 0;
+      uint8_t* const res_sm = smem + L::RES_OFFSET + (warp - 2) * 512;
+      auto load_res = [&](int cc_, uint32_t (&rw)[CH / 4]) {
+#pragma unroll
+        for (int w = 0; w < CH / 4; ++w) rw[w] = 0u;
+        const int cb = col0 + cc_ * CH;
+        const int nc = min(CH, args.n - (n0 + cb));
+        if (res_vec) {
+          if ((lane >> 1) < nc) {
+            const uint8_t* rp = args.res + (long long)(n0 + cb + (lane >> 1)) * chan_stride + (m0 + quarter * 32) + 16 * (lane & 1);
+            const uint4 v4 = __ldg(reinterpret_cast<const uint4*>(rp));
+            rw[0] = v4.x, rw[1] = v4.y, rw[2] = v4.z, rw[3] = v4.w;
+          }
+          return;
+        }
+        if (!row_valid || nc <= 0) return;
+        if (args.out_mode == IGEMM_OUT_NCHW) {
+          const uint8_t* rp = args.res + out_base + (long long)(n0 + cb) * chan_stride;
+#pragma unroll
+          for (int j = 0; j < CH; ++j)
+            if (j < nc) rw[j >> 2] |= (uint32_t)__ldg(rp + (long long)j * chan_stride) << (8 * (j & 3));
+        } else {
+          const uint8_t* rp = args.res + out_base + n0 + cb;
+          if (nc == CH && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+            const uint4 v4 = __ldg(reinterpret_cast<const uint4*>(rp));
+            rw[0] = v4.x, rw[1] = v4.y, rw[2] = v4.z, rw[3] = v4.w;
+          } else {
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+              if (j < nc) rw[j >> 2] |= (uint32_t)__ldg(rp + j) << (8 * (j & 3));
+          }
+        }
+      };
+      uint32_t res_next[CH / 4] = {0u, 0u, 0u, 0u};
+      if (ADD) load_res(0, res_next);
+      if (!ptx::mbar_wait_bounded(tmem_full_bar(acc), acc_phase, abort_flag, 4, args.wait_budget_ns)) break;
+      ptx::tc_fence_after_sync();
 #pragma unroll 1
       for (int cc = 0; cc < L::EPI_COLS / CH; ++cc) {
         const int cbase = col0 + cc * CH;
+        uint32_t res_cur[CH / 4];
+#pragma unroll
+        for (int w = 0; w < CH / 4; ++w) res_cur[w] = res_next[w];
+        if (ADD && cc + 1 < L::EPI_COLS / CH) load_res(cc + 1, res_next);
         uint32_t r[CH];
         ptx::tmem_ld_32x32b_x16(t_warp + (uint32_t)(cc * CH), r);
         ptx::tmem_ld_wait_16(r);
@@ -638,6 +707,26 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
         }
         const int ncols = min(CH, args.n - (n0 + cbase));
+        if (ADD && res_vec) {   // warp-uniform: every lane of the warp holds one piece
+          __syncwarp();         // the previous chunk's bytes have been read
+          *reinterpret_cast<uint4*>(res_sm + lane * 16) = make_uint4(res_cur[0], res_cur[1], res_cur[2], res_cur[3]);
+          __syncwarp();
+        }
+        if (ADD && row_valid) {
+          // fused residual Add: the product's own output (saturated to its type) and the other operand, each through
+          // its multiplier and half-up shift, summed and clamped to the Add's range (its ReLU is the lower bound)
+#pragma unroll
+          for (int j = 0; j < CH; ++j) q[j] = min(max(q[j], sat_lo2), sat_hi);   // (the packed store would have done it)
+          raw = false;
+          const int32_t hs = 1 << (args.add_s_self - 1), hr = 1 << (args.add_s_res - 1);
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            const uint32_t b = res_vec ? (uint32_t)res_sm[j * 32 + lane] : ((res_cur[j >> 2] >> (8 * (j & 3))) & 0xffu);
+            const int32_t x = args.res_unsigned ? (int32_t)b : (int32_t)(int8_t)b;
+            const int32_t v = ((q[j] * args.add_m_self + hs) >> args.add_s_self) + ((x * args.add_m_res + hr) >> args.add_s_res);
+            q[j] = min(max(v, args.add_lo), args.add_hi);
+          }
+        }
         if (args.out_mode == IGEMM_OUT_NCHW) {
           if (row_valid) {
             const long long off0 = out_base + (long long)(n0 + cbase) * chan_stride;
@@ -768,10 +857,10 @@ int make_tmap_u8_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
   return make_tmap_u8(map, base, 2, dims, strides, box);
 }
 
-template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR, int TAPW, bool PERROW = false>
+template <int BLOCK_N, int STAGES, int DIALECT, int RMODE, bool PAIR, int TAPW, bool PERROW = false, bool ADD = false>
 int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& args, int workers, cudaStream_t stream) {
   using L = SmemLayout<BLOCK_N, STAGES, PAIR, TAPW>;
-  auto kfn = igemm_i8_kernel<BLOCK_N, STAGES, DIALECT, RMODE, PAIR, TAPW, PERROW>;
+  auto kfn = igemm_i8_kernel<BLOCK_N, STAGES, DIALECT, RMODE, PAIR, TAPW, PERROW, ADD>;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(PAIR ? 2 * workers : workers);
@@ -797,6 +886,11 @@ template <int BLOCK_N, int STAGES, bool PAIR, int TAPW = 1>
 int launch_dialect(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& a, int workers, cudaStream_t s) {
   const int d = a.epi.dialect, r = a.epi.round_mode;
   if (a.bf16) return launch_one<BLOCK_N, STAGES, KIND_BF16_TAG, -1, PAIR, TAPW>(ta, tb, a, workers, s);
+  if (a.res != nullptr) {   // the fused residual Add is built for the dialect the BM168x lowering emits
+    if (d == B200Q_RQ_MULTIPLIER_SHIFT && r == B200Q_ROUND_HALF_UP && !a.bf16)
+      return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP, PAIR, TAPW, false, true>(ta, tb, a, workers, s);
+    return set_error(B200Q_ERR_UNSUPPORTED, "igemm: the fused Add exists for MultiplierShift / half-up requantisation only");
+  }
   if (d == B200Q_RQ_MULTIPLIER_SHIFT && r == B200Q_ROUND_HALF_UP)
     return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP, PAIR, TAPW>(ta, tb, a, workers, s);
   if (d == B200Q_RQ_QDM && r == B200Q_ROUND_HALF_AWAY_FROM_ZERO)
@@ -808,6 +902,11 @@ int launch_dialect(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs
 template <int BLOCK_N, int STAGES, bool PAIR>
 int launch_per_row(const CUtensorMap& ta, const CUtensorMap& tb, const IGemmArgs& a, int workers, cudaStream_t s) {
   const int d = a.epi.dialect, r = a.epi.round_mode;
+  if (a.res != nullptr) {
+    if (d == B200Q_RQ_MULTIPLIER_SHIFT && r == B200Q_ROUND_HALF_UP)
+      return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP, PAIR, 1, true, true>(ta, tb, a, workers, s);
+    return set_error(B200Q_ERR_UNSUPPORTED, "igemm: the fused Add exists for MultiplierShift / half-up requantisation only");
+  }
   if (d == B200Q_RQ_MULTIPLIER_SHIFT && r == B200Q_ROUND_HALF_UP)
     return launch_one<BLOCK_N, STAGES, B200Q_RQ_MULTIPLIER_SHIFT, B200Q_ROUND_HALF_UP, PAIR, 1, true>(ta, tb, a, workers, s);
   if (d == B200Q_RQ_QDM && r == B200Q_ROUND_HALF_AWAY_FROM_ZERO)
@@ -908,6 +1007,22 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   a.out = p.out;
   a.epi = epi;
   a.status = status;
+  a.res = static_cast<const uint8_t*>(p.res);
+  if (p.res != nullptr) {
+    const bool out8 = epi.out_dtype == B200Q_DT_I8 || epi.out_dtype == B200Q_DT_U8;
+    auto m_ok = [](int m) { return m > -(1 << 23) && m < (1 << 23); };
+    auto s_ok = [](int sft) { return sft >= 1 && sft <= 31; };
+    if (!out8 || p.kind == IGEMM_KIND_BF16 || !m_ok(p.add_m_self) || !m_ok(p.add_m_res) || !s_ok(p.add_s_self) || !s_ok(p.add_s_res) ||
+        p.out_mode == IGEMM_OUT_NHWC_BORDERED)
+      return set_error(B200Q_ERR_UNSUPPORTED, "tcgen05 igemm: fused Add needs 8-bit tensors, |multiplier| < 2^23, shifts in [1,31]");
+    a.res_unsigned = p.res_unsigned;
+    a.add_m_self = p.add_m_self;
+    a.add_s_self = p.add_s_self;
+    a.add_m_res = p.add_m_res;
+    a.add_s_res = p.add_s_res;
+    a.add_lo = p.add_lo;
+    a.add_hi = p.add_hi;
+  }
   a.wait_budget_ns = g_wait_budget_ns.load(std::memory_order_relaxed);
   a.expect_extra = g_expect_extra.load(std::memory_order_relaxed);
   a.bf16 = p.kind == IGEMM_KIND_BF16;
@@ -952,6 +1067,20 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
                    : ptx::make_idesc(2u, p.a_unsigned ? 0u : 1u, p.b_unsigned ? 0u : 1u, tile_m, (uint32_t)block_n);
   a.num_m_tiles = (p.rows + tile_m - 1) / tile_m;
   a.num_n_tiles = (p.n + block_n - 1) / block_n;
+  {
+    // band height of the tile walk: a wave of tiles (one per worker) whose A rows and B rows cost about the same would
+    // be sqrt(workers * block_n / tile_m) row tiles high; twice that measured best on the 8192^3 GEMM (bands of 8 / 12 /
+    // 16 / 24 / 32 row tiles: 3092 / 3127 / 3172 / 3127 / 2993 TOPS, row-major walk 2952).  B200Q_IGEMM_BAND=<n>
+    // overrides (1 = the row-major walk), for A/B timing.
+    const int workers_est = pair ? sms / 2 : sms;
+    int band = (int)(2.0 * sqrt((double)workers_est * block_n / tile_m) + 0.5);
+    static const int band_env = [] {
+      const char* v = getenv("B200Q_IGEMM_BAND");
+      return v ? atoi(v) : 0;
+    }();
+    if (band_env > 0) band = band_env;
+    a.band_m = a.num_n_tiles > 1 ? (band < a.num_m_tiles ? band : a.num_m_tiles) : 1;
+  }
 
   CUtensorMap ta, tb;
   // (a_pitch < k_per_tap: overlapping rows, each spanning several consecutive pixels; the caller keeps

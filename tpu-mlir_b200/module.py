@@ -39,9 +39,16 @@ def _P(t):
 
 
 class module:  # noqa: N801  (name of the reference class)
-    def __init__(self, device: Optional[int] = None, channels_last: bool = False, cuda_graph: bool = False):
+    def __init__(self, device: Optional[int] = None, channels_last: bool = False, cuda_graph: bool = False,
+                 fuse_residual_add: bool = False):
         import torch
         self.channels_last = bool(channels_last)
+        # A tpu.Add whose later operand is a convolution output nobody else reads runs inside that convolution's
+        # kernel: the Add's tensor receives the same values, the convolution's own tensor is never written (reading
+        # it raises).  Off by default: the reference materialises every tensor.
+        self.fuse_residual_add = bool(fuse_residual_add)
+        self._fuse_into: Dict[str, dict] = {}     # convolution name -> the Add op fused into it
+        self._fused_adds: Dict[str, str] = {}     # Add name -> convolution name
         self.cuda_graph = bool(cuda_graph)  # invoke() without hooks replays one captured CUDA graph of all ops
         self._graph = None
         self._nhwc = set()  # names of the tensors stored as [N][H][W][C]
@@ -89,9 +96,45 @@ class module:  # noqa: N801  (name of the reference class)
     def _build_plans(self):
         self._release_handles()
         self._plans, self._keep, self._status, self._graph = [], [], [], None
+        self._fuse_into, self._fused_adds = self._find_residual_adds() if self.fuse_residual_add else ({}, {})
         for op in self.graph["ops"]:
             self._plans.append(self._plan(op))
         self.torch.cuda.synchronize(self.device)
+
+    def _find_residual_adds(self):
+        """Adds that can run in the epilogue of the convolution producing their later operand."""
+        ops = self.graph["ops"]
+        order = {op["name"]: i for i, op in enumerate(ops)}
+        by_name = {op["name"]: op for op in ops}
+        uses: Dict[str, int] = {}
+        for op in ops:
+            for n in op["inputs"]:
+                uses[n] = uses.get(n, 0) + 1
+        fuse_into, fused = {}, {}
+        for op in ops:
+            if op["type"] != "tpu.Add" or len(op["inputs"]) != 2:
+                continue
+            a = op.get("attrs", {})
+            m, s = a.get("multipliers", []), a.get("rshifts", [])
+            if len(m) != 2 or len(s) != 2 or not all(abs(int(v)) < (1 << 23) for v in m) or not all(1 <= int(v) <= 31 for v in s):
+                continue
+            i0, i1 = op["inputs"]
+            later = i0 if order.get(i0, -1) > order.get(i1, -1) else i1
+            other = i1 if later == i0 else i0
+            prod = by_name.get(later)
+            if prod is None or prod["type"] != "tpu.Conv2D" or uses.get(later, 0) != 1 or later in self.graph["outputs"]:
+                continue
+            if prod.get("attrs", {}).get("group", 1) != 1 or later in fuse_into or \
+                    prod.get("attrs", {}).get("quant_mode", "MultiplierShift") != "MultiplierShift":   # the kernel's fused form
+                continue
+            infos = [self._info(later), self._info(other), self._info(op["name"])]
+            if any(i["dtype"] not in ("i8", "u8") for i in infos) or list(infos[0]["shape"]) != list(infos[1]["shape"]):
+                continue
+            if (later in self._nhwc) != (other in self._nhwc) or (later in self._nhwc) != (op["name"] in self._nhwc):
+                continue
+            fuse_into[later] = dict(add=op, other=other, self_index=0 if later == i0 else 1)
+            fused[op["name"]] = later
+        return fuse_into, fused
 
     def _release_handles(self):
         for h in self._handles:
@@ -171,9 +214,25 @@ class module:  # noqa: N801  (name of the reference class)
             self._handles.append(h)
             self._keep.append(cop)
             self._status.append((op["name"], h))
+            xl = L.LAYOUT_NHWC if op["inputs"][0] in self._nhwc else L.LAYOUT_NCHW
+            yl = L.LAYOUT_NHWC if op["name"] in self._nhwc else L.LAYOUT_NCHW
+            fz = self._fuse_into.get(op["name"])
+            if fz is not None and lib.b200q_conv2d_dev_route(h) == 0:      # the CUDA-core route does not fuse
+                del self._fused_adds[fz["add"]["name"]]
+                del self._fuse_into[op["name"]]
+                fz = None
+            if fz is not None:
+                add, si = fz["add"], fz["self_index"]
+                aa = add["attrs"]
+                res = self.tensors[fz["other"]]
+                fa = L.FusedAdd(residual=res.data_ptr(), residual_dtype=_DT[self._info(fz["other"])["dtype"]],
+                                conv_multiplier=int(aa["multipliers"][si]), conv_rshift=int(aa["rshifts"][si]),
+                                residual_multiplier=int(aa["multipliers"][1 - si]), residual_rshift=int(aa["rshifts"][1 - si]),
+                                do_relu=int(bool(aa.get("do_relu", False))), out_dtype=_DT[self._info(add["name"])["dtype"]])
+                self._keep.append(fa)
+                add_out = self.tensors[add["name"]]
+                return lambda: L.check(lib.b200q_conv2d_dev_run_add(h, _P(ins[0]), xl, _P(add_out), yl, C.byref(fa), stream()))
             if self.channels_last:
-                xl = L.LAYOUT_NHWC if op["inputs"][0] in self._nhwc else L.LAYOUT_NCHW
-                yl = L.LAYOUT_NHWC if op["name"] in self._nhwc else L.LAYOUT_NCHW
                 return lambda: L.check(lib.b200q_conv2d_dev_run_layout(h, _P(ins[0]), xl, _P(out), yl, stream()))
             return lambda: L.check(lib.b200q_conv2d_dev_run(h, _P(ins[0]), _P(out), stream()))
         if t == "tpu.MatMul":
@@ -219,6 +278,8 @@ class module:  # noqa: N801  (name of the reference class)
             return lambda: L.check(lib.b200q_gemm_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(w_nk), L.DT_I8, M, N, K,
                                                          C.byref(e), _P(out), _P(status), L.ALGO_AUTO, stream()))
         if t == "tpu.Add":
+            if op["name"] in self._fused_adds:      # computed by the producing convolution's kernel
+                return lambda: None
             m, s = a["multipliers"], a["rshifts"]
             n = out.numel()
             return lambda: L.check(lib.b200q_add_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(ins[1]), _DT[iinfo[1]["dtype"]],
@@ -323,8 +384,9 @@ class module:  # noqa: N801  (name of the reference class)
 
     def invoke_at(self, name: str):
         """One op, with its hooks; returns its output as stored (ModuleInterpreter.cpp:1210-1231)."""
+        target = self._fused_adds.get(name, name)      # a fused Add is computed by its convolution's kernel
         for op, run in zip(self.graph["ops"], self._plans):
-            if op["name"] == name:
+            if op["name"] == target:
                 self._expressed = False
                 self._run_ops([(op, run)])
                 return self.get_tensor(name)
@@ -385,6 +447,9 @@ class module:  # noqa: N801  (name of the reference class)
         return self._nchw(name).cpu().numpy()
 
     def _nchw(self, name: str):
+        if name in self._fuse_into:
+            raise L.B200QError(L.ERR_UNSUPPORTED, f"{name} is not materialised: its Add ({self._fuse_into[name]['add']['name']}) runs inside "
+                               "the convolution kernel (module(fuse_residual_add=True))")
         t = self.tensors[name]
         return t.permute(0, 3, 1, 2).contiguous() if name in self._nhwc else t
 
@@ -398,7 +463,7 @@ class module:  # noqa: N801  (name of the reference class)
 
     def get_all_tensor(self) -> Dict[str, np.ndarray]:
         self.check_status()
-        return {n: self.get_fp32_tensor(n) for n in self.all_tensor_names}
+        return {n: self.get_fp32_tensor(n) for n in self.all_tensor_names if n not in self._fuse_into}
 
     def get_tensor_qinfo(self, name: str):
         info = self._info(name)
