@@ -427,7 +427,7 @@ def resnet50_line(R, steps, warmup, check=True):
     graph, weights = resnet50.lower_int8(ops, table, batch=per)
     m = module(channels_last=os.environ.get("B200Q_RESNET_LAYOUT", "nhwc") == "nhwc",
                cuda_graph=os.environ.get("B200Q_RESNET_GRAPH", "1") == "1",
-               fuse_residual_add=os.environ.get("B200Q_RESNET_FUSE_ADD", "1") == "1")
+               fuse_residual_add=os.environ.get("B200Q_RESNET_FUSE_ADD", "0") == "1")
     m.load(graph, weights)
     n_fused = len(m._fused_adds)
     x_h = torch.from_numpy(synth.calibration_images(seed=5, count=per, start=R.rank * per)).pin_memory()
@@ -501,9 +501,10 @@ def calibration_line(R, total=None):
     images = torch.from_numpy(synth.calibration_images(seed=4, count=per, start=R.rank * per)).to(R.dev)
     fwd = resnet50.Fp32Forward(ops, R.dev)
     cal = ShardedCalibrator(fwd, dist=R.dist)
-    batches = [images[i:i + 32] for i in range(0, per, 32)]
-    if per >= 64:
-        cal.run(batches[:2], samples_per_rank=64)      # warm-up: cuDNN algorithm choice, NCCL channels, allocator
+    CB = int(os.environ.get("B200Q_CALIB_BATCH", "32"))      # samples per forward call
+    batches = [images[i:i + CB] for i in range(0, per, CB)]
+    if per >= 2 * CB:
+        cal.run(batches[:2], samples_per_rank=2 * CB)      # warm-up: cuDNN algorithm choice, NCCL channels, allocator
     R.barrier()
     t0 = time.perf_counter()
     res = cal.run(batches, samples_per_rank=per)
@@ -518,7 +519,7 @@ def calibration_line(R, total=None):
                 scaling="strong", n_gpus=R.world, table_sha256=digest,
                 config=dict(workload=f"ResNet-50 fp32 forward (torch) + min/max, streaming histogram (2048 bins) and KLD on "
                                      f"{len(res)} tensors, {TOTAL} synthetic samples sharded over the ranks",
-                            tensors=len(res), samples_per_rank=per,
+                            tensors=len(res), samples_per_rank=per, forward_batch=CB,
                             allreduce_bytes=cal.allreduce_bytes, allgather_bytes=int(len(res) * per * 8 * R.world) if R.dist else 0,
                             activations_kept_on_device_bytes=cal.cached_bytes,
                             phase_seconds_max_over_ranks=dict(zip(sorted(cal.timings), phases))))

@@ -306,7 +306,7 @@ typedef struct {
   int32_t q_group_size;   /* multiple of 64 */
   int32_t w_transpose;    /* 1 */
   int32_t with_bias;
-  int32_t out_dtype;      /* B200Q_DT_BF16 */
+  int32_t out_dtype;      /* B200Q_DT_BF16 (w4bf16) or B200Q_DT_F16 (w4f16): the type of input, scale and output */
   int32_t weight_version; /* bump after rewriting the weight buffers in place */
 } b200q_a16matmul_desc;
 
@@ -326,6 +326,14 @@ int b200q_a16_w4_dev(const void *x_bf16, const void *wq, const void *scale_bf16,
                      const float *bias_f32, void *y_bf16, int64_t M, int64_t N, int64_t K, int32_t group,
                      int32_t *status, void *stream);
 
+/* The same call with the 16-bit type named: dtype = B200Q_DT_BF16 (w4bf16) or B200Q_DT_F16 (w4f16: x, scale and y are
+ * IEEE half, the output is rounded to nearest even like F16(), lib/Support/Float16.cpp:763-767).  The f16 form runs the
+ * CUDA-core kernel for one token (two where its shape limits allow) and the fused tensor-core kernel (kind::f16 on f16
+ * operands) for everything else. */
+int b200q_a16_w4_dev_dt(const void *x, const void *wq, const void *scale, const void *zp_u8, const float *bias_f32,
+                        void *y, int64_t M, int64_t N, int64_t K, int32_t group, int32_t dtype, int32_t *status,
+                        void *stream);
+
 /* Test aid (no counterpart in the reference): makes a bounded wait of the tensor-core INT8 GEMM/convolution kernel run
  * out without faulting anything.  While extra_tx_bytes > 0 every pipeline stage's barrier expects that many bytes more
  * than the stage's loads deliver, so the consumer's wait ends after `budget_ns` (0 = the default of 2 s) with the
@@ -342,19 +350,22 @@ void b200q_debug_set_wait_fault(int32_t extra_tx_bytes, int64_t budget_ns);
 int b200q_probe_tensor_peak(int32_t kind, int32_t pair, int32_t kblocks, int32_t launches, double *ms, double *ops,
                             void *stream);
 
-/* Which kernel serves b200q_a16_*, process-wide: 0 = chosen per call (default: one or two tokens take the CUDA-core
- * GEMV, everything else the fused-dequantisation tensor-core kernel); 1 = the decode kernels only (8 tokens per
- * launch); 2 = the tensor-core kernel for every M; 3 = handle API with M > 8: dequantise once into a bf16 copy kept in
- * the handle and run a bf16 GEMM (rounds the weight to bf16, which the reference does not).  A measuring control;
- * no counterpart in the reference. */
+/* Which kernel serves b200q_a16_*, process-wide: 0 = chosen per call (default: up to 8 tokens take the CUDA-core
+ * decode kernels; a handle that sees 512 tokens or more dequantises once into a bf16 copy and runs a bf16 GEMM;
+ * everything else takes the fused-dequantisation tensor-core kernel on the packed weights); 1 = the decode kernels
+ * only (8 tokens per launch); 2 = the fused tensor-core kernel for every M; 3 = handle API with M > 8: the bf16 copy
+ * (rounds the weight to bf16, which the reference does not).  A measuring control; no counterpart in the reference. */
 void b200q_a16_set_route(int32_t route);
 
-/* Device face with a handle: the tensors stay the caller's (not copied).  M <= 8 runs the decode kernel on the
- * packed weights; larger M dequantises the weight once into bf16 (kept in the handle, N*K*2 bytes) and runs
- * a bf16 tensor-core GEMM with fp32 accumulation.  b200q_a16_dev_status synchronises the stream and reports a
- * kernel-side timeout. */
+/* Device face with a handle: the tensors stay the caller's (not copied) and are declared constant for the life of
+ * the handle (the decode kernel may request weights before the previous kernel of the stream has finished).  M <= 8
+ * runs the decode kernels on the packed weights, M < 512 the fused tensor-core kernel on the packed weights; from 512
+ * tokens on the weight is dequantised once into bf16 (kept in the handle, N*K*2 bytes) for a bf16 tensor-core GEMM
+ * with fp32 accumulation.  b200q_a16_dev_status synchronises the stream and reports a kernel-side timeout. */
 int b200q_a16_dev_create(const void *wq, const void *scale_bf16, const void *zp_u8, const float *bias_f32,
                          int64_t N, int64_t K, int32_t group, void **handle);
+int b200q_a16_dev_create_dt(const void *wq, const void *scale, const void *zp_u8, const float *bias_f32, int64_t N,
+                            int64_t K, int32_t group, int32_t dtype, void **handle); /* dtype: B200Q_DT_BF16 / _F16 */
 int b200q_a16_dev_run(void *handle, const void *x_bf16, void *y_bf16, int64_t M, void *stream);
 int b200q_a16_dev_status(void *handle, void *stream);
 void b200q_a16_dev_destroy(void **handle);

@@ -95,6 +95,12 @@ def lib():
         L.orc_f32_to_bf16_bits.argtypes = [f32]
         L.orc_a16matmul_w4.restype = None
         L.orc_a16matmul_w4.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]
+        L.orc_a16matmul_w4_f16.restype = None
+        L.orc_a16matmul_w4_f16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]
+        L.orc_f32_to_f16_bits.restype = C.c_uint16
+        L.orc_f32_to_f16_bits.argtypes = [f32]
+        L.orc_f16_bits_to_f32.restype = C.c_float
+        L.orc_f16_bits_to_f32.argtypes = [C.c_uint16]
         L.orc_a16_dequant_w4.restype = None
         L.orc_a16_dequant_w4.argtypes = [vp, vp, vp, i64, i64, i64, vp]
         L.orc_histogram_f32.restype = None
@@ -324,6 +330,20 @@ def f32_to_bf16_bits(x):
     return np.array([f(float(v)) for v in x.ravel()], dtype=np.uint16).reshape(x.shape)
 
 
+def f32_to_f16_bits(x):
+    """F16() of the reference (Float16.cpp:763-767,:663-714), elementwise, returning uint16 bit patterns."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    f = lib().orc_f32_to_f16_bits
+    return np.array([f(float(v)) for v in x.ravel()], dtype=np.uint16).reshape(x.shape)
+
+
+def f16_bits_to_f32(b):
+    """f16_to_f32 of the reference (Float16.cpp:776-786)."""
+    b = np.asarray(b, dtype=np.uint16)
+    f = lib().orc_f16_bits_to_f32
+    return np.array([f(int(v)) for v in b.ravel()], dtype=np.float32).reshape(b.shape)
+
+
 def bf16_bits_to_f32(b):
     return (np.asarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
 
@@ -335,17 +355,18 @@ def f32_to_bf16_bits_fast(x):
     return r.astype(np.uint16)
 
 
-def a16matmul_w4(x_bits, wq, scale_bits, zp, bias=None, *, group=64):
+def a16matmul_w4(x_bits, wq, scale_bits, zp, bias=None, *, group=64, f16=False):
     """tpu.A16MatMul static w4 path with w_transpose=true (A16MatMul.cpp:171-208,:240-246).
-    x_bits uint16 [M,K] (bf16), wq uint8 [N,K/2], scale_bits uint16 [N*K/g], zp uint8 [N*K/g] -> uint16 [M,N]."""
+    x_bits uint16 [M,K] (bf16, or f16 with ``f16=True``), wq uint8 [N,K/2], scale_bits uint16 [N*K/g] (same type as x),
+    zp uint8 [N*K/g] -> uint16 [M,N] (same type)."""
     x_bits = _c(x_bits, np.uint16)
     wq = _c(wq, np.uint8)
     M, K = x_bits.shape
     N = wq.shape[0]
     assert wq.shape[1] * 2 == K
     y = np.empty((M, N), dtype=np.uint16)
-    lib().orc_a16matmul_w4(_p(x_bits), _p(wq), _p(_c(scale_bits, np.uint16)), _p(_c(zp, np.uint8)),
-                           _p(_c(bias, np.float32)), M, K, N, group, _p(y))
+    fn = lib().orc_a16matmul_w4_f16 if f16 else lib().orc_a16matmul_w4
+    fn(_p(x_bits), _p(wq), _p(_c(scale_bits, np.uint16)), _p(_c(zp, np.uint8)), _p(_c(bias, np.float32)), M, K, N, group, _p(y))
     return y
 
 

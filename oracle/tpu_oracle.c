@@ -492,6 +492,51 @@ uint16_t orc_f32_to_bf16_bits(float f) {
   return (uint16_t)(sign << 15);
 }
 
+/* F16(): lib/Support/Float16.cpp:763-767 f32_to_f16 -> fp32_to_fp16_all (:663-714) with ROUNDING_HALF_TO_EVEN:
+ * normal range (biased fp32 exponent 113..254): the 32-bit pattern is rounded half-to-even at bit 13 and converted
+ * exactly (a carry past 65504 gives infinity); exponent 1..112: the 24-bit significand is shifted right by
+ * (113 - exp) + 13 with the same rounding (fp16 subnormals; shifts of 64 and more are undefined in the reference and
+ * give zero here); NaN -> 0x7fff; infinities and zeros keep their sign; fp32 denormals -> signed zero. */
+uint16_t orc_f32_to_f16_bits(float f) {
+  uint32_t bits;
+  memcpy(&bits, &f, 4);
+  const uint32_t exp = (bits >> 23) & 0xff, frac = bits & 0x7fffff, sign = bits >> 31;
+  if (exp > 112 && exp < 255) {
+    const int64_t r = orc_rshift_round((int64_t)bits, 13, RM_HALF_EVEN);
+    const uint32_t b32 = (uint32_t)((r << 13) & 0xFFFFFFFFll);
+    const uint32_t e = (b32 >> 23) & 0xff, m = b32 & 0x7fffff;      /* m has 13 zero low bits now */
+    if (e >= 143) return (uint16_t)((sign << 15) | 0x7c00);          /* 2^16 and above: infinity */
+    return (uint16_t)((sign << 15) | ((e - 112) << 10) | (m >> 13));
+  }
+  if (exp > 0 && exp <= 112) {
+    const int shift = (113 - (int)exp) + 13;
+    if (shift >= 64) return (uint16_t)(sign << 15);
+    const int64_t mant = (int64_t)frac + (1 << 23);
+    const int64_t r = orc_rshift_round(mant, shift, RM_HALF_EVEN);   /* magnitude: the reference negates around the shift */
+    return (uint16_t)((sign << 15) | (uint32_t)(r & 0x7fff));
+  }
+  if (exp == 0xff) return frac ? 0x7fff : (uint16_t)(sign ? 0xfc00 : 0x7c00);
+  return (uint16_t)(sign << 15);
+}
+
+/* f16_to_f32 (Float16.cpp:776-786): NaN -> 0xFFC00000, everything else exact. */
+float orc_f16_bits_to_f32(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h >> 15) << 31, e = (h >> 10) & 0x1f, m = h & 0x3ff;
+  uint32_t bits;
+  if (e == 31) bits = m ? 0xFFC00000u : (sign | 0x7f800000u);
+  else if (e != 0) bits = sign | ((e + 112) << 23) | (m << 13);
+  else if (m == 0) bits = sign;
+  else {
+    int sh = 0;
+    uint32_t mm = m;
+    while (!(mm & 0x400)) { mm <<= 1; ++sh; }
+    bits = sign | ((uint32_t)(113 - sh) << 23) | ((mm & 0x3ff) << 13);
+  }
+  float f;
+  memcpy(&f, &bits, 4);
+  return f;
+}
+
 float orc_bf16_bits_to_f32(uint16_t b) {
   uint32_t bits = (uint32_t)b << 16;
   float f;
@@ -507,18 +552,18 @@ float orc_bf16_bits_to_f32(uint16_t b) {
  * increasing k, which is one admissible order (tolerance, not bit parity, applies to this op).
  *   x: bf16 bits [M,K]; wq: bytes [N, K/2]; scale: bf16 bits [N*K/g]; zp: u8 [N*K/g]; bias f32 [N] or NULL.
  */
-void orc_a16matmul_w4(const uint16_t *x, const uint8_t *wq, const uint16_t *scale, const uint8_t *zp,
-                      const float *bias, int64_t M, int64_t K, int64_t N, int64_t group, uint16_t *y) {
+static void a16matmul_w4_any(const uint16_t *x, const uint8_t *wq, const uint16_t *scale, const uint8_t *zp,
+                             const float *bias, int64_t M, int64_t K, int64_t N, int64_t group, uint16_t *y, int is_f16) {
   float *W = (float *)malloc(sizeof(float) * (size_t)(N * K));
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < N * K; i += 2) {
     /* group > 0 and even => i and i+1 share a group */
     int64_t qi = i / group;
-    float s = orc_bf16_bits_to_f32(scale[qi]);
+    float s = is_f16 ? orc_f16_bits_to_f32(scale[qi]) : orc_bf16_bits_to_f32(scale[qi]);
     int z = zp[qi];
     W[i] = (float)(((int)wq[i / 2] & 0x0F) - z) * s;
     int64_t qj = (i + 1) / group;
-    float s1 = orc_bf16_bits_to_f32(scale[qj]);
+    float s1 = is_f16 ? orc_f16_bits_to_f32(scale[qj]) : orc_bf16_bits_to_f32(scale[qj]);
     int z1 = zp[qj];
     W[i + 1] = (float)(((int)wq[(i + 1) / 2] >> 4) - z1) * s1;
   }
@@ -526,11 +571,23 @@ void orc_a16matmul_w4(const uint16_t *x, const uint8_t *wq, const uint16_t *scal
   for (int64_t m = 0; m < M; ++m)
     for (int64_t n = 0; n < N; ++n) {
       float acc = 0.f;
-      for (int64_t k = 0; k < K; ++k) acc += orc_bf16_bits_to_f32(x[m * K + k]) * W[n * K + k];
+      for (int64_t k = 0; k < K; ++k)
+        acc += (is_f16 ? orc_f16_bits_to_f32(x[m * K + k]) : orc_bf16_bits_to_f32(x[m * K + k])) * W[n * K + k];
       if (bias) acc += bias[n];
-      y[m * N + n] = orc_f32_to_bf16_bits(acc);
+      y[m * N + n] = is_f16 ? orc_f32_to_f16_bits(acc) : orc_f32_to_bf16_bits(acc);
     }
   free(W);
+}
+
+void orc_a16matmul_w4(const uint16_t *x, const uint8_t *wq, const uint16_t *scale, const uint8_t *zp,
+                      const float *bias, int64_t M, int64_t K, int64_t N, int64_t group, uint16_t *y) {
+  a16matmul_w4_any(x, wq, scale, zp, bias, M, K, N, group, y, 0);
+}
+
+/* The same op with f16 activations, scales and output (the op's storage type decides, A16MatMul.cpp:240-246). */
+void orc_a16matmul_w4_f16(const uint16_t *x, const uint8_t *wq, const uint16_t *scale, const uint8_t *zp,
+                          const float *bias, int64_t M, int64_t K, int64_t N, int64_t group, uint16_t *y) {
+  a16matmul_w4_any(x, wq, scale, zp, bias, M, K, N, group, y, 1);
 }
 
 /* fp32 dequantised weight only (used by the fp32-GEMM timing leg and by tests) */

@@ -182,3 +182,59 @@ def test_prefill_ragged_with_bias(route):
     check(run_handle(c, M, N, K, g, bias), ref)
     route(3)
     check_rounded_weight(run_handle(c, M, N, K, g, bias), oracle.bf16_bits_to_f32(ref))
+
+
+# ------------------------------------------------------------------ w4f16
+def check_f16(y_bits, ref_bits):
+    """The same plain bound on IEEE half outputs."""
+    y = np.asarray(y_bits, dtype=np.uint16).view(np.float16).astype(np.float64)
+    r = np.asarray(ref_bits, dtype=np.uint16).view(np.float16).astype(np.float64)
+    rms = np.sqrt(np.mean(r * r))
+    bad = np.abs(y - r) > 1e-2 * np.maximum(np.abs(r), 1e-2 * rms)
+    assert not bad.any(), (int(bad.sum()), float(np.abs(y - r).max()), float(rms))
+
+
+@pytest.mark.parametrize("case", [dict(M=1, K=4096, N=11008, g=64), dict(M=2, K=4096, N=1000, g=64), dict(M=1, K=96, N=7, g=32),
+                                  dict(M=5, K=1024, N=300, g=128), dict(M=16, K=4096, N=2048, g=64),
+                                  dict(M=100, K=512, N=384, g=64), dict(M=300, K=2048, N=1000, g=256)])
+def test_w4f16_device_face(case):
+    """out_dtype = F16 (A16MatMul.cpp:240-246 rounds with F16()): f16 activations and scales, f16 output rounded to
+    nearest even; one or two tokens on the CUDA cores, everything else through kind::f16 on f16 operands."""
+    M, K, N, g = case["M"], case["K"], case["N"], case["g"]
+    c = synth.a16_w4(seed=11, M=M, K=K, N=N, group=g, f16=True)
+    bias = np.random.default_rng(2).standard_normal(N).astype(np.float32)
+    ref = oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], bias, group=g, f16=True)
+    x, wq, sc, zp, b = dev(c["x"]), dev(c["wq"]), dev(c["scale"]), dev(c["zp"]), dev(bias)
+    y = torch.empty((M, N), dtype=torch.uint16, device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    L.check(L.lib().b200q_a16_w4_dev_dt(ptr(x), ptr(wq), ptr(sc), ptr(zp), ptr(b), ptr(y), M, N, K, g, L.DT_F16, ptr(st), None))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    check_f16(y.cpu().numpy(), ref)
+    # handle API
+    h = C.c_void_p()
+    L.check(L.lib().b200q_a16_dev_create_dt(ptr(wq), ptr(sc), ptr(zp), ptr(b), N, K, g, L.DT_F16, C.byref(h)))
+    y2 = torch.empty_like(y)
+    L.check(L.lib().b200q_a16_dev_run(h, ptr(x), ptr(y2), M, None))
+    L.check(L.lib().b200q_a16_dev_status(h, None))
+    L.lib().b200q_a16_dev_destroy(C.byref(h))
+    assert torch.equal(y, y2)
+
+
+def test_w4f16_operator_face_and_exact_rounding():
+    """Through host float buffers; and on a case whose fp32 sums are exact (integer activations, power-of-two scales) the
+    f16 output must be the reference's F16() rounding bit for bit."""
+    M, K, N, g = 3, 256, 64, 64
+    rng = np.random.default_rng(5)
+    q = rng.integers(0, 16, size=(N, K), dtype=np.uint8)
+    wq = (q[:, 0::2] | (q[:, 1::2] << 4)).astype(np.uint8)
+    scale = np.full(N * K // g, 2.0 ** -9, np.float32) * rng.choice([1.0, 2.0, 4.0], N * K // g).astype(np.float32)
+    zp = rng.integers(0, 16, size=N * K // g, dtype=np.uint8)
+    x = rng.integers(-3, 4, size=(M, K)).astype(np.float32)         # every product and partial sum is exact in fp32
+    ref = oracle.a16matmul_w4(x.astype(np.float16).view(np.uint16), wq, scale.astype(np.float16).view(np.uint16), zp, group=g, f16=True)
+    op = A16MatMulOp(M=M, K=K, N=N, q_group_size=g, out_dtype=L.DT_F16)
+    out = np.zeros((M, N), np.float32)
+    p = InferenceParameter(inputs=[x, wq.astype(np.float32), scale, zp.astype(np.float32), None], outputs=[out])
+    op.inference(p)
+    assert np.array_equal(out.astype(np.float16).view(np.uint16), ref)
+    assert np.array_equal(out.astype(np.float16).astype(np.float32), out), "output is f16-representable"

@@ -195,3 +195,30 @@ def test_bf16_conversion_matches_compiled_reference():
         got = oracle.bf16_bits_to_f32(np.array([b], dtype=np.uint16))[0]
         want = np.float32(R.ref_bf16_to_f32(b))
         assert got.tobytes() == want.tobytes() or (np.isnan(got) and np.isnan(want)), hex(b)
+
+
+@pytest.mark.skipif(not oracle.ref_float16_available(), reason="compiled reference Float16.cpp not present")
+def test_f16_conversion_matches_compiled_reference():
+    """The oracle's F16 rounding against the reference's own f32_to_f16 / f16_to_f32 (lib/Support/Float16.cpp:763-786):
+    random bit patterns whose magnitude fp16 can express or nearly so, the subnormal band, ties, overflow to infinity,
+    infinities, NaNs, zeros, fp32 denormals; and every fp16 pattern back to fp32.  (Inputs below 2^-63 make the
+    reference shift by 64 bits or more, which C leaves undefined: not compared.)"""
+    R = oracle.ref_float16()
+    rng = np.random.default_rng(1)
+    exps = rng.integers(127 - 40, 127 + 18, 60000).astype(np.uint32)       # 2^-40 .. 2^17
+    bits = (rng.integers(0, 2, 60000).astype(np.uint32) << 31) | (exps << 23) | rng.integers(0, 1 << 23, 60000).astype(np.uint32)
+    edge = [0, 0x80000000, 0x7f800000, 0xff800000, 0x7fc00000, 0x7f800001, 0x00000001, 0x007fffff, 0x477fe000, 0x477ff000,
+            0x477fefff, 0x477ff001, 0xc77ff000, 0x47800000, 0x38800000, 0x387fffff, 0x387fe000, 0x33800000, 0x33000000,
+            0x33000001, 0x32ffffff, 0x3c001000, 0x3c003000, 0x3c000fff, 0x3c001001, 0x7f7fffff, 0xb3000001]
+    bits = np.concatenate([bits, np.array(edge, dtype=np.uint32)])
+    f = oracle.lib().orc_f32_to_f16_bits
+    for v, b in zip(bits.view(np.float32), bits):
+        assert int(f(float(v))) == int(R.ref_f32_to_f16(float(v))) & 0xffff, hex(int(b))
+    # and numpy's IEEE conversion agrees on everything but the NaN pattern: what the kernels' hardware rounding computes
+    finite = bits.view(np.float32)[np.isfinite(bits.view(np.float32))]
+    with np.errstate(over="ignore"):
+        assert np.array_equal(oracle.f32_to_f16_bits(finite[:5000]), finite[:5000].astype(np.float16).view(np.uint16))
+    g = oracle.lib().orc_f16_bits_to_f32
+    for h in range(1 << 16):
+        got, want = np.float32(g(h)), np.float32(R.ref_f16_to_f32(h))
+        assert got.tobytes() == want.tobytes() or (np.isnan(got) and np.isnan(want)), hex(h)

@@ -118,6 +118,10 @@ SIGNATURES = {
     "b200q_a16_w4_dev": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
                                    C.c_void_p]),
     "b200q_a16_set_route": (None, [C.c_int32]),
+    "b200q_a16_w4_dev_dt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                      C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "b200q_a16_dev_create_dt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
+                                          C.POINTER(C.c_void_p)]),
     "b200q_debug_set_wait_fault": (None, [C.c_int32, C.c_int64]),
     "b200q_probe_tensor_peak": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_double), C.POINTER(C.c_double), C.c_void_p]),
     "b200q_a16_dev_create": (C.c_int, [C.c_void_p] * 4 + [C.c_int64, C.c_int64, C.c_int32, _VPP]),

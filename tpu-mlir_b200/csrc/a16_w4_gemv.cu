@@ -15,6 +15,7 @@
 // to the nibble order the extraction yields.  The group scale multiplies the fp32 partial sum of each group,
 // so the only rounding is fp32 accumulation.  Every wait is bounded; a wait that runs out sets *status.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "a16.h"
 #include "internal.h"
@@ -47,6 +48,19 @@ __device__ __forceinline__ void fma2_f32_bf16(float& acc, uint32_t a, uint32_t b
       "mov.b32 {bl, bh}, %2;\n\t"
       "fma.rn.f32.bf16 %0, al, bl, %0;\n\t"
       "fma.rn.f32.bf16 %0, ah, bh, %0;\n\t"
+      "}"
+      : "+f"(acc)
+      : "r"(a), "r"(b));
+}
+
+// the same with IEEE half operands
+__device__ __forceinline__ void fma2_f32_f16(float& acc, uint32_t a, uint32_t b) {
+  asm("{\n\t"
+      ".reg .b16 al, ah, bl, bh;\n\t"
+      "mov.b32 {al, ah}, %1;\n\t"
+      "mov.b32 {bl, bh}, %2;\n\t"
+      "fma.rn.f32.f16 %0, al, bl, %0;\n\t"
+      "fma.rn.f32.f16 %0, ah, bh, %0;\n\t"
       "}"
       : "+f"(acc)
       : "r"(a), "r"(b));
@@ -338,12 +352,16 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
 // Programmatic dependent launch: every block releases its dependents at once, and when the caller vouches that the
 // weights are constant (`early_weights`) the first PF rows are requested BEFORE griddepcontrol.wait, i.e. while the
 // previous kernel of the stream is still draining; activations are read and results written only after the wait.
-template <int M_T, int SL, int PF, int MINB>
+// F16: activations, scales and output are IEEE half instead of bf16; the nibbles become 1024 + q (0x6400 | q).
+template <int M_T, int SL, int PF, int MINB, bool F16 = false>
 __global__ void __launch_bounds__(512, MINB)
-a16_w4_gemv_direct_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
-                          const __nv_bfloat16* __restrict__ scale, const uint8_t* __restrict__ zp,
-                          const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int N, int K, int group,
+a16_w4_gemv_direct_kernel(const uint16_t* __restrict__ x, const uint8_t* __restrict__ wq,
+                          const uint16_t* __restrict__ scale, const uint8_t* __restrict__ zp,
+                          const float* __restrict__ bias, uint16_t* __restrict__ y, int N, int K, int group,
                           int wpr, int early_weights) {
+  auto to_bits = [](float v) -> uint16_t {
+    return F16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  };
   __shared__ float red[2][16][PF][M_T];   // [buffer][warp][row of the iteration][token]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int T = K >> 5;                    // 32-k slices per row
@@ -353,7 +371,7 @@ a16_w4_gemv_direct_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __
   const long long units = (long long)gridDim.x * rows_par;
   const long long unit = (long long)blockIdx.x * rows_par + rs;
   const int r0 = (int)(unit * N / units), r1 = (int)((unit + 1) * N / units);
-  const uint16_t* sc16 = reinterpret_cast<const uint16_t*>(scale);
+  const uint16_t* sc16 = scale;
   ptx::griddep_launch_dependents();
 
   int slice[SL];
@@ -430,7 +448,14 @@ a16_w4_gemv_direct_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __
           xw[m][sl][4 * q + 3] = __byte_perm(v.y, v.w, 0x7632);  // (x3, x7)
           const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) xsum[m][sl] += __uint_as_float(wv[j] << 16) + __uint_as_float(wv[j] & 0xffff0000u);
+          for (int j = 0; j < 4; ++j) {
+            if (F16) {
+              const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&wv[j]));
+              xsum[m][sl] += f2.x + f2.y;
+            } else {
+              xsum[m][sl] += __uint_as_float(wv[j] << 16) + __uint_as_float(wv[j] & 0xffff0000u);
+            }
+          }
         }
       }
     }
@@ -447,8 +472,8 @@ a16_w4_gemv_direct_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __
 #pragma unroll
         for (int sl = 0; sl < SL; ++sl) {
           const uint32_t ww[4] = {wb[p][sl].x, wb[p][sl].y, wb[p][sl].z, wb[p][sl].w};
-          const float sc = __uint_as_float(sb[p][sl] << 16);
-          const float zoff = __uint_as_float(0x43000000u | (zb[p][sl] << 16));  // 128 + zp, zp <= 127
+          const float sc = F16 ? __half2float(__ushort_as_half((unsigned short)sb[p][sl])) : __uint_as_float(sb[p][sl] << 16);
+          const float zoff = F16 ? 1024.f + (float)zb[p][sl] : __uint_as_float(0x43000000u | (zb[p][sl] << 16));  // 128 + zp, zp <= 127
           float acc[M_T][4];
 #pragma unroll
           for (int m = 0; m < M_T; ++m)
@@ -458,9 +483,12 @@ a16_w4_gemv_direct_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __
           for (int q = 0; q < 4; ++q) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const uint32_t pq = ((ww[q] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // bf16x2 {128 + q_j, 128 + q_(j+4)}
+              const uint32_t pq = ((ww[q] >> (4 * j)) & 0x000F000Fu) | (F16 ? 0x64006400u : 0x43004300u);  // {128 + q_j, 128 + q_(j+4)}
 #pragma unroll
-              for (int m = 0; m < M_T; ++m) fma2_f32_bf16(acc[m][q], pq, xw[m][sl][4 * q + j]);
+              for (int m = 0; m < M_T; ++m) {
+                if (F16) fma2_f32_f16(acc[m][q], pq, xw[m][sl][4 * q + j]);
+                else fma2_f32_bf16(acc[m][q], pq, xw[m][sl][4 * q + j]);
+              }
             }
           }
 #pragma unroll
@@ -514,7 +542,7 @@ a16_w4_gemv_direct_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __
       if (my_row >= 0 && r + my_row < r1) {
 #pragma unroll
         for (int m = 0; m < M_T; ++m)
-          y[(size_t)m * N + r + my_row] = __float2bfloat16_rn(bias ? mine[m] + bias[r + my_row] : mine[m]);
+          y[(size_t)m * N + r + my_row] = to_bits(bias ? mine[m] + bias[r + my_row] : mine[m]);
       }
     } else {
       if (my_row >= 0) {
@@ -528,7 +556,7 @@ a16_w4_gemv_direct_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __
         const int p = lane / M_T, m = lane - p * M_T;
         float v = 0.f;
         for (int w = 0; w < wpr; ++w) v += red[it & 1][warp + w][p][m];
-        if (r + p < r1) y[(size_t)m * N + r + p] = __float2bfloat16_rn(bias ? v + bias[r + p] : v);
+        if (r + p < r1) y[(size_t)m * N + r + p] = to_bits(bias ? v + bias[r + p] : v);
       }
     }
   }
@@ -542,12 +570,13 @@ static bool gemv_uses_fma(int M, int K, int group) {
   return M <= 2 && K % 32 == 0 && group % 32 == 0 && K <= 32 * 32 * 16 * (M == 1 ? 4 : 2);
 }
 
-int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why) {
+int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why, bool f16) {
   const char* w = nullptr;
   if (M < 1 || M > MAX_M) w = "M must be in [1, 8]";
   else if (N < 1) w = "empty N";
   else if (group < 1 || K % group != 0) w = "the group size must divide K";
   else if (gemv_uses_fma(M, K, group)) w = nullptr;
+  else if (f16) w = "the f16 decode form exists for one or two tokens (K a multiple of 32, at most 65536 / 32768)";
   else if (K % CHUNK_K != 0) w = "K must be a multiple of 64";
   else if (group < CHUNK_K || group % CHUNK_K != 0) w = "group size must be a multiple of 64 dividing K";
   else if (gemv_plan(M, K, group, true).stages < 2) w = "two 16-row weight slabs plus the activations do not fit in shared memory";
@@ -555,7 +584,7 @@ int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why) {
   return w == nullptr;
 }
 
-template <int M_T, int SL, int PF, int MINB>
+template <int M_T, int SL, int PF, int MINB, bool F16 = false>
 static int launch_direct(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
                          int N, int K, int group, int wpr, int blocks, int early, cudaStream_t stream) {
   cudaLaunchConfig_t cfg{};
@@ -568,17 +597,17 @@ static int launch_direct(const void* x, const void* wq, const void* scale, const
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  CUDA_TRY(cudaLaunchKernelEx(&cfg, a16_w4_gemv_direct_kernel<M_T, SL, PF, MINB>, static_cast<const __nv_bfloat16*>(x),
-                              static_cast<const uint8_t*>(wq), static_cast<const __nv_bfloat16*>(scale),
-                              static_cast<const uint8_t*>(zp), bias, static_cast<__nv_bfloat16*>(y), N, K, group, wpr,
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, a16_w4_gemv_direct_kernel<M_T, SL, PF, MINB, F16>, static_cast<const uint16_t*>(x),
+                              static_cast<const uint8_t*>(wq), static_cast<const uint16_t*>(scale),
+                              static_cast<const uint8_t*>(zp), bias, static_cast<uint16_t*>(y), N, K, group, wpr,
                               early));
   return B200Q_OK;
 }
 
 int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
-                       int M, int N, int K, int group, int* status, cudaStream_t stream, bool weights_constant) {
+                       int M, int N, int K, int group, int* status, cudaStream_t stream, bool weights_constant, bool f16) {
   const char* why = nullptr;
-  if (!a16_w4_gemv_supported(M, N, K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: %s", why);
+  if (!a16_w4_gemv_supported(M, N, K, group, &why, f16)) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: %s", why);
   if ((reinterpret_cast<uintptr_t>(wq) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
     return set_error(B200Q_ERR_INVALID, "a16 w4 gemv: weights and activations must be 16-byte aligned");
   int dev = 0, sms = 0;
@@ -587,7 +616,7 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
   // two tokens: the tensor-core decode kernel is the faster one where it applies (measured 14.3 us against 16.2 us at
   // N = 11008, K = 4096); the CUDA-core form then only takes what that kernel cannot (groups of 32, K % 64 != 0)
   const bool mma_ok = K % CHUNK_K == 0 && group >= CHUNK_K && group % CHUNK_K == 0 && gemv_plan(M, K, group, true).stages >= 2;
-  if (gemv_uses_fma(M, K, group) && (M == 1 || !mma_ok)) {
+  if (gemv_uses_fma(M, K, group) && (M == 1 || !mma_ok || f16)) {
     // warps per row: the smallest power of two that leaves a lane at most SL slices
     const int T = K / 32;
     const int early = weights_constant ? 1 : 0;
@@ -596,15 +625,15 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
       while (wpr < 16 && wpr * 32 < T) wpr *= 2;
       while (sl * wpr * 32 < T) sl *= 2;  // K > 16384: more slices per lane
       const int blocks = 2 * sms;
-      if (sl == 1) return launch_direct<1, 1, 4, 2>(x, wq, scale, zp, bias, y, N, K, group, wpr, blocks, early, stream);
-      if (sl == 2) return launch_direct<1, 2, 4, 1>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
-      return launch_direct<1, 4, 1, 1>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
+      if (sl == 1) return f16 ? launch_direct<1, 1, 4, 2, true>(x, wq, scale, zp, bias, y, N, K, group, wpr, blocks, early, stream) : launch_direct<1, 1, 4, 2, false>(x, wq, scale, zp, bias, y, N, K, group, wpr, blocks, early, stream);
+      if (sl == 2) return f16 ? launch_direct<1, 2, 4, 1, true>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream) : launch_direct<1, 2, 4, 1, false>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
+      return f16 ? launch_direct<1, 4, 1, 1, true>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream) : launch_direct<1, 4, 1, 1, false>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
     }
     int sl = 1, wpr = 1;
     while (wpr < 16 && wpr * 32 < T) wpr *= 2;
     while (sl * wpr * 32 < T) sl *= 2;
-    if (sl == 1) return launch_direct<2, 1, 6, 1>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
-    return launch_direct<2, 2, 3, 1>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
+    if (sl == 1) return f16 ? launch_direct<2, 1, 6, 1, true>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream) : launch_direct<2, 1, 6, 1, false>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
+    return f16 ? launch_direct<2, 2, 3, 1, true>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream) : launch_direct<2, 2, 3, 1, false>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
   }
   const GemvPlan P = gemv_plan(M, K, group, true);
   if (P.stages < 2) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: the weight slabs do not fit in shared memory");

@@ -40,6 +40,7 @@
 // unwinds, TMEM is freed and *status receives the code.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "a16.h"
@@ -105,13 +106,25 @@ struct UmmaArgs {
   int* status;
 };
 
-// 8 nibbles of `w` (k0..k7, k0 lowest) -> four bf16x2 words {q_j - zp, q_(j+4) - zp}, j = 0..3
+// 8 nibbles of `w` (k0..k7, k0 lowest) -> four packed 16-bit float words {q_j - zp, q_(j+4) - zp}, j = 0..3.
+// bf16: 0x4300 | q = 128 + q (ulp 1 at 128..255); f16: 0x6400 | q = 1024 + q (ulp 1 at 1024..2047).
+template <bool F16 = false>
 __device__ __forceinline__ void dequant_word(uint32_t w, uint32_t negz, uint32_t (&p)[4]) {
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const uint32_t t = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // {128 + q_j, 128 + q_(j+4)}
-    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(p[j]) : "r"(t), "r"(0x3F803F80u), "r"(negz));  // exact: small integers
+    const uint32_t t = ((w >> (4 * j)) & 0x000F000Fu) | (F16 ? 0x64006400u : 0x43004300u);
+    if (F16) asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(p[j]) : "r"(t), "r"(0x3C003C00u), "r"(negz));  // exact: small integers
+    else asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(p[j]) : "r"(t), "r"(0x3F803F80u), "r"(negz));
   }
+}
+// the 16-bit storage type of activations, scales and output
+template <bool F16>
+__device__ __forceinline__ float bits_to_f32(uint32_t b) {
+  return F16 ? __half2float(__ushort_as_half((unsigned short)b)) : __uint_as_float(b << 16);
+}
+template <bool F16>
+__device__ __forceinline__ uint16_t f32_to_bits(float v) {
+  return F16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
 // Scales (bf16) or zero points (bytes) of the rows [row0, row0 + nrows) transposed into shared memory as T[g][n]:
@@ -167,7 +180,7 @@ __device__ __forceinline__ void stage_meta(T* dstT, const T* src, int row0, int 
   }
 }
 
-template <int MT>
+template <int MT, bool F16 = false>
 __global__ void __launch_bounds__(THREADS, 1)
 a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                    const UmmaArgs args) {
@@ -418,7 +431,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           w1 = *reinterpret_cast<const uint4*>(rrow + (((2 * sub + 1) ^ (row & 7)) << 4));
         }
         const uint32_t z = live ? zpT[(kb / args.kpg) * ZP_PITCH + row] : 0u;
-        const uint32_t negz = __byte_perm(z, 0xC3u, 0x4040);  // bf16x2 {-(128 + zp), -(128 + zp)}: 0xC300 | zp
+        const uint32_t negz = __byte_perm(z, F16 ? 0xE4u : 0xC3u, 0x4040);  // {-(128 + zp)} x2 as bf16: 0xC300 | zp; f16 -(1024 + zp): 0xE400 | zp
         if (!(ok = warp_wait(a_empty(as), aphase ^ 1u, 7))) break;
         ptx::tc_fence_after_sync();
         const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
@@ -428,7 +441,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint32_t p[4];
-            dequant_word(ww[4 * h + q], negz, p);
+            dequant_word<F16>(ww[4 * h + q], negz, p);
             if (FEW) {   // k order 0,4,1,5,2,6,3,7 inside every 8 (B is written in the same order)
               o[4 * q + 0] = p[0];
               o[4 * q + 1] = p[1];
@@ -498,7 +511,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * N_MMA + part * MY_COLS);
         const int g0 = pi * args.G;
         float s;
-        if (!FEW) s = __uint_as_float((uint32_t)scaleT[min(g0, args.gpr - 1) * SCALE_PITCH + n_safe] << 16);
+        if (!FEW) s = bits_to_f32<F16>((uint32_t)scaleT[min(g0, args.gpr - 1) * SCALE_PITCH + n_safe]);
 #pragma unroll
         for (int c0 = 0; c0 < MY_COLS / 16; ++c0) {
           uint32_t r[16];
@@ -515,7 +528,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             for (int c = 0; c < 16; ++c) {
               int g = g0 + (c >> mtok_shift);
               if (g >= args.gpr) g = args.gpr - 1;   // columns of groups past K hold zeros
-              const float sg = __uint_as_float((uint32_t)scaleT[g * SCALE_PITCH + n_safe] << 16);
+              const float sg = bits_to_f32<F16>((uint32_t)scaleT[g * SCALE_PITCH + n_safe]);
               running[c] = fmaf(sg, __uint_as_float(r[c]), running[c]);
             }
           } else {
@@ -542,7 +555,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
               for (int c = 0; c < 16; ++c)
                 if ((c & (mtok - 1)) == m) v += running[c];
-              args.y[(size_t)m * args.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(v + b));
+              args.y[(size_t)m * args.N + n] = f32_to_bits<F16>(v + b);
             }
           }
         } else {
@@ -550,7 +563,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
           for (int c = 0; c < MY_COLS; ++c) {
             const int m = m0 + c;
-            if (m < args.M) args.y[(size_t)m * args.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(running[c] + b));
+            if (m < args.M) args.y[(size_t)m * args.N + n] = f32_to_bits<F16>(running[c] + b);
           }
         }
       }
@@ -567,7 +580,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   if (threadIdx.x == 0 && *abort_flag != 0 && args.status != nullptr) atomicCAS(args.status, 0, *abort_flag);
 }
 
-template <int MT>
+template <int MT, bool F16>
 int launch_umma(const CUtensorMap& tw, const CUtensorMap& tx, UmmaArgs a, int grid, cudaStream_t stream) {
   using C = Cfg<MT>;
   const int x_bytes = MT == 0 ? a.mtok * a.K * 2 : 0;
@@ -576,8 +589,8 @@ int launch_umma(const CUtensorMap& tw, const CUtensorMap& tx, UmmaArgs a, int gr
   while (a.raw_stages > 2 && C::total(a.raw_stages, a.gpr, x_bytes) > 227 * 1024) --a.raw_stages;
   const int smem = C::total(a.raw_stages, a.gpr, x_bytes);
   if (smem > 227 * 1024) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 tensor-core kernel: shared memory does not hold two raw stages");
-  a.idesc = ptx::make_idesc(1u, 1u, 1u, (uint32_t)TILE_ROWS, (uint32_t)C::N_MMA);
-  auto kfn = a16_w4_umma_kernel<MT>;
+  a.idesc = ptx::make_idesc(1u, F16 ? 0u : 1u, F16 ? 0u : 1u, (uint32_t)TILE_ROWS, (uint32_t)C::N_MMA);  // f32 accumulate
+  auto kfn = a16_w4_umma_kernel<MT, F16>;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)grid);
@@ -991,7 +1004,7 @@ int a16_w4_umma_supported(long long M, int N, int K, int group, const char** why
 }
 
 int a16_w4_umma_launch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
-                       long long M, int N, int K, int group, int* status, cudaStream_t stream) {
+                       long long M, int N, int K, int group, int* status, cudaStream_t stream, bool f16) {
   const char* why = nullptr;
   if (!a16_w4_umma_supported(M, N, K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 tensor-core kernel: %s", why);
   if ((reinterpret_cast<uintptr_t>(wq) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
@@ -1015,7 +1028,7 @@ int a16_w4_umma_launch(const void* x, const void* wq, const void* scale, const v
   a.status = status;
   // few-token form: up to 4 tokens whose activations fit in shared memory next to two raw stages
   const int mtok_few = M <= 1 ? 1 : M <= 2 ? 2 : 4;
-  const bool few = M <= 4 && FewCfg::total(2, a.gpr, mtok_few * K * 2) <= 227 * 1024;
+  const bool few = !f16 && M <= 4 && FewCfg::total(2, a.gpr, mtok_few * K * 2) <= 227 * 1024;   // (the few-token form is built for bf16)
   int mt = 0;
   if (few) {
     a.mtok = mtok_few;
@@ -1060,9 +1073,14 @@ int a16_w4_umma_launch(const void* x, const void* wq, const void* scale, const v
     const uint32_t box[2] = {128u, (uint32_t)mt};
     B200Q_TRY(make_tmap_u8(&tx, x, 2, dims, strides, box));
   }
-  if (mt == 32) return launch_umma<32>(tw, tx, a, grid, stream);
-  if (mt == 64) return launch_umma<64>(tw, tx, a, grid, stream);
-  return launch_umma<128>(tw, tx, a, grid, stream);
+  if (f16) {
+    if (mt == 32) return launch_umma<32, true>(tw, tx, a, grid, stream);
+    if (mt == 64) return launch_umma<64, true>(tw, tx, a, grid, stream);
+    return launch_umma<128, true>(tw, tx, a, grid, stream);
+  }
+  if (mt == 32) return launch_umma<32, false>(tw, tx, a, grid, stream);
+  if (mt == 64) return launch_umma<64, false>(tw, tx, a, grid, stream);
+  return launch_umma<128, false>(tw, tx, a, grid, stream);
 }
 
 }  // namespace b200q

@@ -1,6 +1,7 @@
 // C ABI for tpu.A16MatMul with 4-bit weights (lib/Dialect/Tpu/Interfaces/Common/A16MatMul.cpp:16-249):
 // operator face over host float buffers and device face over native bf16 / packed-nibble tensors.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <new>
 
@@ -22,6 +23,19 @@ __global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ x, float* _
   if (i < n) y[i] = __bfloat162float(x[i]);
 }
 
+__global__ void f32_to_f16_kernel(const float* __restrict__ x, __half* __restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = __float2half_rn(x[i]);  // exact: the interpreter's f16 tensors hold f16-representable floats
+}
+__global__ void f16_to_f32_kernel(const __half* __restrict__ x, float* __restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = __half2float(x[i]);
+}
+
+// float <-> the op's 16-bit storage type (bf16, or IEEE half for w4f16)
+int f32_to_16(const float* x, void* y, long long n, bool f16, cudaStream_t s);
+int f16_or_bf16_to_f32(const void* x, float* y, long long n, bool f16, cudaStream_t s);
+
 int f32_to_bf16(const float* x, void* y, long long n, cudaStream_t s) {
   if (n == 0) return B200Q_OK;
   f32_to_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, static_cast<__nv_bfloat16*>(y), n);
@@ -31,6 +45,21 @@ int f32_to_bf16(const float* x, void* y, long long n, cudaStream_t s) {
 int bf16_to_f32(const void* x, float* y, long long n, cudaStream_t s) {
   if (n == 0) return B200Q_OK;
   bf16_to_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), y, n);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int f32_to_16(const float* x, void* y, long long n, bool f16, cudaStream_t s) {
+  if (!f16) return f32_to_bf16(x, y, n, s);
+  if (n == 0) return B200Q_OK;
+  f32_to_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, static_cast<__half*>(y), n);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+int f16_or_bf16_to_f32(const void* x, float* y, long long n, bool f16, cudaStream_t s) {
+  if (!f16) return bf16_to_f32(x, y, n, s);
+  if (n == 0) return B200Q_OK;
+  f16_to_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const __half*>(x), y, n);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }
@@ -97,7 +126,8 @@ int validate(const b200q_a16matmul_desc& d) {
   if (d.weight_bits != 4) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: only weight_bits = 4 is implemented");
   if (!d.w_transpose) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: only w_transpose = true (weight stored [N, K/2]) is implemented");
   if (d.q_group_size <= 0) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: per-channel (q_group_size = 0) weights are not implemented");
-  if (d.out_dtype != B200Q_DT_BF16) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: only bf16 activations/outputs are implemented");
+  if (d.out_dtype != B200Q_DT_BF16 && d.out_dtype != B200Q_DT_F16)
+    return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: activations/outputs are bf16 (w4bf16) or f16 (w4f16)");
   return B200Q_OK;
 }
 
@@ -108,7 +138,7 @@ int g_a16_route = 0;
 // Decode shapes go to the GEMV kernel; larger M is processed in slices of 8 tokens.
 int a16_dispatch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
                  long long M, int N, int K, int group, int* status, cudaStream_t s, DevBuf* w16 = nullptr,
-                 bool* w16_ready = nullptr, bool weights_constant = false) {
+                 bool* w16_ready = nullptr, bool weights_constant = false, bool f16 = false) {
   const char* why = nullptr;
   // both routes index scales and zero points as [n][k / group]: the group must tile K exactly, and a byte holds
   // two consecutive k of one row
@@ -116,9 +146,10 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
   const int route = g_a16_route;
   if (M == 0) return B200Q_OK;
   const bool umma_ok = a16_w4_umma_supported(M, N, K, group, nullptr) != 0;
-  const bool gemv_ok = M <= 8 && a16_w4_gemv_supported((int)M, N, K, group, nullptr) != 0;
+  // w4f16: the one-token CUDA-core kernel (two tokens where it applies) and the fused tensor-core kernel have the form
+  const bool gemv_ok = M <= 8 && a16_w4_gemv_supported((int)M, N, K, group, nullptr, f16) != 0;
   // the one-time bf16 copy + bf16 GEMM: only through a handle (which owns the copy), only for prefill-sized M
-  const bool resident_ok = M > 8 && w16 && K % 8 == 0 && group % 8 == 0 && M <= 0x7fffffffLL;
+  const bool resident_ok = !f16 && M > 8 && w16 && K % 8 == 0 && group % 8 == 0 && M <= 0x7fffffffLL;
   bool use_umma = false, use_resident = false;
   switch (route) {
     case 1: break;
@@ -134,7 +165,7 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
       if (resident_ok && M >= 512) use_resident = true;
       else use_umma = umma_ok;
   }
-  if (use_umma) return a16_w4_umma_launch(x, wq, scale, zp, bias, y, M, N, K, group, status, s);
+  if (use_umma) return a16_w4_umma_launch(x, wq, scale, zp, bias, y, M, N, K, group, status, s, f16);
   if (use_resident) {
     // dequantise once (kept for the life of the handle / weight version), then a bf16 GEMM
     if (!*w16_ready) {
@@ -145,12 +176,12 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
     return a16_prefill_gemm(x, w16->p, bias, y, M, N, K, status, s);
   }
   // decode kernels, 8 tokens per launch (also the fallback for shapes the tensor-core kernel does not take)
-  if (!a16_w4_gemv_supported((int)(M < 8 ? M : 8), N, K, group, &why) || (M > 8 && !a16_w4_gemv_supported(8, N, K, group, &why))) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: %s", why);
+  if (!a16_w4_gemv_supported((int)(M < 8 ? M : 8), N, K, group, &why, f16) || (M > 8 && !a16_w4_gemv_supported(8, N, K, group, &why, f16))) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: %s", why);
   for (long long m0 = 0; m0 < M; m0 += 8) {
     const int mm = (int)((M - m0) < 8 ? (M - m0) : 8);
     B200Q_TRY(a16_w4_gemv_launch(static_cast<const uint8_t*>(x) + (size_t)m0 * K * 2, wq, scale, zp, bias,
                                  static_cast<uint8_t*>(y) + (size_t)m0 * N * 2, mm, N, K, group, status, s,
-                                 weights_constant));
+                                 weights_constant, f16));
   }
   return B200Q_OK;
 }
@@ -162,6 +193,7 @@ struct A16Handle {
   const void *d_wq = nullptr, *d_scale = nullptr, *d_zp = nullptr;
   const float* d_bias = nullptr;
   int N = 0, K = 0, group = 0;
+  bool f16 = false;   // device face: the tensors are IEEE half instead of bf16
   bool weights_ready = false;
   int weight_version = -1;
   const float* weight_ptr = nullptr;
@@ -202,6 +234,7 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
   A16Handle* h = static_cast<A16Handle*>(*handle);
   cudaStream_t s = 0;
   int rc = B200Q_OK;
+  const bool f16 = d.out_dtype == B200Q_DT_F16;
   do {
     const size_t w_elems = (size_t)d.N * (d.K / 2), q_elems = (size_t)d.N * (d.K / d.q_group_size);
     const float* bias_f = (d.with_bias && n_inputs > 4) ? inputs[4] : nullptr;
@@ -216,7 +249,7 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
       if (cudaMemcpyAsync(h->stage.p, inputs[1], w_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D weight", __FILE__, __LINE__); break; }
       if ((rc = f32_to_q8(h->stage.as<float>(), h->wq.p, (long long)w_elems, s))) break;
       if (cudaMemcpyAsync(h->stage.p, inputs[2], q_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D scale", __FILE__, __LINE__); break; }
-      if ((rc = f32_to_bf16(h->stage.as<float>(), h->scale.p, (long long)q_elems, s))) break;
+      if ((rc = f32_to_16(h->stage.as<float>(), h->scale.p, (long long)q_elems, f16, s))) break;
       if (cudaMemcpyAsync(h->stage.p, inputs[3], q_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D zp", __FILE__, __LINE__); break; }
       if ((rc = f32_to_q8(h->stage.as<float>(), h->zp.p, (long long)q_elems, s))) break;
       if (bias_f && (rc = h->bias.upload(bias_f, (size_t)d.N * 4, s))) break;
@@ -234,10 +267,10 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
     if ((rc = h->status.ensure(4))) break;
     if (cudaMemsetAsync(h->status.p, 0, 4, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "memset", __FILE__, __LINE__); break; }
     if (cudaMemcpyAsync(h->stage.p, inputs[0], x_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D input", __FILE__, __LINE__); break; }
-    if ((rc = f32_to_bf16(h->stage.as<float>(), h->x16.p, (long long)x_elems, s))) break;
+    if ((rc = f32_to_16(h->stage.as<float>(), h->x16.p, (long long)x_elems, f16, s))) break;
     if ((rc = a16_dispatch(h->x16.p, h->wq.p, h->scale.p, h->zp.p, bias_f ? h->bias.as<float>() : nullptr, h->y16.p,
-                           d.M, (int)d.N, (int)d.K, d.q_group_size, h->status.as<int>(), s, &h->w16, &h->w16_ready))) break;
-    if ((rc = bf16_to_f32(h->y16.p, h->y32.as<float>(), (long long)y_elems, s))) break;
+                           d.M, (int)d.N, (int)d.K, d.q_group_size, h->status.as<int>(), s, &h->w16, &h->w16_ready, false, f16))) break;
+    if ((rc = f16_or_bf16_to_f32(h->y16.p, h->y32.as<float>(), (long long)y_elems, f16, s))) break;
     if (cudaMemcpyAsync(outputs[0], h->y32.p, y_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__); break; }
     int hstat = 0;
     if (cudaMemcpyAsync(&hstat, h->status.p, 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H status", __FILE__, __LINE__); break; }
@@ -251,13 +284,19 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
 
 void b200q_a16_set_route(int32_t route) { g_a16_route = (route >= 0 && route <= 3) ? route : 0; }
 
+int b200q_a16_w4_dev_dt(const void* x, const void* wq, const void* scale, const void* zp_u8, const float* bias_f32, void* y,
+                        int64_t M, int64_t N, int64_t K, int32_t group, int32_t dtype, int32_t* status, void* stream) {
+  if (!x || !wq || !scale || !zp_u8 || !y) return set_error(B200Q_ERR_INVALID, "a16_w4_dev: null argument");
+  if (M < 0 || N < 1 || K < 1 || N > 0x7fffffffLL || K > 0x7fffffffLL || group < 1) return set_error(B200Q_ERR_INVALID, "a16_w4_dev: bad shape");
+  if (dtype != B200Q_DT_BF16 && dtype != B200Q_DT_F16) return set_error(B200Q_ERR_INVALID, "a16_w4_dev: dtype must be bf16 or f16");
+  return a16_dispatch(x, wq, scale, zp_u8, bias_f32, y, M, (int)N, (int)K, group, status, static_cast<cudaStream_t>(stream),
+                      nullptr, nullptr, false, dtype == B200Q_DT_F16);
+}
+
 int b200q_a16_w4_dev(const void* x_bf16, const void* wq, const void* scale_bf16, const void* zp_u8,
                      const float* bias_f32, void* y_bf16, int64_t M, int64_t N, int64_t K, int32_t group,
                      int32_t* status, void* stream) {
-  if (!x_bf16 || !wq || !scale_bf16 || !zp_u8 || !y_bf16) return set_error(B200Q_ERR_INVALID, "a16_w4_dev: null argument");
-  if (M < 0 || N < 1 || K < 1 || N > 0x7fffffffLL || K > 0x7fffffffLL || group < 1) return set_error(B200Q_ERR_INVALID, "a16_w4_dev: bad shape");
-  return a16_dispatch(x_bf16, wq, scale_bf16, zp_u8, bias_f32, y_bf16, M, (int)N, (int)K, group, status,
-                      static_cast<cudaStream_t>(stream));
+  return b200q_a16_w4_dev_dt(x_bf16, wq, scale_bf16, zp_u8, bias_f32, y_bf16, M, N, K, group, B200Q_DT_BF16, status, stream);
 }
 
 }  // extern "C"
@@ -266,10 +305,16 @@ extern "C" {
 
 int b200q_a16_dev_create(const void* wq, const void* scale_bf16, const void* zp_u8, const float* bias_f32, int64_t N,
                          int64_t K, int32_t group, void** handle) {
+  return b200q_a16_dev_create_dt(wq, scale_bf16, zp_u8, bias_f32, N, K, group, B200Q_DT_BF16, handle);
+}
+
+int b200q_a16_dev_create_dt(const void* wq, const void* scale_bf16, const void* zp_u8, const float* bias_f32, int64_t N,
+                            int64_t K, int32_t group, int32_t dtype, void** handle) {
   if (!wq || !scale_bf16 || !zp_u8 || !handle) return set_error(B200Q_ERR_INVALID, "a16_dev_create: null argument");
   if (N < 1 || K < 1 || group < 1 || N > 0x7fffffffLL || K > 0x7fffffffLL) return set_error(B200Q_ERR_INVALID, "a16_dev_create: bad shape");
+  if (dtype != B200Q_DT_BF16 && dtype != B200Q_DT_F16) return set_error(B200Q_ERR_INVALID, "a16_dev_create: dtype must be bf16 or f16");
   const char* why = nullptr;
-  if (!a16_w4_gemv_supported(1, (int)N, (int)K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16_dev_create: %s", why);
+  if (!a16_w4_gemv_supported(1, (int)N, (int)K, group, &why, dtype == B200Q_DT_F16)) return set_error(B200Q_ERR_UNSUPPORTED, "a16_dev_create: %s", why);
   auto* h = new (std::nothrow) A16Handle();
   if (!h) return set_error(B200Q_ERR_NOMEM, "a16_dev_create: out of host memory");
   h->d_wq = wq;
@@ -279,6 +324,7 @@ int b200q_a16_dev_create(const void* wq, const void* scale_bf16, const void* zp_
   h->N = (int)N;
   h->K = (int)K;
   h->group = group;
+  h->f16 = dtype == B200Q_DT_F16;
   int rc = h->status.ensure(4);
   if (rc == B200Q_OK && cudaMemset(h->status.p, 0, 4) != cudaSuccess) rc = cuda_error(cudaGetLastError(), "memset", __FILE__, __LINE__);
   if (rc != B200Q_OK) {
@@ -293,7 +339,7 @@ int b200q_a16_dev_run(void* handle, const void* x_bf16, void* y_bf16, int64_t M,
   if (!handle || !x_bf16 || !y_bf16 || M < 0) return set_error(B200Q_ERR_INVALID, "a16_dev_run: bad argument");
   A16Handle* h = static_cast<A16Handle*>(handle);
   return a16_dispatch(x_bf16, h->d_wq, h->d_scale, h->d_zp, h->d_bias, y_bf16, M, h->N, h->K, h->group,
-                      h->status.as<int>(), static_cast<cudaStream_t>(stream), &h->w16, &h->w16_ready, true);
+                      h->status.as<int>(), static_cast<cudaStream_t>(stream), &h->w16, &h->w16_ready, true, h->f16);
 }
 
 int b200q_a16_dev_status(void* handle, void* stream) {

@@ -51,15 +51,17 @@ def f32_to_bf16_bits(x):
     return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
 
 
-def a16_w4(seed=2, M=1, K=4096, N=11008, group=64):
+def a16_w4(seed=2, M=1, K=4096, N=11008, group=64, f16=False):
     """Config 2: packed uint4 weights [N, K/2] (even k in the low nibble), bf16 scales and uint8 zero points per
-    group of `group` along K, bf16 normal(0,1) activations [M, K]."""
+    group of `group` along K, bf16 normal(0,1) activations [M, K].  ``f16=True``: the same values as IEEE half bit
+    patterns (w4f16)."""
     rng = np.random.default_rng(seed)
     q = rng.integers(0, 16, size=(N, K), dtype=np.uint8)
     wq = (q[:, 0::2] | (q[:, 1::2] << 4)).astype(np.uint8)
-    scale = f32_to_bf16_bits(rng.uniform(0.001, 0.02, size=N * K // group).astype(np.float32))
+    to_bits = (lambda a: a.astype(np.float16).view(np.uint16)) if f16 else f32_to_bf16_bits
+    scale = to_bits(rng.uniform(0.001, 0.02, size=N * K // group).astype(np.float32))
     zp = rng.integers(0, 16, size=N * K // group, dtype=np.uint8)
-    x = f32_to_bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    x = to_bits(rng.standard_normal((M, K)).astype(np.float32))
     return dict(x=x, wq=wq, scale=scale, zp=zp)
 
 
