@@ -327,7 +327,7 @@ def kernel_lines(workload, steps, warmup, a16_m=(1, 2, 4, 8, 16, 128, 2048)):
             # the two bounds cross where 2*M*N*K / bf16 peak = packed bytes / HBM peak: M ~ 33 for this layer
             bound_is_hbm = nbytes / (peaks["hbm_gbs"] * 1e9) >= 2.0 * M * 11008 * 4096 / (peaks["bf16_tflops"] * 1e12)
             route = ("decode kernel (CUDA cores, packed weights read once)" if M <= 8 else
-                     "bf16 copy of the weight kept in the handle (90 MB) + bf16 tensor-core GEMM" if M >= 512 else
+                     "bf16 copy of the weight kept in the handle (90 MB) + bf16 tensor-core GEMM" if M >= 64 else
                      "fused kernel: packed weights by TMA, dequantised in registers into tensor memory, tcgen05 kind::f16")
             lines.append(dict(metric="A16MatMul w4bf16 " + ("GB/s" if bound_is_hbm else "TFLOP/s"),
                               value=gbs if bound_is_hbm else tf, unit="GB/s" if bound_is_hbm else "TFLOP/s",

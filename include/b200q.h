@@ -351,7 +351,7 @@ int b200q_probe_tensor_peak(int32_t kind, int32_t pair, int32_t kblocks, int32_t
                             void *stream);
 
 /* Which kernel serves b200q_a16_*, process-wide: 0 = chosen per call (default: up to 8 tokens take the CUDA-core
- * decode kernels; a handle that sees 512 tokens or more dequantises once into a bf16 copy and runs a bf16 GEMM;
+ * decode kernels; a handle that sees 64 tokens or more dequantises once into a bf16 copy and runs a bf16 GEMM;
  * everything else takes the fused-dequantisation tensor-core kernel on the packed weights); 1 = the decode kernels
  * only (8 tokens per launch); 2 = the fused tensor-core kernel for every M; 3 = handle API with M > 8: the bf16 copy
  * (rounds the weight to bf16, which the reference does not).  A measuring control; no counterpart in the reference. */
@@ -359,7 +359,7 @@ void b200q_a16_set_route(int32_t route);
 
 /* Device face with a handle: the tensors stay the caller's (not copied) and are declared constant for the life of
  * the handle (the decode kernel may request weights before the previous kernel of the stream has finished).  M <= 8
- * runs the decode kernels on the packed weights, M < 512 the fused tensor-core kernel on the packed weights; from 512
+ * runs the decode kernels on the packed weights, M < 64 the fused tensor-core kernel on the packed weights; from 64
  * tokens on the weight is dequantised once into bf16 (kept in the handle, N*K*2 bytes) for a bf16 tensor-core GEMM
  * with fp32 accumulation.  b200q_a16_dev_status synchronises the stream and reports a kernel-side timeout. */
 int b200q_a16_dev_create(const void *wq, const void *scale_bf16, const void *zp_u8, const float *bias_f32,

@@ -92,7 +92,7 @@ def check_f32(y_bits, ref_f32):
 
 def check_rounded_weight(y_bits, ref_f32):
     """The route that keeps a bf16 copy of the dequantised weight (b200q_a16_set_route(3), and the handle's choice from
-    512 tokens on) rounds W to bf16 (2^-9 relative per weight, ~1e-3 * rms(y) of absolute noise), which the reference
+    64 tokens on) rounds W to bf16 (2^-9 relative per weight, ~1e-3 * rms(y) of absolute noise), which the reference
     does not; its bound has rms(y_ref) as the floor and one bf16 ulp for the output rounding on both sides:
     |y - y_ref| <= 1e-2 * max(|y_ref|, rms(y_ref)) + ulp_bf16(y_ref)."""
     y = oracle.bf16_bits_to_f32(y_bits).astype(np.float64)
@@ -129,12 +129,25 @@ def run_handle(c, M, N, K, group, bias=None):
     return y.cpu().numpy()
 
 
-@pytest.mark.parametrize("M", [16, 128])
+@pytest.mark.parametrize("M", [16, 48, 128])
 def test_prefill_llama_mlp_shape_against_oracle(M):
-    """Default route above 8 tokens: the fused-dequantisation tensor-core kernel, held to the plain bound."""
+    """Default routes of the handle API above 8 tokens: below 64 tokens the fused-dequantisation tensor-core kernel, held
+    to the plain bound; from 64 tokens the bf16 copy of the weight, held to the bound that allows for its rounding."""
     c = synth.a16_w4(seed=2, M=M)
+    if M < 64:
+        ref = oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], group=64)
+        check(run_handle(c, M, 11008, 4096, 64), ref)
+    else:
+        W = oracle.a16_dequant_w4(c["wq"], c["scale"], c["zp"], group=64)
+        ref = oracle.bf16_bits_to_f32(c["x"]).astype(np.float32) @ W.T
+        check_rounded_weight(run_handle(c, M, 11008, 4096, 64), ref)
+
+
+def test_stateless_call_never_rounds_the_weight():
+    """b200q_a16_w4_dev has no handle to keep a copy in: every M above 8 takes the fused kernel, plain bound."""
+    c = synth.a16_w4(seed=3, M=128, K=4096, N=2048)
     ref = oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], group=64)
-    check(run_handle(c, M, 11008, 4096, 64), ref)
+    check(run_dev(c, 128, 2048, 4096, 64), ref)
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 33, 300])
@@ -150,6 +163,9 @@ def test_tensor_core_kernel_every_token_count(route, M):
 @pytest.mark.parametrize("case", [dict(M=1, K=64, N=16, g=64), dict(M=4, K=192, N=100, g=64), dict(M=9, K=256, N=128, g=64),
                                   dict(M=2, K=11008, N=130, g=64), dict(M=33, K=11008, N=130, g=64),
                                   dict(M=100, K=4096, N=384, g=128), dict(M=40, K=2048, N=17, g=256),
+                                  # groups of two / four / eight k-blocks with narrow token tiles: fewer MMA issuers in use
+                                  dict(M=20, K=4096, N=700, g=128), dict(M=12, K=2048, N=300, g=256), dict(M=50, K=1024, N=260, g=512),
+                                  dict(M=24, K=4160, N=200, g=64),
                                   dict(M=3, K=8192, N=300, g=128)])
 def test_tensor_core_kernel_shapes(route, case):
     """Ragged rows, K that is not a multiple of a raw stage (256), groups of 128 and 256, many groups per row."""

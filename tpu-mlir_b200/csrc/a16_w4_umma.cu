@@ -39,6 +39,8 @@
 // Every mbarrier wait is bounded (2 s); a wait that runs out leaves its site code in a shared flag, every role
 // unwinds, TMEM is freed and *status receives the code.
 #include <cuda.h>
+
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -57,24 +59,40 @@ constexpr int RAW_KB = 4;                // k-blocks per raw stage (128 bytes of
 constexpr int RAW_STAGE_BYTES = TILE_ROWS * 128;
 constexpr int A_COLS = 32;               // TMEM columns of one k-block of A (two bf16 per column)
 constexpr int TMEM_COLS = 512;
-constexpr int MAX_RAW = 8, MAX_AS = 12, MAX_ACC = 4;
+constexpr int MAX_RAW = 8, MAX_AS = 12, MAX_ACC = 8;
 constexpr int THREADS = 1024;
 constexpr int SCALE_PITCH = TILE_ROWS + 2;   // scaleT[g][n], bf16: transposed so that lanes (rows) read one group conflict-free
 constexpr int ZP_PITCH = TILE_ROWS + 4;      // zpT[g][n], bytes
 constexpr uint64_t WAIT_NS = 2000000000ull;
+#ifndef POLL_SLEEP_NS
+#define POLL_SLEEP_NS 300
+#endif
 
 // MT == 0: few-token form (M <= 4); else the token tile width of the many-token form
 template <int MT>
 struct Cfg {
   static constexpr bool FEW = MT == 0;
-  static constexpr int W = FEW ? 6 : (MT == 128 ? 3 : 5);     // dequantisation warps per lane quarter
+  // MMA-issuing threads.  One thread issuing every k-block's four MMAs, two commits and two barrier tests is the
+  // slowest actor of the kernel for narrow token tiles (each of those instructions takes it 50-100 cycles), so the
+  // drain periods go round NI issuers (lane 0 of warps 0..NI-1, one per scheduler): period P runs on issuer P % NI
+  // into accumulator P % NACC, and an accumulator always belongs to the same issuer (NI divides NACC).
+  static constexpr int NI = (FEW || MT == 128) ? 1 : 4;
+  static constexpr int RAW_WARP = NI > 1 ? 4 : 0, B_WARP = NI > 1 ? 5 : 2;   // the two TMA producers
+  static constexpr int W = FEW ? 6 : (MT == 128 ? 3 : 4);     // dequantisation warps per lane quarter
   static constexpr int E = FEW ? 4 : (MT == 128 ? 16 : 8);    // epilogue warps (a multiple of 4)
   static constexpr int N_MMA = FEW ? 16 : MT;
   static constexpr int NACC = FEW ? 2 : (MT == 128 ? 2 : 4);  // accumulator buffers
-  static constexpr int AS = FEW ? 12 : (MT == 32 ? 12 : 8);   // k-blocks of A in TMEM
+  // accumulators are handed over in sets: the MMA thread signals a set when its last group is complete and the epilogue
+  // drains the whole set behind ONE wait / arrive pair (the hand-over, not the arithmetic, is what a drain costs)
+#ifndef UMMA_SET_DIV
+#define UMMA_SET_DIV 2
+#endif
+  static constexpr int SET = (FEW || NI > 1) ? 1 : (NACC / UMMA_SET_DIV > 0 ? NACC / UMMA_SET_DIV : 1);
+  static_assert(NACC % NI == 0, "an accumulator belongs to one issuer");
+  static constexpr int AS = FEW ? 12 : (MT == 32 ? 12 : 8);   // k-blocks of A in TMEM (what is in flight between conversion and MMA)
   static constexpr int A_COL0 = TMEM_COLS - AS * A_COLS;      // accumulators from column 0, A stages at the top
   static constexpr int B_STAGE_BYTES = FEW ? 32 * 128 : MT * 128;
-  static constexpr int FIRST_DQ = 4, FIRST_EPI = 4 + 4 * W;
+  static constexpr int FIRST_DQ = NI > 1 ? 8 : 4, FIRST_EPI = FIRST_DQ + 4 * W;
   static constexpr int MY_COLS = N_MMA / (E / 4);             // accumulator columns per epilogue thread
   static_assert(FIRST_EPI + E == THREADS / 32, "32 warps");
   static_assert(NACC * N_MMA <= A_COL0, "accumulators and A stages share 512 columns");
@@ -101,9 +119,12 @@ struct UmmaArgs {
   int G;                  // groups per drain period
   int rows_item;          // output channels per work item (multiple of 16, <= 128)
   int items_n, items_m;   // work items: items_n row chunks x items_m token tiles
+  int ni;                 // MMA issuers in use (1, 2 or 4): chosen so that a stage of A is always consumed by the same issuer
+  int raw_box_rows;       // rows of one raw-weight TMA box: rows_item (one box per raw stage) or 16
   int raw_stages;         // depth of the raw ring (chosen by the host so that everything fits in shared memory)
   uint32_t idesc;
   int* status;
+  int debug;   // timing experiments only (B200Q_UMMA_DEBUG), bits: 1 = conversion warps skip the arithmetic and the TMEM stores, 2 = no MMAs are issued
 };
 
 // 8 nibbles of `w` (k0..k7, k0 lowest) -> four packed 16-bit float words {q_j - zp, q_(j+4) - zp}, j = 0..3.
@@ -186,7 +207,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                    const UmmaArgs args) {
   using C = Cfg<MT>;
   constexpr bool FEW = C::FEW;
-  constexpr int W = C::W, E = C::E, AS = C::AS, NACC = C::NACC, N_MMA = C::N_MMA;
+  constexpr int W = C::W, E = C::E, AS = C::AS, NACC = C::NACC, N_MMA = C::N_MMA, SET = C::SET, NSETS = NACC / SET;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int RS = args.raw_stages;
@@ -223,8 +244,10 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     return ok_;
   };
   // every lane of the warp runs the same wait (the barrier test is one warp instruction either way)
+  // (the conversion and epilogue warps have slack: they sleep longer between polls so that the single MMA-issuing
+  // thread, which shares a scheduler with eight of them, gets the issue slots)
   auto warp_wait = [&](uint32_t bar, uint32_t parity, int where) -> bool {
-    return ptx::mbar_wait_bounded_fast(bar, parity, abort_flag, where, WAIT_NS);
+    return ptx::mbar_wait_bounded_fast<POLL_SLEEP_NS>(bar, parity, abort_flag, where, WAIT_NS);
   };
 
   ptx::griddep_launch_dependents();
@@ -237,7 +260,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       ptx::mbar_init(a_full(s), FEW ? 4 : 5);     // the four quarters (+ the activation tile's TMA)
       ptx::mbar_init(a_empty(s), 1);
     }
-    for (int a = 0; a < NACC; ++a) {
+    for (int a = 0; a < NSETS; ++a) {   // one pair of barriers per SET of accumulators
       ptx::mbar_init(acc_full(a), 1);
       ptx::mbar_init(acc_empty(a), E);
     }
@@ -289,7 +312,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const int kb_per_period = args.G * args.kpg;
   const int periods_per_item = (num_kb + kb_per_period - 1) / kb_per_period;
 
-  if (warp == 0) {
+  if (warp == C::RAW_WARP) {
     // ------------------------------------------------------------ TMA producer: packed weights
     if (lane == 0) {
       bool ok = true;
@@ -299,13 +322,16 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const int in_ = it / args.items_m;
         const int row0 = in_ * args.rows_item;
         const int nrows = min(args.rows_item, args.N - row0);
-        const int boxes = (nrows + 15) >> 4;
+        // one box of rows_item rows per raw stage where the tensor map was built that way (rows past N arrive as
+        // zeros and count), else 16-row boxes
+        const int brows = args.raw_box_rows;
+        const int boxes = (nrows + brows - 1) / brows;
         for (int rsi = 0; rsi < raws_per_item; ++rsi) {
           ok = ptx::mbar_wait_bounded_fast(raw_empty(rs), rphase ^ 1u, abort_flag, 1, WAIT_NS);
           if (!ok) break;
-          ptx::mbar_arrive_expect_tx(raw_full(rs), (uint32_t)boxes * 16u * 128u);
+          ptx::mbar_arrive_expect_tx(raw_full(rs), (uint32_t)(boxes * brows) * 128u);
           const uint32_t dst = smem_base + (uint32_t)rs * RAW_STAGE_BYTES;
-          for (int b = 0; b < boxes; ++b) ptx::tma_load_2d(dst + (uint32_t)b * 2048u, &tmap_w, raw_full(rs), rsi * 128, row0 + b * 16);
+          for (int b = 0; b < boxes; ++b) ptx::tma_load_2d(dst + (uint32_t)(b * brows) * 128u, &tmap_w, raw_full(rs), rsi * 128, row0 + b * brows);
           // a last raw stage with fewer than four k-blocks: nobody reads the missing ones, stand in for their arrivals
           const int nreal = min(RAW_KB, num_kb - rsi * RAW_KB);
           if (nreal < RAW_KB) ptx::mbar_arrive_n(raw_empty(rs), (uint32_t)(4 * (RAW_KB - nreal)));
@@ -316,7 +342,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
       }
     }
-  } else if (warp == 2) {
+  } else if (warp == C::B_WARP) {
     // ------------------------------------------------------------ TMA producer: activation tiles (many-token form)
     if (!FEW && lane == 0) {
       bool ok = true;
@@ -336,7 +362,44 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (C::NI > 1 && warp < C::NI) {
+    // ------------------------------------------------------------ MMA issuers (one per scheduler)
+    if (lane == 0) {
+      bool ok = true;
+      const uint64_t bdesc0 = ptx::make_smem_desc_kmajor(smem_base + (uint32_t)b_off, 1024, 2);
+      const uint32_t b_hi = (uint32_t)(bdesc0 >> 32);
+      const uint32_t b_lo0 = (uint32_t)bdesc0;
+      const uint32_t a_t0 = tmem_base + (uint32_t)C::A_COL0;
+      const uint32_t idesc = args.idesc;
+      // An mbarrier tells only the parity of its phase, so the issuer that waits for the n-th filling of a stage must
+      // be the one that consumed the (n-1)-th (else it could take the completion of filling n-2 for the one it needs):
+      // the host picks the number of issuers in use so that a stage always meets the same issuer.
+      const int NI = args.ni;
+      for (int it = item_begin; it < item_end && ok && warp < NI; ++it) {
+        const int pbase = (it - item_begin) * periods_per_item, jbase = (it - item_begin) * num_kb;
+        int p = (warp - pbase % NI + NI) % NI;   // this issuer's first period of the item
+        for (; p < periods_per_item && ok; p += NI) {
+          const int P = pbase + p, acc = P % NACC;
+          ok = ptx::mbar_wait_bounded_fast(acc_empty(acc), (((uint32_t)(P / NACC)) & 1u) ^ 1u, abort_flag, 3, WAIT_NS);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const int kb0 = p * kb_per_period, kb1 = min(kb0 + kb_per_period, num_kb);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            const int j = jbase + kb, as = j % AS;
+            ok = ptx::mbar_wait_bounded_fast(a_full(as), ((uint32_t)(j / AS)) & 1u, abort_flag, 4, WAIT_NS);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            if (!(args.debug & 2))
+              ptx::umma_kblock_f16_ts(tmem_base + (uint32_t)(acc * N_MMA), a_t0 + (uint32_t)(as * A_COLS),
+                                      b_lo0 + (uint32_t)as * (uint32_t)(C::B_STAGE_BYTES >> 4), b_hi, idesc, kb != kb0 ? 1u : 0u);
+            ptx::umma_commit(a_empty(as));
+          }
+          if (!ok) break;
+          ptx::umma_commit(acc_full(acc));
+        }
+      }
+    }
+  } else if (C::NI == 1 && warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = true;
@@ -356,15 +419,15 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         int in_period = 0, in_group = 0;
         uint32_t b_row = b_row_first;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (in_period == 0) {
-            ok = ptx::mbar_wait_bounded_fast(acc_empty(acc), acc_phase ^ 1u, abort_flag, 3, WAIT_NS);
+          if (in_period == 0 && acc % SET == 0) {   // the first accumulator of a set: the epilogue has drained the set
+            ok = ptx::mbar_wait_bounded_fast(acc_empty(acc / SET), acc_phase ^ 1u, abort_flag, 3, WAIT_NS);
             if (!ok) break;
             ptx::tc_fence_after_sync();
           }
           ok = ptx::mbar_wait_bounded_fast(a_full(as), aphase, abort_flag, 4, WAIT_NS);
           if (!ok) break;
           ptx::tc_fence_after_sync();
-          ptx::umma_kblock_f16_ts(tmem_base + (uint32_t)(acc * N_MMA), a_t, b_lo + b_row, b_hi, idesc, in_period != 0 ? 1u : 0u);
+          if (!(args.debug & 2)) ptx::umma_kblock_f16_ts(tmem_base + (uint32_t)(acc * N_MMA), a_t, b_lo + b_row, b_hi, idesc, in_period != 0 ? 1u : 0u);
           ptx::umma_commit(a_empty(as));
           if (++as == AS) {
             as = 0;
@@ -380,10 +443,16 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             b_row -= b_row_step;
           }
           if (++in_period == kb_per_period || kb == num_kb - 1) {
-            ptx::umma_commit(acc_full(acc));
             in_period = 0;
             b_row = b_row_first;
-            if (++acc == NACC) {
+            const bool item_done = kb == num_kb - 1;
+            if ((acc + 1) % SET == 0 || item_done) {
+              ptx::umma_commit(acc_full(acc / SET));          // the set (or what the item fills of it) is complete
+              acc = (acc / SET + 1) * SET;                     // an item always starts on a set boundary
+            } else {
+              ++acc;
+            }
+            if (acc == NACC) {
               acc = 0;
               acc_phase ^= 1u;
             }
@@ -436,7 +505,7 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         ptx::tc_fence_after_sync();
         const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < 2 && !(args.debug & 1); ++h) {
           uint32_t o[16];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -505,38 +574,47 @@ a16_w4_umma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       for (int c = 0; c < MY_COLS; ++c) running[c] = 0.f;
       const bool live = row < nrows;
       const int n_safe = live ? row : 0;
-      for (int pi = 0; pi < periods_per_item && ok; ++pi) {
-        if (!(ok = warp_wait(acc_full(acc), acc_phase, 8))) break;
+      for (int ps = 0; ps < periods_per_item && ok; ps += SET) {
+        const int set = acc / SET;
+        if (!(ok = warp_wait(acc_full(set), acc_phase, 8))) break;
         ptx::tc_fence_after_sync();
-        const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * N_MMA + part * MY_COLS);
-        const int g0 = pi * args.G;
-        float s;
-        if (!FEW) s = bits_to_f32<F16>((uint32_t)scaleT[min(g0, args.gpr - 1) * SCALE_PITCH + n_safe]);
+        const int nvalid = min(SET, periods_per_item - ps);
 #pragma unroll
-        for (int c0 = 0; c0 < MY_COLS / 16; ++c0) {
-          uint32_t r[16];
-          ptx::tmem_ld_32x32b_x16(t_addr + (uint32_t)(c0 * 16), r);
-          ptx::tmem_ld_wait_16(r);
-          if (c0 == MY_COLS / 16 - 1) {   // the last columns are in registers: the buffer goes back before the arithmetic
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(acc_empty(acc));
-          }
-          if (FEW) {
-            // column c = g_local * mtok + token; running[] stays indexed by column so that every index is a constant
+        for (int a = 0; a < SET; ++a) {
+          if (a < nvalid) {
+            const int pi = ps + a;
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((acc + a) * N_MMA + part * MY_COLS);
+            const int g0 = pi * args.G;
+            float s;
+            if (!FEW) s = bits_to_f32<F16>((uint32_t)scaleT[min(g0, args.gpr - 1) * SCALE_PITCH + n_safe]);
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              int g = g0 + (c >> mtok_shift);
-              if (g >= args.gpr) g = args.gpr - 1;   // columns of groups past K hold zeros
-              const float sg = bits_to_f32<F16>((uint32_t)scaleT[g * SCALE_PITCH + n_safe]);
-              running[c] = fmaf(sg, __uint_as_float(r[c]), running[c]);
+            for (int c0 = 0; c0 < MY_COLS / 16; ++c0) {
+              uint32_t r[16];
+              ptx::tmem_ld_32x32b_x16(t_addr + (uint32_t)(c0 * 16), r);
+              ptx::tmem_ld_wait_16(r);
+              if (a == nvalid - 1 && c0 == MY_COLS / 16 - 1) {   // the set's last columns are in registers: hand the set back
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(acc_empty(set));
+              }
+              if (FEW) {
+                // column c = g_local * mtok + token; running[] stays indexed by column so that every index is a constant
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                  int g = g0 + (c >> mtok_shift);
+                  if (g >= args.gpr) g = args.gpr - 1;   // columns of groups past K hold zeros
+                  const float sg = bits_to_f32<F16>((uint32_t)scaleT[g * SCALE_PITCH + n_safe]);
+                  running[c] = fmaf(sg, __uint_as_float(r[c]), running[c]);
+                }
+              } else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) running[c0 * 16 + c] = fmaf(s, __uint_as_float(r[c]), running[c0 * 16 + c]);
+              }
             }
-          } else {
-#pragma unroll
-            for (int c = 0; c < 16; ++c) running[c0 * 16 + c] = fmaf(s, __uint_as_float(r[c]), running[c0 * 16 + c]);
           }
         }
-        if (++acc == NACC) {
+        acc += SET;
+        if (acc == NACC) {
           acc = 0;
           acc_phase ^= 1u;
         }
@@ -590,6 +668,16 @@ int launch_umma(const CUtensorMap& tw, const CUtensorMap& tx, UmmaArgs a, int gr
   const int smem = C::total(a.raw_stages, a.gpr, x_bytes);
   if (smem > 227 * 1024) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 tensor-core kernel: shared memory does not hold two raw stages");
   a.idesc = ptx::make_idesc(1u, F16 ? 0u : 1u, F16 ? 0u : 1u, (uint32_t)TILE_ROWS, (uint32_t)C::N_MMA);  // f32 accumulate
+  {
+    // issuers in use: drain periods go round them, and a period's k-blocks occupy consecutive A stages; the ring of AS
+    // stages must hold a whole number of rounds, and periods must not straddle items
+    const int kbpp = a.G * a.kpg;
+    int ni = C::NI;
+    if (C::AS % kbpp != 0 || a.num_kb % kbpp != 0) ni = 1;
+    else
+      while (ni > 1 && (C::AS / kbpp) % ni != 0) ni /= 2;
+    a.ni = ni;
+  }
   auto kfn = a16_w4_umma_kernel<MT, F16>;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   cudaLaunchConfig_t cfg{};
@@ -1026,6 +1114,13 @@ int a16_w4_umma_launch(const void* x, const void* wq, const void* scale, const v
   a.num_kb = K / KB;
   a.kpg = group / KB;
   a.status = status;
+  {
+    static const int dbg = [] {
+      const char* v = getenv("B200Q_UMMA_DEBUG");
+      return v ? atoi(v) : 0;
+    }();
+    a.debug = dbg;
+  }
   // few-token form: up to 4 tokens whose activations fit in shared memory next to two raw stages
   const int mtok_few = M <= 1 ? 1 : M <= 2 ? 2 : 4;
   const bool few = !f16 && M <= 4 && FewCfg::total(2, a.gpr, mtok_few * K * 2) <= 227 * 1024;   // (the few-token form is built for bf16)
@@ -1063,7 +1158,9 @@ int a16_w4_umma_launch(const void* x, const void* wq, const void* scale, const v
   {
     const uint64_t dims[2] = {(uint64_t)(K / 2), (uint64_t)N};
     const uint64_t strides[1] = {(uint64_t)(K / 2)};
-    const uint32_t box[2] = {128u, 16u};
+    // 16-row boxes (one box of rows_item rows per raw stage was measured: no faster below 64 tokens, slower above)
+    a.raw_box_rows = 16;
+    const uint32_t box[2] = {128u, (uint32_t)a.raw_box_rows};
     B200Q_TRY(make_tmap_u8(&tw, wq, 2, dims, strides, box));
   }
   if (few) return launch_umma_few(tw, a, grid, stream);

@@ -160,9 +160,11 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
     case 3: use_resident = resident_ok; use_umma = !resident_ok && !gemv_ok && umma_ok; break;
     default:
       // up to 8 tokens: the decode kernels.  Above: the fused kernel (exact group scaling, no copy of the weight);
-      // from 512 tokens on a handle trades 2^-9 of relative weight rounding for the plain bf16 GEMM's speed.
+      // from 64 tokens on a handle trades 2^-9 of relative weight rounding for the plain bf16 GEMM's speed (measured
+      // at N = 11008, K = 4096: 16 / 32 tokens 29.7 us either way, 64 tokens 30.8 against 32-38 us, 128 tokens 33.4
+      // against 46-53 us, 512 tokens 56 against 150 us).
       if (gemv_ok) break;
-      if (resident_ok && M >= 512) use_resident = true;
+      if (resident_ok && M >= 64) use_resident = true;
       else use_umma = umma_ok;
   }
   if (use_umma) return a16_w4_umma_launch(x, wq, scale, zp, bias, y, M, N, K, group, status, s, f16);

@@ -136,6 +136,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 
 // The same bounded wait for hand-offs that happen every few hundred cycles: plain try_wait in a loop (each try blocks
 // in hardware for a short, system-chosen time), no software back-off whose sleep would add to every hand-off.
+template <unsigned SLEEP_NS = 40>
 __device__ __forceinline__ bool mbar_wait_bounded_fast(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where,
                                                        uint64_t budget_ns) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -143,7 +144,7 @@ __device__ __forceinline__ bool mbar_wait_bounded_fast(uint32_t bar, uint32_t pa
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(40);   // a waiting warp must not take issue slots from the warps it is waiting for
+    __nanosleep(SLEEP_NS);   // a waiting warp must not take issue slots from the warps it is waiting for
     if ((++spins & 255u) == 0u) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > budget_ns) {
@@ -165,6 +166,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// 3-D tile load (no multicast): the box lands as [c2][c1][c0 bytes] in shared memory.
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar, int32_t c0, int32_t c1,
+                                            int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 
