@@ -127,7 +127,8 @@ typedef struct {
   int64_t batch, M, K, N;
   int32_t with_bias, do_relu;
   int32_t right_transpose;   /* right operand stored [N,K] instead of [K,N] */
-  int32_t left_transpose, output_transpose, hdim_is_batch; /* must be 0: B200Q_ERR_UNSUPPORTED otherwise */
+  int32_t left_transpose, output_transpose; /* input stored [batch][K][M] / output stored [batch][N][M] */
+  int32_t hdim_is_batch;                    /* must be 0: B200Q_ERR_UNSUPPORTED otherwise */
   int32_t right_batched;     /* right operand has the batch dimension (activation x activation) */
   int32_t right_is_weight;   /* constant right operand: uploaded once per (handle, weight_version) */
   int32_t weight_version;    /* bump after rewriting the weight buffers in place */

@@ -31,10 +31,14 @@ def run(graph, weights, inputs):
         elif t == "tpu.MatMul":
             fuse_rq = bool(a.get("fuse_rq", False))
             mult = oracle.through_f32(weights[name + "_multi"]) if fuse_rq else a["multipliers"]
+            if a.get("left_transpose", False):      # stored [K, M]: lib/Support/Dnnl/MatMul.cpp:182-186 transposes it first
+                x = np.ascontiguousarray(x.T)
             T[name] = oracle.matmul_int8(x, weights[name + "_filter"], weights.get(name + "_bias"), do_relu=a["do_relu"],
                                          right_transpose=bool(a.get("right_transpose", False)),
                                          qmode=_QM[a["quant_mode"]], fuse_rq=fuse_rq, mult=mult, rshift=a["rshifts"][:1] if fuse_rq else a["rshifts"],
                                          out_zp=o["zp"], out_dt=_DT[o["dtype"]])
+            if a.get("output_transpose", False):    # stored [N, M]: lib/Support/Dnnl/MatMul.cpp:229-238
+                T[name] = np.ascontiguousarray(T[name].T)
         elif t == "tpu.Add":
             m, s = a["multipliers"], a["rshifts"]
             T[name] = oracle.add_int8(x, T[op["inputs"][1]], m[0], s[0], m[1], s[1], do_relu=a["do_relu"], out_dt=_DT[o["dtype"]])

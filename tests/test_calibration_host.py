@@ -99,13 +99,18 @@ def _worker(rank, world, port, total, q):
     batches = [mine[i:i + 3] for i in range(0, per, 3)]
     cal = ShardedCalibrator(_forward, math=OracleMath(), dist=dist)
     res = cal.run(batches, samples_per_rank=per)
+    shard_dir = os.environ.get("B200Q_TEST_SHARD_DIR")
+    if shard_dir:
+        from tpu_mlir_b200.calibration import save_shard
+        save_shard(cal, os.path.join(shard_dir, f"shard{rank}.npz"))
     if rank == 0:
         q.put({n: (cal.histograms[n].numpy().copy(), r.width, r.kl, r.bins, r.threshold) for n, r in res.items()})
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_sharded_calibrator_two_ranks_matches_streaming_reference():
+def test_sharded_calibrator_two_ranks_matches_streaming_reference(tmp_path, monkeypatch):
+    monkeypatch.setenv("B200Q_TEST_SHARD_DIR", str(tmp_path))
     total, world = 12, 2
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -127,6 +132,14 @@ def test_sharded_calibrator_two_ranks_matches_streaming_reference():
         assert np.float32(g_width).tobytes() == np.float32(width).tobytes()
         assert np.float32(g_kl).tobytes() == np.float32(kl).tobytes()
     assert got["zero"][3] == 0 and got["zero"][4] == 1e-5
+    # the per-rank shard files re-merge to the same result without the ranks; a missing shard is refused
+    from tpu_mlir_b200.calibration import merge_shards
+    merged = merge_shards([str(tmp_path / "shard1.npz"), str(tmp_path / "shard0.npz")], math=OracleMath())
+    for name in ("a", "b", "zero"):
+        assert merged[name].bins == got[name][3] and np.float32(merged[name].kl).tobytes() == np.float32(got[name][2]).tobytes()
+        assert merged[name].threshold == got[name][4]
+    with pytest.raises(ValueError):
+        merge_shards([str(tmp_path / "shard0.npz")], math=OracleMath())
 
 
 def test_single_process_path():

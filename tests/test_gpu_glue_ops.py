@@ -308,10 +308,37 @@ def test_executor_matmul_honours_its_attributes(case, tmp_path):
         assert np.array_equal(m.get_tensor("fc"), want["fc"]) and want["fc"].any()
 
 
+@pytest.mark.parametrize("lt,ot", [(True, False), (False, True), (True, True)])
+def test_executor_matmul_transposed_operands(lt, ot):
+    """left_transpose: the input tensor is stored [K, M]; output_transpose: the output tensor is stored [N, M]
+    (MatMul.cpp:24-135, lib/Support/Dnnl/MatMul.cpp:182-186,:229-238)."""
+    import oracle_graph
+    from tpu_mlir_b200.module import module
+    rng = np.random.default_rng(21)
+    M, K, N = 37, 64, 24
+    in_shape, out_shape = ([K, M] if lt else [M, K]), ([N, M] if ot else [M, N])
+    tens = {"input": dict(shape=in_shape, dtype="f32"), "q": dict(shape=in_shape, dtype="i8", scale=0.05, zp=0),
+            "fc": dict(shape=out_shape, dtype="i8", scale=0.2, zp=0), "out": dict(shape=out_shape, dtype="f32")}
+    ops = [dict(type="tpu.Cast", name="q", inputs=["input"]),
+           dict(type="tpu.MatMul", name="fc", inputs=["q"], attrs=dict(do_relu=False, quant_mode="MultiplierShift", multipliers=[777],
+                                                                       rshifts=[14], left_transpose=lt, output_transpose=ot)),
+           dict(type="tpu.Cast", name="out", inputs=["fc"])]
+    g = dict(inputs=["input"], outputs=["out"], tensors=tens, ops=ops)
+    w = {"fc_filter": rng.integers(-127, 128, (K, N), dtype=np.int8), "fc_bias": rng.integers(-500, 500, N, dtype=np.int32)}
+    x = rng.standard_normal(in_shape).astype(np.float32)
+    want = oracle_graph.run(g, w, {"input": x})
+    m = module()
+    m.load(g, w)
+    m.set_tensor("input", x)
+    m.invoke(fixed_to_float=False)
+    assert list(want["fc"].shape) == out_shape and len(np.unique(want["fc"])) > 30
+    assert np.array_equal(m.get_tensor("fc"), want["fc"])
+    assert np.array_equal(m.get_tensor("out"), want["out"])
+
+
 def test_executor_refuses_matmul_attributes_it_does_not_honour():
     from tpu_mlir_b200.module import module
-    for bad in (dict(left_transpose=True), dict(hdim_is_batch=True), dict(output_transpose=True), dict(input_zp=4),
-                dict(quant_mode="OnlyScale")):
+    for bad in (dict(hdim_is_batch=True), dict(input_zp=4), dict(quant_mode="OnlyScale")):
         attrs = dict(quant_mode="MultiplierShift", multipliers=[77], rshifts=[12])
         attrs.update(bad)
         g, w = _matmul_graph(attrs)

@@ -209,10 +209,36 @@ def test_operator_face_zero_points_and_batched_right():
     assert np.array_equal(out, want.astype(np.float32))
 
 
+@pytest.mark.parametrize("lt,ot", [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("batch,right_batched", [(1, False), (3, True), (2, False)])
+def test_operator_face_left_and_output_transpose(lt, ot, batch, right_batched):
+    """left_transpose: inputs[0] holds [batch][K][M]; output_transpose: outputs[0] holds [batch][N][M]
+    (MatMul.cpp:24-135; lib/Support/Dnnl/MatMul.cpp:182-186,:229-238 transpose around the product)."""
+    rng = np.random.default_rng(31 + batch)
+    M, K, N = 45, 96, 40
+    A = rng.integers(-128, 128, size=(batch, M, K), dtype=np.int8)
+    B = rng.integers(-128, 128, size=(batch, K, N) if right_batched else (K, N), dtype=np.int8)
+    bias = rng.integers(-2**12, 2**12, size=N, dtype=np.int32)
+    want = np.stack([oracle.matmul_int8(A[b], B[b] if right_batched else B, bias, qmode=oracle.QM_MULTIPLIER_SHIFT, mult=[5], rshift=[11])
+                     for b in range(batch)])
+    op = MatMulOp(batch=batch, M=M, K=K, N=N, with_bias=True, left_transpose=lt, output_transpose=ot, right_batched=right_batched,
+                  right_is_weight=not right_batched, multipliers=[5], rshifts=[11])
+    a_in = np.ascontiguousarray(A.transpose(0, 2, 1)) if lt else A
+    out = np.zeros((batch, N, M) if ot else (batch, M, N), np.float32)
+    op.inference(InferenceParameter(inputs=[f32(a_in), f32(B), f32(bias)], outputs=[out]))
+    got = out.transpose(0, 2, 1) if ot else out
+    assert np.array_equal(got, want.astype(np.float32)) and len(np.unique(want)) > 50
+
+
 def test_empty_and_errors():
     op = MatMulOp(M=0, K=16, N=8, multipliers=[1], rshifts=[0])
     out = np.zeros((0, 8), np.float32)
     op.inference(InferenceParameter(inputs=[np.zeros((0, 16), np.float32), np.zeros((16, 8), np.float32)], outputs=[out]))
+    op = MatMulOp(M=4, K=16, N=8, hdim_is_batch=True, multipliers=[1], rshifts=[0])
+    with pytest.raises(L.B200QError) as ei:
+        op.inference(InferenceParameter(inputs=[np.zeros((4, 16), np.float32), np.zeros((16, 8), np.float32)],
+                                        outputs=[np.zeros((4, 8), np.float32)]))
+    assert ei.value.code == L.ERR_UNSUPPORTED
     op = MatMulOp(M=4, K=16, N=8, quant_mode=L.QM_QDM, multipliers=[1], rshifts=[0])
     with pytest.raises(L.B200QError) as ei:
         op.inference(InferenceParameter(inputs=[np.zeros((4, 16), np.float32), np.zeros((16, 8), np.float32)],

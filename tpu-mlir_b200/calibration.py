@@ -384,6 +384,9 @@ class ShardedCalibrator:
             done += next(iter(acts.values())).shape[0]
             del acts
         t0 = lap("pass2_histograms", t0)
+        # this rank's own contribution, kept for save_shard (the all-reduce below overwrites `flat` with the sum)
+        self._shard = dict(names=list(names), minmax=mm_local.cpu().numpy(), hist=flat.cpu().numpy().copy(), sizes=np.asarray(sizes, np.int64),
+                           rank=rank, world=world, samples_per_rank=int(samples_per_rank), bin_num=int(self.bin_num))
         self.allreduce_bytes = int(flat.numel() * 4) if self.dist else 0
         self.cached_bytes = int(held)
         if self.dist:
@@ -403,6 +406,53 @@ class ShardedCalibrator:
         self.timings = tm
         self.histograms = {n: views[n] for n in names}
         return out
+
+
+def save_shard(calibrator: ShardedCalibrator, path: str) -> None:
+    """Persist this rank's part of a finished ``run``: its per-sample (min, max) pairs and its local histograms (before
+    the all-reduce), so that a calibration can be re-merged without the ranks, or one shard recomputed after a failure
+    (the reference keeps only the final table, kld_calibrator.py:804-884)."""
+    sh = calibrator._shard
+    np.savez(path, names=np.array(sh["names"]), minmax=sh["minmax"], hist=sh["hist"], sizes=sh["sizes"],
+             meta=np.array([sh["rank"], sh["world"], sh["samples_per_rank"], sh["bin_num"]], np.int64))
+
+
+def merge_shards(paths: Sequence[str], math=None, dst_bins: int = 128) -> Dict[str, TensorResult]:
+    """Rebuild the result of a sharded run from the files ``save_shard`` wrote, one per rank: the bin schedule is
+    recomputed from all ranks' (min, max) pairs in rank order, the int32 histograms are summed (what the all-reduce
+    does) and the thresholds searched again.  Raises if a shard is missing or was histogrammed under another schedule
+    (e.g. recomputed with different samples)."""
+    import torch
+    shards = sorted((dict(np.load(p)) for p in paths), key=lambda d: int(d["meta"][0]))
+    world = int(shards[0]["meta"][1])
+    if [int(d["meta"][0]) for d in shards] != list(range(world)):
+        raise ValueError(f"need one shard per rank 0..{world - 1}, got ranks {[int(d['meta'][0]) for d in shards]}")
+    names = [str(n) for n in shards[0]["names"]]
+    bin_num = int(shards[0]["meta"][3])
+    for d in shards:
+        if [str(n) for n in d["names"]] != names or int(d["meta"][3]) != bin_num or int(d["meta"][2]) != int(shards[0]["meta"][2]):
+            raise ValueError("shards disagree on tensors, samples per rank or bin count")
+    mm_all = np.concatenate([d["minmax"] for d in shards], axis=1)
+    sched = bin_schedule_many(mm_all[:, :, 0], mm_all[:, :, 1], bin_num)
+    sizes = np.array([max(sc.final_bins, 1) for sc in sched], np.int64)
+    for d in shards:
+        if not np.array_equal(d["sizes"], sizes):
+            raise ValueError("a shard's histograms were built under a different bin schedule: recompute it with the same samples")
+    flat = np.sum([d["hist"].astype(np.int64) for d in shards], axis=0).astype(np.int32)
+    offs = np.concatenate(([0], np.cumsum(sizes)))
+    m = math if math is not None else CaliMathB200()
+    dev = "cuda" if isinstance(m, CaliMathB200) else "cpu"
+    tflat = torch.from_numpy(flat).to(dev)
+    views = [tflat[int(offs[t]):int(offs[t + 1])] for t in range(len(names))]
+    live = [t for t, sc in enumerate(sched) if sc.final_bins]
+    kl = m.find_thresholds([views[t] for t in live], [sched[t].width for t in live], dst_bins) if live else []
+    out: Dict[str, TensorResult] = {}
+    for t, n in enumerate(names):
+        sc = sched[t]
+        k = float(kl[live.index(t)]) if t in live else 0.0
+        out[n] = TensorResult(name=n, min=float(sc.min), max=float(sc.max), abs_max=float(sc.abs_max), bins=sc.final_bins,
+                              width=float(sc.width), kl=k, threshold=table_threshold(k, sc.abs_max) if t in live else 1e-5)
+    return out
 
 
 def dump_cali_table(path: str, results: Dict[str, TensorResult], *, order: Optional[List[str]] = None, mlir_file: str = "",

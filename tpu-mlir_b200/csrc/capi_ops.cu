@@ -152,7 +152,7 @@ int resolve_matmul(const b200q_matmul_desc& d, const float* multi_operand, int b
 int validate_matmul(const b200q_matmul_desc& d) {
   if (d.batch < 1 || d.M < 0 || d.K < 1 || d.N < 1) return set_error(B200Q_ERR_INVALID, "matmul: bad shape");
   if (d.M * d.batch > 0x7fffffffLL || d.N > 0x7fffffffLL || d.K > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: dimension exceeds int32");
-  if (d.left_transpose || d.output_transpose || d.hdim_is_batch) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: left/output transpose and hdim_is_batch are not implemented");
+  if (d.hdim_is_batch) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: hdim_is_batch is not implemented");
   if (!is_q8(d.input_dtype) || !is_q8(d.right_dtype)) return set_error(B200Q_ERR_INVALID, "matmul: operands must be int8/uint8");
   return B200Q_OK;
 }
@@ -632,7 +632,15 @@ int b200q_matmul_inference(const b200q_matmul_desc* desc, float* const* inputs, 
     if ((rc = h->out_q.ensure(o_elems * dtype_size(d.out_dtype)))) break;
     if ((rc = h->out_f32.ensure(o_elems * 4))) break;
     if (cudaMemcpyAsync(h->stage_f32.p, inputs[0], a_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D input", __FILE__, __LINE__); break; }
-    if ((rc = f32_to_q8(h->stage_f32.as<float>(), h->a_q8.p, (long long)a_elems, s))) break;
+    if (d.left_transpose) {
+      // the input is stored [batch][K][M] (MatMul.cpp:24-135 reads M from the last dimension; lib/Support/Dnnl/MatMul.cpp:
+      // 182-186 transposes every batch entry before the product)
+      for (int64_t b = 0; b < d.batch && rc == B200Q_OK; ++b)
+        rc = transpose_to_u8(h->stage_f32.as<float>() + b * d.K * d.M, 1, h->a_q8.as<uint8_t>() + b * d.M * d.K, (int)d.K, (int)d.M, s);
+      if (rc) break;
+    } else if ((rc = f32_to_q8(h->stage_f32.as<float>(), h->a_q8.p, (long long)a_elems, s))) {
+      break;
+    }
     const int n_launch = (d.right_batched || d.is_cv18xx) ? (int)d.batch : 1;
     const int64_t rows_per = (n_launch == 1) ? rows : d.M;
     for (int b = 0; b < n_launch && rc == B200Q_OK; ++b) {
@@ -650,7 +658,16 @@ int b200q_matmul_inference(const b200q_matmul_desc* desc, float* const* inputs, 
     }
     if (rc) break;
     if ((rc = q_to_f32(h->out_q.p, d.out_dtype, h->out_f32.as<float>(), (long long)o_elems, s))) break;
-    if (cudaMemcpyAsync(outputs[0], h->out_f32.p, o_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__); break; }
+    const float* result = h->out_f32.as<float>();
+    if (d.output_transpose) {
+      // the output is stored [batch][N][M] (lib/Support/Dnnl/MatMul.cpp:229-238)
+      if ((rc = h->stage_f32.ensure(o_elems * 4))) break;
+      for (int64_t b = 0; b < d.batch && rc == B200Q_OK; ++b)
+        rc = transpose_f32(h->out_f32.as<float>() + b * d.M * d.N, h->stage_f32.as<float>() + b * d.M * d.N, (int)d.M, (int)d.N, s);
+      if (rc) break;
+      result = h->stage_f32.as<float>();
+    }
+    if (cudaMemcpyAsync(outputs[0], result, o_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__); break; }
     rc = read_status(h->status, s, "matmul");
   } while (0);
   if (rc != B200Q_OK) cudaStreamSynchronize(s);

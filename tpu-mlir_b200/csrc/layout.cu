@@ -376,6 +376,30 @@ int transpose_to_u8(const void* src, int src_is_f32, void* dst, int rows, int co
   return B200Q_OK;
 }
 
+// dst[c][r] = src[r][c] for float matrices (the output_transpose of tpu.MatMul, lib/Support/Dnnl/MatMul.cpp:229-238)
+__global__ void transpose_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int cols) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int r = r0 + j, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = src[(size_t)r * cols + c];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) dst[(size_t)c * rows + r] = tile[threadIdx.x][j];
+  }
+}
+
+int transpose_f32(const float* src, float* dst, int rows, int cols, cudaStream_t s) {
+  if (rows == 0 || cols == 0) return B200Q_OK;
+  dim3 grid(ceil_div(cols, 32), ceil_div(rows, 32)), block(32, 8);
+  if (grid.y > 65535) return set_error(B200Q_ERR_UNSUPPORTED, "transpose: too many rows");
+  transpose_f32_kernel<<<grid, block, 0, s>>>(src, dst, rows, cols);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
 int f32_to_q8(const float* x, void* y, long long n, cudaStream_t s) {
   if (n == 0) return B200Q_OK;
   f32_to_q8_kernel<<<blocks_for(n, 256), 256, 0, s>>>(x, (uint8_t*)y, n);

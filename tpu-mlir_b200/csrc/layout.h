@@ -16,6 +16,7 @@ int repack_weight_pairs64(const void* w, int w_is_f32, void* wr, int OC, int KH,
 int repack_weight_fy_c_fx8(const void* w, int w_is_f32, void* wr, int OC, int C, int KH, int KW, int kpad, cudaStream_t s);
 // [rows][cols] -> [cols][rows] bytes.
 int transpose_to_u8(const void* src, int src_is_f32, void* dst, int rows, int cols, cudaStream_t s);
+int transpose_f32(const float* src, float* dst, int rows, int cols, cudaStream_t s);
 int f32_to_q8(const float* x, void* y, long long n, cudaStream_t s);
 int f32_to_i32(const float* x, int32_t* y, long long n, cudaStream_t s);
 int q_to_f32(const void* x, int dt, float* y, long long n, cudaStream_t s);

@@ -239,16 +239,20 @@ class module:  # noqa: N801  (name of the reference class)
             # What the reference reads from the op (MatMul.cpp:24-135,:636-728): anything this plan does not honour is
             # refused, never computed differently.
             qmode = a.get("quant_mode", "MultiplierShift")
-            for key in ("left_transpose", "output_transpose", "hdim_is_batch"):
-                if a.get(key, False):
-                    raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.MatMul with {key} is not implemented")
+            if a.get("hdim_is_batch", False):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.MatMul with hdim_is_batch is not implemented")
+            lt, ot = bool(a.get("left_transpose", False)), bool(a.get("output_transpose", False))
+            if (lt or ot) and (int(np.prod(iinfo[0]["shape"][:-2])) != 1 or len(iinfo[0]["shape"]) < 2):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: the executor takes left/output transposes of 2-D operands only")
             if int(a.get("input_zp", 0)) != 0 or int(a.get("right_zp", 0)) != 0 or int(iinfo[0].get("zp", 0)) != 0:
                 raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.MatMul with operand zero points is not implemented by the executor")
             w = self.weights[op["name"] + "_filter"]
             w_nk = w.contiguous() if a.get("right_transpose", False) else w.t().contiguous()   # right operand K-major
             b = self.weights.get(op["name"] + "_bias")
-            M = int(np.prod(iinfo[0]["shape"][:-1]))
             N, K = w_nk.shape
+            # left_transpose: the input is stored [K, M]; output_transpose: the output is stored [N, M]
+            # (MatMul.cpp:24-135, lib/Support/Dnnl/MatMul.cpp:182-186,:229-238)
+            M = int(iinfo[0]["shape"][-1]) if lt else int(np.prod(iinfo[0]["shape"][:-1]))
             mults, shifts = [int(v) for v in a["multipliers"]], [int(v) for v in a["rshifts"]]
             fuse_rq = bool(a.get("fuse_rq", False))
             if qmode == "MultiplierShift" and fuse_rq:
@@ -275,6 +279,15 @@ class module:  # noqa: N801  (name of the reference class)
             status = self.torch.zeros(1, dtype=self.torch.int32, device=self.device)
             self._keep += [w_nk, mult, shift, e, status]
             self._status.append((op["name"], status))
+            if lt or ot:
+                def run_transposed():
+                    x_mk = ins[0].reshape(K, M).t().contiguous() if lt else ins[0]
+                    y_mn = self.torch.empty((M, N), dtype=out.dtype, device=self.device) if ot else out
+                    L.check(lib.b200q_gemm_i8_dev(_P(x_mk), _DT[iinfo[0]["dtype"]], _P(w_nk), L.DT_I8, M, N, K, C.byref(e),
+                                                  _P(y_mn), _P(status), L.ALGO_AUTO, stream()))
+                    if ot:
+                        out.copy_(y_mn.t().reshape(out.shape))
+                return run_transposed
             return lambda: L.check(lib.b200q_gemm_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(w_nk), L.DT_I8, M, N, K,
                                                          C.byref(e), _P(out), _P(status), L.ALGO_AUTO, stream()))
         if t == "tpu.Add":
