@@ -501,7 +501,7 @@ def calibration_line(R, total=None):
     images = torch.from_numpy(synth.calibration_images(seed=4, count=per, start=R.rank * per)).to(R.dev)
     fwd = resnet50.Fp32Forward(ops, R.dev)
     cal = ShardedCalibrator(fwd, dist=R.dist)
-    CB = int(os.environ.get("B200Q_CALIB_BATCH", "32"))      # samples per forward call
+    CB = int(os.environ.get("B200Q_CALIB_BATCH", "64"))      # samples per forward call (cuDNN picks its algorithms by batch size, so the table depends on it; the same at every N)
     batches = [images[i:i + CB] for i in range(0, per, CB)]
     if per >= 2 * CB:
         cal.run(batches[:2], samples_per_rank=2 * CB)      # warm-up: cuDNN algorithm choice, NCCL channels, allocator

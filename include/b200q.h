@@ -160,6 +160,11 @@ void b200q_matmul_deinit(void **handle);
  * Replaces MatMul::run (lib/Support/Dnnl/MatMul.cpp:223-241) + the requant loop (MatMul.cpp:636-728). */
 int b200q_gemm_i8_dev(const void *a, int a_dtype, const void *b_nk, int b_dtype, int64_t M, int64_t N, int64_t K,
                       const b200q_epilogue *epilogue, void *out, int32_t *status, int algo, void *stream);
+/* The same product with operand zero points subtracted first, (A - input_zp) * (B - right_zp)^T, as
+ * lib/Support/Dnnl/MatMul.cpp:193-205 does before the product; non-zero zero points take the CUDA-core kernel. */
+int b200q_gemm_i8_zp_dev(const void *a, int a_dtype, const void *b_nk, int b_dtype, int64_t M, int64_t N, int64_t K,
+                         int32_t input_zp, int32_t right_zp, const b200q_epilogue *epilogue, void *out, int32_t *status,
+                         int algo, void *stream);
 
 /* ------------------------------------------------------------------ tpu.Conv2D (INT8)
  * conv_attr_t (include/tpu_mlir/Support/AttrStruct.h:15-43) + the requant attributes of tpu.Conv2D

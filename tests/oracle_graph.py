@@ -35,6 +35,7 @@ def run(graph, weights, inputs):
                 x = np.ascontiguousarray(x.T)
             T[name] = oracle.matmul_int8(x, weights[name + "_filter"], weights.get(name + "_bias"), do_relu=a["do_relu"],
                                          right_transpose=bool(a.get("right_transpose", False)),
+                                         input_zp=int(a.get("input_zp", 0)), right_zp=int(a.get("right_zp", 0)),
                                          qmode=_QM[a["quant_mode"]], fuse_rq=fuse_rq, mult=mult, rshift=a["rshifts"][:1] if fuse_rq else a["rshifts"],
                                          out_zp=o["zp"], out_dt=_DT[o["dtype"]])
             if a.get("output_transpose", False):    # stored [N, M]: lib/Support/Dnnl/MatMul.cpp:229-238

@@ -164,7 +164,11 @@ def test_kld_random_against_oracle(m):
     assert np.array_equal(got, np.array(want, dtype=np.float32))
 
 
-def test_sharded_calibrator_single_gpu_matches_streaming_oracle(m):
+@pytest.mark.parametrize("cache_bytes", [None, 0, 4 * 2 * 4 * 33 * 17 * 4 + 64],
+                         ids=["whole_shard_kept", "second_forward", "first_batch_kept"])
+def test_sharded_calibrator_single_gpu_matches_streaming_oracle(m, cache_bytes):
+    """The three ways the second pass gets its activations: one region per tensor holding the whole shard (one kernel
+    launch per tensor), nothing kept (the network runs again, as in the reference), and a kept prefix of the batches."""
     rng = np.random.default_rng(8)
     x = torch.from_numpy((rng.standard_normal((10, 4, 33, 17)) * rng.uniform(0.5, 2.5, size=(10, 1, 1, 1)))
                          .astype(np.float32)).cuda()
@@ -173,7 +177,8 @@ def test_sharded_calibrator_single_gpu_matches_streaming_oracle(m):
         return {"conv": torch.nn.functional.avg_pool2d(b, 3, 1, 1), "relu": torch.relu(b)}
 
     cal = ShardedCalibrator(forward, math=m)
-    res = cal.run([x[0:4], x[4:8], x[8:10]], samples_per_rank=10)
+    res = cal.run([x[0:4], x[4:8], x[8:10]], samples_per_rank=10, cache_bytes=cache_bytes)
+    assert cal.cached_bytes == {None: 10 * 2 * 4 * 33 * 17 * 4, 0: 0}.get(cache_bytes, 4 * 2 * 4 * 33 * 17 * 4)
     for name in ("conv", "relu"):
         st = oracle.StreamingHistogram()
         for i in range(10):

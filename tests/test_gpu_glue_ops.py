@@ -280,7 +280,7 @@ def _matmul_graph(attrs, weights_extra=None, w_shape=(64, 24), zp=0):
     return dict(inputs=["input"], outputs=["out"], tensors=tens, ops=ops), weights
 
 
-@pytest.mark.parametrize("case", ["tflite", "tflite_lshift", "right_transpose", "fuse_rq"])
+@pytest.mark.parametrize("case", ["tflite", "tflite_lshift", "right_transpose", "fuse_rq", "zero_points"])
 def test_executor_matmul_honours_its_attributes(case, tmp_path):
     """tpu.MatMul through the executor with the attributes a lowered model can carry (MatMul.cpp:636-728): TFLite
     requantisation, a right operand stored [N, K], per-channel multipliers with a common shift; the graph goes through
@@ -291,6 +291,8 @@ def test_executor_matmul_honours_its_attributes(case, tmp_path):
     rng = np.random.default_rng(13)
     if case in ("tflite", "tflite_lshift"):
         g, w = _matmul_graph(dict(quant_mode="TFLite" if case == "tflite" else "TFLite_LShift", multipliers=[1518500250], rshifts=[9]), zp=3)
+    elif case == "zero_points":
+        g, w = _matmul_graph(dict(quant_mode="MultiplierShift", input_zp=4, right_zp=-3, multipliers=[777], rshifts=[14]))
     elif case == "right_transpose":
         g, w = _matmul_graph(dict(quant_mode="MultiplierShift", right_transpose=True, multipliers=[777], rshifts=[14]), w_shape=(24, 64))
     else:
@@ -338,7 +340,7 @@ def test_executor_matmul_transposed_operands(lt, ot):
 
 def test_executor_refuses_matmul_attributes_it_does_not_honour():
     from tpu_mlir_b200.module import module
-    for bad in (dict(hdim_is_batch=True), dict(input_zp=4), dict(quant_mode="OnlyScale")):
+    for bad in (dict(hdim_is_batch=True), dict(quant_mode="OnlyScale")):
         attrs = dict(quant_mode="MultiplierShift", multipliers=[77], rshifts=[12])
         attrs.update(bad)
         g, w = _matmul_graph(attrs)

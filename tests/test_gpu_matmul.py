@@ -133,6 +133,24 @@ def test_ragged_shapes_tensor_core(shape):
     assert np.array_equal(got, ref)
 
 
+def test_unsigned_by_unsigned_extreme_accumulators():
+    """u8 x u8 products reach 65025: the folded epilogue forms must size their accumulator bound from the operand
+    signedness.  All-255 operands, a large multiplier and a small shift drive every intermediate to its limit; half of
+    the columns use a mild pair so that unsaturated values are checked too."""
+    M, K, N = 128, 2048, 128
+    A = np.full((M, K), 255, np.uint8)
+    B = np.full((K, N), 255, np.uint8)
+    B[:, ::3] = np.random.default_rng(1).integers(0, 256, (K, len(range(0, N, 3))), dtype=np.uint8)
+    mult = np.where(np.arange(N) % 2 == 0, 30000, 3).astype(np.int64)
+    shift = np.where(np.arange(N) % 2 == 0, 3, 21).astype(np.int64)
+    acc = A.astype(np.int64) @ B.astype(np.int64)
+    for out_dt, odt in ((L.DT_I8, oracle.DT_I8), (L.DT_U8, oracle.DT_U8)):
+        want = oracle_requant(acc, L.RQ_MULTIPLIER_SHIFT, L.ROUND_HALF_UP, mult, shift, 0, False, odt)
+        got = run_gemm_dev(A, B, dict(dialect=L.RQ_MULTIPLIER_SHIFT, round_mode=L.ROUND_HALF_UP, mult=mult, shift=shift, out_dtype=out_dt),
+                           L.ALGO_TENSOR_CORE)
+        assert np.array_equal(got.astype(np.int64), want) and len(np.unique(want)) > 5, out_dt
+
+
 # ------------------------------------------------------------------ operator face (host float buffers)
 def f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)

@@ -86,6 +86,8 @@ SIGNATURES = {
     "b200q_matmul_deinit": (None, [_VPP]),
     "b200q_gemm_i8_dev": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64,
                                     C.POINTER(Epilogue), C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "b200q_gemm_i8_zp_dev": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
+                                       C.POINTER(Epilogue), C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "b200q_conv2d_init": (C.c_int, [C.POINTER(Conv2DDesc), _FLOATPP, C.c_int, _VPP]),
     "b200q_conv2d_inference": (C.c_int, [C.POINTER(Conv2DDesc), _FLOATPP, C.c_int, _FLOATPP, C.c_int, _VPP]),
     "b200q_conv2d_deinit": (None, [_VPP]),

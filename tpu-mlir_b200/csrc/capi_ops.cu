@@ -686,6 +686,17 @@ int b200q_gemm_i8_dev(const void* a, int a_dtype, const void* b_nk, int b_dtype,
   return gemm_dispatch(a, a_dtype, b_nk, b_dtype, M, N, K, 0, 0, e, out, status, algo, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_gemm_i8_zp_dev(const void* a, int a_dtype, const void* b_nk, int b_dtype, int64_t M, int64_t N, int64_t K,
+                         int32_t input_zp, int32_t right_zp, const b200q_epilogue* epilogue, void* out, int32_t* status,
+                         int algo, void* stream) {
+  if (!a || !b_nk || !epilogue || !out) return set_error(B200Q_ERR_INVALID, "gemm_i8_zp_dev: null argument");
+  if (!is_q8(a_dtype) || !is_q8(b_dtype)) return set_error(B200Q_ERR_INVALID, "gemm_i8_zp_dev: operands must be int8/uint8");
+  if (M < 0 || N < 1 || K < 1 || M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return set_error(B200Q_ERR_INVALID, "gemm_i8_zp_dev: bad shape");
+  Epilogue e;
+  std::memcpy(&e, epilogue, sizeof(e));
+  return gemm_dispatch(a, a_dtype, b_nk, b_dtype, M, N, K, input_zp, right_zp, e, out, status, algo, static_cast<cudaStream_t>(stream));
+}
+
 // ------------------------------------------------------------------------------------------------ Conv2D
 // Operator face: filter and bias from the host float buffers into the handle (upload, conversion, repacking).
 static int conv_upload_weights(ConvHandle* h, const b200q_conv2d_desc& d, float* const* inputs, int n_inputs, cudaStream_t s) {

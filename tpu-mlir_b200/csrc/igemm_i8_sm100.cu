@@ -1027,7 +1027,9 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   a.expect_extra = g_expect_extra.load(std::memory_order_relaxed);
   a.bf16 = p.kind == IGEMM_KIND_BF16;
   // |accumulator| < 2^29 for every 8-bit operand pair: lets the epilogue fold the bias into one 64-bit constant
-  a.acc_small = ((long long)a.num_kb * BLOCK_K * 32640ll) < (1ll << 29);
+  // largest |a * b| of one product: 255 * 255 for two unsigned operands, 255 * 128 mixed, 128 * 128 for two signed ones
+  const long long max_prod = (p.a_unsigned && p.b_unsigned) ? 65025ll : ((p.a_unsigned || p.b_unsigned) ? 32640ll : 16384ll);
+  a.acc_small = ((long long)a.num_kb * BLOCK_K * max_prod) < (1ll << 29);
   {
     int lo, hi;
     switch (epi.out_dtype) {
@@ -1046,7 +1048,7 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
     a.floor_needed = a.sat_lo2 > lo;
   }
   a.dependent_launch = p.dependent_launch;
-  a.acc_bound = a.acc_small ? (int)((long long)a.num_kb * BLOCK_K * 32640ll) : (1 << 29);
+  a.acc_bound = a.acc_small ? (int)((long long)a.num_kb * BLOCK_K * max_prod) : (1 << 29);
   a.bias_f32 = p.bias_f32;
   {
     const long long out_elems = p.out_mode == IGEMM_OUT_NCHW

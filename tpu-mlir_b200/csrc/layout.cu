@@ -2,6 +2,7 @@
 // tensors and the zero-bordered NHWC image the implicit GEMM reads, weight repacking (once per op),
 // and the float <-> native-integer conversions of the operator face (the interpreter keeps every tensor,
 // integer ones included, as float: bindings/pymlir/host/ModuleInterpreter.cpp:396-492).
+#include <cstdlib>
 #include "internal.h"
 #include "layout.h"
 
@@ -113,40 +114,50 @@ struct Pix16<float> {
   }
 };
 
-template <typename T>
+// TILES pixel tiles of 128 per block.  Two tiles (all loads issued before the first transposition, 832 blocks for a
+// 32 x 256 x 56 x 56 image, all resident at once) were measured against one tile (1600 blocks): 19.0 us against 15.1 us
+// inside the convolution step, so one tile is what runs; B200Q_LAYOUT_TILES=2 selects the other for A/B timing.
+template <typename T, int TILES>
 __global__ void __launch_bounds__(256)
 nchw_to_bordered_nhwc_wide_kernel(const T* __restrict__ x, uint8_t* __restrict__ y, int C, int H, int W, int bh, int bw) {
-  __shared__ uint32_t tile[128][32];  // [pixel][4-channel word], word column XORed with (pixel >> 2) & 31
+  __shared__ uint32_t tile[TILES][128][32];  // [pixel][4-channel word], word column XORed with (pixel >> 2) & 31
   // The convolution kernel that follows may become resident while this grid drains (it waits for this grid's
   // completion before it reads the image).  (Launching this grid itself as a programmatic dependent of the previous
   // convolution was measured and dropped: 54.6-55.1 us per step against 53.2 us.)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int HW = H * W, Wp = W + 2 * bw, Hp = H + 2 * bh;
-  const int p0 = blockIdx.x * 128, c0 = blockIdx.y * 128, n = blockIdx.z;
+  const int p0 = blockIdx.x * (128 * TILES), c0 = blockIdx.y * 128, n = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   {
     const int cg = threadIdx.x >> 3;  // channel group of 4 (word column), 0..31
     const int pc = threadIdx.x & 7;   // 16-pixel chunk of the tile
-    const int c = c0 + 4 * cg, pix = p0 + 16 * pc;
-    uint4 ch[4];
+    const int c = c0 + 4 * cg;
+    uint4 ch[TILES][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) ch[i] = make_uint4(0, 0, 0, 0);
-    if (pix < HW && c < C) {  // H*W % 16 == 0 and C % 4 == 0: a chunk / group is entirely inside or outside
-      const T* src = x + ((long long)n * C + c) * HW + pix;
+    for (int u = 0; u < TILES; ++u) {
+      const int pix = p0 + 128 * u + 16 * pc;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) ch[i] = Pix16<T>::load(src + (long long)i * HW);
+      for (int i = 0; i < 4; ++i) ch[u][i] = make_uint4(0, 0, 0, 0);
+      if (pix < HW && c < C) {  // H*W % 16 == 0 and C % 4 == 0: a chunk / group is entirely inside or outside
+        const T* src = x + ((long long)n * C + c) * HW + pix;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ch[u][i] = Pix16<T>::load(src + (long long)i * HW);
+      }
     }
 #pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) {  // pixels 4*q4 .. 4*q4+3 of the chunk
-      const uint32_t a = (&ch[0].x)[q4], b = (&ch[1].x)[q4], cc = (&ch[2].x)[q4], d = (&ch[3].x)[q4];
-      const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(cc, d, 0x5140);
-      const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(cc, d, 0x7362);
-      const int row = 16 * pc + 4 * q4;
-      const int col = cg ^ ((row >> 2) & 31);
-      tile[row + 0][col] = __byte_perm(t0, t1, 0x5410);
-      tile[row + 1][col] = __byte_perm(t0, t1, 0x7632);
-      tile[row + 2][col] = __byte_perm(t2, t3, 0x5410);
-      tile[row + 3][col] = __byte_perm(t2, t3, 0x7632);
+    for (int u = 0; u < TILES; ++u) {
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {  // pixels 4*q4 .. 4*q4+3 of the chunk
+        const uint32_t a = (&ch[u][0].x)[q4], b = (&ch[u][1].x)[q4], cc = (&ch[u][2].x)[q4], d = (&ch[u][3].x)[q4];
+        const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(cc, d, 0x5140);
+        const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(cc, d, 0x7362);
+        const int row = 16 * pc + 4 * q4;
+        const int col = cg ^ ((row >> 2) & 31);
+        tile[u][row + 0][col] = __byte_perm(t0, t1, 0x5410);
+        tile[u][row + 1][col] = __byte_perm(t0, t1, 0x7632);
+        tile[u][row + 2][col] = __byte_perm(t2, t3, 0x5410);
+        tile[u][row + 3][col] = __byte_perm(t2, t3, 0x7632);
+      }
     }
   }
   __syncthreads();
@@ -154,16 +165,19 @@ nchw_to_bordered_nhwc_wide_kernel(const T* __restrict__ x, uint8_t* __restrict__
   const int k = lane & 7;  // 16-channel chunk of the pixel
   const int c = c0 + 16 * k;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    // the four pixel rows a warp reads at once lie in four different swizzle groups: no bank conflicts
-    const int r = warp * 16 + (lane >> 3) * 4 + i;
-    const int p = p0 + r;
-    if (p < HW && c < C) {
-      const int sw = (r >> 2) & 31;
-      const uint4 v = make_uint4(tile[r][(4 * k + 0) ^ sw], tile[r][(4 * k + 1) ^ sw], tile[r][(4 * k + 2) ^ sw],
-                                 tile[r][(4 * k + 3) ^ sw]);
-      const int h = p / W, w = p - h * W;
-      *reinterpret_cast<uint4*>(yn + ((long long)(h + bh) * Wp + (w + bw)) * C + c) = v;
+  for (int u = 0; u < TILES; ++u) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // the four pixel rows a warp reads at once lie in four different swizzle groups: no bank conflicts
+      const int r = warp * 16 + (lane >> 3) * 4 + i;
+      const int p = p0 + 128 * u + r;
+      if (p < HW && c < C) {
+        const int sw = (r >> 2) & 31;
+        const uint4 v = make_uint4(tile[u][r][(4 * k + 0) ^ sw], tile[u][r][(4 * k + 1) ^ sw], tile[u][r][(4 * k + 2) ^ sw],
+                                   tile[u][r][(4 * k + 3) ^ sw]);
+        const int h = p / W, w = p - h * W;
+        *reinterpret_cast<uint4*>(yn + ((long long)(h + bh) * Wp + (w + bw)) * C + c) = v;
+      }
     }
   }
 }
@@ -284,11 +298,22 @@ int nchw_to_bordered_nhwc(const void* x, int x_is_f32, void* y, int N, int C, in
   const bool aligned = (reinterpret_cast<uintptr_t>(x) % (x_is_f32 ? 16 : 4) == 0) && (reinterpret_cast<uintptr_t>(y) % 4 == 0);
   if (HW % 16 == 0 && C % 16 == 0 && N <= 65535 && ceil_div(C, 128) <= 65535 &&
       reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
-    dim3 grid(ceil_div(HW, 128), ceil_div(C, 128), N);
-    if (x_is_f32)
-      nchw_to_bordered_nhwc_wide_kernel<float><<<grid, 256, 0, s>>>((const float*)x, (uint8_t*)y, C, H, W, bh, bw);
-    else
-      nchw_to_bordered_nhwc_wide_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, C, H, W, bh, bw);
+    const long long blocks1 = (long long)ceil_div(HW, 128) * ceil_div(C, 128) * N;
+    static const int force_tiles = [] {
+      const char* v = getenv("B200Q_LAYOUT_TILES");   // 1 or 2: A/B timing
+      return v ? atoi(v) : 0;
+    }();
+    const bool two = force_tiles == 2 && blocks1 >= 1024 && !x_is_f32;
+    if (two) {
+      dim3 grid(ceil_div(HW, 256), ceil_div(C, 128), N);
+      nchw_to_bordered_nhwc_wide_kernel<uint8_t, 2><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, C, H, W, bh, bw);
+    } else {
+      dim3 grid(ceil_div(HW, 128), ceil_div(C, 128), N);
+      if (x_is_f32)
+        nchw_to_bordered_nhwc_wide_kernel<float, 1><<<grid, 256, 0, s>>>((const float*)x, (uint8_t*)y, C, H, W, bh, bw);
+      else
+        nchw_to_bordered_nhwc_wide_kernel<uint8_t, 1><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, C, H, W, bh, bw);
+    }
     CUDA_TRY(cudaGetLastError());
     return B200Q_OK;
   }

@@ -244,8 +244,7 @@ class module:  # noqa: N801  (name of the reference class)
             lt, ot = bool(a.get("left_transpose", False)), bool(a.get("output_transpose", False))
             if (lt or ot) and (int(np.prod(iinfo[0]["shape"][:-2])) != 1 or len(iinfo[0]["shape"]) < 2):
                 raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: the executor takes left/output transposes of 2-D operands only")
-            if int(a.get("input_zp", 0)) != 0 or int(a.get("right_zp", 0)) != 0 or int(iinfo[0].get("zp", 0)) != 0:
-                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.MatMul with operand zero points is not implemented by the executor")
+            izp, rzp = int(a.get("input_zp", 0)), int(a.get("right_zp", 0))   # the op's attributes (MatMul.cpp:30-33), subtracted first
             w = self.weights[op["name"] + "_filter"]
             w_nk = w.contiguous() if a.get("right_transpose", False) else w.t().contiguous()   # right operand K-major
             b = self.weights.get(op["name"] + "_bias")
@@ -283,13 +282,13 @@ class module:  # noqa: N801  (name of the reference class)
                 def run_transposed():
                     x_mk = ins[0].reshape(K, M).t().contiguous() if lt else ins[0]
                     y_mn = self.torch.empty((M, N), dtype=out.dtype, device=self.device) if ot else out
-                    L.check(lib.b200q_gemm_i8_dev(_P(x_mk), _DT[iinfo[0]["dtype"]], _P(w_nk), L.DT_I8, M, N, K, C.byref(e),
-                                                  _P(y_mn), _P(status), L.ALGO_AUTO, stream()))
+                    L.check(lib.b200q_gemm_i8_zp_dev(_P(x_mk), _DT[iinfo[0]["dtype"]], _P(w_nk), L.DT_I8, M, N, K, izp, rzp, C.byref(e),
+                                                     _P(y_mn), _P(status), L.ALGO_AUTO, stream()))
                     if ot:
                         out.copy_(y_mn.t().reshape(out.shape))
                 return run_transposed
-            return lambda: L.check(lib.b200q_gemm_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(w_nk), L.DT_I8, M, N, K,
-                                                         C.byref(e), _P(out), _P(status), L.ALGO_AUTO, stream()))
+            return lambda: L.check(lib.b200q_gemm_i8_zp_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(w_nk), L.DT_I8, M, N, K, izp, rzp,
+                                                            C.byref(e), _P(out), _P(status), L.ALGO_AUTO, stream()))
         if t == "tpu.Add":
             if op["name"] in self._fused_adds:      # computed by the producing convolution's kernel
                 return lambda: None
