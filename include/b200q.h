@@ -399,7 +399,8 @@ int b200q_calib_minmax(void *ctx, const float *x, int64_t n_per_sample, int64_t 
  * current); make that first call before starting any stream capture.  All calls on a device share the one
  * array and it keeps the last call's contents (the counters are cleared on the stream before each launch), so
  * two calls whose kernels can overlap on the GPU (different streams) race: keep them on one stream or
- * otherwise ordered.  Asynchronous on `stream`. */
+ * otherwise ordered.  Asynchronous on `stream`, which must belong to the device that is current at the call (the
+ * array's address is looked up per current device). */
 int b200q_calib_minmax_noalloc(const float *x, int64_t n_per_sample, int64_t samples, float *out_minmax,
                                void *stream);
 

@@ -117,6 +117,7 @@ struct Pix16<float> {
 // TILES pixel tiles of 128 per block.  Two tiles (all loads issued before the first transposition, 832 blocks for a
 // 32 x 256 x 56 x 56 image, all resident at once) were measured against one tile (1600 blocks): 19.0 us against 15.1 us
 // inside the convolution step, so one tile is what runs; B200Q_LAYOUT_TILES=2 selects the other for A/B timing.
+// (Half-size blocks, 64 pixels and 128 threads, measured the same as one tile: 15.0-15.1 us.)
 template <typename T, int TILES>
 __global__ void __launch_bounds__(256)
 nchw_to_bordered_nhwc_wide_kernel(const T* __restrict__ x, uint8_t* __restrict__ y, int C, int H, int W, int bh, int bw) {
