@@ -501,10 +501,10 @@ def calibration_line(R, total=None):
     images = torch.from_numpy(synth.calibration_images(seed=4, count=per, start=R.rank * per)).to(R.dev)
     fwd = resnet50.Fp32Forward(ops, R.dev)
     cal = ShardedCalibrator(fwd, dist=R.dist)
-    CB = int(os.environ.get("B200Q_CALIB_BATCH", "64"))      # samples per forward call (cuDNN picks its algorithms by batch size, so the table depends on it; the same at every N)
+    CB = int(os.environ.get("B200Q_CALIB_BATCH", "64"))      # samples per forward call (the same at every N)
     batches = [images[i:i + CB] for i in range(0, per, CB)]
     if per >= 2 * CB:
-        cal.run(batches[:2], samples_per_rank=2 * CB)      # warm-up: cuDNN algorithm choice, NCCL channels, allocator
+        cal.run(batches[:2], samples_per_rank=2 * CB)      # warm-up: NCCL channels, allocator
     R.barrier()
     t0 = time.perf_counter()
     res = cal.run(batches, samples_per_rank=per)
@@ -517,7 +517,7 @@ def calibration_line(R, total=None):
     digest = hashlib.sha256("".join(f"{n} {r.threshold:.7f} {r.min:.7f} {r.max:.7f}\n" for n, r in res.items()).encode()).hexdigest()
     return dict(metric="calibration samples/s", value=TOTAL / dt, unit="samples/s", ms_per_step=dt * 1e3, steps=1,
                 scaling="strong", n_gpus=R.world, table_sha256=digest,
-                config=dict(workload=f"ResNet-50 fp32 forward (torch) + min/max, streaming histogram (2048 bins) and KLD on "
+                config=dict(workload=f"ResNet-50 fp32 forward (own full-fp32 Top-dialect kernels) + min/max, streaming histogram (2048 bins) and KLD on "
                                      f"{len(res)} tensors, {TOTAL} synthetic samples sharded over the ranks",
                             tensors=len(res), samples_per_rank=per, forward_batch=CB,
                             allreduce_bytes=cal.allreduce_bytes, allgather_bytes=int(len(res) * per * 8 * R.world) if R.dist else 0,

@@ -360,7 +360,9 @@ int b200q_probe_tensor_peak(int32_t kind, int32_t pair, int32_t kblocks, int32_t
  * decode kernels; a handle that sees 64 tokens or more dequantises once into a bf16 copy and runs a bf16 GEMM;
  * everything else takes the fused-dequantisation tensor-core kernel on the packed weights); 1 = the decode kernels
  * only (8 tokens per launch); 2 = the fused tensor-core kernel for every M; 3 = handle API with M > 8: the bf16 copy
- * (rounds the weight to bf16, which the reference does not).  A measuring control; no counterpart in the reference. */
+ * (rounds the weight to bf16, which the reference does not); 4 = the warpgroup kernel (up to 32 tokens: every lane
+ * dequantises its own output channel into tensor memory as an exact hi + lo pair; measured no faster than the default
+ * routes, kept for comparison).  A measuring control; no counterpart in the reference. */
 void b200q_a16_set_route(int32_t route);
 
 /* Device face with a handle: the tensors stay the caller's (not copied) and are declared constant for the life of
@@ -426,6 +428,36 @@ void b200q_calib_set_histogram_layout(int32_t mode);
 int b200q_calib_find_thresholds(void *ctx, int32_t tensors, const int32_t *const *hist, const int64_t *n_bins,
                                 const float *widths, int64_t dst_bins, float *thresholds_host, float *kl_host,
                                 void *stream);
+
+/* ------------------------------------------------------------------ fp32 Top-dialect forward (calibration's float graph)
+ * conv_attr_t of top::ConvOp (lib/Dialect/Top/Interfaces/Conv.cpp:19-199); NCHW fp32, OIHW filter. */
+typedef struct {
+  int64_t n, ic, ih, iw, oc, kh, kw, sh, sw, dh, dw, pht, phb, pwl, pwr, groups;
+  int32_t with_bias, do_relu;
+  float relu_limit;          /* <= 0: none (function_relu, lib/Support/MathUtils.cpp:891-903) */
+} b200q_top_conv_desc;
+
+/* top::ConvOp::inference (Conv.cpp:222-231) over HOST float buffers: inputs = {input, filter OIHW, bias or NULL},
+ * outputs[0] [n, oc, oh, ow].  Full fp32 products and sums on the CUDA cores (no tf32). */
+int b200q_top_conv2d_inference(const b200q_top_conv_desc *desc, float *const *inputs, int n_inputs,
+                               float *const *outputs, int n_outputs);
+/* Device face: the handle keeps a transposed copy of the filter; `bias` stays the caller's.  run() takes any batch. */
+int b200q_top_conv2d_dev_create(const b200q_top_conv_desc *desc, const float *filter_oihw, const float *bias, void **handle);
+int b200q_top_conv2d_dev_run(void *handle, const float *x, float *y, int64_t batch, void *stream);
+void b200q_top_conv2d_dev_output_shape(void *handle, int64_t *oh, int64_t *ow);
+void b200q_top_conv2d_dev_destroy(void **handle);
+/* top::MatMulOp without transposes: y[M,N] = relu(x[M,K] * w[K,N] + bias[N]) (lib/Dialect/Top/Interfaces/MatMul.cpp). */
+int b200q_top_matmul_f32_dev(const float *x, const float *w_kn, const float *bias, float *y, int64_t M, int64_t K, int64_t N,
+                             int32_t do_relu, float relu_limit, void *stream);
+/* top::MaxPoolOp / top::AvgPoolOp, 2-D, over nc = n * c planes (lib/Support/Dnnl/Pool.cpp: -inf padding for max;
+ * avg divides by the window clipped to the padded image when count_include_pad, else by the cells inside the image). */
+int b200q_top_pool2d_f32_dev(const float *x, float *y, int64_t nc, int32_t ih, int32_t iw, int32_t kh, int32_t kw,
+                             int32_t sh, int32_t sw, int32_t pht, int32_t phb, int32_t pwl, int32_t pwr, int32_t is_max,
+                             int32_t count_include_pad, int32_t do_relu, float relu_limit, void *stream);
+/* top::AddOp with two equal-shape inputs (Add.cpp:45-85) and top::ReluOp (Relu.cpp:17-24). */
+int b200q_top_add_f32_dev(const float *a, const float *b, float *y, int64_t count, int32_t do_relu, float relu_limit,
+                          void *stream);
+int b200q_top_relu_f32_dev(const float *x, float *y, int64_t count, float relu_limit, void *stream);
 
 /* The two symbols of the reference's calibration_math.so (bindings/kld/calibration_math.cpp:326-337), with
  * HOST buffers, so python/calibration/kld_calibrator.py:50-59 can load this library in its place.

@@ -97,6 +97,10 @@ def lib():
         L.orc_a16matmul_w4.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]
         L.orc_a16matmul_w4_f16.restype = None
         L.orc_a16matmul_w4_f16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp]
+        L.orc_top_conv2d_f32.restype = None
+        L.orc_top_conv2d_f32.argtypes = [vp, vp, vp] + [i64] * 16 + [i32, f32, vp]
+        L.orc_top_pool2d_f32.restype = None
+        L.orc_top_pool2d_f32.argtypes = [vp] + [i64] * 11 + [i32, i32, i32, f32, vp]
         L.orc_f32_to_f16_bits.restype = C.c_uint16
         L.orc_f32_to_f16_bits.argtypes = [f32]
         L.orc_f16_bits_to_f32.restype = C.c_float
@@ -589,3 +593,33 @@ def ref_oploops():
         L.ref_cast_dequant.restype, L.ref_cast_dequant.argtypes = f32, [f32, f64, i64, i32]
         _ref_oploops = L
     return _ref_oploops
+
+
+# ------------------------------------------------------------------ fp32 Top-dialect forward
+def top_conv2d_f32(x, w, bias=None, *, stride=(1, 1), pads=(0, 0, 0, 0), dilation=(1, 1), groups=1, do_relu=False,
+                   relu_limit=-1.0):
+    """top::ConvOp::inference (lib/Dialect/Top/Interfaces/Conv.cpp:222-231): NCHW x, OIHW w, pads = (top, bottom, left,
+    right); double accumulation in index order (oneDNN's order is not defined: compare by tolerance)."""
+    x, w, bias = _c(x, np.float32), _c(w, np.float32), _c(bias, np.float32)
+    n, ic, ih, iw = x.shape
+    oc, icg, kh, kw = w.shape
+    assert icg * groups == ic
+    oh = (ih + pads[0] + pads[1] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+    ow = (iw + pads[2] + pads[3] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+    out = np.empty((n, oc, oh, ow), np.float32)
+    lib().orc_top_conv2d_f32(_p(x), _p(w), _p(bias), n, ic, ih, iw, oc, kh, kw, stride[0], stride[1], dilation[0],
+                             dilation[1], pads[0], pads[1], pads[2], pads[3], groups, int(do_relu), float(relu_limit), _p(out))
+    return out
+
+
+def top_pool2d_f32(x, *, kernel, stride, pads=(0, 0, 0, 0), is_max=True, count_include_pad=False, do_relu=False,
+                   relu_limit=-1.0):
+    """top::MaxPoolOp / top::AvgPoolOp over NCHW (lib/Support/Dnnl/Pool.cpp)."""
+    x = _c(x, np.float32)
+    n, c, ih, iw = x.shape
+    oh = (ih + pads[0] + pads[1] - kernel[0]) // stride[0] + 1
+    ow = (iw + pads[2] + pads[3] - kernel[1]) // stride[1] + 1
+    out = np.empty((n, c, oh, ow), np.float32)
+    lib().orc_top_pool2d_f32(_p(x), n * c, ih, iw, kernel[0], kernel[1], stride[0], stride[1], pads[0], pads[1], pads[2],
+                             pads[3], int(is_max), int(count_include_pad), int(do_relu), float(relu_limit), _p(out))
+    return out

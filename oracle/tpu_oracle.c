@@ -703,3 +703,84 @@ int orc_num_threads(void) {
   return 1;
 #endif
 }
+
+/* ------------------------------------------------------------------ fp32 Top-dialect forward
+ * top::ConvOp::inference (lib/Dialect/Top/Interfaces/Conv.cpp:222-231: oneDNN fp32 convolution, NCHW / OIHW, zero
+ * padding, bias, then ReLU with relu_limit, lib/Support/Dnnl/Conv.cpp:98-215).  oneDNN does not define its summation
+ * order, so this restatement sums k = (c, kh, kw) in index order with a double accumulator and the comparison with
+ * either implementation is by tolerance. */
+void orc_top_conv2d_f32(const float *x, const float *w, const float *bias, int64_t n, int64_t ic, int64_t ih, int64_t iw,
+                        int64_t oc, int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t dh, int64_t dw, int64_t pht,
+                        int64_t phb, int64_t pwl, int64_t pwr, int64_t groups, int do_relu, float relu_limit, float *out) {
+  const int64_t oh = (ih + pht + phb - dh * (kh - 1) - 1) / sh + 1;
+  const int64_t ow = (iw + pwl + pwr - dw * (kw - 1) - 1) / sw + 1;
+  const int64_t icg = ic / groups, ocg = oc / groups;
+#pragma omp parallel for collapse(2) schedule(dynamic)
+  for (int64_t in = 0; in < n; ++in) {
+    for (int64_t o = 0; o < oc; ++o) {
+      const int64_t g = o / ocg;
+      for (int64_t y = 0; y < oh; ++y) {
+        for (int64_t xo = 0; xo < ow; ++xo) {
+          double acc = 0.0;
+          for (int64_t c = 0; c < icg; ++c) {
+            for (int64_t a = 0; a < kh; ++a) {
+              const int64_t h = y * sh - pht + a * dh;
+              if (h < 0 || h >= ih) continue;
+              for (int64_t b = 0; b < kw; ++b) {
+                const int64_t ww = xo * sw - pwl + b * dw;
+                if (ww < 0 || ww >= iw) continue;
+                acc += (double)x[((in * ic + g * icg + c) * ih + h) * iw + ww] * (double)w[((o * icg + c) * kh + a) * kw + b];
+              }
+            }
+          }
+          float v = (float)acc + (bias ? bias[o] : 0.f);
+          if (do_relu) { /* function_relu, lib/Support/MathUtils.cpp:891-903 */
+            v = v > 0.f ? v : 0.f;
+            if (relu_limit > 0.f && v > relu_limit) v = relu_limit;
+          }
+          out[((in * oc + o) * oh + y) * ow + xo] = v;
+        }
+      }
+    }
+  }
+}
+
+/* top::MaxPoolOp / top::AvgPoolOp through lib/Support/Dnnl/Pool.cpp: max ignores the padding; avg divides by the
+ * window clipped to the padded image when count_include_pad, else by the number of cells inside the image. */
+void orc_top_pool2d_f32(const float *x, int64_t nc, int64_t ih, int64_t iw, int64_t kh, int64_t kw, int64_t sh, int64_t sw,
+                        int64_t pht, int64_t phb, int64_t pwl, int64_t pwr, int is_max, int count_include_pad, int do_relu,
+                        float relu_limit, float *out) {
+  const int64_t oh = (ih + pht + phb - kh) / sh + 1, ow = (iw + pwl + pwr - kw) / sw + 1;
+#pragma omp parallel for schedule(static)
+  for (int64_t p = 0; p < nc; ++p) {
+    for (int64_t y = 0; y < oh; ++y) {
+      for (int64_t xo = 0; xo < ow; ++xo) {
+        const int64_t h0 = y * sh - pht, w0 = xo * sw - pwl;
+        float acc = is_max ? -INFINITY : 0.f;
+        int64_t inside = 0;
+        for (int64_t a = 0; a < kh; ++a) {
+          for (int64_t b = 0; b < kw; ++b) {
+            const int64_t h = h0 + a, ww = w0 + b;
+            if (h < 0 || h >= ih || ww < 0 || ww >= iw) continue;
+            const float v = x[(p * ih + h) * iw + ww];
+            acc = is_max ? (v > acc ? v : acc) : acc + v;
+            ++inside;
+          }
+        }
+        if (!is_max) {
+          int64_t div = inside;
+          if (count_include_pad) {
+            const int64_t he = h0 + kh < ih + phb ? h0 + kh : ih + phb, we = w0 + kw < iw + pwr ? w0 + kw : iw + pwr;
+            div = (he - h0) * (we - w0);
+          }
+          acc = div > 0 ? acc / (float)div : 0.f;
+        }
+        if (do_relu) {
+          acc = acc > 0.f ? acc : 0.f;
+          if (relu_limit > 0.f && acc > relu_limit) acc = relu_limit;
+        }
+        out[(p * oh + y) * ow + xo] = acc;
+      }
+    }
+  }
+}

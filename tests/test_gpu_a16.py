@@ -254,3 +254,40 @@ def test_w4f16_operator_face_and_exact_rounding():
     op.inference(p)
     assert np.array_equal(out.astype(np.float16).view(np.uint16), ref)
     assert np.array_equal(out.astype(np.float16).astype(np.float32), out), "output is f16-representable"
+
+
+# ------------------------------------------------------------------ warpgroup kernel (route 4)
+@pytest.mark.parametrize("case", [dict(M=4, K=64, N=128, g=64), dict(M=16, K=256, N=128, g=64), dict(M=2, K=1024, N=300, g=128),
+                                  dict(M=9, K=256, N=128, g=32), dict(M=17, K=4096, N=256, g=64), dict(M=32, K=2048, N=512, g=256),
+                                  dict(M=1, K=4096, N=11008, g=64), dict(M=16, K=4096, N=11008, g=64),
+                                  dict(M=32, K=4096, N=11008, g=64), dict(M=3, K=11008, N=4096, g=64),
+                                  dict(M=30, K=11008, N=130, g=128), dict(M=4, K=192, N=100, g=64),
+                                  dict(M=12, K=1024, N=700, g=512)])
+@pytest.mark.parametrize("f16", [False, True])
+def test_warpgroup_kernel(route, case, f16):
+    """b200q_a16_set_route(4): up to 32 tokens, weights by TMA, each lane converts its own output channel, the exact
+    hi + lo split of (q - zp) * scale in two MMAs, K slices summed in a workspace that every launch leaves zeroed - so
+    the second call must give the first one's bits as far as the (unordered) float additions allow: the bound again."""
+    route(4)
+    M, K, N, g = case["M"], case["K"], case["N"], case["g"]
+    c = synth.a16_w4(seed=17, M=M, K=K, N=N, group=g, f16=f16)
+    bias = np.random.default_rng(4).standard_normal(N).astype(np.float32)
+    ref = oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], bias, group=g, f16=f16)
+    x, wq, sc, zp, b = dev(c["x"]), dev(c["wq"]), dev(c["scale"]), dev(c["zp"]), dev(bias)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        y = torch.zeros((M, N), dtype=torch.uint16, device="cuda")
+        L.check(L.lib().b200q_a16_w4_dev_dt(ptr(x), ptr(wq), ptr(sc), ptr(zp), ptr(b), ptr(y), M, N, K, g,
+                                            L.DT_F16 if f16 else L.DT_BF16, ptr(st), None))
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        (check_f16 if f16 else check)(y.cpu().numpy(), ref)
+
+
+def test_warpgroup_kernel_refuses_more_than_32_tokens(route):
+    route(4)
+    c = synth.a16_w4(seed=1, M=33, K=256, N=128, group=64)
+    x, wq, sc, zp = dev(c["x"]), dev(c["wq"]), dev(c["scale"]), dev(c["zp"])
+    y = torch.zeros((33, 128), dtype=torch.uint16, device="cuda")
+    rc = L.lib().b200q_a16_w4_dev(ptr(x), ptr(wq), ptr(sc), ptr(zp), None, ptr(y), 33, 128, 256, 64, None, None)
+    assert rc == L.ERR_UNSUPPORTED

@@ -222,3 +222,24 @@ def test_f16_conversion_matches_compiled_reference():
     for h in range(1 << 16):
         got, want = np.float32(g(h)), np.float32(R.ref_f16_to_f32(h))
         assert got.tobytes() == want.tobytes() or (np.isnan(got) and np.isnan(want)), hex(h)
+
+
+def test_top_fp32_oracle_against_onednn():
+    """The fp32 Top-dialect restatements (convolution, pooling) against torch's CPU operators, which call oneDNN - the
+    library top::ConvOp / top::MaxPoolOp / top::AvgPoolOp call (lib/Support/Dnnl/Conv.cpp, Pool.cpp)."""
+    torch = pytest.importorskip("torch")
+    F = torch.nn.functional
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((2, 8, 9, 11)).astype(np.float32)
+    w = rng.standard_normal((12, 4, 3, 3)).astype(np.float32)
+    b = rng.standard_normal(12).astype(np.float32)
+    got = oracle.top_conv2d_f32(x, w, b, stride=(2, 1), pads=(1, 1, 2, 2), dilation=(1, 2), groups=2, do_relu=True, relu_limit=3.0)
+    ref = F.conv2d(F.pad(torch.from_numpy(x), (2, 2, 1, 1)), torch.from_numpy(w), torch.from_numpy(b), stride=(2, 1),
+                   dilation=(1, 2), groups=2).clamp(0, 3).numpy()
+    assert got.shape == ref.shape and np.allclose(got, ref, rtol=1e-5, atol=1e-5)
+    t = torch.from_numpy(x)
+    assert np.array_equal(oracle.top_pool2d_f32(x, kernel=(3, 3), stride=(2, 2), pads=(1, 1, 1, 1), is_max=True),
+                          F.max_pool2d(t, 3, 2, 1).numpy())
+    for cip in (True, False):
+        assert np.allclose(oracle.top_pool2d_f32(x, kernel=(3, 3), stride=(2, 2), pads=(1, 1, 1, 1), is_max=False, count_include_pad=cip),
+                           F.avg_pool2d(t, 3, 2, 1, count_include_pad=cip).numpy(), rtol=1e-6, atol=1e-6)

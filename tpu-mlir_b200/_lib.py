@@ -61,6 +61,12 @@ class Conv2DDesc(C.Structure):
                 ("weight_version", C.c_int32), ("algo", C.c_int32)]
 
 
+class TopConvDesc(C.Structure):
+    _fields_ = [(k, C.c_int64) for k in ("n", "ic", "ih", "iw", "oc", "kh", "kw", "sh", "sw", "dh", "dw", "pht",
+                                         "phb", "pwl", "pwr", "groups")] + \
+               [("with_bias", C.c_int32), ("do_relu", C.c_int32), ("relu_limit", C.c_float)]
+
+
 class RequantDesc(C.Structure):
     _fields_ = [("outer", C.c_int64), ("channels", C.c_int64), ("inner", C.c_int64), ("per_axis", C.c_int32),
                 ("quant_mode", C.c_int32), ("round_mode", C.c_int32), ("fuse_rq_axis", C.c_int32), ("in_zp", C.c_int32),
@@ -120,6 +126,16 @@ SIGNATURES = {
     "b200q_a16_w4_dev": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
                                    C.c_void_p]),
     "b200q_a16_set_route": (None, [C.c_int32]),
+    "b200q_top_conv2d_inference": (C.c_int, [C.POINTER(TopConvDesc), _FLOATPP, C.c_int, _FLOATPP, C.c_int]),
+    "b200q_top_conv2d_dev_create": (C.c_int, [C.POINTER(TopConvDesc), C.c_void_p, C.c_void_p, _VPP]),
+    "b200q_top_conv2d_dev_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "b200q_top_conv2d_dev_output_shape": (None, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "b200q_top_conv2d_dev_destroy": (None, [_VPP]),
+    "b200q_top_matmul_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                           C.c_int32, C.c_float, C.c_void_p]),
+    "b200q_top_pool2d_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64] + [C.c_int32] * 13 + [C.c_float, C.c_void_p]),
+    "b200q_top_add_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),
+    "b200q_top_relu_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p]),
     "b200q_a16_w4_dev_dt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                       C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "b200q_a16_dev_create_dt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32,

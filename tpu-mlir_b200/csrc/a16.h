@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "devbuf.h"
+
 namespace b200q {
 
 int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why, bool f16 = false);
@@ -19,5 +21,17 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
 int a16_w4_umma_supported(long long M, int N, int K, int group, const char** why);
 int a16_w4_umma_launch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
                        long long M, int N, int K, int group, int* status, cudaStream_t stream, bool f16 = false);
+
+// Warpgroup form for a handful of tokens (a16_w4_wg.cu): M <= 32; K a multiple of 64; group 32 or a multiple of 64.
+int a16_w4_wg_supported(long long M, int N, int K, int group, const char** why);
+struct A16WgScratch {   // fp32 partial sums [M][N] and per-tile arrival counters, zero between launches
+  DevBuf ws, counters;
+  size_t ws_elems = 0;
+  int tiles = 0;
+};
+// scratch: the caller's (a handle's), or null for one kept per (device, stream) by the launcher
+int a16_w4_wg_launch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
+                     long long M, int N, int K, int group, int* status, cudaStream_t stream, bool f16 = false,
+                     A16WgScratch* scratch = nullptr);
 
 }  // namespace b200q

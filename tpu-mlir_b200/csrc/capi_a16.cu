@@ -132,13 +132,15 @@ int validate(const b200q_a16matmul_desc& d) {
 }
 
 // Route of b200q_a16_*: 0 = chosen per call; 1 = CUDA-core / mma.sync decode kernels (8 tokens at a time);
-// 2 = fused-dequantisation tensor-core kernel; 3 = one-time bf16 copy of the weight + bf16 GEMM (handle API, M > 8).
+// 2 = fused-dequantisation tensor-core kernel; 3 = one-time bf16 copy of the weight + bf16 GEMM (handle API, M > 8);
+// 4 = warpgroup kernel (M <= 32).
 int g_a16_route = 0;
 
 // Decode shapes go to the GEMV kernel; larger M is processed in slices of 8 tokens.
 int a16_dispatch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
                  long long M, int N, int K, int group, int* status, cudaStream_t s, DevBuf* w16 = nullptr,
-                 bool* w16_ready = nullptr, bool weights_constant = false, bool f16 = false) {
+                 bool* w16_ready = nullptr, bool weights_constant = false, bool f16 = false,
+                 A16WgScratch* wg_scratch = nullptr) {
   const char* why = nullptr;
   // both routes index scales and zero points as [n][k / group]: the group must tile K exactly, and a byte holds
   // two consecutive k of one row
@@ -157,6 +159,9 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
       if (!umma_ok) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: the tensor-core kernel needs K and the group size to be multiples of 64");
       use_umma = true;
       break;
+    case 4:
+      if (!a16_w4_wg_supported(M, N, K, group, &why)) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: %s", why);
+      return a16_w4_wg_launch(x, wq, scale, zp, bias, y, M, N, K, group, status, s, f16, wg_scratch);
     case 3: use_resident = resident_ok; use_umma = !resident_ok && !gemv_ok && umma_ok; break;
     default:
       // up to 8 tokens: the decode kernels.  Above: the fused kernel (exact group scaling, no copy of the weight);
@@ -190,6 +195,7 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
 
 struct A16Handle {
   DevBuf stage, x16, wq, scale, zp, bias, y16, y32, status, w16;
+  A16WgScratch wg_scratch;
   bool w16_ready = false;
   // device face: the caller's tensors (not owned)
   const void *d_wq = nullptr, *d_scale = nullptr, *d_zp = nullptr;
@@ -271,7 +277,7 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
     if (cudaMemcpyAsync(h->stage.p, inputs[0], x_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D input", __FILE__, __LINE__); break; }
     if ((rc = f32_to_16(h->stage.as<float>(), h->x16.p, (long long)x_elems, f16, s))) break;
     if ((rc = a16_dispatch(h->x16.p, h->wq.p, h->scale.p, h->zp.p, bias_f ? h->bias.as<float>() : nullptr, h->y16.p,
-                           d.M, (int)d.N, (int)d.K, d.q_group_size, h->status.as<int>(), s, &h->w16, &h->w16_ready, false, f16))) break;
+                           d.M, (int)d.N, (int)d.K, d.q_group_size, h->status.as<int>(), s, &h->w16, &h->w16_ready, false, f16, &h->wg_scratch))) break;
     if ((rc = f16_or_bf16_to_f32(h->y16.p, h->y32.as<float>(), (long long)y_elems, f16, s))) break;
     if (cudaMemcpyAsync(outputs[0], h->y32.p, y_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__); break; }
     int hstat = 0;
@@ -284,7 +290,7 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
   return rc;
 }
 
-void b200q_a16_set_route(int32_t route) { g_a16_route = (route >= 0 && route <= 3) ? route : 0; }
+void b200q_a16_set_route(int32_t route) { g_a16_route = (route >= 0 && route <= 4) ? route : 0; }
 
 int b200q_a16_w4_dev_dt(const void* x, const void* wq, const void* scale, const void* zp_u8, const float* bias_f32, void* y,
                         int64_t M, int64_t N, int64_t K, int32_t group, int32_t dtype, int32_t* status, void* stream) {
@@ -341,7 +347,7 @@ int b200q_a16_dev_run(void* handle, const void* x_bf16, void* y_bf16, int64_t M,
   if (!handle || !x_bf16 || !y_bf16 || M < 0) return set_error(B200Q_ERR_INVALID, "a16_dev_run: bad argument");
   A16Handle* h = static_cast<A16Handle*>(handle);
   return a16_dispatch(x_bf16, h->d_wq, h->d_scale, h->d_zp, h->d_bias, y_bf16, M, h->N, h->K, h->group,
-                      h->status.as<int>(), static_cast<cudaStream_t>(stream), &h->w16, &h->w16_ready, true, h->f16);
+                      h->status.as<int>(), static_cast<cudaStream_t>(stream), &h->w16, &h->w16_ready, true, h->f16, &h->wg_scratch);
 }
 
 int b200q_a16_dev_status(void* handle, void* stream) {

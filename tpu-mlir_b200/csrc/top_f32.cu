@@ -1,0 +1,318 @@
+// fp32 forward of the Top-dialect ops a calibration pass runs: Conv (+ bias, ReLU), MatMul, Add, MaxPool, AvgPool, Relu.
+//
+// Semantics: top::ConvOp::inference (lib/Dialect/Top/Interfaces/Conv.cpp:222-231: fp32 convolution, bias, optional ReLU
+// with relu_limit), top::MatMulOp, top::AddOp::inference (Add.cpp:45-85), top::MaxPoolOp / top::AvgPoolOp (the pooling
+// of lib/Support/Dnnl/Pool.cpp: pad value -inf for max, count_include_pad for avg), top::ReluOp (Relu.cpp:17-24 over
+// function_relu, lib/Support/MathUtils.cpp:891-903).  Tensors are NCHW fp32 like the interpreter's buffers.
+//
+// The convolution is an implicit GEMM on the CUDA cores in full fp32 (calibration statistics should not depend on a
+// reduced-precision product): C[co][pixel] = sum_k Wt[k][co] * X[k][pixel], k = (c, kh, kw).  A block computes 128 (or
+// 64) output channels x 128 pixels, K in slices of 8 through double-buffered shared memory; a thread owns 8 x 8 (4 x 8)
+// results.  The weight is kept transposed [K][oc] so its tile loads are contiguous; the activation tile is gathered
+// with a per-k table (offset of (c, kh, kw) inside an image and the two shifts for the border test), the pixel's own
+// decomposition (image, row, column) is computed once per thread.  In NCHW consecutive pixels are consecutive
+// addresses for a fixed k, so both the gather and the store run along the fast axis.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "internal.h"
+#include "top_f32.h"
+
+namespace b200q {
+namespace {
+
+constexpr int TN = 128;   // pixels per block
+constexpr int TK = 8;     // k per slice
+constexpr int CONV_THREADS = 256;
+
+__device__ __forceinline__ float relu_f(float v, int do_relu, float limit) {
+  if (do_relu) {
+    v = v > 0.f ? v : 0.f;
+    if (limit > 0.f && v > limit) v = limit;
+  }
+  return v;
+}
+
+// KHW: 1 = 1x1 filter, 9 = 3x3 filter (the position of k inside the image comes from arithmetic on k, so the gather
+// does not wait for a table entry first); 0 = any filter, through the table.
+template <int TM, int KHW>
+__global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* __restrict__ x, const float* __restrict__ wt,
+                                                                   const int2* __restrict__ ktab, const float* __restrict__ bias,
+                                                                   float* __restrict__ y, const TopConvPlan p) {
+  constexpr int RM = TM / 16;   // output channels per thread: 8 or 4
+  __shared__ __align__(16) float As[2][TK][TM];
+  __shared__ __align__(16) float Bs[2][TK][TN];
+  const int tid = threadIdx.x;
+  const int g = blockIdx.z;
+  const int co0 = blockIdx.y * TM;                 // inside the group
+  const long long pix0 = (long long)blockIdx.x * TN;
+  const int ohow = p.oh * p.ow;
+  const long long P = (long long)p.n * ohow;
+  const float* wg = wt + (size_t)g * p.K * p.ocg;
+
+  // ---- this thread's pixel for the gather
+  const int bp = tid & (TN - 1);
+  const int bk = tid >> 7;                         // 0 / 1: k rows bk, bk + 2, bk + 4, bk + 6
+  const long long pix = pix0 + bp;
+  const bool pvalid = pix < P;
+  int hi0 = 0, wi0 = 0;
+  long long xbase = 0;
+  if (pvalid) {
+    const int b = (int)(pix / ohow), r = (int)(pix - (long long)b * ohow);
+    const int ho = r / p.ow, wo = r - ho * p.ow;
+    hi0 = ho * p.sh - p.pht;
+    wi0 = wo * p.sw - p.pwl;
+    xbase = ((long long)b * p.ic + (long long)g * p.icg) * p.ih * p.iw + (long long)hi0 * p.iw + wi0;
+  }
+  // ---- this thread's piece of the weight tile: one float4 of row ak
+  constexpr int A_VECS = TK * TM / 4;              // 256 or 128
+  const int ak = tid / (TM / 4), ac = (tid % (TM / 4)) * 4;
+  const bool a_active = tid < A_VECS;
+  const bool a_vec = (p.ocg & 3) == 0;
+
+  float4 a_reg = make_float4(0.f, 0.f, 0.f, 0.f);
+  float b_reg[4];
+  auto fetch = [&](int k0) {
+    if (a_active) {
+      const int k = k0 + ak;
+      a_reg = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (k < p.K) {
+        const float* src = wg + (size_t)k * p.ocg + co0 + ac;
+        if (a_vec && co0 + ac + 3 < p.ocg) a_reg = __ldg(reinterpret_cast<const float4*>(src));
+        else {
+          if (co0 + ac + 0 < p.ocg) a_reg.x = __ldg(src + 0);
+          if (co0 + ac + 1 < p.ocg) a_reg.y = __ldg(src + 1);
+          if (co0 + ac + 2 < p.ocg) a_reg.z = __ldg(src + 2);
+          if (co0 + ac + 3 < p.ocg) a_reg.w = __ldg(src + 3);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + bk + 2 * i;
+      float v = 0.f;
+      if (pvalid && k < p.K) {
+        int koff, khd, kwd;
+        if (KHW == 1) {
+          koff = k * p.ih * p.iw;
+          khd = kwd = 0;
+        } else if (KHW == 9) {
+          const int c = k / 9, r = k - c * 9, a = r / 3, b = r - a * 3;
+          khd = a * p.dh;
+          kwd = b * p.dw;
+          koff = c * p.ih * p.iw + khd * p.iw + kwd;
+        } else {
+          const int2 t = __ldg(ktab + k);
+          koff = t.x;
+          khd = t.y & 0xffff;
+          kwd = t.y >> 16;
+        }
+        if ((unsigned)(hi0 + khd) < (unsigned)p.ih && (unsigned)(wi0 + kwd) < (unsigned)p.iw) v = __ldg(x + xbase + koff);
+      }
+      b_reg[i] = v;
+    }
+  };
+  auto stash = [&](int buf) {
+    if (a_active) *reinterpret_cast<float4*>(&As[buf][ak][ac]) = a_reg;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) Bs[buf][bk + 2 * i][bp] = b_reg[i];
+  };
+
+  const int tx = tid & 15, ty = tid >> 4;
+  float acc[RM][8];
+#pragma unroll
+  for (int i = 0; i < RM; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  const int nslices = (p.K + TK - 1) / TK;
+  for (int s = 0; s < nslices; ++s) {
+    const int buf = s & 1;
+    if (s + 1 < nslices) fetch((s + 1) * TK);
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      float a[RM], b[8];
+      {
+        const float4 v = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
+        a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
+        if (RM == 8) {
+          const float4 u = *reinterpret_cast<const float4*>(&As[buf][kk][(TM / 2) + ty * 4]);
+          a[RM - 4] = u.x; a[RM - 3] = u.y; a[RM - 2] = u.z; a[RM - 1] = u.w;
+        }
+      }
+      {
+        const float4 v = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
+        const float4 u = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
+        b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w; b[4] = u.x; b[5] = u.y; b[6] = u.z; b[7] = u.w;
+      }
+#pragma unroll
+      for (int i = 0; i < RM; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (s + 1 < nslices) {
+      stash(buf ^ 1);
+      __syncthreads();
+    }
+  }
+
+  // ---- bias, ReLU, store: rows ty * 4 + {0..3} (and TM / 2 + the same), pixels tx * 4 + {0..3} and 64 + the same
+  const bool vec_store = (ohow & 3) == 0;
+#pragma unroll
+  for (int i = 0; i < RM; ++i) {
+    const int co = co0 + (i < 4 ? ty * 4 + i : (TM / 2) + ty * 4 + (i - 4));
+    if (co >= p.ocg) continue;
+    const int oc = g * p.ocg + co;
+    const float bv = bias ? __ldg(bias + oc) : 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long q0 = pix0 + h * 64 + tx * 4;
+      if (q0 >= P) continue;
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = relu_f(acc[i][h * 4 + j] + bv, p.do_relu, p.relu_limit);
+      if (vec_store && q0 + 3 < P) {
+        const long long b = q0 / ohow, r = q0 - b * ohow;
+        *reinterpret_cast<float4*>(y + (b * p.oc + oc) * ohow + r) = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const long long q = q0 + j;
+          if (q < P) {
+            const long long b = q / ohow, r = q - b * ohow;
+            y[(b * p.oc + oc) * ohow + r] = v[j];
+          }
+        }
+      }
+    }
+  }
+}
+
+// (c, kh, kw) of every k: offset inside an image and the two border shifts
+__global__ void conv_ktab_kernel(int2* ktab, int K, int kh, int kw, int ih, int iw, int dh, int dw) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= K) return;
+  const int c = k / (kh * kw), r = k - c * kh * kw, a = r / kw, b = r - a * kw;
+  ktab[k] = make_int2(c * ih * iw + a * dh * iw + b * dw, (a * dh) | ((b * dw) << 16));
+}
+
+// OIHW [groups * ocg][K] -> [groups][K][ocg]
+__global__ void conv_wt_kernel(const float* __restrict__ w, float* __restrict__ wt, int groups, int ocg, int K) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)groups * ocg * K;
+  if (i >= total) return;
+  const int co = (int)(i % ocg);
+  const long long r = i / ocg;
+  const int k = (int)(r % K), g = (int)(r / K);
+  wt[i] = w[((size_t)g * ocg + co) * K + k];
+}
+
+__global__ void pool2d_f32_kernel(const float* __restrict__ x, float* __restrict__ y, long long total, int ih, int iw, int oh,
+                                  int ow, int kh, int kw, int sh, int sw, int pht, int pwl, int is_max,
+                                  int count_include_pad, int phb, int pwr, int do_relu, float relu_limit) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int wo = (int)(i % ow);
+  const long long r = i / ow;
+  const int ho = (int)(r % oh);
+  const long long nc = r / oh;
+  const float* src = x + nc * ih * iw;
+  const int h0 = ho * sh - pht, w0 = wo * sw - pwl;
+  float acc = is_max ? -INFINITY : 0.f;
+  int inside = 0;
+  for (int a = 0; a < kh; ++a) {
+    const int h = h0 + a;
+    if ((unsigned)h >= (unsigned)ih) continue;
+    for (int b = 0; b < kw; ++b) {
+      const int w = w0 + b;
+      if ((unsigned)w >= (unsigned)iw) continue;
+      const float v = __ldg(src + (size_t)h * iw + w);
+      acc = is_max ? fmaxf(acc, v) : acc + v;
+      ++inside;
+    }
+  }
+  if (!is_max) {
+    int div = inside;
+    if (count_include_pad) {   // the window clipped to the padded image
+      const int he = min(h0 + kh, ih + phb), we = min(w0 + kw, iw + pwr);
+      div = (he - h0) * (we - w0);
+    }
+    acc = div > 0 ? acc / (float)div : 0.f;
+  }
+  y[i] = relu_f(acc, do_relu, relu_limit);
+}
+
+__global__ void add_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y, long long n,
+                               int do_relu, float relu_limit) {
+  const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 + 3 < n) {
+    const float4 u = *reinterpret_cast<const float4*>(a + i4);
+    const float4 v = b ? *reinterpret_cast<const float4*>(b + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(y + i4) = make_float4(relu_f(u.x + v.x, do_relu, relu_limit), relu_f(u.y + v.y, do_relu, relu_limit),
+                                                     relu_f(u.z + v.z, do_relu, relu_limit), relu_f(u.w + v.w, do_relu, relu_limit));
+  } else {
+    for (long long i = i4; i < n; ++i) y[i] = relu_f(a[i] + (b ? b[i] : 0.f), do_relu, relu_limit);
+  }
+}
+
+}  // namespace
+
+int top_conv_prepare(const TopConvPlan& p, const float* w_oihw, float* wt, int2* ktab, cudaStream_t s) {
+  const long long total = (long long)p.groups * p.ocg * p.K;
+  conv_wt_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(w_oihw, wt, p.groups, p.ocg, p.K);
+  conv_ktab_kernel<<<(p.K + 255) / 256, 256, 0, s>>>(ktab, p.K, p.kh, p.kw, p.ih, p.iw, p.dh, p.dw);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_conv_launch(const TopConvPlan& p, const float* x, const float* wt, const int2* ktab, const float* bias, float* y,
+                    cudaStream_t s) {
+  const long long P = (long long)p.n * p.oh * p.ow;
+  if (P == 0) return B200Q_OK;
+  const long long ptiles = (P + TN - 1) / TN;
+  if (ptiles > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "top conv: too many pixels");
+  if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(wt) & 15) || (reinterpret_cast<uintptr_t>(y) & 15))
+    return set_error(B200Q_ERR_INVALID, "top conv: operands must be 16-byte aligned");
+  const int khw = (p.kh == 1 && p.kw == 1) ? 1 : (p.kh == 3 && p.kw == 3) ? 9 : 0;
+  if (khw == 0 && !ktab) return set_error(B200Q_ERR_INVALID, "top conv: this filter size needs the gather table");
+  if (p.ocg > 64) {
+    dim3 grid((unsigned)ptiles, (unsigned)((p.ocg + 127) / 128), (unsigned)p.groups);
+    if (khw == 1) conv2d_f32_kernel<128, 1><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
+    else if (khw == 9) conv2d_f32_kernel<128, 9><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
+    else conv2d_f32_kernel<128, 0><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
+  } else {
+    dim3 grid((unsigned)ptiles, (unsigned)((p.ocg + 63) / 64), (unsigned)p.groups);
+    if (khw == 1) conv2d_f32_kernel<64, 1><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
+    else if (khw == 9) conv2d_f32_kernel<64, 9><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
+    else conv2d_f32_kernel<64, 0><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
+  }
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_pool2d_launch(const float* x, float* y, long long nc, int ih, int iw, int oh, int ow, int kh, int kw, int sh, int sw,
+                      int pht, int phb, int pwl, int pwr, bool is_max, bool count_include_pad, bool do_relu, float relu_limit,
+                      cudaStream_t s) {
+  const long long total = nc * oh * ow;
+  if (total == 0) return B200Q_OK;
+  pool2d_f32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, y, total, ih, iw, oh, ow, kh, kw, sh, sw, pht, pwl,
+                                                                    is_max ? 1 : 0, count_include_pad ? 1 : 0, phb, pwr,
+                                                                    do_relu ? 1 : 0, relu_limit);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_add_launch(const float* a, const float* b, float* y, long long n, bool do_relu, float relu_limit, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (reinterpret_cast<uintptr_t>(y) & 15))
+    return set_error(B200Q_ERR_INVALID, "top add: operands must be 16-byte aligned");
+  const long long vecs = (n + 3) / 4;
+  add_f32_kernel<<<(unsigned)((vecs + 255) / 256), 256, 0, s>>>(a, b, y, n, do_relu ? 1 : 0, relu_limit);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+}  // namespace b200q

@@ -1,0 +1,28 @@
+// fp32 Top-dialect forward kernels (top_f32.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200q {
+
+struct TopConvPlan {
+  int n, ic, ih, iw, oc, oh, ow, kh, kw, sh, sw, dh, dw, pht, pwl, groups;
+  int icg, ocg;   // channels per group
+  int K;          // icg * kh * kw
+  int do_relu;
+  float relu_limit;
+};
+
+// One-time: OIHW weight -> [groups][K][ocg], and the per-k gather table (K entries).
+int top_conv_prepare(const TopConvPlan& p, const float* w_oihw, float* wt, int2* ktab, cudaStream_t s);
+// y[n][oc][oh][ow] = relu(conv(x[n][ic][ih][iw]) + bias); wt / ktab from top_conv_prepare.  A matrix product
+// y[M][N] = x[M][K] * w[K][N] is the case ih = iw = kh = kw = 1 with wt = w and ktab = null.
+int top_conv_launch(const TopConvPlan& p, const float* x, const float* wt, const int2* ktab, const float* bias, float* y,
+                    cudaStream_t s);
+int top_pool2d_launch(const float* x, float* y, long long nc, int ih, int iw, int oh, int ow, int kh, int kw, int sh, int sw,
+                      int pht, int phb, int pwl, int pwr, bool is_max, bool count_include_pad, bool do_relu, float relu_limit,
+                      cudaStream_t s);
+// y = relu(a + b); b may be null (plain ReLU)
+int top_add_launch(const float* a, const float* b, float* y, long long n, bool do_relu, float relu_limit, cudaStream_t s);
+
+}  // namespace b200q

@@ -152,6 +152,35 @@ class Conv2DOp:
             p.handle = None
 
 
+class TopConvOp:
+    """top.Conv in fp32 (lib/Dialect/Top/Interfaces/Conv.cpp:19-231): operands input, filter (OIHW), bias; attributes
+    ``kernel_shape, strides, dilations, pads (top, left, bottom, right), group, do_relu, relu_limit``.  The reference
+    keeps a oneDNN primitive in ``p.handle``; this operator face is stateless (init / deinit only mark the handle)."""
+
+    def __init__(self, *, input_shape, oc, kernel_shape, strides=(1, 1), dilations=(1, 1), pads=(0, 0, 0, 0), group=1,
+                 with_bias=True, do_relu=False, relu_limit=-1.0):
+        n, ic, ih, iw = input_shape
+        pht, pwl, phb, pwr = pads
+        self.desc = L.TopConvDesc(n=n, ic=ic, ih=ih, iw=iw, oc=oc, kh=kernel_shape[0], kw=kernel_shape[1], sh=strides[0],
+                                  sw=strides[1], dh=dilations[0], dw=dilations[1], pht=pht, phb=phb, pwl=pwl, pwr=pwr,
+                                  groups=group, with_bias=int(with_bias), do_relu=int(do_relu), relu_limit=float(relu_limit))
+        self.out_shape = (n, oc, (ih + pht + phb - dilations[0] * (kernel_shape[0] - 1) - 1) // strides[0] + 1,
+                          (iw + pwl + pwr - dilations[1] * (kernel_shape[1] - 1) - 1) // strides[1] + 1)
+
+    def init(self, p: InferenceParameter):
+        p.handle = True
+
+    def inference(self, p: InferenceParameter):
+        if p.handle is None:
+            raise L.B200QError(L.ERR_INVALID, "Conv inference without init (the reference fails the same way)")
+        ins = [_f32(a) for a in p.inputs]
+        outs = [_f32(a) for a in p.outputs]
+        L.check(L.lib().b200q_top_conv2d_inference(C.byref(self.desc), L.float_pp(ins), len(ins), L.float_pp(outs), len(outs)))
+
+    def deinit(self, p: InferenceParameter):
+        p.handle = None
+
+
 class A16MatMulOp:
     """tpu.A16MatMul, static 4-bit weights (lib/Dialect/Tpu/Interfaces/Common/A16MatMul.cpp:16-249).
 

@@ -51,44 +51,128 @@ def build_fp32(seed: int = 3) -> List[dict]:
 
 
 class Fp32Forward:
-    """fp32 forward of the fused graph on a torch device; returns every activation (the calibration targets)."""
+    """fp32 forward of the fused graph with this library's Top-dialect kernels (full-fp32 implicit-GEMM convolution,
+    pooling, add, matrix product: csrc/top_f32.cu); returns every activation (the calibration targets) as NCHW device
+    tensors.  Needs the CUDA library: there is no other path."""
 
     def __init__(self, ops: List[dict], device):
+        import ctypes as C
+
         import torch
-        self.torch = torch
+
+        from . import _lib as L
+        self.torch, self.C, self.L = torch, C, L
         self.ops = ops
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise L.B200QError(L.ERR_UNSUPPORTED, "Fp32Forward runs on a CUDA device only")
         self.par = {}
-        for op in ops:
-            if "w" in op:
-                self.par[op["name"]] = (torch.from_numpy(op["w"]).to(device),
-                                        torch.from_numpy(op["b"]).to(device) if op.get("b") is not None else None)
+        self.handles = {}
+        self.shape = {}
+        with torch.cuda.device(self.device):
+            shapes = {"input": (3, 224, 224)}
+            for op in ops:
+                cin = shapes[op["inputs"][0]]
+                if op["type"] == "conv":
+                    w = torch.from_numpy(op["w"]).to(self.device).contiguous()
+                    b = torch.from_numpy(op["b"]).to(self.device).contiguous()
+                    oc, _, kh, kw = op["w"].shape
+                    d = L.TopConvDesc(n=1, ic=cin[0], ih=cin[1], iw=cin[2], oc=oc, kh=kh, kw=kw, sh=op["stride"][0],
+                                      sw=op["stride"][1], dh=1, dw=1, pht=op["pad"][0], phb=op["pad"][0], pwl=op["pad"][1],
+                                      pwr=op["pad"][1], groups=1, with_bias=1, do_relu=int(op["relu"]), relu_limit=-1.0)
+                    h = C.c_void_p()
+                    L.check(L.lib().b200q_top_conv2d_dev_create(C.byref(d), C.c_void_p(w.data_ptr()), C.c_void_p(b.data_ptr()),
+                                                                C.byref(h)))
+                    oh, ow = C.c_int64(), C.c_int64()
+                    L.lib().b200q_top_conv2d_dev_output_shape(h, C.byref(oh), C.byref(ow))
+                    self.handles[op["name"]] = h
+                    self.par[op["name"]] = (w, b)          # the handle reads the bias in place: keep it alive
+                    shapes[op["name"]] = (oc, oh.value, ow.value)
+                elif op["type"] == "maxpool":
+                    k, s_, p_ = op["kernel"], op["stride"], op["pad"]
+                    shapes[op["name"]] = (cin[0], (cin[1] + 2 * p_[0] - k[0]) // s_[0] + 1, (cin[2] + 2 * p_[1] - k[1]) // s_[1] + 1)
+                elif op["type"] == "add":
+                    shapes[op["name"]] = cin
+                elif op["type"] == "avgpool":
+                    k = op["kernel"]
+                    shapes[op["name"]] = (cin[0], (cin[1] - k[0]) // k[0] + 1, (cin[2] - k[1]) // k[1] + 1)
+                elif op["type"] == "fc":
+                    self.par[op["name"]] = (torch.from_numpy(op["w"]).to(self.device).contiguous(),
+                                            torch.from_numpy(op["b"]).to(self.device).contiguous())
+                    shapes[op["name"]] = (op["w"].shape[1],)
+                else:
+                    raise ValueError(op["type"])
+            self.shape = shapes
+
+    def __del__(self):
+        try:
+            for h in self.handles.values():
+                self.L.lib().b200q_top_conv2d_dev_destroy(self.C.byref(h))
+        except Exception:
+            pass
 
     def __call__(self, x) -> Dict[str, "object"]:
-        F = self.torch.nn.functional
-        self.torch.backends.cudnn.allow_tf32 = False
-        self.torch.backends.cuda.matmul.allow_tf32 = False
+        torch, C, L = self.torch, self.C, self.L
+        lib = L.lib()
+        P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        x = x.to(self.device, dtype=torch.float32).contiguous()
+        if tuple(x.shape[1:]) != self.shape["input"]:
+            raise L.B200QError(L.ERR_INVALID, f"input must be [B, 3, 224, 224], got {tuple(x.shape)}")
+        B = x.shape[0]
         acts = {"input": x}
-        for op in self.ops:
-            a = acts[op["inputs"][0]]
-            t = op["type"]
-            if t == "conv":
-                w, b = self.par[op["name"]]
-                y = F.conv2d(a, w, b, stride=op["stride"], padding=op["pad"])
-                y = F.relu(y) if op["relu"] else y
-            elif t == "maxpool":
-                y = F.max_pool2d(a, op["kernel"], op["stride"], op["pad"])
-            elif t == "add":
-                y = a + acts[op["inputs"][1]]
-                y = F.relu(y) if op["relu"] else y
-            elif t == "avgpool":
-                y = F.avg_pool2d(a, op["kernel"])
-            elif t == "fc":
-                w, b = self.par[op["name"]]
-                y = a.flatten(1) @ w + b
-            else:
-                raise ValueError(t)
-            acts[op["name"]] = y
+        with torch.cuda.device(self.device):
+            stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            for op in self.ops:
+                a = acts[op["inputs"][0]]
+                t = op["type"]
+                y = torch.empty((B,) + tuple(self.shape[op["name"]]), dtype=torch.float32, device=self.device)
+                if t == "conv":
+                    L.check(lib.b200q_top_conv2d_dev_run(self.handles[op["name"]], P(a), P(y), B, stream))
+                elif t == "maxpool":
+                    k, s_, p_ = op["kernel"], op["stride"], op["pad"]
+                    L.check(lib.b200q_top_pool2d_f32_dev(P(a), P(y), B * a.shape[1], a.shape[2], a.shape[3], k[0], k[1], s_[0],
+                                                         s_[1], p_[0], p_[0], p_[1], p_[1], 1, 0, 0, -1.0, stream))
+                elif t == "add":
+                    L.check(lib.b200q_top_add_f32_dev(P(a), P(acts[op["inputs"][1]]), P(y), y.numel(), int(op["relu"]), -1.0, stream))
+                elif t == "avgpool":
+                    k = op["kernel"]
+                    L.check(lib.b200q_top_pool2d_f32_dev(P(a), P(y), B * a.shape[1], a.shape[2], a.shape[3], k[0], k[1], k[0],
+                                                         k[1], 0, 0, 0, 0, 0, 1, 0, -1.0, stream))
+                elif t == "fc":
+                    w, b = self.par[op["name"]]
+                    L.check(lib.b200q_top_matmul_f32_dev(P(a), P(w), P(b), P(y), B, w.shape[0], w.shape[1], 0, -1.0, stream))
+                else:
+                    raise ValueError(t)
+                acts[op["name"]] = y
         return acts
+
+
+def fp32_forward_torch(ops: List[dict], x):
+    """The same graph through torch's own operators (on CPU: oneDNN, the library the reference's Top dialect calls).
+    Test infrastructure: a second opinion on Fp32Forward, never on the product path."""
+    import torch
+    F = torch.nn.functional
+    acts = {"input": x}
+    for op in ops:
+        a = acts[op["inputs"][0]]
+        t = op["type"]
+        if t == "conv":
+            y = F.conv2d(a, torch.from_numpy(op["w"]).to(a.device), torch.from_numpy(op["b"]).to(a.device), stride=op["stride"],
+                         padding=op["pad"])
+            y = F.relu(y) if op["relu"] else y
+        elif t == "maxpool":
+            y = F.max_pool2d(a, op["kernel"], op["stride"], op["pad"])
+        elif t == "add":
+            y = a + acts[op["inputs"][1]]
+            y = F.relu(y) if op["relu"] else y
+        elif t == "avgpool":
+            y = F.avg_pool2d(a, op["kernel"])
+        elif t == "fc":
+            y = a.flatten(1) @ torch.from_numpy(op["w"]).to(a.device) + torch.from_numpy(op["b"]).to(a.device)
+        else:
+            raise ValueError(t)
+        acts[op["name"]] = y
+    return acts
 
 
 def lower_int8(ops: List[dict], table: Dict[str, tuple], batch: int):
