@@ -458,6 +458,11 @@ int b200q_top_pool2d_f32_dev(const float *x, float *y, int64_t nc, int32_t ih, i
 int b200q_top_add_f32_dev(const float *a, const float *b, float *y, int64_t count, int32_t do_relu, float relu_limit,
                           void *stream);
 int b200q_top_relu_f32_dev(const float *x, float *y, int64_t count, float relu_limit, void *stream);
+/* The two array operations of the threshold tuner (python/calibration/simple_tunner.py): import_quant_bias (:43-50),
+ * y = clip(round_half_even(x * 127 / threshold), -128, 127) * threshold / 127; and the sums behind calc_distance
+ * (:334-358), ACCUMULATED into five device doubles: sum (ref - x)^2, sum |ref|, sum x * ref, sum x^2, sum ref^2. */
+int b200q_top_fake_quant_f32_dev(const float *x, float *y, int64_t count, double threshold, void *stream);
+int b200q_top_distance_f32_dev(const float *x, const float *ref, int64_t count, double *sums5, void *stream);
 
 /* The two symbols of the reference's calibration_math.so (bindings/kld/calibration_math.cpp:326-337), with
  * HOST buffers, so python/calibration/kld_calibrator.py:50-59 can load this library in its place.

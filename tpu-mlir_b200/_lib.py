@@ -136,6 +136,8 @@ SIGNATURES = {
     "b200q_top_pool2d_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64] + [C.c_int32] * 13 + [C.c_float, C.c_void_p]),
     "b200q_top_add_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),
     "b200q_top_relu_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p]),
+    "b200q_top_fake_quant_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_double, C.c_void_p]),
+    "b200q_top_distance_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200q_a16_w4_dev_dt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                       C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "b200q_a16_dev_create_dt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32,

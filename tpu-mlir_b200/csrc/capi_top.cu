@@ -154,4 +154,14 @@ int b200q_top_relu_f32_dev(const float* x, float* y, int64_t count, float relu_l
   return top_add_launch(x, nullptr, y, count, true, relu_limit, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_top_fake_quant_f32_dev(const float* x, float* y, int64_t count, double threshold, void* stream) {
+  if (!x || !y || count < 0) return set_error(B200Q_ERR_INVALID, "top_fake_quant_f32_dev: bad argument");
+  return top_fake_quant_launch(x, y, count, threshold, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_top_distance_f32_dev(const float* x, const float* ref, int64_t count, double* sums5, void* stream) {
+  if (!x || !ref || !sums5 || count < 0) return set_error(B200Q_ERR_INVALID, "top_distance_f32_dev: bad argument");
+  return top_distance_launch(x, ref, count, sums5, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -258,7 +258,61 @@ __global__ void add_f32_kernel(const float* __restrict__ a, const float* __restr
   }
 }
 
+// import_quant_bias of the threshold tuner (python/calibration/simple_tunner.py:43-50): the value on the int8 grid of
+// `threshold`, round(v * 127 / th) clipped to [-128, 127], back in float.  np.round rounds halves to even.
+__global__ void fake_quant_f32_kernel(const float* __restrict__ x, float* __restrict__ y, long long n, float scale) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = rintf(x[i] * scale);
+  v = fminf(fmaxf(v, -128.f), 127.f);
+  y[i] = v / scale;
+}
+
+// sums for the tuner's distance and cosine similarity (simple_tunner.py:334-358): out[0] += sum (ref - x)^2,
+// out[1] += sum |ref|, out[2] += sum x * ref, out[3] += sum x^2, out[4] += sum ref^2; double accumulation
+__global__ void distance_f32_kernel(const float* __restrict__ x, const float* __restrict__ ref, long long n, double* out) {
+  double s[5] = {0, 0, 0, 0, 0};
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const double a = x[i], r = ref[i], d = r - a;
+    s[0] += d * d;
+    s[1] += fabs(r);
+    s[2] += a * r;
+    s[3] += a * a;
+    s[4] += r * r;
+  }
+  __shared__ double sh[5][8];
+#pragma unroll
+  for (int k = 0; k < 5; ++k) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s[k] += __shfl_xor_sync(0xffffffffu, s[k], o);
+    if ((threadIdx.x & 31) == 0) sh[k][threadIdx.x >> 5] = s[k];
+  }
+  __syncthreads();
+  if (threadIdx.x < 5) {
+    double t = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sh[threadIdx.x][w];
+    atomicAdd(out + threadIdx.x, t);
+  }
+}
+
 }  // namespace
+
+int top_fake_quant_launch(const float* x, float* y, long long n, double threshold, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  if (!(threshold > 0.0)) return set_error(B200Q_ERR_INVALID, "fake quant: the threshold must be positive");
+  fake_quant_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, y, n, (float)(127.0 / threshold));   // the scale is formed in double and used as a float, like numpy does
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_distance_launch(const float* x, const float* ref, long long n, double* sums5, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  long long blocks = (n + 256 * 8 - 1) / (256 * 8);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  distance_f32_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, ref, n, sums5);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
 
 int top_conv_prepare(const TopConvPlan& p, const float* w_oihw, float* wt, int2* ktab, cudaStream_t s) {
   const long long total = (long long)p.groups * p.ocg * p.K;

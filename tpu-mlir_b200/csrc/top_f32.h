@@ -25,4 +25,9 @@ int top_pool2d_launch(const float* x, float* y, long long nc, int ih, int iw, in
 // y = relu(a + b); b may be null (plain ReLU)
 int top_add_launch(const float* a, const float* b, float* y, long long n, bool do_relu, float relu_limit, cudaStream_t s);
 
+// y = clip(rint(x * 127 / threshold), -128, 127) * threshold / 127
+int top_fake_quant_launch(const float* x, float* y, long long n, double threshold, cudaStream_t s);
+// sums5 (device, accumulated into): sum (ref - x)^2, sum |ref|, sum x * ref, sum x^2, sum ref^2
+int top_distance_launch(const float* x, const float* ref, long long n, double* sums5, cudaStream_t s);
+
 }  // namespace b200q

@@ -61,6 +61,7 @@ class module:  # noqa: N801  (name of the reference class)
         self.tensors: Dict[str, "torch.Tensor"] = {}
         self._plans: List[Callable] = []
         self._handles: List[C.c_void_p] = []
+        self._top_handles: List[C.c_void_p] = []   # fp32 Top-dialect convolutions
         self._keep = []
         self._before: List[Callable] = []
         self._after: List[Callable] = []
@@ -140,6 +141,9 @@ class module:  # noqa: N801  (name of the reference class)
         for h in self._handles:
             self.lib.b200q_conv2d_dev_destroy(C.byref(h))
         self._handles = []
+        for h in self._top_handles:
+            self.lib.b200q_top_conv2d_dev_destroy(C.byref(h))
+        self._top_handles = []
 
     def __del__(self):
         try:
@@ -189,6 +193,8 @@ class module:  # noqa: N801  (name of the reference class)
         iinfo = [self._info(n) for n in op["inputs"]]
         oinfo = self._info(op["name"])
         stream = lambda: C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)  # noqa: E731
+        if t.startswith("top."):
+            return self._plan_top(op, ins, out, iinfo, stream)
         if t == "tpu.Cast":
             n = out.numel()
             if iinfo[0]["dtype"] == "f32":
@@ -336,6 +342,61 @@ class module:  # noqa: N801  (name of the reference class)
             return lambda: out.copy_(ins[0].reshape(out.shape))
         raise L.B200QError(L.ERR_UNSUPPORTED, f"op type {t} is not implemented by the executor")
 
+    def _plan_top(self, op, ins, out, iinfo, stream) -> Callable:
+        """fp32 Top-dialect ops (the float graph a calibration pass and the threshold tuner run): top.Conv, top.MatMul,
+        top.Add, top.MaxPool, top.AvgPool, top.Relu, top.Reshape, with the attribute names of TopOps.td."""
+        t, a, lib = op["type"], op.get("attrs", {}), self.lib
+        limit = float(a.get("relu_limit", -1.0))
+        relu = int(bool(a.get("do_relu", False)))
+        if any(i["dtype"] != "f32" for i in iinfo) or self._info(op["name"])["dtype"] != "f32":
+            raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: Top-dialect ops run on f32 tensors")
+        if t == "top.Conv":
+            w = self.weights[op["name"] + "_filter"].to(self.torch.float32).contiguous()
+            b = self.weights.get(op["name"] + "_bias")
+            b = b.to(self.torch.float32).contiguous() if b is not None else None
+            n, ic, ih, iw = iinfo[0]["shape"]
+            kh, kw = a["kernel_shape"]
+            sh, sw = a.get("strides", [1, 1])
+            dh, dw = a.get("dilations", [1, 1])
+            pht, pwl, phb, pwr = a.get("pads", [0, 0, 0, 0])
+            d = L.TopConvDesc(n=n, ic=ic, ih=ih, iw=iw, oc=w.shape[0], kh=kh, kw=kw, sh=sh, sw=sw, dh=dh, dw=dw, pht=pht, phb=phb,
+                              pwl=pwl, pwr=pwr, groups=a.get("group", 1), with_bias=int(b is not None), do_relu=relu, relu_limit=limit)
+            h = C.c_void_p()
+            L.check(lib.b200q_top_conv2d_dev_create(C.byref(d), _P(w), _P(b), C.byref(h)))
+            self._top_handles.append(h)
+            self._keep.append((w, b))
+            return lambda: L.check(lib.b200q_top_conv2d_dev_run(h, _P(ins[0]), _P(out), n, stream()))
+        if t == "top.MatMul":
+            if a.get("right_transpose") or a.get("left_transpose") or a.get("output_transpose") or a.get("hdim_is_batch"):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: top.MatMul with transposes is not implemented")
+            w = self.weights[op["name"] + "_filter"].to(self.torch.float32).contiguous()      # [K, N]
+            b = self.weights.get(op["name"] + "_bias")
+            b = b.to(self.torch.float32).contiguous() if b is not None else None
+            K, N = w.shape
+            M = ins[0].numel() // K
+            self._keep.append((w, b))
+            return lambda: L.check(lib.b200q_top_matmul_f32_dev(_P(ins[0]), _P(w), _P(b), _P(out), M, K, N, relu, limit, stream()))
+        if t == "top.Add":
+            if len(ins) != 2 or tuple(iinfo[0]["shape"]) != tuple(iinfo[1]["shape"]):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: top.Add takes two tensors of one shape here")
+            n = out.numel()
+            return lambda: L.check(lib.b200q_top_add_f32_dev(_P(ins[0]), _P(ins[1]), _P(out), n, relu, limit, stream()))
+        if t in ("top.MaxPool", "top.AvgPool"):
+            nb, c, ih, iw = iinfo[0]["shape"]
+            kh, kw = a["kernel_shape"]
+            sh, sw = a.get("strides", [1, 1])
+            pht, pwl, phb, pwr = a.get("pads", [0, 0, 0, 0])
+            is_max = int(t == "top.MaxPool")
+            cip = int(bool(a.get("count_include_pad", False)))
+            return lambda: L.check(lib.b200q_top_pool2d_f32_dev(_P(ins[0]), _P(out), nb * c, ih, iw, kh, kw, sh, sw, pht, phb, pwl,
+                                                                pwr, is_max, cip, relu, limit, stream()))
+        if t == "top.Relu":
+            n = out.numel()
+            return lambda: L.check(lib.b200q_top_relu_f32_dev(_P(ins[0]), _P(out), n, limit, stream()))
+        if t == "top.Reshape":
+            return lambda: out.copy_(ins[0].reshape(out.shape))
+        raise L.B200QError(L.ERR_UNSUPPORTED, f"op type {t} is not implemented by the executor")
+
     # ------------------------------------------------------------------ pymlir.module surface
     def set_tensor(self, name: str, data, shape=None):
         """Float input of the graph (quantisation happens in the graph's own tpu.Cast, as in a lowered model)."""
@@ -402,6 +463,16 @@ class module:  # noqa: N801  (name of the reference class)
                 self._expressed = False
                 self._run_ops([(op, run)])
                 return self.get_tensor(name)
+        raise KeyError(name)
+
+    def invoke_op(self, name: str):
+        """invoke_at without the copy to the host: the op's output stays in ``tensors[name]`` on the device."""
+        target = self._fused_adds.get(name, name)
+        for op, run in zip(self.graph["ops"], self._plans):
+            if op["name"] == target:
+                self._expressed = False
+                self._run_ops([(op, run)])
+                return
         raise KeyError(name)
 
     def invoke_from(self, name: str):

@@ -175,6 +175,43 @@ def fp32_forward_torch(ops: List[dict], x):
     return acts
 
 
+def top_graph(ops: List[dict], batch: int):
+    """The fused fp32 op list as a Top-dialect graph for the executor (module.py): (graph, weights)."""
+    tensors = {"input": {"shape": [batch, 3, 224, 224], "dtype": "f32"}}
+    gops, weights = [], {}
+    for op in ops:
+        cin = tensors[op["inputs"][0]]["shape"]
+        t, name = op["type"], op["name"]
+        if t == "conv":
+            oc, _, kh, kw = op["w"].shape
+            p, s_ = op["pad"], op["stride"]
+            shape = [batch, oc, (cin[2] + 2 * p[0] - kh) // s_[0] + 1, (cin[3] + 2 * p[1] - kw) // s_[1] + 1]
+            gops.append(dict(type="top.Conv", name=name, inputs=list(op["inputs"]),
+                             attrs=dict(kernel_shape=[kh, kw], strides=list(s_), pads=[p[0], p[1], p[0], p[1]], do_relu=op["relu"])))
+            weights[name + "_filter"], weights[name + "_bias"] = op["w"], op["b"]
+        elif t == "maxpool":
+            k, s_, p = op["kernel"], op["stride"], op["pad"]
+            shape = [batch, cin[1], (cin[2] + 2 * p[0] - k[0]) // s_[0] + 1, (cin[3] + 2 * p[1] - k[1]) // s_[1] + 1]
+            gops.append(dict(type="top.MaxPool", name=name, inputs=list(op["inputs"]),
+                             attrs=dict(kernel_shape=list(k), strides=list(s_), pads=[p[0], p[1], p[0], p[1]])))
+        elif t == "add":
+            shape = list(cin)
+            gops.append(dict(type="top.Add", name=name, inputs=list(op["inputs"]), attrs=dict(do_relu=op["relu"])))
+        elif t == "avgpool":
+            k = op["kernel"]
+            shape = [batch, cin[1], cin[2] // k[0], cin[3] // k[1]]
+            gops.append(dict(type="top.AvgPool", name=name, inputs=list(op["inputs"]),
+                             attrs=dict(kernel_shape=list(k), strides=list(k), pads=[0, 0, 0, 0], count_include_pad=True)))
+        elif t == "fc":
+            shape = [batch, op["w"].shape[1]]
+            gops.append(dict(type="top.MatMul", name=name, inputs=list(op["inputs"]), attrs={}))
+            weights[name + "_filter"], weights[name + "_bias"] = op["w"], op["b"]
+        else:
+            raise ValueError(t)
+        tensors[name] = {"shape": shape, "dtype": "f32"}
+    return dict(inputs=["input"], outputs=[ops[-1]["name"]], tensors=tensors, ops=gops, state="TOP_F32"), weights
+
+
 def lower_int8(ops: List[dict], table: Dict[str, tuple], batch: int):
     """INT8 symmetric lowering.  ``table[name] = (threshold, min, max)`` is the calibration table.  Returns
     (graph, weights) in the format module.load takes."""
