@@ -7,8 +7,9 @@
 //
 // The convolution is an implicit GEMM on the CUDA cores in full fp32 (calibration statistics should not depend on a
 // reduced-precision product): C[co][pixel] = sum_k Wt[k][co] * X[k][pixel], k = (c, kh, kw).  A block computes 128 (or
-// 64) output channels x 128 pixels, K in slices of 8 through double-buffered shared memory; a thread owns 8 x 8 (4 x 8)
-// results.  The weight is kept transposed [K][oc] so its tile loads are contiguous; the activation tile is gathered
+// 64) output channels x 128 pixels, K in slices of 8 through a four-stage ring in shared memory; a thread owns 8 x 8 (4 x 8)
+// results; the tiles travel by cp.async, three slices ahead.  The weight is kept transposed [K][oc] so its tile loads
+// are contiguous; the activation tile is gathered
 // with a per-k table (offset of (c, kh, kw) inside an image and the two shifts for the border test), the pixel's own
 // decomposition (image, row, column) is computed once per thread.  In NCHW consecutive pixels are consecutive
 // addresses for a fixed k, so both the gather and the store run along the fast axis.
@@ -24,6 +25,21 @@ namespace {
 constexpr int TN = 128;   // pixels per block
 constexpr int TK = 8;     // k per slice
 constexpr int CONV_THREADS = 256;
+constexpr int STAGES = 4;   // slices of K in flight (shared memory: 4 x 8 KB at 128 output channels)
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// asynchronous global -> shared copies; src_bytes < the copy size zero-fills the rest (0: nothing is read)
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 __device__ __forceinline__ float relu_f(float v, int do_relu, float limit) {
   if (do_relu) {
@@ -40,8 +56,8 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
                                                                    const int2* __restrict__ ktab, const float* __restrict__ bias,
                                                                    float* __restrict__ y, const TopConvPlan p) {
   constexpr int RM = TM / 16;   // output channels per thread: 8 or 4
-  __shared__ __align__(16) float As[2][TK][TM];
-  __shared__ __align__(16) float Bs[2][TK][TN];
+  __shared__ __align__(16) float As[STAGES][TK][TM];
+  __shared__ __align__(16) float Bs[STAGES][TK][TN];
   const int tid = threadIdx.x;
   const int g = blockIdx.z;
   const int co0 = blockIdx.y * TM;                 // inside the group
@@ -70,27 +86,30 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
   const bool a_active = tid < A_VECS;
   const bool a_vec = (p.ocg & 3) == 0;
 
-  float4 a_reg = make_float4(0.f, 0.f, 0.f, 0.f);
-  float b_reg[4];
-  auto fetch = [&](int k0) {
+  // Tiles go from global to shared memory with cp.async (no staging registers), STAGES - 1 slices ahead of the
+  // arithmetic: 16 bytes per thread of the weight tile, four 4-byte gathers of the activation tile whose source size
+  // is 0 outside the image (the copy then writes zeros).
+  auto issue = [&](int k0, int buf) {
     if (a_active) {
       const int k = k0 + ak;
-      a_reg = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (k < p.K) {
-        const float* src = wg + (size_t)k * p.ocg + co0 + ac;
-        if (a_vec && co0 + ac + 3 < p.ocg) a_reg = __ldg(reinterpret_cast<const float4*>(src));
-        else {
-          if (co0 + ac + 0 < p.ocg) a_reg.x = __ldg(src + 0);
-          if (co0 + ac + 1 < p.ocg) a_reg.y = __ldg(src + 1);
-          if (co0 + ac + 2 < p.ocg) a_reg.z = __ldg(src + 2);
-          if (co0 + ac + 3 < p.ocg) a_reg.w = __ldg(src + 3);
+      const uint32_t dst = smem_addr(&As[buf][ak][ac]);
+      const float* src = wg + (size_t)(k < p.K ? k : 0) * p.ocg + co0 + ac;
+      if (a_vec) {
+        const bool ok = k < p.K && co0 + ac + 3 < p.ocg;
+        cp_async_16(dst, ok ? src : wg, ok ? 16 : 0);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const bool ok = k < p.K && co0 + ac + e < p.ocg;
+          cp_async_4(dst + 4 * e, ok ? src + e : wg, ok ? 4 : 0);
         }
       }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int k = k0 + bk + 2 * i;
-      float v = 0.f;
+      const float* src = x;
+      int bytes = 0;
       if (pvalid && k < p.K) {
         int koff, khd, kwd;
         if (KHW == 1) {
@@ -107,15 +126,13 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
           khd = t.y & 0xffff;
           kwd = t.y >> 16;
         }
-        if ((unsigned)(hi0 + khd) < (unsigned)p.ih && (unsigned)(wi0 + kwd) < (unsigned)p.iw) v = __ldg(x + xbase + koff);
+        if ((unsigned)(hi0 + khd) < (unsigned)p.ih && (unsigned)(wi0 + kwd) < (unsigned)p.iw) {
+          src = x + xbase + koff;
+          bytes = 4;
+        }
       }
-      b_reg[i] = v;
+      cp_async_4(smem_addr(&Bs[buf][bk + 2 * i][bp]), src, bytes);
     }
-  };
-  auto stash = [&](int buf) {
-    if (a_active) *reinterpret_cast<float4*>(&As[buf][ak][ac]) = a_reg;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) Bs[buf][bk + 2 * i][bp] = b_reg[i];
   };
 
   const int tx = tid & 15, ty = tid >> 4;
@@ -125,13 +142,18 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
-  fetch(0);
-  stash(0);
-  __syncthreads();
   const int nslices = (p.K + TK - 1) / TK;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < nslices) issue(s * TK, s);
+    cp_async_commit();
+  }
   for (int s = 0; s < nslices; ++s) {
-    const int buf = s & 1;
-    if (s + 1 < nslices) fetch((s + 1) * TK);
+    const int buf = s % STAGES;
+    cp_async_wait<STAGES - 2>();   // slice s has landed (for this thread's copies; the barrier extends that to all)
+    __syncthreads();               // ... and everybody is done with the buffer that the next copies overwrite
+    if (s + STAGES - 1 < nslices) issue((s + STAGES - 1) * TK, (s + STAGES - 1) % STAGES);
+    cp_async_commit();
 #pragma unroll
     for (int kk = 0; kk < TK; ++kk) {
       float a[RM], b[8];
@@ -153,11 +175,8 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
     }
-    if (s + 1 < nslices) {
-      stash(buf ^ 1);
-      __syncthreads();
-    }
   }
+  cp_async_wait<0>();
 
   // ---- bias, ReLU, store: rows ty * 4 + {0..3} (and TM / 2 + the same), pixels tx * 4 + {0..3} and 64 + the same
   const bool vec_store = (ohow & 3) == 0;
@@ -332,6 +351,8 @@ int top_conv_launch(const TopConvPlan& p, const float* x, const float* wt, const
     return set_error(B200Q_ERR_INVALID, "top conv: operands must be 16-byte aligned");
   const int khw = (p.kh == 1 && p.kw == 1) ? 1 : (p.kh == 3 && p.kw == 3) ? 9 : 0;
   if (khw == 0 && !ktab) return set_error(B200Q_ERR_INVALID, "top conv: this filter size needs the gather table");
+  // (64-channel tiles for the layers whose 128-channel grid does not fill the GPU were measured: no faster - those
+  // layers are bound by the length of their K loop, not by the number of blocks)
   if (p.ocg > 64) {
     dim3 grid((unsigned)ptiles, (unsigned)((p.ocg + 127) / 128), (unsigned)p.groups);
     if (khw == 1) conv2d_f32_kernel<128, 1><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
