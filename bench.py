@@ -359,6 +359,46 @@ def kernel_lines(workload, steps, warmup, a16_m=(1, 2, 4, 8, 16, 128, 2048)):
                               roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s",
                                             frac=gbs / peaks["hbm_gbs"], traffic=None,
                                             peak_basis=f"{peaks['source']} copy bandwidth (read-only kernel)")))
+    elif workload == "top":
+        # fp32 Top-dialect forward (calibration's float graph): one 3x3 convolution and the whole ResNet-50 forward.
+        # The bound is the CUDA cores' fp32 FMA rate: SMs x 128 lanes x 2 flop x the SM clock sampled during the run.
+        from tpu_mlir_b200 import resnet50
+        n, ic, hw, oc = 64, 128, 28, 128
+        x = torch.randn(n, ic, hw, hw, device="cuda")
+        w = torch.randn(oc, ic, 3, 3, device="cuda")
+        b = torch.randn(oc, device="cuda")
+        d = L.TopConvDesc(n=n, ic=ic, ih=hw, iw=hw, oc=oc, kh=3, kw=3, sh=1, sw=1, dh=1, dw=1, pht=1, phb=1, pwl=1, pwr=1,
+                          groups=1, with_bias=1, do_relu=1, relu_limit=-1.0)
+        h = C.c_void_p()
+        L.check(lib.b200q_top_conv2d_dev_create(C.byref(d), P(w), P(b), C.byref(h)))
+        y = torch.empty(n, oc, hw, hw, device="cuda")
+        sampler = ClockSampler(torch.cuda.current_device())
+        sampler.start()
+        mean_c = _time_steps(lambda i: L.check(lib.b200q_top_conv2d_dev_run(h, P(x), P(y), n, None)), min(steps, 200), warmup)
+        lib.b200q_top_conv2d_dev_destroy(C.byref(h))
+        ops = resnet50.build_fp32()
+        fwd = resnet50.Fp32Forward(ops, torch.device("cuda"))
+        xb = torch.randn(64, 3, 224, 224, device="cuda")
+        mean_f = _time_steps(lambda i: fwd(xb), 10, 3)
+        clocks = sampler.stop()
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        mhz = float(clocks.get("sm_mhz") or clocks.get("sm_max_mhz") or 1965.0)
+        peak = sms * 128 * 2 * mhz * 1e6 / 1e12
+        tf_c = 2.0 * n * oc * hw * hw * ic * 9 / (mean_c * 1e-3) / 1e12
+        flop_img = sum(2.0 * np.prod(fwd.shape[o["name"]]) * np.prod(o["w"].shape[1:]) for o in ops if o["type"] == "conv")
+        tf_f = 64 * flop_img / (mean_f * 1e-3) / 1e12
+        basis = f"{sms} SMs x 128 fp32 lanes x 2 flop x {mhz:.0f} MHz (median SM clock sampled during the run)"
+        lines.append(dict(metric="fp32 conv TFLOP/s", value=tf_c, unit="TFLOP/s", ms_per_step=mean_c, dtype="f32", clocks=clocks,
+                          config=dict(workload="top.Conv fp32 NCHW n64 c128 28x28 oc128 k3 s1 p1 relu (ResNet-50 layer2)",
+                                      l2="input 25.7 MB + output 25.7 MB, L2-resident: the kernel is FMA-bound"),
+                          roofline=dict(bound="fp32 fma", achieved=tf_c, peak=peak, unit="TFLOP/s", frac=tf_c / peak, traffic=None,
+                                        peak_basis=basis)))
+        lines.append(dict(metric="ResNet-50 fp32 forward img/s", value=64 / (mean_f * 1e-3), unit="img/s", ms_per_step=mean_f,
+                          steps=10, dtype="f32",
+                          config=dict(workload="ResNet-50 fp32 Top-dialect forward, batch 64, every activation kept (the calibration "
+                                               "forward): 53 convolutions, pooling, adds, fc on this library's kernels"),
+                          roofline=dict(bound="fp32 fma", achieved=tf_f, peak=peak, unit="TFLOP/s", frac=tf_f / peak, traffic=None,
+                                        peak_basis=basis)))
     elif workload == "peak":
         lines.append(dict(metric="tensor-pipe peak", **tensor_peaks()))
     else:
@@ -697,7 +737,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="conv",
-                    choices=["conv", "gemm", "conv1x1", "a16", "hist", "peak", "resnet50", "calib"],
+                    choices=["conv", "gemm", "conv1x1", "a16", "hist", "top", "peak", "resnet50", "calib"],
                     help="conv = the benchmark contract (BASELINE config 1) with every other workload under `extras`; "
                          "any other value prints that workload's lines alone")
     ap.add_argument("--no-extras", action="store_true", help="headline only")
@@ -736,7 +776,7 @@ def main():
             if R.rank == 0:
                 extras["resnet50"], extras["calibration"] = r, c
                 if R.world == 1:
-                    for wl in ("gemm", "conv1x1", "a16", "hist"):
+                    for wl in ("gemm", "conv1x1", "a16", "hist", "top"):
                         extras[wl] = guarded(kernel_lines, wl, 100, 5)
                 extras["seconds"] = time.time() - t0
                 line["extras"] = extras
