@@ -374,6 +374,22 @@ def a16matmul_w4(x_bits, wq, scale_bits, zp, bias=None, *, group=64, f16=False):
     return y
 
 
+def a16matmul_w8(x_bits, w, scale_bits, zp, bias=None, *, group=64):
+    """tpu.A16MatMul static w8 path with w_transpose=true (A16MatMul.cpp:209-246): w [N,K] integers (any of the 8-bit
+    ranges), the dequantised weight (w - zp) * scale is rounded to bf16 before the fp32 matmul, the result rounded to
+    bf16.  ``group`` = K is the per-channel form (q_group_size = 0).  numpy: float64 accumulation of exact products."""
+    x = bf16_bits_to_f32(_c(x_bits, np.uint16)).astype(np.float64)
+    w = np.asarray(w, dtype=np.float32)
+    N, K = w.shape
+    s = np.repeat(bf16_bits_to_f32(_c(scale_bits, np.uint16)).reshape(N, K // group), group, axis=1)
+    z = np.repeat(np.asarray(zp, dtype=np.float32).reshape(N, K // group), group, axis=1)
+    W = bf16_bits_to_f32(f32_to_bf16_bits_fast(((w - z) * s).astype(np.float32))).astype(np.float64)
+    y = x @ W.T
+    if bias is not None:
+        y = y + np.asarray(bias, dtype=np.float64)
+    return f32_to_bf16_bits_fast(y.astype(np.float32))
+
+
 def a16_dequant_w4(wq, scale_bits, zp, *, group=64):
     wq = _c(wq, np.uint8)
     N, K = wq.shape[0], wq.shape[1] * 2

@@ -291,3 +291,55 @@ def test_warpgroup_kernel_refuses_more_than_32_tokens(route):
     y = torch.zeros((33, 128), dtype=torch.uint16, device="cuda")
     rc = L.lib().b200q_a16_w4_dev(ptr(x), ptr(wq), ptr(sc), ptr(zp), None, ptr(y), 33, 128, 256, 64, None, None)
     assert rc == L.ERR_UNSUPPORTED
+
+
+# ------------------------------------------------------------------ per-channel w4 and w8bf16 (operator face)
+@pytest.mark.parametrize("M", [1, 4, 20, 70])
+def test_per_channel_w4(M):
+    """q_group_size = 0: one scale and zero point per output channel (A16MatMul.cpp:176-187) = a group of K."""
+    K, N = 1024, 200
+    c = synth.a16_w4(seed=21, M=M, K=K, N=N, group=K)
+    ref = oracle.a16matmul_w4(c["x"], c["wq"], c["scale"], c["zp"], group=K)
+    f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)  # noqa: E731
+    op = A16MatMulOp(M=M, K=K, N=N, q_group_size=0)
+    out = np.zeros((M, N), np.float32)
+    p = InferenceParameter(inputs=[oracle.bf16_bits_to_f32(c["x"]), f32(c["wq"]), oracle.bf16_bits_to_f32(c["scale"]), f32(c["zp"]), None],
+                           outputs=[out])
+    op.inference(p)
+    if M >= 64:
+        check_rounded_weight(oracle.f32_to_bf16_bits_fast(out), oracle.bf16_bits_to_f32(ref))   # the handle's bf16-copy route
+    else:
+        check(oracle.f32_to_bf16_bits_fast(out), ref)
+
+
+@pytest.mark.parametrize("case", [dict(M=1, K=512, N=96, g=64, signed=False), dict(M=5, K=4096, N=300, g=128, signed=True),
+                                  dict(M=130, K=1024, N=257, g=0, signed=False), dict(M=33, K=264, N=40, g=8, signed=True)])
+def test_w8bf16_operator_face(case):
+    """weight_bits = 8 (A16MatMul.cpp:209-246): the reference rounds the dequantised weight to bf16 and multiplies in fp32;
+    here that bf16 matrix is built once per weight version and every M runs the bf16 tensor-core GEMM.  Weights signed or
+    unsigned, float-stored like every interpreter buffer.  The plain bound, with a bias."""
+    M, K, N, g = case["M"], case["K"], case["N"], case["g"]
+    group = g if g else K
+    rng = np.random.default_rng(31)
+    w = (rng.integers(-128, 128, size=(N, K)) if case["signed"] else rng.integers(0, 256, size=(N, K))).astype(np.float32)
+    zp = (rng.integers(-8, 8, size=N * K // group) if case["signed"] else rng.integers(120, 136, size=N * K // group)).astype(np.float32)
+    scale = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits_fast((rng.random(N * K // group) * 0.01 + 0.002).astype(np.float32)))
+    x = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits_fast(rng.standard_normal((M, K)).astype(np.float32)))
+    bias = rng.standard_normal(N).astype(np.float32)
+    ref = oracle.a16matmul_w8(oracle.f32_to_bf16_bits_fast(x), w, oracle.f32_to_bf16_bits_fast(scale), zp, bias, group=group)
+    op = A16MatMulOp(M=M, K=K, N=N, q_group_size=g, weight_bits=8, with_bias=True)
+    out = np.zeros((M, N), np.float32)
+    p = InferenceParameter(inputs=[x, w, scale, zp, bias], outputs=[out])
+    op.init(p)
+    op.inference(p)
+    op.inference(p)
+    op.deinit(p)
+    check(oracle.f32_to_bf16_bits_fast(out), ref)
+
+
+def test_w8_f16_is_refused():
+    op = A16MatMulOp(M=1, K=64, N=16, q_group_size=64, weight_bits=8, out_dtype=L.DT_F16)
+    with pytest.raises(L.B200QError) as ei:
+        op.inference(InferenceParameter(inputs=[np.zeros((1, 64), np.float32), np.zeros((16, 64), np.float32), np.zeros(16, np.float32),
+                                                np.zeros(16, np.float32), None], outputs=[np.zeros((1, 16), np.float32)]))
+    assert ei.value.code == L.ERR_UNSUPPORTED

@@ -100,6 +100,42 @@ int dequant_w4_bf16(const void* wq, const void* scale, const void* zp, void* W, 
   return B200Q_OK;
 }
 
+// 8-bit weights: W[n,k] = bf16((q - zp) * scale), which is the matrix the reference itself multiplies with
+// (A16MatMul.cpp:213-232 rounds the dequantised weight with BF16() before its matmul).  The weight and the zero points
+// are read as the interpreter stores them (floats holding integers, signed or unsigned); 8 weights per thread.
+__global__ void dequant_w8_bf16_kernel(const float4* __restrict__ wq, const __nv_bfloat16* __restrict__ scale,
+                                       const float* __restrict__ zp, uint4* __restrict__ W, long long octets, int K,
+                                       int group) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= octets) return;
+  const long long e0 = i * 8;
+  const long long n = e0 / K;
+  const int k = (int)(e0 - n * K);
+  const long long gi = n * (K / group) + k / group;   // group % 8 == 0: the 8 weights share a group
+  const float s = __bfloat162float(scale[gi]);
+  const float z = zp[gi];
+  const float4 lo = wq[2 * i], hi = wq[2 * i + 1];
+  const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn((v[2 * j] - z) * s, (v[2 * j + 1] - z) * s);
+    o[j] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  W[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+int dequant_w8_bf16(const float* wq_f32, const void* scale, const float* zp_f32, void* W, long long N, int K, int group,
+                    cudaStream_t s) {
+  const long long octets = N * K / 8;
+  if (octets == 0) return B200Q_OK;
+  dequant_w8_bf16_kernel<<<(unsigned)((octets + 255) / 256), 256, 0, s>>>(
+      reinterpret_cast<const float4*>(wq_f32), static_cast<const __nv_bfloat16*>(scale), zp_f32, static_cast<uint4*>(W),
+      octets, K, group);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
 // Prefill: y = x * W^T on the bf16 tensor cores (tcgen05 kind::f16, fp32 accumulation in TMEM).
 int a16_prefill_gemm(const void* x, const void* W16, const float* bias, void* y, long long M, int N, int K, int* status,
                      cudaStream_t s) {
@@ -123,11 +159,16 @@ int a16_prefill_gemm(const void* x, const void* W16, const float* bias, void* y,
 int validate(const b200q_a16matmul_desc& d) {
   if (d.M < 0 || d.K < 1 || d.N < 1 || d.M > 0x7fffffffLL || d.K > 0x7fffffffLL || d.N > 0x7fffffffLL)
     return set_error(B200Q_ERR_INVALID, "a16matmul: bad shape");
-  if (d.weight_bits != 4) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: only weight_bits = 4 is implemented");
+  if (d.weight_bits != 4 && d.weight_bits != 8) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: weight_bits must be 4 or 8");
   if (!d.w_transpose) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: only w_transpose = true (weight stored [N, K/2]) is implemented");
-  if (d.q_group_size <= 0) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: per-channel (q_group_size = 0) weights are not implemented");
+  if (d.q_group_size < 0) return set_error(B200Q_ERR_INVALID, "a16matmul: negative q_group_size");
   if (d.out_dtype != B200Q_DT_BF16 && d.out_dtype != B200Q_DT_F16)
     return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: activations/outputs are bf16 (w4bf16) or f16 (w4f16)");
+  if (d.weight_bits == 8) {
+    if (d.out_dtype != B200Q_DT_BF16) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: 8-bit weights are implemented for bf16 (w8bf16) only");
+    const int64_t g = d.q_group_size ? d.q_group_size : d.K;
+    if (d.K % 8 != 0 || g % 8 != 0 || d.K % g != 0) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: w8 needs K and the group size to be multiples of 8, the group dividing K");
+  }
   return B200Q_OK;
 }
 
@@ -244,12 +285,32 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
   int rc = B200Q_OK;
   const bool f16 = d.out_dtype == B200Q_DT_F16;
   do {
-    const size_t w_elems = (size_t)d.N * (d.K / 2), q_elems = (size_t)d.N * (d.K / d.q_group_size);
+    // q_group_size = 0: one scale and zero point per output channel (A16MatMul.cpp:176-187,:216-222) = a group of K
+    const int group = d.q_group_size ? d.q_group_size : (int)d.K;
+    const bool w8 = d.weight_bits == 8;
+    const size_t w_elems = w8 ? (size_t)d.N * d.K : (size_t)d.N * (d.K / 2), q_elems = (size_t)d.N * (d.K / group);
     const float* bias_f = (d.with_bias && n_inputs > 4) ? inputs[4] : nullptr;
     if (d.with_bias && !bias_f) { rc = set_error(B200Q_ERR_INVALID, "a16matmul: with_bias but inputs[4] is null"); break; }
     const bool cached = h->weights_ready && h->weight_version == d.weight_version && h->weight_ptr == inputs[1];
     if (!cached) {
       // weight bytes, scales and zero points arrive float-stored (WeightOp::read_as_float)
+      if (w8) {
+        // the reference multiplies with the bf16-rounded dequantised weight: build that matrix once per weight version
+        if ((rc = h->stage.ensure(w_elems * 4))) break;
+        if ((rc = h->scale.ensure(q_elems * 2))) break;
+        if ((rc = h->zp.ensure(q_elems * 4))) break;
+        if ((rc = h->w16.ensure(w_elems * 2))) break;
+        if (cudaMemcpyAsync(h->stage.p, inputs[2], q_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D scale", __FILE__, __LINE__); break; }
+        if ((rc = f32_to_16(h->stage.as<float>(), h->scale.p, (long long)q_elems, false, s))) break;
+        if (cudaMemcpyAsync(h->zp.p, inputs[3], q_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D zp", __FILE__, __LINE__); break; }
+        if (cudaMemcpyAsync(h->stage.p, inputs[1], w_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D weight", __FILE__, __LINE__); break; }
+        if ((rc = dequant_w8_bf16(h->stage.as<float>(), h->scale.p, h->zp.as<float>(), h->w16.p, d.N, (int)d.K, group, s))) break;
+        if (bias_f && (rc = h->bias.upload(bias_f, (size_t)d.N * 4, s))) break;
+        h->weights_ready = true;
+        h->w16_ready = true;
+        h->weight_version = d.weight_version;
+        h->weight_ptr = inputs[1];
+      } else {
       if ((rc = h->stage.ensure(w_elems * 4))) break;
       if ((rc = h->wq.ensure(w_elems))) break;
       if ((rc = h->scale.ensure(q_elems * 2))) break;
@@ -265,6 +326,7 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
       h->w16_ready = false;
       h->weight_version = d.weight_version;
       h->weight_ptr = inputs[1];
+      }
     }
     const size_t x_elems = (size_t)d.M * d.K, y_elems = (size_t)d.M * d.N;
     if (x_elems == 0) break;
@@ -276,8 +338,11 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
     if (cudaMemsetAsync(h->status.p, 0, 4, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "memset", __FILE__, __LINE__); break; }
     if (cudaMemcpyAsync(h->stage.p, inputs[0], x_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D input", __FILE__, __LINE__); break; }
     if ((rc = f32_to_16(h->stage.as<float>(), h->x16.p, (long long)x_elems, f16, s))) break;
-    if ((rc = a16_dispatch(h->x16.p, h->wq.p, h->scale.p, h->zp.p, bias_f ? h->bias.as<float>() : nullptr, h->y16.p,
-                           d.M, (int)d.N, (int)d.K, d.q_group_size, h->status.as<int>(), s, &h->w16, &h->w16_ready, false, f16, &h->wg_scratch))) break;
+    if (w8) {
+      if ((rc = a16_prefill_gemm(h->x16.p, h->w16.p, bias_f ? h->bias.as<float>() : nullptr, h->y16.p, d.M, (int)d.N, (int)d.K,
+                                 h->status.as<int>(), s))) break;
+    } else if ((rc = a16_dispatch(h->x16.p, h->wq.p, h->scale.p, h->zp.p, bias_f ? h->bias.as<float>() : nullptr, h->y16.p,
+                                  d.M, (int)d.N, (int)d.K, group, h->status.as<int>(), s, &h->w16, &h->w16_ready, false, f16, &h->wg_scratch))) break;
     if ((rc = f16_or_bf16_to_f32(h->y16.p, h->y32.as<float>(), (long long)y_elems, f16, s))) break;
     if (cudaMemcpyAsync(outputs[0], h->y32.p, y_elems * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__); break; }
     int hstat = 0;
