@@ -343,3 +343,38 @@ def test_w8_f16_is_refused():
         op.inference(InferenceParameter(inputs=[np.zeros((1, 64), np.float32), np.zeros((16, 64), np.float32), np.zeros(16, np.float32),
                                                 np.zeros(16, np.float32), None], outputs=[np.zeros((1, 16), np.float32)]))
     assert ei.value.code == L.ERR_UNSUPPORTED
+
+
+# ------------------------------------------------------------------ output rounding, bit for bit
+@pytest.mark.parametrize("M", [1, 4, 20])
+def test_bf16_output_rounding_matches_reference_on_edge_values(M):
+    """BF16() (lib/Support/Float16.cpp:603-645 with the denormal rule of :550-601, restated by the oracle and pinned there
+    against the reference's own code): every output here is ONE exact product x[m,0] * scale[n] (all other weights equal
+    their zero point), chosen around the places where the rule differs from a plain hardware conversion - fp32
+    denormals (flushed to zero, or to the smallest normal from fraction 0x7f8000 on), ties, the largest finite value,
+    infinity.  One token takes the CUDA-core kernel, four the mma.sync kernel, twenty the tcgen05 kernel."""
+    K, g = 64, 64
+    bf = lambda v: oracle.f32_to_bf16_bits_fast(np.asarray(v, dtype=np.float32))  # noqa: E731
+    scales = np.array([2.0 ** -20, 2.0 ** -27, 1.9921875 * 2.0 ** -28, 1.9921875 * 2.0 ** -27, 1.5 * 2.0 ** -27, 2.0 ** -26, 1.0, 1.0078125,
+                       1.0234375, 3.0, 2.0 ** 27, 1.9921875 * 2.0 ** 27, 2.0 ** 28, 0.0, 1.25 * 2.0 ** -30, 1.75 * 2.0 ** -33], np.float32)
+    N = scales.size
+    xs = np.array([2.0 ** -100, 1.9921875 * 2.0 ** -100, -1.5 * 2.0 ** -99, 1.0078125, -1.0234375, 1.9921875 * 2.0 ** 99, -(2.0 ** 100), 1.4921875 * 2.0 ** -101,
+                   1.0, 257.0 / 256.0 * 0 + 1.5, 2.0 ** -96, -(2.0 ** -104), 1.9921875, 0.0, -(2.0 ** 99), 1.0625, 2.0 ** -98, 1.75 * 2.0 ** -100, 1.1171875 * 2.0 ** -99,
+                   -1.3359375 * 2.0 ** -100], np.float32)[:M]
+    x = np.zeros((M, K), np.float32)
+    x[:, 0] = oracle.bf16_bits_to_f32(bf(xs))
+    zp = np.full(N, 7, np.uint8)
+    q = np.full((N, K), 7, np.uint8)
+    q[:, 0] = 8                                            # (q - zp) = 1 at k = 0, 0 elsewhere
+    wq = (q[:, 0::2] | (q[:, 1::2] << 4)).astype(np.uint8)
+    sb = bf(scales)
+    with np.errstate(over="ignore"):
+        prod = (x[:, :1] * oracle.bf16_bits_to_f32(sb)[None, :]).astype(np.float32)       # exact or IEEE-rounded once, like the kernels' fp32
+    want = np.array([[oracle.lib().orc_f32_to_bf16_bits(float(v)) for v in row] for row in prod], np.uint16)
+    want[prod == 0] = 0                                    # an exact zero is summed with the +0 of the other 63 terms
+    xd, wd, sd, zd = dev(bf(x)), dev(wq), dev(sb), dev(zp)
+    y = torch.zeros((M, N), dtype=torch.uint16, device="cuda")
+    L.check(L.lib().b200q_a16_w4_dev(ptr(xd), ptr(wd), ptr(sd), ptr(zd), None, ptr(y), M, N, K, g, None, None))
+    torch.cuda.synchronize()
+    got = y.cpu().numpy()
+    assert np.array_equal(got, want), [(m, n, hex(int(got[m, n])), hex(int(want[m, n])), float(prod[m, n])) for m in range(M) for n in range(N) if got[m, n] != want[m, n]][:8]

@@ -20,6 +20,7 @@
 #include "a16.h"
 #include "internal.h"
 #include "ptx_sm100.cuh"
+#include "round16.cuh"
 
 namespace b200q {
 namespace {
@@ -324,7 +325,7 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
 #pragma unroll
           for (int w = 0; w < CWARPS; ++w) v += rb[w * (ROWS * 8)];
           if (bias) v += bias[n];
-          y[(size_t)m * N + n] = __float2bfloat16_rn(v);
+          y[(size_t)m * N + n] = __ushort_as_bfloat16(f32_to_bf16_bits_ref(v));
         }
       }
     }
@@ -360,7 +361,7 @@ a16_w4_gemv_direct_kernel(const uint16_t* __restrict__ x, const uint8_t* __restr
                           const float* __restrict__ bias, uint16_t* __restrict__ y, int N, int K, int group,
                           int wpr, int early_weights) {
   auto to_bits = [](float v) -> uint16_t {
-    return F16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    return F16 ? __half_as_ushort(__float2half_rn(v)) : f32_to_bf16_bits_ref(v);
   };
   __shared__ float red[2][16][PF][M_T];   // [buffer][warp][row of the iteration][token]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

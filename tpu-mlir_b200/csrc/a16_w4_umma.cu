@@ -49,6 +49,7 @@
 #include "igemm.h"
 #include "internal.h"
 #include "ptx_sm100.cuh"
+#include "round16.cuh"
 
 namespace b200q {
 namespace {
@@ -145,7 +146,7 @@ __device__ __forceinline__ float bits_to_f32(uint32_t b) {
 }
 template <bool F16>
 __device__ __forceinline__ uint16_t f32_to_bits(float v) {
-  return F16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  return F16 ? __half_as_ushort(__float2half_rn(v)) : f32_to_bf16_bits_ref(v);
 }
 
 // Scales (bf16) or zero points (bytes) of the rows [row0, row0 + nrows) transposed into shared memory as T[g][n]:
@@ -1036,7 +1037,7 @@ a16_w4_umma_few_kernel(const __grid_constant__ CUtensorMap tmap_w, const UmmaArg
 #pragma unroll
             for (int c = 0; c < 16; ++c)
               if ((c & (mtok - 1)) == m) v += running[c];
-            args.y[(size_t)m * args.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(v + b));
+            args.y[(size_t)m * args.N + n] = f32_to_bf16_bits_ref(v + b);
           }
         }
       }

@@ -40,6 +40,7 @@
 #include "igemm.h"
 #include "internal.h"
 #include "ptx_sm100.cuh"
+#include "round16.cuh"
 
 namespace b200q {
 namespace {
@@ -375,7 +376,7 @@ a16_w4_wg_kernel(const __grid_constant__ CUtensorMap wmap, const WgArgs args) {
             for (int e = 0; e < 8; ++e) {
               if (c0 + e < args.M) {
                 const float r = v[e] + bv;
-                args.y[(size_t)(c0 + e) * args.N + n] = F16 ? __half_as_ushort(__float2half_rn(r)) : __bfloat16_as_ushort(__float2bfloat16_rn(r));
+                args.y[(size_t)(c0 + e) * args.N + n] = F16 ? __half_as_ushort(__float2half_rn(r)) : f32_to_bf16_bits_ref(r);
               }
             }
           }

@@ -22,6 +22,7 @@
 #include "igemm.h"
 #include "internal.h"
 #include "ptx_sm100.cuh"
+#include "round16.cuh"
 #include <atomic>
 #include <cmath>
 
@@ -630,8 +631,7 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             for (int j = 0; j < CH / 2; ++j) {
               const float v0 = __uint_as_float(r[2 * j]) + __int_as_float(chan[cbase + 2 * j].x);
               const float v1 = __uint_as_float(r[2 * j + 1]) + __int_as_float(chan[cbase + 2 * j + 1].x);
-              const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-              pk[j] = *reinterpret_cast<const uint32_t*>(&h);
+              pk[j] = (uint32_t)f32_to_bf16_bits_ref(v0) | ((uint32_t)f32_to_bf16_bits_ref(v1) << 16);
             }
             if (nc == CH && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
               reinterpret_cast<uint4*>(o)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
