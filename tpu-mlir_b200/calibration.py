@@ -82,10 +82,13 @@ def bin_schedule(sample_min: Sequence[float], sample_max: Sequence[float], bin_n
 
 
 def bin_schedule_many(sample_min: np.ndarray, sample_max: np.ndarray, bin_num: int = 2048) -> List[Schedule]:
-    """``bin_schedule`` for T tensors at once: ``sample_min / sample_max`` are float32 [T, S].  The recurrence runs over
-    the samples (it cannot be reordered), every step is one set of numpy operations over the T tensors, in the same
-    float32 arithmetic as the scalar form; the results are identical (tested).  With thousands of samples and tens of
-    tensors this is what keeps the host out of the calibration's critical path."""
+    """``bin_schedule`` for T tensors at once: ``sample_min / sample_max`` are float32 [T, S], the results are identical
+    to the scalar form (tested).  The recurrence cannot be reordered, but its state (threshold, bin count) only changes
+    at a sample that raises a tensor's running absolute maximum (or starts it): the running extrema of all samples are
+    accumulated in one pass, the recurrence's step runs only at the columns where some tensor's running maximum
+    rises - one set of numpy operations over the T tensors, in the same float32 arithmetic as the scalar form - and the
+    columns in between are filled from the unchanged state.  With thousands of samples and tens of tensors this keeps
+    the host out of the calibration's critical path (every rank computes the same schedule)."""
     smin = np.ascontiguousarray(sample_min, dtype=np.float32)
     smax = np.ascontiguousarray(sample_max, dtype=np.float32)
     T, S = smin.shape
@@ -100,11 +103,36 @@ def bin_schedule_many(sample_min: np.ndarray, sample_max: np.ndarray, bin_num: i
     last_reset = np.zeros(T, np.int64)
     one = np.float32(1)
     with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
-        for i in range(S):
-            run_min = np.minimum(smin[:, i], run_min)
-            run_max = np.maximum(smax[:, i], run_max)
-            abs_value = np.maximum(np.abs(run_min), np.abs(run_max))
-            live = ~(np.maximum(np.abs(smin[:, i]), np.abs(smax[:, i])) < np.float32(ALL_ZERO_EPS))
+        if S:
+            run_min_all = np.minimum.accumulate(smin, axis=1)
+            run_max_all = np.maximum.accumulate(smax, axis=1)
+            abs_all = np.maximum(np.abs(run_min_all), np.abs(run_max_all))
+            live_all = ~(np.maximum(np.abs(smin), np.abs(smax)) < np.float32(ALL_ZERO_EPS))
+            rises = np.ones(S, bool)
+            rises[1:] = (abs_all[:, 1:] > abs_all[:, :-1]).any(axis=0) | (abs_all[:, 1:] != abs_all[:, 1:]).any(axis=0)
+            run_min, run_max = run_min_all[:, -1].copy(), run_max_all[:, -1].copy()
+            events = np.flatnonzero(rises)
+        else:
+            events = np.zeros(0, np.int64)
+        filled = 0          # columns [0, filled) of th_s / nb_s are final
+        k = 0
+        forced = -1         # a column that must run although no maximum rises there (see `pending`)
+        while True:
+            nxt = int(events[k]) if k < events.size else S
+            if 0 <= forced < nxt:
+                i = forced
+            elif nxt < S:
+                i = nxt
+                k += 1
+            else:
+                break
+            forced = -1
+            if i > filled:   # the state did not change in [filled, i)
+                lv = live_all[:, filled:i]
+                th_s[:, filled:i] = np.where(lv, th[:, None], 0)
+                nb_s[:, filled:i] = np.where(lv, nb[:, None], 0)
+            abs_value = abs_all[:, i]
+            live = live_all[:, i]
             first = live & ~started
             grow = live & started & (abs_value > th)
             if first.any():
@@ -127,6 +155,15 @@ def bin_schedule_many(sample_min: np.ndarray, sample_max: np.ndarray, bin_num: i
                 width = np.where(upd, th / (nb - 1).astype(np.float32), width)
             th_s[:, i] = np.where(live, th, 0)
             nb_s[:, i] = np.where(live, nb, 0)
+            filled = i + 1
+            # float32 rounding can leave a grown threshold a hair below the maximum it grew for; the scalar form then
+            # grows again at the tensor's next live sample even though no maximum rises there: run the next column too
+            if i + 1 < S and (started & (abs_value > th)).any():
+                forced = i + 1
+        if S > filled:
+            lv = live_all[:, filled:S]
+            th_s[:, filled:S] = np.where(lv, th[:, None], 0)
+            nb_s[:, filled:S] = np.where(lv, nb[:, None], 0)
     out = []
     for t in range(T):
         lr = int(last_reset[t])
