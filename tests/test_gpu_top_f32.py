@@ -149,3 +149,28 @@ def test_resnet50_forward_against_onednn():
         assert g.shape == r.shape, op["name"]
         rms = float(np.sqrt(np.mean(r.astype(np.float64) ** 2))) + 1e-12
         assert float(np.abs(g - r).max()) <= 2e-4 * rms, (op["name"], float(np.abs(g - r).max()), rms)
+
+
+def test_conv_split_k_is_deterministic_and_matches():
+    """A layer with few output tiles and a long K (ResNet-50 layer4: 512 -> 512, 3x3 on 7x7) runs as several K splits
+    whose partial sums are added in a fixed order: two runs give the same bits, and the values meet the bound."""
+    rng = np.random.default_rng(13)
+    n, ic, hw, oc = 8, 512, 7, 512
+    x = rng.standard_normal((n, ic, hw, hw)).astype(np.float32)
+    w = (rng.standard_normal((oc, ic, 3, 3)) / np.sqrt(ic * 9)).astype(np.float32)
+    b = rng.standard_normal(oc).astype(np.float32)
+    ref = oracle.top_conv2d_f32(x, w, b, pads=(1, 1, 1, 1), do_relu=True)
+    d = L.TopConvDesc(n=n, ic=ic, ih=hw, iw=hw, oc=oc, kh=3, kw=3, sh=1, sw=1, dh=1, dw=1, pht=1, phb=1, pwl=1, pwr=1, groups=1,
+                      with_bias=1, do_relu=1, relu_limit=-1.0)
+    xd, wd, bd = dev(x), dev(w), dev(b)
+    h = C.c_void_p()
+    L.check(L.lib().b200q_top_conv2d_dev_create(C.byref(d), ptr(wd), ptr(bd), C.byref(h)))
+    outs = []
+    for _ in range(2):
+        y = torch.full(ref.shape, float("nan"), dtype=torch.float32, device="cuda")
+        L.check(L.lib().b200q_top_conv2d_dev_run(h, ptr(xd), ptr(y), n, None))
+        torch.cuda.synchronize()
+        outs.append(y.cpu().numpy())
+    L.lib().b200q_top_conv2d_dev_destroy(C.byref(h))
+    assert np.array_equal(outs[0], outs[1])
+    assert np.all(np.abs(outs[0] - ref) <= conv_bound(x, w, pads=(1, 1, 1, 1)))

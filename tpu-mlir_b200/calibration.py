@@ -338,7 +338,10 @@ class ShardedCalibrator:
             return time.perf_counter()
 
         if cache_bytes is None:
-            cache_bytes = max(0, torch.cuda.mem_get_info()[0] - (24 << 30)) if cuda else 0   # leave 24 GB to the forward
+            # what the driver has free plus what torch's allocator holds without using (blocks of an earlier run), less
+            # 24 GB for the forward
+            idle = torch.cuda.memory_reserved() - torch.cuda.memory_allocated() if cuda else 0
+            cache_bytes = max(0, torch.cuda.mem_get_info()[0] + idle - (24 << 30)) if cuda else 0
         # ---- pass 1: per-sample min/max of every tensor
         t0 = time.perf_counter()
         names: List[str] = []

@@ -14,7 +14,7 @@ namespace {
 
 struct TopConvHandle {
   TopConvPlan plan{};
-  DevBuf wt, ktab, bias, w_stage, x, y;
+  DevBuf wt, ktab, bias, w_stage, x, y, ws;
   bool with_bias = false;
   const float* d_bias = nullptr;   // device face: the caller's
 };
@@ -38,6 +38,7 @@ int make_plan(const b200q_top_conv_desc& d, TopConvPlan* out) {
   p.icg = p.ic / p.groups; p.ocg = p.oc / p.groups; p.K = (int)K;
   p.do_relu = d.do_relu ? 1 : 0;
   p.relu_limit = d.relu_limit;
+  p.splits = 1;
   *out = p;
   return B200Q_OK;
 }
@@ -73,7 +74,12 @@ int b200q_top_conv2d_dev_run(void* handle, const float* x, float* y, int64_t bat
   TopConvHandle* h = static_cast<TopConvHandle*>(handle);
   TopConvPlan p = h->plan;
   p.n = (int)batch;
-  return top_conv_launch(p, x, h->wt.as<float>(), h->ktab.as<int2>(), h->d_bias, y, static_cast<cudaStream_t>(stream));
+  int dev = 0, sms = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  p.splits = top_conv_splits(p, sms);
+  if (p.splits > 1) B200Q_TRY(h->ws.ensure((size_t)p.splits * p.n * p.oc * p.oh * p.ow * 4));   // grows on the first call of a batch size
+  return top_conv_launch(p, x, h->wt.as<float>(), h->ktab.as<int2>(), h->d_bias, y, h->ws.as<float>(), static_cast<cudaStream_t>(stream));
 }
 
 void b200q_top_conv2d_dev_output_shape(void* handle, int64_t* oh, int64_t* ow) {
@@ -112,7 +118,7 @@ int b200q_top_conv2d_inference(const b200q_top_conv_desc* desc, float* const* in
     if ((rc = h.x.upload(inputs[0], x_bytes, s))) break;
     if ((rc = h.y.ensure(y_bytes))) break;
     if ((rc = top_conv_launch(p, h.x.as<float>(), h.wt.as<float>(), h.ktab.as<int2>(), bias_h ? h.bias.as<float>() : nullptr,
-                              h.y.as<float>(), s))) break;
+                              h.y.as<float>(), nullptr, s))) break;
     if (cudaMemcpyAsync(outputs[0], h.y.p, y_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "D2H output", __FILE__, __LINE__); break; }
     if (cudaStreamSynchronize(s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "sync", __FILE__, __LINE__); break; }
   } while (0);
@@ -129,7 +135,7 @@ int b200q_top_matmul_f32_dev(const float* x, const float* w_kn, const float* bia
   TopConvPlan p{};
   p.n = (int)M; p.ic = (int)K; p.ih = p.iw = p.oh = p.ow = 1; p.oc = (int)N; p.kh = p.kw = p.sh = p.sw = p.dh = p.dw = 1;
   p.groups = 1; p.icg = (int)K; p.ocg = (int)N; p.K = (int)K; p.do_relu = do_relu ? 1 : 0; p.relu_limit = relu_limit;
-  return top_conv_launch(p, x, w_kn, nullptr, bias, y, s);
+  return top_conv_launch(p, x, w_kn, nullptr, bias, y, nullptr, s);
 }
 
 int b200q_top_pool2d_f32_dev(const float* x, float* y, int64_t nc, int32_t ih, int32_t iw, int32_t kh, int32_t kw, int32_t sh,

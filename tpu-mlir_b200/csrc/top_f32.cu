@@ -59,7 +59,10 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
   __shared__ __align__(16) float As[STAGES][TK][TM];
   __shared__ __align__(16) float Bs[STAGES][TK][TN];
   const int tid = threadIdx.x;
-  const int g = blockIdx.z;
+  // blockIdx.z = group * splits + split: with splits > 1 every split sums its own range of K into its own plane of the
+  // output buffer (which is then a workspace: no bias, no ReLU; splitk_reduce_kernel adds the planes in a fixed order)
+  const int g = blockIdx.z / p.splits, split = blockIdx.z - g * p.splits;
+  const int k_begin = split * p.k_per_split, k_end = min(p.K, k_begin + p.k_per_split);
   const int co0 = blockIdx.y * TM;                 // inside the group
   const long long pix0 = (long long)blockIdx.x * TN;
   const int ohow = p.oh * p.ow;
@@ -93,14 +96,14 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
     if (a_active) {
       const int k = k0 + ak;
       const uint32_t dst = smem_addr(&As[buf][ak][ac]);
-      const float* src = wg + (size_t)(k < p.K ? k : 0) * p.ocg + co0 + ac;
+      const float* src = wg + (size_t)(k < k_end ? k : 0) * p.ocg + co0 + ac;
       if (a_vec) {
-        const bool ok = k < p.K && co0 + ac + 3 < p.ocg;
+        const bool ok = k < k_end && co0 + ac + 3 < p.ocg;
         cp_async_16(dst, ok ? src : wg, ok ? 16 : 0);
       } else {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const bool ok = k < p.K && co0 + ac + e < p.ocg;
+          const bool ok = k < k_end && co0 + ac + e < p.ocg;
           cp_async_4(dst + 4 * e, ok ? src + e : wg, ok ? 4 : 0);
         }
       }
@@ -110,7 +113,7 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
       const int k = k0 + bk + 2 * i;
       const float* src = x;
       int bytes = 0;
-      if (pvalid && k < p.K) {
+      if (pvalid && k < k_end) {
         int koff, khd, kwd;
         if (KHW == 1) {
           koff = k * p.ih * p.iw;
@@ -142,17 +145,17 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
-  const int nslices = (p.K + TK - 1) / TK;
+  const int nslices = (k_end - k_begin + TK - 1) / TK;
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < nslices) issue(s * TK, s);
+    if (s < nslices) issue(k_begin + s * TK, s);
     cp_async_commit();
   }
   for (int s = 0; s < nslices; ++s) {
     const int buf = s % STAGES;
     cp_async_wait<STAGES - 2>();   // slice s has landed (for this thread's copies; the barrier extends that to all)
     __syncthreads();               // ... and everybody is done with the buffer that the next copies overwrite
-    if (s + STAGES - 1 < nslices) issue((s + STAGES - 1) * TK, (s + STAGES - 1) % STAGES);
+    if (s + STAGES - 1 < nslices) issue(k_begin + (s + STAGES - 1) * TK, (s + STAGES - 1) % STAGES);
     cp_async_commit();
 #pragma unroll
     for (int kk = 0; kk < TK; ++kk) {
@@ -180,19 +183,21 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
 
   // ---- bias, ReLU, store: rows ty * 4 + {0..3} (and TM / 2 + the same), pixels tx * 4 + {0..3} and 64 + the same
   const bool vec_store = (ohow & 3) == 0;
+  const bool partial = p.splits > 1;
+  if (partial) y += (size_t)split * P * p.oc;
 #pragma unroll
   for (int i = 0; i < RM; ++i) {
     const int co = co0 + (i < 4 ? ty * 4 + i : (TM / 2) + ty * 4 + (i - 4));
     if (co >= p.ocg) continue;
     const int oc = g * p.ocg + co;
-    const float bv = bias ? __ldg(bias + oc) : 0.f;
+    const float bv = (bias && !partial) ? __ldg(bias + oc) : 0.f;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const long long q0 = pix0 + h * 64 + tx * 4;
       if (q0 >= P) continue;
       float v[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] = relu_f(acc[i][h * 4 + j] + bv, p.do_relu, p.relu_limit);
+      for (int j = 0; j < 4; ++j) v[j] = relu_f(acc[i][h * 4 + j] + bv, partial ? 0 : p.do_relu, p.relu_limit);
       if (vec_store && q0 + 3 < P) {
         const long long b = q0 / ohow, r = q0 - b * ohow;
         *reinterpret_cast<float4*>(y + (b * p.oc + oc) * ohow + r) = make_float4(v[0], v[1], v[2], v[3]);
@@ -207,6 +212,32 @@ __global__ void __launch_bounds__(CONV_THREADS) conv2d_f32_kernel(const float* _
         }
       }
     }
+  }
+}
+
+// y = relu(sum over the splits' planes, in plane order, + bias): 4 outputs per thread (count is a multiple of 4 or the
+// tail runs element by element)
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, const float* __restrict__ bias, float* __restrict__ y,
+                                     long long count, int splits, int oc, int ohow, int do_relu, float relu_limit) {
+  const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 >= count) return;
+  const int n = (int)min((long long)4, count - i4);
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (n == 4 && (ohow & 3) == 0) {
+    for (int s = 0; s < splits; ++s) {
+      const float4 u = __ldg(reinterpret_cast<const float4*>(ws + (size_t)s * count + i4));
+      v[0] += u.x; v[1] += u.y; v[2] += u.z; v[3] += u.w;
+    }
+    const float bv = bias ? __ldg(bias + (int)((i4 / ohow) % oc)) : 0.f;   // the four share a channel: ohow % 4 == 0
+    *reinterpret_cast<float4*>(y + i4) = make_float4(relu_f(v[0] + bv, do_relu, relu_limit), relu_f(v[1] + bv, do_relu, relu_limit),
+                                                     relu_f(v[2] + bv, do_relu, relu_limit), relu_f(v[3] + bv, do_relu, relu_limit));
+    return;
+  }
+  for (int e = 0; e < n; ++e) {
+    float a = 0.f;
+    for (int s = 0; s < splits; ++s) a += __ldg(ws + (size_t)s * count + i4 + e);
+    const float bv = bias ? __ldg(bias + (int)(((i4 + e) / ohow) % oc)) : 0.f;
+    y[i4 + e] = relu_f(a + bv, do_relu, relu_limit);
   }
 }
 
@@ -341,8 +372,33 @@ int top_conv_prepare(const TopConvPlan& p, const float* w_oihw, float* wt, int2*
   return B200Q_OK;
 }
 
-int top_conv_launch(const TopConvPlan& p, const float* x, const float* wt, const int2* ktab, const float* bias, float* y,
-                    cudaStream_t s) {
+// K splits for a launch whose grid would leave SMs idle.  Model: the launch takes `waves` rounds of (k per split + a
+// fixed cost per block worth about 128 k); the split count with the smallest product wins, each split at least 256 k.
+int top_conv_splits(const TopConvPlan& p, int sms) {
+  const long long P = (long long)p.n * p.oh * p.ow;
+  const long long ptiles = (P + TN - 1) / TN;
+  const int tm = p.ocg > 64 ? 128 : 64;
+  const long long blocks = ptiles * ((p.ocg + tm - 1) / tm) * p.groups;
+  const long long slots = 2LL * sms;
+  if (blocks <= 0 || blocks >= slots) return 1;   // (grids of one to four waves were tried too: no gain in the sum)
+  int best = 1;
+  long long best_cost = 0, cost1 = 0;
+  for (int sp = 1; sp <= 8; ++sp) {
+    if (sp > 1 && p.K / sp < 256) break;
+    const long long waves = (blocks * sp + slots - 1) / slots;
+    const long long cost = waves * ((p.K + sp - 1) / sp + 128);
+    if (sp == 1) cost1 = cost;
+    if (sp == 1 || cost < best_cost) {
+      best = sp;
+      best_cost = cost;
+    }
+  }
+  return best_cost * 10 <= cost1 * 9 ? best : 1;   // the partial sums cost a pass over the output: worth it from 10 % on
+}
+
+int top_conv_launch(const TopConvPlan& plan, const float* x, const float* wt, const int2* ktab, const float* bias, float* y,
+                    float* workspace, cudaStream_t s) {
+  TopConvPlan p = plan;
   const long long P = (long long)p.n * p.oh * p.ow;
   if (P == 0) return B200Q_OK;
   const long long ptiles = (P + TN - 1) / TN;
@@ -351,20 +407,32 @@ int top_conv_launch(const TopConvPlan& p, const float* x, const float* wt, const
     return set_error(B200Q_ERR_INVALID, "top conv: operands must be 16-byte aligned");
   const int khw = (p.kh == 1 && p.kw == 1) ? 1 : (p.kh == 3 && p.kw == 3) ? 9 : 0;
   if (khw == 0 && !ktab) return set_error(B200Q_ERR_INVALID, "top conv: this filter size needs the gather table");
+  if (p.splits < 1 || !workspace) p.splits = 1;
+  p.k_per_split = p.splits > 1 ? ((p.K + p.splits - 1) / p.splits + TK - 1) / TK * TK : p.K;
+  if (p.splits > 1) p.splits = (p.K + p.k_per_split - 1) / p.k_per_split;
+  float* out = p.splits > 1 ? workspace : y;
+  if ((long long)p.groups * p.splits > 65535) return set_error(B200Q_ERR_UNSUPPORTED, "top conv: too many groups");
   // (64-channel tiles for the layers whose 128-channel grid does not fill the GPU were measured: no faster - those
-  // layers are bound by the length of their K loop, not by the number of blocks)
+  // layers are bound by the length of their K loop, which the K splits shorten)
   if (p.ocg > 64) {
-    dim3 grid((unsigned)ptiles, (unsigned)((p.ocg + 127) / 128), (unsigned)p.groups);
-    if (khw == 1) conv2d_f32_kernel<128, 1><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
-    else if (khw == 9) conv2d_f32_kernel<128, 9><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
-    else conv2d_f32_kernel<128, 0><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
+    dim3 grid((unsigned)ptiles, (unsigned)((p.ocg + 127) / 128), (unsigned)(p.groups * p.splits));
+    if (khw == 1) conv2d_f32_kernel<128, 1><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, out, p);
+    else if (khw == 9) conv2d_f32_kernel<128, 9><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, out, p);
+    else conv2d_f32_kernel<128, 0><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, out, p);
   } else {
-    dim3 grid((unsigned)ptiles, (unsigned)((p.ocg + 63) / 64), (unsigned)p.groups);
-    if (khw == 1) conv2d_f32_kernel<64, 1><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
-    else if (khw == 9) conv2d_f32_kernel<64, 9><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
-    else conv2d_f32_kernel<64, 0><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, y, p);
+    dim3 grid((unsigned)ptiles, (unsigned)((p.ocg + 63) / 64), (unsigned)(p.groups * p.splits));
+    if (khw == 1) conv2d_f32_kernel<64, 1><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, out, p);
+    else if (khw == 9) conv2d_f32_kernel<64, 9><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, out, p);
+    else conv2d_f32_kernel<64, 0><<<grid, CONV_THREADS, 0, s>>>(x, wt, ktab, bias, out, p);
   }
   CUDA_TRY(cudaGetLastError());
+  if (p.splits > 1) {
+    const long long count = P * p.oc;
+    const long long vecs = (count + 3) / 4;
+    splitk_reduce_kernel<<<(unsigned)((vecs + 255) / 256), 256, 0, s>>>(workspace, bias, y, count, p.splits, p.oc, p.oh * p.ow,
+                                                                        p.do_relu, p.relu_limit);
+    CUDA_TRY(cudaGetLastError());
+  }
   return B200Q_OK;
 }
 

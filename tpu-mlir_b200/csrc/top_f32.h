@@ -11,14 +11,19 @@ struct TopConvPlan {
   int K;          // icg * kh * kw
   int do_relu;
   float relu_limit;
+  int splits;       // K splits (1 = none); set by the caller from top_conv_splits, needs the workspace
+  int k_per_split;  // filled by top_conv_launch
 };
 
 // One-time: OIHW weight -> [groups][K][ocg], and the per-k gather table (K entries).
 int top_conv_prepare(const TopConvPlan& p, const float* w_oihw, float* wt, int2* ktab, cudaStream_t s);
 // y[n][oc][oh][ow] = relu(conv(x[n][ic][ih][iw]) + bias); wt / ktab from top_conv_prepare.  A matrix product
 // y[M][N] = x[M][K] * w[K][N] is the case ih = iw = kh = kw = 1 with wt = w and ktab = null.
+// p.splits > 1: `workspace` holds p.splits x (n * oc * oh * ow) floats; every split writes its partial sums there and a
+// second kernel adds them in split order (deterministic) with the bias and the ReLU.
 int top_conv_launch(const TopConvPlan& p, const float* x, const float* wt, const int2* ktab, const float* bias, float* y,
-                    cudaStream_t s);
+                    float* workspace, cudaStream_t s);
+int top_conv_splits(const TopConvPlan& p, int sms);
 int top_pool2d_launch(const float* x, float* y, long long nc, int ih, int iw, int oh, int ow, int kh, int kw, int sh, int sw,
                       int pht, int phb, int pwl, int pwr, bool is_max, bool count_include_pad, bool do_relu, float relu_limit,
                       cudaStream_t s);
