@@ -459,6 +459,29 @@ int b200q_top_pool2d_f32_dev(const float *x, float *y, int64_t nc, int32_t ih, i
 int b200q_top_add_f32_dev(const float *a, const float *b, float *y, int64_t count, int32_t do_relu, float relu_limit,
                           void *stream);
 int b200q_top_relu_f32_dev(const float *x, float *y, int64_t count, float relu_limit, void *stream);
+/* Elementwise float ops of the Top dialect (lib/Dialect/Top/Interfaces/<Op>.cpp), y = relu(op(a, b or const_val)):
+ * AddConst, SubConst (and its is_reverse form), MulConst, MaxConst, MinConst, Mul, Sub, Div (and reversed), Sigmoid (and its
+ * log form), SiLU, GELU, Floor.  Every expression is evaluated in the type the reference's C++ evaluates it in. */
+typedef enum {
+  B200Q_TOP_ADD_CONST = 0, B200Q_TOP_SUB_CONST, B200Q_TOP_RSUB_CONST, B200Q_TOP_MUL_CONST, B200Q_TOP_MAX_CONST, B200Q_TOP_MIN_CONST,
+  B200Q_TOP_MUL, B200Q_TOP_SUB, B200Q_TOP_RSUB, B200Q_TOP_DIV, B200Q_TOP_RDIV, B200Q_TOP_SIGMOID, B200Q_TOP_LOG_SIGMOID,
+  B200Q_TOP_SILU, B200Q_TOP_GELU, B200Q_TOP_FLOOR
+} b200q_top_eltwise_op;
+int b200q_top_eltwise_f32_dev(int32_t op, const float *a, const float *b, double const_val, float *y, int64_t count,
+                              int32_t do_relu, float relu_limit, void *stream);
+/* top::ScaleOp (Scale.cpp:19-44): y[o, c, i] = relu(x * scale[c] + bias[c]). */
+int b200q_top_scale_f32_dev(const float *x, const float *scale, const float *bias, float *y, int64_t outer, int32_t channels,
+                            int64_t inner, int32_t do_relu, float relu_limit, void *stream);
+/* Data movement of either dialect (Slice, Permute, Tile, Upsample, Pad, Concat) as one index mapping over up to six
+ * dimensions: walking dims[], the source coordinate of dimension d is ((i / div) % mod) * mul + off (mod 0: no wrap) and
+ * must lie in [0, extent) or the element becomes *pad_value (zero bytes if NULL); src / dst strides in elements,
+ * elem_bytes 1, 2 or 4.  Unused leading dimensions have dims = 1. */
+typedef struct {
+  int64_t dims[6], src_stride[6], mul[6], div[6], mod[6], off[6], extent[6], dst_stride[6];
+  int64_t dst_offset;
+} b200q_remap_desc;
+int b200q_remap_dev(const void *src, void *dst, int32_t elem_bytes, const b200q_remap_desc *desc, const void *pad_value,
+                    void *stream);
 /* The two array operations of the threshold tuner (python/calibration/simple_tunner.py): import_quant_bias (:43-50),
  * y = clip(round_half_even(x * 127 / threshold), -128, 127) * threshold / 127; and the sums behind calc_distance
  * (:334-358), ACCUMULATED into five device doubles: sum (ref - x)^2, sum |ref|, sum x * ref, sum x^2, sum ref^2. */

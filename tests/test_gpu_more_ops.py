@@ -1,0 +1,128 @@
+"""Further ops of the py_cuda set in the executor: the Top dialect's elementwise float ops and Scale, and the data-movement
+ops (Slice, Permute, Tile, Upsample, Pad, Concat, Squeeze, Unsqueeze) of both dialects, against numpy restatements of
+the reference's inference loops (lib/Dialect/Top/Interfaces/<Op>.cpp)."""
+import math
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from tpu_mlir_b200 import _lib as L  # noqa: E402
+from tpu_mlir_b200.module import module  # noqa: E402
+
+
+def run_graph(tensors, ops, weights, feeds, **kw):
+    g = dict(inputs=list(feeds), outputs=[ops[-1]["name"]], tensors=tensors, ops=ops, state="TOP_F32")
+    m = module(**kw)
+    m.load(g, weights)
+    for k, v in feeds.items():
+        m.set_tensor(k, v)
+    m.invoke(fixed_to_float=False)
+    return m
+
+
+def f32(shape):
+    return {"shape": list(shape), "dtype": "f32"}
+
+
+def test_top_elementwise_ops():
+    rng = np.random.default_rng(0)
+    x = (rng.standard_normal((2, 3, 5, 7)) * 3).astype(np.float32)
+    y2 = (rng.standard_normal((2, 3, 5, 7)) + 2.5).astype(np.float32)
+    sh = x.shape
+    ops = [dict(type="top.AddConst", name="addc", inputs=["x"], attrs=dict(const_val=1.7, do_relu=True, relu_limit=3.0)),
+           dict(type="top.SubConst", name="subc", inputs=["x"], attrs=dict(const_val=0.3)),
+           dict(type="top.SubConst", name="rsubc", inputs=["x"], attrs=dict(const_val=0.3, is_reverse=True)),
+           dict(type="top.MulConst", name="mulc", inputs=["x"], attrs=dict(const_val=0.1)),
+           dict(type="top.MaxConst", name="maxc", inputs=["x"], attrs=dict(const_val=-0.5)),
+           dict(type="top.MinConst", name="minc", inputs=["x"], attrs=dict(const_val=0.5)),
+           dict(type="top.Mul", name="mul", inputs=["x", "y"], attrs=dict(do_relu=True)),
+           dict(type="top.Sub", name="sub", inputs=["x", "y"], attrs={}),
+           dict(type="top.Sub", name="rsub", inputs=["x", "y"], attrs=dict(is_reverse=True)),
+           dict(type="top.Div", name="div", inputs=["x", "y"], attrs={}),
+           dict(type="top.Sigmoid", name="sig", inputs=["x"], attrs={}),
+           dict(type="top.Sigmoid", name="lsig", inputs=["x"], attrs=dict(log=True)),
+           dict(type="top.SiLU", name="silu", inputs=["x"], attrs={}),
+           dict(type="top.GELU", name="gelu", inputs=["x"], attrs={}),
+           dict(type="top.Floor", name="floor", inputs=["x"], attrs={}),
+           dict(type="top.Scale", name="scale", inputs=["x"], attrs=dict(do_relu=True))]
+    tensors = {"x": f32(sh), "y": f32(sh)}
+    tensors.update({o["name"]: f32(sh) for o in ops})
+    sc, bi = rng.standard_normal(3).astype(np.float32), rng.standard_normal(3).astype(np.float32)
+    m = run_graph(tensors, ops, {"scale_scale": sc, "scale_bias": bi}, {"x": x, "y": y2})
+    g = m.get_tensor
+    one = np.float32(1)
+    assert np.array_equal(g("addc"), np.clip(x + np.float32(1.7), 0, 3))
+    assert np.array_equal(g("subc"), x - np.float32(0.3))
+    assert np.array_equal(g("rsubc"), np.float32(0.3) - x)
+    assert np.array_equal(g("mulc"), (x.astype(np.float64) * 0.1).astype(np.float32))          # float * double, rounded once
+    assert np.array_equal(g("maxc"), np.maximum(x, np.float32(-0.5)))
+    assert np.array_equal(g("minc"), np.minimum(x, np.float32(0.5)))
+    assert np.array_equal(g("mul"), np.maximum(x * y2, 0))
+    assert np.array_equal(g("sub"), x - y2)
+    assert np.array_equal(g("rsub"), y2 - x)
+    assert np.array_equal(g("div"), x / y2)
+    sig = one / (one + np.exp(-x))
+    assert np.allclose(g("sig"), sig, rtol=3e-7, atol=1e-7)                                      # expf: a few ulps between libraries
+    assert np.allclose(g("lsig"), np.log(sig), rtol=1e-5, atol=1e-6)
+    assert np.allclose(g("silu"), x / (one + np.exp(-x)), rtol=3e-7, atol=1e-7)
+    gelu = np.array([0.5 * float(v) * (1.0 + math.erf(float(v) / math.sqrt(2.0))) for v in x.ravel()]).astype(np.float32).reshape(sh)
+    assert np.allclose(g("gelu"), gelu, rtol=1e-6, atol=1e-7)
+    assert np.array_equal(g("floor"), np.floor(x))
+    assert np.array_equal(g("scale"), np.maximum(x * sc.reshape(1, 3, 1, 1) + bi.reshape(1, 3, 1, 1), 0))
+
+
+def movement_ops(dt):
+    return [dict(type=f"{dt}.Slice", name="slice", inputs=["x"], attrs=dict(offset=[0, 1, 2, -5], steps=[1, 2, 1, 2])),
+            dict(type=f"{dt}.Permute", name="perm", inputs=["x"], attrs=dict(order=[0, 2, 3, 1])),
+            dict(type=f"{dt}.Tile", name="tile", inputs=["x"], attrs=dict(tile=[2, 1, 1, 3])),
+            dict(type=f"{dt}.Upsample", name="up", inputs=["x"], attrs=dict(scale_h=2, scale_w=3)),
+            dict(type=f"{dt}.Pad", name="pad", inputs=["x"], attrs=dict(paddings=[0, 1, 2, 0, 0, 0, 1, 3], val=-3.0, mode="constant")),
+            dict(type=f"{dt}.Pad", name="crop", inputs=["x"], attrs=dict(paddings=[0, 0, -1, 1, 0, -1, 0, 0], val=0.0)),
+            dict(type=f"{dt}.Concat", name="cat", inputs=["x", "perm2", "x"], attrs=dict(axis=1)),
+            dict(type=f"{dt}.Unsqueeze", name="unsq", inputs=["x"], attrs=dict(axes=[1])),
+            dict(type=f"{dt}.Squeeze", name="sq", inputs=["unsq"], attrs=dict(axes=[1]))]
+
+
+def movement_expect(x, p2):
+    return dict(slice=x[:, 1::2, 2:, 2::2], perm=np.transpose(x, (0, 2, 3, 1)), tile=np.tile(x, (2, 1, 1, 3)),
+                up=np.repeat(np.repeat(x, 2, axis=2), 3, axis=3),
+                pad=np.pad(x, ((0, 0), (1, 0), (2, 1), (0, 3)), constant_values=-3),
+                crop=np.pad(x[:, :-1, 1:, :], ((0, 0), (0, 0), (0, 0), (1, 0)), constant_values=0),
+                cat=np.concatenate([x, p2, x], axis=1), unsq=x[:, None], sq=x)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "i8"])
+def test_data_movement_ops(dtype):
+    rng = np.random.default_rng(1)
+    sh = (2, 4, 6, 7)
+    if dtype == "f32":
+        x = rng.standard_normal(sh).astype(np.float32)
+        p2 = rng.standard_normal((2, 3, 6, 7)).astype(np.float32)
+        dt = "top"
+    else:
+        x = rng.integers(-128, 128, sh).astype(np.int8)
+        p2 = rng.integers(-128, 128, (2, 3, 6, 7)).astype(np.int8)
+        dt = "tpu"
+    ops = movement_ops(dt)
+    want = movement_expect(x, p2)
+    ti = lambda shape: {"shape": list(shape), "dtype": dtype, "scale": 1.0, "zp": 0}  # noqa: E731
+    tensors = {"x": ti(sh), "perm2": ti(p2.shape)}
+    tensors.update({o["name"]: ti(want[o["name"]].shape) for o in ops})
+    m = run_graph(tensors, ops, {}, {"x": x, "perm2": p2})
+    for o in ops:
+        got = m.get_raw_tensor(o["name"])
+        assert got.shape == want[o["name"]].shape, o["name"]
+        assert np.array_equal(got, want[o["name"]].astype(got.dtype)), o["name"]
+
+
+def test_concat_relu_and_refusals():
+    x = np.random.default_rng(2).standard_normal((1, 2, 3, 3)).astype(np.float32)
+    ops = [dict(type="top.Concat", name="cat", inputs=["x", "x"], attrs=dict(axis=-3, do_relu=True, relu_limit=0.5))]
+    m = run_graph({"x": f32(x.shape), "cat": f32((1, 4, 3, 3))}, ops, {}, {"x": x})
+    assert np.array_equal(m.get_tensor("cat"), np.clip(np.concatenate([x, x], axis=1), 0, 0.5))
+    with pytest.raises(L.B200QError):
+        run_graph({"x": f32(x.shape), "p": f32((1, 2, 5, 5))}, [dict(type="top.Pad", name="p", inputs=["x"], attrs=dict(paddings=[0, 0, 1, 1, 0, 0, 1, 1], mode="reflect"))],
+                  {}, {"x": x})

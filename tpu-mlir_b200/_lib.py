@@ -67,6 +67,15 @@ class TopConvDesc(C.Structure):
                [("with_bias", C.c_int32), ("do_relu", C.c_int32), ("relu_limit", C.c_float)]
 
 
+class RemapDesc(C.Structure):
+    _fields_ = [(k, C.c_int64 * 6) for k in ("dims", "src_stride", "mul", "div", "mod", "off", "extent", "dst_stride")] + \
+               [("dst_offset", C.c_int64)]
+
+
+(TOP_ADD_CONST, TOP_SUB_CONST, TOP_RSUB_CONST, TOP_MUL_CONST, TOP_MAX_CONST, TOP_MIN_CONST, TOP_MUL, TOP_SUB, TOP_RSUB, TOP_DIV,
+ TOP_RDIV, TOP_SIGMOID, TOP_LOG_SIGMOID, TOP_SILU, TOP_GELU, TOP_FLOOR) = range(16)
+
+
 class RequantDesc(C.Structure):
     _fields_ = [("outer", C.c_int64), ("channels", C.c_int64), ("inner", C.c_int64), ("per_axis", C.c_int32),
                 ("quant_mode", C.c_int32), ("round_mode", C.c_int32), ("fuse_rq_axis", C.c_int32), ("in_zp", C.c_int32),
@@ -136,6 +145,9 @@ SIGNATURES = {
     "b200q_top_pool2d_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64] + [C.c_int32] * 13 + [C.c_float, C.c_void_p]),
     "b200q_top_add_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),
     "b200q_top_relu_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p]),
+    "b200q_top_eltwise_f32_dev": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_double, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),
+    "b200q_top_scale_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),
+    "b200q_remap_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(RemapDesc), C.c_void_p, C.c_void_p]),
     "b200q_top_fake_quant_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_double, C.c_void_p]),
     "b200q_top_distance_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200q_a16_w4_dev_dt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,

@@ -1,6 +1,8 @@
 // C ABI of the fp32 Top-dialect forward: the ops a calibration pass runs on the float graph.  A convolution handle
 // keeps the transposed weight and the gather table; the other ops are stateless device calls.  The operator face of
 // the convolution takes HOST float buffers like top::ConvOp::inference (lib/Dialect/Top/Interfaces/Conv.cpp:222-231).
+#include <string.h>
+
 #include <new>
 
 #include "../../include/b200q.h"
@@ -158,6 +160,26 @@ int b200q_top_add_f32_dev(const float* a, const float* b, float* y, int64_t coun
 int b200q_top_relu_f32_dev(const float* x, float* y, int64_t count, float relu_limit, void* stream) {
   if (!x || !y || count < 0) return set_error(B200Q_ERR_INVALID, "top_relu_f32_dev: bad argument");
   return top_add_launch(x, nullptr, y, count, true, relu_limit, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_top_eltwise_f32_dev(int32_t op, const float* a, const float* b, double const_val, float* y, int64_t count, int32_t do_relu,
+                              float relu_limit, void* stream) {
+  if (!a || !y || count < 0) return set_error(B200Q_ERR_INVALID, "top_eltwise_f32_dev: bad argument");
+  return top_eltwise_launch(op, a, b, const_val, y, count, do_relu != 0, relu_limit, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_top_scale_f32_dev(const float* x, const float* scale, const float* bias, float* y, int64_t outer, int32_t channels,
+                            int64_t inner, int32_t do_relu, float relu_limit, void* stream) {
+  if (!x || !scale || !y || outer < 0 || channels < 1 || inner < 1) return set_error(B200Q_ERR_INVALID, "top_scale_f32_dev: bad argument");
+  return top_scale_launch(x, scale, bias, y, outer, channels, inner, do_relu != 0, relu_limit, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_remap_dev(const void* src, void* dst, int32_t elem_bytes, const b200q_remap_desc* desc, const void* pad_value, void* stream) {
+  if (!src || !dst || !desc) return set_error(B200Q_ERR_INVALID, "remap_dev: null argument");
+  static_assert(sizeof(b200q_remap_desc) == sizeof(TopRemap), "the two descriptors must stay layout-compatible");
+  TopRemap m;
+  memcpy(&m, desc, sizeof(m));
+  return top_remap_launch(src, dst, elem_bytes, m, pad_value, static_cast<cudaStream_t>(stream));
 }
 
 int b200q_top_fake_quant_f32_dev(const float* x, float* y, int64_t count, double threshold, void* stream) {

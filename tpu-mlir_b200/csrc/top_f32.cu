@@ -15,6 +15,7 @@
 // addresses for a fixed k, so both the gather and the store run along the fast axis.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "internal.h"
 #include "top_f32.h"
@@ -345,7 +346,118 @@ __global__ void distance_f32_kernel(const float* __restrict__ x, const float* __
   }
 }
 
+// ---- elementwise float ops of the Top dialect (lib/Dialect/Top/Interfaces/<Op>.cpp, each op's inference loop): the
+// arithmetic type of every expression follows the reference's C++ (float unless a double constant promotes it)
+__global__ void eltwise_f32_kernel(int op, const float* __restrict__ a, const float* __restrict__ b, double cd,
+                                   float* __restrict__ y, long long n, int do_relu, float relu_limit) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float x = a[i];
+  const float c = (float)cd;
+  float v;
+  switch (op) {
+    case TOP_ADD_CONST: v = __fadd_rn(x, c); break;                                   // AddConst.cpp:26
+    case TOP_SUB_CONST: v = __fsub_rn(x, c); break;                                   // SubConst.cpp:31
+    case TOP_RSUB_CONST: v = __fsub_rn(c, x); break;                                  // SubConst.cpp:26 (is_reverse)
+    case TOP_MUL_CONST: v = (float)((double)x * cd); break;                           // MulConst.cpp:25: float * double
+    case TOP_MAX_CONST: v = fmaxf(x, c); break;                                       // MaxConst.cpp:26
+    case TOP_MIN_CONST: v = fminf(x, c); break;                                       // MinConst.cpp:26
+    case TOP_MUL: v = __fmul_rn(x, b[i]); break;
+    case TOP_SUB: v = __fsub_rn(x, b[i]); break;
+    case TOP_RSUB: v = __fsub_rn(b[i], x); break;
+    case TOP_DIV: v = __fdiv_rn(x, b[i]); break;
+    case TOP_RDIV: v = __fdiv_rn(b[i], x); break;
+    case TOP_SIGMOID: v = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-x))); break;            // Sigmoid.cpp:28
+    case TOP_LOG_SIGMOID: v = logf(__fdiv_rn(1.f, __fadd_rn(1.f, expf(-x)))); break;
+    case TOP_SILU: v = __fdiv_rn(x, __fadd_rn(1.f, expf(-x))); break;                 // SiLU.cpp:26
+    case TOP_GELU: v = (float)(0.5 * (double)x * (1.0 + erf((double)x / sqrt(2.0)))); break;   // GELU.cpp:24: double
+    case TOP_FLOOR: v = floorf(x); break;                                             // Floor.cpp:24
+    default: v = x;
+  }
+  y[i] = relu_f(v, do_relu, relu_limit);
+}
+
+// top::ScaleOp (Scale.cpp:19-44): y = x * scale[c] + bias[c], a multiply and an add (no fused multiply-add)
+__global__ void scale_f32_kernel(const float* __restrict__ x, const float* __restrict__ sc, const float* __restrict__ bi,
+                                 float* __restrict__ y, long long n, int channels, long long inner, int do_relu, float relu_limit) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int c = (int)((i / inner) % channels);
+  y[i] = relu_f(__fadd_rn(__fmul_rn(x[i], sc[c]), bi ? bi[c] : 0.f), do_relu, relu_limit);
+}
+
+// Data movement by index arithmetic (Slice, Permute, Tile, Upsample, Pad, Concat of either dialect): the output (or, for
+// Concat, one input's region of it) is walked in up to six dimensions; per dimension the source coordinate is
+// ((i / div) % mod) * mul + off (mod 0 = no wrap), valid inside [0, extent); an invalid coordinate writes the pad value.
+template <typename T>
+__global__ void remap_kernel(const T* __restrict__ src, T* __restrict__ dst, const TopRemap m, T pad, long long total) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  long long so = 0, dofs = m.dst_offset;
+  bool ok = true;
+#pragma unroll
+  for (int d = TOP_REMAP_DIMS - 1; d >= 0; --d) {
+    const long long dim = m.dims[d];
+    const long long id = i % dim;
+    i /= dim;
+    long long sidx = id / m.div[d];
+    if (m.mod[d] > 0) sidx %= m.mod[d];
+    sidx = sidx * m.mul[d] + m.off[d];
+    ok = ok && sidx >= 0 && sidx < m.extent[d];
+    so += sidx * m.src_stride[d];
+    dofs += id * m.dst_stride[d];
+  }
+  dst[dofs] = ok ? src[so] : pad;
+}
+
 }  // namespace
+
+int top_eltwise_launch(int op, const float* a, const float* b, double c, float* y, long long n, bool do_relu, float relu_limit,
+                       cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  if (op < 0 || op >= TOP_ELTWISE_OPS) return set_error(B200Q_ERR_INVALID, "top eltwise: unknown op %d", op);
+  const bool binary = op == TOP_MUL || op == TOP_SUB || op == TOP_RSUB || op == TOP_DIV || op == TOP_RDIV;
+  if (binary && !b) return set_error(B200Q_ERR_INVALID, "top eltwise: the op needs a second operand");
+  eltwise_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(op, a, b, c, y, n, do_relu ? 1 : 0, relu_limit);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_scale_launch(const float* x, const float* scale, const float* bias, float* y, long long outer, int channels, long long inner,
+                     bool do_relu, float relu_limit, cudaStream_t s) {
+  const long long n = outer * channels * inner;
+  if (n == 0) return B200Q_OK;
+  scale_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, scale, bias, y, n, channels, inner, do_relu ? 1 : 0, relu_limit);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_remap_launch(const void* src, void* dst, int elem_bytes, const TopRemap& m, const void* pad_value, cudaStream_t s) {
+  long long total = 1;
+  for (int d = 0; d < TOP_REMAP_DIMS; ++d) {
+    if (m.dims[d] < 0 || m.div[d] < 1 || m.mod[d] < 0) return set_error(B200Q_ERR_INVALID, "remap: bad dimension %d", d);
+    total *= m.dims[d];
+  }
+  if (total == 0) return B200Q_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (elem_bytes == 4) {
+    uint32_t pad = 0;
+    if (pad_value) memcpy(&pad, pad_value, 4);
+    remap_kernel<uint32_t><<<blocks, 256, 0, s>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), m, pad, total);
+  } else if (elem_bytes == 2) {
+    uint16_t pad = 0;
+    if (pad_value) memcpy(&pad, pad_value, 2);
+    remap_kernel<uint16_t><<<blocks, 256, 0, s>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), m, pad, total);
+  } else if (elem_bytes == 1) {
+    uint8_t pad = 0;
+    if (pad_value) memcpy(&pad, pad_value, 1);
+    remap_kernel<uint8_t><<<blocks, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), m, pad, total);
+  } else {
+    return set_error(B200Q_ERR_INVALID, "remap: element size %d", elem_bytes);
+  }
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
 
 int top_fake_quant_launch(const float* x, float* y, long long n, double threshold, cudaStream_t s) {
   if (n == 0) return B200Q_OK;

@@ -30,6 +30,21 @@ int top_pool2d_launch(const float* x, float* y, long long nc, int ih, int iw, in
 // y = relu(a + b); b may be null (plain ReLU)
 int top_add_launch(const float* a, const float* b, float* y, long long n, bool do_relu, float relu_limit, cudaStream_t s);
 
+// elementwise float ops (same numbering as b200q_top_eltwise_op in the C header)
+enum { TOP_ADD_CONST = 0, TOP_SUB_CONST, TOP_RSUB_CONST, TOP_MUL_CONST, TOP_MAX_CONST, TOP_MIN_CONST, TOP_MUL, TOP_SUB, TOP_RSUB,
+       TOP_DIV, TOP_RDIV, TOP_SIGMOID, TOP_LOG_SIGMOID, TOP_SILU, TOP_GELU, TOP_FLOOR, TOP_ELTWISE_OPS };
+int top_eltwise_launch(int op, const float* a, const float* b, double c, float* y, long long n, bool do_relu, float relu_limit,
+                       cudaStream_t s);
+int top_scale_launch(const float* x, const float* scale, const float* bias, float* y, long long outer, int channels, long long inner,
+                     bool do_relu, float relu_limit, cudaStream_t s);
+constexpr int TOP_REMAP_DIMS = 6;
+struct TopRemap {   // layout-compatible with b200q_remap_desc
+  long long dims[TOP_REMAP_DIMS], src_stride[TOP_REMAP_DIMS], mul[TOP_REMAP_DIMS], div[TOP_REMAP_DIMS], mod[TOP_REMAP_DIMS],
+      off[TOP_REMAP_DIMS], extent[TOP_REMAP_DIMS], dst_stride[TOP_REMAP_DIMS];
+  long long dst_offset;
+};
+int top_remap_launch(const void* src, void* dst, int elem_bytes, const TopRemap& m, const void* pad_value, cudaStream_t s);
+
 // y = clip(rint(x * 127 / threshold), -128, 127) * threshold / 127
 int top_fake_quant_launch(const float* x, float* y, long long n, double threshold, cudaStream_t s);
 // sums5 (device, accumulated into): sum (ref - x)^2, sum |ref|, sum x * ref, sum x^2, sum ref^2

@@ -34,6 +34,9 @@ _DT = {"i8": L.DT_I8, "u8": L.DT_U8, "i32": L.DT_I32, "f32": L.DT_F32}
 _QM = {"TFLite_LShift": 0, "TFLite": 1, "MultiplierShift": 2, "OnlyShift": 3, "QDM": 4, "OnlyScale": 5}
 
 
+_MOVE_OPS = ("Slice", "Permute", "Tile", "Upsample", "Pad", "Concat", "Squeeze", "Unsqueeze")
+
+
 def _P(t):
     return C.c_void_p(t.data_ptr()) if t is not None else None
 
@@ -193,6 +196,8 @@ class module:  # noqa: N801  (name of the reference class)
         iinfo = [self._info(n) for n in op["inputs"]]
         oinfo = self._info(op["name"])
         stream = lambda: C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)  # noqa: E731
+        if t.split(".", 1)[-1] in _MOVE_OPS:
+            return self._plan_move(op, stream)
         if t.startswith("top."):
             return self._plan_top(op, ins, out, iinfo, stream)
         if t == "tpu.Cast":
@@ -342,6 +347,107 @@ class module:  # noqa: N801  (name of the reference class)
             return lambda: out.copy_(ins[0].reshape(out.shape))
         raise L.B200QError(L.ERR_UNSUPPORTED, f"op type {t} is not implemented by the executor")
 
+    def _strides(self, name):
+        """Element strides of tensor `name` in its graph (NCHW) index order, whatever its storage order."""
+        shape = list(self._info(name)["shape"])
+        if name in self._nhwc:
+            n, c, h, w = shape
+            return [h * w * c, 1, w * c, c]
+        st, acc = [], 1
+        for d in reversed(shape):
+            st.insert(0, acc)
+            acc *= d
+        return st
+
+    def _plan_move(self, op, stream) -> Callable:
+        """Slice, Permute, Tile, Upsample, Pad, Concat, Squeeze, Unsqueeze of either dialect: pure data movement, one index
+        mapping kernel per input (lib/Dialect/Top/Interfaces/{Slice,Permute,Tile,Upsample,Pad,Concat}.cpp; the Tpu-dialect
+        ops move the stored values the same way)."""
+        t, a, lib = op["type"].split(".", 1)[-1], op.get("attrs", {}), self.lib
+        name, srcs = op["name"], op["inputs"]
+        out = self.tensors[name]
+        oshape = list(self._info(name)["shape"])
+        odt = self._info(name)["dtype"]
+        if name in self._nhwc:
+            raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: data-movement ops write NCHW tensors")
+        if any(self._info(sn)["dtype"] != odt for sn in srcs):
+            raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: {op['type']} moves values of one storage type")
+        if bool(a.get("do_relu", False)) and not (odt == "f32" and t in ("Upsample", "Concat")):
+            raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: do_relu on {op['type']} is implemented for f32 Upsample / Concat only")
+        ebytes = out.element_size()
+        ostr, acc = [], 1
+        for d in reversed(oshape):
+            ostr.insert(0, acc)
+            acc *= d
+
+        def desc(dims, sstr, mul, div, mod, off, ext, dstr, doff=0):
+            r = len(dims)
+            if r > 6:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: more than six dimensions")
+            padn = 6 - r
+            f = lambda v, fill: (C.c_int64 * 6)(*([fill] * padn + [int(x) for x in v]))  # noqa: E731
+            return L.RemapDesc(dims=f(dims, 1), src_stride=f(sstr, 0), mul=f(mul, 1), div=f(div, 1), mod=f(mod, 0), off=f(off, 0),
+                               extent=f(ext, 1), dst_stride=f(dstr, 0), dst_offset=int(doff))
+
+        runs = []
+        pad_buf = None
+        ishape = list(self._info(srcs[0])["shape"])
+        istr = self._strides(srcs[0])
+        r = len(oshape)
+        ones, zeros = [1] * r, [0] * r
+        if t in ("Squeeze", "Unsqueeze"):
+            src = self.tensors[srcs[0]]
+            if srcs[0] in self._nhwc:
+                return lambda: out.copy_(src.permute(0, 3, 1, 2).reshape(out.shape))
+            return lambda: out.copy_(src.reshape(out.shape))
+        if t == "Slice":
+            off = list(a.get("offset", zeros)) + [0] * (r - len(a.get("offset", zeros)))
+            steps = list(a.get("steps", ones)) + [1] * (r - len(a.get("steps", ones)))
+            off = [o + ishape[i] if o < 0 else o for i, o in enumerate(off)]
+            runs.append((srcs[0], desc(oshape, istr, steps, ones, zeros, off, ishape, ostr)))
+        elif t == "Permute":
+            order = list(a["order"])
+            runs.append((srcs[0], desc(oshape, [istr[o] for o in order], ones, ones, zeros, zeros, [ishape[o] for o in order], ostr)))
+        elif t == "Tile":
+            runs.append((srcs[0], desc(oshape, istr, ones, ones, ishape, zeros, ishape, ostr)))
+        elif t == "Upsample":
+            div = [1] * (r - 2) + [int(a.get("scale_h", 1)), int(a.get("scale_w", 1))]
+            runs.append((srcs[0], desc(oshape, istr, ones, div, zeros, zeros, ishape, ostr)))
+        elif t == "Pad":
+            if a.get("mode", "constant") != "constant":
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: Pad mode {a.get('mode')} is not implemented")
+            pads = list(a["paddings"])
+            if len(pads) != 2 * r:
+                raise L.B200QError(L.ERR_INVALID, f"{name}: paddings must hold 2 x rank values")
+            pad_buf = self.torch.tensor([a.get("val", 0.0)]).to(out.dtype).to(self.device)      # the pad value in the storage type
+            runs.append((srcs[0], desc(oshape, istr, ones, ones, zeros, [-p for p in pads[:r]], ishape, ostr)))
+        elif t == "Concat":
+            axis = int(a.get("axis", 1))
+            axis += r if axis < 0 else 0
+            if any(int(m) != 1 for m in a.get("multipliers", [])) or any(int(v) != 0 for v in a.get("rshifts", [])):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: Concat with per-input requantisation is not implemented")
+            at = 0
+            for sn in srcs:
+                sshape = list(self._info(sn)["shape"])
+                runs.append((sn, desc(sshape, self._strides(sn), ones, ones, zeros, zeros, sshape, ostr, at * ostr[axis])))
+                at += sshape[axis]
+        else:
+            raise L.B200QError(L.ERR_UNSUPPORTED, f"op type {op['type']} is not implemented by the executor")
+        self._keep.append((runs, pad_buf))
+        relu = bool(a.get("do_relu", False))
+        limit = float(a.get("relu_limit", -1.0))
+        pad_host = None
+        if pad_buf is not None:
+            pad_host = pad_buf.cpu().numpy().tobytes()
+            self._keep.append(pad_host)
+
+        def run():
+            for sn, d in runs:
+                L.check(lib.b200q_remap_dev(_P(self.tensors[sn]), _P(out), ebytes, C.byref(d), pad_host, stream()))
+            if relu:
+                L.check(lib.b200q_top_relu_f32_dev(_P(out), _P(out), out.numel(), limit, stream()))
+        return run
+
     def _plan_top(self, op, ins, out, iinfo, stream) -> Callable:
         """fp32 Top-dialect ops (the float graph a calibration pass and the threshold tuner run): top.Conv, top.MatMul,
         top.Add, top.MaxPool, top.AvgPool, top.Relu, top.Reshape, with the attribute names of TopOps.td."""
@@ -395,6 +501,31 @@ class module:  # noqa: N801  (name of the reference class)
             return lambda: L.check(lib.b200q_top_relu_f32_dev(_P(ins[0]), _P(out), n, limit, stream()))
         if t == "top.Reshape":
             return lambda: out.copy_(ins[0].reshape(out.shape))
+        n_el = out.numel()
+        const_ops = {"top.AddConst": L.TOP_ADD_CONST, "top.MulConst": L.TOP_MUL_CONST, "top.MaxConst": L.TOP_MAX_CONST,
+                     "top.MinConst": L.TOP_MIN_CONST}
+        if t in const_ops or t == "top.SubConst":
+            code = const_ops.get(t, L.TOP_RSUB_CONST if a.get("is_reverse", False) else L.TOP_SUB_CONST)
+            cv = float(a["const_val"])
+            return lambda: L.check(lib.b200q_top_eltwise_f32_dev(code, _P(ins[0]), None, cv, _P(out), n_el, relu, limit, stream()))
+        binary = {"top.Mul": (L.TOP_MUL, L.TOP_MUL), "top.Sub": (L.TOP_SUB, L.TOP_RSUB), "top.Div": (L.TOP_DIV, L.TOP_RDIV)}
+        if t in binary:
+            if len(ins) != 2 or tuple(iinfo[0]["shape"]) != tuple(iinfo[1]["shape"]):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: {t} takes two tensors of one shape here")
+            code = binary[t][1 if a.get("is_reverse", False) else 0]
+            return lambda: L.check(lib.b200q_top_eltwise_f32_dev(code, _P(ins[0]), _P(ins[1]), 0.0, _P(out), n_el, relu, limit, stream()))
+        unary = {"top.SiLU": L.TOP_SILU, "top.GELU": L.TOP_GELU, "top.Floor": L.TOP_FLOOR}
+        if t in unary or t == "top.Sigmoid":
+            code = unary.get(t, L.TOP_LOG_SIGMOID if a.get("log", False) else L.TOP_SIGMOID)
+            return lambda: L.check(lib.b200q_top_eltwise_f32_dev(code, _P(ins[0]), None, 0.0, _P(out), n_el, 0, -1.0, stream()))
+        if t == "top.Scale":
+            sc = self.weights[op["name"] + "_scale"].to(self.torch.float32).contiguous()
+            bi = self.weights[op["name"] + "_bias"].to(self.torch.float32).contiguous()
+            shape = list(iinfo[0]["shape"])
+            ch = shape[1]
+            inner = int(np.prod(shape[2:])) if len(shape) > 2 else 1
+            self._keep.append((sc, bi))
+            return lambda: L.check(lib.b200q_top_scale_f32_dev(_P(ins[0]), _P(sc), _P(bi), _P(out), shape[0], ch, inner, relu, limit, stream()))
         raise L.B200QError(L.ERR_UNSUPPORTED, f"op type {t} is not implemented by the executor")
 
     # ------------------------------------------------------------------ pymlir.module surface
