@@ -472,6 +472,12 @@ int b200q_top_eltwise_f32_dev(int32_t op, const float *a, const float *b, double
 /* top::ScaleOp (Scale.cpp:19-44): y[o, c, i] = relu(x * scale[c] + bias[c]). */
 int b200q_top_scale_f32_dev(const float *x, const float *scale, const float *bias, float *y, int64_t outer, int32_t channels,
                             int64_t inner, int32_t do_relu, float relu_limit, void *stream);
+/* top::SoftmaxOp (Softmax.cpp:53-80) over the middle dimension of [outer, channels, inner] (log_softmax when log_form), and
+ * top::LayerNormOp (LayerNorm.cpp:24-78) over rows of `inner` values with optional weight / bias of that length. */
+int b200q_top_softmax_f32_dev(const float *x, float *y, int64_t outer, int32_t channels, int64_t inner, int32_t log_form,
+                              void *stream);
+int b200q_top_layernorm_f32_dev(const float *x, const float *weight, const float *bias, float *y, int64_t outer,
+                                int64_t inner, float eps, void *stream);
 /* Data movement of either dialect (Slice, Permute, Tile, Upsample, Pad, Concat) as one index mapping over up to six
  * dimensions: walking dims[], the source coordinate of dimension d is ((i / div) % mod) * mul + off (mod 0: no wrap) and
  * must lie in [0, extent) or the element becomes *pad_value (zero bytes if NULL); src / dst strides in elements,

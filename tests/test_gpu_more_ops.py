@@ -126,3 +126,27 @@ def test_concat_relu_and_refusals():
     with pytest.raises(L.B200QError):
         run_graph({"x": f32(x.shape), "p": f32((1, 2, 5, 5))}, [dict(type="top.Pad", name="p", inputs=["x"], attrs=dict(paddings=[0, 0, 1, 1, 0, 0, 1, 1], mode="reflect"))],
                   {}, {"x": x})
+
+
+def test_softmax_and_layernorm():
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal((3, 10, 4, 5)) * 2).astype(np.float32)
+    w, b = rng.standard_normal(20).astype(np.float32), rng.standard_normal(20).astype(np.float32)
+    ops = [dict(type="top.Softmax", name="sm1", inputs=["x"], attrs=dict(axis=1)),
+           dict(type="top.Softmax", name="sm3", inputs=["x"], attrs=dict(axis=-1, log=True)),
+           dict(type="top.LayerNorm", name="ln", inputs=["x"], attrs=dict(axis=2, eps=1e-5)),
+           dict(type="top.LayerNorm", name="ln0", inputs=["x"], attrs=dict(axis=-1, eps=1e-3))]
+    tensors = {"x": f32(x.shape)}
+    tensors.update({o["name"]: f32(x.shape) for o in ops})
+    m = run_graph(tensors, ops, {"ln_weight": w, "ln_bias": b}, {"x": x})
+    x64 = x.astype(np.float64)
+    e = np.exp(x64 - x64.max(axis=1, keepdims=True))
+    assert np.allclose(m.get_tensor("sm1"), e / e.sum(axis=1, keepdims=True), rtol=1e-5, atol=1e-7)
+    d = x64 - x64.max(axis=-1, keepdims=True)
+    assert np.allclose(m.get_tensor("sm3"), d - np.log(np.exp(d).sum(axis=-1, keepdims=True)), rtol=1e-5, atol=1e-5)
+    r = x64.reshape(30, 20)
+    ln = (r - r.mean(axis=1, keepdims=True)) / np.sqrt(r.var(axis=1, keepdims=True) + 1e-5) * w + b
+    assert np.allclose(m.get_tensor("ln"), ln.reshape(x.shape), rtol=1e-4, atol=1e-5)
+    r = x64.reshape(120, 5)
+    ln0 = (r - r.mean(axis=1, keepdims=True)) / np.sqrt(r.var(axis=1, keepdims=True) + 1e-3)
+    assert np.allclose(m.get_tensor("ln0"), ln0.reshape(x.shape), rtol=1e-4, atol=1e-5)

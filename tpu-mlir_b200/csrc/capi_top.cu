@@ -174,6 +174,17 @@ int b200q_top_scale_f32_dev(const float* x, const float* scale, const float* bia
   return top_scale_launch(x, scale, bias, y, outer, channels, inner, do_relu != 0, relu_limit, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_top_softmax_f32_dev(const float* x, float* y, int64_t outer, int32_t channels, int64_t inner, int32_t log_form, void* stream) {
+  if (!x || !y || outer < 0 || channels < 0 || inner < 1) return set_error(B200Q_ERR_INVALID, "top_softmax_f32_dev: bad argument");
+  return top_softmax_launch(x, y, outer, channels, inner, log_form != 0, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_top_layernorm_f32_dev(const float* x, const float* weight, const float* bias, float* y, int64_t outer, int64_t inner, float eps,
+                                void* stream) {
+  if (!x || !y || outer < 0 || inner < 0) return set_error(B200Q_ERR_INVALID, "top_layernorm_f32_dev: bad argument");
+  return top_layernorm_launch(x, weight, bias, y, outer, inner, eps, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_remap_dev(const void* src, void* dst, int32_t elem_bytes, const b200q_remap_desc* desc, const void* pad_value, void* stream) {
   if (!src || !dst || !desc) return set_error(B200Q_ERR_INVALID, "remap_dev: null argument");
   static_assert(sizeof(b200q_remap_desc) == sizeof(TopRemap), "the two descriptors must stay layout-compatible");

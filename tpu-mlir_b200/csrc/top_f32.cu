@@ -386,6 +386,65 @@ __global__ void scale_f32_kernel(const float* __restrict__ x, const float* __res
   y[i] = relu_f(__fadd_rn(__fmul_rn(x[i], sc[c]), bi ? bi[c] : 0.f), do_relu, relu_limit);
 }
 
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float u = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, u) : v + u;
+  }
+  __syncthreads();   // the previous use of `sh` is over
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = sh[0];
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) r = is_max ? fmaxf(r, sh[w]) : r + sh[w];
+  return r;
+}
+
+// top::SoftmaxOp (Softmax.cpp:53-80, oneDNN softmax over the middle dimension of [outer, channels, inner]): one block per
+// (outer, inner) pair; the usual max-subtracted form, log_softmax when `log`.
+__global__ void softmax_f32_kernel(const float* __restrict__ x, float* __restrict__ y, int channels, long long inner, int log_form) {
+  __shared__ float sh[8];
+  const long long o = blockIdx.x / inner, i = blockIdx.x - o * inner;
+  const float* src = x + o * channels * inner + i;
+  float* dst = y + o * channels * inner + i;
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) mx = fmaxf(mx, src[(long long)c * inner]);
+  mx = block_reduce(mx, true, sh);
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) sum += expf(src[(long long)c * inner] - mx);
+  sum = block_reduce(sum, false, sh);
+  const float lsum = logf(sum);
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    const float d = src[(long long)c * inner] - mx;
+    dst[(long long)c * inner] = log_form ? d - lsum : expf(d) / sum;
+  }
+}
+
+// top::LayerNormOp (LayerNorm.cpp:24-78): per row of `inner` values mean, biased variance + eps, (x - mean) * rstd, then
+// the optional weight and bias of the normalised shape.  One block per row; the sums are tree reductions (the reference
+// adds sequentially: agreement to rounding).
+__global__ void layernorm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                     float* __restrict__ y, long long inner, float eps) {
+  __shared__ float sh[8];
+  const float* src = x + (long long)blockIdx.x * inner;
+  float* dst = y + (long long)blockIdx.x * inner;
+  float s = 0.f;
+  for (long long j = threadIdx.x; j < inner; j += blockDim.x) s += src[j];
+  const float mean = block_reduce(s, false, sh) / (float)inner;
+  float v = 0.f;
+  for (long long j = threadIdx.x; j < inner; j += blockDim.x) {
+    const float d = src[j] - mean;
+    v += d * d;
+  }
+  const float rstd = 1.0f / sqrtf(block_reduce(v, false, sh) / (float)inner + eps);
+  for (long long j = threadIdx.x; j < inner; j += blockDim.x) {
+    float r = __fmul_rn(src[j] - mean, rstd);
+    if (w) r = __fmul_rn(r, w[j]);
+    if (b) r = __fadd_rn(r, b[j]);
+    dst[j] = r;
+  }
+}
+
 // Data movement by index arithmetic (Slice, Permute, Tile, Upsample, Pad, Concat of either dialect): the output (or, for
 // Concat, one input's region of it) is walked in up to six dimensions; per dimension the source coordinate is
 // ((i / div) % mod) * mul + off (mod 0 = no wrap), valid inside [0, extent); an invalid coordinate writes the pad value.
@@ -428,6 +487,24 @@ int top_scale_launch(const float* x, const float* scale, const float* bias, floa
   const long long n = outer * channels * inner;
   if (n == 0) return B200Q_OK;
   scale_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, scale, bias, y, n, channels, inner, do_relu ? 1 : 0, relu_limit);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_softmax_launch(const float* x, float* y, long long outer, int channels, long long inner, bool log_form, cudaStream_t s) {
+  const long long rows = outer * inner;
+  if (rows == 0 || channels == 0) return B200Q_OK;
+  if (rows > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "softmax: too many rows");
+  softmax_f32_kernel<<<(unsigned)rows, 256, 0, s>>>(x, y, channels, inner, log_form ? 1 : 0);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_layernorm_launch(const float* x, const float* w, const float* b, float* y, long long outer, long long inner, float eps,
+                         cudaStream_t s) {
+  if (outer == 0 || inner == 0) return B200Q_OK;
+  if (outer > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "layernorm: too many rows");
+  layernorm_f32_kernel<<<(unsigned)outer, 256, 0, s>>>(x, w, b, y, inner, eps);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

@@ -37,6 +37,10 @@ int top_eltwise_launch(int op, const float* a, const float* b, double c, float* 
                        cudaStream_t s);
 int top_scale_launch(const float* x, const float* scale, const float* bias, float* y, long long outer, int channels, long long inner,
                      bool do_relu, float relu_limit, cudaStream_t s);
+// softmax over the middle dimension of [outer, channels, inner]; layer normalisation of rows of `inner` values
+int top_softmax_launch(const float* x, float* y, long long outer, int channels, long long inner, bool log_form, cudaStream_t s);
+int top_layernorm_launch(const float* x, const float* w, const float* b, float* y, long long outer, long long inner, float eps,
+                         cudaStream_t s);
 constexpr int TOP_REMAP_DIMS = 6;
 struct TopRemap {   // layout-compatible with b200q_remap_desc
   long long dims[TOP_REMAP_DIMS], src_stride[TOP_REMAP_DIMS], mul[TOP_REMAP_DIMS], div[TOP_REMAP_DIMS], mod[TOP_REMAP_DIMS],

@@ -518,6 +518,25 @@ class module:  # noqa: N801  (name of the reference class)
         if t in unary or t == "top.Sigmoid":
             code = unary.get(t, L.TOP_LOG_SIGMOID if a.get("log", False) else L.TOP_SIGMOID)
             return lambda: L.check(lib.b200q_top_eltwise_f32_dev(code, _P(ins[0]), None, 0.0, _P(out), n_el, 0, -1.0, stream()))
+        if t == "top.Softmax":
+            shape = list(iinfo[0]["shape"])
+            axis = int(a.get("axis", 1))
+            axis += len(shape) if axis < 0 else 0
+            outer, ch, inner = int(np.prod(shape[:axis])), shape[axis], int(np.prod(shape[axis + 1:]))
+            lg = int(bool(a.get("log", False)))
+            return lambda: L.check(lib.b200q_top_softmax_f32_dev(_P(ins[0]), _P(out), outer, ch, inner, lg, stream()))
+        if t == "top.LayerNorm":
+            shape = list(iinfo[0]["shape"])
+            axis = int(a.get("axis", -1))
+            axis += len(shape) if axis < 0 else 0
+            outer, inner = int(np.prod(shape[:axis])), int(np.prod(shape[axis:]))
+            w = self.weights.get(op["name"] + "_weight")
+            b = self.weights.get(op["name"] + "_bias")
+            w = w.to(self.torch.float32).contiguous() if w is not None else None
+            b = b.to(self.torch.float32).contiguous() if b is not None else None
+            eps = float(a.get("eps", 1e-5))
+            self._keep.append((w, b))
+            return lambda: L.check(lib.b200q_top_layernorm_f32_dev(_P(ins[0]), _P(w), _P(b), _P(out), outer, inner, eps, stream()))
         if t == "top.Scale":
             sc = self.weights[op["name"] + "_scale"].to(self.torch.float32).contiguous()
             bi = self.weights[op["name"] + "_bias"].to(self.torch.float32).contiguous()
