@@ -279,6 +279,11 @@ int b200q_lut_dev(const void *x, int64_t count, const void *table, int32_t table
 /* tpu.MulShift (MulShift.cpp:19-41): out = saturate(RSR((x - in_zp) * multiplier, rshift, half-up) + out_zp). */
 int b200q_mulshift_i8_dev(const void *x, int32_t dtype, int64_t count, int32_t multiplier, int32_t rshift,
                           int32_t in_zp, int32_t out_zp, int32_t out_dtype, void *out, void *stream);
+/* tpu.AddConst with a uniform-quantized output (lib/Dialect/Tpu/Interfaces/Common/AddConst.cpp:26-47):
+ * out = saturate(relu(RSR((x - in_zp) * multiplier + const_val, rshift, half-up))); with const_val = 0 and in_zp = 0 it is the
+ * symmetric tpu.MulConst (MulConst.cpp:50-62). */
+int b200q_addconst_i8_dev(const void *x, int32_t dtype, int64_t count, int32_t multiplier, double const_val, int32_t rshift,
+                          int32_t in_zp, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
 /* tpu.Mul, symmetric int8 operands of equal shape (Mul.cpp:23-29,:72-85): the op's ReLU acts on the product, then
  * out = saturate(RSR(product * multiplier, rshift, half-up)).  Broadcasting operands are not implemented. */
 int b200q_mul_i8_dev(const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t count,

@@ -150,3 +150,26 @@ def test_softmax_and_layernorm():
     r = x64.reshape(120, 5)
     ln0 = (r - r.mean(axis=1, keepdims=True)) / np.sqrt(r.var(axis=1, keepdims=True) + 1e-3)
     assert np.allclose(m.get_tensor("ln0"), ln0.reshape(x.shape), rtol=1e-4, atol=1e-5)
+
+
+def test_tpu_addconst_and_mulconst_int8():
+    """tpu.AddConst (AddConst.cpp:26-47) and the symmetric tpu.MulConst (MulConst.cpp:50-62) on int8 / uint8 tensors."""
+    rng = np.random.default_rng(4)
+    x = rng.integers(-128, 128, (3, 5, 7)).astype(np.int8)
+    ops = [dict(type="tpu.AddConst", name="ac", inputs=["x"], attrs=dict(multiplier=77, rshift=6, const_val=-300.0, do_relu=False)),
+           dict(type="tpu.AddConst", name="acr", inputs=["x"], attrs=dict(multiplier=5, rshift=0, const_val=17.0, do_relu=True)),
+           dict(type="tpu.MulConst", name="mc", inputs=["x"], attrs=dict(multiplier=-93, rshift=7, do_relu=True))]
+    tensors = {"x": {"shape": list(x.shape), "dtype": "i8", "scale": 1.0, "zp": 0}, "ac": {"shape": list(x.shape), "dtype": "i8", "scale": 1.0, "zp": 0},
+               "acr": {"shape": list(x.shape), "dtype": "u8", "scale": 1.0, "zp": 0}, "mc": {"shape": list(x.shape), "dtype": "u8", "scale": 1.0, "zp": 0}}
+    m = run_graph(tensors, ops, {}, {"x": x})
+
+    def rsr(v, s):
+        return (v + (1 << (s - 1))) >> s if s > 0 else v
+
+    xi = x.astype(np.int64)
+    ac = np.clip(np.vectorize(lambda v: rsr(int(v) * 77 - 300, 6))(xi), -128, 127)
+    acr = np.clip(np.maximum(np.vectorize(lambda v: rsr(int(v) * 5 + 17, 0))(xi), 0), 0, 255)
+    mc = np.clip(np.maximum(np.vectorize(lambda v: rsr(int(v) * -93, 7))(xi), 0), 0, 255)
+    assert np.array_equal(m.get_raw_tensor("ac").astype(np.int64), ac)
+    assert np.array_equal(m.get_raw_tensor("acr").astype(np.int64), acr)
+    assert np.array_equal(m.get_raw_tensor("mc").astype(np.int64), mc)

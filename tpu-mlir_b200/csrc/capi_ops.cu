@@ -924,6 +924,13 @@ int b200q_mulshift_i8_dev(const void* x, int32_t dtype, int64_t count, int32_t m
   return mulshift_i8_launch(x, dtype, count, multiplier, rshift, in_zp, out_zp, out_dtype, out, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_addconst_i8_dev(const void* x, int32_t dtype, int64_t count, int32_t multiplier, double const_val, int32_t rshift, int32_t in_zp,
+                          int32_t do_relu, int32_t out_dtype, void* out, void* stream) {
+  if (!x || !out || count < 0 || !is_q8(dtype) || rshift < 0 || rshift > 62)
+    return set_error(B200Q_ERR_INVALID, "addconst_i8_dev: bad argument");
+  return addconst_i8_launch(x, dtype, count, multiplier, const_val, rshift, in_zp, do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_mul_i8_dev(const void* a, int32_t a_dtype, const void* b, int32_t b_dtype, int64_t count, int32_t multiplier,
                      int32_t rshift, int32_t do_relu, int32_t out_dtype, void* out, void* stream) {
   if (!a || !b || !out || count < 0 || !is_q8(a_dtype) || !is_q8(b_dtype) || rshift < 0 || rshift > 62)

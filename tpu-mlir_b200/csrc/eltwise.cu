@@ -422,6 +422,20 @@ mulshift_i8_kernel(const void* __restrict__ x, int dt, long long n, int m, int s
   st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
 }
 
+// tpu.AddConst with a uniform-quantized output (AddConst.cpp:26-47): sum = (x - in_zp) * m; sum += const_val (a double,
+// truncated toward zero where applyMultiplierAndRShift takes it as an int64); out = saturate(relu(RSR(sum, s, half-up))).
+// With const_val = 0 and in_zp = 0 this is the symmetric tpu.MulConst (MulConst.cpp:50-62).
+__global__ void __launch_bounds__(256)
+addconst_i8_kernel(const void* __restrict__ x, int dt, long long n, int m, double const_val, int sft, int in_zp, int do_relu,
+                   int out_dt, void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const double sum = (double)((int64_t)(ld_q(x, i, dt) - in_zp) * m) + const_val;
+  int64_t v = rshift_round((int64_t)sum, sft, B200Q_ROUND_HALF_UP);
+  if (do_relu && v < 0) v = 0;
+  st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
+}
+
 // tpu.Mul, symmetric 8-bit tensors of equal shape (Mul.cpp:23-29,:72-85): the ReLU acts on the product, then
 // out = saturate(RSR(prod * m, s, half-up))
 __global__ void __launch_bounds__(256)
@@ -675,6 +689,14 @@ int lut_launch(const void* x, long long n, const void* table, int elem_size, voi
   } else {
     return set_error(B200Q_ERR_INVALID, "lut: table entries are 1, 2 or 4 bytes");
   }
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int addconst_i8_launch(const void* x, int dt, long long n, int m, double const_val, int sft, int in_zp, int do_relu, int out_dt,
+                       void* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  addconst_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(x, dt, n, m, const_val, sft, in_zp, do_relu, out_dt, out);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

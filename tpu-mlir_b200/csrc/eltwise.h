@@ -17,6 +17,8 @@ int pool2d_i8_launch(const void* x, int dt, int NC, int ih, int iw, int kh, int 
                      int pwl, int pwr, int mode, int multi, int rshift, int do_relu, int out_dt, void* out, cudaStream_t s);
 // tpu.Lut / tpu.MulShift / tpu.Mul (8-bit, equal shapes)
 int lut_launch(const void* x, long long n, const void* table, int elem_size, void* out, cudaStream_t s);
+int addconst_i8_launch(const void* x, int dt, long long n, int m, double const_val, int sft, int in_zp, int do_relu, int out_dt,
+                       void* out, cudaStream_t s);
 int mulshift_i8_launch(const void* x, int dt, long long n, int m, int sft, int in_zp, int out_zp, int out_dt, void* out,
                        cudaStream_t s);
 int mul_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n, int m, int sft, int do_relu, int out_dt,

@@ -333,6 +333,15 @@ class module:  # noqa: N801  (name of the reference class)
             return lambda: L.check(lib.b200q_mulshift_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], n, int(a["multiplier"]),
                                                              int(a["rshift"]), int(iinfo[0].get("zp", 0)),
                                                              int(oinfo.get("zp", 0)), _DT[oinfo["dtype"]], _P(out), stream()))
+        if t in ("tpu.AddConst", "tpu.MulConst"):
+            n = out.numel()
+            cv = float(a.get("const_val", 0.0)) if t == "tpu.AddConst" else 0.0
+            izp = int(iinfo[0].get("zp", 0)) if t == "tpu.AddConst" else 0
+            if t == "tpu.MulConst" and (int(iinfo[0].get("zp", 0)) != 0 or int(oinfo.get("zp", 0)) != 0):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: asymmetric tpu.MulConst is not implemented")
+            return lambda: L.check(lib.b200q_addconst_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], n, int(a["multiplier"]), cv,
+                                                             int(a["rshift"]), izp, int(bool(a.get("do_relu", False))),
+                                                             _DT[oinfo["dtype"]], _P(out), stream()))
         if t == "tpu.Mul":
             if tuple(iinfo[0]["shape"]) != tuple(iinfo[1]["shape"]):
                 raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.Mul with broadcasting is not implemented")
