@@ -14,6 +14,8 @@
 // columns.  Because a dot product does not care about the order of k, the activations are stored pre-permuted
 // to the nibble order the extraction yields.  The group scale multiplies the fp32 partial sum of each group,
 // so the only rounding is fp32 accumulation.  Every wait is bounded; a wait that runs out sets *status.
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -336,6 +338,233 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
 
 
 // ---------------------------------------------------------------------------------------------------------------
+// Resident form of the kernel above for shapes whose whole weight slice fits in shared memory (N = 11008, K = 4096 on
+// 148 SMs: five 16-row slabs of 35 KB per block).  The time of a decode call is the latency of its first bytes plus the
+// barriers between slabs, not its arithmetic, so here
+//   * the producer warp requests EVERY slab of the block at once when the kernel starts (no ring, no empty barriers):
+//     the HBM system has the block's whole slice in flight from the first microsecond;
+//   * a consumer warp keeps its activations (its 1/16 of K for its token) in registers, read once from global memory, so
+//     shared memory holds nothing but weights and the per-slab loop has no shared read of x;
+//   * the K parts of the 16 warps are combined once per slab at the END, when every slab's sums sit in registers: the
+//     per-slab barrier of the ring form, which serialised 4-chunk work items behind a 512-thread barrier, is gone from
+//     the part of the kernel that waits for memory.
+constexpr int RES_MAX_SLABS = 6;   // slabs a block may own
+constexpr int RES_MAX_CPW = 4;     // 64-k chunks per warp whose activations stay in registers (K <= 4096)
+
+struct ResidentPlan {
+  int gpr, scale_off, zp_off, stage_bytes, red_off, bar_off, total;
+};
+// red_planes: buffers of 16 warps x 128 partial sums for the final combination: one per slab (a single barrier) when
+// they fit, else two used in turn (a barrier per slab)
+__host__ __device__ inline ResidentPlan resident_plan(int K, int group, int slabs_per_block, int red_planes = 2) {
+  ResidentPlan p;
+  p.gpr = K / group;
+  p.scale_off = ROWS * (K / 2);
+  p.zp_off = p.scale_off + ((ROWS * p.gpr * 2 + 15) & ~15);
+  p.stage_bytes = (p.zp_off + ROWS * p.gpr + 127) & ~127;
+  p.red_off = slabs_per_block * p.stage_bytes;
+  p.bar_off = p.red_off + red_planes * CWARPS * ROWS * 8 * 4;
+  p.total = p.bar_off + 128;
+  return p;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+a16_w4_gemv_resident_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
+                            const __nv_bfloat16* __restrict__ scale, const uint8_t* __restrict__ zp,
+                            const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int M, int N, int K, int group,
+                            int slabs_per_block, int red_planes, int early_weights, int* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const ResidentPlan P = resident_plan(K, group, slabs_per_block, red_planes);
+  // Programmatic dependent launch: the next kernel of the stream may take an SM as soon as this block has left it; when
+  // the caller vouches that the weights are constant, this block requests them before it waits for its predecessor.
+  ptx::griddep_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t bar_base = ptx::smem_u32(smem + P.bar_off);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P.bar_off + 8 * RES_MAX_SLABS);
+  const int num_slabs = (N + ROWS - 1) / ROWS;
+  // this block's slabs: blockIdx.x, + gridDim.x, ...
+  int nsl = 0;
+  for (int sl = blockIdx.x; sl < num_slabs && nsl < slabs_per_block; sl += gridDim.x) ++nsl;
+
+  if (tid == 0) {
+    for (int s = 0; s < RES_MAX_SLABS; ++s) ptx::mbar_init(full_bar(s), 2);  // bulk-copy issue (with byte count) + metadata ready
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+  }
+  __syncthreads();
+
+  if (warp == CWARPS) {
+    // ---- producer: every slab at once
+    if (!early_weights) ptx::griddep_wait();
+    for (int s = 0; s < nsl; ++s) {
+      const int slab = blockIdx.x + s * gridDim.x;
+      uint8_t* st = smem + (size_t)s * P.stage_bytes;
+      const int n0 = slab * ROWS;
+      const int rows = min(ROWS, N - n0);
+      const int nmeta = rows * P.gpr;
+      const __nv_bfloat16* gs = scale + (size_t)n0 * P.gpr;
+      const uint8_t* gz = zp + (size_t)n0 * P.gpr;
+      __nv_bfloat16* ss = reinterpret_cast<__nv_bfloat16*>(st + P.scale_off);
+      uint8_t* sz = st + P.zp_off;
+      const bool meta_bulk = (nmeta % 16 == 0) && ((reinterpret_cast<uintptr_t>(gs) & 15) == 0) && ((reinterpret_cast<uintptr_t>(gz) & 15) == 0);
+      if (lane == 0) {
+        ptx::mbar_arrive_expect_tx(full_bar(s), (uint32_t)rows * (uint32_t)(K / 2) + (meta_bulk ? (uint32_t)nmeta * 3u : 0u));
+        ptx::bulk_load_1d(ptx::smem_u32(st), wq + (size_t)n0 * (K / 2), (uint32_t)rows * (uint32_t)(K / 2), full_bar(s));
+        if (meta_bulk) {
+          ptx::bulk_load_1d(ptx::smem_u32(ss), gs, (uint32_t)nmeta * 2u, full_bar(s));
+          ptx::bulk_load_1d(ptx::smem_u32(sz), gz, (uint32_t)nmeta, full_bar(s));
+        }
+      }
+      if (!meta_bulk) {  // ragged tail or unaligned metadata: plain loads
+        for (int i = lane; i < nmeta; i += 32) {
+          ss[i] = gs[i];
+          sz[i] = gz[i];
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(full_bar(s));  // second arrival: metadata is in place
+    }
+  } else {
+    // ------------------------------------------------------------ consumer warps
+    ptx::griddep_wait();   // activations are read and outputs written only after the predecessor has finished
+    const int g = lane >> 2, c = lane & 3;
+    const int chunks = K / CHUNK_K;
+    const int cpw = (chunks + CWARPS - 1) / CWARPS;   // <= RES_MAX_CPW (host)
+    const int ch_begin = min(warp * cpw, chunks), ch_end = min(chunks, ch_begin + cpw);
+    const int cpg = group / CHUNK_K;
+    // this lane's activations: token g, k in [64 ch + 16 c, + 16) of each of the warp's chunks, in nibble-pair order
+    uint4 xr[RES_MAX_CPW][2];
+#pragma unroll
+    for (int i = 0; i < RES_MAX_CPW; ++i) {
+      xr[i][0] = xr[i][1] = make_uint4(0, 0, 0, 0);
+      const int ch = ch_begin + i;
+      if (g < M && ch < ch_end) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)g * K + (size_t)ch * CHUNK_K + c * 16);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint4 v = __ldg(src + h);
+          xr[i][h].x = __byte_perm(v.x, v.z, 0x5410);  // (k0, k4)
+          xr[i][h].y = __byte_perm(v.x, v.z, 0x7632);  // (k1, k5)
+          xr[i][h].z = __byte_perm(v.y, v.w, 0x5410);  // (k2, k6)
+          xr[i][h].w = __byte_perm(v.y, v.w, 0x7632);  // (k3, k7)
+        }
+      }
+    }
+    float tot[RES_MAX_SLABS][4];
+#pragma unroll
+    for (int s = 0; s < RES_MAX_SLABS; ++s) tot[s][0] = tot[s][1] = tot[s][2] = tot[s][3] = 0.f;
+    bool ok = true;
+#pragma unroll
+    for (int s = 0; s < RES_MAX_SLABS; ++s) {
+      if (s >= nsl || !ok) continue;
+      if (!ptx::mbar_wait_bounded(full_bar(s), 0u, abort_flag, 2, WAIT_NS)) {
+        ok = false;
+        continue;
+      }
+      const uint8_t* st = smem + (size_t)s * P.stage_bytes;
+      const int n0 = (blockIdx.x + s * gridDim.x) * ROWS;
+      const int rows = min(ROWS, N - n0);
+      const int rl0 = min(g, rows - 1), rl1 = min(g + 8, rows - 1);
+      const uint8_t* w0p = st + (size_t)rl0 * (K / 2) + c * 8;
+      const uint8_t* w1p = st + (size_t)rl1 * (K / 2) + c * 8;
+      const __nv_bfloat16* sc0 = reinterpret_cast<const __nv_bfloat16*>(st + P.scale_off) + rl0 * P.gpr;
+      const __nv_bfloat16* sc1 = reinterpret_cast<const __nv_bfloat16*>(st + P.scale_off) + rl1 * P.gpr;
+      const uint8_t* zp0 = st + P.zp_off + rl0 * P.gpr;
+      const uint8_t* zp1 = st + P.zp_off + rl1 * P.gpr;
+      float acc[4][4] = {};
+      int grp = ch_begin / cpg, in_grp = ch_begin - grp * cpg;
+      uint32_t zc0 = __byte_perm((uint32_t)zp0[grp], 0x43u, 0x4040), zc1 = __byte_perm((uint32_t)zp1[grp], 0x43u, 0x4040);
+#pragma unroll
+      for (int i = 0; i < RES_MAX_CPW; ++i) {
+        const int ch = ch_begin + i;
+        if (ch >= ch_end) break;
+        const uint2 wa = *reinterpret_cast<const uint2*>(w0p + ch * 32);
+        const uint2 wb = *reinterpret_cast<const uint2*>(w1p + ch * 32);
+        const uint32_t wwa[2] = {wa.x, wa.y}, wwb[2] = {wb.x, wb.y};
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          const uint32_t a = wwa[w], b = wwb[w];
+          const uint32_t a4 = a >> 4, a8 = a >> 8, a12 = a >> 12;
+          const uint32_t b4 = b >> 4, b8 = b >> 8, b12 = b >> 12;
+          uint32_t a0 = sub_bf16x2((a & 0x000F000Fu) | 0x43004300u, zc0);
+          uint32_t a2 = sub_bf16x2((a4 & 0x000F000Fu) | 0x43004300u, zc0);
+          uint32_t a1 = sub_bf16x2((b & 0x000F000Fu) | 0x43004300u, zc1);
+          uint32_t a3 = sub_bf16x2((b4 & 0x000F000Fu) | 0x43004300u, zc1);
+          mma_bf16_16816(acc[2 * w], a0, a1, a2, a3, xr[i][w].x, xr[i][w].y);
+          a0 = sub_bf16x2((a8 & 0x000F000Fu) | 0x43004300u, zc0);
+          a2 = sub_bf16x2((a12 & 0x000F000Fu) | 0x43004300u, zc0);
+          a1 = sub_bf16x2((b8 & 0x000F000Fu) | 0x43004300u, zc1);
+          a3 = sub_bf16x2((b12 & 0x000F000Fu) | 0x43004300u, zc1);
+          mma_bf16_16816(acc[2 * w + 1], a0, a1, a2, a3, xr[i][w].z, xr[i][w].w);
+        }
+        if (++in_grp == cpg || ch + 1 == ch_end) {
+          const float s0 = __bfloat162float(sc0[grp]), s1 = __bfloat162float(sc1[grp]);
+          float sum4[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            sum4[j] = (acc[0][j] + acc[1][j]) + (acc[2][j] + acc[3][j]);
+            acc[0][j] = acc[1][j] = acc[2][j] = acc[3][j] = 0.f;
+          }
+          tot[s][0] = fmaf(sum4[0], s0, tot[s][0]);
+          tot[s][1] = fmaf(sum4[1], s0, tot[s][1]);
+          tot[s][2] = fmaf(sum4[2], s1, tot[s][2]);
+          tot[s][3] = fmaf(sum4[3], s1, tot[s][3]);
+          in_grp = 0;
+          ++grp;
+          if (ch + 1 < ch_end) {
+            zc0 = __byte_perm((uint32_t)zp0[grp], 0x43u, 0x4040);
+            zc1 = __byte_perm((uint32_t)zp1[grp], 0x43u, 0x4040);
+          }
+        }
+      }
+    }
+    // ---- combine the K parts of the warps
+    float* red = reinterpret_cast<float*>(smem + P.red_off);
+    constexpr int PLANE = CWARPS * ROWS * 8;
+    auto put = [&](int s, int plane) {
+      float* mine = red + (size_t)plane * PLANE + warp * (ROWS * 8);
+      mine[g * 8 + 2 * c] = tot[s][0];
+      mine[g * 8 + 2 * c + 1] = tot[s][1];
+      mine[(g + 8) * 8 + 2 * c] = tot[s][2];
+      mine[(g + 8) * 8 + 2 * c + 1] = tot[s][3];
+    };
+    auto finish = [&](int s, int plane, int e) {   // output e (row, token) of slab s
+      const int row = e >> 3, m = e & 7;
+      const int n = (blockIdx.x + s * gridDim.x) * ROWS + row;
+      if (n < N && m < M) {
+        const float* rb = red + (size_t)plane * PLANE + e;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < CWARPS; ++w) v += rb[w * (ROWS * 8)];
+        if (bias) v += bias[n];
+        y[(size_t)m * N + n] = __ushort_as_bfloat16(f32_to_bf16_bits_ref(v));
+      }
+    };
+    if (red_planes >= nsl) {   // one plane per slab: a single barrier, then all outputs at once
+#pragma unroll
+      for (int s = 0; s < RES_MAX_SLABS; ++s)
+        if (s < nsl) put(s, s);
+      asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory");
+      if (*abort_flag == 0)
+        for (int e = tid; e < nsl * ROWS * 8; e += CWARPS * 32) finish(e / (ROWS * 8), e / (ROWS * 8), e % (ROWS * 8));
+    } else {                   // two planes used in turn: one barrier per slab
+#pragma unroll
+      for (int s = 0; s < RES_MAX_SLABS; ++s) {
+        if (s >= nsl) continue;
+        put(s, s & 1);
+        asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory");
+        if (tid < ROWS * 8 && *abort_flag == 0) finish(s, s & 1, tid);
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0 && status != nullptr) atomicCAS(status, 0, *abort_flag);
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------
 // M <= 2: CUDA-core form, weights straight from global memory.  One or two tokens waste 7/8 of every MMA above, and
 // mma.sync is the slow legacy tensor path on sm_100, so for these shapes the dot products run as fp32 FMAs.
 //
@@ -617,6 +846,37 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
   // two tokens: the tensor-core decode kernel is the faster one where it applies (measured 14.3 us against 16.2 us at
   // N = 11008, K = 4096); the CUDA-core form then only takes what that kernel cannot (groups of 32, K % 64 != 0)
   const bool mma_ok = K % CHUNK_K == 0 && group >= CHUNK_K && group % CHUNK_K == 0 && gemv_plan(M, K, group, true).stages >= 2;
+  {
+    // the resident form: the block's whole weight slice in shared memory, activations in registers
+    const int slabs = (N + ROWS - 1) / ROWS;
+    const int blocks = slabs < sms ? slabs : sms;
+    const int spb = (slabs + blocks - 1) / blocks;
+    const int chunks = K / CHUNK_K;
+    // B200Q_GEMV_RESIDENT (A/B timing): 0 = never, 1 = two to eight tokens (default), 2 = one token too
+    static const int resident_mode = [] { const char* v = getenv("B200Q_GEMV_RESIDENT"); return v ? atoi(v) : 1; }();
+    if (resident_mode > 0 && (M > 1 || resident_mode > 1) && mma_ok && !f16 && spb <= RES_MAX_SLABS && (chunks + CWARPS - 1) / CWARPS <= RES_MAX_CPW) {
+      const int planes = resident_plan(K, group, spb, spb).total <= 226 * 1024 ? spb : 2;
+      const ResidentPlan RP = resident_plan(K, group, spb, planes);
+      if (RP.total <= 226 * 1024) {
+        auto rfn = a16_w4_gemv_resident_kernel;
+        CUDA_TRY(cudaFuncSetAttribute(rfn, cudaFuncAttributeMaxDynamicSharedMemorySize, RP.total));
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)blocks);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = (size_t)RP.total;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, rfn, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
+                                    static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp), bias,
+                                    static_cast<__nv_bfloat16*>(y), M, N, K, group, spb, planes, weights_constant ? 1 : 0, status));
+        return B200Q_OK;
+      }
+    }
+  }
   if (gemv_uses_fma(M, K, group) && (M == 1 || !mma_ok || f16)) {
     // warps per row: the smallest power of two that leaves a lane at most SL slices
     const int T = K / 32;
