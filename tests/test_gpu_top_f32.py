@@ -174,3 +174,32 @@ def test_conv_split_k_is_deterministic_and_matches():
     L.lib().b200q_top_conv2d_dev_destroy(C.byref(h))
     assert np.array_equal(outs[0], outs[1])
     assert np.all(np.abs(outs[0] - ref) <= conv_bound(x, w, pads=(1, 1, 1, 1)))
+
+
+def test_empty_and_invalid_arguments():
+    """Zero-sized work returns OK without launching; bad attributes and null pointers are reported, never computed."""
+    lib = L.lib()
+    y = torch.zeros(4, dtype=torch.float32, device="cuda")
+    assert lib.b200q_top_add_f32_dev(ptr(y), ptr(y), ptr(y), 0, 0, -1.0, None) == L.OK
+    assert lib.b200q_top_relu_f32_dev(ptr(y), ptr(y), 0, -1.0, None) == L.OK
+    assert lib.b200q_top_eltwise_f32_dev(L.TOP_GELU, ptr(y), None, 0.0, ptr(y), 0, 0, -1.0, None) == L.OK
+    assert lib.b200q_top_eltwise_f32_dev(99, ptr(y), None, 0.0, ptr(y), 4, 0, -1.0, None) == L.ERR_INVALID
+    assert lib.b200q_top_eltwise_f32_dev(L.TOP_MUL, ptr(y), None, 0.0, ptr(y), 4, 0, -1.0, None) == L.ERR_INVALID   # no second operand
+    assert lib.b200q_top_fake_quant_f32_dev(ptr(y), ptr(y), 4, 0.0, None) == L.ERR_INVALID                          # threshold must be positive
+    assert lib.b200q_top_pool2d_f32_dev(ptr(y), ptr(y), 1, 2, 2, 3, 3, 1, 1, 0, 0, 0, 0, 1, 0, 0, -1.0, None) == L.ERR_INVALID  # empty output
+    assert lib.b200q_top_matmul_f32_dev(ptr(y), ptr(y), None, ptr(y), 0, 2, 2, 0, -1.0, None) == L.OK
+    d = L.TopConvDesc(n=1, ic=3, ih=4, iw=4, oc=4, kh=5, kw=5, sh=1, sw=1, dh=1, dw=1, pht=0, phb=0, pwl=0, pwr=0, groups=1,
+                      with_bias=0, do_relu=0, relu_limit=-1.0)
+    h = C.c_void_p()
+    assert lib.b200q_top_conv2d_dev_create(C.byref(d), ptr(y), None, C.byref(h)) == L.ERR_INVALID                    # filter larger than the image
+    d2 = L.TopConvDesc(n=1, ic=3, ih=4, iw=4, oc=4, kh=1, kw=1, sh=1, sw=1, dh=1, dw=1, pht=0, phb=0, pwl=0, pwr=0, groups=2,
+                       with_bias=0, do_relu=0, relu_limit=-1.0)
+    assert lib.b200q_top_conv2d_dev_create(C.byref(d2), ptr(y), None, C.byref(h)) == L.ERR_INVALID                   # channels do not divide into groups
+    # a batch of zero images through a valid handle
+    d3 = L.TopConvDesc(n=1, ic=2, ih=3, iw=3, oc=2, kh=1, kw=1, sh=1, sw=1, dh=1, dw=1, pht=0, phb=0, pwl=0, pwr=0, groups=1,
+                       with_bias=0, do_relu=0, relu_limit=-1.0)
+    w = torch.ones(4, dtype=torch.float32, device="cuda")
+    L.check(lib.b200q_top_conv2d_dev_create(C.byref(d3), ptr(w), None, C.byref(h)))
+    assert lib.b200q_top_conv2d_dev_run(h, ptr(y), ptr(y), 0, None) == L.OK
+    lib.b200q_top_conv2d_dev_destroy(C.byref(h))
+    assert h.value is None
