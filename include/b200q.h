@@ -477,6 +477,10 @@ int b200q_top_eltwise_f32_dev(int32_t op, const float *a, const float *b, double
 /* top::ScaleOp (Scale.cpp:19-44): y[o, c, i] = relu(x * scale[c] + bias[c]). */
 int b200q_top_scale_f32_dev(const float *x, const float *scale, const float *bias, float *y, int64_t outer, int32_t channels,
                             int64_t inner, int32_t do_relu, float relu_limit, void *stream);
+/* top::ReduceOp over one run of adjacent axes (Reduce.cpp:59-108): x [outer, axis, inner] -> y [outer, inner]; mode 0 ReduceMean,
+ * 1 ReduceSum, 2 ReduceMax, 3 ReduceMin, 4 ReduceProd, 5 ReduceL2, 6 ReduceL1; sums run along the axis in order like the
+ * reference's loop. */
+int b200q_top_reduce_f32_dev(int32_t mode, const float *x, float *y, int64_t outer, int32_t axis, int64_t inner, void *stream);
 /* top::SoftmaxOp (Softmax.cpp:53-80) over the middle dimension of [outer, channels, inner] (log_softmax when log_form), and
  * top::LayerNormOp (LayerNorm.cpp:24-78) over rows of `inner` values with optional weight / bias of that length. */
 int b200q_top_softmax_f32_dev(const float *x, float *y, int64_t outer, int32_t channels, int64_t inner, int32_t log_form,

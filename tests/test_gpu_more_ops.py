@@ -173,3 +173,26 @@ def test_tpu_addconst_and_mulconst_int8():
     assert np.array_equal(m.get_raw_tensor("ac").astype(np.int64), ac)
     assert np.array_equal(m.get_raw_tensor("acr").astype(np.int64), acr)
     assert np.array_equal(m.get_raw_tensor("mc").astype(np.int64), mc)
+
+
+def test_reduce_and_tpu_relu():
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((2, 3, 4, 5)) + 0.5).astype(np.float32)
+    cases = [("ReduceMean", [2, 3]), ("ReduceSum", [1]), ("ReduceMax", [-1]), ("ReduceMin", [0, 1]), ("ReduceProd", [2]), ("ReduceL2", [3]), ("ReduceL1", [1, 2])]
+    ops, tensors = [], {"x": f32(x.shape)}
+    for i, (mode, axes) in enumerate(cases):
+        ax = [v % 4 for v in axes]
+        shape = [1 if d in ax else x.shape[d] for d in range(4)]
+        ops.append(dict(type="top.Reduce", name=f"r{i}", inputs=["x"], attrs=dict(mode=mode, axes=axes, keepdims=True)))
+        tensors[f"r{i}"] = f32(shape)
+    m = run_graph(tensors, ops, {}, {"x": x})
+    fns = dict(ReduceMean=np.mean, ReduceSum=np.sum, ReduceMax=np.max, ReduceMin=np.min, ReduceProd=np.prod,
+               ReduceL2=lambda v, axis, keepdims: np.sqrt(np.sum(v * v, axis=axis, keepdims=keepdims)),
+               ReduceL1=lambda v, axis, keepdims: np.sum(np.abs(v), axis=axis, keepdims=keepdims))
+    for i, (mode, axes) in enumerate(cases):
+        want = fns[mode](x.astype(np.float64), axis=tuple(v % 4 for v in axes), keepdims=True)
+        assert np.allclose(m.get_tensor(f"r{i}"), want, rtol=2e-6, atol=1e-6), mode
+    xi = rng.integers(-128, 128, (4, 9)).astype(np.int8)
+    t = {"x": {"shape": [4, 9], "dtype": "i8", "scale": 1.0, "zp": 0}, "r": {"shape": [4, 9], "dtype": "i8", "scale": 1.0, "zp": 0}}
+    m2 = run_graph(t, [dict(type="tpu.Relu", name="r", inputs=["x"], attrs={})], {}, {"x": xi})
+    assert np.array_equal(m2.get_raw_tensor("r"), np.maximum(xi, 0))

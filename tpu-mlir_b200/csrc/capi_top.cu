@@ -174,6 +174,11 @@ int b200q_top_scale_f32_dev(const float* x, const float* scale, const float* bia
   return top_scale_launch(x, scale, bias, y, outer, channels, inner, do_relu != 0, relu_limit, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_top_reduce_f32_dev(int32_t mode, const float* x, float* y, int64_t outer, int32_t axis, int64_t inner, void* stream) {
+  if (!x || !y || outer < 0 || inner < 0) return set_error(B200Q_ERR_INVALID, "top_reduce_f32_dev: bad argument");
+  return top_reduce_launch(mode, x, y, outer, axis, inner, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_top_softmax_f32_dev(const float* x, float* y, int64_t outer, int32_t channels, int64_t inner, int32_t log_form, void* stream) {
   if (!x || !y || outer < 0 || channels < 0 || inner < 1) return set_error(B200Q_ERR_INVALID, "top_softmax_f32_dev: bad argument");
   return top_softmax_launch(x, y, outer, channels, inner, log_form != 0, static_cast<cudaStream_t>(stream));

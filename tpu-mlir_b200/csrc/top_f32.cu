@@ -445,6 +445,37 @@ __global__ void layernorm_f32_kernel(const float* __restrict__ x, const float* _
   }
 }
 
+// top::ReduceOp over one run of adjacent axes (Reduce.cpp:59-108): [outer, axis, inner] -> [outer, inner].  One thread per
+// output walks the axis in order, as the reference's loop does (sequential float sums: the same rounding).
+__global__ void reduce_f32_kernel(int mode, const float* __restrict__ x, float* __restrict__ y, long long outer, int axis,
+                                  long long inner) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= outer * inner) return;
+  const long long o = i / inner, in = i - o * inner;
+  const float* src = x + o * axis * inner + in;
+  float v;
+  if (mode == TOP_REDUCE_MAX || mode == TOP_REDUCE_MIN || mode == TOP_REDUCE_PROD) {
+    v = src[0];
+    for (int a = 1; a < axis; ++a) {
+      const float u = src[(long long)a * inner];
+      if (mode == TOP_REDUCE_MAX) v = u > v ? u : v;
+      else if (mode == TOP_REDUCE_MIN) v = u < v ? u : v;
+      else v = __fmul_rn(v, u);
+    }
+  } else {
+    v = 0.f;
+    for (int a = 0; a < axis; ++a) {
+      const float u = src[(long long)a * inner];
+      if (mode == TOP_REDUCE_L2) v = __fadd_rn(v, (float)pow((double)u, 2.0));      // std::pow(float, int) computes in double
+      else if (mode == TOP_REDUCE_L1) v = __fadd_rn(v, fabsf(u));
+      else v = __fadd_rn(v, u);
+    }
+    if (mode == TOP_REDUCE_MEAN) v = __fdiv_rn(v, (float)axis);
+    if (mode == TOP_REDUCE_L2) v = (float)pow((double)v, 0.5);
+  }
+  y[i] = v;
+}
+
 // Data movement by index arithmetic (Slice, Permute, Tile, Upsample, Pad, Concat of either dialect): the output (or, for
 // Concat, one input's region of it) is walked in up to six dimensions; per dimension the source coordinate is
 // ((i / div) % mod) * mul + off (mod 0 = no wrap), valid inside [0, extent); an invalid coordinate writes the pad value.
@@ -487,6 +518,15 @@ int top_scale_launch(const float* x, const float* scale, const float* bias, floa
   const long long n = outer * channels * inner;
   if (n == 0) return B200Q_OK;
   scale_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, scale, bias, y, n, channels, inner, do_relu ? 1 : 0, relu_limit);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_reduce_launch(int mode, const float* x, float* y, long long outer, int axis, long long inner, cudaStream_t s) {
+  const long long n = outer * inner;
+  if (n == 0) return B200Q_OK;
+  if (mode < 0 || mode >= TOP_REDUCE_MODES || axis < 1) return set_error(B200Q_ERR_INVALID, "reduce: bad mode or empty axis");
+  reduce_f32_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(mode, x, y, outer, axis, inner);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

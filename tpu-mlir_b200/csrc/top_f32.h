@@ -37,6 +37,8 @@ int top_eltwise_launch(int op, const float* a, const float* b, double c, float* 
                        cudaStream_t s);
 int top_scale_launch(const float* x, const float* scale, const float* bias, float* y, long long outer, int channels, long long inner,
                      bool do_relu, float relu_limit, cudaStream_t s);
+enum { TOP_REDUCE_MEAN = 0, TOP_REDUCE_SUM, TOP_REDUCE_MAX, TOP_REDUCE_MIN, TOP_REDUCE_PROD, TOP_REDUCE_L2, TOP_REDUCE_L1, TOP_REDUCE_MODES };
+int top_reduce_launch(int mode, const float* x, float* y, long long outer, int axis, long long inner, cudaStream_t s);
 // softmax over the middle dimension of [outer, channels, inner]; layer normalisation of rows of `inner` values
 int top_softmax_launch(const float* x, float* y, long long outer, int channels, long long inner, bool log_form, cudaStream_t s);
 int top_layernorm_launch(const float* x, const float* w, const float* b, float* y, long long outer, long long inner, float eps,

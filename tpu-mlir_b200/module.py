@@ -333,6 +333,15 @@ class module:  # noqa: N801  (name of the reference class)
             return lambda: L.check(lib.b200q_mulshift_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], n, int(a["multiplier"]),
                                                              int(a["rshift"]), int(iinfo[0].get("zp", 0)),
                                                              int(oinfo.get("zp", 0)), _DT[oinfo["dtype"]], _P(out), stream()))
+        if t == "tpu.Relu":
+            if float(a.get("relu_limit", -1.0)) > 0:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.Relu with a limit is not implemented")
+            n = out.numel()
+            if iinfo[0]["dtype"] == "f32":
+                return lambda: L.check(lib.b200q_top_relu_f32_dev(_P(ins[0]), _P(out), n, -1.0, stream()))
+            # function_relu on integer storage (MathUtils.cpp:891-903): max(x, 0), saturated to the output type
+            return lambda: L.check(lib.b200q_addconst_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], n, 1, 0.0, 0, 0, 1,
+                                                             _DT[oinfo["dtype"]], _P(out), stream()))
         if t in ("tpu.AddConst", "tpu.MulConst"):
             n = out.numel()
             cv = float(a.get("const_val", 0.0)) if t == "tpu.AddConst" else 0.0
@@ -527,6 +536,16 @@ class module:  # noqa: N801  (name of the reference class)
         if t in unary or t == "top.Sigmoid":
             code = unary.get(t, L.TOP_LOG_SIGMOID if a.get("log", False) else L.TOP_SIGMOID)
             return lambda: L.check(lib.b200q_top_eltwise_f32_dev(code, _P(ins[0]), None, 0.0, _P(out), n_el, 0, -1.0, stream()))
+        if t == "top.Reduce":
+            modes = {"ReduceMean": 0, "ReduceSum": 1, "ReduceMax": 2, "ReduceMin": 3, "ReduceProd": 4, "ReduceL2": 5, "ReduceL1": 6}
+            shape = list(iinfo[0]["shape"])
+            axes = sorted(int(x) + (len(shape) if int(x) < 0 else 0) for x in a["axes"])
+            if a["mode"] not in modes or any(axes[i] + 1 != axes[i + 1] for i in range(len(axes) - 1)):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: top.Reduce over one run of adjacent axes only")
+            outer, ax = int(np.prod(shape[:axes[0]])), int(np.prod(shape[axes[0]:axes[-1] + 1]))
+            inner = int(np.prod(shape[axes[-1] + 1:]))
+            mode = modes[a["mode"]]
+            return lambda: L.check(lib.b200q_top_reduce_f32_dev(mode, _P(ins[0]), _P(out), outer, ax, inner, stream()))
         if t == "top.Softmax":
             shape = list(iinfo[0]["shape"])
             axis = int(a.get("axis", 1))
