@@ -362,8 +362,9 @@ void b200q_debug_set_wait_fault(int32_t extra_tx_bytes, int64_t budget_ns);
 int b200q_probe_tensor_peak(int32_t kind, int32_t pair, int32_t kblocks, int32_t launches, double *ms, double *ops,
                             void *stream);
 
-/* Which kernel serves b200q_a16_*, process-wide: 0 = chosen per call (default: up to 8 tokens take the CUDA-core
- * decode kernels; a handle that sees 64 tokens or more dequantises once into a bf16 copy and runs a bf16 GEMM;
+/* Which kernel serves b200q_a16_*, process-wide: 0 = chosen per call (default: up to 8 tokens take the
+ * decode kernels, and 9 to 16 tokens two launches of them where their shared-memory-resident form applies; a handle
+ * that sees 64 tokens or more dequantises once into a bf16 copy and runs a bf16 GEMM;
  * everything else takes the fused-dequantisation tensor-core kernel on the packed weights); 1 = the decode kernels
  * only (8 tokens per launch); 2 = the fused tensor-core kernel for every M; 3 = handle API with M > 8: the bf16 copy
  * (rounds the weight to bf16, which the reference does not); 4 = the warpgroup kernel (up to 32 tokens: every lane

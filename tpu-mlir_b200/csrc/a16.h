@@ -14,6 +14,9 @@ int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why, bool
 int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
                        int M, int N, int K, int group, int* status, cudaStream_t stream, bool weights_constant = false,
                        bool f16 = false);
+// Whether two to eight tokens of this shape run the resident form of the decode kernel (the faster one: then nine to
+// sixteen tokens are better served by two decode launches than by the fused tensor-core kernel).
+int a16_w4_gemv_resident_applies(int N, int K, int group, bool f16);
 // f16 = true: x, scale and y hold IEEE half values instead of bf16 (w4f16); the one-token kernel and the tensor-core
 // kernel have that form.
 

@@ -834,6 +834,19 @@ static int launch_direct(const void* x, const void* wq, const void* scale, const
   return B200Q_OK;
 }
 
+// Whether two to eight tokens of this shape take the resident form (the block's whole weight slice in shared memory).
+int a16_w4_gemv_resident_applies(int N, int K, int group, bool f16) {
+  if (f16 || K % CHUNK_K != 0 || group < CHUNK_K || group % CHUNK_K != 0 || K % group != 0) return 0;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) return 0;
+  const int slabs = (N + ROWS - 1) / ROWS;
+  const int blocks = slabs < sms ? slabs : sms;
+  const int spb = (slabs + blocks - 1) / blocks;
+  const int chunks = K / CHUNK_K;
+  if (spb > RES_MAX_SLABS || (chunks + CWARPS - 1) / CWARPS > RES_MAX_CPW) return 0;
+  return resident_plan(K, group, spb, 2).total <= 226 * 1024;
+}
+
 int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const void* zp, const float* bias, void* y,
                        int M, int N, int K, int group, int* status, cudaStream_t stream, bool weights_constant, bool f16) {
   const char* why = nullptr;
@@ -851,10 +864,9 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
     const int slabs = (N + ROWS - 1) / ROWS;
     const int blocks = slabs < sms ? slabs : sms;
     const int spb = (slabs + blocks - 1) / blocks;
-    const int chunks = K / CHUNK_K;
     // B200Q_GEMV_RESIDENT (A/B timing): 0 = never, 1 = two to eight tokens (default), 2 = one token too
     static const int resident_mode = [] { const char* v = getenv("B200Q_GEMV_RESIDENT"); return v ? atoi(v) : 1; }();
-    if (resident_mode > 0 && (M > 1 || resident_mode > 1) && mma_ok && !f16 && spb <= RES_MAX_SLABS && (chunks + CWARPS - 1) / CWARPS <= RES_MAX_CPW) {
+    if (resident_mode > 0 && (M > 1 || resident_mode > 1) && a16_w4_gemv_resident_applies(N, K, group, f16)) {
       const int planes = resident_plan(K, group, spb, spb).total <= 226 * 1024 ? spb : 2;
       const ResidentPlan RP = resident_plan(K, group, spb, planes);
       if (RP.total <= 226 * 1024) {

@@ -210,6 +210,11 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
       // at N = 11008, K = 4096: 16 / 32 tokens 29.7 us either way, 64 tokens 30.8 against 32-38 us, 128 tokens 33.4
       // against 46-53 us, 512 tokens 56 against 150 us).
       if (gemv_ok) break;
+      // 9 to 16 tokens: two launches of the resident decode kernel (23 us at N = 11008, K = 4096) beat the fused kernel
+      // (28.8 us); three launches (35 us at 24 tokens) do not
+      if (M <= 16 && a16_w4_gemv_resident_applies(N, K, group, f16) && a16_w4_gemv_supported(8, N, K, group, nullptr, f16) &&
+          a16_w4_gemv_supported((int)(M - 8), N, K, group, nullptr, f16))
+        break;
       if (resident_ok && M >= 64) use_resident = true;
       else use_umma = umma_ok;
   }
