@@ -225,7 +225,7 @@ def tensor_peaks(sustained=True):
     return out
 
 
-def kernel_lines(workload, steps, warmup, a16_m=(1, 2, 4, 8, 16, 128, 2048)):
+def kernel_lines(workload, steps, warmup, a16_m=(1, 2, 4, 8, 16, 32, 128, 2048)):
     """Single-kernel lines, device resident, each against its roofline (N=1 only)."""
     import torch
     import tpu_mlir_b200._lib as L
@@ -326,7 +326,9 @@ def kernel_lines(workload, steps, warmup, a16_m=(1, 2, 4, 8, 16, 128, 2048)):
                           frac=tf / peaks["bf16_tflops"], traffic=None, peak_basis=f"{peaks['source']} dense bf16 (burst)")
             # the two bounds cross where 2*M*N*K / bf16 peak = packed bytes / HBM peak: M ~ 33 for this layer
             bound_is_hbm = nbytes / (peaks["hbm_gbs"] * 1e9) >= 2.0 * M * 11008 * 4096 / (peaks["bf16_tflops"] * 1e12)
-            route = ("decode kernel (CUDA cores, packed weights read once)" if M <= 8 else
+            route = ("decode kernel (one token: CUDA cores, weights straight from global memory)" if M == 1 else
+                     "decode kernel, resident form (the block's weight slice in shared memory, mma.sync)" if M <= 8 else
+                     "two launches of the resident decode kernel (8 tokens each)" if M <= 16 else
                      "bf16 copy of the weight kept in the handle (90 MB) + bf16 tensor-core GEMM" if M >= 64 else
                      "fused kernel: packed weights by TMA, dequantised in registers into tensor memory, tcgen05 kind::f16")
             lines.append(dict(metric="A16MatMul w4bf16 " + ("GB/s" if bound_is_hbm else "TFLOP/s"),
@@ -741,7 +743,7 @@ def main():
                     help="conv = the benchmark contract (BASELINE config 1) with every other workload under `extras`; "
                          "any other value prints that workload's lines alone")
     ap.add_argument("--no-extras", action="store_true", help="headline only")
-    ap.add_argument("--a16-m", default="1,2,4,8,16,128,2048", help="token counts of --workload a16 (profiling runs pick one)")
+    ap.add_argument("--a16-m", default="1,2,4,8,16,32,128,2048", help="token counts of --workload a16 (profiling runs pick one)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU legs (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
