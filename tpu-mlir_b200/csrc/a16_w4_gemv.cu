@@ -184,9 +184,12 @@ __global__ void __launch_bounds__(THREADS, 1)
 a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
                    const __nv_bfloat16* __restrict__ scale, const uint8_t* __restrict__ zp,
                    const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int M, int N, int K, int group,
-                   int* __restrict__ status) {
+                   int early_weights, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t smem[];
   const GemvPlan P = gemv_plan(M, K, group);
+  // Programmatic dependent launch: the next kernel of the stream may take an SM as soon as this block has left it; when
+  // the caller vouches that the weights are constant, the producer requests them before waiting for the predecessor.
+  ptx::griddep_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t bar_base = ptx::smem_u32(smem + P.bar_off);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -207,9 +210,11 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
   __syncthreads();
 
   if (warp == CWARPS) {
+    if (!early_weights) ptx::griddep_wait();
     gemv_producer(smem, P, bar_base, abort_flag, wq, scale, zp, N, K, num_slabs, lane);
   } else {
     // ------------------------------------------------------------ consumer warps
+    ptx::griddep_wait();   // activations are read and outputs written only after the predecessor has finished
     uint8_t* xs = smem + P.x_off;
     // stage the activations once per block (bf16, 8 values per 16-byte move, permuted to nibble order)
     const int kv = K / 8;
@@ -914,10 +919,19 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
   const int blocks = slabs < sms ? slabs : sms;
   auto kfn = a16_w4_gemv_kernel;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, P.total));
-  kfn<<<blocks, THREADS, P.total, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
-                                            static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp),
-                                            bias, static_cast<__nv_bfloat16*>(y), M, N, K, group, status);
-  CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = (size_t)P.total;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, kfn, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
+                              static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp), bias,
+                              static_cast<__nv_bfloat16*>(y), M, N, K, group, weights_constant ? 1 : 0, status));
   return B200Q_OK;
 }
 
