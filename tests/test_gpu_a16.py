@@ -49,7 +49,11 @@ def test_llama_mlp_shape(M):
                                   dict(M=2, K=12288, N=20, g=256),
                                   # groups of 32, several slices per lane, rows fewer than row lanes
                                   dict(M=1, K=96, N=7, g=32), dict(M=2, K=160, N=9, g=32), dict(M=1, K=32768, N=5, g=128),
-                                  dict(M=2, K=20480, N=3, g=64), dict(M=1, K=4096, N=1200, g=64)])
+                                  dict(M=2, K=20480, N=3, g=64), dict(M=1, K=4096, N=1200, g=64),
+                                  # long rows: the activations of 3 to 8 tokens and two weight stages do not fit in shared memory,
+                                  # so K runs as two or three ranges whose fp32 partial sums meet in a workspace
+                                  dict(M=5, K=11008, N=130, g=64), dict(M=8, K=11008, N=4096, g=64), dict(M=8, K=12288, N=40, g=128),
+                                  dict(M=8, K=16512, N=33, g=64), dict(M=3, K=11008, N=17, g=128)])
 def test_small_and_ragged_shapes_with_bias(case):
     c = synth.a16_w4(seed=7, M=case["M"], K=case["K"], N=case["N"], group=case["g"])
     bias = np.random.default_rng(1).standard_normal(case["N"]).astype(np.float32)

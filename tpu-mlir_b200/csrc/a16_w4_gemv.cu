@@ -15,11 +15,15 @@
 // to the nibble order the extraction yields.  The group scale multiplies the fp32 partial sum of each group,
 // so the only rounding is fp32 accumulation.  Every wait is bounded; a wait that runs out sets *status.
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "a16.h"
+#include "devbuf.h"
 #include "internal.h"
 #include "ptx_sm100.cuh"
 #include "round16.cuh"
@@ -118,9 +122,12 @@ __host__ __device__ inline GemvPlan gemv_plan(int M, int K, int group, bool x_in
 
 // Producer warp of both decode kernels: streams 16-row weight slabs (one bulk copy each) plus the slab's scales
 // and zero points into the shared-memory ring, running ahead of the consumer warps.
+// K is the length of the k range this launch covers, starting at k0 of rows that are KT long (K = KT, k0 = 0: the whole
+// row; otherwise a slab's rows are 16 separate pieces, one bulk copy each, and its scales / zero points are gathered).
 __device__ __forceinline__ void gemv_producer(uint8_t* smem, const GemvPlan& P, uint32_t bar_base, volatile int* abort_flag,
                                               const uint8_t* __restrict__ wq, const __nv_bfloat16* __restrict__ scale,
-                                              const uint8_t* __restrict__ zp, int N, int K, int num_slabs, int lane) {
+                                              const uint8_t* __restrict__ zp, int N, int K, int num_slabs, int lane,
+                                              int KT, int k0, int group) {
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
   int stage = 0;
@@ -133,12 +140,51 @@ __device__ __forceinline__ void gemv_producer(uint8_t* smem, const GemvPlan& P, 
     uint8_t* st = smem + (size_t)stage * P.stage_bytes;
     const int n0 = slab * ROWS;
     const int rows = min(ROWS, N - n0);
+    __nv_bfloat16* ss = reinterpret_cast<__nv_bfloat16*>(st + P.scale_off);
+    uint8_t* sz = st + P.zp_off;
+    if (K != KT) {
+      // a k range of longer rows: one bulk copy per row piece, metadata gathered row by row
+      const int gprT = KT / group, g0 = k0 / group;
+      if (lane == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)rows * (uint32_t)(K / 2));
+      __syncwarp();
+      if (lane < rows)
+        ptx::bulk_load_1d(ptx::smem_u32(st + (size_t)lane * (K / 2)), wq + (size_t)(n0 + lane) * (KT / 2) + (k0 >> 1), (uint32_t)(K / 2),
+                          full_bar(stage));
+      const int nm = rows * P.gpr;
+      for (int i0 = 0; i0 < nm; i0 += 32 * 8) {   // eight loads in flight per lane before the first store
+        __nv_bfloat16 tv[8];
+        uint8_t tz[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = i0 + j * 32 + lane;
+          if (i < nm) {
+            const int r = i / P.gpr, g = i - r * P.gpr;
+            const size_t src = (size_t)(n0 + r) * gprT + g0 + g;
+            tv[j] = scale[src];
+            tz[j] = zp[src];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = i0 + j * 32 + lane;
+          if (i < nm) {
+            ss[i] = tv[j];
+            sz[i] = tz[j];
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(full_bar(stage));
+      if (++stage == P.stages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+      continue;
+    }
     // scales and zero points of the slab are contiguous in global memory (rows are adjacent)
     const int nmeta = rows * P.gpr;
     const __nv_bfloat16* gs = scale + (size_t)n0 * P.gpr;
     const uint8_t* gz = zp + (size_t)n0 * P.gpr;
-    __nv_bfloat16* ss = reinterpret_cast<__nv_bfloat16*>(st + P.scale_off);
-    uint8_t* sz = st + P.zp_off;
     const bool meta_bulk = (nmeta % 16 == 0) && ((reinterpret_cast<uintptr_t>(gs) & 15) == 0) &&
                            ((reinterpret_cast<uintptr_t>(gz) & 15) == 0);
     if (lane == 0) {
@@ -184,7 +230,9 @@ __global__ void __launch_bounds__(THREADS, 1)
 a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ wq,
                    const __nv_bfloat16* __restrict__ scale, const uint8_t* __restrict__ zp,
                    const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int M, int N, int K, int group,
-                   int early_weights, int* __restrict__ status) {
+                   int early_weights, int* __restrict__ status, int KT, int k_first, int pass_mode, float* __restrict__ ws) {
+  // K: the k range of this launch (k_first .. k_first + K of rows KT long).  pass_mode bit 0: add the partial sums in ws (an earlier
+  // range of k) first; bit 1: this is not the last range - leave the fp32 sums in ws instead of rounding them into y.
   extern __shared__ __align__(128) uint8_t smem[];
   const GemvPlan P = gemv_plan(M, K, group);
   // Programmatic dependent launch: the next kernel of the stream may take an SM as soon as this block has left it; when
@@ -211,7 +259,7 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
 
   if (warp == CWARPS) {
     if (!early_weights) ptx::griddep_wait();
-    gemv_producer(smem, P, bar_base, abort_flag, wq, scale, zp, N, K, num_slabs, lane);
+    gemv_producer(smem, P, bar_base, abort_flag, wq, scale, zp, N, K, num_slabs, lane, KT, k_first, group);
   } else {
     // ------------------------------------------------------------ consumer warps
     ptx::griddep_wait();   // activations are read and outputs written only after the predecessor has finished
@@ -220,7 +268,7 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
     const int kv = K / 8;
     for (int i = tid; i < M * kv; i += CWARPS * 32) {
       const int m = i / kv, k0 = (i - m * kv) * 8;
-      const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + k0);
+      const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * KT + k_first + k0);
       uint4 o;
       o.x = __byte_perm(v.x, v.z, 0x5410);  // (k0, k4)
       o.y = __byte_perm(v.x, v.z, 0x7632);  // (k1, k5)
@@ -331,8 +379,13 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
           float v = 0.f;
 #pragma unroll
           for (int w = 0; w < CWARPS; ++w) v += rb[w * (ROWS * 8)];
-          if (bias) v += bias[n];
-          y[(size_t)m * N + n] = __ushort_as_bfloat16(f32_to_bf16_bits_ref(v));
+          if (pass_mode & 1) v += ws[(size_t)m * N + n];
+          if (pass_mode & 2) {
+            ws[(size_t)m * N + n] = v;
+          } else {
+            if (bias) v += bias[n];
+            y[(size_t)m * N + n] = __ushort_as_bfloat16(f32_to_bf16_bits_ref(v));
+          }
         }
       }
     }
@@ -805,6 +858,19 @@ static bool gemv_uses_fma(int M, int K, int group) {
   return M <= 2 && K % 32 == 0 && group % 32 == 0 && K <= 32 * 32 * 16 * (M == 1 ? 4 : 2);
 }
 
+// In how many ranges of k the ring form runs M tokens: 1 when the activations and two weight stages fit in shared memory;
+// else the smallest split (2, 3, 4) of K into equal ranges of whole groups and 64-k chunks that fits (K = 11008: the
+// activations of 3 to 8 tokens need two); 0 if none does.
+static int gemv_passes(int M, int K, int group) {
+  for (int p = 1; p <= 4; ++p) {
+    if (K % p != 0) continue;
+    const int kl = K / p;
+    if (kl % CHUNK_K != 0 || kl % group != 0) continue;
+    if (gemv_plan(M, kl, group, true).stages >= 2) return p;
+  }
+  return 0;
+}
+
 int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why, bool f16) {
   const char* w = nullptr;
   if (M < 1 || M > MAX_M) w = "M must be in [1, 8]";
@@ -814,7 +880,7 @@ int a16_w4_gemv_supported(int M, int N, int K, int group, const char** why, bool
   else if (f16) w = "the f16 decode form exists for one or two tokens (K a multiple of 32, at most 65536 / 32768)";
   else if (K % CHUNK_K != 0) w = "K must be a multiple of 64";
   else if (group < CHUNK_K || group % CHUNK_K != 0) w = "group size must be a multiple of 64 dividing K";
-  else if (gemv_plan(M, K, group, true).stages < 2) w = "two 16-row weight slabs plus the activations do not fit in shared memory";
+  else if (gemv_passes(M, K, group) == 0) w = "two 16-row weight slabs plus the activations do not fit in shared memory";
   if (why) *why = w;
   return w == nullptr;
 }
@@ -863,7 +929,7 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
   CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   // two tokens: the tensor-core decode kernel is the faster one where it applies (measured 14.3 us against 16.2 us at
   // N = 11008, K = 4096); the CUDA-core form then only takes what that kernel cannot (groups of 32, K % 64 != 0)
-  const bool mma_ok = K % CHUNK_K == 0 && group >= CHUNK_K && group % CHUNK_K == 0 && gemv_plan(M, K, group, true).stages >= 2;
+  const bool mma_ok = K % CHUNK_K == 0 && group >= CHUNK_K && group % CHUNK_K == 0 && gemv_passes(M, K, group) > 0;
   {
     // the resident form: the block's whole weight slice in shared memory, activations in registers
     const int slabs = (N + ROWS - 1) / ROWS;
@@ -894,7 +960,7 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
       }
     }
   }
-  if (gemv_uses_fma(M, K, group) && (M == 1 || !mma_ok || f16)) {
+  if (gemv_uses_fma(M, K, group) && (M == 1 || !mma_ok || f16 || gemv_passes(M, K, group) > 1)) {
     // warps per row: the smallest power of two that leaves a lane at most SL slices
     const int T = K / 32;
     const int early = weights_constant ? 1 : 0;
@@ -913,25 +979,41 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
     if (sl == 1) return f16 ? launch_direct<2, 1, 6, 1, true>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream) : launch_direct<2, 1, 6, 1, false>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
     return f16 ? launch_direct<2, 2, 3, 1, true>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream) : launch_direct<2, 2, 3, 1, false>(x, wq, scale, zp, bias, y, N, K, group, wpr, sms, early, stream);
   }
-  const GemvPlan P = gemv_plan(M, K, group, true);
-  if (P.stages < 2) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: the weight slabs do not fit in shared memory");
+  const int passes = gemv_passes(M, K, group);
+  if (passes == 0) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: the weight slabs do not fit in shared memory");
+  const int kl = K / passes;
+  const GemvPlan P = gemv_plan(M, kl, group, true);
   const int slabs = (N + ROWS - 1) / ROWS;
   const int blocks = slabs < sms ? slabs : sms;
+  float* ws = nullptr;
+  if (passes > 1) {
+    // fp32 partial sums [M][N] between the ranges of k: one buffer per (device, stream), launches of a stream run in order
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, DevBuf> scratch;
+    std::lock_guard<std::mutex> lock(mu);
+    DevBuf& b = scratch[std::make_pair(dev, stream)];
+    B200Q_TRY(b.ensure((size_t)MAX_M * N * 4));
+    ws = b.as<float>();
+  }
   auto kfn = a16_w4_gemv_kernel;
   CUDA_TRY(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, P.total));
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)blocks);
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = (size_t)P.total;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  CUDA_TRY(cudaLaunchKernelEx(&cfg, kfn, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
-                              static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp), bias,
-                              static_cast<__nv_bfloat16*>(y), M, N, K, group, weights_constant ? 1 : 0, status));
+  for (int pass = 0; pass < passes; ++pass) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = (size_t)P.total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int mode = (pass > 0 ? 1 : 0) | (pass + 1 < passes ? 2 : 0);
+    CUDA_TRY(cudaLaunchKernelEx(&cfg, kfn, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(wq),
+                                static_cast<const __nv_bfloat16*>(scale), static_cast<const uint8_t*>(zp), bias,
+                                static_cast<__nv_bfloat16*>(y), M, N, kl, group, weights_constant ? 1 : 0, status, K, pass * kl, mode,
+                                ws));
+  }
   return B200Q_OK;
 }
 
