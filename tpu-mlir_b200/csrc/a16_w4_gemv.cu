@@ -101,10 +101,12 @@ struct GemvPlan {
   int x_off, red_off, bar_off, total;
   int stages;
 };
-__host__ __device__ inline GemvPlan gemv_plan(int M, int K, int group, bool x_in_smem = true) {
+// K: the k range a launch covers; KT: the length of the rows it is a part of (the scales and zero points of WHOLE rows are
+// staged - a slab's are contiguous in global memory only then - and indexed from the range's first group)
+__host__ __device__ inline GemvPlan gemv_plan(int M, int K, int group, bool x_in_smem = true, int KT = 0) {
   GemvPlan p;
   p.w_pitch = K / 2;  // dense: the slab is one contiguous piece of global memory and arrives as ONE bulk copy
-  p.gpr = K / group;
+  p.gpr = (KT > 0 ? KT : K) / group;
   p.scale_off = ROWS * p.w_pitch;
   p.zp_off = p.scale_off + ((ROWS * p.gpr * 2 + 15) & ~15);
   p.stage_bytes = (p.zp_off + ROWS * p.gpr + 127) & ~127;
@@ -123,7 +125,8 @@ __host__ __device__ inline GemvPlan gemv_plan(int M, int K, int group, bool x_in
 // Producer warp of both decode kernels: streams 16-row weight slabs (one bulk copy each) plus the slab's scales
 // and zero points into the shared-memory ring, running ahead of the consumer warps.
 // K is the length of the k range this launch covers, starting at k0 of rows that are KT long (K = KT, k0 = 0: the whole
-// row; otherwise a slab's rows are 16 separate pieces, one bulk copy each, and its scales / zero points are gathered).
+// row; otherwise a slab's rows are 16 separate pieces, one bulk copy each; the scales / zero points of the whole rows are
+// staged either way, contiguous in global memory).
 __device__ __forceinline__ void gemv_producer(uint8_t* smem, const GemvPlan& P, uint32_t bar_base, volatile int* abort_flag,
                                               const uint8_t* __restrict__ wq, const __nv_bfloat16* __restrict__ scale,
                                               const uint8_t* __restrict__ zp, int N, int K, int num_slabs, int lane,
@@ -142,45 +145,6 @@ __device__ __forceinline__ void gemv_producer(uint8_t* smem, const GemvPlan& P, 
     const int rows = min(ROWS, N - n0);
     __nv_bfloat16* ss = reinterpret_cast<__nv_bfloat16*>(st + P.scale_off);
     uint8_t* sz = st + P.zp_off;
-    if (K != KT) {
-      // a k range of longer rows: one bulk copy per row piece, metadata gathered row by row
-      const int gprT = KT / group, g0 = k0 / group;
-      if (lane == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)rows * (uint32_t)(K / 2));
-      __syncwarp();
-      if (lane < rows)
-        ptx::bulk_load_1d(ptx::smem_u32(st + (size_t)lane * (K / 2)), wq + (size_t)(n0 + lane) * (KT / 2) + (k0 >> 1), (uint32_t)(K / 2),
-                          full_bar(stage));
-      const int nm = rows * P.gpr;
-      for (int i0 = 0; i0 < nm; i0 += 32 * 8) {   // eight loads in flight per lane before the first store
-        __nv_bfloat16 tv[8];
-        uint8_t tz[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int i = i0 + j * 32 + lane;
-          if (i < nm) {
-            const int r = i / P.gpr, g = i - r * P.gpr;
-            const size_t src = (size_t)(n0 + r) * gprT + g0 + g;
-            tv[j] = scale[src];
-            tz[j] = zp[src];
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int i = i0 + j * 32 + lane;
-          if (i < nm) {
-            ss[i] = tv[j];
-            sz[i] = tz[j];
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(full_bar(stage));
-      if (++stage == P.stages) {
-        stage = 0;
-        phase ^= 1u;
-      }
-      continue;
-    }
     // scales and zero points of the slab are contiguous in global memory (rows are adjacent)
     const int nmeta = rows * P.gpr;
     const __nv_bfloat16* gs = scale + (size_t)n0 * P.gpr;
@@ -189,11 +153,17 @@ __device__ __forceinline__ void gemv_producer(uint8_t* smem, const GemvPlan& P, 
                            ((reinterpret_cast<uintptr_t>(gz) & 15) == 0);
     if (lane == 0) {
       ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)rows * (uint32_t)(K / 2) + (meta_bulk ? (uint32_t)nmeta * 3u : 0u));
-      ptx::bulk_load_1d(ptx::smem_u32(st), wq + (size_t)n0 * (K / 2), (uint32_t)rows * (uint32_t)(K / 2), full_bar(stage));
+      if (K == KT) ptx::bulk_load_1d(ptx::smem_u32(st), wq + (size_t)n0 * (K / 2), (uint32_t)rows * (uint32_t)(K / 2), full_bar(stage));
       if (meta_bulk) {
         ptx::bulk_load_1d(ptx::smem_u32(ss), gs, (uint32_t)nmeta * 2u, full_bar(stage));
         ptx::bulk_load_1d(ptx::smem_u32(sz), gz, (uint32_t)nmeta, full_bar(stage));
       }
+    }
+    if (K != KT) {   // a k range of longer rows: one bulk copy per row piece (the byte count is registered above)
+      __syncwarp();
+      if (lane < rows)
+        ptx::bulk_load_1d(ptx::smem_u32(st + (size_t)lane * (K / 2)), wq + (size_t)(n0 + lane) * (KT / 2) + (k0 >> 1), (uint32_t)(K / 2),
+                          full_bar(stage));
     }
     if (!meta_bulk) {  // ragged tail or unaligned metadata: plain loads, all issued before the stores
       for (int i0 = 0; i0 < nmeta; i0 += 32 * 8) {
@@ -234,7 +204,8 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
   // K: the k range of this launch (k_first .. k_first + K of rows KT long).  pass_mode bit 0: add the partial sums in ws (an earlier
   // range of k) first; bit 1: this is not the last range - leave the fp32 sums in ws instead of rounding them into y.
   extern __shared__ __align__(128) uint8_t smem[];
-  const GemvPlan P = gemv_plan(M, K, group);
+  const GemvPlan P = gemv_plan(M, K, group, true, KT);
+  const int g_first = k_first / group;   // the staged metadata covers whole rows
   // Programmatic dependent launch: the next kernel of the stream may take an SM as soon as this block has left it; when
   // the caller vouches that the weights are constant, the producer requests them before waiting for the predecessor.
   ptx::griddep_launch_dependents();
@@ -304,6 +275,7 @@ a16_w4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restric
       float tot[4] = {0.f, 0.f, 0.f, 0.f};
       float acc[4][4] = {};  // one accumulator per k-step of a chunk: four independent MMA chains
       int grp = ch_begin / cpg, in_grp = ch_begin - grp * cpg;
+      grp += g_first;
       uint32_t z0 = zp0[grp], z1 = zp1[grp];
       uint32_t zc0 = __byte_perm(z0, 0x43u, 0x4040), zc1 = __byte_perm(z1, 0x43u, 0x4040);  // bf16x2 (128 + zp)
 #pragma unroll 4
@@ -866,7 +838,7 @@ static int gemv_passes(int M, int K, int group) {
     if (K % p != 0) continue;
     const int kl = K / p;
     if (kl % CHUNK_K != 0 || kl % group != 0) continue;
-    if (gemv_plan(M, kl, group, true).stages >= 2) return p;
+    if (gemv_plan(M, kl, group, true, K).stages >= 2) return p;
   }
   return 0;
 }
@@ -960,7 +932,7 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
       }
     }
   }
-  if (gemv_uses_fma(M, K, group) && (M == 1 || !mma_ok || f16 || gemv_passes(M, K, group) > 1)) {
+  if (gemv_uses_fma(M, K, group) && (M == 1 || !mma_ok || f16)) {
     // warps per row: the smallest power of two that leaves a lane at most SL slices
     const int T = K / 32;
     const int early = weights_constant ? 1 : 0;
@@ -982,7 +954,7 @@ int a16_w4_gemv_launch(const void* x, const void* wq, const void* scale, const v
   const int passes = gemv_passes(M, K, group);
   if (passes == 0) return set_error(B200Q_ERR_UNSUPPORTED, "a16 w4 gemv: the weight slabs do not fit in shared memory");
   const int kl = K / passes;
-  const GemvPlan P = gemv_plan(M, kl, group, true);
+  const GemvPlan P = gemv_plan(M, kl, group, true, K);
   const int slabs = (N + ROWS - 1) / ROWS;
   const int blocks = slabs < sms ? slabs : sms;
   float* ws = nullptr;
