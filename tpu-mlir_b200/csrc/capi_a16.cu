@@ -212,8 +212,10 @@ int a16_dispatch(const void* x, const void* wq, const void* scale, const void* z
       if (gemv_ok) break;
       // 9 to 16 tokens: two launches of the resident decode kernel (23 us at N = 11008, K = 4096) beat the fused kernel
       // (28.8 us); three launches (35 us at 24 tokens) do not
-      if (M <= 16 && a16_w4_gemv_resident_applies(N, K, group, f16) && a16_w4_gemv_supported(8, N, K, group, nullptr, f16) &&
-          a16_w4_gemv_supported((int)(M - 8), N, K, group, nullptr, f16))
+      // (the same holds for long rows, K >= 8192, where the fused kernel's time grows with K: 53 us and more against
+      // decode launches of about 18 us each: up to three of them win at K = 11008)
+      if (!f16 && ((M <= 16 && a16_w4_gemv_resident_applies(N, K, group, f16)) || (M <= 24 && K >= 8192)) &&
+          a16_w4_gemv_supported(8, N, K, group, nullptr, f16) && a16_w4_gemv_supported((int)(M % 8 ? M % 8 : 8), N, K, group, nullptr, f16))
         break;
       if (resident_ok && M >= 64) use_resident = true;
       else use_umma = umma_ok;
