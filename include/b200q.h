@@ -475,11 +475,17 @@ typedef enum {
 } b200q_top_eltwise_op;
 int b200q_top_eltwise_f32_dev(int32_t op, const float *a, const float *b, double const_val, float *y, int64_t count,
                               int32_t do_relu, float relu_limit, void *stream);
+/* tpu::ActiveOp on float tensors (lib/Dialect/Tpu/Interfaces/Common/Active.cpp:20-32 with the function table of
+ * lib/Support/ActiveUtils.cpp:66-181): y = (float)func((double)x).  `mode` is the dialect's ActiveMode number (TANH 0 ... QGELU
+ * 37); coeff0 / coeff1 are the op's `coeffs` (ELU alpha; SWISH beta; HSIGMOID beta, alpha).  Modes without a function in the
+ * reference's table (RELU, IS_FINITE, ARCSIN, ARCSINH, ARCCOSH) return B200Q_ERR_UNSUPPORTED. */
+int b200q_active_f32_dev(int32_t mode, const float *x, double coeff0, double coeff1, float *y, int64_t count, void *stream);
 /* top::ScaleOp (Scale.cpp:19-44): y[o, c, i] = relu(x * scale[c] + bias[c]). */
 int b200q_top_scale_f32_dev(const float *x, const float *scale, const float *bias, float *y, int64_t outer, int32_t channels,
                             int64_t inner, int32_t do_relu, float relu_limit, void *stream);
 /* top::ReduceOp over one run of adjacent axes (Reduce.cpp:59-108): x [outer, axis, inner] -> y [outer, inner]; mode 0 ReduceMean,
- * 1 ReduceSum, 2 ReduceMax, 3 ReduceMin, 4 ReduceProd, 5 ReduceL2, 6 ReduceL1; sums run along the axis in order like the
+ * 1 ReduceSum, 2 ReduceMax, 3 ReduceMin, 4 ReduceProd, 5 ReduceL2, 6 ReduceL1, 7 the mean of tpu::ReduceOp (the sum times
+ * float(1.0 / axis), lib/Dialect/Tpu/Interfaces/Common/Reduce.cpp:132-138); sums run along the axis in order like the
  * reference's loop. */
 int b200q_top_reduce_f32_dev(int32_t mode, const float *x, float *y, int64_t outer, int32_t axis, int64_t inner, void *stream);
 /* top::SoftmaxOp (Softmax.cpp:53-80) over the middle dimension of [outer, channels, inner] (log_softmax when log_form), and

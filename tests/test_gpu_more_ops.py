@@ -196,3 +196,137 @@ def test_reduce_and_tpu_relu():
     t = {"x": {"shape": [4, 9], "dtype": "i8", "scale": 1.0, "zp": 0}, "r": {"shape": [4, 9], "dtype": "i8", "scale": 1.0, "zp": 0}}
     m2 = run_graph(t, [dict(type="tpu.Relu", name="r", inputs=["x"], attrs={})], {}, {"x": xi})
     assert np.array_equal(m2.get_raw_tensor("r"), np.maximum(xi, 0))
+
+
+def d2s_ref(x, out_shape, bh, bw, crd, inv, in_nchw, out_nchw, swap):
+    """Depth2Space.cpp:19-103, loop for loop."""
+    def nchw(shape, f):
+        return (shape[0], shape[1], shape[2], shape[3]) if f else (shape[0], shape[3], shape[1], shape[2])
+    n_, ic, ih, iw = nchw(x.shape, in_nchw)
+    on, oc, oh, ow = nchw(out_shape, out_nchw)
+    ist = [ic * ih * iw, ih * iw, iw, 1] if in_nchw else [ic * ih * iw, 1, iw * ic, ic]
+    ost = [oc * oh * ow, oh * ow, ow, 1] if out_nchw else [oc * oh * ow, 1, ow * oc, oc]
+    if inv:
+        n_, on, ic, oc, ih, oh, iw, ow, ist, ost = on, n_, oc, ic, oh, ih, ow, iw, ost, ist
+    src = x.ravel()
+    dst = np.zeros(int(np.prod(out_shape)), x.dtype)
+    for i in range(n_ * ic):
+        n, c = divmod(i, ic)
+        if crd:
+            new_c, left = divmod(c, bh * bw)
+        else:
+            new_c, left = c % oc, c // oc
+        if swap:
+            c1, c2 = divmod(left, bw)
+            rleft = c2 * bh + c1
+            c = new_c * (bh * bw) + rleft if crd else rleft * oc + new_c
+        for h in range(ih):
+            for w in range(iw):
+                ii = n * ist[0] + c * ist[1] + h * ist[2] + w * ist[3]
+                oi = n * ost[0] + new_c * ost[1] + (h * bh + left // bw) * ost[2] + (w * bw + left % bw) * ost[3]
+                if inv:
+                    dst[ii] = src[oi]
+                else:
+                    dst[oi] = src[ii]
+    return dst.reshape(out_shape)
+
+
+@pytest.mark.parametrize("cfg", [dict(crd=False, inv=False, in_nchw=True, out_nchw=True, swap=False), dict(crd=True, inv=False, in_nchw=True, out_nchw=True, swap=True),
+                                 dict(crd=False, inv=True, in_nchw=True, out_nchw=True, swap=False), dict(crd=True, inv=False, in_nchw=False, out_nchw=True, swap=False),
+                                 dict(crd=False, inv=True, in_nchw=True, out_nchw=False, swap=True)])
+def test_depth2space(cfg):
+    rng = np.random.default_rng(6)
+    bh, bw, c, h, w = 2, 3, 4, 3, 2
+    deep_nchw, shallow_nchw = (2, c * bh * bw, h, w), (2, c, h * bh, w * bw)
+    to_layout = lambda shp, f: shp if f else (shp[0], shp[2], shp[3], shp[1])  # noqa: E731
+    if cfg["inv"]:
+        in_shape, out_shape = to_layout(shallow_nchw, cfg["in_nchw"]), to_layout(deep_nchw, cfg["out_nchw"])
+    else:
+        in_shape, out_shape = to_layout(deep_nchw, cfg["in_nchw"]), to_layout(shallow_nchw, cfg["out_nchw"])
+    x = rng.standard_normal(in_shape).astype(np.float32)
+    want = d2s_ref(x, out_shape, bh, bw, cfg["crd"], cfg["inv"], cfg["in_nchw"], cfg["out_nchw"], cfg["swap"])
+    ops = [dict(type="top.Depth2Space", name="d", inputs=["x"], attrs=dict(block_h=bh, block_w=bw, is_CRD=cfg["crd"], is_inversed=cfg["inv"],
+                                                                         in_is_NCHW=cfg["in_nchw"], out_is_NCHW=cfg["out_nchw"], swap_cr=cfg["swap"]))]
+    m = run_graph({"x": f32(in_shape), "d": f32(out_shape)}, ops, {}, {"x": x})
+    assert np.array_equal(m.get_tensor("d"), want)
+
+
+def test_tpu_active_modes():
+    """tpu::ActiveOp on f32 tensors against the function table of lib/Support/ActiveUtils.cpp:16-181 evaluated in Python doubles
+    (one float ulp of slack, plus a few double ulps of the input's size where 1 + erf or 1 + tanh cancels: the device's double
+    functions and the C library's may differ in their last bit)."""
+    rng = np.random.default_rng(8)
+    x = np.concatenate([(rng.standard_normal(4000) * 2).astype(np.float32), np.float32([0, -0.0, 1, -1, 25, -25, 0.5])]).reshape(1, -1)
+    pos = np.abs(x) + np.float32(0.01)
+    unit = np.clip(x / 4, -0.99, 0.99).astype(np.float32)
+    sig = lambda v: 1 / (1 + math.exp(-v))  # noqa: E731
+    table = {
+        "TANH": (x, math.tanh, None), "SIGMOID": (x, sig, None), "EXP": (x, math.exp, None),
+        "ELU": (x, lambda v: v if v > 0 else 0.7 * (math.exp(v) - 1), [0.7]), "SQRT": (pos, math.sqrt, None), "SQUARE": (x, lambda v: v * v, None),
+        "RSQRT": (pos, lambda v: float(np.float32(1) / np.float32(math.sqrt(v))), None), "ABSVAL": (x, abs, None), "LN": (pos, math.log, None),
+        "ROUND": (x, lambda v: math.copysign(math.floor(abs(v) + 0.5), v), None), "CEIL": (x, math.ceil, None), "FLOOR": (x, math.floor, None),
+        "SIN": (x, math.sin, None), "COS": (x, math.cos, None), "SWISH": (x, lambda v: v / (1 + math.exp(-v * 1.3)), [1.3]),
+        "HSWISH": (x, lambda v: v * max(0.0, min(1.0, (v + 3.0) / 6.0)), None), "SILU": (x, lambda v: v / (1 + math.exp(-v)), None),
+        "ARCCOS": (unit, math.acos, None), "ARCTANH": (unit, math.atanh, None), "SINH": (x, math.sinh, None), "COSH": (x, math.cosh, None),
+        "TAN": (unit, math.tan, None), "SIGN": (x, lambda v: -1.0 if v < 0 else 1.0, None),
+        "GELU": (x, lambda v: 0.5 * v * (1 + math.erf(v / math.sqrt(2.0))), None), "ERF": (x, math.erf, None),
+        "HSIGMOID": (x, lambda v: max(0.0, min(1.0, 0.2 * v + 0.5)), [0.5, 0.2]), "LOG_SIGMOID": (x, lambda v: math.log(sig(v)), None),
+        "SOFT_PLUS": (x, lambda v: v if v > 20 else math.log(math.exp(v) + 1), None), "SOFT_SIGN": (x, lambda v: v / (1 + abs(v)), None),
+        "LOG2": (pos, math.log2, None),
+        "TGELU": (x, lambda v: 0.5 * v * (1.0 + math.tanh(v * 0.7978845608 * (1.0 + 0.044715 * v * v))), None),
+        "QGELU": (x, lambda v: v * sig(1.702 * v), None),
+    }
+    for mode, (inp, fn, coeffs) in table.items():
+        ops = [dict(type="tpu.Active", name="y", inputs=["x"], attrs=dict(mode=mode, coeffs=coeffs))]
+        m = run_graph({"x": f32(inp.shape), "y": f32(inp.shape)}, ops, {}, {"x": inp})
+        want = np.array([fn(float(v)) for v in inp.ravel()], dtype=np.float64).astype(np.float32).reshape(inp.shape)
+        got = m.get_tensor("y")
+        exact = mode in ("SQUARE", "ABSVAL", "ROUND", "CEIL", "FLOOR", "SIGN", "HSWISH", "HSIGMOID", "SOFT_SIGN", "SQRT", "RSQRT")
+        if exact:
+            assert np.array_equal(got, want), mode
+        else:
+            assert np.all(np.abs(got.astype(np.float64) - want) <= np.spacing(np.abs(want)).astype(np.float64) + 1e-14 * (1 + np.abs(inp))), mode
+    # MISH works in float in the reference (GenericCpuFunc.cpp:25-33): a float restatement, a few ulps for exp/log
+    f = np.float32
+    sp = np.log(np.exp(x) + f(1))
+    want = x * (f(2) / (f(1) + np.exp(f(-2) * sp)) - f(1))
+    m = run_graph({"x": f32(x.shape), "y": f32(x.shape)}, [dict(type="tpu.Active", name="y", inputs=["x"], attrs=dict(mode="MISH"))], {}, {"x": x})
+    np.testing.assert_allclose(m.get_tensor("y"), want, rtol=2e-6, atol=1e-6)
+    with pytest.raises(L.B200QError):
+        run_graph({"x": f32(x.shape), "y": f32(x.shape)}, [dict(type="tpu.Active", name="y", inputs=["x"], attrs=dict(mode="ARCSIN"))], {}, {"x": x})
+
+
+def test_tpu_float_mode_ops_follow_top():
+    """F32-mode Tpu ops that share the Top op's arithmetic, and tpu.Reduce's mean (sum * float(1 / n), Reduce.cpp:132-138)."""
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal((2, 7, 5)) * 3).astype(np.float32)
+    y2 = (rng.standard_normal((2, 7, 5)) + 2.5).astype(np.float32)
+    sh = x.shape
+    ops = [dict(type="tpu.Sub", name="sub", inputs=["x", "y"], attrs=dict(is_reverse=True, do_relu=True)),
+           dict(type="tpu.Div", name="div", inputs=["x", "y"], attrs={}),
+           dict(type="tpu.MaxConst", name="maxc", inputs=["x"], attrs=dict(const_val=-0.5)),
+           dict(type="tpu.MinConst", name="minc", inputs=["x"], attrs=dict(const_val=0.5)),
+           dict(type="tpu.SubConst", name="subc", inputs=["x"], attrs=dict(const_val=0.3, is_reverse=True)),
+           dict(type="tpu.Softmax", name="sm", inputs=["x"], attrs=dict(axis=1)),
+           dict(type="tpu.LayerNorm", name="ln", inputs=["x"], attrs=dict(axis=2, eps=1e-5, normalized_shape=[5])),
+           dict(type="tpu.Reduce", name="mean", inputs=["x"], attrs=dict(axes=[1], keepdims=False, mode="ReduceMean")),
+           dict(type="top.Reduce", name="tmean", inputs=["x"], attrs=dict(axes=[1], keepdims=False, mode="ReduceMean"))]
+    tensors = {"x": f32(sh), "y": f32(sh), "mean": f32((2, 5)), "tmean": f32((2, 5))}
+    tensors.update({o["name"]: f32(sh) for o in ops if o["name"] not in tensors})
+    lw, lb = rng.standard_normal(5).astype(np.float32), rng.standard_normal(5).astype(np.float32)
+    m = run_graph(tensors, ops, {"ln_weight": lw, "ln_bias": lb}, {"x": x, "y": y2})
+    g = m.get_tensor
+    assert np.array_equal(g("sub"), np.maximum(y2 - x, 0))
+    assert np.array_equal(g("div"), x / y2)
+    assert np.array_equal(g("maxc"), np.maximum(x, np.float32(-0.5)))
+    assert np.array_equal(g("minc"), np.minimum(x, np.float32(0.5)))
+    assert np.array_equal(g("subc"), np.float32(0.3) - x)
+    e = np.exp(x - x.max(axis=1, keepdims=True))
+    np.testing.assert_allclose(g("sm"), e / e.sum(axis=1, keepdims=True), rtol=1e-6)
+    mu = x.mean(axis=2, keepdims=True)
+    np.testing.assert_allclose(g("ln"), (x - mu) / np.sqrt(((x - mu) ** 2).mean(axis=2, keepdims=True) + 1e-5) * lw + lb, rtol=1e-4, atol=1e-5)
+    s = np.zeros((2, 5), np.float32)
+    for a_ in range(7):
+        s = s + x[:, a_, :]
+    assert np.array_equal(g("mean"), s * np.float32(1.0 / 7))
+    assert np.array_equal(g("tmean"), s / np.float32(7))

@@ -147,6 +147,7 @@ SIGNATURES = {
     "b200q_top_pool2d_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64] + [C.c_int32] * 13 + [C.c_float, C.c_void_p]),
     "b200q_top_add_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),
     "b200q_top_relu_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p]),
+    "b200q_active_f32_dev": (C.c_int, [C.c_int32, C.c_void_p, C.c_double, C.c_double, C.c_void_p, C.c_int64, C.c_void_p]),
     "b200q_top_eltwise_f32_dev": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_double, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),
     "b200q_top_scale_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),
     "b200q_top_reduce_f32_dev": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_void_p]),

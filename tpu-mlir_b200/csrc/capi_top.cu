@@ -168,6 +168,11 @@ int b200q_top_eltwise_f32_dev(int32_t op, const float* a, const float* b, double
   return top_eltwise_launch(op, a, b, const_val, y, count, do_relu != 0, relu_limit, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_active_f32_dev(int32_t mode, const float* x, double coeff0, double coeff1, float* y, int64_t count, void* stream) {
+  if (!x || !y || count < 0) return set_error(B200Q_ERR_INVALID, "active_f32_dev: bad argument");
+  return top_active_launch(mode, x, coeff0, coeff1, y, count, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_top_scale_f32_dev(const float* x, const float* scale, const float* bias, float* y, int64_t outer, int32_t channels,
                             int64_t inner, int32_t do_relu, float relu_limit, void* stream) {
   if (!x || !scale || !y || outer < 0 || channels < 1 || inner < 1) return set_error(B200Q_ERR_INVALID, "top_scale_f32_dev: bad argument");

@@ -377,6 +377,60 @@ __global__ void eltwise_f32_kernel(int op, const float* __restrict__ a, const fl
   y[i] = relu_f(v, do_relu, relu_limit);
 }
 
+// tpu::ActiveOp (lib/Dialect/Tpu/Interfaces/Common/Active.cpp:20-32): out = (float)func((double)in) with func from
+// lib/Support/ActiveUtils.cpp:16-181; `mode` is the dialect's ActiveMode number.  Everything is evaluated in double, as
+// there, except MISH, whose helper works in float (lib/Support/GenericCpuFunc.cpp:25-33).  Modes the reference's switch
+// does not hold (RELU, IS_FINITE, ARCSIN, ARCSINH, ARCCOSH) are refused by the launcher.
+__global__ void active_f32_kernel(int mode, const float* __restrict__ x, double c0, double c1, float* __restrict__ y, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const double v = (double)x[i];
+  double r;
+  switch (mode) {
+    case 0: r = tanh(v); break;
+    case 1: r = 1.0 / (1.0 + exp(-v)); break;
+    case 3: r = exp(v); break;
+    case 4: r = v > 0 ? v : c0 * (exp(v) - 1.0); break;                                  // ELU, alpha = coeffs[0]
+    case 5: r = sqrt(v); break;
+    case 6: r = v * v; break;
+    case 7: r = (double)(1.f / (float)sqrt(v)); break;                                   // RSQRT: `1.f / std::sqrt(val)` then double
+    case 8: r = fabs(v); break;
+    case 9: r = log(v); break;
+    case 10: r = round(v); break;
+    case 11: r = ceil(v); break;
+    case 12: r = floor(v); break;
+    case 13: r = sin(v); break;
+    case 14: r = cos(v); break;
+    case 16: {                                                                           // MISH in float
+      const float xf = x[i];
+      const float sp = logf(__fadd_rn(expf(xf), 1.f));
+      const float th = __fsub_rn(__fdiv_rn(2.f, __fadd_rn(1.f, expf(__fmul_rn(-2.f, sp)))), 1.f);
+      r = (double)__fmul_rn(xf, th);
+      break;
+    }
+    case 17: r = v / (1.0 + exp(-v * c0)); break;                                        // SWISH, beta = coeffs[0]
+    case 18: r = v * fmax(0.0, fmin(1.0, (v + 3.0) / 6.0)); break;                       // HSWISH
+    case 19: r = v / (1.0 + exp(-v)); break;                                             // SILU
+    case 21: r = acos(v); break;
+    case 24: r = atanh(v); break;
+    case 25: r = sinh(v); break;
+    case 26: r = cosh(v); break;
+    case 27: r = tan(v); break;
+    case 28: r = v < 0 ? -1.0 : 1.0; break;                                              // SIGN as the reference evaluates it: 1 at 0
+    case 29: r = 0.5 * v * (1.0 + erf(v / sqrt(2.0))); break;                            // GELU
+    case 30: r = erf(v); break;
+    case 31: r = fmax(0.0, fmin(1.0, c1 * v + c0)); break;                               // HSIGMOID: alpha = coeffs[1], beta = coeffs[0]
+    case 32: r = log(1.0 / (1.0 + exp(-v))); break;                                      // LOG_SIGMOID
+    case 33: r = v > 20 ? v : log(exp(v) + 1.0); break;                                  // SOFT_PLUS
+    case 34: r = v / (1.0 + fabs(v)); break;                                             // SOFT_SIGN
+    case 35: r = log2(v); break;
+    case 36: r = 0.5 * v * (1.0 + tanh(v * 0.7978845608 * (1.0 + 0.044715 * v * v))); break;   // TGELU
+    case 37: r = v * (1.0 / (1.0 + exp(-(1.702 * v)))); break;                           // QGELU
+    default: r = v;
+  }
+  y[i] = (float)r;
+}
+
 // top::ScaleOp (Scale.cpp:19-44): y = x * scale[c] + bias[c], a multiply and an add (no fused multiply-add)
 __global__ void scale_f32_kernel(const float* __restrict__ x, const float* __restrict__ sc, const float* __restrict__ bi,
                                  float* __restrict__ y, long long n, int channels, long long inner, int do_relu, float relu_limit) {
@@ -471,6 +525,7 @@ __global__ void reduce_f32_kernel(int mode, const float* __restrict__ x, float* 
       else v = __fadd_rn(v, u);
     }
     if (mode == TOP_REDUCE_MEAN) v = __fdiv_rn(v, (float)axis);
+    if (mode == TOP_REDUCE_MEAN_RCP) v = __fmul_rn(v, (float)(1.0 / (double)axis));     // tpu::ReduceOp, Reduce.cpp:132-138
     if (mode == TOP_REDUCE_L2) v = (float)pow((double)v, 0.5);
   }
   y[i] = v;
@@ -509,6 +564,15 @@ int top_eltwise_launch(int op, const float* a, const float* b, double c, float* 
   const bool binary = op == TOP_MUL || op == TOP_SUB || op == TOP_RSUB || op == TOP_DIV || op == TOP_RDIV;
   if (binary && !b) return set_error(B200Q_ERR_INVALID, "top eltwise: the op needs a second operand");
   eltwise_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(op, a, b, c, y, n, do_relu ? 1 : 0, relu_limit);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_active_launch(int mode, const float* x, double c0, double c1, float* y, long long n, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  const bool known = mode >= 0 && mode <= 37 && mode != 2 && mode != 15 && mode != 20 && mode != 22 && mode != 23;
+  if (!known) return set_error(B200Q_ERR_UNSUPPORTED, "active: mode %d has no function in the reference", mode);
+  active_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(mode, x, c0, c1, y, n);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

@@ -35,9 +35,12 @@ enum { TOP_ADD_CONST = 0, TOP_SUB_CONST, TOP_RSUB_CONST, TOP_MUL_CONST, TOP_MAX_
        TOP_DIV, TOP_RDIV, TOP_SIGMOID, TOP_LOG_SIGMOID, TOP_SILU, TOP_GELU, TOP_FLOOR, TOP_ELTWISE_OPS };
 int top_eltwise_launch(int op, const float* a, const float* b, double c, float* y, long long n, bool do_relu, float relu_limit,
                        cudaStream_t s);
+// tpu::ActiveOp on float tensors; `mode` is the dialect's ActiveMode number, c0 / c1 its coeffs
+int top_active_launch(int mode, const float* x, double c0, double c1, float* y, long long n, cudaStream_t s);
 int top_scale_launch(const float* x, const float* scale, const float* bias, float* y, long long outer, int channels, long long inner,
                      bool do_relu, float relu_limit, cudaStream_t s);
-enum { TOP_REDUCE_MEAN = 0, TOP_REDUCE_SUM, TOP_REDUCE_MAX, TOP_REDUCE_MIN, TOP_REDUCE_PROD, TOP_REDUCE_L2, TOP_REDUCE_L1, TOP_REDUCE_MODES };
+enum { TOP_REDUCE_MEAN = 0, TOP_REDUCE_SUM, TOP_REDUCE_MAX, TOP_REDUCE_MIN, TOP_REDUCE_PROD, TOP_REDUCE_L2, TOP_REDUCE_L1, TOP_REDUCE_MEAN_RCP,
+       TOP_REDUCE_MODES };
 int top_reduce_launch(int mode, const float* x, float* y, long long outer, int axis, long long inner, cudaStream_t s);
 // softmax over the middle dimension of [outer, channels, inner]; layer normalisation of rows of `inner` values
 int top_softmax_launch(const float* x, float* y, long long outer, int channels, long long inner, bool log_form, cudaStream_t s);

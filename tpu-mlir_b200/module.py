@@ -34,7 +34,13 @@ _DT = {"i8": L.DT_I8, "u8": L.DT_U8, "i32": L.DT_I32, "f32": L.DT_F32}
 _QM = {"TFLite_LShift": 0, "TFLite": 1, "MultiplierShift": 2, "OnlyShift": 3, "QDM": 4, "OnlyScale": 5}
 
 
-_MOVE_OPS = ("Slice", "Permute", "Tile", "Upsample", "Pad", "Concat", "Squeeze", "Unsqueeze")
+# Tpu-dialect ops that, on f32 tensors, compute what the Top op of the same name computes
+_TPU_F32_AS_TOP = ("tpu.Sub", "tpu.Div", "tpu.MaxConst", "tpu.MinConst", "tpu.SubConst", "tpu.Softmax", "tpu.LayerNorm", "tpu.Reduce")
+# Tpu_ActiveMode (include/tpu_mlir/Dialect/Tpu/IR/TpuOps.td:284-321)
+_ACTIVE_MODES = {n: i for i, n in enumerate(
+    "TANH SIGMOID RELU EXP ELU SQRT SQUARE RSQRT ABSVAL LN ROUND CEIL FLOOR SIN COS IS_FINITE MISH SWISH HSWISH SILU ARCSIN ARCCOS "
+    "ARCSINH ARCCOSH ARCTANH SINH COSH TAN SIGN GELU ERF HSIGMOID LOG_SIGMOID SOFT_PLUS SOFT_SIGN LOG2 TGELU QGELU".split())}
+_MOVE_OPS = ("Slice", "Permute", "Tile", "Upsample", "Pad", "Concat", "Squeeze", "Unsqueeze", "Depth2Space")
 
 
 def _P(t):
@@ -200,6 +206,20 @@ class module:  # noqa: N801  (name of the reference class)
             return self._plan_move(op, stream)
         if t.startswith("top."):
             return self._plan_top(op, ins, out, iinfo, stream)
+        if t in _TPU_F32_AS_TOP and oinfo["dtype"] == "f32" and all(i["dtype"] == "f32" for i in iinfo):
+            # F32-mode Tpu ops whose inference is the Top op's arithmetic (lib/Dialect/Tpu/Interfaces/Common/<Op>.cpp)
+            top_op = dict(op, type="top." + t[4:])
+            if t == "tpu.Reduce" and op.get("attrs", {}).get("mode") == "ReduceMean":
+                top_op["attrs"] = dict(op["attrs"], mode="ReduceMeanRcp")
+            return self._plan_top(top_op, ins, out, iinfo, stream)
+        if t == "tpu.Active":
+            if oinfo["dtype"] != "f32" or iinfo[0]["dtype"] != "f32":
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.Active runs on f32 tensors here")
+            mode = a["mode"]
+            mode = _ACTIVE_MODES[mode] if isinstance(mode, str) else int(mode)
+            co = [float(v) for v in (a.get("coeffs") or [])] + [0.0, 0.0]
+            n = out.numel()
+            return lambda: L.check(lib.b200q_active_f32_dev(mode, _P(ins[0]), co[0], co[1], _P(out), n, stream()))
         if t == "tpu.Cast":
             n = out.numel()
             if iinfo[0]["dtype"] == "f32":
@@ -439,6 +459,40 @@ class module:  # noqa: N801  (name of the reference class)
                 raise L.B200QError(L.ERR_INVALID, f"{name}: paddings must hold 2 x rank values")
             pad_buf = self.torch.tensor([a.get("val", 0.0)]).to(out.dtype).to(self.device)      # the pad value in the storage type
             runs.append((srcs[0], desc(oshape, istr, ones, ones, zeros, [-p for p in pads[:r]], ishape, ostr)))
+        elif t == "Depth2Space":
+            # Depth2Space.cpp:19-103: the deep tensor's channel is (new_c, l1, l2) in CRD or (l1, l2, new_c) in DCR order (l1, l2
+            # swapped in the channel index when swap_cr), the shallow tensor's pixel is (h * bh + l1, w * bw + l2); either tensor
+            # may be NHWC; is_inversed copies the other way.  Every index is linear in (n, new_c, l1, l2, h, w): one remap.
+            if srcs[0] in self._nhwc:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: Depth2Space on a channels-last stored input")
+            bh, bw = int(a["block_h"]), int(a["block_w"])
+            crd, inv, swap = bool(a.get("is_CRD", False)), bool(a.get("is_inversed", False)), bool(a.get("swap_cr", False))
+            in_nchw, out_nchw = bool(a.get("in_is_NCHW", True)), bool(a.get("out_is_NCHW", True))
+
+            def nchw(shape, is_nchw):
+                return (shape[0], shape[1], shape[2], shape[3]) if is_nchw else (shape[0], shape[3], shape[1], shape[2])
+
+            def strides(c, h, w, is_nchw):     # (n, c, h, w) element strides
+                return (c * h * w, h * w, w, 1) if is_nchw else (c * h * w, 1, w * c, c)
+            n_, ic, ih, iw = nchw(ishape, in_nchw)
+            _, oc, oh, ow = nchw(oshape, out_nchw)
+            sn, sc_, sh_, sw_ = strides(ic, ih, iw, in_nchw)
+            dn, dc, dh, dw = strides(oc, oh, ow, out_nchw)
+            if inv:   # the "input" of the formulas is the op's output and the copy runs backwards
+                ic, oc, ih, oh, iw, ow = oc, ic, oh, ih, ow, iw
+                (sn, sc_, sh_, sw_), (dn, dc, dh, dw) = (dn, dc, dh, dw), (sn, sc_, sh_, sw_)
+            if ic != oc * bh * bw:
+                raise L.B200QError(L.ERR_INVALID, f"{name}: Depth2Space shapes do not match the block")
+            cm = 1 if crd else oc                                         # channel step of one unit of `left`
+            deep = [sn, (bh * bw if crd else 1) * sc_, (1 if swap else bw) * cm * sc_, (bh if swap else 1) * cm * sc_, sh_, sw_]
+            shallow = [dn, dc, dh, dw, bh * dh, bw * dw]
+            shallow = [shallow[0], shallow[1], shallow[2], shallow[3], shallow[4], shallow[5]]
+            dims6 = [n_, oc, bh, bw, ih, iw]
+            big = [1 << 40] * 6
+            src_s, dst_s = (shallow, deep) if inv else (deep, shallow)
+            runs.append((srcs[0], L.RemapDesc(dims=(C.c_int64 * 6)(*dims6), src_stride=(C.c_int64 * 6)(*src_s), mul=(C.c_int64 * 6)(*[1] * 6),
+                                              div=(C.c_int64 * 6)(*[1] * 6), mod=(C.c_int64 * 6)(*[0] * 6), off=(C.c_int64 * 6)(*[0] * 6),
+                                              extent=(C.c_int64 * 6)(*big), dst_stride=(C.c_int64 * 6)(*dst_s), dst_offset=0)))
         elif t == "Concat":
             axis = int(a.get("axis", 1))
             axis += r if axis < 0 else 0
@@ -537,7 +591,7 @@ class module:  # noqa: N801  (name of the reference class)
             code = unary.get(t, L.TOP_LOG_SIGMOID if a.get("log", False) else L.TOP_SIGMOID)
             return lambda: L.check(lib.b200q_top_eltwise_f32_dev(code, _P(ins[0]), None, 0.0, _P(out), n_el, 0, -1.0, stream()))
         if t == "top.Reduce":
-            modes = {"ReduceMean": 0, "ReduceSum": 1, "ReduceMax": 2, "ReduceMin": 3, "ReduceProd": 4, "ReduceL2": 5, "ReduceL1": 6}
+            modes = {"ReduceMean": 0, "ReduceSum": 1, "ReduceMax": 2, "ReduceMin": 3, "ReduceProd": 4, "ReduceL2": 5, "ReduceL1": 6, "ReduceMeanRcp": 7}
             shape = list(iinfo[0]["shape"])
             axes = sorted(int(x) + (len(shape) if int(x) < 0 else 0) for x in a["axes"])
             if a["mode"] not in modes or any(axes[i] + 1 != axes[i + 1] for i in range(len(axes) - 1)):
