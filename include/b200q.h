@@ -284,6 +284,11 @@ int b200q_mulshift_i8_dev(const void *x, int32_t dtype, int64_t count, int32_t m
  * symmetric tpu.MulConst (MulConst.cpp:50-62). */
 int b200q_addconst_i8_dev(const void *x, int32_t dtype, int64_t count, int32_t multiplier, double const_val, int32_t rshift,
                           int32_t in_zp, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
+/* tpu.PRelu (lib/Dialect/Tpu/Interfaces/Common/PRelu.cpp:35-88); slope index c = (i / inner) % num_slope.  f32 -> f32 with
+ * float slopes: x > 0 ? x : x * slope[c].  8-bit -> 8-bit (symmetric) with int8 slopes: x < 0 becomes
+ * saturate(RSR(x * slope[c], rshift, half-up)), other values pass through. */
+int b200q_prelu_dev(const void *x, int32_t dtype, const void *slope, int64_t count, int64_t inner, int32_t num_slope,
+                    int32_t rshift, int32_t out_dtype, void *out, void *stream);
 /* tpu.Mul, symmetric int8 operands of equal shape (Mul.cpp:23-29,:72-85): the op's ReLU acts on the product, then
  * out = saturate(RSR(product * multiplier, rshift, half-up)).  Broadcasting operands are not implemented. */
 int b200q_mul_i8_dev(const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t count,
@@ -504,6 +509,15 @@ typedef struct {
 } b200q_remap_desc;
 int b200q_remap_dev(const void *src, void *dst, int32_t elem_bytes, const b200q_remap_desc *desc, const void *pad_value,
                     void *stream);
+/* top::GatherOp / tpu::GatherOp (lib/Dialect/Top/Interfaces/Gather.cpp:17-49): dst[o, j, k] = src[o, indices[j], k] over
+ * src [outer, axis_dim, inner]; a negative index counts from the end.  top::GatherElementsOp (GatherElements.cpp:20-79): dst
+ * has the shape of `indices` and takes src at the same coordinate except on `axis`, where the index stands (rank <= 8).
+ * Indices are float (the reference interpreter's storage) or int32; one outside the axis yields 0 rather than a read outside
+ * the tensor.  elem_bytes 1, 2 or 4. */
+int b200q_gather_dev(const void *src, int32_t elem_bytes, const void *indices, int32_t index_is_float, void *dst, int64_t outer,
+                     int64_t axis_dim, int64_t num_indices, int64_t inner, void *stream);
+int b200q_gather_elements_dev(const void *src, int32_t elem_bytes, const void *indices, int32_t index_is_float, void *dst,
+                              int32_t ndim, const int64_t *src_shape, const int64_t *indices_shape, int32_t axis, void *stream);
 /* The two array operations of the threshold tuner (python/calibration/simple_tunner.py): import_quant_bias (:43-50),
  * y = clip(round_half_even(x * 127 / threshold), -128, 127) * threshold / 127; and the sums behind calc_distance
  * (:334-358), ACCUMULATED into five device doubles: sum (ref - x)^2, sum |ref|, sum x * ref, sum x^2, sum ref^2. */

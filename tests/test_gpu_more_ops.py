@@ -330,3 +330,62 @@ def test_tpu_float_mode_ops_follow_top():
         s = s + x[:, a_, :]
     assert np.array_equal(g("mean"), s * np.float32(1.0 / 7))
     assert np.array_equal(g("tmean"), s / np.float32(7))
+
+
+def test_gather_and_gather_elements():
+    rng = np.random.default_rng(10)
+    x = rng.standard_normal((3, 6, 4)).astype(np.float32)
+    idx = np.float32([[5, 0, -1], [2, 2, -6]])                      # float-stored indices, negatives count from the end
+    ops = [dict(type="top.Gather", name="g", inputs=["x", "i"], attrs=dict(axis=1))]
+    m = run_graph({"x": f32(x.shape), "i": f32(idx.shape), "g": f32((3, 2, 3, 4))}, ops, {}, {"x": x, "i": idx})
+    assert np.array_equal(m.get_tensor("g"), np.take(x, idx.astype(np.int64), axis=1))
+    # indices as a weight, int32; an int8 tensor through the Tpu op
+    q = rng.integers(-128, 128, (5, 7), dtype=np.int8)
+    ops = [dict(type="tpu.Gather", name="g", inputs=["x"], attrs=dict(axis=0))]
+    m = run_graph({"x": dict(shape=[5, 7], dtype="i8", scale=0.1, zp=0), "g": dict(shape=[3, 7], dtype="i8", scale=0.1, zp=0)}, ops,
+                  {"g_indices": np.int32([4, -5, 2])}, {"x": q})
+    assert np.array_equal(m.get_raw_tensor("g"), q[[4, 0, 2]])
+    # GatherElements: indices smaller than the source off the axis
+    src = rng.standard_normal((4, 5, 6)).astype(np.float32)
+    ind = rng.integers(0, 5, (3, 2, 6)).astype(np.float32)
+    ops = [dict(type="top.GatherElements", name="ge", inputs=["x", "i"], attrs=dict(axis=1))]
+    m = run_graph({"x": f32(src.shape), "i": f32(ind.shape), "ge": f32(ind.shape)}, ops, {}, {"x": src, "i": ind})
+    want = np.zeros(ind.shape, np.float32)
+    for a_ in range(3):
+        for b_ in range(2):
+            for c_ in range(6):
+                want[a_, b_, c_] = src[a_, int(ind[a_, b_, c_]), c_]
+    assert np.array_equal(m.get_tensor("ge"), want)
+    ops = [dict(type="tpu.GatherElements", name="ge", inputs=["x", "i"], attrs=dict(axis=-1))]
+    ind2 = rng.integers(0, 6, (4, 5, 2)).astype(np.int32)
+    m = run_graph({"x": f32(src.shape), "i": dict(shape=list(ind2.shape), dtype="i32"), "ge": f32(ind2.shape)}, ops, {}, {"x": src, "i": ind2})
+    assert np.array_equal(m.get_tensor("ge"), np.take_along_axis(src, ind2.astype(np.int64), axis=2))
+
+
+def test_swap_dim_inner():
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((2, 5, 6, 7)).astype(np.float32)
+    for offs in ([0, 0, 2, 0], [0, 3, 0, 4], [0, 0, 0, 7]):
+        ops = [dict(type="top.SwapDimInner", name="s", inputs=["x"], attrs=dict(offset=offs))]
+        m = run_graph({"x": f32(x.shape), "s": f32(x.shape)}, ops, {}, {"x": x})
+        want = x
+        for ax, o in enumerate(offs):
+            if o:
+                want = np.roll(want, -o, axis=ax)      # out[b] = in[(b + offset) % dim]
+        assert np.array_equal(m.get_tensor("s"), want), offs
+
+
+def test_tpu_prelu():
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((2, 3, 4, 5)).astype(np.float32)
+    sl = np.float32([0.1, -0.25, 0.5]).reshape(1, 3, 1, 1)
+    ops = [dict(type="tpu.PRelu", name="p", inputs=["x"], attrs={})]
+    m = run_graph({"x": f32(x.shape), "p": f32(x.shape)}, ops, {"p_slope": sl}, {"x": x})
+    assert np.array_equal(m.get_tensor("p"), np.where(x > 0, x, x * sl))
+    q = rng.integers(-128, 128, (2, 3, 4, 5), dtype=np.int8)
+    qs = np.int8([13, -7, 100]).reshape(1, 3, 1, 1)
+    qi = dict(shape=list(q.shape), dtype="i8", scale=0.05, zp=0)
+    m = run_graph({"x": qi, "p": dict(qi)}, [dict(type="tpu.PRelu", name="p", inputs=["x"], attrs=dict(rshift=5))], {"p_slope": qs}, {"x": q})
+    prod = q.astype(np.int64) * qs
+    neg = np.clip((prod + 16) >> 5, -128, 127)                                    # round half up
+    assert np.array_equal(m.get_raw_tensor("p"), np.where(q < 0, neg, q).astype(np.int8))

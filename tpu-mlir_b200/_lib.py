@@ -135,6 +135,7 @@ SIGNATURES = {
     "b200q_a16_w4_dev": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
                                    C.c_void_p]),
     "b200q_a16_set_route": (None, [C.c_int32]),
+    "b200q_prelu_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "b200q_addconst_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_double, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                         C.c_void_p, C.c_void_p]),
     "b200q_top_conv2d_inference": (C.c_int, [C.POINTER(TopConvDesc), _FLOATPP, C.c_int, _FLOATPP, C.c_int]),
@@ -147,6 +148,9 @@ SIGNATURES = {
     "b200q_top_pool2d_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64] + [C.c_int32] * 13 + [C.c_float, C.c_void_p]),
     "b200q_top_add_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),
     "b200q_top_relu_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_void_p]),
+    "b200q_gather_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "b200q_gather_elements_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int64),
+                                            C.POINTER(C.c_int64), C.c_int32, C.c_void_p]),
     "b200q_active_f32_dev": (C.c_int, [C.c_int32, C.c_void_p, C.c_double, C.c_double, C.c_void_p, C.c_int64, C.c_void_p]),
     "b200q_top_eltwise_f32_dev": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_double, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),
     "b200q_top_scale_f32_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_float, C.c_void_p]),

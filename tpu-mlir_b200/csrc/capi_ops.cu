@@ -931,6 +931,17 @@ int b200q_addconst_i8_dev(const void* x, int32_t dtype, int64_t count, int32_t m
   return addconst_i8_launch(x, dtype, count, multiplier, const_val, rshift, in_zp, do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_prelu_dev(const void* x, int32_t dtype, const void* slope, int64_t count, int64_t inner, int32_t num_slope, int32_t rshift,
+                    int32_t out_dtype, void* out, void* stream) {
+  if (!x || !slope || !out || count < 0 || inner < 1 || num_slope < 1 || rshift < 0 || rshift > 62)
+    return set_error(B200Q_ERR_INVALID, "prelu_dev: bad argument");
+  if (dtype == B200Q_DT_F32 && out_dtype == B200Q_DT_F32)
+    return prelu_f32_launch(static_cast<const float*>(x), static_cast<const float*>(slope), count, inner, num_slope, static_cast<float*>(out),
+                            static_cast<cudaStream_t>(stream));
+  if (!is_q8(dtype) || !is_q8(out_dtype)) return set_error(B200Q_ERR_UNSUPPORTED, "prelu_dev: f32 -> f32 or 8-bit -> 8-bit");
+  return prelu_i8_launch(x, dtype, slope, count, inner, num_slope, rshift, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_mul_i8_dev(const void* a, int32_t a_dtype, const void* b, int32_t b_dtype, int64_t count, int32_t multiplier,
                      int32_t rshift, int32_t do_relu, int32_t out_dtype, void* out, void* stream) {
   if (!a || !b || !out || count < 0 || !is_q8(a_dtype) || !is_q8(b_dtype) || rshift < 0 || rshift > 62)

@@ -195,6 +195,27 @@ int b200q_top_layernorm_f32_dev(const float* x, const float* weight, const float
   return top_layernorm_launch(x, weight, bias, y, outer, inner, eps, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_gather_dev(const void* src, int32_t elem_bytes, const void* indices, int32_t index_is_float, void* dst, int64_t outer,
+                     int64_t axis_dim, int64_t num_indices, int64_t inner, void* stream) {
+  if (!src || !indices || !dst || outer < 0 || axis_dim < 1 || num_indices < 0 || inner < 0)
+    return set_error(B200Q_ERR_INVALID, "gather_dev: bad argument");
+  return top_gather_launch(src, elem_bytes, indices, index_is_float != 0, dst, outer, axis_dim, num_indices, inner,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int b200q_gather_elements_dev(const void* src, int32_t elem_bytes, const void* indices, int32_t index_is_float, void* dst, int32_t ndim,
+                              const int64_t* src_shape, const int64_t* indices_shape, int32_t axis, void* stream) {
+  if (!src || !indices || !dst || !src_shape || !indices_shape) return set_error(B200Q_ERR_INVALID, "gather_elements_dev: bad argument");
+  long long ss[8], is[8];
+  if (ndim < 1 || ndim > 8) return set_error(B200Q_ERR_INVALID, "gather_elements_dev: rank %d", ndim);
+  for (int i = 0; i < ndim; ++i) {
+    ss[i] = src_shape[i];
+    is[i] = indices_shape[i];
+    if (ss[i] < 1 || is[i] < 0) return set_error(B200Q_ERR_INVALID, "gather_elements_dev: bad shape");
+  }
+  return top_gather_elements_launch(src, elem_bytes, indices, index_is_float != 0, dst, ndim, ss, is, axis, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_remap_dev(const void* src, void* dst, int32_t elem_bytes, const b200q_remap_desc* desc, const void* pad_value, void* stream) {
   if (!src || !dst || !desc) return set_error(B200Q_ERR_INVALID, "remap_dev: null argument");
   static_assert(sizeof(b200q_remap_desc) == sizeof(TopRemap), "the two descriptors must stay layout-compatible");

@@ -436,6 +436,29 @@ addconst_i8_kernel(const void* __restrict__ x, int dt, long long n, int m, doubl
   st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
 }
 
+// tpu.PRelu (lib/Dialect/Tpu/Interfaces/Common/PRelu.cpp:35-88).  8-bit symmetric: a negative input becomes
+// saturate(RSR(x * slope[c], rshift, half-up)) with int8 slopes, anything else passes through; c = (i / inner) % num_slope.
+__global__ void __launch_bounds__(256)
+prelu_i8_kernel(const void* __restrict__ x, int dt, const int8_t* __restrict__ slope, long long n, long long inner, int num_slope,
+                int sft, int out_dt, void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int v = ld_q(x, i, dt);
+  int64_t r = v;
+  if (v < 0) r = clamp_dtype(rshift_round((int64_t)v * slope[(i / inner) % num_slope], sft, B200Q_ROUND_HALF_UP), out_dt);
+  st_q(out, i, out_dt, (int32_t)r);
+}
+
+// the float form is the library PReLU the reference calls (lib/Support/Dnnl/PRelu.cpp): x > 0 ? x : x * slope[c]
+__global__ void __launch_bounds__(256)
+prelu_f32_kernel(const float* __restrict__ x, const float* __restrict__ slope, long long n, long long inner, int num_slope,
+                 float* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = x[i];
+  out[i] = v > 0.f ? v : __fmul_rn(v, slope[(i / inner) % num_slope]);
+}
+
 // tpu.Mul, symmetric 8-bit tensors of equal shape (Mul.cpp:23-29,:72-85): the ReLU acts on the product, then
 // out = saturate(RSR(prod * m, s, half-up))
 __global__ void __launch_bounds__(256)
@@ -697,6 +720,21 @@ int addconst_i8_launch(const void* x, int dt, long long n, int m, double const_v
                        void* out, cudaStream_t s) {
   if (n == 0) return B200Q_OK;
   addconst_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(x, dt, n, m, const_val, sft, in_zp, do_relu, out_dt, out);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int prelu_i8_launch(const void* x, int dt, const void* slope, long long n, long long inner, int num_slope, int sft, int out_dt, void* out,
+                    cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  prelu_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(x, dt, static_cast<const int8_t*>(slope), n, inner, num_slope, sft, out_dt, out);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int prelu_f32_launch(const float* x, const float* slope, long long n, long long inner, int num_slope, float* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  prelu_f32_kernel<<<nblk(n, 256), 256, 0, s>>>(x, slope, n, inner, num_slope, out);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

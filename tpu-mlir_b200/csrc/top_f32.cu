@@ -531,6 +531,46 @@ __global__ void reduce_f32_kernel(int mode, const float* __restrict__ x, float* 
   y[i] = v;
 }
 
+// top::GatherOp / tpu::GatherOp (lib/Dialect/Top/Interfaces/Gather.cpp:17-49): dst[o, j, k] = src[o, idx[j], k], a negative
+// index counts from the end of the axis.  Indices are floats (the interpreter's storage) or int32.  An index outside the axis
+// writes zero instead of reading outside the tensor.
+template <typename T>
+__global__ void gather_kernel(const T* __restrict__ src, const void* __restrict__ indices, int index_is_float, T* __restrict__ dst,
+                              long long outer, long long axis_dim, long long num_indices, long long inner) {
+  const long long total = outer * num_indices * inner;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long k = i % inner, j = (i / inner) % num_indices, o = i / (inner * num_indices);
+    long long ix;
+    if (index_is_float) {
+      const float f = static_cast<const float*>(indices)[j];
+      ix = (long long)(f < 0 ? f + (float)axis_dim : f);
+    } else {
+      ix = static_cast<const int*>(indices)[j];
+      if (ix < 0) ix += axis_dim;
+    }
+    dst[i] = (ix >= 0 && ix < axis_dim) ? src[(o * axis_dim + ix) * inner + k] : T(0);
+  }
+}
+
+// top::GatherElementsOp (GatherElements.cpp:20-79): the output has the shape of `indices`; the source coordinate equals the
+// output's except on `axis`, where it is the index.  Up to eight dimensions, as there.
+struct GatherElemDims { long long idx_shape[8], src_stride[8]; int ndim, axis; long long axis_dim; };
+template <typename T>
+__global__ void gather_elements_kernel(const T* __restrict__ src, const void* __restrict__ indices, int index_is_float,
+                                       T* __restrict__ dst, const GatherElemDims d, long long total) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    long long rem = i, at = 0;
+    for (int k = d.ndim - 1; k >= 0; --k) {
+      const long long c = rem % d.idx_shape[k];
+      rem /= d.idx_shape[k];
+      if (k != d.axis) at += c * d.src_stride[k];
+    }
+    long long ix = index_is_float ? (long long)static_cast<const float*>(indices)[i] : (long long)static_cast<const int*>(indices)[i];
+    if (ix < 0) ix += d.axis_dim;
+    dst[i] = (ix >= 0 && ix < d.axis_dim) ? src[at + ix * d.src_stride[d.axis]] : T(0);
+  }
+}
+
 // Data movement by index arithmetic (Slice, Permute, Tile, Upsample, Pad, Concat of either dialect): the output (or, for
 // Concat, one input's region of it) is walked in up to six dimensions; per dimension the source coordinate is
 // ((i / div) % mod) * mul + off (mod 0 = no wrap), valid inside [0, extent); an invalid coordinate writes the pad value.
@@ -609,6 +649,58 @@ int top_layernorm_launch(const float* x, const float* w, const float* b, float* 
   if (outer == 0 || inner == 0) return B200Q_OK;
   if (outer > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "layernorm: too many rows");
   layernorm_f32_kernel<<<(unsigned)outer, 256, 0, s>>>(x, w, b, y, inner, eps);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_gather_launch(const void* src, int elem_bytes, const void* indices, bool index_is_float, void* dst, long long outer,
+                      long long axis_dim, long long num_indices, long long inner, cudaStream_t s) {
+  const long long total = outer * num_indices * inner;
+  if (total == 0) return B200Q_OK;
+  const unsigned blocks = (unsigned)std::min<long long>((total + 255) / 256, 148LL * 32);
+  if (elem_bytes == 4)
+    gather_kernel<uint32_t><<<blocks, 256, 0, s>>>(static_cast<const uint32_t*>(src), indices, index_is_float, static_cast<uint32_t*>(dst),
+                                                    outer, axis_dim, num_indices, inner);
+  else if (elem_bytes == 2)
+    gather_kernel<uint16_t><<<blocks, 256, 0, s>>>(static_cast<const uint16_t*>(src), indices, index_is_float, static_cast<uint16_t*>(dst),
+                                                    outer, axis_dim, num_indices, inner);
+  else if (elem_bytes == 1)
+    gather_kernel<uint8_t><<<blocks, 256, 0, s>>>(static_cast<const uint8_t*>(src), indices, index_is_float, static_cast<uint8_t*>(dst),
+                                                   outer, axis_dim, num_indices, inner);
+  else
+    return set_error(B200Q_ERR_INVALID, "gather: element size %d", elem_bytes);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_gather_elements_launch(const void* src, int elem_bytes, const void* indices, bool index_is_float, void* dst, int ndim,
+                               const long long* src_shape, const long long* idx_shape, int axis, cudaStream_t s) {
+  if (ndim < 1 || ndim > 8 || axis < 0 || axis >= ndim) return set_error(B200Q_ERR_INVALID, "gather_elements: rank %d, axis %d", ndim, axis);
+  GatherElemDims d{};
+  d.ndim = ndim;
+  d.axis = axis;
+  d.axis_dim = src_shape[axis];
+  long long acc = 1, total = 1;
+  for (int k = ndim - 1; k >= 0; --k) {
+    d.src_stride[k] = acc;
+    acc *= src_shape[k];
+    d.idx_shape[k] = idx_shape[k];
+    total *= idx_shape[k];
+    if (k != axis && idx_shape[k] > src_shape[k]) return set_error(B200Q_ERR_INVALID, "gather_elements: indices exceed the source on dimension %d", k);
+  }
+  if (total == 0) return B200Q_OK;
+  const unsigned blocks = (unsigned)std::min<long long>((total + 255) / 256, 148LL * 32);
+  if (elem_bytes == 4)
+    gather_elements_kernel<uint32_t><<<blocks, 256, 0, s>>>(static_cast<const uint32_t*>(src), indices, index_is_float,
+                                                             static_cast<uint32_t*>(dst), d, total);
+  else if (elem_bytes == 2)
+    gather_elements_kernel<uint16_t><<<blocks, 256, 0, s>>>(static_cast<const uint16_t*>(src), indices, index_is_float,
+                                                             static_cast<uint16_t*>(dst), d, total);
+  else if (elem_bytes == 1)
+    gather_elements_kernel<uint8_t><<<blocks, 256, 0, s>>>(static_cast<const uint8_t*>(src), indices, index_is_float,
+                                                            static_cast<uint8_t*>(dst), d, total);
+  else
+    return set_error(B200Q_ERR_INVALID, "gather_elements: element size %d", elem_bytes);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

@@ -52,6 +52,10 @@ struct TopRemap {   // layout-compatible with b200q_remap_desc
       off[TOP_REMAP_DIMS], extent[TOP_REMAP_DIMS], dst_stride[TOP_REMAP_DIMS];
   long long dst_offset;
 };
+int top_gather_launch(const void* src, int elem_bytes, const void* indices, bool index_is_float, void* dst, long long outer,
+                      long long axis_dim, long long num_indices, long long inner, cudaStream_t s);
+int top_gather_elements_launch(const void* src, int elem_bytes, const void* indices, bool index_is_float, void* dst, int ndim,
+                               const long long* src_shape, const long long* idx_shape, int axis, cudaStream_t s);
 int top_remap_launch(const void* src, void* dst, int elem_bytes, const TopRemap& m, const void* pad_value, cudaStream_t s);
 
 // y = clip(rint(x * 127 / threshold), -128, 127) * threshold / 127

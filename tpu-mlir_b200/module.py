@@ -24,6 +24,7 @@ otherwise bound by the host's launch rate).
 from __future__ import annotations
 
 import ctypes as C
+import itertools
 from typing import Callable, Dict, List, Optional
 
 import numpy as np
@@ -40,7 +41,7 @@ _TPU_F32_AS_TOP = ("tpu.Sub", "tpu.Div", "tpu.MaxConst", "tpu.MinConst", "tpu.Su
 _ACTIVE_MODES = {n: i for i, n in enumerate(
     "TANH SIGMOID RELU EXP ELU SQRT SQUARE RSQRT ABSVAL LN ROUND CEIL FLOOR SIN COS IS_FINITE MISH SWISH HSWISH SILU ARCSIN ARCCOS "
     "ARCSINH ARCCOSH ARCTANH SINH COSH TAN SIGN GELU ERF HSIGMOID LOG_SIGMOID SOFT_PLUS SOFT_SIGN LOG2 TGELU QGELU".split())}
-_MOVE_OPS = ("Slice", "Permute", "Tile", "Upsample", "Pad", "Concat", "Squeeze", "Unsqueeze", "Depth2Space")
+_MOVE_OPS = ("Slice", "Permute", "Tile", "Upsample", "Pad", "Concat", "Squeeze", "Unsqueeze", "Depth2Space", "SwapDimInner")
 
 
 def _P(t):
@@ -204,6 +205,8 @@ class module:  # noqa: N801  (name of the reference class)
         stream = lambda: C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)  # noqa: E731
         if t.split(".", 1)[-1] in _MOVE_OPS:
             return self._plan_move(op, stream)
+        if t.split(".", 1)[-1] in ("Gather", "GatherElements"):
+            return self._plan_gather(op, ins, out, iinfo, stream)
         if t.startswith("top."):
             return self._plan_top(op, ins, out, iinfo, stream)
         if t in _TPU_F32_AS_TOP and oinfo["dtype"] == "f32" and all(i["dtype"] == "f32" for i in iinfo):
@@ -212,6 +215,18 @@ class module:  # noqa: N801  (name of the reference class)
             if t == "tpu.Reduce" and op.get("attrs", {}).get("mode") == "ReduceMean":
                 top_op["attrs"] = dict(op["attrs"], mode="ReduceMeanRcp")
             return self._plan_top(top_op, ins, out, iinfo, stream)
+        if t == "tpu.PRelu":
+            fl = oinfo["dtype"] == "f32"
+            w = self.weights[op["name"] + "_slope"]
+            w = (w.to(self.torch.float32) if fl else w.to(self.torch.int8)).contiguous().reshape(-1)
+            self._keep.append(w)
+            if op["inputs"][0] in self._nhwc or op["name"] in self._nhwc:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.PRelu on channels-last stored tensors")
+            shape = list(iinfo[0]["shape"])
+            inner = int(np.prod(shape[2:])) if len(shape) > 2 else 1
+            n, ns, sft = out.numel(), w.numel(), int(a.get("rshift", 0))
+            return lambda: L.check(lib.b200q_prelu_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(w), n, inner, ns, sft, _DT[oinfo["dtype"]],
+                                                       _P(out), stream()))
         if t == "tpu.Active":
             if oinfo["dtype"] != "f32" or iinfo[0]["dtype"] != "f32":
                 raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.Active runs on f32 tensors here")
@@ -459,6 +474,22 @@ class module:  # noqa: N801  (name of the reference class)
                 raise L.B200QError(L.ERR_INVALID, f"{name}: paddings must hold 2 x rank values")
             pad_buf = self.torch.tensor([a.get("val", 0.0)]).to(out.dtype).to(self.device)      # the pad value in the storage type
             runs.append((srcs[0], desc(oshape, istr, ones, ones, zeros, [-p for p in pads[:r]], ishape, ostr)))
+        elif t == "SwapDimInner":
+            # SwapDimInner.cpp:17-46 with swap_dim_data (lib/Support/MathUtils.cpp:1539-1564): every axis with an offset is rotated,
+            # out[b] = in[(b + offset) % dim]; the two halves of each such axis are one run each
+            offs = list(a["offset"]) + [0] * (r - len(a["offset"]))
+            axes = [i for i, o in enumerate(offs) if o != 0]
+            if any(not 0 < offs[i] <= ishape[i] for i in axes):
+                raise L.B200QError(L.ERR_INVALID, f"{name}: SwapDimInner offsets must lie inside their axes")
+            for combo in itertools.product((0, 1), repeat=len(axes)):
+                dims, off, dstart = list(ishape), [0] * r, [0] * r
+                for ax, part in zip(axes, combo):
+                    if part == 0:
+                        dims[ax], off[ax] = ishape[ax] - offs[ax], offs[ax]
+                    else:
+                        dims[ax], dstart[ax] = offs[ax], ishape[ax] - offs[ax]
+                if all(d > 0 for d in dims):
+                    runs.append((srcs[0], desc(dims, istr, ones, ones, zeros, off, ishape, ostr, sum(x * y for x, y in zip(dstart, ostr)))))
         elif t == "Depth2Space":
             # Depth2Space.cpp:19-103: the deep tensor's channel is (new_c, l1, l2) in CRD or (l1, l2, new_c) in DCR order (l1, l2
             # swapped in the channel index when swap_cr), the shallow tensor's pixel is (h * bh + l1, w * bw + l2); either tensor
@@ -519,6 +550,41 @@ class module:  # noqa: N801  (name of the reference class)
             if relu:
                 L.check(lib.b200q_top_relu_f32_dev(_P(out), _P(out), out.numel(), limit, stream()))
         return run
+
+    def _plan_gather(self, op, ins, out, iinfo, stream) -> Callable:
+        """Gather / GatherElements of either dialect (lib/Dialect/Top/Interfaces/Gather.cpp:17-49, GatherElements.cpp:20-107).  The
+        indices are the second input (f32 as the reference's interpreter stores them, or i32) or the weight `<name>_indices`."""
+        t, a, lib = op["type"].split(".", 1)[-1], op.get("attrs", {}), self.lib
+        name = op["name"]
+        if op["inputs"][0] in self._nhwc or name in self._nhwc:
+            raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: {op['type']} on channels-last stored tensors")
+        if iinfo[0]["dtype"] != self._info(name)["dtype"]:
+            raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: {op['type']} moves values of one storage type")
+        if len(ins) > 1:
+            idx, idx_shape, idt = ins[1], list(iinfo[1]["shape"]), iinfo[1]["dtype"]
+        else:
+            w = self.weights[name + "_indices"]
+            idt = "i32" if not w.dtype.is_floating_point else "f32"
+            idx = w.to(self.torch.int32 if idt == "i32" else self.torch.float32).contiguous()
+            idx_shape = list(w.shape)
+            self._keep.append(idx)
+        if idt not in ("f32", "i32"):
+            raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: indices must be f32 or i32")
+        is_float = int(idt == "f32")
+        shape = list(iinfo[0]["shape"])
+        ax = int(a.get("axis", 0))
+        ax += len(shape) if ax < 0 else 0
+        eb = out.element_size()
+        if t == "Gather":
+            outer, inner = int(np.prod(shape[:ax])), int(np.prod(shape[ax + 1:]))
+            nidx = int(np.prod(idx_shape)) if idx_shape else 1
+            if out.numel() != outer * nidx * inner:
+                raise L.B200QError(L.ERR_INVALID, f"{name}: output shape does not match the gather")
+            return lambda: L.check(lib.b200q_gather_dev(_P(ins[0]), eb, _P(idx), is_float, _P(out), outer, shape[ax], nidx, inner, stream()))
+        if len(idx_shape) != len(shape) or out.numel() != int(np.prod(idx_shape)):
+            raise L.B200QError(L.ERR_INVALID, f"{name}: GatherElements takes indices of the input's rank and an output of their shape")
+        ss, ish = (C.c_int64 * len(shape))(*shape), (C.c_int64 * len(shape))(*idx_shape)
+        return lambda: L.check(lib.b200q_gather_elements_dev(_P(ins[0]), eb, _P(idx), is_float, _P(out), len(shape), ss, ish, ax, stream()))
 
     def _plan_top(self, op, ins, out, iinfo, stream) -> Callable:
         """fp32 Top-dialect ops (the float graph a calibration pass and the threshold tuner run): top.Conv, top.MatMul,
