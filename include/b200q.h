@@ -284,6 +284,11 @@ int b200q_mulshift_i8_dev(const void *x, int32_t dtype, int64_t count, int32_t m
  * symmetric tpu.MulConst (MulConst.cpp:50-62). */
 int b200q_addconst_i8_dev(const void *x, int32_t dtype, int64_t count, int32_t multiplier, double const_val, int32_t rshift,
                           int32_t in_zp, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
+/* tpu.RequantFp to an integer type (lib/Dialect/Tpu/Interfaces/Common/RequantFp.cpp:17-66): x is f32, or int32 converted to
+ * float the way the reference's interpreter stores it.  TFLite / TFLite_LShift: saturate(to_int(x * scale) + out_zp);
+ * MultiplierShift: saturate(to_int(x * scale + offset)).  The 8-bit float outputs of OnlyScale are not implemented. */
+int b200q_requant_fp_dev(const void *x, int32_t dtype, int64_t count, double scale, double offset, int32_t out_zp,
+                         int32_t quant_mode, int32_t round_mode, int32_t out_dtype, void *out, void *stream);
 /* tpu.PRelu (lib/Dialect/Tpu/Interfaces/Common/PRelu.cpp:35-88); slope index c = (i / inner) % num_slope.  f32 -> f32 with
  * float slopes: x > 0 ? x : x * slope[c].  8-bit -> 8-bit (symmetric) with int8 slopes: x < 0 becomes
  * saturate(RSR(x * slope[c], rshift, half-up)), other values pass through. */

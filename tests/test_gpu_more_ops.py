@@ -389,3 +389,61 @@ def test_tpu_prelu():
     prod = q.astype(np.int64) * qs
     neg = np.clip((prod + 16) >> 5, -128, 127)                                    # round half up
     assert np.array_equal(m.get_raw_tensor("p"), np.where(q < 0, neg, q).astype(np.int8))
+
+
+def _rsr(v, s, half_away):
+    """RightShiftRound on Python integers: half up, or half away from zero."""
+    if s <= 0:
+        return v << (-s)
+    val, mant, half = v >> s, v & ((1 << s) - 1), 1 << (s - 1)
+    if half_away:
+        return val + (1 if (mant >= half if v >= 0 else mant > half) else 0)
+    return val + (1 if mant >= half else 0)
+
+
+def test_tpu_requant_fp_and_int_axis():
+    rng = np.random.default_rng(13)
+    acc = rng.integers(-60000, 60000, (2, 4, 3, 5), dtype=np.int32)
+    acc.ravel()[:4] = [250, -250, 750, -750]                          # ties at scale 0.002 * ... below
+    i32 = dict(shape=list(acc.shape), dtype="i32")
+    # RequantFp, MultiplierShift: to_int(float(x) * scale + offset), half away from zero
+    sc, of = 0.002, 0.5
+    out = dict(shape=list(acc.shape), dtype="i8", scale=1.0, zp=0)
+    m = run_graph({"x": i32, "y": out}, [dict(type="tpu.RequantFp", name="y", inputs=["x"], attrs=dict(scale=sc, offset=of, quant_mode="MultiplierShift"))],
+                  {}, {"x": acc})
+    f = acc.astype(np.float32) * np.float32(sc) + np.float32(of)
+    want = np.clip(np.sign(f) * np.floor(np.abs(f) + np.float32(0.5)), -128, 127).astype(np.int8)
+    assert np.array_equal(m.get_raw_tensor("y"), want)
+    # RequantFp, TFLite: to_int(x * scale) + zp, half to even, uint8 output
+    out = dict(shape=list(acc.shape), dtype="u8", scale=1.0, zp=7)
+    m = run_graph({"x": i32, "y": out}, [dict(type="tpu.RequantFp", name="y", inputs=["x"], attrs=dict(scale=sc, quant_mode="TFLite", round_mode="HalfToEven"))],
+                  {}, {"x": acc})
+    want = np.clip(np.rint(acc.astype(np.float32) * np.float32(sc)).astype(np.int64) + 7, 0, 255).astype(np.uint8)
+    assert np.array_equal(m.get_raw_tensor("y"), want)
+    # RequantIntAxis, MultiplierShift per channel: zp + RSR(x * m, -shift), half away from zero by default
+    table = np.int32([[3, -9, 2], [17, -12, -3], [1, -5, 0], [-5, -10, 1]])
+    out = dict(shape=list(acc.shape), dtype="i8", scale=1.0, zp=0)
+    m = run_graph({"x": i32, "y": out}, [dict(type="tpu.RequantIntAxis", name="y", inputs=["x"], attrs=dict(quant_mode="MultiplierShift"))],
+                  {"y_quant": table}, {"x": acc})
+    want = np.zeros(acc.shape, np.int8)
+    for idx in np.ndindex(*acc.shape):
+        mu, sh, zp = (int(v) for v in table[idx[1]])
+        want[idx] = max(-128, min(127, zp + _rsr(int(acc[idx]) * mu, -sh, True)))
+    assert np.array_equal(m.get_raw_tensor("y"), want)
+    # fused along the last dimension, half up, shift as it stands
+    table = np.int32([[3, 9, 2], [17, 12, -3], [1, 5, 0], [-5, 10, 1], [7, 11, 4]])
+    m = run_graph({"x": i32, "y": out}, [dict(type="tpu.RequantIntAxis", name="y", inputs=["x"],
+                                              attrs=dict(quant_mode="MultiplierShift", fuse_rq_axis=True, round_mode="HalfUp"))],
+                  {"y_quant": table}, {"x": acc})
+    for idx in np.ndindex(*acc.shape):
+        mu, sh, zp = (int(v) for v in table[idx[3]])
+        want[idx] = max(-128, min(127, zp + _rsr(int(acc[idx]) * mu, sh, False)))
+    assert np.array_equal(m.get_raw_tensor("y"), want)
+    # TFLite: zp + MultiplyByQuantizedMultiplier(x, m, shift): RSR(x * m, 31, half up), then RSR by -shift (half away from zero)
+    table = np.int32([[1518500250, -7, 3], [1073741824, -9, -2], [2000000000, -6, 0], [1300000000, -8, 5]])
+    m = run_graph({"x": i32, "y": out}, [dict(type="tpu.RequantIntAxis", name="y", inputs=["x"], attrs=dict(quant_mode="TFLite"))],
+                  {"y_quant": table}, {"x": acc})
+    for idx in np.ndindex(*acc.shape):
+        mu, sh, zp = (int(v) for v in table[idx[1]])
+        want[idx] = max(-128, min(127, zp + _rsr(_rsr(int(acc[idx]) * mu, 31, False), -sh, True)))
+    assert np.array_equal(m.get_raw_tensor("y"), want)

@@ -931,6 +931,17 @@ int b200q_addconst_i8_dev(const void* x, int32_t dtype, int64_t count, int32_t m
   return addconst_i8_launch(x, dtype, count, multiplier, const_val, rshift, in_zp, do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_requant_fp_dev(const void* x, int32_t dtype, int64_t count, double scale, double offset, int32_t out_zp, int32_t quant_mode,
+                         int32_t round_mode, int32_t out_dtype, void* out, void* stream) {
+  if (!x || !out || count < 0 || (dtype != B200Q_DT_I32 && dtype != B200Q_DT_F32) || out_dtype >= B200Q_DT_F32)
+    return set_error(B200Q_ERR_INVALID, "requant_fp_dev: bad argument");
+  const bool tflite = quant_mode == B200Q_QM_TFLITE || quant_mode == B200Q_QM_TFLITE_LSHIFT;
+  if (!tflite && quant_mode != B200Q_QM_MULTIPLIER_SHIFT)
+    return set_error(B200Q_ERR_UNSUPPORTED, "requant_fp_dev: quant mode %d (the 8-bit float outputs of OnlyScale are not implemented)", quant_mode);
+  return requant_fp_launch(x, dtype == B200Q_DT_I32, count, (float)scale, (float)offset, out_zp, tflite, round_mode, out_dtype, out,
+                           static_cast<cudaStream_t>(stream));
+}
+
 int b200q_prelu_dev(const void* x, int32_t dtype, const void* slope, int64_t count, int64_t inner, int32_t num_slope, int32_t rshift,
                     int32_t out_dtype, void* out, void* stream) {
   if (!x || !slope || !out || count < 0 || inner < 1 || num_slope < 1 || rshift < 0 || rshift > 62)

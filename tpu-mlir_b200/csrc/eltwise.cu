@@ -436,6 +436,21 @@ addconst_i8_kernel(const void* __restrict__ x, int dt, long long n, int m, doubl
   st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
 }
 
+// tpu.RequantFp (lib/Dialect/Tpu/Interfaces/Common/RequantFp.cpp:17-66) to an integer type.  The input is the float the reference's
+// interpreter holds (an int32 tensor is converted the way its storage converts it).  tflite != 0: to_int(x * scale) + zp (TFLite,
+// TFLite_LShift); else to_int(x * scale + offset) (MultiplierShift); a float multiply and a float add, not fused.
+__global__ void __launch_bounds__(256)
+requant_fp_kernel(const void* __restrict__ x, int in_is_i32, long long n, float scale, float offset, int zp, int tflite, int rmode,
+                  int out_dt, void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = in_is_i32 ? (float)static_cast<const int32_t*>(x)[i] : static_cast<const float*>(x)[i];
+  int64_t r;
+  if (tflite) r = (int64_t)(int32_t)to_int_f32(__fmul_rn(v, scale), rmode) + zp;
+  else r = (int32_t)to_int_f32(__fadd_rn(__fmul_rn(v, scale), offset), rmode);
+  st_q(out, i, out_dt, (int32_t)clamp_dtype((int64_t)(int32_t)r, out_dt));
+}
+
 // tpu.PRelu (lib/Dialect/Tpu/Interfaces/Common/PRelu.cpp:35-88).  8-bit symmetric: a negative input becomes
 // saturate(RSR(x * slope[c], rshift, half-up)) with int8 slopes, anything else passes through; c = (i / inner) % num_slope.
 __global__ void __launch_bounds__(256)
@@ -720,6 +735,14 @@ int addconst_i8_launch(const void* x, int dt, long long n, int m, double const_v
                        void* out, cudaStream_t s) {
   if (n == 0) return B200Q_OK;
   addconst_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(x, dt, n, m, const_val, sft, in_zp, do_relu, out_dt, out);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int requant_fp_launch(const void* x, int in_is_i32, long long n, float scale, float offset, int zp, int tflite, int rmode, int out_dt,
+                      void* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  requant_fp_kernel<<<nblk(n, 256), 256, 0, s>>>(x, in_is_i32, n, scale, offset, zp, tflite, rmode, out_dt, out);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

@@ -17,6 +17,8 @@ int pool2d_i8_launch(const void* x, int dt, int NC, int ih, int iw, int kh, int 
                      int pwl, int pwr, int mode, int multi, int rshift, int do_relu, int out_dt, void* out, cudaStream_t s);
 // tpu.Lut / tpu.MulShift / tpu.Mul (8-bit, equal shapes)
 int lut_launch(const void* x, long long n, const void* table, int elem_size, void* out, cudaStream_t s);
+int requant_fp_launch(const void* x, int in_is_i32, long long n, float scale, float offset, int zp, int tflite, int rmode, int out_dt,
+                      void* out, cudaStream_t s);
 int prelu_i8_launch(const void* x, int dt, const void* slope, long long n, long long inner, int num_slope, int sft, int out_dt, void* out,
                     cudaStream_t s);
 int prelu_f32_launch(const float* x, const float* slope, long long n, long long inner, int num_slope, float* out, cudaStream_t s);

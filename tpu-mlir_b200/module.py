@@ -32,6 +32,8 @@ import numpy as np
 from . import _lib as L
 
 _DT = {"i8": L.DT_I8, "u8": L.DT_U8, "i32": L.DT_I32, "f32": L.DT_F32}
+_RM = {"HalfAwayFromZero": 0, "HalfUp": 1, "HalfDown": 2, "HalfToEven": 3, "HalfToOdd": 4, "HalfTowardsZero": 5, "TowardsZero": 6,
+       "AwayFromZero": 7, "Up": 8, "Down": 9}
 _QM = {"TFLite_LShift": 0, "TFLite": 1, "MultiplierShift": 2, "OnlyShift": 3, "QDM": 4, "OnlyScale": 5}
 
 
@@ -215,6 +217,38 @@ class module:  # noqa: N801  (name of the reference class)
             if t == "tpu.Reduce" and op.get("attrs", {}).get("mode") == "ReduceMean":
                 top_op["attrs"] = dict(op["attrs"], mode="ReduceMeanRcp")
             return self._plan_top(top_op, ins, out, iinfo, stream)
+        if t in ("tpu.RequantFp", "tpu.RequantIntAxis"):
+            if op["inputs"][0] in self._nhwc or op["name"] in self._nhwc:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: {t} on channels-last stored tensors")
+            n = out.numel()
+            qm, rm = _QM[a["quant_mode"]], _RM[a.get("round_mode", "HalfAwayFromZero")]
+            idt, odt = _DT[iinfo[0]["dtype"]], _DT[oinfo["dtype"]]
+            if t == "tpu.RequantFp":
+                sc, of, zp = float(a["scale"]), float(a.get("offset", 0.0)), int(oinfo.get("zp", 0))
+                return lambda: L.check(lib.b200q_requant_fp_dev(_P(ins[0]), idt, n, sc, of, zp, qm, rm, odt, _P(out), stream()))
+            # RequantIntAxis.cpp:16-125, quant operand [C][3] = (multiplier, shift, zero point) (the BM1684X layout, :45-48)
+            if iinfo[0]["dtype"] != "i32":
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.RequantIntAxis takes an int32 tensor here")
+            shape = list(oinfo["shape"])
+            fuse = bool(a.get("fuse_rq_axis", False))
+            ch = shape[-1] if fuse else shape[1]
+            inner = 1 if fuse else (int(np.prod(shape[2:])) if len(shape) > 2 else 1)
+            outer = n // (ch * inner)
+            table = self.weights[op["name"] + "_quant"].to(self.torch.int32).reshape(-1)
+            if table.numel() != 3 * ch:
+                raise L.B200QError(L.ERR_INVALID, f"{op['name']}: the quant table must hold (multiplier, shift, zero point) per channel")
+            table = table.reshape(ch, 3)
+            tf = qm in (L.QM_TFLITE, L.QM_TFLITE_LSHIFT)
+            if not tf and qm != L.QM_MULTIPLIER_SHIFT:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.RequantIntAxis quant_mode {a['quant_mode']}")
+            mu = table[:, 0].contiguous()
+            sh = (table[:, 1] if (tf or fuse) else -table[:, 1]).contiguous()          # :96-98 negates the shift word; :73-87 does not
+            zp = table[:, 2].contiguous()
+            self._keep.append((mu, sh, zp))
+            dialect = L.RQ_QDM if tf else L.RQ_MULTIPLIER_SHIFT
+            izp = int(iinfo[0].get("zp", 0))
+            return lambda: L.check(lib.b200q_requant_int_axis_dev(_P(ins[0]), outer, ch, inner, _P(mu), _P(sh), _P(zp), dialect, rm, izp, odt,
+                                                                  _P(out), stream()))
         if t == "tpu.PRelu":
             fl = oinfo["dtype"] == "f32"
             w = self.weights[op["name"] + "_slope"]
