@@ -514,6 +514,15 @@ typedef struct {
 } b200q_remap_desc;
 int b200q_remap_dev(const void *src, void *dst, int32_t elem_bytes, const b200q_remap_desc *desc, const void *pad_value,
                     void *stream);
+/* top::ArgOp / tpu::ArgOp (lib/Dialect/Top/Interfaces/Arg.cpp:39-83): over x [outer, axis, inner] the index of the maximum
+ * (is_max) or minimum along the axis, as float or int32, and the value itself when `values` is not NULL; ties keep the first
+ * index, or the last when select_last_index. */
+int b200q_arg_f32_dev(const float *x, int64_t outer, int32_t axis, int64_t inner, int32_t is_max, int32_t select_last_index,
+                      void *indices, int32_t index_is_float, float *values, void *stream);
+/* top::CastOp (lib/Dialect/Top/Interfaces/Cast.cpp:18-68): saturate(to_int(x, round_mode)) to `to_dtype` (a b200q_dtype; F32
+ * copies), stored as float like the reference's tensors (out_dtype F32) or in the integer type itself (out_dtype = to_dtype). */
+int b200q_top_cast_f32_dev(const float *x, int64_t count, int32_t to_dtype, int32_t round_mode, int32_t out_dtype, void *out,
+                           void *stream);
 /* top::GatherOp / tpu::GatherOp (lib/Dialect/Top/Interfaces/Gather.cpp:17-49): dst[o, j, k] = src[o, indices[j], k] over
  * src [outer, axis_dim, inner]; a negative index counts from the end.  top::GatherElementsOp (GatherElements.cpp:20-79): dst
  * has the shape of `indices` and takes src at the same coordinate except on `axis`, where the index stands (rank <= 8).

@@ -447,3 +447,32 @@ def test_tpu_requant_fp_and_int_axis():
         mu, sh, zp = (int(v) for v in table[idx[1]])
         want[idx] = max(-128, min(127, zp + _rsr(_rsr(int(acc[idx]) * mu, 31, False), -sh, True)))
     assert np.array_equal(m.get_raw_tensor("y"), want)
+
+
+def test_arg_and_top_cast():
+    rng = np.random.default_rng(14)
+    x = rng.integers(-3, 4, (3, 9, 5)).astype(np.float32)             # many ties
+    for mode, last in (("ArgMax", True), ("ArgMax", False), ("ArgMin", True), ("ArgMin", False)):
+        ops = [dict(type="top.Arg", name="idx", values="val", inputs=["x"], attrs=dict(axis=1, keepdims=True, mode=mode, select_last_index=last))]
+        m = run_graph({"x": f32(x.shape), "idx": f32((3, 1, 5)), "val": f32((3, 1, 5))}, ops, {}, {"x": x})
+        ext = x.max(axis=1) if mode == "ArgMax" else x.min(axis=1)
+        hit = x == ext[:, None, :]
+        first = hit.argmax(axis=1)
+        want = (x.shape[1] - 1 - hit[:, ::-1, :].argmax(axis=1)) if last else first
+        assert np.array_equal(m.get_tensor("idx").reshape(3, 5), want.astype(np.float32)), (mode, last)
+        assert np.array_equal(m.get_tensor("val").reshape(3, 5), ext)
+    ops = [dict(type="tpu.Arg", name="idx", inputs=["x"], attrs=dict(axis=-1, keepdims=False, mode="ArgMin", select_last_index=False))]
+    m = run_graph({"x": f32(x.shape), "idx": dict(shape=[3, 9], dtype="i32")}, ops, {}, {"x": x})
+    assert np.array_equal(m.get_raw_tensor("idx"), x.argmin(axis=2).astype(np.int32))
+    v = np.float32([-300.5, -128.5, -2.5, -1.5, -0.5, 0.5, 1.5, 2.5, 126.5, 127.5, 255.5, 300.2, 40000.7, -40000.7]).reshape(1, -1)
+    away = np.sign(v) * np.floor(np.abs(v) + np.float32(0.5))
+    cases = [("INT8", "HalfAwayFromZero", np.clip(away, -128, 127)), ("UINT8", "HalfToEven", np.clip(np.rint(v), 0, 255)),
+             ("INT16", "Down", np.clip(np.floor(v), -32768, 32767)), ("UINT16", "Up", np.clip(np.ceil(v), 0, 65535)),
+             ("INT32", "TowardsZero", np.trunc(v)), ("F32", "HalfAwayFromZero", v)]
+    for to, rm, want in cases:
+        ops = [dict(type="top.Cast", name="y", inputs=["x"], attrs=dict(to=to, round_mode=rm))]
+        m = run_graph({"x": f32(v.shape), "y": f32(v.shape)}, ops, {}, {"x": v})
+        assert np.array_equal(m.get_tensor("y"), want.astype(np.float32)), to
+    m = run_graph({"x": f32(v.shape), "y": dict(shape=list(v.shape), dtype="i8", scale=1.0, zp=0)},
+                  [dict(type="top.Cast", name="y", inputs=["x"], attrs=dict(to="INT8"))], {}, {"x": v})
+    assert np.array_equal(m.get_raw_tensor("y"), np.clip(away, -128, 127).astype(np.int8))

@@ -195,6 +195,20 @@ int b200q_top_layernorm_f32_dev(const float* x, const float* weight, const float
   return top_layernorm_launch(x, weight, bias, y, outer, inner, eps, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_arg_f32_dev(const float* x, int64_t outer, int32_t axis, int64_t inner, int32_t is_max, int32_t select_last_index, void* indices,
+                      int32_t index_is_float, float* values, void* stream) {
+  if (!x || !indices || outer < 0 || axis < 1 || inner < 1) return set_error(B200Q_ERR_INVALID, "arg_f32_dev: bad argument");
+  return top_arg_launch(x, outer, axis, inner, is_max != 0, select_last_index != 0, indices, index_is_float != 0, values,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int b200q_top_cast_f32_dev(const float* x, int64_t count, int32_t to_dtype, int32_t round_mode, int32_t out_dtype, void* out, void* stream) {
+  if (!x || !out || count < 0) return set_error(B200Q_ERR_INVALID, "top_cast_f32_dev: bad argument");
+  if (to_dtype < B200Q_DT_I8 || to_dtype > B200Q_DT_F32 || (out_dtype != B200Q_DT_F32 && out_dtype != to_dtype))
+    return set_error(B200Q_ERR_INVALID, "top_cast_f32_dev: the output is stored as float or in the target type");
+  return top_cast_launch(x, count, to_dtype, round_mode, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_gather_dev(const void* src, int32_t elem_bytes, const void* indices, int32_t index_is_float, void* dst, int64_t outer,
                      int64_t axis_dim, int64_t num_indices, int64_t inner, void* stream) {
   if (!src || !indices || !dst || outer < 0 || axis_dim < 1 || num_indices < 0 || inner < 0)

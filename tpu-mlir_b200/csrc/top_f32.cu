@@ -18,6 +18,7 @@
 #include <string.h>
 
 #include "internal.h"
+#include "requant.cuh"
 #include "top_f32.h"
 
 namespace b200q {
@@ -531,6 +532,50 @@ __global__ void reduce_f32_kernel(int mode, const float* __restrict__ x, float* 
   y[i] = v;
 }
 
+// top::ArgOp / tpu::ArgOp (lib/Dialect/Top/Interfaces/Arg.cpp:39-83): along the middle dimension of [outer, axis, inner] the index
+// (and, if asked, the value) of the maximum or minimum; a tie keeps the first index, or the last with select_last_index (the
+// comparison is then >= / <=).  One thread per output walks the axis in order, like the reference's loop.
+__global__ void arg_f32_kernel(const float* __restrict__ x, long long outer, int axis, long long inner, int is_max, int select_last,
+                               void* __restrict__ idx_out, int idx_is_float, float* __restrict__ val_out) {
+  const long long n = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= outer * inner) return;
+  const float* p = x + (n / inner) * axis * inner + (n % inner);
+  float best = p[0];
+  int at = 0;
+  for (int a = 1; a < axis; ++a) {
+    const float v = p[(long long)a * inner];
+    const bool take = is_max ? (select_last ? v >= best : v > best) : (select_last ? v <= best : v < best);
+    if (take) {
+      best = v;
+      at = a;
+    }
+  }
+  if (idx_is_float) static_cast<float*>(idx_out)[n] = (float)at;
+  else static_cast<int*>(idx_out)[n] = at;
+  if (val_out) val_out[n] = best;
+}
+
+// top::CastOp (lib/Dialect/Top/Interfaces/Cast.cpp:18-68): to an integer type, saturate(to_int(x, round_mode)); the result is
+// written as a float (the reference's storage) or in the integer type itself.  `to` F32 copies.
+__global__ void top_cast_kernel(const float* __restrict__ x, long long n, int to_dt, int rmode, int out_dt, void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = x[i];
+  if (to_dt == B200Q_DT_F32) {
+    static_cast<float*>(out)[i] = v;
+    return;
+  }
+  const long long r = clamp_dtype(to_int_f32(v, rmode), to_dt);
+  switch (out_dt) {
+    case B200Q_DT_F32: static_cast<float*>(out)[i] = (float)r; break;
+    case B200Q_DT_I8: static_cast<int8_t*>(out)[i] = (int8_t)r; break;
+    case B200Q_DT_U8: static_cast<uint8_t*>(out)[i] = (uint8_t)r; break;
+    case B200Q_DT_I16: static_cast<int16_t*>(out)[i] = (int16_t)r; break;
+    case B200Q_DT_U16: static_cast<uint16_t*>(out)[i] = (uint16_t)r; break;
+    default: static_cast<int32_t*>(out)[i] = (int32_t)r; break;
+  }
+}
+
 // top::GatherOp / tpu::GatherOp (lib/Dialect/Top/Interfaces/Gather.cpp:17-49): dst[o, j, k] = src[o, idx[j], k], a negative
 // index counts from the end of the axis.  Indices are floats (the interpreter's storage) or int32.  An index outside the axis
 // writes zero instead of reading outside the tensor.
@@ -649,6 +694,22 @@ int top_layernorm_launch(const float* x, const float* w, const float* b, float* 
   if (outer == 0 || inner == 0) return B200Q_OK;
   if (outer > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "layernorm: too many rows");
   layernorm_f32_kernel<<<(unsigned)outer, 256, 0, s>>>(x, w, b, y, inner, eps);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_arg_launch(const float* x, long long outer, int axis, long long inner, bool is_max, bool select_last, void* idx_out,
+                   bool idx_is_float, float* val_out, cudaStream_t s) {
+  const long long n = outer * inner;
+  if (n == 0) return B200Q_OK;
+  arg_f32_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(x, outer, axis, inner, is_max, select_last, idx_out, idx_is_float, val_out);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_cast_launch(const float* x, long long n, int to_dt, int rmode, int out_dt, void* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  top_cast_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, n, to_dt, rmode, out_dt, out);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

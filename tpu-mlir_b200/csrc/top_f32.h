@@ -52,6 +52,9 @@ struct TopRemap {   // layout-compatible with b200q_remap_desc
       off[TOP_REMAP_DIMS], extent[TOP_REMAP_DIMS], dst_stride[TOP_REMAP_DIMS];
   long long dst_offset;
 };
+int top_arg_launch(const float* x, long long outer, int axis, long long inner, bool is_max, bool select_last, void* idx_out,
+                   bool idx_is_float, float* val_out, cudaStream_t s);
+int top_cast_launch(const float* x, long long n, int to_dt, int rmode, int out_dt, void* out, cudaStream_t s);
 int top_gather_launch(const void* src, int elem_bytes, const void* indices, bool index_is_float, void* dst, long long outer,
                       long long axis_dim, long long num_indices, long long inner, cudaStream_t s);
 int top_gather_elements_launch(const void* src, int elem_bytes, const void* indices, bool index_is_float, void* dst, int ndim,

@@ -207,6 +207,32 @@ class module:  # noqa: N801  (name of the reference class)
         stream = lambda: C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)  # noqa: E731
         if t.split(".", 1)[-1] in _MOVE_OPS:
             return self._plan_move(op, stream)
+        if t in ("top.Arg", "tpu.Arg"):
+            # Arg.cpp:39-83; the op's own tensor holds the indices (f32 as the reference stores them, or i32), the optional
+            # `values` entry of the op names the tensor of the extreme values
+            if iinfo[0]["dtype"] != "f32" or oinfo["dtype"] not in ("f32", "i32") or op["inputs"][0] in self._nhwc:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: {t} takes an f32 NCHW tensor and writes f32 or i32 indices")
+            if a["mode"] not in ("ArgMax", "ArgMin"):
+                raise L.B200QError(L.ERR_INVALID, f"{op['name']}: mode {a['mode']}")
+            shape = list(iinfo[0]["shape"])
+            ax = int(a["axis"])
+            ax += len(shape) if ax < 0 else 0
+            outer, inner = int(np.prod(shape[:ax])), int(np.prod(shape[ax + 1:]))
+            vals = self.tensors[op["values"]] if op.get("values") else None
+            if out.numel() != outer * inner or (vals is not None and (vals.numel() != outer * inner or self._info(op["values"])["dtype"] != "f32")):
+                raise L.B200QError(L.ERR_INVALID, f"{op['name']}: output shapes do not match the reduction")
+            is_max, last, isf = int(a["mode"] == "ArgMax"), int(bool(a.get("select_last_index", True))), int(oinfo["dtype"] == "f32")
+            return lambda: L.check(lib.b200q_arg_f32_dev(_P(ins[0]), outer, shape[ax], inner, is_max, last, _P(out), isf, _P(vals), stream()))
+        if t == "top.Cast":
+            # Cast.cpp:18-68
+            to = {"INT8": "i8", "UINT8": "u8", "INT16": "i16", "UINT16": "u16", "INT32": "i32", "UINT32": "i32", "F32": "f32"}.get(a.get("to", ""))
+            codes = dict(_DT, i16=L.DT_I16, u16=L.DT_U16)
+            if to is None or iinfo[0]["dtype"] != "f32" or oinfo["dtype"] not in ("f32", to):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: top.Cast to '{a.get('to')}' from {iinfo[0]['dtype']} into {oinfo['dtype']}")
+            if (op["inputs"][0] in self._nhwc) != (op["name"] in self._nhwc):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: top.Cast between differently stored tensors")
+            n, rm = out.numel(), _RM[a.get("round_mode", "HalfAwayFromZero")]
+            return lambda: L.check(lib.b200q_top_cast_f32_dev(_P(ins[0]), n, codes[to], rm, codes[oinfo["dtype"]], _P(out), stream()))
         if t.split(".", 1)[-1] in ("Gather", "GatherElements"):
             return self._plan_gather(op, ins, out, iinfo, stream)
         if t.startswith("top."):
