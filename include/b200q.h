@@ -514,6 +514,11 @@ typedef struct {
 } b200q_remap_desc;
 int b200q_remap_dev(const void *src, void *dst, int32_t elem_bytes, const b200q_remap_desc *desc, const void *pad_value,
                     void *stream);
+/* top::GridSamplerOp / tpu::GridSamplerOp with a 4-D grid (GridSamplerFunc::invoke, lib/Support/GenericCpuFunc.cpp:3390-3455):
+ * x [n, c, ih, iw], grid [n, oh, ow, 2] of (x, y) in [-1, 1], y [n, c, oh, ow]; mode 0 bilinear / 1 nearest, padding_mode 0 zeros /
+ * 1 border / 2 reflection (the reference's numbering).  5-D grids are not implemented. */
+int b200q_grid_sampler_f32_dev(const float *x, const float *grid, float *y, int32_t n, int32_t c, int32_t ih, int32_t iw,
+                               int32_t oh, int32_t ow, int32_t mode, int32_t padding_mode, int32_t align_corners, void *stream);
 /* top::ArgOp / tpu::ArgOp (lib/Dialect/Top/Interfaces/Arg.cpp:39-83): over x [outer, axis, inner] the index of the maximum
  * (is_max) or minimum along the axis, as float or int32, and the value itself when `values` is not NULL; ties keep the first
  * index, or the last when select_last_index. */

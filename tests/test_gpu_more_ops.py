@@ -476,3 +476,62 @@ def test_arg_and_top_cast():
     m = run_graph({"x": f32(v.shape), "y": dict(shape=list(v.shape), dtype="i8", scale=1.0, zp=0)},
                   [dict(type="top.Cast", name="y", inputs=["x"], attrs=dict(to="INT8"))], {}, {"x": v})
     assert np.array_equal(m.get_raw_tensor("y"), np.clip(away, -128, 127).astype(np.int8))
+
+
+def grid_sampler_ref(x, grid, mode, padding, align):
+    """GridSamplerFunc::invoke for a 4-D grid (lib/Support/GenericCpuFunc.cpp:3332-3455) in numpy float32 scalars."""
+    f = np.float32
+    N, C, IH, IW = x.shape
+    OH, OW = grid.shape[1:3]
+
+    def clip(v, lim):
+        return min(f(lim - 1), max(v, f(0)))
+
+    def reflect(v, lo2, hi2):
+        if lo2 == hi2:
+            return f(0)
+        mn, span = f(lo2) / f(2), f(hi2 - lo2) / f(2)
+        v = f(abs(f(v - mn)))
+        extra = f(math.fmod(v, span))
+        flips = int(math.floor(f(v / span)))
+        return f(extra + mn) if flips % 2 == 0 else f(f(span - extra) + mn)
+
+    def index(coord, size):
+        r = f(f(f(coord + f(1)) * f(.5)) * f(size - 1)) if align else f(f(f(f(coord + f(1)) * f(size)) - f(1)) * f(.5))
+        if padding == 1:
+            r = clip(r, size)
+        elif padding == 2:
+            r = clip(reflect(r, 0, 2 * (size - 1)) if align else reflect(r, -1, 2 * size - 1), size)
+        return f(r)
+    y = np.zeros((N, C, OH, OW), np.float32)
+    for n in range(N):
+        for h in range(OH):
+            for w in range(OW):
+                fx, fy = index(grid[n, h, w, 0], IW), index(grid[n, h, w, 1], IH)
+                if mode == 0:
+                    xx, yy = int(math.floor(fx)), int(math.floor(fy))
+                    dx, dy = f(fx - f(xx)), f(fy - f(yy))
+                    tx, ty = f(f(1) - dx), f(f(1) - dy)
+                    for c in range(C):
+                        o = f(0)
+                        for (py, px, wt) in ((yy, xx, f(tx * ty)), (yy, xx + 1, f(dx * ty)), (yy + 1, xx, f(tx * dy)), (yy + 1, xx + 1, f(dx * dy))):
+                            if 0 <= py < IH and 0 <= px < IW:
+                                o = f(o + f(x[n, c, py, px] * wt))
+                        y[n, c, h, w] = o
+                else:
+                    xx, yy = int(np.rint(fx)), int(np.rint(fy))
+                    if 0 <= yy < IH and 0 <= xx < IW:
+                        y[n, :, h, w] = x[n, :, yy, xx]
+    return y
+
+
+@pytest.mark.parametrize("mode,padding,align", [(0, 0, False), (0, 1, True), (0, 2, False), (0, 2, True), (1, 0, True), (1, 2, False)])
+def test_grid_sampler(mode, padding, align):
+    rng = np.random.default_rng(15)
+    x = rng.standard_normal((2, 3, 5, 7)).astype(np.float32)
+    grid = (rng.random((2, 4, 6, 2)) * 3 - 1.5).astype(np.float32)          # some samples fall outside [-1, 1]
+    grid[0, 0, 0] = [-1, 1]
+    grid[0, 0, 1] = [0, 0]
+    ops = [dict(type="top.GridSampler", name="y", inputs=["x", "g"], attrs=dict(mode=mode, padding_mode=padding, align_corners=align))]
+    m = run_graph({"x": f32(x.shape), "g": f32(grid.shape), "y": f32((2, 3, 4, 6))}, ops, {}, {"x": x, "g": grid})
+    assert np.array_equal(m.get_tensor("y"), grid_sampler_ref(x, grid, mode, padding, align))

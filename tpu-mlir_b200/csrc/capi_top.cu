@@ -195,6 +195,12 @@ int b200q_top_layernorm_f32_dev(const float* x, const float* weight, const float
   return top_layernorm_launch(x, weight, bias, y, outer, inner, eps, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_grid_sampler_f32_dev(const float* x, const float* grid, float* y, int32_t n, int32_t c, int32_t ih, int32_t iw, int32_t oh, int32_t ow,
+                               int32_t mode, int32_t padding_mode, int32_t align_corners, void* stream) {
+  if (!x || !grid || !y || n < 0 || c < 0 || ih < 1 || iw < 1 || oh < 0 || ow < 0) return set_error(B200Q_ERR_INVALID, "grid_sampler_f32_dev: bad argument");
+  return top_grid_sampler_launch(x, grid, y, n, c, ih, iw, oh, ow, mode, padding_mode, align_corners != 0, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_arg_f32_dev(const float* x, int64_t outer, int32_t axis, int64_t inner, int32_t is_max, int32_t select_last_index, void* indices,
                       int32_t index_is_float, float* values, void* stream) {
   if (!x || !indices || outer < 0 || axis < 1 || inner < 1) return set_error(B200Q_ERR_INVALID, "arg_f32_dev: bad argument");

@@ -532,6 +532,51 @@ __global__ void reduce_f32_kernel(int mode, const float* __restrict__ x, float* 
   y[i] = v;
 }
 
+// top::GridSamplerOp / tpu::GridSamplerOp with a 4-D grid [N, OH, OW, 2] (GridSamplerFunc, lib/Support/GenericCpuFunc.cpp:3332-3455):
+// mode 0 bilinear, 1 nearest (nearbyint); padding 0 zeros, 1 border, 2 reflection.  Float arithmetic in the reference's order,
+// products and sums kept apart.
+__device__ __forceinline__ float grid_clip(float v, int limit) { return fminf((float)(limit - 1), fmaxf(v, 0.f)); }
+__device__ __forceinline__ float grid_reflect(float v, int twice_low, int twice_high) {
+  if (twice_low == twice_high) return 0.f;
+  const float mn = __fdiv_rn((float)twice_low, 2.f), span = __fdiv_rn((float)(twice_high - twice_low), 2.f);
+  v = fabsf(__fsub_rn(v, mn));
+  const float extra = fmodf(v, span);
+  const int flips = (int)floorf(__fdiv_rn(v, span));
+  return (flips % 2 == 0) ? __fadd_rn(extra, mn) : __fadd_rn(__fsub_rn(span, extra), mn);
+}
+__device__ __forceinline__ float grid_index(float coord, int size, int padding, int align) {
+  float r = align ? __fmul_rn(__fmul_rn(__fadd_rn(coord, 1.f), .5f), (float)(size - 1))
+                  : __fmul_rn(__fsub_rn(__fmul_rn(__fadd_rn(coord, 1.f), (float)size), 1.f), .5f);
+  if (padding == 1) r = grid_clip(r, size);
+  else if (padding == 2) r = grid_clip(align ? grid_reflect(r, 0, 2 * (size - 1)) : grid_reflect(r, -1, 2 * size - 1), size);
+  return r;
+}
+__global__ void grid_sampler_f32_kernel(const float* __restrict__ x, const float* __restrict__ grid, float* __restrict__ y, int N, int C,
+                                        int IH, int IW, int OH, int OW, int mode, int padding, int align) {
+  const long long total = (long long)N * C * OH * OW;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int w = (int)(i % OW), h = (int)((i / OW) % OH), c = (int)((i / ((long long)OW * OH)) % C), n = (int)(i / ((long long)OW * OH * C));
+  const float* g = grid + (((long long)n * OH + h) * OW + w) * 2;
+  const float fx = grid_index(g[0], IW, padding, align), fy = grid_index(g[1], IH, padding, align);
+  const float* in = x + ((long long)n * C + c) * IH * IW;
+  float o = 0.f;
+  if (mode == 0) {
+    const int xx = (int)floorf(fx), yy = (int)floorf(fy);
+    const float dx = __fsub_rn(fx, (float)xx), dy = __fsub_rn(fy, (float)yy), tx = __fsub_rn(1.f, dx), ty = __fsub_rn(1.f, dy);
+    const bool y0 = yy >= 0 && yy < IH, y1 = yy + 1 >= 0 && yy + 1 < IH, x0 = xx >= 0 && xx < IW, x1 = xx + 1 >= 0 && xx + 1 < IW;
+    const long long at = (long long)yy * IW + xx;
+    if (y0 && x0) o = __fadd_rn(o, __fmul_rn(in[at], __fmul_rn(tx, ty)));
+    if (y0 && x1) o = __fadd_rn(o, __fmul_rn(in[at + 1], __fmul_rn(dx, ty)));
+    if (y1 && x0) o = __fadd_rn(o, __fmul_rn(in[at + IW], __fmul_rn(tx, dy)));
+    if (y1 && x1) o = __fadd_rn(o, __fmul_rn(in[at + IW + 1], __fmul_rn(dx, dy)));
+  } else {
+    const int xx = (int)rintf(fx), yy = (int)rintf(fy);
+    if (yy >= 0 && yy < IH && xx >= 0 && xx < IW) o = in[(long long)yy * IW + xx];
+  }
+  y[i] = o;
+}
+
 // top::ArgOp / tpu::ArgOp (lib/Dialect/Top/Interfaces/Arg.cpp:39-83): along the middle dimension of [outer, axis, inner] the index
 // (and, if asked, the value) of the maximum or minimum; a tie keeps the first index, or the last with select_last_index (the
 // comparison is then >= / <=).  One thread per output walks the axis in order, like the reference's loop.
@@ -694,6 +739,16 @@ int top_layernorm_launch(const float* x, const float* w, const float* b, float* 
   if (outer == 0 || inner == 0) return B200Q_OK;
   if (outer > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "layernorm: too many rows");
   layernorm_f32_kernel<<<(unsigned)outer, 256, 0, s>>>(x, w, b, y, inner, eps);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int top_grid_sampler_launch(const float* x, const float* grid, float* y, int N, int C, int IH, int IW, int OH, int OW, int mode, int padding,
+                            bool align_corners, cudaStream_t s) {
+  const long long total = (long long)N * C * OH * OW;
+  if (total == 0) return B200Q_OK;
+  if (mode < 0 || mode > 1 || padding < 0 || padding > 2) return set_error(B200Q_ERR_INVALID, "grid_sampler: mode %d, padding %d", mode, padding);
+  grid_sampler_f32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, grid, y, N, C, IH, IW, OH, OW, mode, padding, align_corners);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

@@ -207,6 +207,15 @@ class module:  # noqa: N801  (name of the reference class)
         stream = lambda: C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)  # noqa: E731
         if t.split(".", 1)[-1] in _MOVE_OPS:
             return self._plan_move(op, stream)
+        if t in ("top.GridSampler", "tpu.GridSampler"):
+            gshape = list(iinfo[1]["shape"])
+            if any(i["dtype"] != "f32" for i in iinfo) or oinfo["dtype"] != "f32" or len(gshape) != 4 or gshape[3] != 2 \
+                    or any(nm in self._nhwc for nm in list(op["inputs"]) + [op["name"]]):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: {t} takes f32 NCHW tensors and a [N, OH, OW, 2] grid")
+            nb, ch, ih, iw = iinfo[0]["shape"]
+            oh, ow = gshape[1], gshape[2]
+            mode, pad, al = int(a.get("mode", 0)), int(a.get("padding_mode", 0)), int(bool(a.get("align_corners", False)))
+            return lambda: L.check(lib.b200q_grid_sampler_f32_dev(_P(ins[0]), _P(ins[1]), _P(out), nb, ch, ih, iw, oh, ow, mode, pad, al, stream()))
         if t in ("top.Arg", "tpu.Arg"):
             # Arg.cpp:39-83; the op's own tensor holds the indices (f32 as the reference stores them, or i32), the optional
             # `values` entry of the op names the tensor of the extreme values
