@@ -514,6 +514,11 @@ typedef struct {
 } b200q_remap_desc;
 int b200q_remap_dev(const void *src, void *dst, int32_t elem_bytes, const b200q_remap_desc *desc, const void *pad_value,
                     void *stream);
+/* top::InterpOp / tpu::InterpOp, modes "nearest" (0) and "linear" (1), over nc = n * c planes [ih, iw] -> [oh, ow]
+ * (lib/Dialect/Top/Interfaces/Interp.cpp:28-181,:226-287).  coord_mode: 0 half_pixel, 1 pytorch_half_pixel, 2 align_corners,
+ * 3 asymmetric; platform (module::getPlatform() of the model): 0 ONNX or any other, 1 TORCH, 2 TFLITE, 3 CAFFE. */
+int b200q_interp_f32_dev(const float *x, float *y, int64_t nc, int32_t ih, int32_t iw, int32_t oh, int32_t ow, int32_t mode,
+                         int32_t coord_mode, int32_t platform, void *stream);
 /* top::GridSamplerOp / tpu::GridSamplerOp with a 4-D grid (GridSamplerFunc::invoke, lib/Support/GenericCpuFunc.cpp:3390-3455):
  * x [n, c, ih, iw], grid [n, oh, ow, 2] of (x, y) in [-1, 1], y [n, c, oh, ow]; mode 0 bilinear / 1 nearest, padding_mode 0 zeros /
  * 1 border / 2 reflection (the reference's numbering).  5-D grids are not implemented. */

@@ -535,3 +535,71 @@ def test_grid_sampler(mode, padding, align):
     ops = [dict(type="top.GridSampler", name="y", inputs=["x", "g"], attrs=dict(mode=mode, padding_mode=padding, align_corners=align))]
     m = run_graph({"x": f32(x.shape), "g": f32(grid.shape), "y": f32((2, 3, 4, 6))}, ops, {}, {"x": x, "g": grid})
     assert np.array_equal(m.get_tensor("y"), grid_sampler_ref(x, grid, mode, padding, align))
+
+
+def interp_ref(x, oh, ow, mode, coord_mode, platform):
+    """interp_core with the mode resolution of InterpOp::inference (lib/Dialect/Top/Interfaces/Interp.cpp:28-181,:226-287)."""
+    f = np.float32
+    coord = {"half_pixel": 0, "pytorch_half_pixel": 1, "align_corners": 2, "asymmetric": 3}[coord_mode]
+    if mode == "nearest":
+        sp = {"CAFFE": "caffe_nearest", "TORCH": "pytorch_nearest", "TFLITE": "tf_nearest"}.get(platform, "onnx_nearest")
+        align, half = coord != 3, False
+    else:
+        sp = "caffe" if platform == "CAFFE" else "pytorch"
+        align, half = coord == 2, coord in (0, 1)
+
+    def scale(i, o):
+        if sp in ("caffe", "caffe_nearest") or (sp in ("tf_nearest", "pytorch", "onnx_nearest") and align):
+            if o <= 1:
+                return f(0)
+            i, o = i - 1, o - 1
+        return f(i) / f(o)
+
+    def bmap(o, sc, d):
+        o, hi = f(o), f(d - 1)
+        clampf = lambda v: min(max(f(v), f(0)), hi)  # noqa: E731
+        rnd = lambda v: int(math.floor(abs(v) + 0.5) * (1 if v >= 0 else -1))  # noqa: E731
+        if sp == "tf_nearest":
+            xs = clampf(f(f(o + f(.5)) * sc) if half else f(o * sc))
+            return xs, (rnd(xs) if align else int(math.floor(xs)))
+        if sp == "pytorch":
+            xs = clampf(f(o * sc) if align else f(f(f(o + f(.5)) * sc) - f(.5)))
+            return xs, int(math.floor(xs))
+        if sp == "onnx_nearest" and not half:
+            xs = clampf(f(o * sc))
+            return xs, (rnd(xs) if align else int(math.floor(xs)))
+        xs = clampf(f(o * sc))
+        return xs, int(math.floor(xs))
+    n, c, ih, iw = x.shape
+    hs, ws = scale(ih, oh), scale(iw, ow)
+    Y = [bmap(o, hs, ih) for o in range(oh)]
+    X = [bmap(o, ws, iw) for o in range(ow)]
+    out = np.zeros((n, c, oh, ow), np.float32)
+    for p_ in range(n):
+        for q_ in range(c):
+            src = x[p_, q_]
+            if sp in ("pytorch", "caffe"):
+                buf = np.zeros((oh, iw), np.float32)
+                for yo, (ys, yi) in enumerate(Y):
+                    buf[yo] = src[ih - 1] if yi == ih - 1 else src[yi] + f(ys - f(yi)) * (src[yi + 1] - src[yi])
+                for xo, (xs, xi) in enumerate(X):
+                    out[p_, q_, :, xo] = buf[:, iw - 1] if xi == iw - 1 else buf[:, xi] + f(xs - f(xi)) * (buf[:, xi + 1] - buf[:, xi])
+            else:
+                for yo, (_, yi) in enumerate(Y):
+                    for xo, (_, xi) in enumerate(X):
+                        out[p_, q_, yo, xo] = src[yi, xi]
+    return out
+
+
+@pytest.mark.parametrize("mode,coord,platform,osz", [("linear", "half_pixel", "ONNX", (9, 11)), ("linear", "align_corners", "ONNX", (9, 11)),
+                                                     ("linear", "asymmetric", "TORCH", (3, 4)), ("linear", "pytorch_half_pixel", "CAFFE", (10, 14)),
+                                                     ("nearest", "asymmetric", "ONNX", (10, 14)), ("nearest", "half_pixel", "ONNX", (9, 11)),
+                                                     ("nearest", "half_pixel", "TORCH", (7, 5)), ("nearest", "align_corners", "TFLITE", (8, 13)),
+                                                     ("nearest", "half_pixel", "CAFFE", (1, 1))])
+def test_interp(mode, coord, platform, osz):
+    rng = np.random.default_rng(16)
+    x = rng.standard_normal((2, 3, 5, 7)).astype(np.float32)
+    for tname in ("top.Interp", "tpu.Interp"):
+        ops = [dict(type=tname, name="y", inputs=["x"], attrs=dict(mode=mode, coord_mode=coord, platform=platform, scale_h=osz[0] / 5, scale_w=osz[1] / 7))]
+        m = run_graph({"x": f32(x.shape), "y": f32((2, 3) + osz)}, ops, {}, {"x": x})
+        assert np.array_equal(m.get_tensor("y"), interp_ref(x, osz[0], osz[1], mode, coord, platform)), tname

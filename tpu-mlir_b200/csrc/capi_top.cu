@@ -195,6 +195,12 @@ int b200q_top_layernorm_f32_dev(const float* x, const float* weight, const float
   return top_layernorm_launch(x, weight, bias, y, outer, inner, eps, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_interp_f32_dev(const float* x, float* y, int64_t nc, int32_t ih, int32_t iw, int32_t oh, int32_t ow, int32_t mode, int32_t coord_mode,
+                         int32_t platform, void* stream) {
+  if (!x || !y || nc < 0 || ih < 1 || iw < 1 || oh < 0 || ow < 0) return set_error(B200Q_ERR_INVALID, "interp_f32_dev: bad argument");
+  return top_interp_launch(x, y, nc, ih, iw, oh, ow, mode, coord_mode, platform, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_grid_sampler_f32_dev(const float* x, const float* grid, float* y, int32_t n, int32_t c, int32_t ih, int32_t iw, int32_t oh, int32_t ow,
                                int32_t mode, int32_t padding_mode, int32_t align_corners, void* stream) {
   if (!x || !grid || !y || n < 0 || c < 0 || ih < 1 || iw < 1 || oh < 0 || ow < 0) return set_error(B200Q_ERR_INVALID, "grid_sampler_f32_dev: bad argument");

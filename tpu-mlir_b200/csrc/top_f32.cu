@@ -532,6 +532,66 @@ __global__ void reduce_f32_kernel(int mode, const float* __restrict__ x, float* 
   y[i] = v;
 }
 
+// top::InterpOp / tpu::InterpOp, modes nearest and linear (interp_core, lib/Dialect/Top/Interfaces/Interp.cpp:28-181): per output
+// row / column the source coordinate comes from backward_map (:52-98); linear blends rows first (buf = a + dy * (b - a)), then
+// columns, each a subtract, a multiply and an add in float, with the last row / column copied.
+enum { INTERP_PYTORCH_SUPPORT = 0, INTERP_CAFFE_SUPPORT, INTERP_TENSORFLOW_NEAREST, INTERP_PYTORCH_NEAREST, INTERP_ONNX_NEAREST,
+       INTERP_CAFFE_NEAREST };
+__device__ __forceinline__ void interp_map(int o, float scale, int d, int align, int half_pixel, int sp, float& xs, int& xi) {
+  const float of = (float)o, hi = (float)(d - 1);
+  switch (sp) {
+    case INTERP_TENSORFLOW_NEAREST:
+      xs = half_pixel ? __fmul_rn(__fadd_rn(of, 0.5f), scale) : __fmul_rn(of, scale);
+      xs = fminf(fmaxf(xs, 0.f), hi);
+      xi = align ? (int)roundf(xs) : (int)floorf(xs);
+      break;
+    case INTERP_PYTORCH_SUPPORT:
+      xs = align ? __fmul_rn(of, scale) : __fsub_rn(__fmul_rn(__fadd_rn(of, 0.5f), scale), 0.5f);
+      xs = fminf(fmaxf(xs, 0.f), hi);
+      xi = (int)floorf(xs);
+      break;
+    case INTERP_ONNX_NEAREST:
+      if (half_pixel) {
+        xs = fminf(fmaxf(__fsub_rn(__fmul_rn(__fadd_rn(of, 0.5f), scale), 0.5f), 0.f), hi);
+        xi = (int)floorf(xs);
+      } else {
+        xs = fminf(fmaxf(__fmul_rn(of, scale), 0.f), hi);
+        xi = align ? (int)roundf(xs) : (int)floorf(xs);
+      }
+      break;
+    default:   // PYTORCH_NEAREST, CAFFE_SUPPORT, CAFFE_NEAREST
+      xs = fminf(fmaxf(__fmul_rn(of, scale), 0.f), hi);
+      xi = (int)floorf(xs);
+  }
+}
+__global__ void interp_f32_kernel(const float* __restrict__ x, float* __restrict__ y, long long nc, int ih, int iw, int oh, int ow,
+                                  float h_scale, float w_scale, int align, int half_pixel, int sp) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nc * oh * ow) return;
+  const int xo = (int)(i % ow), yo = (int)((i / ow) % oh);
+  const float* in = x + (i / ((long long)ow * oh)) * ih * iw;
+  float ys, xs;
+  int yi, xi;
+  interp_map(yo, h_scale, ih, align, half_pixel, sp, ys, yi);
+  interp_map(xo, w_scale, iw, align, half_pixel, sp, xs, xi);
+  if (sp != INTERP_PYTORCH_SUPPORT && sp != INTERP_CAFFE_SUPPORT) {
+    y[i] = in[(long long)yi * iw + xi];
+    return;
+  }
+  const float dy = __fsub_rn(ys, (float)yi), dx = __fsub_rn(xs, (float)xi);
+  auto row_blend = [&](int xf) {
+    if (yi == ih - 1) return in[(long long)(ih - 1) * iw + xf];
+    const float a = in[(long long)yi * iw + xf], b = in[(long long)(yi + 1) * iw + xf];
+    return __fadd_rn(a, __fmul_rn(dy, __fsub_rn(b, a)));
+  };
+  if (xi == iw - 1) {
+    y[i] = row_blend(iw - 1);
+  } else {
+    const float a = row_blend(xi), b = row_blend(xi + 1);
+    y[i] = __fadd_rn(a, __fmul_rn(dx, __fsub_rn(b, a)));
+  }
+}
+
 // top::GridSamplerOp / tpu::GridSamplerOp with a 4-D grid [N, OH, OW, 2] (GridSamplerFunc, lib/Support/GenericCpuFunc.cpp:3332-3455):
 // mode 0 bilinear, 1 nearest (nearbyint); padding 0 zeros, 1 border, 2 reflection.  Float arithmetic in the reference's order,
 // products and sums kept apart.
@@ -739,6 +799,42 @@ int top_layernorm_launch(const float* x, const float* w, const float* b, float* 
   if (outer == 0 || inner == 0) return B200Q_OK;
   if (outer > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "layernorm: too many rows");
   layernorm_f32_kernel<<<(unsigned)outer, 256, 0, s>>>(x, w, b, y, inner, eps);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+// calc_resize_scale (Interp.cpp:28-50)
+static float interp_scale(int in_size, int out_size, bool align, int sp) {
+  const bool caffe = sp == INTERP_CAFFE_NEAREST || sp == INTERP_CAFFE_SUPPORT;
+  const bool may_align = sp == INTERP_TENSORFLOW_NEAREST || sp == INTERP_PYTORCH_SUPPORT || sp == INTERP_ONNX_NEAREST;
+  if (caffe || (may_align && align)) {
+    if (out_size <= 1) return 0.f;
+    --in_size;
+    --out_size;
+  }
+  return in_size / (float)out_size;
+}
+
+// mode 0 nearest / 1 linear; coord_mode 0 half_pixel, 1 pytorch_half_pixel, 2 align_corners, 3 asymmetric; platform 0 ONNX (and any
+// other), 1 TORCH, 2 TFLITE, 3 CAFFE: the resolution of Interp.cpp:226-279
+int top_interp_launch(const float* x, float* y, long long nc, int ih, int iw, int oh, int ow, int mode, int coord_mode, int platform,
+                      cudaStream_t s) {
+  if (mode < 0 || mode > 1 || coord_mode < 0 || coord_mode > 3) return set_error(B200Q_ERR_UNSUPPORTED, "interp: mode %d, coord mode %d", mode, coord_mode);
+  int sp;
+  bool align, half_pixel;
+  if (mode == 0) {
+    sp = platform == 3 ? INTERP_CAFFE_NEAREST : platform == 1 ? INTERP_PYTORCH_NEAREST : platform == 2 ? INTERP_TENSORFLOW_NEAREST : INTERP_ONNX_NEAREST;
+    align = coord_mode != 3;
+    half_pixel = false;
+  } else {
+    sp = platform == 3 ? INTERP_CAFFE_SUPPORT : INTERP_PYTORCH_SUPPORT;
+    align = coord_mode == 2;
+    half_pixel = coord_mode == 0 || coord_mode == 1;
+  }
+  const long long total = nc * oh * ow;
+  if (total == 0) return B200Q_OK;
+  interp_f32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, y, nc, ih, iw, oh, ow, interp_scale(ih, oh, align, sp),
+                                                                     interp_scale(iw, ow, align, sp), align, half_pixel, sp);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

@@ -52,6 +52,8 @@ struct TopRemap {   // layout-compatible with b200q_remap_desc
       off[TOP_REMAP_DIMS], extent[TOP_REMAP_DIMS], dst_stride[TOP_REMAP_DIMS];
   long long dst_offset;
 };
+int top_interp_launch(const float* x, float* y, long long nc, int ih, int iw, int oh, int ow, int mode, int coord_mode, int platform,
+                      cudaStream_t s);
 int top_grid_sampler_launch(const float* x, const float* grid, float* y, int N, int C, int IH, int IW, int OH, int OW, int mode, int padding,
                             bool align_corners, cudaStream_t s);
 int top_arg_launch(const float* x, long long outer, int axis, long long inner, bool is_max, bool select_last, void* idx_out,

@@ -207,6 +207,18 @@ class module:  # noqa: N801  (name of the reference class)
         stream = lambda: C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)  # noqa: E731
         if t.split(".", 1)[-1] in _MOVE_OPS:
             return self._plan_move(op, stream)
+        if t in ("top.Interp", "tpu.Interp"):
+            modes = {"nearest": 0, "linear": 1}
+            coords = {"half_pixel": 0, "pytorch_half_pixel": 1, "align_corners": 2, "asymmetric": 3}
+            plats = {"ONNX": 0, "TORCH": 1, "TFLITE": 2, "CAFFE": 3}
+            ishape, oshape = list(iinfo[0]["shape"]), list(oinfo["shape"])
+            if iinfo[0]["dtype"] != "f32" or oinfo["dtype"] != "f32" or a.get("mode") not in modes or a.get("coord_mode") not in coords \
+                    or len(ishape) != 4 or op["inputs"][0] in self._nhwc or op["name"] in self._nhwc or len(ins) > 1:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: {t} takes a 4-D f32 NCHW tensor, mode nearest / linear, a fixed output shape")
+            nc, ih, iw, oh, ow = ishape[0] * ishape[1], ishape[2], ishape[3], oshape[2], oshape[3]
+            mode, coord = modes[a["mode"]], coords[a["coord_mode"]]
+            plat = plats.get(str(a.get("platform", self.graph.get("platform", "ONNX"))).upper(), 0)
+            return lambda: L.check(lib.b200q_interp_f32_dev(_P(ins[0]), _P(out), nc, ih, iw, oh, ow, mode, coord, plat, stream()))
         if t in ("top.GridSampler", "tpu.GridSampler"):
             gshape = list(iinfo[1]["shape"])
             if any(i["dtype"] != "f32" for i in iinfo) or oinfo["dtype"] != "f32" or len(gshape) != 4 or gshape[3] != 2 \
