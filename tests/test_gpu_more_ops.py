@@ -603,3 +603,69 @@ def test_interp(mode, coord, platform, osz):
         ops = [dict(type=tname, name="y", inputs=["x"], attrs=dict(mode=mode, coord_mode=coord, platform=platform, scale_h=osz[0] / 5, scale_w=osz[1] / 7))]
         m = run_graph({"x": f32(x.shape), "y": f32((2, 3) + osz)}, ops, {}, {"x": x})
         assert np.array_equal(m.get_tensor("y"), interp_ref(x, osz[0], osz[1], mode, coord, platform)), tname
+
+
+def deconv_ref(x, w, b, izp, strides, dil, pads, opad, mult, rshift, ozp, relu, groups=1):
+    """tpu.Deconv as the reference computes it (Deconv.cpp:95-150): without an input zero point the scatter form of a transposed
+    convolution; with one, the spread input padded with the zero point and correlated with the rotated filter
+    (lib/Support/Dnnl/Deconv.cpp:17-110, MathUtils.cpp:673-705).  Then RSR(acc * m, s, half up) + zp, saturated to int8."""
+    n, ic, ih, iw = x.shape
+    oc, icg, kh, kw = w.shape
+    sh, sw = strides
+    dh, dw = dil
+    pt, pl, pb, pr = pads
+    oh = (ih - 1) * sh + 1 + dh * (kh - 1) - pt - pb + opad[0]
+    ow = (iw - 1) * sw + 1 + dw * (kw - 1) - pl - pr + opad[1]
+    acc = np.zeros((n, oc, oh, ow), np.int64)
+    ocg = oc // groups
+    if izp == 0:
+        full = np.zeros((n, oc, (ih - 1) * sh + dh * (kh - 1) + 1 + opad[0] + pt + pb, (iw - 1) * sw + dw * (kw - 1) + 1 + opad[1] + pl + pr), np.int64)
+        for o in range(oc):
+            g = o // ocg
+            for c in range(icg):
+                for i in range(kh):
+                    for j in range(kw):
+                        full[:, o, i * dh:i * dh + (ih - 1) * sh + 1:sh, j * dw:j * dw + (iw - 1) * sw + 1:sw] += \
+                            x[:, g * icg + c].astype(np.int64) * int(w[o, c, i, j])
+        acc = full[:, :, pt:pt + oh, pl:pl + ow].copy()
+    else:
+        hs, ws = oh + kh - 1, ow + kw - 1
+        st = np.full((n, ic, hs, ws), izp, np.int64)
+        st[:, :, kh - 1 - pt:kh - 1 - pt + (ih - 1) * sh + 1:sh, kw - 1 - pl:kw - 1 - pl + (iw - 1) * sw + 1:sw] = x
+        wr = w[:, :, ::-1, ::-1].astype(np.int64)
+        for o in range(oc):
+            g = o // ocg
+            for i in range(kh):
+                for j in range(kw):
+                    acc[:, o] += (st[:, g * icg:(g + 1) * icg, i:i + oh, j:j + ow] * wr[o, :, i, j][None, :, None, None]).sum(axis=1)
+    if b is not None:
+        acc += b.astype(np.int64)[None, :, None, None]
+    if relu:
+        acc = np.maximum(acc, 0)
+    m_ = np.asarray(mult, np.int64).reshape(1, -1, 1, 1)
+    s_ = np.asarray(rshift, np.int64).reshape(1, -1, 1, 1)
+    v = ((acc * m_ + (1 << (s_ - 1))) >> s_) + ozp
+    return np.clip(v, -128, 127).astype(np.int8)
+
+
+@pytest.mark.parametrize("cfg", [dict(ic=16, oc=32, k=(2, 2), s=(2, 2), pads=(0, 0, 0, 0)), dict(ic=8, oc=16, k=(3, 3), s=(2, 2), pads=(1, 1, 1, 1), opad=(1, 1), relu=True),
+                                 dict(ic=16, oc=16, k=(4, 4), s=(2, 2), pads=(1, 1, 1, 1), izp=-5, ozp=3), dict(ic=8, oc=8, k=(3, 2), s=(1, 3), pads=(0, 1, 2, 0), dil=(2, 1)),
+                                 dict(ic=8, oc=12, k=(3, 3), s=(2, 1), pads=(1, 0, 0, 1), groups=4, izp=7)])
+def test_tpu_deconv(cfg):
+    rng = np.random.default_rng(17)
+    ic, oc, (kh, kw), groups = cfg["ic"], cfg["oc"], cfg["k"], cfg.get("groups", 1)
+    strides, dil, pads, opad = cfg["s"], cfg.get("dil", (1, 1)), cfg["pads"], cfg.get("opad", (0, 0))
+    izp, ozp, relu = cfg.get("izp", 0), cfg.get("ozp", 0), cfg.get("relu", False)
+    x = rng.integers(-128, 128, (2, ic, 5, 6), dtype=np.int8)
+    w = rng.integers(-128, 128, (oc, ic // groups, kh, kw), dtype=np.int8)
+    b = rng.integers(-5000, 5000, oc, dtype=np.int32)
+    mult = rng.integers(1000, 20000, oc).tolist()
+    rshift = rng.integers(18, 22, oc).tolist()
+    want = deconv_ref(x, w, b, izp, strides, dil, pads, opad, mult, rshift, ozp, relu, groups)
+    ops = [dict(type="tpu.Deconv", name="y", inputs=["x"], attrs=dict(kernel_shape=[kh, kw], strides=list(strides), dilations=list(dil), pads=list(pads),
+                                                                     output_padding=list(opad), group=groups, do_relu=relu, multiplier=mult, rshift=rshift,
+                                                                     quant_mode="MultiplierShift"))]
+    tensors = {"x": dict(shape=list(x.shape), dtype="i8", scale=0.1, zp=izp), "y": dict(shape=list(want.shape), dtype="i8", scale=0.1, zp=ozp)}
+    m = run_graph(tensors, ops, {"y_filter": w, "y_bias": b}, {"x": x})
+    m.check_status()
+    assert np.array_equal(m.get_raw_tensor("y"), want)

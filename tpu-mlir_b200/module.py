@@ -362,6 +362,57 @@ class module:  # noqa: N801  (name of the reference class)
             if self.channels_last:
                 return lambda: L.check(lib.b200q_conv2d_dev_run_layout(h, _P(ins[0]), xl, _P(out), yl, stream()))
             return lambda: L.check(lib.b200q_conv2d_dev_run(h, _P(ins[0]), _P(out), stream()))
+        if t == "tpu.Deconv":
+            # tpu.Deconv with 8-bit tensors (lib/Dialect/Tpu/Interfaces/Common/Deconv.cpp:95-150) the way the reference's own
+            # zero-point route computes it (lib/Support/Dnnl/Deconv.cpp:17-46,:95-110 with pad_tensor_for_deconv, MathUtils.cpp:673-705):
+            # the input is spread by the strides into a buffer filled with the input zero point, then convolved at stride 1
+            # with the filter turned by 180 degrees, on the INT8 convolution kernel.  ReLU acts on the accumulator there
+            # (a library post-op), here after the requantisation, which is the same while no multiplier is negative.
+            from .ops import Conv2DOp
+            name = op["name"]
+            w = self.weights[name + "_filter"]
+            b = self.weights.get(name + "_bias")
+            n, ic, ih, iw = iinfo[0]["shape"]
+            kh, kw = a["kernel_shape"]
+            sh, sw = a.get("strides", [1, 1])
+            dh, dw = a.get("dilations", [1, 1])
+            pt, pl, pb, pr = a.get("pads", [0, 0, 0, 0])
+            oph, opw = a.get("output_padding", [0, 0])
+            izp = int(iinfo[0].get("zp", 0))
+            if iinfo[0]["dtype"] not in ("i8", "u8") or oinfo["dtype"] != "i8" or op["inputs"][0] in self._nhwc or name in self._nhwc:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: tpu.Deconv takes an 8-bit NCHW tensor and writes int8 (the reference saturates to int8)")
+            if izp != 0 and (dh != 1 or dw != 1):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: a dilated tpu.Deconv with an input zero point is not implemented")
+            top_, left, bot, right = dh * (kh - 1) - pt, dw * (kw - 1) - pl, dh * (kh - 1) - pb + oph, dw * (kw - 1) - pr + opw
+            if min(top_, left, bot, right) < 0:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: tpu.Deconv pads larger than the dilated kernel are not implemented")
+            if a.get("do_relu", False) and any(int(m) < 0 for m in a["multiplier"]):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: tpu.Deconv with do_relu and a negative multiplier is not implemented")
+            hs, ws = (ih - 1) * sh + 1 + top_ + bot, (iw - 1) * sw + 1 + left + right
+            stage = self.torch.full((n, ic, hs, ws), izp, dtype=ins[0].dtype, device=self.device)
+            spread = L.RemapDesc(dims=(C.c_int64 * 6)(1, 1, n, ic, ih, iw), src_stride=(C.c_int64 * 6)(0, 0, ic * ih * iw, ih * iw, iw, 1),
+                                 mul=(C.c_int64 * 6)(*[1] * 6), div=(C.c_int64 * 6)(*[1] * 6), mod=(C.c_int64 * 6)(*[0] * 6),
+                                 off=(C.c_int64 * 6)(*[0] * 6), extent=(C.c_int64 * 6)(1, 1, n, ic, ih, iw),
+                                 dst_stride=(C.c_int64 * 6)(0, 0, ic * hs * ws, hs * ws, sh * ws, sw), dst_offset=top_ * ws + left)
+            w_rot = w.flip(2, 3).contiguous()
+            cop = Conv2DOp(input_shape=(n, ic, hs, ws), oc=w.shape[0], kernel_shape=(kh, kw), strides=(1, 1), dilations=(dh, dw),
+                           pads=(0, 0, 0, 0), group=a.get("group", 1), with_bias=b is not None, do_relu=bool(a.get("do_relu", False)),
+                           input_dtype=_DT[iinfo[0]["dtype"]], out_dtype=_DT[oinfo["dtype"]],
+                           quant_mode=_QM[a.get("quant_mode", "MultiplierShift")], out_zp=int(oinfo.get("zp", 0)),
+                           multiplier=a["multiplier"], rshift=a["rshift"])
+            if tuple(cop.out_shape) != tuple(oinfo["shape"]):
+                raise L.B200QError(L.ERR_INVALID, f"{name}: output shape {oinfo['shape']} does not match the deconvolution ({cop.out_shape})")
+            h = C.c_void_p()
+            L.check(lib.b200q_conv2d_dev_create(C.byref(cop.desc), _P(w_rot), _P(b), C.byref(h)))
+            self._handles.append(h)
+            self._keep.append((cop, stage, spread, w_rot))
+            self._status.append((name, h))
+            eb = ins[0].element_size()
+
+            def run_deconv():
+                L.check(lib.b200q_remap_dev(_P(ins[0]), _P(stage), eb, C.byref(spread), None, stream()))
+                L.check(lib.b200q_conv2d_dev_run(h, _P(stage), _P(out), stream()))
+            return run_deconv
         if t == "tpu.MatMul":
             # What the reference reads from the op (MatMul.cpp:24-135,:636-728): anything this plan does not honour is
             # refused, never computed differently.
