@@ -323,12 +323,12 @@ int b200q_cast_q8_to_f32_dev(const void *x, int32_t dtype, int64_t count, double
  * point per q_group_size consecutive k of a row: W[n,k] = (q - zp) * scale. */
 typedef struct {
   int64_t M, K, N;
-  int32_t weight_bits;    /* 4; 8 (bf16 only: weight [N, K] one value per float, dequantised weight rounded to bf16 as
-                           * A16MatMul.cpp:213-232 does) */
+  int32_t weight_bits;    /* 4; 8 (weight [N, K] one value per float, dequantised weight rounded to bf16, or to f16 in an
+                           * F16 mode, as A16MatMul.cpp:213-232 does) */
   int32_t q_group_size;   /* weights per scale / zero point along k; 0 = one per output channel (A16MatMul.cpp:176-187) */
   int32_t w_transpose;    /* 1 */
   int32_t with_bias;
-  int32_t out_dtype;      /* B200Q_DT_BF16 (w4bf16) or B200Q_DT_F16 (w4f16): the type of input, scale and output */
+  int32_t out_dtype;      /* B200Q_DT_BF16 (w4bf16, w8bf16) or B200Q_DT_F16 (w4f16, w8f16): the type of input, scale and output */
   int32_t weight_version; /* bump after rewriting the weight buffers in place */
 } b200q_a16matmul_desc;
 

@@ -374,20 +374,28 @@ def a16matmul_w4(x_bits, wq, scale_bits, zp, bias=None, *, group=64, f16=False):
     return y
 
 
-def a16matmul_w8(x_bits, w, scale_bits, zp, bias=None, *, group=64):
+def a16matmul_w8(x_bits, w, scale_bits, zp, bias=None, *, group=64, f16=False):
     """tpu.A16MatMul static w8 path with w_transpose=true (A16MatMul.cpp:209-246): w [N,K] integers (any of the 8-bit
-    ranges), the dequantised weight (w - zp) * scale is rounded to bf16 before the fp32 matmul, the result rounded to
-    bf16.  ``group`` = K is the per-channel form (q_group_size = 0).  numpy: float64 accumulation of exact products."""
-    x = bf16_bits_to_f32(_c(x_bits, np.uint16)).astype(np.float64)
+    ranges), the dequantised weight (w - zp) * scale is rounded to bf16 (F16 modes: to IEEE half, :226-230) before the fp32
+    matmul, the result rounded the same way.  ``group`` = K is the per-channel form (q_group_size = 0).  numpy: float64
+    accumulation of exact products."""
+    if f16:
+        to_f = lambda b: _c(b, np.uint16).view(np.float16).astype(np.float32)  # noqa: E731
+        rnd = lambda v: np.asarray(v, dtype=np.float32).astype(np.float16)  # noqa: E731  (round to nearest even, as F16())
+    else:
+        to_f = lambda b: bf16_bits_to_f32(_c(b, np.uint16))  # noqa: E731
+        rnd = None
+    x = to_f(x_bits).astype(np.float64)
     w = np.asarray(w, dtype=np.float32)
     N, K = w.shape
-    s = np.repeat(bf16_bits_to_f32(_c(scale_bits, np.uint16)).reshape(N, K // group), group, axis=1)
+    s = np.repeat(to_f(scale_bits).reshape(N, K // group), group, axis=1)
     z = np.repeat(np.asarray(zp, dtype=np.float32).reshape(N, K // group), group, axis=1)
-    W = bf16_bits_to_f32(f32_to_bf16_bits_fast(((w - z) * s).astype(np.float32))).astype(np.float64)
+    prod = ((w - z) * s).astype(np.float32)
+    W = (rnd(prod).astype(np.float64) if f16 else bf16_bits_to_f32(f32_to_bf16_bits_fast(prod)).astype(np.float64))
     y = x @ W.T
     if bias is not None:
         y = y + np.asarray(bias, dtype=np.float64)
-    return f32_to_bf16_bits_fast(y.astype(np.float32))
+    return rnd(y.astype(np.float32)).view(np.uint16) if f16 else f32_to_bf16_bits_fast(y.astype(np.float32))
 
 
 def a16_dequant_w4(wq, scale_bits, zp, *, group=64):

@@ -341,12 +341,28 @@ def test_w8bf16_operator_face(case):
     check(oracle.f32_to_bf16_bits_fast(out), ref)
 
 
-def test_w8_f16_is_refused():
-    op = A16MatMulOp(M=1, K=64, N=16, q_group_size=64, weight_bits=8, out_dtype=L.DT_F16)
-    with pytest.raises(L.B200QError) as ei:
-        op.inference(InferenceParameter(inputs=[np.zeros((1, 64), np.float32), np.zeros((16, 64), np.float32), np.zeros(16, np.float32),
-                                                np.zeros(16, np.float32), None], outputs=[np.zeros((1, 16), np.float32)]))
-    assert ei.value.code == L.ERR_UNSUPPORTED
+@pytest.mark.parametrize("case", [dict(M=1, K=512, N=96, g=64, signed=False), dict(M=70, K=1024, N=257, g=0, signed=True)])
+def test_w8f16_operator_face(case):
+    """weight_bits = 8 in an F16 mode (A16MatMul.cpp:226-246): the dequantised weight and the output are rounded with F16();
+    kind::f16 on IEEE half operands."""
+    M, K, N, g = case["M"], case["K"], case["N"], case["g"]
+    group = g if g else K
+    rng = np.random.default_rng(32)
+    h16 = lambda a: np.asarray(a, dtype=np.float32).astype(np.float16)  # noqa: E731
+    w = (rng.integers(-128, 128, size=(N, K)) if case["signed"] else rng.integers(0, 256, size=(N, K))).astype(np.float32)
+    zp = (rng.integers(-8, 8, size=N * K // group) if case["signed"] else rng.integers(120, 136, size=N * K // group)).astype(np.float32)
+    scale = h16(rng.random(N * K // group) * 0.01 + 0.002)
+    x = h16(rng.standard_normal((M, K)))
+    bias = rng.standard_normal(N).astype(np.float32)
+    ref = oracle.a16matmul_w8(x.view(np.uint16), w, scale.view(np.uint16), zp, bias, group=group, f16=True)
+    op = A16MatMulOp(M=M, K=K, N=N, q_group_size=g, weight_bits=8, with_bias=True, out_dtype=L.DT_F16)
+    out = np.zeros((M, N), np.float32)
+    p = InferenceParameter(inputs=[x.astype(np.float32), w, scale.astype(np.float32), zp, bias], outputs=[out])
+    op.init(p)
+    op.inference(p)
+    op.deinit(p)
+    assert np.array_equal(out.astype(np.float16).astype(np.float32), out)          # the outputs are f16 values
+    check_f16(out.astype(np.float16).view(np.uint16), ref)
 
 
 # ------------------------------------------------------------------ output rounding, bit for bit

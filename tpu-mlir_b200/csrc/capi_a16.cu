@@ -103,7 +103,8 @@ int dequant_w4_bf16(const void* wq, const void* scale, const void* zp, void* W, 
 // 8-bit weights: W[n,k] = bf16((q - zp) * scale), which is the matrix the reference itself multiplies with
 // (A16MatMul.cpp:213-232 rounds the dequantised weight with BF16() before its matmul).  The weight and the zero points
 // are read as the interpreter stores them (floats holding integers, signed or unsigned); 8 weights per thread.
-__global__ void dequant_w8_bf16_kernel(const float4* __restrict__ wq, const __nv_bfloat16* __restrict__ scale,
+template <bool F16>
+__global__ void dequant_w8_bf16_kernel(const float4* __restrict__ wq, const uint16_t* __restrict__ scale,
                                        const float* __restrict__ zp, uint4* __restrict__ W, long long octets, int K,
                                        int group) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -112,35 +113,43 @@ __global__ void dequant_w8_bf16_kernel(const float4* __restrict__ wq, const __nv
   const long long n = e0 / K;
   const int k = (int)(e0 - n * K);
   const long long gi = n * (K / group) + k / group;   // group % 8 == 0: the 8 weights share a group
-  const float s = __bfloat162float(scale[gi]);
+  const float s = F16 ? __half2float(__ushort_as_half(scale[gi])) : __uint_as_float((uint32_t)scale[gi] << 16);
   const float z = zp[gi];
   const float4 lo = wq[2 * i], hi = wq[2 * i + 1];
   const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
   uint32_t o[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn((v[2 * j] - z) * s, (v[2 * j + 1] - z) * s);
-    o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    if (F16) {   // F16() of the dequantised weight (A16MatMul.cpp:226-227)
+      const __half2 h = __floats2half2_rn((v[2 * j] - z) * s, (v[2 * j + 1] - z) * s);
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+      const __nv_bfloat162 h = __floats2bfloat162_rn((v[2 * j] - z) * s, (v[2 * j + 1] - z) * s);
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
   }
   W[i] = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-int dequant_w8_bf16(const float* wq_f32, const void* scale, const float* zp_f32, void* W, long long N, int K, int group,
+int dequant_w8_bf16(const float* wq_f32, const void* scale, const float* zp_f32, void* W, long long N, int K, int group, bool f16,
                     cudaStream_t s) {
   const long long octets = N * K / 8;
   if (octets == 0) return B200Q_OK;
-  dequant_w8_bf16_kernel<<<(unsigned)((octets + 255) / 256), 256, 0, s>>>(
-      reinterpret_cast<const float4*>(wq_f32), static_cast<const __nv_bfloat16*>(scale), zp_f32, static_cast<uint4*>(W),
-      octets, K, group);
+  if (f16)
+    dequant_w8_bf16_kernel<true><<<(unsigned)((octets + 255) / 256), 256, 0, s>>>(
+        reinterpret_cast<const float4*>(wq_f32), static_cast<const uint16_t*>(scale), zp_f32, static_cast<uint4*>(W), octets, K, group);
+  else
+    dequant_w8_bf16_kernel<false><<<(unsigned)((octets + 255) / 256), 256, 0, s>>>(
+        reinterpret_cast<const float4*>(wq_f32), static_cast<const uint16_t*>(scale), zp_f32, static_cast<uint4*>(W), octets, K, group);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }
 
 // Prefill: y = x * W^T on the bf16 tensor cores (tcgen05 kind::f16, fp32 accumulation in TMEM).
 int a16_prefill_gemm(const void* x, const void* W16, const float* bias, void* y, long long M, int N, int K, int* status,
-                     cudaStream_t s) {
+                     cudaStream_t s, bool f16 = false) {
   IGemmProblem p{};
-  p.kind = IGEMM_KIND_BF16;
+  p.kind = f16 ? IGEMM_KIND_F16 : IGEMM_KIND_BF16;
   p.a = x;
   p.b = W16;
   p.a_pitch = p.b_pitch = 2LL * K;
@@ -165,7 +174,6 @@ int validate(const b200q_a16matmul_desc& d) {
   if (d.out_dtype != B200Q_DT_BF16 && d.out_dtype != B200Q_DT_F16)
     return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: activations/outputs are bf16 (w4bf16) or f16 (w4f16)");
   if (d.weight_bits == 8) {
-    if (d.out_dtype != B200Q_DT_BF16) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: 8-bit weights are implemented for bf16 (w8bf16) only");
     const int64_t g = d.q_group_size ? d.q_group_size : d.K;
     if (d.K % 8 != 0 || g % 8 != 0 || d.K % g != 0) return set_error(B200Q_ERR_UNSUPPORTED, "a16matmul: w8 needs K and the group size to be multiples of 8, the group dividing K");
   }
@@ -308,10 +316,10 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
         if ((rc = h->zp.ensure(q_elems * 4))) break;
         if ((rc = h->w16.ensure(w_elems * 2))) break;
         if (cudaMemcpyAsync(h->stage.p, inputs[2], q_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D scale", __FILE__, __LINE__); break; }
-        if ((rc = f32_to_16(h->stage.as<float>(), h->scale.p, (long long)q_elems, false, s))) break;
+        if ((rc = f32_to_16(h->stage.as<float>(), h->scale.p, (long long)q_elems, f16, s))) break;
         if (cudaMemcpyAsync(h->zp.p, inputs[3], q_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D zp", __FILE__, __LINE__); break; }
         if (cudaMemcpyAsync(h->stage.p, inputs[1], w_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D weight", __FILE__, __LINE__); break; }
-        if ((rc = dequant_w8_bf16(h->stage.as<float>(), h->scale.p, h->zp.as<float>(), h->w16.p, d.N, (int)d.K, group, s))) break;
+        if ((rc = dequant_w8_bf16(h->stage.as<float>(), h->scale.p, h->zp.as<float>(), h->w16.p, d.N, (int)d.K, group, f16, s))) break;
         if (bias_f && (rc = h->bias.upload(bias_f, (size_t)d.N * 4, s))) break;
         h->weights_ready = true;
         h->w16_ready = true;
@@ -347,7 +355,7 @@ int b200q_a16matmul_inference(const b200q_a16matmul_desc* desc, float* const* in
     if ((rc = f32_to_16(h->stage.as<float>(), h->x16.p, (long long)x_elems, f16, s))) break;
     if (w8) {
       if ((rc = a16_prefill_gemm(h->x16.p, h->w16.p, bias_f ? h->bias.as<float>() : nullptr, h->y16.p, d.M, (int)d.N, (int)d.K,
-                                 h->status.as<int>(), s))) break;
+                                 h->status.as<int>(), s, f16))) break;
     } else if ((rc = a16_dispatch(h->x16.p, h->wq.p, h->scale.p, h->zp.p, bias_f ? h->bias.as<float>() : nullptr, h->y16.p,
                                   d.M, (int)d.N, (int)d.K, group, h->status.as<int>(), s, &h->w16, &h->w16_ready, false, f16, &h->wg_scratch))) break;
     if ((rc = f16_or_bf16_to_f32(h->y16.p, h->y32.as<float>(), (long long)y_elems, f16, s))) break;

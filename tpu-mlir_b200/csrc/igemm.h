@@ -9,7 +9,7 @@
 namespace b200q {
 
 enum { IGEMM_OUT_ROWMAJOR = 0, IGEMM_OUT_NCHW = 1, IGEMM_OUT_NHWC_BORDERED = 2, IGEMM_OUT_NHWC = 3 };  // NHWC: interior pixels only, [N][out_h][out_w][ldc]
-enum { IGEMM_KIND_I8 = 0, IGEMM_KIND_BF16 = 1 };  // operand type; BF16: fp32 accumulate, bf16 row-major output
+enum { IGEMM_KIND_I8 = 0, IGEMM_KIND_BF16 = 1, IGEMM_KIND_F16 = 2 };  // operand type; BF16 / F16: fp32 accumulate, row-major output of the operand type
 
 // What the host asks for.  A is [rows][k_per_tap] (row pitch a_pitch bytes): the GEMM's left matrix, or the
 // pixels of a zero-bordered NHWC image flattened to rows.  B is [n][taps_h*taps_w*k_per_tap] (K-major weights).
@@ -53,7 +53,8 @@ struct IGemmArgs {
   uint32_t idesc;
   int num_m_tiles, num_n_tiles;
   const float* bias_f32;
-  int bf16;
+  int bf16;   // 16-bit float operands (kind::f16); with f16 set they and the output are IEEE half, else bf16
+  int f16;
   int acc_small;
   int out_small;
   int floor_pre, sat_lo2, sat_hi, pack_sat, floor_needed;  // epilogue constants derived from epi (see the kernel)

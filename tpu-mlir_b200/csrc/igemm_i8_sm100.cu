@@ -16,6 +16,7 @@
 // Conv2D.cpp:264-341) and the oneDNN primitives behind them (lib/Support/Dnnl/MatMul.cpp, Conv.cpp).
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdlib.h>
 
@@ -631,7 +632,12 @@ igemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             for (int j = 0; j < CH / 2; ++j) {
               const float v0 = __uint_as_float(r[2 * j]) + __int_as_float(chan[cbase + 2 * j].x);
               const float v1 = __uint_as_float(r[2 * j + 1]) + __int_as_float(chan[cbase + 2 * j + 1].x);
-              pk[j] = (uint32_t)f32_to_bf16_bits_ref(v0) | ((uint32_t)f32_to_bf16_bits_ref(v1) << 16);
+              if (args.f16) {
+                const __half2 h2 = __floats2half2_rn(v0, v1);
+                pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
+              } else {
+                pk[j] = (uint32_t)f32_to_bf16_bits_ref(v0) | ((uint32_t)f32_to_bf16_bits_ref(v1) << 16);
+              }
             }
             if (nc == CH && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
               reinterpret_cast<uint4*>(o)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -1012,7 +1018,7 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
     const bool out8 = epi.out_dtype == B200Q_DT_I8 || epi.out_dtype == B200Q_DT_U8;
     auto m_ok = [](int m) { return m > -(1 << 23) && m < (1 << 23); };
     auto s_ok = [](int sft) { return sft >= 1 && sft <= 31; };
-    if (!out8 || p.kind == IGEMM_KIND_BF16 || !m_ok(p.add_m_self) || !m_ok(p.add_m_res) || !s_ok(p.add_s_self) || !s_ok(p.add_s_res) ||
+    if (!out8 || p.kind != IGEMM_KIND_I8 || !m_ok(p.add_m_self) || !m_ok(p.add_m_res) || !s_ok(p.add_s_self) || !s_ok(p.add_s_res) ||
         p.out_mode == IGEMM_OUT_NHWC_BORDERED)
       return set_error(B200Q_ERR_UNSUPPORTED, "tcgen05 igemm: fused Add needs 8-bit tensors, |multiplier| < 2^23, shifts in [1,31]");
     a.res_unsigned = p.res_unsigned;
@@ -1025,7 +1031,8 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   }
   a.wait_budget_ns = g_wait_budget_ns.load(std::memory_order_relaxed);
   a.expect_extra = g_expect_extra.load(std::memory_order_relaxed);
-  a.bf16 = p.kind == IGEMM_KIND_BF16;
+  a.bf16 = p.kind == IGEMM_KIND_BF16 || p.kind == IGEMM_KIND_F16;
+  a.f16 = p.kind == IGEMM_KIND_F16;
   // |accumulator| < 2^29 for every 8-bit operand pair: lets the epilogue fold the bias into one 64-bit constant
   // largest |a * b| of one product: 255 * 255 for two unsigned operands, 255 * 128 mixed, 128 * 128 for two signed ones
   const long long max_prod = (p.a_unsigned && p.b_unsigned) ? 65025ll : ((p.a_unsigned || p.b_unsigned) ? 32640ll : 16384ll);
@@ -1065,7 +1072,7 @@ int igemm_i8_tcgen05_launch(const IGemmProblem& p, const Epilogue& epi, int* sta
   // three taps per filter row, one pixel apart, no ragged K block: the taps of a row share one activation block
   const bool tapfuse = pair && tapfuse_allowed() && p.taps_w == 3 && a.tap_step_w == 1 && p.k_per_tap % BLOCK_K == 0 && !a.bf16;
   const int tile_m = pair ? 2 * BLOCK_M : BLOCK_M;
-  a.idesc = a.bf16 ? ptx::make_idesc(1u, 1u, 1u, tile_m, (uint32_t)block_n)  // f32 accumulate, bf16 x bf16
+  a.idesc = a.bf16 ? ptx::make_idesc(1u, a.f16 ? 0u : 1u, a.f16 ? 0u : 1u, tile_m, (uint32_t)block_n)  // f32 accumulate, bf16 x bf16 or f16 x f16
                    : ptx::make_idesc(2u, p.a_unsigned ? 0u : 1u, p.b_unsigned ? 0u : 1u, tile_m, (uint32_t)block_n);
   a.num_m_tiles = (p.rows + tile_m - 1) / tile_m;
   a.num_n_tiles = (p.n + block_n - 1) / block_n;
