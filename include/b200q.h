@@ -128,7 +128,8 @@ typedef struct {
   int32_t with_bias, do_relu;
   int32_t right_transpose;   /* right operand stored [N,K] instead of [K,N] */
   int32_t left_transpose, output_transpose; /* input stored [batch][K][M] / output stored [batch][N][M] */
-  int32_t hdim_is_batch;                    /* must be 0: B200Q_ERR_UNSUPPORTED otherwise */
+  int32_t hdim_is_batch;                    /* batch x batch_low independent products; a transposed operand / output keeps
+                                             * batch_low between its matrix dimensions (see batch_low) */
   int32_t right_batched;     /* right operand has the batch dimension (activation x activation) */
   int32_t right_is_weight;   /* constant right operand: uploaded once per (handle, weight_version) */
   int32_t weight_version;    /* bump after rewriting the weight buffers in place */
@@ -143,6 +144,10 @@ typedef struct {
   const int64_t *rshifts;
   double out_scale;          /* B200Q_QM_ONLY_SCALE */
   int32_t algo;              /* 0 = auto, 1 = tensor cores only, 2 = CUDA cores only */
+  int64_t batch_low;         /* matmul_attr_t::batch_low, read with hdim_is_batch (0 = 1).  The layouts are those of
+                              * lib/Support/Dnnl/MatMul.cpp:172-241: left_transpose: input [batch][M][batch_low][K];
+                              * right_transpose: right [batch][K][batch_low][N]; output_transpose: output
+                              * [batch][M][batch_low][N]; an operand without its flag is [batch*batch_low][rows][cols]. */
 } b200q_matmul_desc;
 
 /* Operator face of tpu::MatMulOp::{init,inference,deinit}

@@ -248,15 +248,36 @@ def test_operator_face_left_and_output_transpose(lt, ot, batch, right_batched):
     assert np.array_equal(got, want.astype(np.float32)) and len(np.unique(want)) > 50
 
 
+@pytest.mark.parametrize("lt,rt,ot", [(True, True, True), (False, True, True), (True, False, False), (False, False, True)])
+def test_operator_face_hdim_is_batch(lt, rt, ot):
+    """hdim_is_batch (MatMul.cpp:58-104; lib/Support/Dnnl/MatMul.cpp:172-241): batch x batch_low products; a transposed
+    operand holds batch_low between its matrix dimensions, (B0, M, B1, K) x (B0, K, B1, N) = (B0, M, B1, N), and is put in
+    batch-major order by tensor_hc_transpose; an operand without its flag already is."""
+    rng = np.random.default_rng(41)
+    B0, B1, M, K, N = 2, 3, 37, 64, 48
+    A = rng.integers(-128, 128, size=(B0, B1, M, K), dtype=np.int8)
+    Bm = rng.integers(-128, 128, size=(B0, B1, K, N), dtype=np.int8)
+    want = np.stack([np.stack([oracle.matmul_int8(A[i, j], Bm[i, j], None, qmode=oracle.QM_MULTIPLIER_SHIFT, mult=[7], rshift=[12], out_zp=-2,
+                                                  do_relu=True) for j in range(B1)]) for i in range(B0)])
+    op = MatMulOp(batch=B0, batch_low=B1, M=M, K=K, N=N, hdim_is_batch=True, left_transpose=lt, right_transpose=rt, output_transpose=ot,
+                  right_batched=True, right_is_weight=False, do_relu=True, multipliers=[7], rshifts=[12], out_zp=-2)
+    a_in = np.ascontiguousarray(A.transpose(0, 2, 1, 3)) if lt else A
+    b_in = np.ascontiguousarray(Bm.transpose(0, 2, 1, 3)) if rt else Bm
+    out = np.zeros((B0, M, B1, N) if ot else (B0, B1, M, N), np.float32)
+    op.inference(InferenceParameter(inputs=[f32(a_in), f32(b_in)], outputs=[out]))
+    got = out.transpose(0, 2, 1, 3) if ot else out
+    assert np.array_equal(got, want.astype(np.float32)) and len(np.unique(want)) > 50
+
+
 def test_empty_and_errors():
     op = MatMulOp(M=0, K=16, N=8, multipliers=[1], rshifts=[0])
     out = np.zeros((0, 8), np.float32)
     op.inference(InferenceParameter(inputs=[np.zeros((0, 16), np.float32), np.zeros((16, 8), np.float32)], outputs=[out]))
-    op = MatMulOp(M=4, K=16, N=8, hdim_is_batch=True, multipliers=[1], rshifts=[0])
+    op = MatMulOp(M=4, K=16, N=8, hdim_is_batch=True, multipliers=[1], rshifts=[0])      # needs a batched right operand
     with pytest.raises(L.B200QError) as ei:
         op.inference(InferenceParameter(inputs=[np.zeros((4, 16), np.float32), np.zeros((16, 8), np.float32)],
                                         outputs=[np.zeros((4, 8), np.float32)]))
-    assert ei.value.code == L.ERR_UNSUPPORTED
+    assert ei.value.code == L.ERR_INVALID
     op = MatMulOp(M=4, K=16, N=8, quant_mode=L.QM_QDM, multipliers=[1], rshifts=[0])
     with pytest.raises(L.B200QError) as ei:
         op.inference(InferenceParameter(inputs=[np.zeros((4, 16), np.float32), np.zeros((16, 8), np.float32)],

@@ -41,7 +41,7 @@ class MatMulDesc(C.Structure):
                 ("input_dtype", C.c_int32), ("right_dtype", C.c_int32), ("out_dtype", C.c_int32),
                 ("quant_mode", C.c_int32), ("is_cv18xx", C.c_int32), ("fuse_rq", C.c_int32), ("out_zp", C.c_int32),
                 ("n_quant", C.c_int32), ("multipliers", C.POINTER(C.c_int64)), ("rshifts", C.POINTER(C.c_int64)),
-                ("out_scale", C.c_double), ("algo", C.c_int32)]
+                ("out_scale", C.c_double), ("algo", C.c_int32), ("batch_low", C.c_int64)]
 
 
 class FusedAdd(C.Structure):

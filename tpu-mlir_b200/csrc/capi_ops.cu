@@ -12,6 +12,7 @@
 #include "igemm.h"
 #include "internal.h"
 #include "layout.h"
+#include "top_f32.h"
 
 namespace b200q {
 namespace {
@@ -152,7 +153,11 @@ int resolve_matmul(const b200q_matmul_desc& d, const float* multi_operand, int b
 int validate_matmul(const b200q_matmul_desc& d) {
   if (d.batch < 1 || d.M < 0 || d.K < 1 || d.N < 1) return set_error(B200Q_ERR_INVALID, "matmul: bad shape");
   if (d.M * d.batch > 0x7fffffffLL || d.N > 0x7fffffffLL || d.K > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: dimension exceeds int32");
-  if (d.hdim_is_batch) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: hdim_is_batch is not implemented");
+  if (d.hdim_is_batch) {
+    if (d.batch_low < 0 || d.M * d.batch * (d.batch_low ? d.batch_low : 1) > 0x7fffffffLL) return set_error(B200Q_ERR_INVALID, "matmul: bad batch_low");
+    if (!d.right_batched) return set_error(B200Q_ERR_INVALID, "matmul: hdim_is_batch goes with a batched right operand");
+    if (d.is_cv18xx) return set_error(B200Q_ERR_UNSUPPORTED, "matmul: hdim_is_batch in the CV18xx form is not implemented");
+  }
   if (!is_q8(d.input_dtype) || !is_q8(d.right_dtype)) return set_error(B200Q_ERR_INVALID, "matmul: operands must be int8/uint8");
   return B200Q_OK;
 }
@@ -184,7 +189,7 @@ int gemm_dispatch(const void* a, int a_dt, const void* b_nk, int b_dt, int64_t M
 }
 
 struct MatMulHandle {
-  DevBuf stage_f32, a_q8, b_f32, b_nk, bias, mult, shift, out_q, out_f32, status;
+  DevBuf stage_f32, a_q8, b_f32, b_nk, bias, mult, shift, out_q, out_f32, status, perm;
   bool weights_ready = false;
   int weight_version = -1;
   const float* weight_ptr = nullptr;
@@ -559,6 +564,22 @@ int conv_run(ConvHandle* h, const void* x, int x_is_f32, void* y, cudaStream_t s
   return conv2d_i8_direct_launch(xin, d.input_dtype == B200Q_DT_U8, h->w_oihw.as<int8_t>(), g, h->epi, y, s);
 }
 
+// tensor_hc_transpose (include/tpu_mlir/Support/MathUtils.h:213-228): src [n][c][h][w] -> dst [n][h][c][w]
+int hc_transpose_f32(const float* src, float* dst, long long n, long long c, long long h, long long w, cudaStream_t s) {
+  TopRemap m{};
+  const long long dims[6] = {1, 1, n, h, c, w}, sstr[6] = {0, 0, c * h * w, w, h * w, 1}, dstr[6] = {0, 0, c * h * w, c * w, w, 1};
+  for (int i = 0; i < 6; ++i) {
+    m.dims[i] = dims[i];
+    m.src_stride[i] = sstr[i];
+    m.dst_stride[i] = dstr[i];
+    m.mul[i] = m.div[i] = 1;
+    m.mod[i] = m.off[i] = 0;
+    m.extent[i] = dims[i];
+  }
+  m.dst_offset = 0;
+  return top_remap_launch(src, dst, 4, m, nullptr, s);
+}
+
 }  // namespace
 }  // namespace b200q
 
@@ -598,19 +619,31 @@ int b200q_matmul_inference(const b200q_matmul_desc* desc, float* const* inputs, 
     const float* bias_f = (d.with_bias && n_inputs > 2) ? inputs[2] : nullptr;
     const float* multi_f = (n_inputs > 3) ? inputs[3] : nullptr;
     if (d.with_bias && !bias_f) { rc = set_error(B200Q_ERR_INVALID, "matmul: with_bias but inputs[2] is null"); break; }
-    const int64_t nb = d.right_batched ? d.batch : 1;
-    const int64_t rows = d.right_batched ? d.M : d.batch * d.M;  // a shared right operand folds the batch into M
-    const size_t a_elems = (size_t)(d.batch * d.M * d.K), b_elems = (size_t)(nb * d.K * d.N), o_elems = (size_t)(d.batch * d.M * d.N);
+    // hdim_is_batch: batch x batch_low independent products; a transposed operand / output carries batch_low between its
+    // matrix dimensions and is brought to batch-major order by tensor_hc_transpose first (lib/Support/Dnnl/MatMul.cpp:172-241)
+    const bool hdim = d.hdim_is_batch != 0;
+    const int64_t blow = hdim && d.batch_low > 0 ? d.batch_low : 1;
+    const int64_t B = d.batch * blow;
+    const bool right_t = d.right_transpose && !hdim, left_t = d.left_transpose && !hdim, out_t = d.output_transpose && !hdim;
+    const int64_t nb = d.right_batched ? B : 1;
+    const int64_t rows = d.right_batched ? d.M : B * d.M;  // a shared right operand folds the batch into M
+    const size_t a_elems = (size_t)(B * d.M * d.K), b_elems = (size_t)(nb * d.K * d.N), o_elems = (size_t)(B * d.M * d.N);
     // right operand: [N,K] bytes per batch
     const bool cached = d.right_is_weight && h->weights_ready && h->weight_version == d.weight_version && h->weight_ptr == inputs[1];
     if (!cached) {
       if ((rc = h->b_f32.ensure(b_elems * 4))) break;
       if ((rc = h->b_nk.ensure(b_elems))) break;
       if (cudaMemcpyAsync(h->b_f32.p, inputs[1], b_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D right", __FILE__, __LINE__); break; }
+      const float* right_f = h->b_f32.as<float>();
+      if (hdim && d.right_transpose) {   // [batch][K][batch_low][N] -> [batch][batch_low][K][N]
+        if ((rc = h->perm.ensure(b_elems * 4))) break;
+        if ((rc = hc_transpose_f32(right_f, h->perm.as<float>(), d.batch, d.K, blow, d.N, s))) break;
+        right_f = h->perm.as<float>();
+      }
       for (int64_t b = 0; b < nb && rc == B200Q_OK; ++b) {
-        const float* src = h->b_f32.as<float>() + b * d.K * d.N;
+        const float* src = right_f + b * d.K * d.N;
         uint8_t* dst = h->b_nk.as<uint8_t>() + b * d.K * d.N;
-        rc = d.right_transpose ? f32_to_q8(src, dst, d.K * d.N, s) : transpose_to_u8(src, 1, dst, (int)d.K, (int)d.N, s);
+        rc = right_t ? f32_to_q8(src, dst, d.K * d.N, s) : transpose_to_u8(src, 1, dst, (int)d.K, (int)d.N, s);
       }
       if (rc) break;
       if (bias_f) {
@@ -632,7 +665,11 @@ int b200q_matmul_inference(const b200q_matmul_desc* desc, float* const* inputs, 
     if ((rc = h->out_q.ensure(o_elems * dtype_size(d.out_dtype)))) break;
     if ((rc = h->out_f32.ensure(o_elems * 4))) break;
     if (cudaMemcpyAsync(h->stage_f32.p, inputs[0], a_elems * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) { rc = cuda_error(cudaGetLastError(), "H2D input", __FILE__, __LINE__); break; }
-    if (d.left_transpose) {
+    if (hdim && d.left_transpose) {   // [batch][M][batch_low][K] -> [batch][batch_low][M][K]
+      if ((rc = h->perm.ensure(a_elems * 4))) break;
+      if ((rc = hc_transpose_f32(h->stage_f32.as<float>(), h->perm.as<float>(), d.batch, d.M, blow, d.K, s))) break;
+      if ((rc = f32_to_q8(h->perm.as<float>(), h->a_q8.p, (long long)a_elems, s))) break;
+    } else if (left_t) {
       // the input is stored [batch][K][M] (MatMul.cpp:24-135 reads M from the last dimension; lib/Support/Dnnl/MatMul.cpp:
       // 182-186 transposes every batch entry before the product)
       for (int64_t b = 0; b < d.batch && rc == B200Q_OK; ++b)
@@ -641,7 +678,7 @@ int b200q_matmul_inference(const b200q_matmul_desc* desc, float* const* inputs, 
     } else if ((rc = f32_to_q8(h->stage_f32.as<float>(), h->a_q8.p, (long long)a_elems, s))) {
       break;
     }
-    const int n_launch = (d.right_batched || d.is_cv18xx) ? (int)d.batch : 1;
+    const int n_launch = (d.right_batched || d.is_cv18xx) ? (int)B : 1;
     const int64_t rows_per = (n_launch == 1) ? rows : d.M;
     for (int b = 0; b < n_launch && rc == B200Q_OK; ++b) {
       ResolvedRequant r;
@@ -659,7 +696,11 @@ int b200q_matmul_inference(const b200q_matmul_desc* desc, float* const* inputs, 
     if (rc) break;
     if ((rc = q_to_f32(h->out_q.p, d.out_dtype, h->out_f32.as<float>(), (long long)o_elems, s))) break;
     const float* result = h->out_f32.as<float>();
-    if (d.output_transpose) {
+    if (hdim && d.output_transpose) {   // [batch][batch_low][M][N] -> [batch][M][batch_low][N]
+      if ((rc = h->stage_f32.ensure(o_elems * 4))) break;
+      if ((rc = hc_transpose_f32(h->out_f32.as<float>(), h->stage_f32.as<float>(), d.batch, blow, d.M, d.N, s))) break;
+      result = h->stage_f32.as<float>();
+    } else if (out_t) {
       // the output is stored [batch][N][M] (lib/Support/Dnnl/MatMul.cpp:229-238)
       if ((rc = h->stage_f32.ensure(o_elems * 4))) break;
       for (int64_t b = 0; b < d.batch && rc == B200Q_OK; ++b)

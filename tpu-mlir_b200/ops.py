@@ -50,7 +50,7 @@ class MatMulOp:
                  left_transpose=False, output_transpose=False, hdim_is_batch=False, right_batched=False,
                  right_is_weight=True, input_zp=0, right_zp=0, input_dtype=L.DT_I8, right_dtype=L.DT_I8,
                  out_dtype=L.DT_I8, quant_mode=L.QM_MULTIPLIER_SHIFT, is_cv18xx=False, fuse_rq=False, out_zp=0,
-                 multipliers: Sequence[int] = (), rshifts: Sequence[int] = (), out_scale=0.0, algo=L.ALGO_AUTO):
+                 multipliers: Sequence[int] = (), rshifts: Sequence[int] = (), out_scale=0.0, algo=L.ALGO_AUTO, batch_low=1):
         self._mult, mult_p = _i64_array(multipliers if len(np.atleast_1d(multipliers)) else [1])
         self._rs, rs_p = _i64_array(rshifts if len(np.atleast_1d(rshifts)) else [0])
         n_quant = 0 if (len(np.atleast_1d(multipliers)) == 0 and len(np.atleast_1d(rshifts)) == 0) else \
@@ -69,7 +69,7 @@ class MatMulOp:
                                  weight_version=0, input_zp=input_zp, right_zp=right_zp, input_dtype=input_dtype,
                                  right_dtype=right_dtype, out_dtype=out_dtype, quant_mode=quant_mode,
                                  is_cv18xx=int(is_cv18xx), fuse_rq=int(fuse_rq), out_zp=out_zp, n_quant=n_quant,
-                                 multipliers=mult_p, rshifts=rs_p, out_scale=float(out_scale), algo=algo)
+                                 multipliers=mult_p, rshifts=rs_p, out_scale=float(out_scale), algo=algo, batch_low=int(batch_low))
 
     def invalidate_weights(self):
         """Call after rewriting the weight/bias buffers in place (the interpreter does that in setTensor)."""
