@@ -669,3 +669,36 @@ def test_tpu_deconv(cfg):
     m = run_graph(tensors, ops, {"y_filter": w, "y_bias": b}, {"x": x})
     m.check_status()
     assert np.array_equal(m.get_raw_tensor("y"), want)
+
+
+def test_binary_ops_broadcast():
+    """Operands of different shapes (numpy broadcasting): per-channel and scalar second operands, a broadcast first operand."""
+    rng = np.random.default_rng(18)
+    x = rng.standard_normal((2, 3, 4, 5)).astype(np.float32)
+    c = (rng.standard_normal((1, 3, 1, 1)) + 2).astype(np.float32)
+    row = rng.standard_normal((5,)).astype(np.float32)
+    ops = [dict(type="top.Add", name="add", inputs=["x", "c"], attrs=dict(do_relu=True)),
+           dict(type="top.Mul", name="mul", inputs=["x", "row"], attrs={}),
+           dict(type="top.Sub", name="sub", inputs=["c", "x"], attrs={}),
+           dict(type="top.Div", name="div", inputs=["x", "c"], attrs={}),
+           dict(type="tpu.Sub", name="tsub", inputs=["x", "c"], attrs=dict(is_reverse=True))]
+    tensors = {"x": f32(x.shape), "c": f32(c.shape), "row": f32(row.shape)}
+    tensors.update({o["name"]: f32(x.shape) for o in ops})
+    m = run_graph(tensors, ops, {}, {"x": x, "c": c, "row": row})
+    g = m.get_tensor
+    assert np.array_equal(g("add"), np.maximum(x + c, 0))
+    assert np.array_equal(g("mul"), x * row)
+    assert np.array_equal(g("sub"), c - x)
+    assert np.array_equal(g("div"), x / c)
+    assert np.array_equal(g("tsub"), c - x)
+    # 8-bit: tpu.Mul and tpu.Add with a per-channel operand
+    q = rng.integers(-128, 128, (2, 3, 4, 5), dtype=np.int8)
+    qc = rng.integers(-128, 128, (1, 3, 1, 1), dtype=np.int8)
+    qi = lambda shp: dict(shape=list(shp), dtype="i8", scale=0.05, zp=0)  # noqa: E731
+    ops = [dict(type="tpu.Mul", name="mul", inputs=["x", "c"], attrs=dict(multiplier=77, rshift=12)),
+           dict(type="tpu.Add", name="add", inputs=["c", "x"], attrs=dict(multipliers=[90, 70], rshifts=[7, 7], do_relu=True))]
+    m = run_graph({"x": qi(q.shape), "c": qi(qc.shape), "mul": qi(q.shape), "add": qi(q.shape)}, ops, {}, {"x": q, "c": qc})
+    prod = q.astype(np.int64) * qc
+    assert np.array_equal(m.get_raw_tensor("mul"), np.clip((prod * 77 + (1 << 11)) >> 12, -128, 127).astype(np.int8))
+    ssum = ((qc.astype(np.int64) * 90 + 64) >> 7) + ((q.astype(np.int64) * 70 + 64) >> 7)
+    assert np.array_equal(m.get_raw_tensor("add"), np.clip(np.maximum(ssum, 0), -128, 127).astype(np.int8))

@@ -90,6 +90,7 @@ class module:  # noqa: N801  (name of the reference class)
             from .mlir_text import load_mlir
             graph, weights = load_mlir(graph, weights if isinstance(weights, str) else None)
         self.graph = graph
+        self._extra_info = {}        # expanded copies of broadcast operands (not tensors of the graph)
         self.input_names = list(graph["inputs"])
         self.output_names = list(graph["outputs"])
         self.all_tensor_names = list(graph["tensors"].keys())
@@ -164,7 +165,8 @@ class module:  # noqa: N801  (name of the reference class)
             pass
 
     def _info(self, name):
-        return self.graph["tensors"][name]
+        info = self.graph["tensors"].get(name)
+        return info if info is not None else self._extra_info[name]
 
     @staticmethod
     def _assign_layouts(graph, weights):
@@ -205,6 +207,9 @@ class module:  # noqa: N801  (name of the reference class)
         iinfo = [self._info(n) for n in op["inputs"]]
         oinfo = self._info(op["name"])
         stream = lambda: C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)  # noqa: E731
+        if t.split(".", 1)[-1] in ("Add", "Mul", "Sub", "Div") and len(ins) == 2 and \
+                (list(iinfo[0]["shape"]) != list(oinfo["shape"]) or list(iinfo[1]["shape"]) != list(oinfo["shape"])):
+            return self._plan_broadcast(op, stream)
         if t.split(".", 1)[-1] in _MOVE_OPS:
             return self._plan_move(op, stream)
         if t in ("top.Interp", "tpu.Interp"):
@@ -543,6 +548,50 @@ class module:  # noqa: N801  (name of the reference class)
             st.insert(0, acc)
             acc *= d
         return st
+
+    def _plan_broadcast(self, op, stream) -> Callable:
+        """A binary op whose operands broadcast (numpy rules, as the reference's binary ops do through their library call):
+        the smaller operand is expanded to the output's shape by the index-mapping kernel (stride 0 along the broadcast
+        dimensions), then the op's equal-shape kernel runs."""
+        name, lib = op["name"], self.lib
+        oshape = list(self._info(name)["shape"])
+        r = len(oshape)
+        if r > 6 or name in self._nhwc:
+            raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: broadcasting {op['type']} takes NCHW tensors of at most six dimensions")
+        runs, new_inputs = [], []
+        for k, nm in enumerate(op["inputs"]):
+            ish = list(self._info(nm)["shape"])
+            if ish == oshape:
+                new_inputs.append(nm)
+                continue
+            ish = [1] * (r - len(ish)) + ish
+            if nm in self._nhwc or len(ish) != r or any(d not in (1, o) for d, o in zip(ish, oshape)):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: operand {nm} {ish} does not broadcast to {oshape}")
+            syn = f"{name}__operand{k}"
+            self._extra_info[syn] = dict(self._info(nm), shape=oshape)
+            src = self.tensors[nm]
+            self.tensors[syn] = self.torch.empty(oshape, dtype=src.dtype, device=self.device)
+            sstr, acc = [], 1
+            for d in reversed(ish):
+                sstr.insert(0, 0 if d == 1 else acc)
+                acc *= d
+            ostr, acc = [], 1
+            for d in reversed(oshape):
+                ostr.insert(0, acc)
+                acc *= d
+            pad6 = lambda v, fill: (C.c_int64 * 6)(*([fill] * (6 - r) + [int(x) for x in v]))  # noqa: E731
+            d_ = L.RemapDesc(dims=pad6(oshape, 1), src_stride=pad6(sstr, 0), mul=pad6([1] * r, 1), div=pad6([1] * r, 1), mod=pad6([0] * r, 0),
+                             off=pad6([0] * r, 0), extent=pad6(oshape, 1), dst_stride=pad6(ostr, 0), dst_offset=0)
+            runs.append((nm, syn, d_, src.element_size()))
+            new_inputs.append(syn)
+        inner = self._plan(dict(op, inputs=new_inputs))
+        self._keep.append(runs)
+
+        def run():
+            for nm, syn, d_, eb in runs:
+                L.check(lib.b200q_remap_dev(_P(self.tensors[nm]), _P(self.tensors[syn]), eb, C.byref(d_), None, stream()))
+            inner()
+        return run
 
     def _plan_move(self, op, stream) -> Callable:
         """Slice, Permute, Tile, Upsample, Pad, Concat, Squeeze, Unsqueeze of either dialect: pure data movement, one index
