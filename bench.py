@@ -291,6 +291,31 @@ def kernel_lines(workload, steps, warmup, a16_m=(1, 2, 4, 8, 16, 32, 128, 2048))
                           roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s",
                                         frac=gbs / peaks["hbm_gbs"], traffic=None,
                                         peak_basis=f"{peaks['source']} copy bandwidth")))
+    elif workload == "dwconv":
+        # a depthwise 3x3 layer of a mobile network (MobileNetV2 block, 384 channels at 28x28), NCHW: the CUDA-core patch kernel
+        from tpu_mlir_b200.ops import Conv2DOp
+        N, Cc, H, W = 256, 384, 28, 28
+        rng = np.random.default_rng(0)
+        op = Conv2DOp(input_shape=(N, Cc, H, W), oc=Cc, kernel_shape=(3, 3), pads=(1, 1, 1, 1), group=Cc, do_relu=True,
+                      quant_mode=L.QM_MULTIPLIER_SHIFT, multiplier=rng.integers(5000, 30000, Cc), rshift=rng.integers(14, 20, Cc))
+        x = torch.randint(-128, 128, (N, Cc, H, W), dtype=torch.int8, device="cuda")
+        w = torch.randint(-64, 64, (Cc, 1, 3, 3), dtype=torch.int8, device="cuda")
+        bias = torch.randint(-4096, 4096, (Cc,), dtype=torch.int32, device="cuda")
+        y = torch.empty((N, Cc, H, W), dtype=torch.int8, device="cuda")
+        h = C.c_void_p()
+        L.check(lib.b200q_conv2d_dev_create(C.byref(op.desc), P(w), P(bias), C.byref(h)))
+        mean_ms = _time_steps(lambda i: L.check(lib.b200q_conv2d_dev_run(h, P(x), P(y), None)), min(steps, 100), warmup)
+        L.check(lib.b200q_conv2d_dev_status(h, None))
+        lib.b200q_conv2d_dev_destroy(C.byref(h))
+        nbytes = x.numel() + y.numel() + w.numel()
+        gbs = nbytes / (mean_ms * 1e-3) / 1e9
+        lines.append(dict(metric="int8 depthwise conv GB/s", value=gbs, unit="GB/s", ms_per_step=mean_ms,
+                          config=dict(workload="tpu.Conv2D int8 depthwise NCHW n256 c384 28x28 k3 s1 p1, per-channel MultiplierShift "
+                                               "requant + ReLU (CUDA-core patch kernel)",
+                                      l2="input + output = 154 MB > L2", bytes_per_call=int(nbytes)),
+                          roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s",
+                                        frac=gbs / peaks["hbm_gbs"], traffic=None,
+                                        peak_basis=f"{peaks['source']} copy bandwidth")))
     elif workload == "a16":
         # one MLP layer of a 7B decoder through the handle API (tensors stay the caller's); every M reads the packed
         # weights (24.7 MB) from 8 weight sets used round-robin so that no call finds them in L2
@@ -739,7 +764,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="conv",
-                    choices=["conv", "gemm", "conv1x1", "a16", "hist", "top", "peak", "resnet50", "calib"],
+                    choices=["conv", "gemm", "conv1x1", "dwconv", "a16", "hist", "top", "peak", "resnet50", "calib"],
                     help="conv = the benchmark contract (BASELINE config 1) with every other workload under `extras`; "
                          "any other value prints that workload's lines alone")
     ap.add_argument("--no-extras", action="store_true", help="headline only")
@@ -778,7 +803,7 @@ def main():
             if R.rank == 0:
                 extras["resnet50"], extras["calibration"] = r, c
                 if R.world == 1:
-                    for wl in ("gemm", "conv1x1", "a16", "hist", "top"):
+                    for wl in ("gemm", "conv1x1", "dwconv", "a16", "hist", "top"):
                         extras[wl] = guarded(kernel_lines, wl, 100, 5)
                 extras["seconds"] = time.time() - t0
                 line["extras"] = extras

@@ -126,6 +126,13 @@ def test_conv_tensor_core_shapes(case):
     dict(N=2, C=3, H=32, W=32, OC=16, k=7, stride=(2, 2), pads=(3, 3, 3, 3), group=1, dil=(1, 1)),   # ResNet stem
     dict(N=1, C=16, H=12, W=12, OC=16, k=3, stride=(1, 1), pads=(1, 1, 1, 1), group=16, dil=(1, 1)),  # depthwise
     dict(N=1, C=8, H=15, W=15, OC=12, k=3, stride=(2, 1), pads=(2, 2, 2, 2), group=2, dil=(2, 2)),    # dilation, groups
+    # depthwise shapes of the patch kernel: 4-row and 2-row patches, ragged edges, both strides and filter sizes, uneven pads
+    dict(N=2, C=24, H=28, W=28, OC=24, k=3, stride=(1, 1), pads=(1, 1, 1, 1), group=24, dil=(1, 1)),
+    dict(N=2, C=10, H=29, W=31, OC=10, k=3, stride=(2, 2), pads=(0, 1, 1, 0), group=10, dil=(1, 1)),
+    dict(N=3, C=7, H=7, W=7, OC=7, k=3, stride=(1, 1), pads=(1, 1, 1, 1), group=7, dil=(1, 1)),
+    dict(N=1, C=5, H=17, W=13, OC=5, k=5, stride=(1, 1), pads=(2, 2, 2, 2), group=5, dil=(1, 1)),
+    dict(N=2, C=6, H=14, W=14, OC=6, k=5, stride=(2, 2), pads=(2, 1, 1, 2), group=6, dil=(1, 1)),
+    dict(N=1, C=4, H=3, W=2, OC=4, k=3, stride=(1, 1), pads=(1, 1, 1, 1), group=4, dil=(1, 1)),
 ])
 def test_conv_cuda_core_shapes(case):
     rng = np.random.default_rng(77)

@@ -1,6 +1,7 @@
 // CUDA-core INT8 convolution / GEMM for the shapes the tensor-core implicit GEMM does not take
 // (channel counts that are not a multiple of 16, strides, dilation, groups, zero points, batched right
-// operands).  One thread per output element, int32 accumulation, the same exact epilogue (requant.cuh).
+// operands).  One thread per output element, int32 accumulation, the same exact epilogue (requant.cuh); depthwise 3 x 3 and
+// 5 x 5 convolutions have a kernel of their own (a patch of outputs per thread).
 // Semantics: tpu::Conv2DOp::inference (lib/Dialect/Tpu/Interfaces/Common/Conv2D.cpp:264-341) and
 // tpu::MatMulOp::inference (MatMul.cpp:599-728) for uniform-quantized outputs.
 #include "igemm.h"
@@ -75,12 +76,169 @@ __global__ void gemm_i8_direct_kernel(const void* __restrict__ a, int a_unsigned
   st_q(out, idx, e.out_dtype, finish(acc, col, e));
 }
 
+// RSR(a * m, s, half up) for 1 <= s <= 62, saturated to int32, in 32-bit operations: floor((a * m + 2^(s-1)) / 2^s)
+// (the identity requant.cuh uses; |a * m| < 2^62, so adding the half cannot overflow).
+__device__ __forceinline__ int rshift_half_up_sat32(int a, int m, int s, unsigned half_lo, int half_hi) {
+  const unsigned lo = (unsigned)a * (unsigned)m;
+  int hi = __mulhi(a, m);
+  const unsigned lo2 = lo + half_lo;
+  hi += half_hi + (lo2 < lo ? 1 : 0);
+  const int k1 = s < 31 ? s : 31, k2 = s - k1;      // an arithmetic 64-bit shift by s as two shifts of at most 31
+  const unsigned l1 = __funnelshift_r(lo2, (unsigned)hi, k1);
+  const int h1 = hi >> k1;
+  const unsigned l2 = __funnelshift_r(l1, (unsigned)h1, k2);
+  const int h2 = h1 >> k2;
+  return h2 == ((int)l2 >> 31) ? (int)l2 : (h2 < 0 ? (int)0x80000000 : 0x7fffffff);
+}
+
+// Depthwise convolution (groups == ic == oc), square K x K filter, stride S, no dilation: the memory-bound case of the
+// mobile networks.  One thread owns a patch of R rows x 4 columns of one plane's output; it walks the (R - 1) * S + K input
+// rows the patch needs once, holding one row's span of 3 * S + K bytes and the filter in registers, so every input byte is
+// loaded once per patch and all index arithmetic is 32-bit.  The epilogue is the shared exact one.  8-bit outputs of
+// full patches leave as one 32-bit store per row.
+template <int K, int S, int R, bool FAST_RQ>
+__global__ void __launch_bounds__(256)
+dwconv_i8_kernel(const uint8_t* __restrict__ x, int x_unsigned, const int8_t* __restrict__ w, ConvGeometry g, Epilogue e,
+                 void* __restrict__ y, unsigned xq_per_row, unsigned yt_per_plane, unsigned total) {
+  const unsigned tid = blockIdx.x * blockDim.x + threadIdx.x;       // the launcher keeps the thread count below 2^32
+  if (tid >= total) return;
+  const unsigned per_plane = xq_per_row * yt_per_plane;
+  const unsigned plane = tid / per_plane, in_plane = tid - plane * per_plane;     // plane = n * C + c
+  const int yt = (int)(in_plane / xq_per_row), xq = (int)(in_plane - (unsigned)yt * xq_per_row);
+  const int c = (int)(plane % (unsigned)g.oc);
+  constexpr int SPAN = 3 * S + K, ROWS = (R - 1) * S + K;
+  int wv[K][K];
+#pragma unroll
+  for (int i = 0; i < K; ++i)
+#pragma unroll
+    for (int j = 0; j < K; ++j) wv[i][j] = w[c * K * K + i * K + j];
+  const uint8_t* xp = x + (long long)plane * (g.ih * g.iw);
+  const int x0 = xq * 4, y0 = yt * R;
+  const int ix0 = x0 * S - g.pwl, iy0 = y0 * S - g.pht;
+  int acc[R][4];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int o = 0; o < 4; ++o) acc[r][o] = 0;
+  // a patch whose whole input window lies inside the image (most of them) loads without tests
+  const bool interior = ix0 >= 0 && ix0 + SPAN <= g.iw && iy0 >= 0 && iy0 + ROWS <= g.ih;
+#pragma unroll
+  for (int rel = 0; rel < ROWS; ++rel) {
+    const int iy = iy0 + rel;
+    const uint8_t* rp = xp + iy * g.iw + ix0;
+    int xv[SPAN];
+    if (interior) {
+#pragma unroll
+      for (int j = 0; j < SPAN; ++j) {
+        const int v = rp[j];
+        xv[j] = x_unsigned ? v : (int)(int8_t)v;
+      }
+    } else {
+      const bool row_ok = (unsigned)iy < (unsigned)g.ih;
+#pragma unroll
+      for (int j = 0; j < SPAN; ++j) {
+        int v = g.pad_value;
+        if (row_ok && (unsigned)(ix0 + j) < (unsigned)g.iw) {
+          v = rp[j];
+          if (!x_unsigned) v = (int)(int8_t)v;
+        }
+        xv[j] = v;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int fy = rel - r * S;      // compile-time after unrolling
+      if (fy >= 0 && fy < K) {
+#pragma unroll
+        for (int o = 0; o < 4; ++o)
+#pragma unroll
+          for (int fx = 0; fx < K; ++fx) acc[r][o] += xv[o * S + fx] * wv[fy][fx];
+      }
+    }
+  }
+  const int bias = e.bias ? e.bias[c] : 0;
+  const int qi = e.per_channel ? c : 0;
+  const int32_t m = e.multiplier ? e.multiplier[qi] : 1;
+  const int32_t sft = e.shift ? e.shift[qi] : 0;
+  const bool out8 = e.out_dtype == B200Q_DT_I8 || e.out_dtype == B200Q_DT_U8;
+  // FAST_RQ: MultiplierShift, half up, 8-bit output; a shift outside [1, 62] takes the general function
+  const bool lean = FAST_RQ && sft >= 1 && sft <= 62;
+  const unsigned half_lo = (lean && sft <= 32) ? (1u << (sft - 1)) : 0u;
+  const int half_hi = (lean && sft > 32) ? (1 << (sft - 33)) : 0;
+  const int q_lo = e.out_dtype == B200Q_DT_U8 ? 0 : -128, q_hi = e.out_dtype == B200Q_DT_U8 ? 255 : 127;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int yo = y0 + r;
+    if (yo >= g.oh) break;
+    int q[4];
+#pragma unroll
+    for (int o = 0; o < 4; ++o) {
+      int a = acc[r][o] + bias;
+      if (e.relu == B200Q_RELU_BEFORE_REQUANT && a < 0) a = 0;
+      if (lean) {
+        int v = rshift_half_up_sat32(a, m, sft, half_lo, half_hi);
+        v = max(min(v, 1 << 24), -(1 << 24)) + e.out_zp;      // far outside every 8-bit range already; the zero point cannot wrap it
+        if (e.relu == B200Q_RELU_AFTER_REQUANT) v = max(v, e.out_zp);
+        q[o] = max(min(v, q_hi), q_lo);
+      } else {
+        q[o] = requant_value<-1, -1>(a, m, sft, e);
+      }
+    }
+    const long long at = ((long long)plane * g.oh + yo) * g.ow + x0;
+    if (out8 && x0 + 3 < g.ow && (at & 3) == 0) {
+      reinterpret_cast<uint32_t*>(y)[at >> 2] = (uint32_t)(q[0] & 255) | ((uint32_t)(q[1] & 255) << 8) | ((uint32_t)(q[2] & 255) << 16) |
+                                                 ((uint32_t)(q[3] & 255) << 24);
+    } else {
+#pragma unroll
+      for (int o = 0; o < 4; ++o)
+        if (x0 + o < g.ow) st_q(y, at + o, e.out_dtype, q[o]);
+    }
+  }
+}
+
+template <int K, int S, int R>
+int dwconv_launch_krs(const void* x, int x_unsigned, const int8_t* w, const ConvGeometry& g, const Epilogue& epi, void* y, cudaStream_t stream) {
+  const int xq = (g.ow + 3) / 4, yt = (g.oh + R - 1) / R;
+  const long long total = (long long)g.n * g.oc * xq * yt;
+  if (total == 0) return B200Q_OK;
+  const long long blocks = (total + 255) / 256;
+  if (total >= 0xffffff00LL) return set_error(B200Q_ERR_UNSUPPORTED, "depthwise conv: output too large");
+  const bool fast = epi.dialect == B200Q_RQ_MULTIPLIER_SHIFT && epi.round_mode == B200Q_ROUND_HALF_UP &&
+                    (epi.out_dtype == B200Q_DT_I8 || epi.out_dtype == B200Q_DT_U8);
+  if (fast)
+    dwconv_i8_kernel<K, S, R, true><<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(x), x_unsigned, w, g, epi, y, (unsigned)xq, (unsigned)yt, (unsigned)total);
+  else
+    dwconv_i8_kernel<K, S, R, false><<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(x), x_unsigned, w, g, epi, y, (unsigned)xq, (unsigned)yt, (unsigned)total);
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+// 1 = launched, 0 = not a shape this kernel takes
+template <int K, int S>
+int dwconv_launch_ks(const void* x, int x_unsigned, const int8_t* w, const ConvGeometry& g, const Epilogue& epi, void* y, cudaStream_t stream,
+                     int* rc) {
+  *rc = g.oh >= 12 ? dwconv_launch_krs<K, S, 4>(x, x_unsigned, w, g, epi, y, stream) : dwconv_launch_krs<K, S, 2>(x, x_unsigned, w, g, epi, y, stream);
+  return 1;
+}
+
+int dwconv_try(const void* x, int x_unsigned, const int8_t* w, const ConvGeometry& g, const Epilogue& epi, void* y, cudaStream_t stream, int* rc) {
+  if (g.groups != g.ic || g.oc != g.ic || g.kh != g.kw || g.sh != g.sw || g.dh != 1 || g.dw != 1) return 0;
+  if ((long long)g.ih * g.iw > 0x3fffffffLL) return 0;
+  if (g.kh == 3 && g.sh == 1) return dwconv_launch_ks<3, 1>(x, x_unsigned, w, g, epi, y, stream, rc);
+  if (g.kh == 3 && g.sh == 2) return dwconv_launch_ks<3, 2>(x, x_unsigned, w, g, epi, y, stream, rc);
+  if (g.kh == 5 && g.sh == 1) return dwconv_launch_ks<5, 1>(x, x_unsigned, w, g, epi, y, stream, rc);
+  if (g.kh == 5 && g.sh == 2) return dwconv_launch_ks<5, 2>(x, x_unsigned, w, g, epi, y, stream, rc);
+  return 0;
+}
+
 }  // namespace
 
 int conv2d_i8_direct_launch(const void* x, int x_unsigned, const int8_t* w, const ConvGeometry& g, const Epilogue& epi,
                             void* y, cudaStream_t stream) {
   const long long total = (long long)g.n * g.oc * g.oh * g.ow;
   if (total == 0) return B200Q_OK;
+  int rc = B200Q_OK;
+  if (dwconv_try(x, x_unsigned, w, g, epi, y, stream, &rc)) return rc;
   const int threads = 256;
   const long long blocks = (total + threads - 1) / threads;
   if (blocks > 0x7fffffffLL) return set_error(B200Q_ERR_UNSUPPORTED, "direct conv: output too large");
