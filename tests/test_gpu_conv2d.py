@@ -151,6 +151,23 @@ def test_conv_cuda_core_shapes(case):
         assert np.array_equal(got, want.astype(np.float32)), (case, qmode)
 
 
+@pytest.mark.parametrize("u8_in", [False, True])
+def test_depthwise_requant_forms(u8_in):
+    """The depthwise kernel's three MultiplierShift forms: shifts of 32 and more with 31-bit multipliers, small multipliers
+    under a short shift (scaled to a 32-bit binary point) and multipliers too large for that; signed and unsigned inputs,
+    a non-zero output zero point with ReLU."""
+    rng = np.random.default_rng(78)
+    C_ = 12
+    x = rng.integers(0, 256, size=(2, C_, 19, 23)).astype(np.uint8) if u8_in else rng.integers(-128, 128, size=(2, C_, 19, 23), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(C_, 1, 3, 3), dtype=np.int8)
+    mult = np.array([2**30 + 12345, -(2**30) + 999, 1_500_000_000, 900_000_000, 37, 500, 20000, 19999, 3, 1, 65535, 2**20], dtype=np.int64)
+    rshift = np.array([44, 45, 46, 32, 8, 12, 11, 15, 2, 1, 20, 30], dtype=np.int64)
+    c = dict(x=x, w=w, bias=rng.integers(-3000, 3000, size=C_, dtype=np.int32), mult=mult, rshift=rshift)
+    want, m_, s_ = oracle_conv(c, groups=C_, qmode=oracle.QM_MULTIPLIER_SHIFT, out_zp=5, do_relu=True)
+    got = run_operator_face(c, group=C_, qmode=L.QM_MULTIPLIER_SHIFT, mult=m_, rshift=s_, out_zp=5, do_relu=True)
+    assert np.array_equal(got, want.astype(np.float32)) and len(np.unique(want)) > 40
+
+
 def test_conv_device_face_matches_operator_face():
     c = synth.conv2d_int8(seed=8, N=4, C=128, H=10, W=10, OC=64)
     want, mult, rshift = oracle_conv(c, qmode=oracle.QM_QDM, is_cv18xx=True)

@@ -91,14 +91,28 @@ __device__ __forceinline__ int rshift_half_up_sat32(int a, int m, int s, unsigne
   return h2 == ((int)l2 >> 31) ? (int)l2 : (h2 < 0 ? (int)0x80000000 : 0x7fffffff);
 }
 
+template <bool XU>
+__device__ __forceinline__ int dot4(uint32_t a, uint32_t b, int c) {   // four input bytes (u8 or s8) times four s8 weights
+  int d;
+  if (XU) asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  else asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
 // Depthwise convolution (groups == ic == oc), square K x K filter, stride S, no dilation: the memory-bound case of the
-// mobile networks.  One thread owns a patch of R rows x 4 columns of one plane's output; it walks the (R - 1) * S + K input
-// rows the patch needs once, holding one row's span of 3 * S + K bytes and the filter in registers, so every input byte is
-// loaded once per patch and all index arithmetic is 32-bit.  The epilogue is the shared exact one.  8-bit outputs of
-// full patches leave as one 32-bit store per row.
-template <int K, int S, int R, bool FAST_RQ>
+// mobile networks.  One thread owns a patch of R rows x 4 columns of one plane's output and walks the (R - 1) * S + K input
+// rows the patch needs once.  A row is read as aligned 32-bit words, shifted to the window's first byte, its out-of-image
+// bytes replaced by the pad value through a per-thread byte mask, and fed four bytes at a time to dp4a against the packed
+// filter row (bytes a word holds beyond the filter's width meet zero weights); rows outside the image are the pad word.
+// The words reach up to three bytes before the window and 4 * (NV + 1) bytes past its start, which lies inside the tensor
+// for every patch but the few at its two ends; those (and a tensor that is not 4-byte aligned) take a compact
+// one-output-at-a-time loop.  The code is kept small on purpose: fully unrolled tested byte loads and an inlined general
+// requantisation made the first version wait on instruction fetch more than on anything else.
+__device__ __noinline__ int requant_general(int a, int m, int s, const Epilogue& e) { return requant_value<-1, -1>(a, m, s, e); }
+
+template <int K, int S, int R, bool FAST_RQ, bool XU>
 __global__ void __launch_bounds__(256)
-dwconv_i8_kernel(const uint8_t* __restrict__ x, int x_unsigned, const int8_t* __restrict__ w, ConvGeometry g, Epilogue e,
+dwconv_i8_kernel(const uint8_t* __restrict__ x, long long x_bytes, const int8_t* __restrict__ w, ConvGeometry g, Epilogue e,
                  void* __restrict__ y, unsigned xq_per_row, unsigned yt_per_plane, unsigned total) {
   const unsigned tid = blockIdx.x * blockDim.x + threadIdx.x;       // the launcher keeps the thread count below 2^32
   if (tid >= total) return;
@@ -106,45 +120,91 @@ dwconv_i8_kernel(const uint8_t* __restrict__ x, int x_unsigned, const int8_t* __
   const unsigned plane = tid / per_plane, in_plane = tid - plane * per_plane;     // plane = n * C + c
   const int yt = (int)(in_plane / xq_per_row), xq = (int)(in_plane - (unsigned)yt * xq_per_row);
   const int c = (int)(plane % (unsigned)g.oc);
-  constexpr int SPAN = 3 * S + K, ROWS = (R - 1) * S + K;
-  int wv[K][K];
+  constexpr int ROWS = (R - 1) * S + K;
+  constexpr int T = (K + 3) / 4, LASTB = 3 * S + 4 * (T - 1) + 3, NV = LASTB / 4 + 1;
+  const int x0 = xq * 4, y0 = yt * R;
+  const int ix0 = x0 * S - g.pwl, iy0 = y0 * S - g.pht;
+  const int bias = e.bias ? e.bias[c] : 0;
+  const int qi = e.per_channel ? c : 0;
+  const int32_t m = e.multiplier ? e.multiplier[qi] : 1;
+  const int32_t sft = e.shift ? e.shift[qi] : 0;
+  const long long plane_off = (long long)plane * (g.ih * g.iw);
+  const int iy_first = iy0 > 0 ? iy0 : 0, iy_last = iy0 + ROWS - 1 < g.ih - 1 ? iy0 + ROWS - 1 : g.ih - 1;
+  const bool words_ok = plane_off + (long long)iy_first * g.iw + ix0 >= 0 &&
+                        plane_off + (long long)iy_last * g.iw + ix0 + 4 * (NV + 1) <= x_bytes;
+  if (!words_ok) {
+    // the ends of the tensor: one output at a time, tested byte loads
+    const uint8_t* xp = x + plane_off;
+#pragma unroll 1
+    for (int i = 0; i < R * 4; ++i) {
+      const int yo = y0 + (i >> 2), xo = x0 + (i & 3);
+      if (yo >= g.oh || xo >= g.ow) continue;
+      int a = bias;
+#pragma unroll 1
+      for (int f = 0; f < K * K; ++f) {
+        const int iy = yo * S - g.pht + f / K, ix = xo * S - g.pwl + f % K;
+        int v = g.pad_value;
+        if ((unsigned)iy < (unsigned)g.ih && (unsigned)ix < (unsigned)g.iw) v = XU ? (int)xp[iy * g.iw + ix] : (int)(int8_t)xp[iy * g.iw + ix];
+        a += v * (int)w[c * K * K + f];
+      }
+      if (e.relu == B200Q_RELU_BEFORE_REQUANT && a < 0) a = 0;
+      st_q(y, ((long long)plane * g.oh + yo) * g.ow + xo, e.out_dtype, requant_general(a, m, sft, e));
+    }
+    return;
+  }
+  uint32_t wp[K][T];
 #pragma unroll
   for (int i = 0; i < K; ++i)
 #pragma unroll
-    for (int j = 0; j < K; ++j) wv[i][j] = w[c * K * K + i * K + j];
-  const uint8_t* xp = x + (long long)plane * (g.ih * g.iw);
-  const int x0 = xq * 4, y0 = yt * R;
-  const int ix0 = x0 * S - g.pwl, iy0 = y0 * S - g.pht;
+    for (int t = 0; t < T; ++t) {
+      uint32_t v = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+        if (4 * t + b < K) v |= (uint32_t)((int)w[c * K * K + i * K + 4 * t + b] & 255) << (8 * b);
+      wp[i][t] = v;
+    }
+  // byte masks of the window's columns that lie inside the image, and the pad value in the others
+  const uint32_t padw = (uint32_t)(g.pad_value & 255) * 0x01010101u;
+  uint32_t keep[NV], fill[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    uint32_t k = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+      if ((unsigned)(ix0 + 4 * i + b) < (unsigned)g.iw) k |= 0xffu << (8 * b);
+    keep[i] = k;
+    fill[i] = padw & ~k;
+  }
   int acc[R][4];
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
     for (int o = 0; o < 4; ++o) acc[r][o] = 0;
-  // a patch whose whole input window lies inside the image (most of them) loads without tests
-  const bool interior = ix0 >= 0 && ix0 + SPAN <= g.iw && iy0 >= 0 && iy0 + ROWS <= g.ih;
+  const uintptr_t first = reinterpret_cast<uintptr_t>(x) + (uintptr_t)(plane_off + (long long)iy0 * g.iw + ix0);
 #pragma unroll
   for (int rel = 0; rel < ROWS; ++rel) {
-    const int iy = iy0 + rel;
-    const uint8_t* rp = xp + iy * g.iw + ix0;
-    int xv[SPAN];
-    if (interior) {
+    uint32_t V[NV];
+    if ((unsigned)(iy0 + rel) < (unsigned)g.ih) {
+      const uintptr_t ap = first + (uintptr_t)((long long)rel * g.iw);
+      const uint32_t* a32 = reinterpret_cast<const uint32_t*>(ap & ~(uintptr_t)3);
+      const unsigned sh8 = (unsigned)(ap & 3) * 8;
+      uint32_t W[NV + 1];
 #pragma unroll
-      for (int j = 0; j < SPAN; ++j) {
-        const int v = rp[j];
-        xv[j] = x_unsigned ? v : (int)(int8_t)v;
-      }
+      for (int i = 0; i <= NV; ++i) W[i] = a32[i];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) V[i] = (__funnelshift_r(W[i], W[i + 1], sh8) & keep[i]) | fill[i];
     } else {
-      const bool row_ok = (unsigned)iy < (unsigned)g.ih;
 #pragma unroll
-      for (int j = 0; j < SPAN; ++j) {
-        int v = g.pad_value;
-        if (row_ok && (unsigned)(ix0 + j) < (unsigned)g.iw) {
-          v = rp[j];
-          if (!x_unsigned) v = (int)(int8_t)v;
-        }
-        xv[j] = v;
-      }
+      for (int i = 0; i < NV; ++i) V[i] = padw;
     }
+    uint32_t word[4][T];
+#pragma unroll
+    for (int o = 0; o < 4; ++o)
+#pragma unroll
+      for (int t = 0; t < T; ++t) {
+        const int p_ = o * S + 4 * t;
+        word[o][t] = (p_ % 4 == 0) ? V[p_ / 4] : __funnelshift_r(V[p_ / 4], V[(p_ / 4 + 1) < NV ? (p_ / 4 + 1) : (NV - 1)], 8 * (p_ % 4));
+      }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const int fy = rel - r * S;      // compile-time after unrolling
@@ -152,20 +212,37 @@ dwconv_i8_kernel(const uint8_t* __restrict__ x, int x_unsigned, const int8_t* __
 #pragma unroll
         for (int o = 0; o < 4; ++o)
 #pragma unroll
-          for (int fx = 0; fx < K; ++fx) acc[r][o] += xv[o * S + fx] * wv[fy][fx];
+          for (int t = 0; t < T; ++t) acc[r][o] = dot4<XU>(word[o][t], wp[fy][t], acc[r][o]);
       }
     }
   }
-  const int bias = e.bias ? e.bias[c] : 0;
-  const int qi = e.per_channel ? c : 0;
-  const int32_t m = e.multiplier ? e.multiplier[qi] : 1;
-  const int32_t sft = e.shift ? e.shift[qi] : 0;
   const bool out8 = e.out_dtype == B200Q_DT_I8 || e.out_dtype == B200Q_DT_U8;
-  // FAST_RQ: MultiplierShift, half up, 8-bit output; a shift outside [1, 62] takes the general function
-  const bool lean = FAST_RQ && sft >= 1 && sft <= 62;
-  const unsigned half_lo = (lean && sft <= 32) ? (1u << (sft - 1)) : 0u;
-  const int half_hi = (lean && sft > 32) ? (1 << (sft - 33)) : 0;
+  // FAST_RQ (MultiplierShift, half up, 8-bit output): floor((a * m + 2^(s-1)) / 2^s) is the HIGH word of one 64-bit
+  // multiply-add when the binary point sits at bit 32: for s >= 32 that is hi32(a * m + 2^(s-1)) >> (s - 32); for a smaller
+  // s the multiplier is scaled by 2^(32-s) first, which is exact while it still fits 32 bits (|m| < 2^(s-1)).  The high
+  // word cannot overflow, and the clamp bounds carry the zero point and the ReLU.  Other shifts and multipliers take the
+  // 32-bit sequence above, other dialects the general function.
+  int mode = 0;                                  // 0 general, 1 high-word form, 2 two-shift form
+  int mx = m, post = 0;
+  long long half64 = 0;
+  if (FAST_RQ && sft >= 32 && sft <= 62) {
+    mode = 1;
+    half64 = 1ll << (sft - 1);
+    post = sft - 32;
+  } else if (FAST_RQ && sft >= 1 && sft <= 31) {
+    const int lim = 1 << (sft - 1);
+    if (m > -lim && m < lim) {
+      mode = 1;
+      mx = m * (1 << (32 - sft));               // |m| < 2^(s-1): the product stays below 2^31
+      half64 = 1ll << 31;
+    } else {
+      mode = 2;
+    }
+  }
+  const unsigned half_lo = (mode == 2) ? (1u << (sft - 1)) : 0u;
   const int q_lo = e.out_dtype == B200Q_DT_U8 ? 0 : -128, q_hi = e.out_dtype == B200Q_DT_U8 ? 255 : 127;
+  const int floor_q = (e.relu == B200Q_RELU_AFTER_REQUANT && e.out_zp > q_lo) ? e.out_zp : q_lo;
+  const int b_lo = floor_q - e.out_zp, b_hi = q_hi - e.out_zp;      // bounds of the value before the zero point is added
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int yo = y0 + r;
@@ -175,19 +252,22 @@ dwconv_i8_kernel(const uint8_t* __restrict__ x, int x_unsigned, const int8_t* __
     for (int o = 0; o < 4; ++o) {
       int a = acc[r][o] + bias;
       if (e.relu == B200Q_RELU_BEFORE_REQUANT && a < 0) a = 0;
-      if (lean) {
-        int v = rshift_half_up_sat32(a, m, sft, half_lo, half_hi);
-        v = max(min(v, 1 << 24), -(1 << 24)) + e.out_zp;      // far outside every 8-bit range already; the zero point cannot wrap it
-        if (e.relu == B200Q_RELU_AFTER_REQUANT) v = max(v, e.out_zp);
-        q[o] = max(min(v, q_hi), q_lo);
+      if (mode == 1) {
+        const int v = (int)(((long long)a * mx + half64) >> 32) >> post;
+        q[o] = min(max(v, b_lo), b_hi) + e.out_zp;
+        if (q[o] > q_hi) q[o] = q_hi;             // only when the zero point lies above the type's range
+      } else if (mode == 2) {
+        const int v = rshift_half_up_sat32(a, m, sft, half_lo, 0);
+        q[o] = min(max(max(min(v, 1 << 24), -(1 << 24)), b_lo), b_hi) + e.out_zp;
+        if (q[o] > q_hi) q[o] = q_hi;
       } else {
-        q[o] = requant_value<-1, -1>(a, m, sft, e);
+        q[o] = requant_general(a, m, sft, e);
       }
     }
     const long long at = ((long long)plane * g.oh + yo) * g.ow + x0;
     if (out8 && x0 + 3 < g.ow && (at & 3) == 0) {
-      reinterpret_cast<uint32_t*>(y)[at >> 2] = (uint32_t)(q[0] & 255) | ((uint32_t)(q[1] & 255) << 8) | ((uint32_t)(q[2] & 255) << 16) |
-                                                 ((uint32_t)(q[3] & 255) << 24);
+      const uint32_t lo16 = __byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), hi16 = __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040);
+      reinterpret_cast<uint32_t*>(y)[at >> 2] = __byte_perm(lo16, hi16, 0x5410);
     } else {
 #pragma unroll
       for (int o = 0; o < 4; ++o)
@@ -205,10 +285,14 @@ int dwconv_launch_krs(const void* x, int x_unsigned, const int8_t* w, const Conv
   if (total >= 0xffffff00LL) return set_error(B200Q_ERR_UNSUPPORTED, "depthwise conv: output too large");
   const bool fast = epi.dialect == B200Q_RQ_MULTIPLIER_SHIFT && epi.round_mode == B200Q_ROUND_HALF_UP &&
                     (epi.out_dtype == B200Q_DT_I8 || epi.out_dtype == B200Q_DT_U8);
-  if (fast)
-    dwconv_i8_kernel<K, S, R, true><<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(x), x_unsigned, w, g, epi, y, (unsigned)xq, (unsigned)yt, (unsigned)total);
-  else
-    dwconv_i8_kernel<K, S, R, false><<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(x), x_unsigned, w, g, epi, y, (unsigned)xq, (unsigned)yt, (unsigned)total);
+  // the word-wise path needs a 4-byte aligned tensor; a misaligned one takes the tested byte loads everywhere (x_bytes = 0)
+  const long long x_bytes = (reinterpret_cast<uintptr_t>(x) & 3) == 0 ? (long long)g.n * g.ic * g.ih * g.iw : 0;
+  const uint8_t* xb = static_cast<const uint8_t*>(x);
+  const unsigned nb = (unsigned)blocks, uxq = (unsigned)xq, uyt = (unsigned)yt, utot = (unsigned)total;
+  if (fast && x_unsigned) dwconv_i8_kernel<K, S, R, true, true><<<nb, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, uxq, uyt, utot);
+  else if (fast) dwconv_i8_kernel<K, S, R, true, false><<<nb, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, uxq, uyt, utot);
+  else if (x_unsigned) dwconv_i8_kernel<K, S, R, false, true><<<nb, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, uxq, uyt, utot);
+  else dwconv_i8_kernel<K, S, R, false, false><<<nb, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, uxq, uyt, utot);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }
