@@ -51,6 +51,8 @@ def test_invalid_descriptor_is_reported_not_aborted(built):
     h = C.c_void_p()
     rc = lib.b200q_matmul_init(C.byref(d), C.byref(h))
     assert rc == L.ERR_INVALID and b"shape" in lib.b200q_last_error()
-    d = L.MatMulDesc(batch=1, M=4, K=16, N=4, hdim_is_batch=1, input_dtype=L.DT_I8, right_dtype=L.DT_I8)
+    d = L.MatMulDesc(batch=1, M=4, K=16, N=4, hdim_is_batch=1, input_dtype=L.DT_I8, right_dtype=L.DT_I8)      # no batched right operand
+    assert lib.b200q_matmul_init(C.byref(d), C.byref(h)) == L.ERR_INVALID
+    d = L.MatMulDesc(batch=1, M=4, K=16, N=4, hdim_is_batch=1, right_batched=1, is_cv18xx=1, input_dtype=L.DT_I8, right_dtype=L.DT_I8)
     assert lib.b200q_matmul_init(C.byref(d), C.byref(h)) == L.ERR_UNSUPPORTED
     assert lib.b200q_conv2d_inference(None, None, 0, None, 0, C.byref(h)) == L.ERR_INVALID
