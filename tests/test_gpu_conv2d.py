@@ -133,6 +133,11 @@ def test_conv_tensor_core_shapes(case):
     dict(N=1, C=5, H=17, W=13, OC=5, k=5, stride=(1, 1), pads=(2, 2, 2, 2), group=5, dil=(1, 1)),
     dict(N=2, C=6, H=14, W=14, OC=6, k=5, stride=(2, 2), pads=(2, 1, 1, 2), group=6, dil=(1, 1)),
     dict(N=1, C=4, H=3, W=2, OC=4, k=3, stride=(1, 1), pads=(1, 1, 1, 1), group=4, dil=(1, 1)),
+    # eight-column patches (output width a multiple of 8, or rounding up the same way as to 4), a one-patch plane
+    dict(N=2, C=9, H=13, W=16, OC=9, k=3, stride=(1, 1), pads=(1, 1, 1, 1), group=9, dil=(1, 1)),
+    dict(N=1, C=6, H=27, W=47, OC=6, k=3, stride=(2, 2), pads=(1, 1, 0, 1), group=6, dil=(1, 1)),
+    dict(N=2, C=3, H=56, W=56, OC=3, k=3, stride=(1, 1), pads=(1, 1, 1, 1), group=3, dil=(1, 1)),
+    dict(N=3, C=300, H=2, W=2, OC=300, k=3, stride=(1, 1), pads=(1, 1, 1, 1), group=300, dil=(1, 1)),
 ])
 def test_conv_cuda_core_shapes(case):
     rng = np.random.default_rng(77)

@@ -110,19 +110,26 @@ __device__ __forceinline__ int dot4(uint32_t a, uint32_t b, int c) {   // four i
 // requantisation made the first version wait on instruction fetch more than on anything else.
 __device__ __noinline__ int requant_general(int a, int m, int s, const Epilogue& e) { return requant_value<-1, -1>(a, m, s, e); }
 
-template <int K, int S, int R, bool FAST_RQ, bool XU>
+template <int K, int S, int R, int CW, bool FAST_RQ, bool XU>
 __global__ void __launch_bounds__(256)
 dwconv_i8_kernel(const uint8_t* __restrict__ x, long long x_bytes, const int8_t* __restrict__ w, ConvGeometry g, Epilogue e,
-                 void* __restrict__ y, unsigned xq_per_row, unsigned yt_per_plane, unsigned total) {
-  const unsigned tid = blockIdx.x * blockDim.x + threadIdx.x;       // the launcher keeps the thread count below 2^32
-  if (tid >= total) return;
-  const unsigned per_plane = xq_per_row * yt_per_plane;
-  const unsigned plane = tid / per_plane, in_plane = tid - plane * per_plane;     // plane = n * C + c
-  const int yt = (int)(in_plane / xq_per_row), xq = (int)(in_plane - (unsigned)yt * xq_per_row);
-  const int c = (int)(plane % (unsigned)g.oc);
+                 void* __restrict__ y, unsigned per_plane, unsigned planes_per_block, unsigned inv_per_plane, unsigned xq_per_row,
+                 unsigned inv_xq) {
+  // grid (blocks of one plane, channel groups, images): a plane with at most 256 patches shares its block with the next
+  // channels' planes; divisions are multiplications by the reciprocals the launcher rounded up (exact for these ranges)
+  unsigned pl = 0, rem = blockIdx.x * 256u + threadIdx.x;
+  if (planes_per_block > 1) {
+    pl = per_plane == 1 ? threadIdx.x : __umulhi(threadIdx.x, inv_per_plane);
+    rem = threadIdx.x - pl * per_plane;
+    if (pl >= planes_per_block) return;
+  }
+  const int c = (int)(blockIdx.y * planes_per_block + pl);
+  if (c >= g.oc || rem >= per_plane) return;
+  const unsigned plane = blockIdx.z * (unsigned)g.oc + (unsigned)c;     // n * C + c
+  const int yt = (int)(xq_per_row == 1 ? rem : __umulhi(rem, inv_xq)), xq = (int)(rem - (unsigned)yt * xq_per_row);
   constexpr int ROWS = (R - 1) * S + K;
-  constexpr int T = (K + 3) / 4, LASTB = 3 * S + 4 * (T - 1) + 3, NV = LASTB / 4 + 1;
-  const int x0 = xq * 4, y0 = yt * R;
+  constexpr int T = (K + 3) / 4, LASTB = (CW - 1) * S + 4 * (T - 1) + 3, NV = LASTB / 4 + 1;
+  const int x0 = xq * CW, y0 = yt * R;
   const int ix0 = x0 * S - g.pwl, iy0 = y0 * S - g.pht;
   const int bias = e.bias ? e.bias[c] : 0;
   const int qi = e.per_channel ? c : 0;
@@ -136,8 +143,8 @@ dwconv_i8_kernel(const uint8_t* __restrict__ x, long long x_bytes, const int8_t*
     // the ends of the tensor: one output at a time, tested byte loads
     const uint8_t* xp = x + plane_off;
 #pragma unroll 1
-    for (int i = 0; i < R * 4; ++i) {
-      const int yo = y0 + (i >> 2), xo = x0 + (i & 3);
+    for (int i = 0; i < R * CW; ++i) {
+      const int yo = y0 + i / CW, xo = x0 + i % CW;
       if (yo >= g.oh || xo >= g.ow) continue;
       int a = bias;
 #pragma unroll 1
@@ -175,11 +182,11 @@ dwconv_i8_kernel(const uint8_t* __restrict__ x, long long x_bytes, const int8_t*
     keep[i] = k;
     fill[i] = padw & ~k;
   }
-  int acc[R][4];
+  int acc[R][CW];
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int o = 0; o < 4; ++o) acc[r][o] = 0;
+    for (int o = 0; o < CW; ++o) acc[r][o] = 0;
   const uintptr_t first = reinterpret_cast<uintptr_t>(x) + (uintptr_t)(plane_off + (long long)iy0 * g.iw + ix0);
 #pragma unroll
   for (int rel = 0; rel < ROWS; ++rel) {
@@ -197,9 +204,9 @@ dwconv_i8_kernel(const uint8_t* __restrict__ x, long long x_bytes, const int8_t*
 #pragma unroll
       for (int i = 0; i < NV; ++i) V[i] = padw;
     }
-    uint32_t word[4][T];
+    uint32_t word[CW][T];
 #pragma unroll
-    for (int o = 0; o < 4; ++o)
+    for (int o = 0; o < CW; ++o)
 #pragma unroll
       for (int t = 0; t < T; ++t) {
         const int p_ = o * S + 4 * t;
@@ -210,7 +217,7 @@ dwconv_i8_kernel(const uint8_t* __restrict__ x, long long x_bytes, const int8_t*
       const int fy = rel - r * S;      // compile-time after unrolling
       if (fy >= 0 && fy < K) {
 #pragma unroll
-        for (int o = 0; o < 4; ++o)
+        for (int o = 0; o < CW; ++o)
 #pragma unroll
           for (int t = 0; t < T; ++t) acc[r][o] = dot4<XU>(word[o][t], wp[fy][t], acc[r][o]);
       }
@@ -247,9 +254,9 @@ dwconv_i8_kernel(const uint8_t* __restrict__ x, long long x_bytes, const int8_t*
   for (int r = 0; r < R; ++r) {
     const int yo = y0 + r;
     if (yo >= g.oh) break;
-    int q[4];
+    int q[CW];
 #pragma unroll
-    for (int o = 0; o < 4; ++o) {
+    for (int o = 0; o < CW; ++o) {
       int a = acc[r][o] + bias;
       if (e.relu == B200Q_RELU_BEFORE_REQUANT && a < 0) a = 0;
       if (mode == 1) {
@@ -265,34 +272,41 @@ dwconv_i8_kernel(const uint8_t* __restrict__ x, long long x_bytes, const int8_t*
       }
     }
     const long long at = ((long long)plane * g.oh + yo) * g.ow + x0;
-    if (out8 && x0 + 3 < g.ow && (at & 3) == 0) {
-      const uint32_t lo16 = __byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), hi16 = __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040);
-      reinterpret_cast<uint32_t*>(y)[at >> 2] = __byte_perm(lo16, hi16, 0x5410);
-    } else {
 #pragma unroll
-      for (int o = 0; o < 4; ++o)
-        if (x0 + o < g.ow) st_q(y, at + o, e.out_dtype, q[o]);
+    for (int j = 0; j < CW; j += 4) {
+      if (out8 && x0 + j + 3 < g.ow && ((at + j) & 3) == 0) {
+        const uint32_t lo16 = __byte_perm((uint32_t)q[j], (uint32_t)q[j + 1], 0x0040), hi16 = __byte_perm((uint32_t)q[j + 2], (uint32_t)q[j + 3], 0x0040);
+        reinterpret_cast<uint32_t*>(y)[(at + j) >> 2] = __byte_perm(lo16, hi16, 0x5410);
+      } else {
+#pragma unroll
+        for (int o = j; o < j + 4; ++o)
+          if (x0 + o < g.ow) st_q(y, at + o, e.out_dtype, q[o]);
+      }
     }
   }
 }
 
-template <int K, int S, int R>
+template <int K, int S, int R, int CW>
 int dwconv_launch_krs(const void* x, int x_unsigned, const int8_t* w, const ConvGeometry& g, const Epilogue& epi, void* y, cudaStream_t stream) {
-  const int xq = (g.ow + 3) / 4, yt = (g.oh + R - 1) / R;
-  const long long total = (long long)g.n * g.oc * xq * yt;
-  if (total == 0) return B200Q_OK;
-  const long long blocks = (total + 255) / 256;
-  if (total >= 0xffffff00LL) return set_error(B200Q_ERR_UNSUPPORTED, "depthwise conv: output too large");
+  const unsigned xq = (unsigned)((g.ow + CW - 1) / CW), yt = (unsigned)((g.oh + R - 1) / R);
+  const unsigned per_plane = xq * yt;
+  if ((long long)g.n * g.oc * per_plane == 0) return B200Q_OK;
+  const unsigned ppb = per_plane <= 128 ? 256u / per_plane : 1u;      // planes per block
+  const dim3 grid(ppb > 1 ? 1u : (per_plane + 255u) / 256u, ((unsigned)g.oc + ppb - 1) / ppb, (unsigned)g.n);
+  if (grid.y > 65535u || grid.z > 65535u) return set_error(B200Q_ERR_UNSUPPORTED, "depthwise conv: more than 65535 channel groups or images");
+  // ceil(2^32 / d): __umulhi(v, that) == v / d while v * (d - 1) < 2^32; v stays below 2^16 here (d == 1 is tested apart)
+  auto recip = [](unsigned d) { return d <= 1 ? 0u : (unsigned)((0x100000000ull + d - 1) / d); };
+  if (per_plane >= 65536u) return set_error(B200Q_ERR_UNSUPPORTED, "depthwise conv: plane too large");
   const bool fast = epi.dialect == B200Q_RQ_MULTIPLIER_SHIFT && epi.round_mode == B200Q_ROUND_HALF_UP &&
                     (epi.out_dtype == B200Q_DT_I8 || epi.out_dtype == B200Q_DT_U8);
   // the word-wise path needs a 4-byte aligned tensor; a misaligned one takes the tested byte loads everywhere (x_bytes = 0)
   const long long x_bytes = (reinterpret_cast<uintptr_t>(x) & 3) == 0 ? (long long)g.n * g.ic * g.ih * g.iw : 0;
   const uint8_t* xb = static_cast<const uint8_t*>(x);
-  const unsigned nb = (unsigned)blocks, uxq = (unsigned)xq, uyt = (unsigned)yt, utot = (unsigned)total;
-  if (fast && x_unsigned) dwconv_i8_kernel<K, S, R, true, true><<<nb, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, uxq, uyt, utot);
-  else if (fast) dwconv_i8_kernel<K, S, R, true, false><<<nb, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, uxq, uyt, utot);
-  else if (x_unsigned) dwconv_i8_kernel<K, S, R, false, true><<<nb, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, uxq, uyt, utot);
-  else dwconv_i8_kernel<K, S, R, false, false><<<nb, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, uxq, uyt, utot);
+  const unsigned ipp = recip(per_plane), ixq = recip(xq);
+  if (fast && x_unsigned) dwconv_i8_kernel<K, S, R, CW, true, true><<<grid, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, per_plane, ppb, ipp, xq, ixq);
+  else if (fast) dwconv_i8_kernel<K, S, R, CW, true, false><<<grid, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, per_plane, ppb, ipp, xq, ixq);
+  else if (x_unsigned) dwconv_i8_kernel<K, S, R, CW, false, true><<<grid, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, per_plane, ppb, ipp, xq, ixq);
+  else dwconv_i8_kernel<K, S, R, CW, false, false><<<grid, 256, 0, stream>>>(xb, x_bytes, w, g, epi, y, per_plane, ppb, ipp, xq, ixq);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }
@@ -301,7 +315,9 @@ int dwconv_launch_krs(const void* x, int x_unsigned, const int8_t* w, const Conv
 template <int K, int S>
 int dwconv_launch_ks(const void* x, int x_unsigned, const int8_t* w, const ConvGeometry& g, const Epilogue& epi, void* y, cudaStream_t stream,
                      int* rc) {
-  *rc = g.oh >= 12 ? dwconv_launch_krs<K, S, 4>(x, x_unsigned, w, g, epi, y, stream) : dwconv_launch_krs<K, S, 2>(x, x_unsigned, w, g, epi, y, stream);
+  // four columns per thread: eight (CW = 8) were measured slower on 56- and 112-wide planes (79 registers instead of 58)
+  if (g.oh >= 12) *rc = dwconv_launch_krs<K, S, 4, 4>(x, x_unsigned, w, g, epi, y, stream);
+  else *rc = dwconv_launch_krs<K, S, 2, 4>(x, x_unsigned, w, g, epi, y, stream);
   return 1;
 }
 
