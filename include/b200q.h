@@ -278,6 +278,10 @@ int b200q_requant_int_axis_dev(const int32_t *x, int64_t outer, int64_t C, int64
  * out = saturate(relu(RSR(a*m0, s0, half-up) + RSR(b*m1, s1, half-up))). */
 int b200q_add_i8_dev(const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t count, int32_t m0,
                      int32_t s0, int32_t m1, int32_t s1, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
+/* tpu.Sub, symmetric 8-bit operands of equal shape (lib/Dialect/Tpu/Interfaces/Common/Sub.cpp:88-113):
+ * out = saturate(relu(RSR(a*m0, s0, half-up) - RSR(b*m1, s1, half-up))). */
+int b200q_sub_i8_dev(const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t count, int32_t m0, int32_t s0,
+                     int32_t m1, int32_t s1, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
 /* tpu.Lut (lib/Dialect/Tpu/Interfaces/Common/Lut.cpp:20-32): out[i] = table[x[i] mod 256] (a negative int8 index
  * wraps by +256).  x is 8-bit; `table` holds 256 entries of `table_dtype`, which is also the output type. */
 int b200q_lut_dev(const void *x, int64_t count, const void *table, int32_t table_dtype, void *out, void *stream);

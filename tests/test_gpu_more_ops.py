@@ -700,5 +700,9 @@ def test_binary_ops_broadcast():
     m = run_graph({"x": qi(q.shape), "c": qi(qc.shape), "mul": qi(q.shape), "add": qi(q.shape)}, ops, {}, {"x": q, "c": qc})
     prod = q.astype(np.int64) * qc
     assert np.array_equal(m.get_raw_tensor("mul"), np.clip((prod * 77 + (1 << 11)) >> 12, -128, 127).astype(np.int8))
+    m2 = run_graph({"x": qi(q.shape), "c": qi(qc.shape), "sub": qi(q.shape)},
+                   [dict(type="tpu.Sub", name="sub", inputs=["x", "c"], attrs=dict(multipliers=[90, 70], rshifts=[7, 6]))], {}, {"x": q, "c": qc})
+    diff = ((q.astype(np.int64) * 90 + 64) >> 7) - ((qc.astype(np.int64) * 70 + 32) >> 6)
+    assert np.array_equal(m2.get_raw_tensor("sub"), np.clip(diff, -128, 127).astype(np.int8))
     ssum = ((qc.astype(np.int64) * 90 + 64) >> 7) + ((q.astype(np.int64) * 70 + 64) >> 7)
     assert np.array_equal(m.get_raw_tensor("add"), np.clip(np.maximum(ssum, 0), -128, 127).astype(np.int8))

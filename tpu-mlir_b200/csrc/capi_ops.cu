@@ -953,6 +953,12 @@ int b200q_add_i8_dev(const void* a, int32_t a_dtype, const void* b, int32_t b_dt
   return add_i8_launch(a, a_dtype, b, b_dtype, count, m0, s0, m1, s1, do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_sub_i8_dev(const void* a, int32_t a_dtype, const void* b, int32_t b_dtype, int64_t count, int32_t m0, int32_t s0,
+                     int32_t m1, int32_t s1, int32_t do_relu, int32_t out_dtype, void* out, void* stream) {
+  if (!a || !b || !out || count < 0 || !is_q8(a_dtype) || !is_q8(b_dtype)) return set_error(B200Q_ERR_INVALID, "sub_i8_dev: bad argument");
+  return sub_i8_launch(a, a_dtype, b, b_dtype, count, m0, s0, m1, s1, do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_lut_dev(const void* x, int64_t count, const void* table, int32_t table_dtype, void* out, void* stream) {
   if (!x || !table || !out || count < 0) return set_error(B200Q_ERR_INVALID, "lut_dev: bad argument");
   return lut_launch(x, count, table, (int)dtype_size(table_dtype), out, static_cast<cudaStream_t>(stream));

@@ -68,6 +68,20 @@ __global__ void add_i8_kernel(const void* __restrict__ a, int a_dt, const void* 
   st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
 }
 
+// tpu.Sub, symmetric 8-bit (lib/Dialect/Tpu/Interfaces/Common/Sub.cpp:88-113): each operand is brought to the output's scale
+// with its own multiplier and half-up shift, then out = saturate(relu(lhs - rhs)).  (Negating the second multiplier in the
+// Add kernel would round its ties the other way.)
+__global__ void sub_i8_kernel(const void* __restrict__ a, int a_dt, const void* __restrict__ b, int b_dt, long long n,
+                              int m0, int s0, int m1, int s1, int do_relu, int out_dt, void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t l = rshift_round((int64_t)ld_q(a, i, a_dt) * m0, s0, B200Q_ROUND_HALF_UP);
+  const int64_t r = rshift_round((int64_t)ld_q(b, i, b_dt) * m1, s1, B200Q_ROUND_HALF_UP);
+  int64_t v = l - r;
+  if (do_relu && v < 0) v = 0;
+  st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
+}
+
 // 4 elements per thread for the common 8-bit case
 __global__ void add_i8x4_kernel(const uint32_t* __restrict__ a, int a_unsigned, const uint32_t* __restrict__ b,
                                 int b_unsigned, long long n4, int m0, int s0, int m1, int s1, int do_relu, int out_dt,
@@ -596,6 +610,14 @@ int add_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n,
   } else {
     add_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(a, a_dt, b, b_dt, n, m0, s0, m1, s1, do_relu, out_dt, out);
   }
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int sub_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n, int m0, int s0, int m1, int s1, int do_relu, int out_dt,
+                  void* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  sub_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(a, a_dt, b, b_dt, n, m0, s0, m1, s1, do_relu, out_dt, out);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

@@ -481,6 +481,18 @@ class module:  # noqa: N801  (name of the reference class)
                                                         n, int(m[0]), int(s[0]), int(m[1]), int(s[1]),
                                                         int(bool(a.get("do_relu", False))), _DT[oinfo["dtype"]], _P(out),
                                                         stream()))
+        if t == "tpu.Sub":
+            # 8-bit symmetric form (Sub.cpp:88-113; the f32 form went to the Top arithmetic above).  The reference re-binds its
+            # operands in order on this route whatever is_reverse says; a reversed op is refused rather than guessed at.
+            if a.get("is_reverse", False) or any(i["dtype"] not in ("i8", "u8") for i in iinfo) or oinfo["dtype"] not in ("i8", "u8"):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.Sub takes f32 tensors, or 8-bit ones without is_reverse")
+            if any(nm in self._nhwc for nm in list(op["inputs"]) + [op["name"]]):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.Sub on channels-last stored tensors")
+            m, s = a["multipliers"], a["rshifts"]
+            n = out.numel()
+            return lambda: L.check(lib.b200q_sub_i8_dev(_P(ins[0]), _DT[iinfo[0]["dtype"]], _P(ins[1]), _DT[iinfo[1]["dtype"]],
+                                                        n, int(m[0]), int(s[0]), int(m[1]), int(s[1]),
+                                                        int(bool(a.get("do_relu", False))), _DT[oinfo["dtype"]], _P(out), stream()))
         if t == "tpu.Pool2D":
             nb, c, ih, iw = iinfo[0]["shape"]
             kh, kw = a["kernel_shape"]
