@@ -278,6 +278,14 @@ int b200q_requant_int_axis_dev(const int32_t *x, int64_t outer, int64_t C, int64
  * out = saturate(relu(RSR(a*m0, s0, half-up) + RSR(b*m1, s1, half-up))). */
 int b200q_add_i8_dev(const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t count, int32_t m0,
                      int32_t s0, int32_t m1, int32_t s1, int32_t do_relu, int32_t out_dtype, void *out, void *stream);
+/* tpu.MaxConst (form 0) / tpu.MinConst (1) with a uniform-quantized output (MaxConst.cpp:27-42): the float (x - in_zp) * multiplier is
+ * compared with float(const_val), cut to an integer toward zero, shifted half-up by rshift, ReLU'd and saturated (no output
+ * zero point is added, as there).  tpu.SubConst, symmetric (SubConst.cpp:26-112): form 2 float(x * multiplier - const_val),
+ * form 3 (is_reverse) float(const_val - x * multiplier), the ReLU (with its limit) on that float, then the same cut, shift,
+ * ReLU and saturation. */
+int b200q_constop_i8_dev(int32_t form, const void *x, int32_t dtype, int64_t count, int32_t multiplier, double const_val,
+                         int32_t rshift, int32_t in_zp, int32_t do_relu, float relu_limit, int32_t out_dtype, void *out,
+                         void *stream);
 /* tpu.Sub, symmetric 8-bit operands of equal shape (lib/Dialect/Tpu/Interfaces/Common/Sub.cpp:88-113):
  * out = saturate(relu(RSR(a*m0, s0, half-up) - RSR(b*m1, s1, half-up))). */
 int b200q_sub_i8_dev(const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t count, int32_t m0, int32_t s0,

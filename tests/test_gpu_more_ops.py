@@ -706,3 +706,28 @@ def test_binary_ops_broadcast():
     assert np.array_equal(m2.get_raw_tensor("sub"), np.clip(diff, -128, 127).astype(np.int8))
     ssum = ((qc.astype(np.int64) * 90 + 64) >> 7) + ((q.astype(np.int64) * 70 + 64) >> 7)
     assert np.array_equal(m.get_raw_tensor("add"), np.clip(np.maximum(ssum, 0), -128, 127).astype(np.int8))
+
+
+def test_tpu_const_ops_8bit():
+    """tpu.MaxConst / MinConst / SubConst on 8-bit tensors, in the reference's mix of float and integer steps."""
+    rng = np.random.default_rng(19)
+    q = rng.integers(-128, 128, (2, 3, 4, 5), dtype=np.int8)
+    qi = lambda zp=0: dict(shape=list(q.shape), dtype="i8", scale=0.05, zp=zp)  # noqa: E731
+
+    def rsr(v, s):
+        return (v + (1 << (s - 1))) >> s if s > 0 else v
+    # MaxConst with an input zero point: max(float((x - zp) * m), float(c)) -> int toward zero -> RSR
+    m = run_graph({"x": qi(3), "y": qi()}, [dict(type="tpu.MaxConst", name="y", inputs=["x"], attrs=dict(const_val=-150.7, multiplier=9, rshift=3))],
+                  {}, {"x": q})
+    pf = np.maximum(((q.astype(np.int64) - 3) * 9).astype(np.float32), np.float32(-150.7))
+    assert np.array_equal(m.get_raw_tensor("y"), np.clip(rsr(np.trunc(pf).astype(np.int64), 3), -128, 127).astype(np.int8))
+    m = run_graph({"x": qi(), "y": qi()}, [dict(type="tpu.MinConst", name="y", inputs=["x"], attrs=dict(const_val=200.25, multiplier=7, rshift=2,
+                                                                                                       do_relu=True))], {}, {"x": q})
+    pf = np.minimum((q.astype(np.int64) * 7).astype(np.float32), np.float32(200.25))
+    assert np.array_equal(m.get_raw_tensor("y"), np.clip(np.maximum(rsr(np.trunc(pf).astype(np.int64), 2), 0), -128, 127).astype(np.int8))
+    for rev in (False, True):
+        m = run_graph({"x": qi(), "y": qi()}, [dict(type="tpu.SubConst", name="y", inputs=["x"],
+                                                    attrs=dict(const_val=33.5, multiplier=11, rshift=4, is_reverse=rev))], {}, {"x": q})
+        prod = (q.astype(np.int64) * 11).astype(np.float64)
+        f = (33.5 - prod if rev else prod - 33.5).astype(np.float32)
+        assert np.array_equal(m.get_raw_tensor("y"), np.clip(rsr(np.trunc(f).astype(np.int64), 4), -128, 127).astype(np.int8)), rev

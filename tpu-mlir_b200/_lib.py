@@ -119,6 +119,8 @@ SIGNATURES = {
                                              C.c_void_p]),
     "b200q_add_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 6 +
                          [C.c_void_p, C.c_void_p]),
+    "b200q_constop_i8_dev": (C.c_int, [C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_double, C.c_int32, C.c_int32, C.c_int32,
+                                       C.c_float, C.c_int32, C.c_void_p, C.c_void_p]),
     "b200q_sub_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 6 +
                          [C.c_void_p, C.c_void_p]),
     "b200q_pool2d_i8_dev": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64] + [C.c_int32] * 15 + [C.c_void_p, C.c_void_p]),

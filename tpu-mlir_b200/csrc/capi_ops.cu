@@ -953,6 +953,15 @@ int b200q_add_i8_dev(const void* a, int32_t a_dtype, const void* b, int32_t b_dt
   return add_i8_launch(a, a_dtype, b, b_dtype, count, m0, s0, m1, s1, do_relu, out_dtype, out, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_constop_i8_dev(int32_t form, const void* x, int32_t dtype, int64_t count, int32_t multiplier, double const_val, int32_t rshift,
+                         int32_t in_zp, int32_t do_relu, float relu_limit, int32_t out_dtype, void* out, void* stream) {
+  if (!x || !out || count < 0 || form < 0 || form > 3 || !is_q8(dtype) || rshift < 0 || rshift > 62)
+    return set_error(B200Q_ERR_INVALID, "constop_i8_dev: bad argument");
+  if (form >= 2 && in_zp != 0) return set_error(B200Q_ERR_INVALID, "constop_i8_dev: tpu.SubConst takes no input zero point");
+  return constop_i8_launch(form, x, dtype, count, multiplier, const_val, rshift, in_zp, do_relu, relu_limit, out_dtype, out,
+                           static_cast<cudaStream_t>(stream));
+}
+
 int b200q_sub_i8_dev(const void* a, int32_t a_dtype, const void* b, int32_t b_dtype, int64_t count, int32_t m0, int32_t s0,
                      int32_t m1, int32_t s1, int32_t do_relu, int32_t out_dtype, void* out, void* stream) {
   if (!a || !b || !out || count < 0 || !is_q8(a_dtype) || !is_q8(b_dtype)) return set_error(B200Q_ERR_INVALID, "sub_i8_dev: bad argument");

@@ -68,6 +68,32 @@ __global__ void add_i8_kernel(const void* __restrict__ a, int a_dt, const void* 
   st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
 }
 
+// tpu.MaxConst / MinConst (MaxConst.cpp:27-42, MinConst.cpp alike) and tpu.SubConst (SubConst.cpp:26-112, symmetric) with a
+// uniform-quantized output, in the reference's mix of types: the scaled input (x - in_zp) * m is held in a float, compared
+// with / reduced by the constant there, cut to an integer toward zero where applyMultiplierAndRShift takes it, then shifted
+// half-up, ReLU'd and saturated.  form 0 max, 1 min, 2 x - c, 3 c - x (SubConst takes no input zero point).
+__global__ void __launch_bounds__(256)
+constop_i8_kernel(int form, const void* __restrict__ x, int dt, long long n, int m, double const_val, int sft, int in_zp, int do_relu,
+                  float relu_limit, int out_dt, void* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float f;
+  if (form <= 1) {
+    const float pf = (float)((int64_t)(ld_q(x, i, dt) - in_zp) * m), cf = (float)const_val;
+    f = form == 0 ? fmaxf(pf, cf) : fminf(pf, cf);
+  } else {
+    const double prod = (double)((int64_t)ld_q(x, i, dt) * m);
+    f = (float)(form == 2 ? prod - const_val : const_val - prod);
+    if (do_relu) {
+      f = fmaxf(f, 0.f);
+      if (relu_limit > 0.f) f = fminf(f, relu_limit);
+    }
+  }
+  int64_t v = rshift_round((int64_t)f, sft, B200Q_ROUND_HALF_UP);
+  if (do_relu && v < 0) v = 0;
+  st_q(out, i, out_dt, (int32_t)clamp_dtype(v, out_dt));
+}
+
 // tpu.Sub, symmetric 8-bit (lib/Dialect/Tpu/Interfaces/Common/Sub.cpp:88-113): each operand is brought to the output's scale
 // with its own multiplier and half-up shift, then out = saturate(relu(lhs - rhs)).  (Negating the second multiplier in the
 // Add kernel would round its ties the other way.)
@@ -610,6 +636,14 @@ int add_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n,
   } else {
     add_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(a, a_dt, b, b_dt, n, m0, s0, m1, s1, do_relu, out_dt, out);
   }
+  CUDA_TRY(cudaGetLastError());
+  return B200Q_OK;
+}
+
+int constop_i8_launch(int form, const void* x, int dt, long long n, int m, double const_val, int sft, int in_zp, int do_relu, float relu_limit,
+                      int out_dt, void* out, cudaStream_t s) {
+  if (n == 0) return B200Q_OK;
+  constop_i8_kernel<<<nblk(n, 256), 256, 0, s>>>(form, x, dt, n, m, const_val, sft, in_zp, do_relu, relu_limit, out_dt, out);
   CUDA_TRY(cudaGetLastError());
   return B200Q_OK;
 }

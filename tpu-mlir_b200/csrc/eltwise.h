@@ -10,6 +10,8 @@ namespace b200q {
 int requant_axis_launch(const int32_t* x, long long outer, int C, long long inner, const int32_t* mult,
                         const int32_t* shift, const int32_t* zp, int per_channel, int in_zp, const Epilogue& e, void* out,
                         cudaStream_t s);
+int constop_i8_launch(int form, const void* x, int dt, long long n, int m, double const_val, int sft, int in_zp, int do_relu, float relu_limit,
+                      int out_dt, void* out, cudaStream_t s);
 int sub_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n, int m0, int s0, int m1, int s1, int do_relu, int out_dt,
                   void* out, cudaStream_t s);
 int add_i8_launch(const void* a, int a_dt, const void* b, int b_dt, long long n, int m0, int s0, int m1, int s1,

@@ -481,6 +481,21 @@ class module:  # noqa: N801  (name of the reference class)
                                                         n, int(m[0]), int(s[0]), int(m[1]), int(s[1]),
                                                         int(bool(a.get("do_relu", False))), _DT[oinfo["dtype"]], _P(out),
                                                         stream()))
+        if t in ("tpu.MaxConst", "tpu.MinConst", "tpu.SubConst"):
+            # 8-bit forms (MaxConst.cpp:27-42, SubConst.cpp:26-112); the f32 forms went to the Top arithmetic above
+            if iinfo[0]["dtype"] not in ("i8", "u8") or oinfo["dtype"] not in ("i8", "u8"):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: {t} takes f32 or 8-bit tensors")
+            if (op["inputs"][0] in self._nhwc) != (op["name"] in self._nhwc):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: {t} between differently stored tensors")
+            sub = t == "tpu.SubConst"
+            if sub and (int(iinfo[0].get("zp", 0)) != 0 or int(oinfo.get("zp", 0)) != 0):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: asymmetric tpu.SubConst is not implemented")
+            form = (3 if a.get("is_reverse", False) else 2) if sub else (0 if t == "tpu.MaxConst" else 1)
+            n, mu, sft, cv = out.numel(), int(a.get("multiplier", 1)), int(a.get("rshift", 0)), float(a["const_val"])
+            izp = 0 if sub else int(iinfo[0].get("zp", 0))
+            relu, limit = int(bool(a.get("do_relu", False))), float(a.get("relu_limit", -1.0))
+            return lambda: L.check(lib.b200q_constop_i8_dev(form, _P(ins[0]), _DT[iinfo[0]["dtype"]], n, mu, cv, sft, izp, relu, limit,
+                                                            _DT[oinfo["dtype"]], _P(out), stream()))
         if t == "tpu.Sub":
             # 8-bit symmetric form (Sub.cpp:88-113; the f32 form went to the Top arithmetic above).  The reference re-binds its
             # operands in order on this route whatever is_reverse says; a reversed op is refused rather than guessed at.
