@@ -731,3 +731,21 @@ def test_tpu_const_ops_8bit():
         prod = (q.astype(np.int64) * 11).astype(np.float64)
         f = (33.5 - prod if rev else prod - 33.5).astype(np.float32)
         assert np.array_equal(m.get_raw_tensor("y"), np.clip(rsr(np.trunc(f).astype(np.int64), 4), -128, 127).astype(np.int8)), rev
+
+
+def test_tpu_concat_requant_is_cv18xx_only():
+    """tpu.Concat's multipliers / rshifts are applied by the CV18xx interpreter alone (Concat.cpp:43-60)."""
+    rng = np.random.default_rng(20)
+    a_ = rng.integers(-128, 128, (2, 3, 4), dtype=np.int8)
+    b_ = rng.integers(-128, 128, (2, 5, 4), dtype=np.int8)
+    qi = lambda shp: dict(shape=list(shp), dtype="i8", scale=0.05, zp=0)  # noqa: E731
+    ops = [dict(type="tpu.Concat", name="y", inputs=["a", "b"], attrs=dict(axis=1, multipliers=[1, 3], rshifts=[0, 2]))]
+    for chip in ("bm1684x", "cv183x"):
+        g = dict(inputs=["a", "b"], outputs=["y"], tensors={"a": qi(a_.shape), "b": qi(b_.shape), "y": qi((2, 8, 4))}, ops=ops, chip=chip)
+        m = module()
+        m.load(g, {})
+        m.set_tensor("a", a_)
+        m.set_tensor("b", b_)
+        m.invoke(fixed_to_float=False)
+        second = np.clip((b_.astype(np.int64) * 3 + 2) >> 2, -128, 127).astype(np.int8) if chip.startswith("cv18") else b_
+        assert np.array_equal(m.get_raw_tensor("y"), np.concatenate([a_, second], axis=1)), chip

@@ -650,7 +650,7 @@ class module:  # noqa: N801  (name of the reference class)
             return L.RemapDesc(dims=f(dims, 1), src_stride=f(sstr, 0), mul=f(mul, 1), div=f(div, 1), mod=f(mod, 0), off=f(off, 0),
                                extent=f(ext, 1), dst_stride=f(dstr, 0), dst_offset=int(doff))
 
-        runs = []
+        runs, pre = [], []
         pad_buf = None
         ishape = list(self._info(srcs[0])["shape"])
         istr = self._strides(srcs[0])
@@ -735,10 +735,21 @@ class module:  # noqa: N801  (name of the reference class)
         elif t == "Concat":
             axis = int(a.get("axis", 1))
             axis += r if axis < 0 else 0
-            if any(int(m) != 1 for m in a.get("multipliers", [])) or any(int(v) != 0 for v in a.get("rshifts", [])):
-                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: Concat with per-input requantisation is not implemented")
+            # tpu.Concat's per-input multipliers / rshifts act in the CV18xx interpreter only (Concat.cpp:43-60); for every other
+            # chip the reference copies the stored values as they are, and so does this
+            mults = [int(m) for m in a.get("multipliers", [])] + [1] * len(srcs)
+            rsh = [int(v) for v in a.get("rshifts", [])] + [0] * len(srcs)
+            cv18 = str(self.graph.get("chip", "")).lower().startswith("cv18") and odt in ("i8", "u8")
             at = 0
-            for sn in srcs:
+            for k_, sn in enumerate(srcs):
+                if cv18 and (mults[k_] != 1 or rsh[k_] != 0):
+                    if sn in self._nhwc:
+                        raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: a requantised Concat input stored channels-last")
+                    syn = f"{name}__input{k_}"
+                    self._extra_info[syn] = dict(self._info(sn))
+                    self.tensors[syn] = self.torch.empty_like(self.tensors[sn])
+                    pre.append((sn, syn, mults[k_], rsh[k_], self.tensors[sn].numel()))
+                    sn = syn
                 sshape = list(self._info(sn)["shape"])
                 runs.append((sn, desc(sshape, self._strides(sn), ones, ones, zeros, zeros, sshape, ostr, at * ostr[axis])))
                 at += sshape[axis]
@@ -752,7 +763,11 @@ class module:  # noqa: N801  (name of the reference class)
             pad_host = pad_buf.cpu().numpy().tobytes()
             self._keep.append(pad_host)
 
+        qdt = _DT.get(odt, 0)
+
         def run():
+            for sn, syn, mu, sh, cnt in pre:      # CV18xx Concat: saturate(RSR(x * m, rshift, half up)) of an input before the copy
+                L.check(lib.b200q_mulshift_i8_dev(_P(self.tensors[sn]), qdt, cnt, mu, sh, 0, 0, qdt, _P(self.tensors[syn]), stream()))
             for sn, d in runs:
                 L.check(lib.b200q_remap_dev(_P(self.tensors[sn]), _P(out), ebytes, C.byref(d), pad_host, stream()))
             if relu:
