@@ -124,7 +124,7 @@ def test_concat_relu_and_refusals():
     m = run_graph({"x": f32(x.shape), "cat": f32((1, 4, 3, 3))}, ops, {}, {"x": x})
     assert np.array_equal(m.get_tensor("cat"), np.clip(np.concatenate([x, x], axis=1), 0, 0.5))
     with pytest.raises(L.B200QError):
-        run_graph({"x": f32(x.shape), "p": f32((1, 2, 5, 5))}, [dict(type="top.Pad", name="p", inputs=["x"], attrs=dict(paddings=[0, 0, 1, 1, 0, 0, 1, 1], mode="reflect"))],
+        run_graph({"x": f32(x.shape), "p": f32((1, 2, 5, 5))}, [dict(type="top.Pad", name="p", inputs=["x"], attrs=dict(paddings=[0, 0, 1, 1, 0, 0, 1, 1], mode="symmetric"))],
                   {}, {"x": x})
 
 
@@ -749,3 +749,18 @@ def test_tpu_concat_requant_is_cv18xx_only():
         m.invoke(fixed_to_float=False)
         second = np.clip((b_.astype(np.int64) * 3 + 2) >> 2, -128, 127).astype(np.int8) if chip.startswith("cv18") else b_
         assert np.array_equal(m.get_raw_tensor("y"), np.concatenate([a_, second], axis=1)), chip
+
+
+@pytest.mark.parametrize("mode", ["reflect", "edge"])
+def test_pad_reflect_and_edge(mode):
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((2, 3, 5, 6)).astype(np.float32)
+    pads = [0, 0, 2, 1, 0, 0, 3, 4]
+    ops = [dict(type="top.Pad", name="y", inputs=["x"], attrs=dict(paddings=pads, mode=mode))]
+    m = run_graph({"x": f32(x.shape), "y": f32((2, 3, 10, 11))}, ops, {}, {"x": x})
+    assert np.array_equal(m.get_tensor("y"), np.pad(x, ((0, 0), (0, 0), (2, 3), (1, 4)), mode=mode))
+    q = rng.integers(-128, 128, (1, 2, 4, 4), dtype=np.int8)
+    qi = lambda shp: dict(shape=list(shp), dtype="i8", scale=0.05, zp=0)  # noqa: E731
+    m = run_graph({"x": qi(q.shape), "y": qi((1, 2, 6, 7))}, [dict(type="tpu.Pad", name="y", inputs=["x"],
+                                                                 attrs=dict(paddings=[0, 0, 1, 3, 0, 0, 1, 0], mode=mode))], {}, {"x": q})
+    assert np.array_equal(m.get_raw_tensor("y"), np.pad(q, ((0, 0), (0, 0), (1, 1), (3, 0)), mode=mode))

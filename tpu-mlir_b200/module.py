@@ -675,13 +675,35 @@ class module:  # noqa: N801  (name of the reference class)
             div = [1] * (r - 2) + [int(a.get("scale_h", 1)), int(a.get("scale_w", 1))]
             runs.append((srcs[0], desc(oshape, istr, ones, div, zeros, zeros, ishape, ostr)))
         elif t == "Pad":
-            if a.get("mode", "constant") != "constant":
-                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: Pad mode {a.get('mode')} is not implemented")
+            mode = str(a.get("mode", "constant"))
             pads = list(a["paddings"])
             if len(pads) != 2 * r:
                 raise L.B200QError(L.ERR_INVALID, f"{name}: paddings must hold 2 x rank values")
-            pad_buf = self.torch.tensor([a.get("val", 0.0)]).to(out.dtype).to(self.device)      # the pad value in the storage type
-            runs.append((srcs[0], desc(oshape, istr, ones, ones, zeros, [-p for p in pads[:r]], ishape, ostr)))
+            if mode in ("reflect", "edge"):
+                # Pad.cpp:72-160: the last two dimensions only; reflect mirrors about the edge element without repeating it,
+                # edge repeats it.  Each padded dimension is three pieces (before, body, after), each piece one linear map.
+                if r < 2 or any(pads[i] != 0 or pads[r + i] != 0 for i in range(r - 2)) or any(v < 0 for v in pads):
+                    raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: Pad mode {mode} pads the last two dimensions, by non-negative amounts")
+                if mode == "reflect" and any(pads[i] >= ishape[i] or pads[r + i] >= ishape[i] for i in (r - 2, r - 1)):
+                    raise L.B200QError(L.ERR_INVALID, f"{name}: a reflecting pad must be smaller than the dimension")
+
+                def pieces(n_, pb, pe):      # (count, mul, off, first output index)
+                    if mode == "reflect":
+                        return [(pb, -1, pb, 0), (n_, 1, 0, pb), (pe, -1, n_ - 2, pb + n_)]
+                    return [(pb, 0, 0, 0), (n_, 1, 0, pb), (pe, 0, n_ - 1, pb + n_)]
+                for ph_ in pieces(ishape[r - 2], pads[r - 2], pads[2 * r - 2]):
+                    for pw_ in pieces(ishape[r - 1], pads[r - 1], pads[2 * r - 1]):
+                        if ph_[0] == 0 or pw_[0] == 0:
+                            continue
+                        dims_ = ishape[:r - 2] + [ph_[0], pw_[0]]
+                        mul_ = [1] * (r - 2) + [ph_[1], pw_[1]]
+                        off_ = [0] * (r - 2) + [ph_[2], pw_[2]]
+                        runs.append((srcs[0], desc(dims_, istr, mul_, ones, zeros, off_, ishape, ostr, ph_[3] * ostr[r - 2] + pw_[3] * ostr[r - 1])))
+            elif mode != "constant":
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: Pad mode {mode} is not implemented (the reference has none for it either)")
+            else:
+                pad_buf = self.torch.tensor([a.get("val", 0.0)]).to(out.dtype).to(self.device)      # the pad value in the storage type
+                runs.append((srcs[0], desc(oshape, istr, ones, ones, zeros, [-p for p in pads[:r]], ishape, ostr)))
         elif t == "SwapDimInner":
             # SwapDimInner.cpp:17-46 with swap_dim_data (lib/Support/MathUtils.cpp:1539-1564): every axis with an offset is rotated,
             # out[b] = in[(b + offset) % dim]; the two halves of each such axis are one run each
