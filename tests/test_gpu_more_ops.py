@@ -764,3 +764,19 @@ def test_pad_reflect_and_edge(mode):
     m = run_graph({"x": qi(q.shape), "y": qi((1, 2, 6, 7))}, [dict(type="tpu.Pad", name="y", inputs=["x"],
                                                                  attrs=dict(paddings=[0, 0, 1, 3, 0, 0, 1, 0], mode=mode))], {}, {"x": q})
     assert np.array_equal(m.get_raw_tensor("y"), np.pad(q, ((0, 0), (0, 0), (1, 1), (3, 0)), mode=mode))
+
+
+def test_tpu_reduce_8bit():
+    rng = np.random.default_rng(22)
+    q = rng.integers(-128, 128, (2, 7, 3, 5), dtype=np.int8)
+    qi = lambda shp: dict(shape=list(shp), dtype="i8", scale=0.05, zp=0)  # noqa: E731
+    m = run_graph({"x": qi(q.shape), "y": qi((2, 3, 5))}, [dict(type="tpu.Reduce", name="y", inputs=["x"],
+                                                               attrs=dict(axes=[1], keepdims=False, mode="ReduceMean", multiplier=[77], rshift=[6]))], {}, {"x": q})
+    ssum = np.zeros((2, 3, 5), np.float32)
+    for a_ in range(7):
+        ssum = ssum + q[:, a_].astype(np.float32)
+    mean = np.trunc(ssum * np.float32(1.0 / 7)).astype(np.int64)
+    assert np.array_equal(m.get_raw_tensor("y"), np.clip((mean * 77 + 32) >> 6, -128, 127).astype(np.int8))
+    m = run_graph({"x": qi(q.shape), "y": qi((2, 7))}, [dict(type="tpu.Reduce", name="y", inputs=["x"],
+                                                           attrs=dict(axes=[2, 3], keepdims=False, mode="ReduceMax", multiplier=[1], rshift=[0]))], {}, {"x": q})
+    assert np.array_equal(m.get_raw_tensor("y"), q.max(axis=(2, 3)))

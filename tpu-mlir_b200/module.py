@@ -481,6 +481,39 @@ class module:  # noqa: N801  (name of the reference class)
                                                         n, int(m[0]), int(s[0]), int(m[1]), int(s[1]),
                                                         int(bool(a.get("do_relu", False))), _DT[oinfo["dtype"]], _P(out),
                                                         stream()))
+        if t == "tpu.Reduce":
+            # int8 form (Reduce.cpp:101-214): the reduction runs on the float-stored integers exactly as the f32 form does (mean =
+            # sum * float(1 / n)), the result is cut to an integer toward zero, multiplied and shifted half-up, and saturated to
+            # int8 (to_int8, whatever the output's signedness) - unless multiplier 1 and shift 0, which leave it as it is
+            if iinfo[0]["dtype"] not in ("i8", "u8") or oinfo["dtype"] != "i8" or op["inputs"][0] in self._nhwc or op["name"] in self._nhwc:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.Reduce takes f32 tensors, or 8-bit NCHW ones with an int8 result")
+            modes = {"ReduceMean": 7, "ReduceSum": 1, "ReduceMax": 2, "ReduceMin": 3, "ReduceProd": 4, "ReduceL2": 5, "ReduceL1": 6}
+            shape = list(iinfo[0]["shape"])
+            axes = sorted(int(v) + (len(shape) if int(v) < 0 else 0) for v in a["axes"])
+            if a["mode"] not in modes or any(axes[i] + 1 != axes[i + 1] for i in range(len(axes) - 1)):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: tpu.Reduce over one run of adjacent axes only")
+            outer, ax = int(np.prod(shape[:axes[0]])), int(np.prod(shape[axes[0]:axes[-1] + 1]))
+            inner = int(np.prod(shape[axes[-1] + 1:]))
+            mu = int((a.get("multiplier") or [1])[0])
+            sh = int((a.get("rshift") or [0])[0])
+            plain = mu == 1 and sh == 0
+            if plain and a["mode"] not in ("ReduceMax", "ReduceMin"):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: an unscaled integer {a['mode']} leaves the 8-bit range in the reference")
+            torch = self.torch
+            xf = torch.empty(ins[0].numel(), dtype=torch.float32, device=self.device)
+            rf = torch.empty(out.numel(), dtype=torch.float32, device=self.device)
+            ri = torch.empty(out.numel(), dtype=torch.int32, device=self.device)
+            tab = torch.tensor([mu, sh, 0], dtype=torch.int32, device=self.device)
+            self._keep.append((xf, rf, ri, tab))
+            mode, nin, nout, idt = modes[a["mode"]], ins[0].numel(), out.numel(), _DT[iinfo[0]["dtype"]]
+
+            def run_reduce():
+                L.check(lib.b200q_cast_q8_to_f32_dev(_P(ins[0]), idt, nin, 1.0, 0, _P(xf), stream()))
+                L.check(lib.b200q_top_reduce_f32_dev(mode, _P(xf), _P(rf), outer, ax, inner, stream()))
+                L.check(lib.b200q_top_cast_f32_dev(_P(rf), nout, L.DT_I32, L.ROUND_TOWARDS_ZERO, L.DT_I32, _P(ri), stream()))
+                L.check(lib.b200q_requant_int_axis_dev(_P(ri), nout, 1, 1, _P(tab[0:1]), _P(tab[1:2]), _P(tab[2:3]), L.RQ_MULTIPLIER_SHIFT,
+                                                       L.ROUND_HALF_UP, 0, L.DT_I8, _P(out), stream()))
+            return run_reduce
         if t in ("tpu.MaxConst", "tpu.MinConst", "tpu.SubConst"):
             # 8-bit forms (MaxConst.cpp:27-42, SubConst.cpp:26-112); the f32 forms went to the Top arithmetic above
             if iinfo[0]["dtype"] not in ("i8", "u8") or oinfo["dtype"] not in ("i8", "u8"):
