@@ -1,0 +1,118 @@
+"""The tests' restatements of some ops of the wider op set (tests/op_restatements.py and the expressions the GPU tests use)
+against the reference's OWN code for them, compiled from the checkout into oracle/_ref/moreops_ref.so (oracle/Makefile,
+target ref_moreops): interp_core, GridSamplerFunc, the activation table, swap_dim_data, pad_tensor_for_deconv,
+tensor_hc_transpose.  Skipped where that library could not be built."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from op_restatements import ACTIVE_MODES, active_table, grid_sampler_ref, interp_ref
+
+REF = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "moreops_ref.so")
+pytestmark = pytest.mark.skipif(not os.path.exists(REF), reason="oracle/_ref/moreops_ref.so was not built (no reference checkout)")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    return C.CDLL(REF)
+
+
+def fp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+# PLATFORM_SUPPORT (include/tpu_mlir/Backend/BM168x/Param.h:197-206) as InterpOp::inference picks it (Interp.cpp:226-279)
+def platform_sp(mode, coord_mode, platform):
+    coord = {"half_pixel": 0, "pytorch_half_pixel": 1, "align_corners": 2, "asymmetric": 3}[coord_mode]
+    if mode == "nearest":
+        sp = {"CAFFE": 2, "TORCH": 5, "TFLITE": 3}.get(platform, 7)
+        return sp, coord != 3, False
+    return (0 if platform == "CAFFE" else 4), coord == 2, coord in (0, 1)
+
+
+@pytest.mark.parametrize("mode", ["nearest", "linear"])
+@pytest.mark.parametrize("coord", ["half_pixel", "pytorch_half_pixel", "align_corners", "asymmetric"])
+@pytest.mark.parametrize("platform", ["ONNX", "TORCH", "TFLITE", "CAFFE"])
+def test_interp_restatement(ref, mode, coord, platform):
+    rng = np.random.default_rng(1)
+    for (ih, iw, oh, ow) in ((5, 7, 9, 11), (6, 4, 3, 2), (4, 4, 8, 8), (3, 5, 1, 1), (1, 3, 4, 9)):
+        x = rng.standard_normal((1, 1, ih, iw)).astype(np.float32)
+        want = np.zeros((oh, ow), np.float32)
+        sp, align, half = platform_sp(mode, coord, platform)
+        ref.ref_interp_plane(fp(x), fp(want), ih, iw, oh, ow, int(align), int(half), sp)
+        assert np.array_equal(interp_ref(x, oh, ow, mode, coord, platform)[0, 0], want), (ih, iw, oh, ow)
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("padding", [0, 1, 2])
+@pytest.mark.parametrize("align", [False, True])
+def test_grid_sampler_restatement(ref, mode, padding, align):
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((2, 3, 5, 7)).astype(np.float32)
+    grid = (rng.random((2, 4, 6, 2)) * 3 - 1.5).astype(np.float32)
+    grid[0, 0, 0] = [-1, 1]
+    grid[0, 0, 1] = [0, 0]
+    want = np.zeros((2, 3, 4, 6), np.float32)
+    ref.ref_grid_sampler(fp(x), fp(grid), fp(want), 2, 3, 5, 7, 4, 6, mode, padding, int(align))
+    assert np.array_equal(grid_sampler_ref(x, grid, mode, padding, align), want)
+
+
+def test_activation_table_restatement(ref):
+    ref.ref_active.argtypes = [C.c_int, C.c_int, C.c_double, C.c_double, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_longlong]
+    rng = np.random.default_rng(3)
+    x = np.concatenate([(rng.standard_normal(3000) * 2).astype(np.float32), np.float32([0, -0.0, 1, -1, 25, -25, 0.5])])
+    doms = {"x": x, "pos": np.abs(x) + np.float32(0.01), "unit": np.clip(x / 4, -0.99, 0.99).astype(np.float32)}
+    for mode, (dom, fn, coeffs) in active_table().items():
+        inp = np.ascontiguousarray(doms[dom])
+        want = np.zeros_like(inp)
+        co = list(coeffs or []) + [0.0, 0.0]
+        ref.ref_active(ACTIVE_MODES[mode], len(coeffs or []), co[0], co[1], fp(inp), fp(want), inp.size)
+        got = np.array([fn(float(v)) for v in inp], dtype=np.float64).astype(np.float32)
+        assert np.array_equal(got, want), mode       # Python's math functions are the C library's: equal to the last bit
+    # MISH works in float there (GenericCpuFunc.cpp:25-33)
+    want = np.zeros_like(x)
+    ref.ref_active(ACTIVE_MODES["MISH"], 0, 0.0, 0.0, fp(x), fp(want), x.size)
+    f = np.float32
+    got = x * (f(2) / (f(1) + np.exp(f(-2) * np.log(np.exp(x) + f(1)))) - f(1))
+    np.testing.assert_allclose(got, want, rtol=2e-6, atol=1e-6)
+
+
+def test_swap_dim_inner_is_a_roll(ref):
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((2, 5, 6, 7)).astype(np.float32)
+    for offs in ([0, 0, 2, 0], [0, 3, 0, 4], [0, 0, 0, 7], [1, 0, 5, 1]):
+        want = np.zeros_like(x)
+        ref.ref_swap_dim_inner(fp(x), fp(want), 4, (C.c_int64 * 4)(*x.shape), (C.c_int64 * 4)(*offs))
+        got = x
+        for ax, o in enumerate(offs):
+            if o:
+                got = np.roll(got, -o, axis=ax)
+        assert np.array_equal(got, want), offs
+
+
+def test_deconv_input_spreading(ref):
+    """pad_tensor_for_deconv (MathUtils.cpp:673-705) against the slicing the tests' deconvolution restatement and the executor's
+    plan use: the input lands at (k - 1) * d - pad with the stride between its elements, everything else holds the pad value."""
+    rng = np.random.default_rng(5)
+    ref.ref_pad_tensor_for_deconv.argtypes = [C.POINTER(C.c_float)] * 2 + [C.c_int] * 16 + [C.c_float]
+    for (h, w, kh, kw, sh, sw, pads, opad) in ((5, 6, 3, 3, 2, 2, (1, 1, 1, 1), (1, 1)), (4, 3, 4, 2, 2, 3, (1, 0, 0, 1), (0, 0)),
+                                               (3, 3, 3, 3, 1, 1, (0, 2, 2, 0), (0, 0))):
+        x = rng.standard_normal((2, 3, h, w)).astype(np.float32)
+        pt, pl, pb, pr = pads
+        hs = (h - 1) * sh + 1 + 2 * (kh - 1) - pt - pb + opad[0]
+        ws = (w - 1) * sw + 1 + 2 * (kw - 1) - pl - pr + opad[1]
+        want = np.zeros((2, 3, hs, ws), np.float32)
+        ref.ref_pad_tensor_for_deconv(fp(want), fp(x), 2, 3, h, w, kh, kw, 1, 1, sh, sw, pt, pb, pl, pr, opad[0], opad[1], 7.0)
+        got = np.full((2, 3, hs, ws), 7.0, np.float32)
+        got[:, :, kh - 1 - pt:kh - 1 - pt + (h - 1) * sh + 1:sh, kw - 1 - pl:kw - 1 - pl + (w - 1) * sw + 1:sw] = x
+        assert np.array_equal(got, want)
+
+
+def test_hc_transpose(ref):
+    ref.ref_tensor_hc_transpose.argtypes = [C.POINTER(C.c_float)] * 2 + [C.c_longlong] * 4
+    x = np.random.default_rng(6).standard_normal((2, 3, 4, 5)).astype(np.float32)
+    want = np.zeros((2, 4, 3, 5), np.float32)
+    ref.ref_tensor_hc_transpose(fp(want), fp(x), 2, 3, 4, 5)
+    assert np.array_equal(np.ascontiguousarray(x.transpose(0, 2, 1, 3)), want)

@@ -394,7 +394,7 @@ __global__ void active_f32_kernel(int mode, const float* __restrict__ x, double 
     case 4: r = v > 0 ? v : c0 * (exp(v) - 1.0); break;                                  // ELU, alpha = coeffs[0]
     case 5: r = sqrt(v); break;
     case 6: r = v * v; break;
-    case 7: r = (double)(1.f / (float)sqrt(v)); break;                                   // RSQRT: `1.f / std::sqrt(val)` then double
+    case 7: r = 1.0 / sqrt(v); break;                                                    // RSQRT: `1.f / std::sqrt(val)` divides in double
     case 8: r = fabs(v); break;
     case 9: r = log(v); break;
     case 10: r = round(v); break;
