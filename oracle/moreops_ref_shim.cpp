@@ -21,8 +21,11 @@
 #include <cstring>
 #include <functional>
 #include <memory>
+#include <numeric>
+#include <string>
 #include <vector>
 #include <linux/limits.h>   // XATTR_LIST_MAX, which the reference's sign() tests
+#undef ARG_MAX               // (that header's macro; Arg.cpp has an enumerator of this name)
 
 #define llvm_unreachable(msg) abort()
 #define omp_schedule(n) 1
@@ -116,6 +119,143 @@ void ref_pad_tensor_for_deconv(float* dst, float* src, int n, int c, int h, int 
 
 void ref_tensor_hc_transpose(float* dst, float* src, long long n, long long c, long long h, long long w) {
   tensor_hc_transpose<float>(dst, src, n, c, h, w);
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Whole inference bodies of top::Depth2SpaceOp (Depth2Space.cpp:19-104), top::GatherOp (Gather.cpp:17-82), top::ArgOp
+// (Arg.cpp:17-97 with its comparison helper) and gather_dim8 (GatherElements.cpp:20-80), compiled as members of stand-in
+// operator classes that answer the attribute accessors from plain fields.
+struct LogicalResult {};
+static inline LogicalResult success() { return {}; }
+struct InferenceParameter {
+  std::vector<float*> inputs, outputs;
+};
+#define ASSERT_THIS(x) assert(x)
+struct FakeValue {
+  std::vector<int64_t> shape;
+  bool none = false;
+};
+struct FakeStr {
+  std::string s;
+  std::string str() const { return s; }
+};
+namespace module {
+static inline void getNCHW(const FakeValue& v, int64_t& n, int64_t& c, int64_t& h, int64_t& w, bool) {
+  n = v.shape[0];
+  c = v.shape[1];
+  h = v.shape[2];
+  w = v.shape[3];
+}
+static inline std::vector<int64_t> getShape(const FakeValue& v) { return v.shape; }
+static inline int64_t getNumElements(const FakeValue& v) {
+  int64_t n = 1;
+  for (auto d : v.shape) n *= d;
+  return n;
+}
+static inline bool isNone(const FakeValue& v) { return v.none; }
+static std::vector<int64_t> g_last_shape;
+static inline void setShape(const FakeValue&, const std::vector<int64_t>& s) { g_last_shape = s; }
+}  // namespace module
+
+namespace top {
+struct Depth2SpaceOp {
+  FakeValue in_, out_;
+  bool in_nchw, out_nchw, crd, inv, swap;
+  int64_t bh, bw;
+  FakeValue getInput() { return in_; }
+  FakeValue getOutput() { return out_; }
+  bool getInIs_NCHW() { return in_nchw; }
+  bool getOutIs_NCHW() { return out_nchw; }
+  bool getIs_CRD() { return crd; }
+  bool getIsInversed() { return inv; }
+  bool getSwapCr() { return swap; }
+  int64_t getBlockH() { return bh; }
+  int64_t getBlockW() { return bw; }
+  LogicalResult inference(InferenceParameter& p);
+};
+struct GatherOp {
+  FakeValue in_, idx_, out_;
+  int64_t axis;
+  bool keepdims;
+  FakeValue getInput() { return in_; }
+  FakeValue getIndices() { return idx_; }
+  FakeValue getOutput() { return out_; }
+  int64_t getAxis() { return axis; }
+  bool getKeepdims() { return keepdims; }
+  LogicalResult inference(InferenceParameter& p);
+};
+struct ArgOp {
+  FakeValue in_, idx_, val_;
+  int64_t axis;
+  bool keepdims, select_last;
+  FakeStr mode;
+  FakeValue getInput() { return in_; }
+  FakeValue getIndices() { return idx_; }
+  FakeValue getValues() { return val_; }
+  int64_t getAxis() { return axis; }
+  void setAxis(int64_t a) { axis = a; }
+  bool getKeepdims() { return keepdims; }
+  bool getSelectLastIndex() { return select_last; }
+  FakeStr getMode() { return mode; }
+  LogicalResult inference(InferenceParameter& p);
+};
+}  // namespace top
+
+#include "_ref/depth2space.inc"
+#include "_ref/gather.inc"
+#include "_ref/arg.inc"
+#include "_ref/gather_dim8.inc"
+
+extern "C" {
+
+void ref_depth2space(float* x, float* y, const int64_t* in_shape, const int64_t* out_shape, int bh, int bw, int crd, int inversed, int in_nchw,
+                     int out_nchw, int swap_cr) {
+  top::Depth2SpaceOp op;
+  op.in_.shape.assign(in_shape, in_shape + 4);
+  op.out_.shape.assign(out_shape, out_shape + 4);
+  op.bh = bh;
+  op.bw = bw;
+  op.crd = crd;
+  op.inv = inversed;
+  op.in_nchw = in_nchw;
+  op.out_nchw = out_nchw;
+  op.swap = swap_cr;
+  InferenceParameter p;
+  p.inputs = {x};
+  p.outputs = {y};
+  op.inference(p);
+}
+
+void ref_gather(float* x, float* indices, float* y, int rank, const int64_t* shape, int idx_rank, const int64_t* idx_shape, int axis) {
+  top::GatherOp op;
+  op.in_.shape.assign(shape, shape + rank);
+  op.idx_.shape.assign(idx_shape, idx_shape + idx_rank);
+  op.axis = axis;
+  op.keepdims = true;
+  InferenceParameter p;
+  p.inputs = {x, indices};
+  p.outputs = {y};
+  op.inference(p);
+}
+
+void ref_arg(float* x, float* indices, float* values, int rank, const int64_t* shape, int axis, int is_max, int select_last) {
+  top::ArgOp op;
+  op.in_.shape.assign(shape, shape + rank);
+  op.val_.none = values == nullptr;
+  op.axis = axis;
+  op.keepdims = true;
+  op.select_last = select_last;
+  op.mode.s = is_max ? "ArgMax" : "ArgMin";
+  InferenceParameter p;
+  p.inputs = {x};
+  p.outputs = {indices, values};
+  op.inference(p);
+}
+
+void ref_gather_elements(float* dst, const float* src, const float* indices, const int* indices_shape, int* src_shape, int rank, int axis) {
+  gather_dim8(dst, src, indices, indices_shape, src_shape, rank, axis, rank);
 }
 
 }  // extern "C"

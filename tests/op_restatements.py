@@ -132,3 +132,36 @@ def interp_ref(x, oh, ow, mode, coord_mode, platform):
                     for xo, (_, xi) in enumerate(X):
                         out[p_, q_, yo, xo] = src[yi, xi]
     return out
+
+
+def d2s_ref(x, out_shape, bh, bw, crd, inv, in_nchw, out_nchw, swap):
+    """Depth2Space.cpp:19-103, loop for loop."""
+    def nchw(shape, f):
+        return (shape[0], shape[1], shape[2], shape[3]) if f else (shape[0], shape[3], shape[1], shape[2])
+    n_, ic, ih, iw = nchw(x.shape, in_nchw)
+    on, oc, oh, ow = nchw(out_shape, out_nchw)
+    ist = [ic * ih * iw, ih * iw, iw, 1] if in_nchw else [ic * ih * iw, 1, iw * ic, ic]
+    ost = [oc * oh * ow, oh * ow, ow, 1] if out_nchw else [oc * oh * ow, 1, ow * oc, oc]
+    if inv:
+        n_, on, ic, oc, ih, oh, iw, ow, ist, ost = on, n_, oc, ic, oh, ih, ow, iw, ost, ist
+    src = x.ravel()
+    dst = np.zeros(int(np.prod(out_shape)), x.dtype)
+    for i in range(n_ * ic):
+        n, c = divmod(i, ic)
+        if crd:
+            new_c, left = divmod(c, bh * bw)
+        else:
+            new_c, left = c % oc, c // oc
+        if swap:
+            c1, c2 = divmod(left, bw)
+            rleft = c2 * bh + c1
+            c = new_c * (bh * bw) + rleft if crd else rleft * oc + new_c
+        for h in range(ih):
+            for w in range(iw):
+                ii = n * ist[0] + c * ist[1] + h * ist[2] + w * ist[3]
+                oi = n * ost[0] + new_c * ost[1] + (h * bh + left // bw) * ost[2] + (w * bw + left % bw) * ost[3]
+                if inv:
+                    dst[ii] = src[oi]
+                else:
+                    dst[oi] = src[ii]
+    return dst.reshape(out_shape)

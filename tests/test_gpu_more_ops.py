@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 from tpu_mlir_b200 import _lib as L  # noqa: E402
 from tpu_mlir_b200.module import module  # noqa: E402
-from op_restatements import active_table, grid_sampler_ref, interp_ref  # noqa: E402
+from op_restatements import active_table, d2s_ref, grid_sampler_ref, interp_ref  # noqa: E402
 
 
 def run_graph(tensors, ops, weights, feeds, **kw):
@@ -197,39 +197,6 @@ def test_reduce_and_tpu_relu():
     t = {"x": {"shape": [4, 9], "dtype": "i8", "scale": 1.0, "zp": 0}, "r": {"shape": [4, 9], "dtype": "i8", "scale": 1.0, "zp": 0}}
     m2 = run_graph(t, [dict(type="tpu.Relu", name="r", inputs=["x"], attrs={})], {}, {"x": xi})
     assert np.array_equal(m2.get_raw_tensor("r"), np.maximum(xi, 0))
-
-
-def d2s_ref(x, out_shape, bh, bw, crd, inv, in_nchw, out_nchw, swap):
-    """Depth2Space.cpp:19-103, loop for loop."""
-    def nchw(shape, f):
-        return (shape[0], shape[1], shape[2], shape[3]) if f else (shape[0], shape[3], shape[1], shape[2])
-    n_, ic, ih, iw = nchw(x.shape, in_nchw)
-    on, oc, oh, ow = nchw(out_shape, out_nchw)
-    ist = [ic * ih * iw, ih * iw, iw, 1] if in_nchw else [ic * ih * iw, 1, iw * ic, ic]
-    ost = [oc * oh * ow, oh * ow, ow, 1] if out_nchw else [oc * oh * ow, 1, ow * oc, oc]
-    if inv:
-        n_, on, ic, oc, ih, oh, iw, ow, ist, ost = on, n_, oc, ic, oh, ih, ow, iw, ost, ist
-    src = x.ravel()
-    dst = np.zeros(int(np.prod(out_shape)), x.dtype)
-    for i in range(n_ * ic):
-        n, c = divmod(i, ic)
-        if crd:
-            new_c, left = divmod(c, bh * bw)
-        else:
-            new_c, left = c % oc, c // oc
-        if swap:
-            c1, c2 = divmod(left, bw)
-            rleft = c2 * bh + c1
-            c = new_c * (bh * bw) + rleft if crd else rleft * oc + new_c
-        for h in range(ih):
-            for w in range(iw):
-                ii = n * ist[0] + c * ist[1] + h * ist[2] + w * ist[3]
-                oi = n * ost[0] + new_c * ost[1] + (h * bh + left // bw) * ost[2] + (w * bw + left % bw) * ost[3]
-                if inv:
-                    dst[ii] = src[oi]
-                else:
-                    dst[oi] = src[ii]
-    return dst.reshape(out_shape)
 
 
 @pytest.mark.parametrize("cfg", [dict(crd=False, inv=False, in_nchw=True, out_nchw=True, swap=False), dict(crd=True, inv=False, in_nchw=True, out_nchw=True, swap=True),

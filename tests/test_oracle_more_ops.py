@@ -1,14 +1,14 @@
 """The tests' restatements of some ops of the wider op set (tests/op_restatements.py and the expressions the GPU tests use)
 against the reference's OWN code for them, compiled from the checkout into oracle/_ref/moreops_ref.so (oracle/Makefile,
 target ref_moreops): interp_core, GridSamplerFunc, the activation table, swap_dim_data, pad_tensor_for_deconv,
-tensor_hc_transpose.  Skipped where that library could not be built."""
+tensor_hc_transpose, and the whole inference bodies of top.Depth2Space, top.Gather, top.Arg and gather_dim8.  Skipped where that library could not be built."""
 import ctypes as C
 import os
 
 import numpy as np
 import pytest
 
-from op_restatements import ACTIVE_MODES, active_table, grid_sampler_ref, interp_ref
+from op_restatements import ACTIVE_MODES, active_table, d2s_ref, grid_sampler_ref, interp_ref
 
 REF = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "moreops_ref.so")
 pytestmark = pytest.mark.skipif(not os.path.exists(REF), reason="oracle/_ref/moreops_ref.so was not built (no reference checkout)")
@@ -116,3 +116,50 @@ def test_hc_transpose(ref):
     want = np.zeros((2, 4, 3, 5), np.float32)
     ref.ref_tensor_hc_transpose(fp(want), fp(x), 2, 3, 4, 5)
     assert np.array_equal(np.ascontiguousarray(x.transpose(0, 2, 1, 3)), want)
+
+
+@pytest.mark.parametrize("crd", [False, True])
+@pytest.mark.parametrize("inv", [False, True])
+@pytest.mark.parametrize("in_nchw,out_nchw", [(True, True), (False, True), (True, False), (False, False)])
+@pytest.mark.parametrize("swap", [False, True])
+def test_depth2space_restatement(ref, crd, inv, in_nchw, out_nchw, swap):
+    rng = np.random.default_rng(7)
+    bh, bw, c, h, w = 2, 3, 4, 3, 2
+    deep, shallow = (2, c * bh * bw, h, w), (2, c, h * bh, w * bw)
+    lay = lambda shp, f: shp if f else (shp[0], shp[2], shp[3], shp[1])  # noqa: E731
+    in_shape, out_shape = (lay(shallow, in_nchw), lay(deep, out_nchw)) if inv else (lay(deep, in_nchw), lay(shallow, out_nchw))
+    x = rng.standard_normal(in_shape).astype(np.float32)
+    want = np.zeros(out_shape, np.float32)
+    ref.ref_depth2space(fp(x), fp(want), (C.c_int64 * 4)(*in_shape), (C.c_int64 * 4)(*out_shape), bh, bw, int(crd), int(inv), int(in_nchw),
+                        int(out_nchw), int(swap))
+    assert np.array_equal(d2s_ref(x, out_shape, bh, bw, crd, inv, in_nchw, out_nchw, swap), want)
+
+
+def test_gather_arg_gather_elements_restatements(ref):
+    """The numpy expressions the GPU tests use for Gather (np.take with negative indices wrapped), Arg (first / last extreme)
+    and GatherElements (np.take_along_axis on the indices' extent)."""
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((3, 6, 4)).astype(np.float32)
+    idx = np.float32([[5, 0, -1], [2, 2, -6]])
+    want = np.zeros((3, 2, 3, 4), np.float32)
+    ref.ref_gather(fp(x), fp(idx), fp(want), 3, (C.c_int64 * 3)(*x.shape), 2, (C.c_int64 * 2)(*idx.shape), 1)
+    assert np.array_equal(np.take(x, idx.astype(np.int64), axis=1), want)
+    t = rng.integers(-3, 4, (3, 9, 5)).astype(np.float32)
+    for is_max in (1, 0):
+        for last in (1, 0):
+            wi, wv = np.zeros((3, 5), np.float32), np.zeros((3, 5), np.float32)
+            ref.ref_arg(fp(t), fp(wi), fp(wv), 3, (C.c_int64 * 3)(*t.shape), 1, is_max, last)
+            ext = t.max(axis=1) if is_max else t.min(axis=1)
+            hit = t == ext[:, None, :]
+            gi = (t.shape[1] - 1 - hit[:, ::-1, :].argmax(axis=1)) if last else hit.argmax(axis=1)
+            assert np.array_equal(gi.astype(np.float32), wi) and np.array_equal(ext, wv), (is_max, last)
+    src = rng.standard_normal((4, 5, 6)).astype(np.float32)
+    ind = rng.integers(0, 5, (3, 2, 6)).astype(np.float32)
+    wg = np.zeros(ind.shape, np.float32)
+    ref.ref_gather_elements(fp(wg), fp(src), fp(ind), (C.c_int * 3)(*ind.shape), (C.c_int * 3)(*src.shape), 3, 1)
+    got = np.zeros(ind.shape, np.float32)
+    for a_ in range(3):
+        for b_ in range(2):
+            for c_ in range(6):
+                got[a_, b_, c_] = src[a_, int(ind[a_, b_, c_]), c_]
+    assert np.array_equal(got, wg)
