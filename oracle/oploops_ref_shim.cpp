@@ -14,6 +14,9 @@
 //   lib/Dialect/Tpu/Interfaces/Common/RequantIntAxis.cpp:18-120    tpu.RequantIntAxis::inference, whole body
 //   lib/Dialect/Tpu/Interfaces/Common/RequantInt.cpp:18-71         tpu.RequantInt::inference, whole body
 //   lib/Support/CastUtils.cpp:15-47                                requant / dequant of tpu.Cast
+//   lib/Dialect/Tpu/Interfaces/Common/RequantFp.cpp:19-67          tpu.RequantFp::inference, whole body
+//   lib/Dialect/Tpu/Interfaces/Common/MaxConst.cpp:36-45, MinConst.cpp:36-45   the uniform-quantized loops
+//   lib/Dialect/Tpu/Interfaces/Common/PRelu.cpp:73-96              the symmetric 8-bit loop of tpu.PRelu
 // This file supplies only what those bodies expect from the rest of the reference: the operator's attribute
 // accessors (answered from a context the C entry points fill), the shapes, a stand-in for mlir::Type that knows a
 // width and a signedness, and the element-wise fp32 add (+ ReLU) that the reference obtains from oneDNN's binary
@@ -51,6 +54,8 @@ struct Type {
   bool uns = false, is_int = true;
   void dump() const {}
   bool isInteger(int w) const { return is_int && width == w; }
+  bool isFloat8E4M3FN() const { return false; }
+  bool isFloat8E5M2() const { return false; }
   template <typename T>
   bool isa() const;
 };
@@ -264,6 +269,39 @@ float BF16(float src, bool is_tpu = true);
 #include "_ref/castutils.inc"
 }  // namespace tpu_mlir
 
+// ---------------------------------------------------------------------------------------------- RequantFp, Max/MinConst, PRelu
+struct FpAttr {
+  double v;
+  double convertToDouble() const { return v; }
+};
+static double g_fp_scale = 1.0, g_fp_offset = 0.0;
+static void F8E4M3(float*, float*, int64_t, double, bool) { abort(); }   // 8-bit float outputs are not exercised
+static void F8E5M2(float*, float*, int64_t, double, bool) { abort(); }
+static int requant_fp(InferenceParameter& p) {
+  using tpu::RequantMode;   // the body sits inside namespace tpu in the reference
+  auto getScale = [] { return FpAttr{g_fp_scale}; };
+  auto getOffset = [] { return FpAttr{g_fp_offset}; };
+#include "_ref/requant_fp.inc"
+}
+static void maxconst_q(InferenceParameter& p, int64_t num_elem, double izp, float const_val) {
+  auto out_type = g.out_type;
+  auto getMultiplier = [] { return g.multiplier; };
+  auto getRshift = [] { return g.rshift; };
+#include "_ref/maxconst_q.inc"
+}
+static void minconst_q(InferenceParameter& p, int64_t num_elem, double izp, float const_val) {
+  auto out_type = g.out_type;
+  auto getMultiplier = [] { return g.multiplier; };
+  auto getRshift = [] { return g.rshift; };
+#include "_ref/minconst_q.inc"
+}
+static void prelu_q(InferenceParameter& p, int64_t num_outer, int64_t num_inner, int64_t num_slope, int64_t shift) {
+  auto out_type = g.out_type;
+  const bool is_cv18xx = false;
+  int64_t shift_pos = 0, multiplier_pos = 0;
+#include "_ref/prelu_q.inc"
+}
+
 // ---------------------------------------------------------------------------------------------- C entry points
 static void set_out_type(int width, int is_unsigned) {
   g.out_type.width = width;
@@ -419,6 +457,43 @@ float ref_cast_dequant(float v, double scale, long long zp, int expressed) {
   q.zp = zp;
   q.expressed = expressed;
   return tpu_mlir::dequant(v, q);
+}
+
+void ref_requant_fp(float* x, float* y, long long n, double scale, double offset, int qmode, int round_mode, int width, int is_unsigned,
+                    long long out_zp) {
+  set_out_type(width, is_unsigned);
+  g.out_shape = {(int64_t)n};
+  g.out_q.zp = out_zp;
+  g.qmode = (tpu::RequantMode)qmode;
+  g.round_mode = round_mode;
+  g_fp_scale = scale;
+  g_fp_offset = offset;
+  InferenceParameter p;
+  p.inputs = {x};
+  p.outputs = {y};
+  requant_fp(p);
+}
+
+void ref_maxmin_const(int is_max, float* x, float* y, long long n, double izp, float const_val, long long multiplier, long long rshift,
+                      int do_relu, int width, int is_unsigned) {
+  set_out_type(width, is_unsigned);
+  g.multiplier = multiplier;
+  g.rshift = rshift;
+  g.do_relu = do_relu != 0;
+  InferenceParameter p;
+  p.inputs = {x};
+  p.outputs = {y};
+  if (is_max) maxconst_q(p, n, izp, const_val);
+  else minconst_q(p, n, izp, const_val);
+}
+
+void ref_prelu_int8(float* x, float* slope, float* y, long long num_outer, long long num_inner, long long num_slope, long long shift, int width,
+                    int is_unsigned) {
+  set_out_type(width, is_unsigned);
+  InferenceParameter p;
+  p.inputs = {x, slope};
+  p.outputs = {y};
+  prelu_q(p, num_outer, num_inner, num_slope, shift);
 }
 
 }  // extern "C"

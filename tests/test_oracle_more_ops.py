@@ -163,3 +163,62 @@ def test_gather_arg_gather_elements_restatements(ref):
             for c_ in range(6):
                 got[a_, b_, c_] = src[a_, int(ind[a_, b_, c_]), c_]
     assert np.array_equal(got, wg)
+
+
+# ------------------------------------------------------------------ loops compiled into oracle/_ref/oploops_ref.so
+OPLOOPS = os.path.join(os.path.dirname(REF), "oploops_ref.so")
+
+
+@pytest.fixture(scope="module")
+def loops():
+    if not os.path.exists(OPLOOPS):
+        pytest.skip("oracle/_ref/oploops_ref.so was not built")
+    lib = C.CDLL(OPLOOPS)
+    if not hasattr(lib, "ref_requant_fp"):
+        pytest.skip("an older oploops_ref.so")
+    lib.ref_requant_fp.argtypes = [C.POINTER(C.c_float)] * 2 + [C.c_longlong, C.c_double, C.c_double, C.c_int, C.c_int, C.c_int, C.c_int, C.c_longlong]
+    lib.ref_maxmin_const.argtypes = [C.c_int] + [C.POINTER(C.c_float)] * 2 + [C.c_longlong, C.c_double, C.c_float, C.c_longlong, C.c_longlong, C.c_int,
+                                                                              C.c_int, C.c_int]
+    lib.ref_prelu_int8.argtypes = [C.POINTER(C.c_float)] * 3 + [C.c_longlong] * 4 + [C.c_int, C.c_int]
+    return lib
+
+
+def _rsr(v, s):
+    return (v + (1 << (s - 1))) >> s if s > 0 else v
+
+
+def test_requant_fp_expressions(loops):
+    """tpu.RequantFp::inference (RequantFp.cpp:19-67) against the expressions of tests/test_gpu_more_ops.py."""
+    rng = np.random.default_rng(9)
+    acc = rng.integers(-60000, 60000, 4000).astype(np.float32)
+    acc[:4] = [250, -250, 750, -750]
+    sc, of = 0.002, 0.5
+    want = np.zeros_like(acc)
+    loops.ref_requant_fp(fp(acc), fp(want), acc.size, sc, of, 2, 0, 8, 0, 0)          # MultiplierShift, half away from zero, int8
+    f = acc * np.float32(sc) + np.float32(of)
+    assert np.array_equal(np.clip(np.sign(f) * np.floor(np.abs(f) + np.float32(0.5)), -128, 127), want)
+    loops.ref_requant_fp(fp(acc), fp(want), acc.size, sc, 0.0, 1, 3, 8, 1, 7)           # TFLite, half to even, uint8, zero point 7
+    assert np.array_equal(np.clip(np.rint(acc * np.float32(sc)).astype(np.int64) + 7, 0, 255).astype(np.float32), want)
+
+
+def test_max_min_const_expressions(loops):
+    rng = np.random.default_rng(10)
+    q = rng.integers(-128, 128, 3000).astype(np.float32)
+    want = np.zeros_like(q)
+    loops.ref_maxmin_const(1, fp(q), fp(want), q.size, 3.0, np.float32(-150.7), 9, 3, 0, 8, 0)
+    pf = np.maximum(((q.astype(np.int64) - 3) * 9).astype(np.float32), np.float32(-150.7))
+    assert np.array_equal(np.clip(_rsr(np.trunc(pf).astype(np.int64), 3), -128, 127).astype(np.float32), want)
+    loops.ref_maxmin_const(0, fp(q), fp(want), q.size, 0.0, np.float32(200.25), 7, 2, 1, 8, 0)
+    pf = np.minimum((q.astype(np.int64) * 7).astype(np.float32), np.float32(200.25))
+    assert np.array_equal(np.clip(np.maximum(_rsr(np.trunc(pf).astype(np.int64), 2), 0), -128, 127).astype(np.float32), want)
+
+
+def test_prelu_int8_expression(loops):
+    rng = np.random.default_rng(11)
+    q = rng.integers(-128, 128, (2, 3, 4, 5)).astype(np.float32)
+    slope = np.float32([13, -7, 100])
+    want = np.zeros_like(q)
+    loops.ref_prelu_int8(fp(q), fp(slope), fp(want), 6, 20, 3, 5, 8, 0)
+    prod = q.astype(np.int64) * slope.astype(np.int64).reshape(1, 3, 1, 1)
+    neg = np.clip((prod + 16) >> 5, -128, 127)
+    assert np.array_equal(np.where(q < 0, neg, q).astype(np.float32), want)
