@@ -17,6 +17,8 @@
 //   lib/Dialect/Tpu/Interfaces/Common/RequantFp.cpp:19-67          tpu.RequantFp::inference, whole body
 //   lib/Dialect/Tpu/Interfaces/Common/MaxConst.cpp:36-45, MinConst.cpp:36-45   the uniform-quantized loops
 //   lib/Dialect/Tpu/Interfaces/Common/PRelu.cpp:73-96              the symmetric 8-bit loop of tpu.PRelu
+//   lib/Dialect/Tpu/Interfaces/Common/SubConst.cpp:19-111          tpu.SubConst::inference, whole body
+//   include/tpu_mlir/Support/MathUtils.h:311-337, lib/Dialect/Top/Interfaces/Cast.cpp:18-64   to_int8 ... to_uint16; top.Cast::inference, whole body
 // This file supplies only what those bodies expect from the rest of the reference: the operator's attribute
 // accessors (answered from a context the C entry points fill), the shapes, a stand-in for mlir::Type that knows a
 // width and a signedness, and the element-wise fp32 add (+ ReLU) that the reference obtains from oneDNN's binary
@@ -56,6 +58,8 @@ struct Type {
   bool isInteger(int w) const { return is_int && width == w; }
   bool isFloat8E4M3FN() const { return false; }
   bool isFloat8E5M2() const { return false; }
+  bool isBF16() const { return false; }
+  bool isF16() const { return false; }
   template <typename T>
   bool isa() const;
 };
@@ -129,6 +133,9 @@ static mlir::Type getStorageType(Value) { return g.out_type; }
 static bool isUniformQuantized(Value v) { return v.which == 0 ? true : g.in_quantized; }
 static QType getUniformQuantizedType(Value v) { return v.which == 0 ? g.out_q : g.in_q; }
 static bool isWeight(Value) { return g.right_is_weight; }
+static bool g_module_asym = false;
+static bool isAsymmetric() { return g_module_asym; }
+static void setShape(Value, const std::vector<int64_t>&) {}
 typedef std::shared_ptr<std::vector<int64_t>> i64_array_t;
 typedef std::shared_ptr<std::vector<double>> f64_array_t;
 // Module.cpp:570-578: the attribute's values when present (their count is asserted), else num_elem defaults
@@ -300,6 +307,43 @@ static void prelu_q(InferenceParameter& p, int64_t num_outer, int64_t num_inner,
   const bool is_cv18xx = false;
   int64_t shift_pos = 0, multiplier_pos = 0;
 #include "_ref/prelu_q.inc"
+}
+
+// ---------------------------------------------------------------------------------------------- tpu.SubConst, top.Cast
+namespace tpu_mlir {
+void F16(float* p_src, float* p_dst, int num);                      // lib/Support/Float16.cpp (compiled in)
+void BF16(float* p_src, float* p_dst, int num, bool is_tpu = true);
+}  // namespace tpu_mlir
+static double g_const_val = 0.0, g_relu_limit = -1.0;
+static bool g_is_reverse = false;
+struct LimitAttr {
+  double v;
+  double getValueAsDouble() const { return v; }
+};
+static int subconst(InferenceParameter& p) {
+  using mlir::FloatType;
+  using tpu_mlir::BF16;
+  using tpu_mlir::F16;
+  auto getConstVal = [] { return FpAttr{g_const_val}; };
+  auto getF8Scale = [] { return FpAttr{1.0}; };
+  auto getIsReverse = [] { return g_is_reverse; };
+  auto getMultiplier = [] { return g.multiplier; };
+  auto getRshift = [] { return g.rshift; };
+  auto getReluLimitAttr = [] { return LimitAttr{g_relu_limit}; };
+#include "_ref/subconst.inc"
+}
+#include "_ref/to_intn.inc"
+#define UNREACHABLE_THIS(msg) abort()
+static int failure() { return 1; }
+static std::string g_cast_to;
+static int top_cast(InferenceParameter& p) {
+  struct RmStr {
+    std::string str() const { return ""; }
+  };
+  auto getRoundMode = [] { return RmStr{}; };
+  auto round_mode_convert = [](const std::string&) { return (RoundingMode)g.round_mode; };
+  auto getTo = [] { return g_cast_to; };
+#include "_ref/top_cast.inc"
 }
 
 // ---------------------------------------------------------------------------------------------- C entry points
@@ -494,6 +538,33 @@ void ref_prelu_int8(float* x, float* slope, float* y, long long num_outer, long 
   p.inputs = {x, slope};
   p.outputs = {y};
   prelu_q(p, num_outer, num_inner, num_slope, shift);
+}
+
+void ref_subconst(float* x, float* y, long long n, double const_val, int is_reverse, long long multiplier, long long rshift, int do_relu,
+                  double relu_limit, int width, int is_unsigned) {
+  set_out_type(width, is_unsigned);
+  g.out_shape = {(int64_t)n};
+  g.multiplier = multiplier;
+  g.rshift = rshift;
+  g.do_relu = do_relu != 0;
+  g_const_val = const_val;
+  g_is_reverse = is_reverse != 0;
+  g_relu_limit = relu_limit;
+  module::g_module_asym = false;
+  InferenceParameter p;
+  p.inputs = {x};
+  p.outputs = {y};
+  subconst(p);
+}
+
+void ref_top_cast(float* x, float* y, long long n, const char* to, int round_mode) {
+  g.out_shape = {(int64_t)n};
+  g.round_mode = round_mode;
+  g_cast_to = to;
+  InferenceParameter p;
+  p.inputs = {x};
+  p.outputs = {y};
+  top_cast(p);
 }
 
 }  // extern "C"

@@ -222,3 +222,33 @@ def test_prelu_int8_expression(loops):
     prod = q.astype(np.int64) * slope.astype(np.int64).reshape(1, 3, 1, 1)
     neg = np.clip((prod + 16) >> 5, -128, 127)
     assert np.array_equal(np.where(q < 0, neg, q).astype(np.float32), want)
+
+
+def test_subconst_and_top_cast_expressions(loops):
+    """tpu.SubConst::inference (SubConst.cpp:19-111, symmetric 8-bit) and top.Cast::inference (Cast.cpp:18-64) against the
+    expressions of tests/test_gpu_more_ops.py."""
+    if not hasattr(loops, "ref_subconst"):
+        pytest.skip("an older oploops_ref.so")
+    loops.ref_subconst.argtypes = [C.POINTER(C.c_float)] * 2 + [C.c_longlong, C.c_double, C.c_int, C.c_longlong, C.c_longlong, C.c_int, C.c_double,
+                                                                C.c_int, C.c_int]
+    loops.ref_top_cast.argtypes = [C.POINTER(C.c_float)] * 2 + [C.c_longlong, C.c_char_p, C.c_int]
+    rng = np.random.default_rng(12)
+    q = rng.integers(-128, 128, 3000).astype(np.float32)
+    want = np.zeros_like(q)
+    for rev in (0, 1):
+        loops.ref_subconst(fp(q), fp(want), q.size, 33.5, rev, 11, 4, 0, -1.0, 8, 0)
+        prod = (q.astype(np.int64) * 11).astype(np.float64)
+        f = (33.5 - prod if rev else prod - 33.5).astype(np.float32)
+        assert np.array_equal(np.clip(_rsr(np.trunc(f).astype(np.int64), 4), -128, 127).astype(np.float32), want), rev
+    # with the ReLU and its limit acting on the float before the shift
+    loops.ref_subconst(fp(q), fp(want), q.size, 10.25, 0, 5, 2, 1, 300.0, 8, 0)
+    f = np.minimum(np.maximum(((q.astype(np.int64) * 5).astype(np.float64) - 10.25).astype(np.float32), 0), np.float32(300.0))
+    assert np.array_equal(np.clip(np.maximum(_rsr(np.trunc(f).astype(np.int64), 2), 0), -128, 127).astype(np.float32), want)
+    v = np.float32([-300.5, -128.5, -2.5, -1.5, -0.5, 0.5, 1.5, 2.5, 126.5, 127.5, 255.5, 300.2, 40000.7, -40000.7])
+    away = np.sign(v) * np.floor(np.abs(v) + np.float32(0.5))
+    out = np.zeros_like(v)
+    # RoundingMode numbering of MathUtils.h:28-42: 0 half away, 3 half to even, 6 towards zero, 8 up, 9 down
+    for to, rm, expect in ((b"INT8", 0, np.clip(away, -128, 127)), (b"UINT8", 3, np.clip(np.rint(v), 0, 255)), (b"INT16", 9, np.clip(np.floor(v), -32768, 32767)),
+                           (b"UINT16", 8, np.clip(np.ceil(v), 0, 65535)), (b"INT32", 6, np.trunc(v)), (b"F32", 0, v)):
+        loops.ref_top_cast(fp(v), fp(out), v.size, to, rm)
+        assert np.array_equal(out, expect.astype(np.float32)), to
