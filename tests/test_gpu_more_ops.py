@@ -631,3 +631,52 @@ def test_tpu_reduce_8bit():
     m = run_graph({"x": qi(q.shape), "y": qi((2, 7))}, [dict(type="tpu.Reduce", name="y", inputs=["x"],
                                                            attrs=dict(axes=[2, 3], keepdims=False, mode="ReduceMax", multiplier=[1], rshift=[0]))], {}, {"x": q})
     assert np.array_equal(m.get_raw_tensor("y"), q.max(axis=(2, 3)))
+
+
+def test_inverted_residual_block_against_the_oracle():
+    """A MobileNetV2 block through the executor, every tensor against the oracle's op walk: 1x1 expansion (tensor cores),
+    depthwise 3x3 (the CUDA-core patch kernel), 1x1 projection, residual Add; then a stride-2 depthwise into an Upsample,
+    a channel Concat and a PRelu."""
+    import oracle
+    rng = np.random.default_rng(23)
+    N, Cin, Cexp, H = 2, 32, 96, 14
+    x = rng.integers(-128, 128, (N, Cin, H, H), dtype=np.int8)
+
+    def conv_w(oc, icg, k):
+        return (rng.integers(-127, 128, (oc, icg, k, k), dtype=np.int8), rng.integers(-2000, 2000, oc, dtype=np.int32),
+                rng.integers(8000, 20000, oc).tolist(), rng.integers(19, 23, oc).tolist())
+    w1, b1, m1, s1 = conv_w(Cexp, Cin, 1)
+    wd, bd, md, sd = conv_w(Cexp, 1, 3)
+    w2, b2, m2, s2 = conv_w(Cin, Cexp, 1)
+    wd2, bd2, md2, sd2 = conv_w(Cin, 1, 3)
+    slope = rng.integers(-60, 60, 2 * Cin).astype(np.int8).reshape(1, -1, 1, 1)
+    qi = lambda shp: dict(shape=list(shp), dtype="i8", scale=0.05, zp=0)  # noqa: E731
+    conv = lambda name, src, k, pads, stride=1, group=1, relu=True, m=None, s=None: dict(  # noqa: E731
+        type="tpu.Conv2D", name=name, inputs=[src], attrs=dict(kernel_shape=[k, k], strides=[stride, stride], pads=list(pads), group=group,
+                                                                do_relu=relu, multiplier=m, rshift=s, quant_mode="MultiplierShift"))
+    ops = [conv("exp", "x", 1, (0, 0, 0, 0), m=m1, s=s1), conv("dw", "exp", 3, (1, 1, 1, 1), group=Cexp, m=md, s=sd),
+           conv("proj", "dw", 1, (0, 0, 0, 0), relu=False, m=m2, s=s2),
+           dict(type="tpu.Add", name="res", inputs=["x", "proj"], attrs=dict(multipliers=[64, 70], rshifts=[6, 7])),
+           conv("down", "res", 3, (1, 1, 1, 1), stride=2, group=Cin, m=md2, s=sd2),
+           dict(type="tpu.Upsample", name="up", inputs=["down"], attrs=dict(scale_h=2, scale_w=2)),
+           dict(type="tpu.Concat", name="cat", inputs=["res", "up"], attrs=dict(axis=1)),
+           dict(type="tpu.PRelu", name="out", inputs=["cat"], attrs=dict(rshift=6))]
+    tensors = {"x": qi(x.shape), "exp": qi((N, Cexp, H, H)), "dw": qi((N, Cexp, H, H)), "proj": qi(x.shape), "res": qi(x.shape),
+               "down": qi((N, Cin, H // 2, H // 2)), "up": qi(x.shape), "cat": qi((N, 2 * Cin, H, H)), "out": qi((N, 2 * Cin, H, H))}
+    weights = {"exp_filter": w1, "exp_bias": b1, "dw_filter": wd, "dw_bias": bd, "proj_filter": w2, "proj_bias": b2, "down_filter": wd2,
+               "down_bias": bd2, "out_slope": slope}
+    m = run_graph(tensors, ops, weights, {"x": x})
+    m.check_status()
+    oc_ = lambda t, w, b, mu, sh, **kw: oracle.conv2d_int8(t, w, b, mult=mu, rshift=sh, **kw)  # noqa: E731
+    want = {"exp": oc_(x, w1, b1, m1, s1, do_relu=True)}
+    want["dw"] = oc_(want["exp"], wd, bd, md, sd, pads=(1, 1, 1, 1), groups=Cexp, do_relu=True)
+    want["proj"] = oc_(want["dw"], w2, b2, m2, s2)
+    want["res"] = oracle.add_int8(x, want["proj"], 64, 6, 70, 7)
+    want["down"] = oc_(want["res"], wd2, bd2, md2, sd2, stride=(2, 2), pads=(1, 1, 1, 1), groups=Cin, do_relu=True)
+    want["up"] = np.repeat(np.repeat(want["down"], 2, axis=2), 2, axis=3)
+    want["cat"] = np.concatenate([want["res"], want["up"]], axis=1)
+    prod = want["cat"].astype(np.int64) * slope
+    want["out"] = np.where(want["cat"] < 0, np.clip((prod + 32) >> 6, -128, 127), want["cat"]).astype(np.int8)
+    for name, w_ in want.items():
+        assert np.array_equal(m.get_raw_tensor(name), w_), name
+    assert len(np.unique(want["out"])) > 50
