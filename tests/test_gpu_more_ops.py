@@ -665,8 +665,6 @@ def test_inverted_residual_block_against_the_oracle():
                "down": qi((N, Cin, H // 2, H // 2)), "up": qi(x.shape), "cat": qi((N, 2 * Cin, H, H)), "out": qi((N, 2 * Cin, H, H))}
     weights = {"exp_filter": w1, "exp_bias": b1, "dw_filter": wd, "dw_bias": bd, "proj_filter": w2, "proj_bias": b2, "down_filter": wd2,
                "down_bias": bd2, "out_slope": slope}
-    m = run_graph(tensors, ops, weights, {"x": x})
-    m.check_status()
     oc_ = lambda t, w, b, mu, sh, **kw: oracle.conv2d_int8(t, w, b, mult=mu, rshift=sh, **kw)  # noqa: E731
     want = {"exp": oc_(x, w1, b1, m1, s1, do_relu=True)}
     want["dw"] = oc_(want["exp"], wd, bd, md, sd, pads=(1, 1, 1, 1), groups=Cexp, do_relu=True)
@@ -677,6 +675,10 @@ def test_inverted_residual_block_against_the_oracle():
     want["cat"] = np.concatenate([want["res"], want["up"]], axis=1)
     prod = want["cat"].astype(np.int64) * slope
     want["out"] = np.where(want["cat"] < 0, np.clip((prod + 32) >> 6, -128, 127), want["cat"]).astype(np.int8)
-    for name, w_ in want.items():
-        assert np.array_equal(m.get_raw_tensor(name), w_), name
     assert len(np.unique(want["out"])) > 50
+    # NCHW executor, and the channels-last one (which keeps what the depthwise kernels, Concat's consumer and PRelu read in NCHW)
+    for cl in (False, True):
+        m = run_graph(tensors, ops, weights, {"x": x}, channels_last=cl)
+        m.check_status()
+        for name, w_ in want.items():
+            assert np.array_equal(m.get_raw_tensor(name), w_), (name, cl)

@@ -43,6 +43,10 @@ _TPU_F32_AS_TOP = ("tpu.Sub", "tpu.Div", "tpu.MaxConst", "tpu.MinConst", "tpu.Su
 _ACTIVE_MODES = {n: i for i, n in enumerate(
     "TANH SIGMOID RELU EXP ELU SQRT SQUARE RSQRT ABSVAL LN ROUND CEIL FLOOR SIN COS IS_FINITE MISH SWISH HSWISH SILU ARCSIN ARCCOS "
     "ARCSINH ARCCOSH ARCTANH SINH COSH TAN SIGN GELU ERF HSIGMOID LOG_SIGMOID SOFT_PLUS SOFT_SIGN LOG2 TGELU QGELU".split())}
+# Tpu-dialect ops whose plans take NCHW-stored tensors only (a channels-last executor keeps their inputs NCHW)
+_NCHW_ONLY = ("tpu.Deconv", "tpu.PRelu", "tpu.Sub", "tpu.MaxConst", "tpu.MinConst", "tpu.SubConst", "tpu.Reduce", "tpu.RequantFp",
+              "tpu.RequantIntAxis", "tpu.Gather", "tpu.GatherElements", "tpu.Arg", "tpu.Interp", "tpu.GridSampler", "tpu.Depth2Space",
+              "tpu.Active", "tpu.Div", "tpu.Softmax", "tpu.LayerNorm", "tpu.AddConst", "tpu.MulConst", "tpu.Relu")
 _MOVE_OPS = ("Slice", "Permute", "Tile", "Upsample", "Pad", "Concat", "Squeeze", "Unsqueeze", "Depth2Space", "SwapDimInner")
 
 
@@ -174,30 +178,44 @@ class module:  # noqa: N801  (name of the reference class)
         group, output channels a multiple of 16), and whatever an Add, Pool2D or Cast derives from such tensors."""
         nhwc = set()
         tens = graph["tensors"]
-        for op in graph["ops"]:
-            t, a, name = op["type"], op.get("attrs", {}), op["name"]
-            ins = op["inputs"]
-            if len(tens[name]["shape"]) != 4:
-                continue
-            if t == "tpu.Conv2D":
-                oc = tens[name]["shape"][1]
-                if a.get("group", 1) == 1 and oc % 16 == 0 and tens[name]["dtype"] in ("i8", "u8"):
-                    nhwc.add(name)
-                elif ins[0] in nhwc:
-                    raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: a grouped convolution cannot read a channels-last tensor")
-            elif t == "tpu.Add":
-                if ins[0] in nhwc and ins[1] in nhwc:
-                    nhwc.add(name)
-                elif ins[0] in nhwc or ins[1] in nhwc:
-                    raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: operands in different layouts")
-            elif t in ("tpu.Pool2D", "tpu.Cast", "tpu.Lut", "tpu.MulShift"):
-                if ins[0] in nhwc:
-                    nhwc.add(name)
-            elif t == "tpu.Mul":
-                if ins[0] in nhwc and ins[1] in nhwc:
-                    nhwc.add(name)
-                elif ins[0] in nhwc or ins[1] in nhwc:
-                    raise L.B200QError(L.ERR_UNSUPPORTED, f"{name}: operands in different layouts")
+        pinned = set()      # tensors some consumer can only read as NCHW: their producers write NCHW
+        while True:
+            nhwc, again = set(), False
+            for op in graph["ops"]:
+                t, a, name = op["type"], op.get("attrs", {}), op["name"]
+                ins = op["inputs"]
+                stored = [i for i in ins if i in nhwc]
+                if t == "tpu.Conv2D":
+                    if a.get("group", 1) != 1 and stored:          # the CUDA-core kernels of grouped convolutions read NCHW
+                        pinned.update(stored)
+                        again = True
+                        break
+                    oc = tens[name]["shape"][1] if len(tens[name]["shape"]) == 4 else 0
+                    if a.get("group", 1) == 1 and oc and oc % 16 == 0 and tens[name]["dtype"] in ("i8", "u8") and name not in pinned:
+                        nhwc.add(name)
+                elif t in ("tpu.Add", "tpu.Mul"):
+                    if len(stored) == len(ins) and len(tens[name]["shape"]) == 4 and name not in pinned and \
+                            all(list(tens[i]["shape"]) == list(tens[name]["shape"]) for i in ins):
+                        nhwc.add(name)
+                    elif stored:                                    # mixed layouts, a pinned result or broadcasting: all NCHW
+                        pinned.update(stored)
+                        again = True
+                        break
+                elif t in ("tpu.Pool2D", "tpu.Cast", "tpu.Lut", "tpu.MulShift"):
+                    if stored and name not in pinned:
+                        nhwc.add(name)
+                    elif stored:
+                        pinned.update(stored)
+                        again = True
+                        break
+                elif t.split(".", 1)[-1] in _MOVE_OPS and t.split(".", 1)[-1] != "Depth2Space":
+                    pass                                            # the index-mapping kernel reads either storage order, writes NCHW
+                elif stored and (t in _NCHW_ONLY or t.startswith("top.")):      # these plans read NCHW only
+                    pinned.update(stored)
+                    again = True
+                    break
+            if not again:
+                break
         return nhwc
 
     def _plan(self, op) -> Callable:
