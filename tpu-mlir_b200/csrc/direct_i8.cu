@@ -248,39 +248,56 @@ dwconv_i8_kernel(const uint8_t* __restrict__ x, long long x_bytes, const int8_t*
   }
   const unsigned half_lo = (mode == 2) ? (1u << (sft - 1)) : 0u;
   const int q_lo = e.out_dtype == B200Q_DT_U8 ? 0 : -128, q_hi = e.out_dtype == B200Q_DT_U8 ? 255 : 127;
-  const int floor_q = (e.relu == B200Q_RELU_AFTER_REQUANT && e.out_zp > q_lo) ? e.out_zp : q_lo;
-  const int b_lo = floor_q - e.out_zp, b_hi = q_hi - e.out_zp;      // bounds of the value before the zero point is added
+  const int ozp = e.out_zp;
+  const bool relu_before = e.relu == B200Q_RELU_BEFORE_REQUANT;
+  const int floor_q = (e.relu == B200Q_RELU_AFTER_REQUANT && ozp > q_lo) ? ozp : q_lo;
+  const int b_lo = floor_q - ozp, b_hi = q_hi - ozp;      // bounds of the value before the zero point is added
+  // the form is chosen once per thread, outside the unrolled loops (inside, every output paid its own tests and branches)
+  int q[R][CW];
+  if (mode == 1) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int o = 0; o < CW; ++o) {
+        int a = acc[r][o] + bias;
+        if (relu_before) a = max(a, 0);
+        const int v = (int)(((long long)a * mx + half64) >> 32) >> post;
+        q[r][o] = min(min(max(v, b_lo), b_hi) + ozp, q_hi);      // the last bound acts only when the zero point lies above the type
+      }
+  } else if (mode == 2) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int o = 0; o < CW; ++o) {
+        int a = acc[r][o] + bias;
+        if (relu_before) a = max(a, 0);
+        const int v = rshift_half_up_sat32(a, m, sft, half_lo, 0);
+        q[r][o] = min(min(max(max(min(v, 1 << 24), -(1 << 24)), b_lo), b_hi) + ozp, q_hi);
+      }
+  } else {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int o = 0; o < CW; ++o) {
+        int a = acc[r][o] + bias;
+        if (relu_before) a = max(a, 0);
+        q[r][o] = requant_general(a, m, sft, e);
+      }
+  }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int yo = y0 + r;
     if (yo >= g.oh) break;
-    int q[CW];
-#pragma unroll
-    for (int o = 0; o < CW; ++o) {
-      int a = acc[r][o] + bias;
-      if (e.relu == B200Q_RELU_BEFORE_REQUANT && a < 0) a = 0;
-      if (mode == 1) {
-        const int v = (int)(((long long)a * mx + half64) >> 32) >> post;
-        q[o] = min(max(v, b_lo), b_hi) + e.out_zp;
-        if (q[o] > q_hi) q[o] = q_hi;             // only when the zero point lies above the type's range
-      } else if (mode == 2) {
-        const int v = rshift_half_up_sat32(a, m, sft, half_lo, 0);
-        q[o] = min(max(max(min(v, 1 << 24), -(1 << 24)), b_lo), b_hi) + e.out_zp;
-        if (q[o] > q_hi) q[o] = q_hi;
-      } else {
-        q[o] = requant_general(a, m, sft, e);
-      }
-    }
     const long long at = ((long long)plane * g.oh + yo) * g.ow + x0;
 #pragma unroll
     for (int j = 0; j < CW; j += 4) {
       if (out8 && x0 + j + 3 < g.ow && ((at + j) & 3) == 0) {
-        const uint32_t lo16 = __byte_perm((uint32_t)q[j], (uint32_t)q[j + 1], 0x0040), hi16 = __byte_perm((uint32_t)q[j + 2], (uint32_t)q[j + 3], 0x0040);
+        const uint32_t lo16 = __byte_perm((uint32_t)q[r][j], (uint32_t)q[r][j + 1], 0x0040), hi16 = __byte_perm((uint32_t)q[r][j + 2], (uint32_t)q[r][j + 3], 0x0040);
         reinterpret_cast<uint32_t*>(y)[(at + j) >> 2] = __byte_perm(lo16, hi16, 0x5410);
       } else {
 #pragma unroll
         for (int o = j; o < j + 4; ++o)
-          if (x0 + o < g.ow) st_q(y, at + o, e.out_dtype, q[o]);
+          if (x0 + o < g.ow) st_q(y, at + o, e.out_dtype, q[r][o]);
       }
     }
   }
