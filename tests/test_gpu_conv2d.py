@@ -192,6 +192,35 @@ def test_conv_device_face_matches_operator_face():
     assert np.array_equal(y_d.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("misalign", [0, 1, 3])
+def test_depthwise_device_face_pad_value_and_misaligned_input(misalign):
+    """The depthwise kernel through the device face: unsigned input padded with its zero point (the byte masks' fill value), and
+    an input tensor that does not start on a 4-byte boundary (every patch then takes the byte-wise loop)."""
+    rng = np.random.default_rng(79)
+    C_, H, W = 20, 17, 22
+    x = rng.integers(0, 256, size=(3, C_, H, W)).astype(np.uint8)
+    w = rng.integers(-127, 128, size=(C_, 1, 3, 3), dtype=np.int8)
+    bias = rng.integers(-3000, 3000, size=C_, dtype=np.int32)
+    mult, rshift = rng.integers(2000, 9000, size=C_), rng.integers(17, 21, size=C_)
+    want = oracle.conv2d_int8(x, w, bias, pads=(1, 1, 1, 1), groups=C_, pad_value=131, do_relu=True, qmode=oracle.QM_MULTIPLIER_SHIFT,
+                              mult=mult, rshift=rshift, out_zp=-3)
+    d = Conv2DOp(input_shape=x.shape, oc=C_, kernel_shape=(3, 3), pads=(1, 1, 1, 1), group=C_, pad_value=131, do_relu=True,
+                 input_dtype=L.DT_U8, quant_mode=L.QM_MULTIPLIER_SHIFT, multiplier=mult, rshift=rshift, out_zp=-3).desc
+    buf = torch.zeros(x.size + 8, dtype=torch.uint8, device="cuda")
+    x_d = buf[misalign:misalign + x.size]
+    x_d.copy_(torch.from_numpy(x.reshape(-1)).cuda())
+    assert x_d.data_ptr() % 4 == misalign % 4
+    w_d, b_d = dev(w), dev(bias)
+    y_d = empty_dev(want.shape, L.DT_I8)
+    h = C.c_void_p()
+    lib = L.lib()
+    L.check(lib.b200q_conv2d_dev_create(C.byref(d), ptr(w_d), ptr(b_d), C.byref(h)))
+    L.check(lib.b200q_conv2d_dev_run(h, ptr(x_d), ptr(y_d), None))
+    L.check(lib.b200q_conv2d_dev_status(h, None))
+    lib.b200q_conv2d_dev_destroy(C.byref(h))
+    assert np.array_equal(y_d.cpu().numpy(), want) and len(np.unique(want)) > 40
+
+
 @pytest.mark.parametrize("case", [
     dict(N=2, C=64, H=14, W=14, OC=256, k=1, stride=(1, 1), pads=(0, 0, 0, 0)),     # 1x1: x is read in place
     dict(N=3, C=128, H=13, W=11, OC=80, k=3, stride=(1, 1), pads=(1, 1, 1, 1)),     # 3x3 through the bordered image
