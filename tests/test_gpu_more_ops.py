@@ -682,3 +682,28 @@ def test_inverted_residual_block_against_the_oracle():
         m.check_status()
         for name, w_ in want.items():
             assert np.array_equal(m.get_raw_tensor(name), w_), (name, cl)
+
+
+def test_top_matmul_forms():
+    """top.MatMul with a transposed weight, with a second activation (batched over heads, as in attention), and with a
+    transposed second activation."""
+    rng = np.random.default_rng(24)
+    x = rng.standard_normal((2, 3, 5, 16)).astype(np.float32)
+    wt = rng.standard_normal((24, 16)).astype(np.float32)
+    bias = rng.standard_normal(24).astype(np.float32)
+    k_ = rng.standard_normal((2, 3, 7, 16)).astype(np.float32)       # [.., N, K]: scores = x @ k^T
+    v_ = rng.standard_normal((2, 3, 16, 9)).astype(np.float32)       # [.., K, N]
+    ops = [dict(type="top.MatMul", name="fc", inputs=["x"], attrs=dict(right_transpose=True, do_relu=True)),
+           dict(type="top.MatMul", name="qk", inputs=["x", "k"], attrs=dict(right_transpose=True)),
+           dict(type="top.MatMul", name="xv", inputs=["x", "v"], attrs={})]
+    tensors = {"x": f32(x.shape), "k": f32(k_.shape), "v": f32(v_.shape), "fc": f32((2, 3, 5, 24)), "qk": f32((2, 3, 5, 7)), "xv": f32((2, 3, 5, 9))}
+    g = dict(inputs=["x", "k", "v"], outputs=["fc", "qk", "xv"], tensors=tensors, ops=ops)
+    m = module()
+    m.load(g, {"fc_filter": wt, "fc_bias": bias})
+    for n_, v in (("x", x), ("k", k_), ("v", v_)):
+        m.set_tensor(n_, v)
+    m.invoke(fixed_to_float=False)
+    d = lambda a_: a_.astype(np.float64)  # noqa: E731
+    np.testing.assert_allclose(m.get_tensor("fc"), np.maximum(d(x) @ d(wt).T + bias, 0), rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(m.get_tensor("qk"), d(x) @ d(k_).transpose(0, 1, 3, 2), rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(m.get_tensor("xv"), d(x) @ d(v_), rtol=1e-5, atol=1e-5)

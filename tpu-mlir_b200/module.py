@@ -907,15 +907,62 @@ class module:  # noqa: N801  (name of the reference class)
             self._keep.append((w, b))
             return lambda: L.check(lib.b200q_top_conv2d_dev_run(h, _P(ins[0]), _P(out), n, stream()))
         if t == "top.MatMul":
-            if a.get("right_transpose") or a.get("left_transpose") or a.get("output_transpose") or a.get("hdim_is_batch"):
-                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: top.MatMul with transposes is not implemented")
-            w = self.weights[op["name"] + "_filter"].to(self.torch.float32).contiguous()      # [K, N]
+            # top::MatMulOp (lib/Dialect/Top/Interfaces/MatMul.cpp): a weight or a second activation as the right operand, batched
+            # over the leading dimensions; right_transpose reads it [.., N, K].  One launch of the fp32 kernel per batch entry.
+            if a.get("left_transpose") or a.get("output_transpose") or a.get("hdim_is_batch"):
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: top.MatMul with left / output transposes is not implemented")
+            rt = bool(a.get("right_transpose", False))
             b = self.weights.get(op["name"] + "_bias")
             b = b.to(self.torch.float32).contiguous() if b is not None else None
-            K, N = w.shape
-            M = ins[0].numel() // K
-            self._keep.append((w, b))
-            return lambda: L.check(lib.b200q_top_matmul_f32_dev(_P(ins[0]), _P(w), _P(b), _P(out), M, K, N, relu, limit, stream()))
+            if len(ins) == 1:
+                w = self.weights[op["name"] + "_filter"].to(self.torch.float32)
+                w = (w.transpose(-1, -2) if rt else w).contiguous()      # [K, N]
+                K, N = w.shape[-2], w.shape[-1]
+                M = ins[0].numel() // K
+                self._keep.append((w, b))
+                return lambda: L.check(lib.b200q_top_matmul_f32_dev(_P(ins[0]), _P(w), _P(b), _P(out), M, K, N, relu, limit, stream()))
+            ls, rs = list(iinfo[0]["shape"]), list(iinfo[1]["shape"])
+            if len(rs) < 2 or len(ls) < 2 or op["inputs"][0] in self._nhwc or op["inputs"][1] in self._nhwc:
+                raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: top.MatMul operands must be NCHW tensors of rank two or more")
+            K, N = (rs[-1], rs[-2]) if rt else (rs[-2], rs[-1])
+            M = ls[-2]
+            rb, lb = int(np.prod(rs[:-2])), int(np.prod(ls[:-2]))
+            if ls[-1] != K or rb not in (1, lb):
+                raise L.B200QError(L.ERR_INVALID, f"{op['name']}: top.MatMul shapes {ls} x {rs} do not match")
+            if rb == 1 and not rt:          # a shared right operand folds the batch into M
+                M, lb = M * lb, 1
+            right = ins[1]
+            # the kernel wants 16-byte aligned operands: a batch entry whose size is not a multiple of four floats is staged
+            # through a buffer with a padded pitch
+            pad4 = lambda v: (v + 3) // 4 * 4  # noqa: E731
+            px, pr, po = pad4(M * K), pad4(K * N), pad4(M * N)
+            torch = self.torch
+            xs = torch.empty(lb * px, dtype=torch.float32, device=self.device) if px != M * K and lb > 1 else None
+            rsb = torch.empty(rb * pr, dtype=torch.float32, device=self.device) if (rt or (pr != K * N and rb > 1)) else None
+            os_ = torch.empty(lb * po, dtype=torch.float32, device=self.device) if po != M * N and lb > 1 else None
+            self._keep.append((b, xs, rsb, os_))
+            xin, yout = ins[0], out
+
+            def run_matmul():
+                x0, sx = xin.data_ptr(), M * K
+                if xs is not None:
+                    xs.view(lb, px)[:, :M * K].copy_(xin.reshape(lb, M * K))
+                    x0, sx = xs.data_ptr(), px
+                r0, sr = right.data_ptr(), K * N
+                if rsb is not None:      # [.., N, K] -> [.., K, N] when transposed, at the padded pitch
+                    src = right.reshape(rb, N, K).transpose(1, 2) if rt else right.reshape(rb, K, N)
+                    rsb.view(rb, pr)[:, :K * N].view(rb, K, N).copy_(src) if pr == K * N else \
+                        rsb.view(rb, pr)[:, :K * N].copy_(src.reshape(rb, K * N))
+                    r0, sr = rsb.data_ptr(), pr
+                y0, so = yout.data_ptr(), M * N
+                if os_ is not None:
+                    y0, so = os_.data_ptr(), po
+                for i in range(lb):
+                    L.check(lib.b200q_top_matmul_f32_dev(C.c_void_p(x0 + 4 * i * sx), C.c_void_p(r0 + 4 * (i if rb > 1 else 0) * sr), _P(b),
+                                                         C.c_void_p(y0 + 4 * i * so), M, K, N, relu, limit, stream()))
+                if os_ is not None:
+                    yout.view(lb, M * N).copy_(os_.view(lb, po)[:, :M * N])
+            return run_matmul
         if t == "top.Add":
             if len(ins) != 2 or tuple(iinfo[0]["shape"]) != tuple(iinfo[1]["shape"]):
                 raise L.B200QError(L.ERR_UNSUPPORTED, f"{op['name']}: top.Add takes two tensors of one shape here")
