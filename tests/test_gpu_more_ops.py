@@ -707,3 +707,47 @@ def test_top_matmul_forms():
     np.testing.assert_allclose(m.get_tensor("fc"), np.maximum(d(x) @ d(wt).T + bias, 0), rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(m.get_tensor("qk"), d(x) @ d(k_).transpose(0, 1, 3, 2), rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(m.get_tensor("xv"), d(x) @ d(v_), rtol=1e-5, atol=1e-5)
+
+
+def test_float_attention_block():
+    """A ViT-style attention block in the Top dialect through the executor (LayerNorm, weight and activation MatMuls, Reshape,
+    Permute, MulConst, Softmax, Add, GELU) against numpy in float64: the float graph a calibration of such a model runs."""
+    rng = np.random.default_rng(25)
+    B, T, D, Hh = 2, 10, 32, 4
+    dh = D // Hh
+    x = rng.standard_normal((B, T, D)).astype(np.float32)
+    W = {k: (rng.standard_normal((D, D)) * 0.2).astype(np.float32) for k in "qkvo"}
+    lw, lb = (rng.standard_normal(D) * 0.1 + 1).astype(np.float32), (rng.standard_normal(D) * 0.1).astype(np.float32)
+    heads = lambda n_: [dict(type="top.Reshape", name=n_ + "r", inputs=[n_], attrs={}),  # noqa: E731
+                        dict(type="top.Permute", name=n_ + "h", inputs=[n_ + "r"], attrs=dict(order=[0, 2, 1, 3]))]
+    ops = [dict(type="top.LayerNorm", name="ln", inputs=["x"], attrs=dict(axis=2, eps=1e-5)),
+           dict(type="top.MatMul", name="q", inputs=["ln"], attrs={}), dict(type="top.MatMul", name="k", inputs=["ln"], attrs={}),
+           dict(type="top.MatMul", name="v", inputs=["ln"], attrs={})] + heads("q") + heads("k") + heads("v") + [
+           dict(type="top.MatMul", name="s", inputs=["qh", "kh"], attrs=dict(right_transpose=True)),
+           dict(type="top.MulConst", name="ss", inputs=["s"], attrs=dict(const_val=1.0 / math.sqrt(dh))),
+           dict(type="top.Softmax", name="p", inputs=["ss"], attrs=dict(axis=3)),
+           dict(type="top.MatMul", name="a", inputs=["p", "vh"], attrs={}),
+           dict(type="top.Permute", name="ap", inputs=["a"], attrs=dict(order=[0, 2, 1, 3])),
+           dict(type="top.Reshape", name="ar", inputs=["ap"], attrs={}),
+           dict(type="top.MatMul", name="o", inputs=["ar"], attrs={}),
+           dict(type="top.Add", name="res", inputs=["x", "o"], attrs={}),
+           dict(type="top.GELU", name="y", inputs=["res"], attrs={})]
+    t3, t4, th = f32((B, T, D)), f32((B, T, Hh, dh)), f32((B, Hh, T, dh))
+    tensors = {"x": t3, "ln": t3, "q": t3, "k": t3, "v": t3, "qr": t4, "kr": t4, "vr": t4, "qh": th, "kh": th, "vh": th, "s": f32((B, Hh, T, T)),
+               "ss": f32((B, Hh, T, T)), "p": f32((B, Hh, T, T)), "a": th, "ap": t4, "ar": t3, "o": t3, "res": t3, "y": t3}
+    weights = {"ln_weight": lw, "ln_bias": lb, "q_filter": W["q"], "k_filter": W["k"], "v_filter": W["v"], "o_filter": W["o"]}
+    m = run_graph(tensors, ops, weights, {"x": x})
+    d = lambda a_: np.asarray(a_, dtype=np.float64)  # noqa: E731
+    xd = d(x)
+    mu = xd.mean(axis=2, keepdims=True)
+    ln = (xd - mu) / np.sqrt(((xd - mu) ** 2).mean(axis=2, keepdims=True) + 1e-5) * d(lw) + d(lb)
+    split = lambda t: t.reshape(B, T, Hh, dh).transpose(0, 2, 1, 3)  # noqa: E731
+    q_, k_, v_ = (split(ln @ d(W[c])) for c in "qkv")
+    sc = q_ @ k_.transpose(0, 1, 3, 2) / math.sqrt(dh)
+    e_ = np.exp(sc - sc.max(axis=3, keepdims=True))
+    p_ = e_ / e_.sum(axis=3, keepdims=True)
+    o_ = (p_ @ v_).transpose(0, 2, 1, 3).reshape(B, T, D) @ d(W["o"])
+    res = xd + o_
+    want = 0.5 * res * (1 + np.vectorize(math.erf)(res / math.sqrt(2.0)))
+    np.testing.assert_allclose(m.get_tensor("p"), p_, rtol=2e-4, atol=1e-6)
+    np.testing.assert_allclose(m.get_tensor("y"), want, rtol=2e-4, atol=2e-5)
