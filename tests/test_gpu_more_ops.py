@@ -751,3 +751,29 @@ def test_float_attention_block():
     want = 0.5 * res * (1 + np.vectorize(math.erf)(res / math.sqrt(2.0)))
     np.testing.assert_allclose(m.get_tensor("p"), p_, rtol=2e-4, atol=1e-6)
     np.testing.assert_allclose(m.get_tensor("y"), want, rtol=2e-4, atol=2e-5)
+
+
+def test_run_calibration_on_a_float_graph(tmp_path):
+    """run_calibration (the reference's tool flow) on a small float graph: table written in the reference's format, thresholds
+    within (0, abs max], the min / max columns equal to numpy's over the same samples, tuning only ever raises a threshold."""
+    from tpu_mlir_b200.cali_table import read_cali_table
+    from tpu_mlir_b200.run_calibration import run_calibration
+    rng = np.random.default_rng(26)
+    B, Cc, H = 4, 8, 6
+    w1 = (rng.standard_normal((16, Cc, 3, 3)) * 0.2).astype(np.float32)
+    ops = [dict(type="top.Conv", name="c1", inputs=["x"], attrs=dict(kernel_shape=[3, 3], pads=[1, 1, 1, 1], do_relu=True)),
+           dict(type="top.MaxPool", name="p1", inputs=["c1"], attrs=dict(kernel_shape=[2, 2], strides=[2, 2])),
+           dict(type="top.Sigmoid", name="s1", inputs=["p1"], attrs={})]
+    tensors = {"x": f32((B, Cc, H, H)), "c1": f32((B, 16, H, H)), "p1": f32((B, 16, 3, 3)), "s1": f32((B, 16, 3, 3))}
+    g = dict(inputs=["x"], outputs=["s1"], tensors=tensors, ops=ops)
+    samples = rng.standard_normal((16, Cc, H, H)).astype(np.float32)
+    path = str(tmp_path / "cali_table")
+    th = run_calibration(g, {"c1_filter": w1}, samples, out_table=path)
+    table = read_cali_table(path)
+    assert set(th) == {"x", "c1", "p1", "s1"} and list(table.int8) == ["x", "c1", "p1", "s1"]
+    assert all(0 < v for v in th.values()) and th["x"] <= float(np.abs(samples).max()) + 1e-6
+    assert abs(table.int8["x"][1] - float(samples.min())) < 1e-5 and abs(table.int8["x"][2] - float(samples.max())) < 1e-5
+    assert all(abs(table.int8[n][0] - th[n]) < 1e-6 for n in th)
+    assert table.int8["s1"][1] >= 0.5 - 1e-6 and table.int8["s1"][2] <= 1.0 + 1e-6          # a sigmoid of ReLU'd values
+    tuned = run_calibration(g, {"c1_filter": w1}, samples, tune_num=2)
+    assert all(tuned[n] >= th[n] - 1e-7 for n in th)
