@@ -11,6 +11,7 @@
 //   lib/Support/ActiveUtils.cpp:16-149                             the activation helpers and getActivateFunc(mode, coeffs)
 //   lib/Support/MathUtils.cpp:673-705,:1539-1564                   pad_tensor_for_deconv, swap_dim_data
 //   include/tpu_mlir/Support/MathUtils.h:213-228                   tensor_hc_transpose
+//   lib/Dialect/Top/Interfaces/Pad.cpp:121-213                     the reflect / edge loops of top.Pad
 // This file supplies what those bodies expect from the rest of the reference (the ActiveMode enumeration with the
 // dialect's numbering, two typedefs, llvm_unreachable) and plain C entry points.
 #include <algorithm>
@@ -256,6 +257,17 @@ void ref_arg(float* x, float* indices, float* values, int rank, const int64_t* s
 
 void ref_gather_elements(float* dst, const float* src, const float* indices, const int* indices_shape, int* src_shape, int rank, int axis) {
   gather_dim8(dst, src, indices, indices_shape, src_shape, rank, axis, rank);
+}
+
+// top::PadOp::inference, modes "reflect" and "edge" (Pad.cpp:121-213) on a 4-D tensor padded in its last two dimensions
+void ref_pad_mode(const float* src, float* dst, int n_, int c_, int h_, int w_, int pt, int pl, int pb, int pr, const char* mode) {
+  const int64_t in = n_, ic = c_, ih = h_, iw = w_;
+  std::vector<int> pads = {0, 0, pt, pl, 0, 0, pb, pr};
+  const int64_t oc = ic, oh = pt + pb + ih, ow = pl + pr + iw;
+  const std::string pad_mode = mode;
+#define UNREACHABLE_THIS(msg) abort()
+#include "_ref/pad_modes.inc"
+#undef UNREACHABLE_THIS
 }
 
 }  // extern "C"

@@ -252,3 +252,16 @@ def test_subconst_and_top_cast_expressions(loops):
                            (b"UINT16", 8, np.clip(np.ceil(v), 0, 65535)), (b"INT32", 6, np.trunc(v)), (b"F32", 0, v)):
         loops.ref_top_cast(fp(v), fp(out), v.size, to, rm)
         assert np.array_equal(out, expect.astype(np.float32)), to
+
+
+@pytest.mark.parametrize("mode", ["reflect", "edge"])
+def test_pad_modes_are_numpy_pads(ref, mode):
+    """top.Pad's reflect / edge loops (Pad.cpp:121-213) against numpy.pad, which the GPU test holds the executor to."""
+    if not hasattr(ref, "ref_pad_mode"):
+        pytest.skip("an older moreops_ref.so")
+    rng = np.random.default_rng(13)
+    for (h, w, pt, pl, pb, pr) in ((5, 6, 2, 1, 3, 4), (4, 4, 1, 3, 1, 0), (3, 7, 0, 0, 2, 2)):
+        x = rng.standard_normal((2, 3, h, w)).astype(np.float32)
+        want = np.zeros((2, 3, h + pt + pb, w + pl + pr), np.float32)
+        ref.ref_pad_mode(fp(x), fp(want), 2, 3, h, w, pt, pl, pb, pr, mode.encode())
+        assert np.array_equal(np.pad(x, ((0, 0), (0, 0), (pt, pb), (pl, pr)), mode=mode), want)
