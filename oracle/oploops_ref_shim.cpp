@@ -18,6 +18,8 @@
 //   lib/Dialect/Tpu/Interfaces/Common/MaxConst.cpp:36-45, MinConst.cpp:36-45   the uniform-quantized loops
 //   lib/Dialect/Tpu/Interfaces/Common/PRelu.cpp:73-96              the symmetric 8-bit loop of tpu.PRelu
 //   lib/Dialect/Tpu/Interfaces/Common/SubConst.cpp:19-111          tpu.SubConst::inference, whole body
+//   lib/Dialect/Tpu/Interfaces/Common/Sub.cpp:160-185              tpu.Sub, symmetric int8, BM168x
+//   lib/Dialect/Tpu/Interfaces/Common/Reduce.cpp:206-213           the requantisation tail of tpu.Reduce
 //   include/tpu_mlir/Support/MathUtils.h:311-337, lib/Dialect/Top/Interfaces/Cast.cpp:18-64   to_int8 ... to_uint16; top.Cast::inference, whole body
 // This file supplies only what those bodies expect from the rest of the reference: the operator's attribute
 // accessors (answered from a context the C entry points fill), the shapes, a stand-in for mlir::Type that knows a
@@ -146,6 +148,7 @@ static i64_array_t getI64Array(const std::optional<std::vector<int64_t>>& a, int
   }
   return std::make_shared<std::vector<int64_t>>(num_elem, default_value);
 }
+static i64_array_t getI64Array(const std::optional<std::vector<int64_t>>& a) { return std::make_shared<std::vector<int64_t>>(*a); }
 static f64_array_t getF64Array(const std::vector<double>& a) { return std::make_shared<std::vector<double>>(a); }
 }  // namespace module
 using module::f64_array_t;
@@ -212,7 +215,7 @@ struct Binary {
   const float *l = nullptr, *r = nullptr;
   float* dst = nullptr;
   int64_t count = 0;
-  bool relu = false;
+  bool relu = false, sub = false;
   Binary& lhs(const float* p, const std::vector<int64_t>&) {
     l = p;
     return *this;
@@ -223,7 +226,7 @@ struct Binary {
   }
   void run() {
     for (int64_t i = 0; i < count; ++i) {
-      float v = l[i] + r[i];
+      float v = sub ? l[i] - r[i] : l[i] + r[i];
       dst[i] = relu && v < 0.f ? 0.f : v;
     }
   }
@@ -344,6 +347,25 @@ static int top_cast(InferenceParameter& p) {
   auto round_mode_convert = [](const std::string&) { return (RoundingMode)g.round_mode; };
   auto getTo = [] { return g_cast_to; };
 #include "_ref/top_cast.inc"
+}
+
+// ---------------------------------------------------------------------------------------------- tpu.Sub (int8), tpu.Reduce tail
+static void sub_int8(InferenceParameter& p, int64_t num_elem) {
+  auto out_type = g.out_type;
+  {
+#include "_ref/sub_int8.inc"
+  }
+}
+struct OptArr {
+  std::optional<std::vector<int64_t>> a;
+  const std::optional<std::vector<int64_t>>& value() const { return a; }
+};
+static void reduce_tail(float* output_v, size_t num_elem, int64_t multiplier, int64_t rshift) {
+  auto getRshift = [&] { return OptArr{std::vector<int64_t>{rshift}}; };
+  auto getMultiplier = [&] { return OptArr{std::vector<int64_t>{multiplier}}; };
+  {
+#include "_ref/reduce_tail.inc"
+  }
 }
 
 // ---------------------------------------------------------------------------------------------- C entry points
@@ -566,5 +588,26 @@ void ref_top_cast(float* x, float* y, long long n, const char* to, int round_mod
   p.outputs = {y};
   top_cast(p);
 }
+
+void ref_sub_int8(const float* a, const float* b, float* out, long long count, long long m0, long long s0, long long m1, long long s1,
+                  int do_relu, int out_width, int out_unsigned) {
+  g = Ctx();
+  g.multipliers = std::vector<int64_t>{m0, m1};
+  g.rshifts = std::vector<int64_t>{s0, s1};
+  g.out_shape = {count};
+  set_out_type(out_width, out_unsigned);
+  Binary bin;
+  bin.dst = out;
+  bin.count = count;
+  bin.relu = do_relu != 0;
+  bin.sub = true;
+  InferenceParameter p;
+  p.inputs = {const_cast<float*>(a), const_cast<float*>(b)};
+  p.outputs = {out};
+  p.handle = &bin;
+  sub_int8(p, count);
+}
+
+void ref_reduce_tail(float* values, long long count, long long multiplier, long long rshift) { reduce_tail(values, (size_t)count, multiplier, rshift); }
 
 }  // extern "C"

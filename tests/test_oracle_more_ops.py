@@ -265,3 +265,29 @@ def test_pad_modes_are_numpy_pads(ref, mode):
         want = np.zeros((2, 3, h + pt + pb, w + pl + pr), np.float32)
         ref.ref_pad_mode(fp(x), fp(want), 2, 3, h, w, pt, pl, pb, pr, mode.encode())
         assert np.array_equal(np.pad(x, ((0, 0), (0, 0), (pt, pb), (pl, pr)), mode=mode), want)
+
+
+def test_sub_int8_and_reduce_tail_expressions(loops):
+    """tpu.Sub's symmetric int8 branch (Sub.cpp:160-185) and the requantisation tail of tpu.Reduce (Reduce.cpp:206-213)."""
+    if not hasattr(loops, "ref_sub_int8"):
+        pytest.skip("an older oploops_ref.so")
+    loops.ref_sub_int8.argtypes = [C.POINTER(C.c_float)] * 3 + [C.c_longlong] * 5 + [C.c_int] * 3
+    loops.ref_reduce_tail.argtypes = [C.POINTER(C.c_float)] + [C.c_longlong] * 3
+    rng = np.random.default_rng(14)
+    a_ = rng.integers(-128, 128, 4000).astype(np.float32)
+    b_ = rng.integers(-128, 128, 4000).astype(np.float32)
+    want = np.zeros_like(a_)
+    loops.ref_sub_int8(fp(a_), fp(b_), fp(want), a_.size, 90, 7, 70, 6, 0, 8, 0)
+    diff = ((a_.astype(np.int64) * 90 + 64) >> 7) - ((b_.astype(np.int64) * 70 + 32) >> 6)
+    assert np.array_equal(np.clip(diff, -128, 127).astype(np.float32), want)
+    loops.ref_sub_int8(fp(a_), fp(b_), fp(want), a_.size, 90, 7, 70, 6, 1, 8, 0)
+    assert np.array_equal(np.clip(np.maximum(diff, 0), -128, 127).astype(np.float32), want)
+    # the mean of int8 values as the float loop leaves it (sum * float(1 / n)), then cut, multiplied, shifted, saturated to int8
+    q = rng.integers(-128, 128, (300, 7)).astype(np.float32)
+    ssum = np.zeros(300, np.float32)
+    for k in range(7):
+        ssum = ssum + q[:, k]
+    vals = (ssum * np.float32(1.0 / 7)).astype(np.float32)
+    got = np.clip((np.trunc(vals).astype(np.int64) * 77 + 32) >> 6, -128, 127).astype(np.float32)
+    loops.ref_reduce_tail(fp(vals), vals.size, 77, 6)
+    assert np.array_equal(got, vals)
